@@ -1,0 +1,159 @@
+/* blr_b200.h -- C ABI of the B200 (sm_100a) structured-matmul library.
+ *
+ * The reference project (pabillam/mem-efficient-blr) has no native interface: its operator API is a
+ * set of Python free functions, picked by dotted name from YAML (layer.py:30-38,
+ * models/wrappers.py:143-146).  Each entry point below is what a binding for one family of those
+ * functions calls; the comment above it names the reference functions it stands in for.
+ *
+ * Conventions
+ *   - All pointers are device pointers unless stated otherwise.  Nothing here allocates device memory;
+ *     scratch comes from the caller (`ws`, sized by blr_workspace_bytes).
+ *   - `stream` is a cudaStream_t passed as void*.  Calls enqueue work and return; they never
+ *     synchronise the host.  Calls that share a workspace must be ordered on one stream.
+ *   - `dtype` selects the 16-bit type of x, the 16-bit factors and out.
+ *   - x is (N, in_features) with row stride `ldx` elements; out is (N, out_features) with row stride
+ *     `ldo` elements.  Input feature j*P+p belongs to input block j; output feature i*Q+q to block i.
+ *   - Weight layouts: BLR_W_KMAJOR = [block][out_row][k] (contraction index contiguous, the
+ *     reference's torch layouts); BLR_W_MMAJOR = [block][k][out_row] (output index contiguous, the
+ *     layouts of the reference's Triton entry points).
+ *   - Return value: 0 on success, a negative BLR_ERR_* code otherwise; blr_last_error() has the text.
+ *     Token counts up to 16 run one weight-streaming kernel; larger counts run the tensor-core pipeline.
+ */
+#ifndef BLR_B200_H_
+#define BLR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BLR_DTYPE_F16 0
+#define BLR_DTYPE_BF16 1
+
+#define BLR_W_KMAJOR 0
+#define BLR_W_MMAJOR 1
+
+/* Column order of Monarch's first factor. TORCH: column c of block k feeds out1[c % b][k*per + c / b]
+ * (torch_funcs/monarch_funcs.py:41).  GROUPED: column l*per + jj feeds out1[l][k*per + jj]
+ * (the regrouping the reference's harness applies for its kernels, layer.py:221-224). */
+#define BLR_MONARCH_COLS_TORCH 0
+#define BLR_MONARCH_COLS_GROUPED 1
+
+/* Output feature order of Monarch. INTERLEAVED: s*b + l (monarch_funcs.py:44);
+ * BLOCKED: l*S + s (triton_monarch_right_ideal, monarch_kernels.py:1004). */
+#define BLR_OUT_INTERLEAVED 0
+#define BLR_OUT_BLOCKED 1
+
+#define BLR_FLAG_NONE 0
+/* Round both BLAST intermediates to the nearest integer in [-128, 127], no scale: the semantics of
+ * triton_blast_bmm_int8_fp16 (blast_sym_quant_kernels.py:105-108, 227-230). */
+#define BLR_FLAG_ACT_INT8 1
+
+#define BLR_OK 0
+#define BLR_ERR_ARG (-1)
+#define BLR_ERR_SHAPE (-2)
+#define BLR_ERR_ALIGN (-3)
+#define BLR_ERR_WORKSPACE (-4)
+#define BLR_ERR_CUDA (-5)
+#define BLR_ERR_UNSUPPORTED (-6)
+#define BLR_ERR_TIMEOUT (-7)
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int blr_version(void);
+
+/* Text of the last error on the calling thread. No reference counterpart (the reference raises
+ * Python AssertionError, e.g. blast_kernels.py:1951-1955). */
+const char* blr_last_error(void);
+
+/* Bytes of scratch a call needs: `groups` blocks, `width` intermediate features per block, N tokens
+ * (BLAST: b, R; Monarch: b, rank; low-rank: 1, R; dense: 0, 0).  No reference counterpart: the
+ * reference allocates its intermediates with torch.empty per call (blast_kernels.py:1967, 2703). */
+size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width);
+
+/* Zeroes the control words at the start of a workspace.  Required once after allocation and after
+ * a call reported BLR_ERR_TIMEOUT through blr_workspace_status. No reference counterpart. */
+int blr_workspace_init(void* ws, size_t ws_bytes, void* stream);
+
+/* Reads the status word of a workspace (synchronises `stream`): 0, or BLR_ERR_TIMEOUT if a kernel
+ * gave up on a device-side wait. No reference counterpart. */
+int blr_workspace_status(const void* ws, void* stream);
+
+/* BLAST: y_j = x_j V_j^T ; z_i = sum_j S_ij (.) y_j ; out_i = z_i U_i^T.
+ * Replaces torch_blast_baseline / torch_blast_bmm (torch_funcs/blast_funcs.py:3-47, 49-91) and
+ * triton_blast_{partial,partial_grouped,partial_grouped_persistent,full,bmm}_fp16
+ * (triton_funcs/blast_kernels.py:2666-2707, 2762-2803, 2858-2899, 2955-2995, 3043-3065), and with
+ * BLR_FLAG_ACT_INT8 triton_blast_bmm_int8_fp16 (blast_sym_quant_kernels.py:558-580).
+ * U: b blocks of Q rows x R; V: b blocks of R rows x P; S element (i, j, r) at i*s_i + j*s_j + r*s_r. */
+int blr_blast(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+              const void* U, int u_layout, const void* V, int v_layout,
+              const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+              int b, int P, int Q, int R, int flags,
+              void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
+
+/* BLAST with int8 / packed-int4 factors and fp16 scales.  No reference counterpart (the reference's
+ * sym-quant kernels round activations, not weights); the format is: Uq int8 (b,Q,R) or uint8 (b,Q,R/2),
+ * Vq int8 (b,R,P) or uint8 (b,R,P/2), contraction index contiguous, two int4 per byte with the even
+ * index in the low nibble; u_scale fp16 (b,Q), v_scale fp16 (b,R); weight = q * scale.
+ * `group` must be 0 (one scale per output channel). */
+int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+                 const void* Uq, const void* u_scale, const void* Vq, const void* v_scale,
+                 const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                 int bits, int group, int b, int P, int Q, int R,
+                 void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
+
+/* Monarch: block-diagonal w1, permutation, block-diagonal w2.
+ * Replaces torch_monarch_baseline (torch_funcs/monarch_funcs.py:4-45) and
+ * triton_monarch_{right,right_ideal,right_left}_fp16 (triton_funcs/monarch_kernels.py:869-909,
+ * 961-1005, 1060-1099).  w1: b blocks, `rank` outputs each over P inputs; w2: b blocks, Qs outputs
+ * each over `rank` inputs. */
+int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+                const void* w1, int w1_layout, int w1_cols, const void* w2, int w2_layout,
+                int b, int P, int rank, int Qs, int out_order,
+                void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
+
+/* Low rank: out = (x V^T) U^T.  Replaces torch_low_rank_baseline (torch_funcs/low_rank_funcs.py:4-28)
+ * and triton_low_rank_fp16 (triton_funcs/low_rank_kernels.py:410-417).  V: R x I, U: O x R. */
+int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+                 const void* V, int v_layout, const void* U, int u_layout,
+                 int I, int R, int O,
+                 void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
+
+/* Dense: out = x W^T.  Replaces torch_dense_baseline (torch_funcs/dense_funcs.py:4-25) and
+ * triton_dense_fp16 (triton_funcs/dense_kernels.py:375-381).  W: O x I. */
+int blr_dense(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+              const void* W, int w_layout, int I, int O,
+              void* out, int64_t ldo, void* stream);
+
+/* fp32 verification variants: exact fp32 FMA arithmetic, intermediates returned.
+ * Replace triton_blast_*_fp32 (blast_kernels.py:2614-2664 ... 2998-3041; out, z (b,N,R), y (b,N,R)),
+ * triton_monarch_*_fp32 (monarch_kernels.py:823-867, 911-959, 1007-1058; out, out1 (b,N,rank)),
+ * triton_low_rank_fp32 (low_rank_kernels.py:394-408; out, z (N,R)) and
+ * triton_dense_fp32 (dense_kernels.py:360-373).  All tensors fp32 and dense row-major; the
+ * intermediates y, z, out1 are caller-provided outputs and must not be NULL. */
+int blr_blast_f32(const float* x, int64_t ldx, int64_t n_tokens,
+                  const float* U, int u_layout, const float* V, int v_layout,
+                  const float* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                  int b, int P, int Q, int R,
+                  float* out, int64_t ldo, float* z, float* y, void* stream);
+int blr_monarch_f32(const float* x, int64_t ldx, int64_t n_tokens,
+                    const float* w1, int w1_layout, int w1_cols, const float* w2, int w2_layout,
+                    int b, int P, int rank, int Qs, int out_order,
+                    float* out, int64_t ldo, float* out1, void* stream);
+int blr_low_rank_f32(const float* x, int64_t ldx, int64_t n_tokens,
+                     const float* V, int v_layout, const float* U, int u_layout,
+                     int I, int R, int O, float* out, int64_t ldo, float* z, void* stream);
+int blr_dense_f32(const float* x, int64_t ldx, int64_t n_tokens,
+                  const float* W, int w_layout, int I, int O, float* out, int64_t ldo, void* stream);
+
+/* Symmetric weight quantiser (device): w (rows, K) 16-bit, contraction index contiguous ->
+ * q int8 (rows, K) or packed uint8 (rows, K/2) and scale fp16 (rows) = max|w| / (127 | 7).
+ * No reference counterpart. */
+int blr_quantize_sym(const void* w, int dtype, int64_t rows, int64_t K, int bits,
+                     void* q, void* scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLR_B200_H_ */

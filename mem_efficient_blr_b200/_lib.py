@@ -1,0 +1,115 @@
+"""ctypes binding of libblr_b200.so (the C ABI in include/blr_b200.h) plus workspace handling."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libblr_b200.so")
+
+F16, BF16 = 0, 1
+KMAJOR, MMAJOR = 0, 1
+COLS_TORCH, COLS_GROUPED = 0, 1
+OUT_INTERLEAVED, OUT_BLOCKED = 0, 1
+FLAG_NONE, FLAG_ACT_INT8 = 0, 1
+STREAM_MAX_TOKENS = 16
+
+_i64, _int, _vp, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
+
+# name -> (restype, argtypes); must list every symbol include/blr_b200.h declares
+SIGNATURES = {
+    "blr_version": (_int, []),
+    "blr_last_error": (C.c_char_p, []),
+    "blr_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "blr_workspace_init": (_int, [_vp, _sz, _vp]),
+    "blr_workspace_status": (_int, [_vp, _vp]),
+    "blr_blast": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
+                         _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
+    "blr_blast_wq": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                            _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
+    "blr_monarch": (_int, [_vp, _i64, _i64, _int, _vp, _int, _int, _vp, _int,
+                           _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
+    "blr_low_rank": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _int, _int, _int,
+                            _vp, _i64, _vp, _sz, _vp]),
+    "blr_dense": (_int, [_vp, _i64, _i64, _int, _vp, _int, _int, _int, _vp, _i64, _vp]),
+    "blr_blast_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
+                             _int, _int, _int, _int, _vp, _i64, _vp, _vp, _vp]),
+    "blr_monarch_f32": (_int, [_vp, _i64, _i64, _vp, _int, _int, _vp, _int,
+                               _int, _int, _int, _int, _int, _vp, _i64, _vp, _vp]),
+    "blr_low_rank_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _int, _int, _int, _int, _vp, _i64, _vp, _vp]),
+    "blr_dense_f32": (_int, [_vp, _i64, _i64, _vp, _int, _int, _int, _vp, _i64, _vp]),
+    "blr_quantize_sym": (_int, [_vp, _int, _i64, _i64, _int, _vp, _vp, _vp]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> C.CDLL:
+    """Loads the shared library; raises if it has not been built (there is no fallback path)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(
+                    f"{LIB_PATH} is missing: build it with `python -m mem_efficient_blr_b200.build` "
+                    "(needs nvcc); this package has no CPU or Triton fallback")
+            lib = C.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = load().blr_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"blr_b200 error {rc}: {msg}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return F16
+    if dt == torch.bfloat16:
+        return BF16
+    raise AssertionError(f"expected float16 or bfloat16 tensors, got {dt}")
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# ----------------------------------------------------------------------------- workspaces
+# One scratch buffer per (device, stream): calls that share a workspace must be ordered on one stream.
+_workspaces: dict = {}
+
+
+def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        cap = max(nbytes, 1 << 20)
+        if ws is not None:
+            cap = max(cap, 2 * ws.numel())
+        ws = torch.empty(cap, dtype=torch.uint8, device=device)
+        check(load().blr_workspace_init(ws.data_ptr(), ws.numel(), stream))
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_status(device: torch.device) -> None:
+    """Raises if a kernel that used this device's current-stream workspace reported a timed-out wait."""
+    st = stream_ptr(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), st)
+    ws = _workspaces.get(key)
+    if ws is not None:
+        rc = load().blr_workspace_status(ws.data_ptr(), st)
+        if rc != 0:
+            load().blr_workspace_init(ws.data_ptr(), ws.numel(), st)
+            check(rc)

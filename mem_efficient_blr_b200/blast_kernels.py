@@ -1,0 +1,147 @@
+"""BLAST operators with the reference's names and argument layouts (triton_funcs/blast_kernels.py).
+
+Layouts per family (models/wrappers.py:151-163, layer.py:191-201):
+  partial / partial_grouped / partial_grouped_persistent / full:
+      U (b, R, Q)   V (b, P, R)   S (b_in, b_out, R)
+  bmm:
+      U (b, Q, R)   V (b, P, R)   S (R, b_out, b_in)
+The ``_fp16`` functions take 16-bit tensors (bfloat16 like the reference, or float16), return the
+output only and accept the reference's optional trailing ``config`` (ignored: there is nothing to
+autotune at run time).  The ``_fp32`` functions take float32 tensors and return ``(out, z, y)``.
+All five families run the same CUDA path; the reference's distinction between them was how far its
+Triton kernels managed to fuse (blast_kernels.py:1124-1125).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+
+def _dims_partial(x, U, V, S):
+    b1, p, r = V.shape
+    b2, r2, q = U.shape
+    assert b1 == b2, "b1 must equal b2"
+    assert b1 != 1 and b2 != 1, "b must not be 1"
+    assert r2 == r and tuple(S.shape) == (b1, b2, r), "inconsistent factor shapes"
+    assert x.shape[-1] == b1 * p, "x last dim must be b*P"
+    assert U.is_contiguous() and V.is_contiguous() and S.is_contiguous()
+    return b1, p, q, r
+
+
+def _dims_bmm(x, U, V, S):
+    b1, p, r = V.shape
+    b2, q, r2 = U.shape
+    assert b1 == b2, "b1 must equal b2"
+    assert b1 != 1 and b2 != 1, "b must not be 1"
+    assert r2 == r and tuple(S.shape) == (r, b2, b1), "inconsistent factor shapes"
+    assert x.shape[-1] == b1 * p, "x last dim must be b*P"
+    assert U.is_contiguous() and V.is_contiguous() and S.is_contiguous()
+    return b1, p, q, r
+
+
+def _partial_fp16(x, U, V, S, flags=L.FLAG_NONE):
+    b, p, q, r = _dims_partial(x, U, V, S)
+    out = ops.blast_op(ops._flat2d(x), U, V, S, L.MMAJOR, L.MMAJOR, r, b * r, 1, b, p, q, r, flags)
+    return out.reshape(*x.shape[:-1], b * q)
+
+
+def _partial_fp32(x, U, V, S):
+    b, p, q, r = _dims_partial(x, U, V, S)
+    out, z, y = ops.blast_f32(ops.flat2d_f32(x), U, V, S, L.MMAJOR, L.MMAJOR, r, b * r, 1, b, p, q, r)
+    return out.reshape(*x.shape[:-1], b * q), z, y
+
+
+def triton_blast_partial_fp16(x, U, V, S, config=None):
+    """Replaces triton_blast_partial_fp16 (blast_kernels.py:2666-2707)."""
+    return _partial_fp16(x, U, V, S)
+
+
+def triton_blast_partial_fp32(x, U, V, S):
+    """Replaces triton_blast_partial_fp32 (blast_kernels.py:2614-2664): (out, z (b,N,R), y (b,N,R))."""
+    return _partial_fp32(x, U, V, S)
+
+
+def triton_blast_partial_grouped_fp16(x, U, V, S, config=None):
+    """Replaces triton_blast_partial_grouped_fp16 (blast_kernels.py:2762-2803)."""
+    return _partial_fp16(x, U, V, S)
+
+
+def triton_blast_partial_grouped_fp32(x, U, V, S):
+    """Replaces triton_blast_partial_grouped_fp32 (blast_kernels.py:2710-2760)."""
+    return _partial_fp32(x, U, V, S)
+
+
+def triton_blast_partial_grouped_persistent_fp16(x, U, V, S, config=None):
+    """Replaces triton_blast_partial_grouped_persistent_fp16 (blast_kernels.py:2858-2899)."""
+    return _partial_fp16(x, U, V, S)
+
+
+def triton_blast_partial_grouped_persistent_fp32(x, U, V, S):
+    """Replaces triton_blast_partial_grouped_persistent_fp32 (blast_kernels.py:2806-2856)."""
+    return _partial_fp32(x, U, V, S)
+
+
+def triton_blast_full_fp16(x, U, V, S, config=None):
+    """Replaces triton_blast_full_fp16 (blast_kernels.py:2955-2995), which the reference could not make work."""
+    return _partial_fp16(x, U, V, S)
+
+
+def triton_blast_full_fp32(x, U, V, S):
+    """Replaces triton_blast_full_fp32 (blast_kernels.py:2902-2953)."""
+    return _partial_fp32(x, U, V, S)
+
+
+def triton_blast_bmm_fp16(x, U, V, S, config=(None, None, None)):
+    """Replaces triton_blast_bmm_fp16 (blast_kernels.py:3043-3065)."""
+    b, p, q, r = _dims_bmm(x, U, V, S)
+    out = ops.blast_op(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_NONE)
+    return out.reshape(*x.shape[:-1], b * q)
+
+
+def triton_blast_bmm_fp32(x, U, V, S):
+    """Replaces triton_blast_bmm_fp32 (blast_kernels.py:2998-3041): (out, z (b,R,N), y (R,b,N))."""
+    b, p, q, r = _dims_bmm(x, U, V, S)
+    out, z, y = ops.blast_f32(ops.flat2d_f32(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r)
+    return out.reshape(*x.shape[:-1], b * q), z.transpose(1, 2), y.permute(2, 0, 1)
+
+
+def blast_torch_layout(x, U, Vt, S, flags=L.FLAG_NONE):
+    """Same operator on the reference's torch layouts (torch_funcs/blast_funcs.py:3-47):
+    U (b,Q,R), Vt (b,R,P), S (b_out,b_in,R); returns out only."""
+    b, r, p = Vt.shape
+    b2, q, r2 = U.shape
+    assert b == b2 and b != 1 and r2 == r and tuple(S.shape) == (b2, b, r)
+    out = ops.blast_op(ops._flat2d(x), U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags)
+    return out.reshape(*x.shape[:-1], b * q)
+
+
+# The reference exposes its autotuner's winning configuration (blast_kernels.py:3068-3086) and pickles
+# it (layer.py:310-326).  Tile shapes here are fixed at build time, so there is nothing to report.
+def get_triton_blast_partial_fp16_config():
+    return None
+
+
+def get_triton_blast_partial_grouped_fp16_config():
+    return None
+
+
+def get_triton_blast_partial_grouped_persistent_fp16_config():
+    return None
+
+
+def get_triton_blast_full_fp16_config():
+    return None
+
+
+def get_triton_blast_bmm_xv_fp16_config():
+    return None
+
+
+def get_triton_blast_bmm_sxv_fp16_config():
+    return None
+
+
+def get_triton_blast_bmm_usxv_fp16_config():
+    return None

@@ -1,0 +1,57 @@
+"""Quantised BLAST operators.
+
+``triton_blast_bmm_int8_fp16`` keeps the reference's signature and semantics
+(triton_funcs/blast_sym_quant_kernels.py:558-580): 16-bit factors, both intermediates rounded to the
+nearest integer in [-128, 127] with no scale.  ``blast_wq`` is the weight-quantised operator
+(int8 / packed int4 factors with fp16 per-channel scales), which the reference does not have;
+``quantize_blast_factors`` produces its inputs from torch-layout factors.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import ops
+from .blast_kernels import _dims_bmm
+
+
+def triton_blast_bmm_int8_fp16(x, U, V, S, config=(None, None, None)):
+    """U (b,Q,R), V (b,P,R), S (R,b_out,b_in), all 16-bit; activations rounded like the reference's kernels
+    (blast_sym_quant_kernels.py:105-108, 227-230)."""
+    b, p, q, r = _dims_bmm(x, U, V, S)
+    out = ops.blast_op(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_ACT_INT8)
+    return out.reshape(*x.shape[:-1], b * q)
+
+
+def get_triton_blast_bmm_xv_int8_fp16_config():
+    return None
+
+
+def get_triton_blast_bmm_sxv_int8_fp16_config():
+    return None
+
+
+def get_triton_blast_bmm_usxv_int8_fp16_config():
+    return None
+
+
+def quantize_blast_factors(U: torch.Tensor, Vt: torch.Tensor, bits: int):
+    """torch-layout factors U (b,Q,R), Vt (b,R,P) -> (Uq, u_scale (b,Q), Vq, v_scale (b,R)).
+    One fp16 scale per output channel, scale = max|w| / (127 | 7); int4 packed two per byte along the
+    contraction axis, even index in the low nibble."""
+    Uq, us = ops.quantize_sym(U.contiguous(), bits)
+    Vq, vs = ops.quantize_sym(Vt.contiguous(), bits)
+    return Uq, us, Vq, vs
+
+
+def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
+    """Weight-quantised BLAST. Uq (b,Q,R) int8 or (b,Q,R/2) uint8; Vq (b,R,P) int8 or (b,R,P/2) uint8;
+    scales fp16 (b,Q) / (b,R); S (b_out, b_in, R) in x's dtype."""
+    assert bits in (8, 4)
+    b, q = u_scale.shape
+    b2, r = v_scale.shape
+    p = Vq.shape[-1] * (1 if bits == 8 else 2)
+    assert b == b2 and b != 1 and tuple(S.shape) == (b, b, r)
+    assert Uq.shape[-1] * (1 if bits == 8 else 2) == r and x.shape[-1] == b * p
+    out = ops.blast_wq_op(ops._flat2d(x), Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
+    return out.reshape(*x.shape[:-1], b * q)

@@ -1,0 +1,279 @@
+// C ABI: argument checking, descriptor set-up and dispatch between the weight-streaming kernel
+// (N <= 16 tokens) and the tensor-core pipeline (N > 16).
+#include "../../include/blr_b200.h"
+
+#include "pipeline.h"
+#include "stream.h"
+#include "tmap.h"
+
+namespace blr {
+const char* last_error();
+
+static constexpr size_t kCtrlBytes = 256;
+static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct Workspace {
+  unsigned* counters;
+  void* region_a;  // 4 bytes per intermediate element
+  void* region_b;  // 2 bytes per intermediate element
+};
+
+static int carve(void* ws, size_t ws_bytes, int64_t N, int64_t groups, int64_t width, Workspace* w) {
+  const size_t need = blr_workspace_bytes(N, groups, width);
+  BLR_REQUIRE(ws != nullptr && ws_bytes >= need, BLR_ERR_WORKSPACE, "workspace of %zu bytes needed, got %zu", need,
+              ws == nullptr ? (size_t)0 : ws_bytes);
+  BLR_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255) == 0, BLR_ERR_ALIGN, "workspace must be 256-byte aligned");
+  uint8_t* p = static_cast<uint8_t*>(ws);
+  w->counters = reinterpret_cast<unsigned*>(p);
+  w->region_a = p + kCtrlBytes;
+  w->region_b = p + kCtrlBytes + align256((size_t)groups * N * width * 4);
+  return BLR_OK;
+}
+
+static CUtensorMapDataType dt16(int dtype) {
+  return dtype == BLR_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+// Fills the weight side of a phase.
+static int phase_weights(PhaseDesc& ph, int dtype, const void* W, int layout, int wbits, int G, int M, int K) {
+  ph.G = G; ph.M = M; ph.K = K; ph.kmajor = layout == BLR_W_KMAJOR; ph.wbits = wbits;
+  ph.tiles_per_g = (M + kTileRows - 1) / kTileRows;
+  ph.ntiles = G * ph.tiles_per_g;
+  ph.a_boxes = 16 / wbits;
+  if (wbits == 16) {
+    if (ph.kmajor) {
+      BLR_REQUIRE(K % 8 == 0, BLR_ERR_SHAPE, "contraction length %d must be a multiple of 8", K);
+      const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)G};
+      const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * K * 2};
+      const uint32_t box[3] = {64, kTileRows, 1};
+      ph.nchunks = (K + 63) / 64;
+      return encode_tmap_3d(&ph.tmW, dt16(dtype), W, dims, str, box, Swz::B128);
+    }
+    BLR_REQUIRE(M % 8 == 0, BLR_ERR_SHAPE, "block output width %d must be a multiple of 8", M);
+    const uint64_t dims[3] = {(uint64_t)M, (uint64_t)K, (uint64_t)G};
+    const uint64_t str[2] = {(uint64_t)M * 2, (uint64_t)M * K * 2};
+    const uint32_t box[3] = {kTileRows, 64, 1};
+    ph.nchunks = (K + 63) / 64;
+    return encode_tmap_3d(&ph.tmW, dt16(dtype), W, dims, str, box, Swz::B64);
+  }
+  BLR_REQUIRE(ph.kmajor, BLR_ERR_UNSUPPORTED, "quantised factors must have the contraction index contiguous");
+  const int kb = wbits == 8 ? K : K / 2;  // bytes per row
+  BLR_REQUIRE(kb % 16 == 0, BLR_ERR_SHAPE, "quantised rows must be multiples of 16 bytes (K=%d, %d bits)", K, wbits);
+  const uint64_t dims[3] = {(uint64_t)kb, (uint64_t)M, (uint64_t)G};
+  const uint64_t str[2] = {(uint64_t)kb, (uint64_t)M * kb};
+  const uint32_t box[3] = {128, kTileRows, 1};
+  ph.nchunks = (kb + 127) / 128;
+  return encode_tmap_3d(&ph.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, dims, str, box, Swz::B128);
+}
+
+// Activation side: A[g][n][k] with element strides (1, ld_n, ld_g).
+static int phase_acts(PhaseDesc& ph, int dtype, const void* A, int K, int64_t N, int G, int64_t ld_n, int64_t ld_g) {
+  BLR_REQUIRE(ld_n % 8 == 0 && ld_g % 8 == 0, BLR_ERR_ALIGN,
+              "activation strides (%lld, %lld elements) must be multiples of 8", (long long)ld_n, (long long)ld_g);
+  const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)G};
+  const uint64_t str[2] = {(uint64_t)ld_n * 2, (uint64_t)(G > 1 ? ld_g : ld_n * N) * 2};
+  const uint32_t box[3] = {64, (uint32_t)(N <= 8 ? 8 : 16), 1};
+  return encode_tmap_3d(&ph.tmA, dt16(dtype), A, dims, str, box, Swz::B128);
+}
+
+static void phase_out(PhaseDesc& ph, void* out, int out_f32, long long os_g, long long os_n, int per, long long os_hi,
+                      long long os_lo, const void* scale, int round_out) {
+  ph.out = out; ph.out_f32 = out_f32; ph.os_g = os_g; ph.os_n = os_n; ph.per = per; ph.os_hi = os_hi; ph.os_lo = os_lo;
+  ph.scale = static_cast<const __half*>(scale); ph.round_out = round_out;
+}
+
+static void finish_params(StreamParams& p, int64_t N) {
+  p.N = (int)N;
+  int amax = 1;
+  for (int i = 0; i < p.nphases; ++i) amax = p.ph[i].a_boxes > amax ? p.ph[i].a_boxes : amax;
+  const int nb = N <= 8 ? 8 : 16;
+  p.stage_bytes = kBatchTiles * kTileBytes + amax * nb * 128;
+  const int budget = 232448 - 2 * 128 * kRedStride * 4 - 2 * 16 * 8 - 64 - 1024;
+  int nst = budget / p.stage_bytes;
+  p.nstages = nst > 16 ? 16 : nst;
+}
+
+static int check_common(const void* x, int64_t ldx, int64_t N, int dtype, const void* out, int64_t ldo) {
+  BLR_REQUIRE(x != nullptr && out != nullptr, BLR_ERR_ARG, "x and out must not be null");
+  BLR_REQUIRE(N >= 1, BLR_ERR_ARG, "token count must be positive, got %lld", (long long)N);
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  BLR_REQUIRE(ldx > 0 && ldo > 0, BLR_ERR_ARG, "leading dimensions must be positive");
+  return BLR_OK;
+}
+static int check_layout(int layout) {
+  BLR_REQUIRE(layout == BLR_W_KMAJOR || layout == BLR_W_MMAJOR, BLR_ERR_ARG, "unknown weight layout %d", layout);
+  return BLR_OK;
+}
+
+// ---------------------------------------------------------------------------------- BLAST (16-bit and quantised)
+static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
+                      const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, const void* S,
+                      int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R, int flags, void* out,
+                      int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  int rc = check_common(x, ldx, N, dtype, out, ldo);
+  if (rc) return rc;
+  BLR_REQUIRE(U && V && S, BLR_ERR_ARG, "factor pointers must not be null");
+  BLR_REQUIRE(b >= 2, BLR_ERR_SHAPE, "BLAST needs at least 2 blocks per side, got %d (the reference asserts b != 1)", b);
+  BLR_REQUIRE(P > 0 && Q > 0 && R > 0, BLR_ERR_SHAPE, "P, Q, R must be positive");
+  BLR_REQUIRE(ldx >= (int64_t)b * P && ldo >= (int64_t)b * Q, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
+  if ((rc = check_layout(u_layout)) || (rc = check_layout(v_layout))) return rc;
+  Workspace w;
+  if ((rc = carve(ws, ws_bytes, N, b, R, &w))) return rc;
+  const int act8 = (flags & BLR_FLAG_ACT_INT8) ? 1 : 0;
+
+  if (N <= kStreamMaxTokens) {
+    StreamParams p = {};
+    p.nphases = 2; p.mix = 1; p.b = b; p.R = R; p.round_z = act8;
+    p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
+    p.y32 = static_cast<float*>(w.region_a); p.z16 = w.region_b; p.counters = w.counters;
+    if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, v_bits, b, R, P))) return rc;
+    if ((rc = phase_acts(p.ph[0], dtype, x, P, N, b, ldx, P))) return rc;
+    phase_out(p.ph[0], w.region_a, 1, (long long)N * R, R, R, 0, 1, v_scale, act8);
+    if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, b, Q, R))) return rc;
+    if ((rc = phase_acts(p.ph[1], dtype, w.region_b, R, N, b, R, (int64_t)N * R))) return rc;
+    phase_out(p.ph[1], out, 0, Q, ldo, Q, 0, 1, u_scale, 0);
+    finish_params(p, N);
+    return launch_stream(p, dtype == BLR_DTYPE_BF16, stream);
+  }
+  BLR_REQUIRE(u_bits == 16 && v_bits == 16, BLR_ERR_UNSUPPORTED,
+              "quantised factors are implemented for up to %d tokens per call", kStreamMaxTokens);
+  return pipeline_blast(x, ldx, N, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b, P, Q, R, act8, out, ldo,
+                        w.region_a, w.region_b, stream);
+}
+
+}  // namespace blr
+
+using namespace blr;
+
+extern "C" {
+
+int blr_version(void) { return 100; }
+const char* blr_last_error(void) { return blr::last_error(); }
+
+size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
+  if (n_tokens < 0 || groups < 0 || width < 0) return 0;
+  const size_t e = (size_t)groups * (size_t)n_tokens * (size_t)width;
+  return kCtrlBytes + align256(e * 4) + align256(e * 2);
+}
+
+int blr_workspace_init(void* ws, size_t ws_bytes, void* stream) {
+  BLR_REQUIRE(ws != nullptr && ws_bytes >= kCtrlBytes, BLR_ERR_WORKSPACE, "workspace too small");
+  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes, static_cast<cudaStream_t>(stream)));
+  return BLR_OK;
+}
+
+int blr_workspace_status(const void* ws, void* stream) {
+  BLR_REQUIRE(ws != nullptr, BLR_ERR_WORKSPACE, "workspace is null");
+  unsigned words[4] = {0, 0, 0, 0};
+  BLR_CUDA_OK(cudaMemcpyAsync(words, ws, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  BLR_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (words[3] != 0) {
+    set_last_error("a kernel gave up on a device-side wait (status word %u)", words[3]);
+    return BLR_ERR_TIMEOUT;
+  }
+  return BLR_OK;
+}
+
+int blr_blast(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
+              int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R, int flags,
+              void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, P,
+                    Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* Uq, const void* u_scale,
+                 const void* Vq, const void* v_scale, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int bits,
+                 int group, int b, int P, int Q, int R, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
+  BLR_REQUIRE(bits == 8 || bits == 4, BLR_ERR_ARG, "bits must be 8 or 4, got %d", bits);
+  BLR_REQUIRE(group == 0, BLR_ERR_UNSUPPORTED, "only one scale per output channel (group = 0) is implemented");
+  BLR_REQUIRE(u_scale && v_scale, BLR_ERR_ARG, "scale pointers must not be null");
+  return blast_impl(x, ldx, n_tokens, dtype, Uq, BLR_W_KMAJOR, bits, u_scale, Vq, BLR_W_KMAJOR, bits, v_scale, S, s_i,
+                    s_j, s_r, b, P, Q, R, BLR_FLAG_NONE, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* w1, int w1_layout, int w1_cols,
+                const void* w2, int w2_layout, int b, int P, int rank, int Qs, int out_order, void* out, int64_t ldo,
+                void* ws, size_t ws_bytes, void* stream) {
+  const int64_t N = n_tokens;
+  int rc = check_common(x, ldx, N, dtype, out, ldo);
+  if (rc) return rc;
+  BLR_REQUIRE(w1 && w2, BLR_ERR_ARG, "factor pointers must not be null");
+  BLR_REQUIRE(b >= 1 && P > 0 && rank > 0 && Qs > 0, BLR_ERR_SHAPE, "b, P, rank, Qs must be positive");
+  BLR_REQUIRE(rank % b == 0, BLR_ERR_SHAPE, "rank %d must be a multiple of the block count %d (wrappers.py:14)", rank, b);
+  BLR_REQUIRE(w1_cols == BLR_MONARCH_COLS_TORCH || w1_cols == BLR_MONARCH_COLS_GROUPED, BLR_ERR_ARG, "unknown w1_cols %d", w1_cols);
+  BLR_REQUIRE(out_order == BLR_OUT_INTERLEAVED || out_order == BLR_OUT_BLOCKED, BLR_ERR_ARG, "unknown out_order %d", out_order);
+  BLR_REQUIRE(ldx >= (int64_t)b * P && ldo >= (int64_t)b * Qs, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
+  if ((rc = check_layout(w1_layout)) || (rc = check_layout(w2_layout))) return rc;
+  Workspace w;
+  if ((rc = carve(ws, ws_bytes, N, b, rank, &w))) return rc;
+  const int per = rank / b;
+  // intermediate Z[l][n][k*per + jj] lives in region_b (16-bit)
+  const long long zplane = (long long)N * rank;
+  const int grouped = w1_cols == BLR_MONARCH_COLS_GROUPED;
+  if (N <= kStreamMaxTokens) {
+    StreamParams p = {};
+    p.nphases = 2; p.mix = 0; p.counters = w.counters;
+    if ((rc = phase_weights(p.ph[0], dtype, w1, w1_layout, 16, b, rank, P))) return rc;
+    if ((rc = phase_acts(p.ph[0], dtype, x, P, N, b, ldx, P))) return rc;
+    if (grouped) phase_out(p.ph[0], w.region_b, 0, per, rank, per, zplane, 1, nullptr, 0);
+    else phase_out(p.ph[0], w.region_b, 0, per, rank, b, 1, zplane, nullptr, 0);
+    if ((rc = phase_weights(p.ph[1], dtype, w2, w2_layout, 16, b, Qs, rank))) return rc;
+    if ((rc = phase_acts(p.ph[1], dtype, w.region_b, rank, N, b, rank, zplane))) return rc;
+    if (out_order == BLR_OUT_INTERLEAVED) phase_out(p.ph[1], out, 0, 1, ldo, Qs, 0, b, nullptr, 0);
+    else phase_out(p.ph[1], out, 0, Qs, ldo, Qs, 0, 1, nullptr, 0);
+    finish_params(p, N);
+    return launch_stream(p, dtype == BLR_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  }
+  return pipeline_monarch(x, ldx, N, dtype, w1, w1_layout, grouped, w2, w2_layout, b, P, rank, Qs,
+                          out_order == BLR_OUT_INTERLEAVED, out, ldo, w.region_b, static_cast<cudaStream_t>(stream));
+}
+
+int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* V, int v_layout, const void* U,
+                 int u_layout, int I, int R, int O, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
+  const int64_t N = n_tokens;
+  int rc = check_common(x, ldx, N, dtype, out, ldo);
+  if (rc) return rc;
+  BLR_REQUIRE(V && U, BLR_ERR_ARG, "factor pointers must not be null");
+  BLR_REQUIRE(I > 0 && R > 0 && O > 0, BLR_ERR_SHAPE, "I, R, O must be positive");
+  BLR_REQUIRE(ldx >= I && ldo >= O, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
+  if ((rc = check_layout(v_layout)) || (rc = check_layout(u_layout))) return rc;
+  Workspace w;
+  if ((rc = carve(ws, ws_bytes, N, 1, R, &w))) return rc;
+  if (N <= kStreamMaxTokens) {
+    StreamParams p = {};
+    p.nphases = 2; p.mix = 0; p.counters = w.counters;
+    if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, 16, 1, R, I))) return rc;
+    if ((rc = phase_acts(p.ph[0], dtype, x, I, N, 1, ldx, 0))) return rc;
+    phase_out(p.ph[0], w.region_b, 0, 0, R, R, 0, 1, nullptr, 0);
+    if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, 16, 1, O, R))) return rc;
+    if ((rc = phase_acts(p.ph[1], dtype, w.region_b, R, N, 1, R, 0))) return rc;
+    phase_out(p.ph[1], out, 0, 0, ldo, O, 0, 1, nullptr, 0);
+    finish_params(p, N);
+    return launch_stream(p, dtype == BLR_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  }
+  return pipeline_low_rank(x, ldx, N, dtype, V, v_layout, U, u_layout, I, R, O, out, ldo, w.region_b,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int blr_dense(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* W, int w_layout, int I, int O,
+              void* out, int64_t ldo, void* stream) {
+  const int64_t N = n_tokens;
+  int rc = check_common(x, ldx, N, dtype, out, ldo);
+  if (rc) return rc;
+  BLR_REQUIRE(W, BLR_ERR_ARG, "weight pointer must not be null");
+  BLR_REQUIRE(I > 0 && O > 0, BLR_ERR_SHAPE, "I, O must be positive");
+  BLR_REQUIRE(ldx >= I && ldo >= O, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
+  if ((rc = check_layout(w_layout))) return rc;
+  if (N <= kStreamMaxTokens) {
+    StreamParams p = {};
+    p.nphases = 1; p.mix = 0; p.counters = nullptr;
+    if ((rc = phase_weights(p.ph[0], dtype, W, w_layout, 16, 1, O, I))) return rc;
+    if ((rc = phase_acts(p.ph[0], dtype, x, I, N, 1, ldx, 0))) return rc;
+    phase_out(p.ph[0], out, 0, 0, ldo, O, 0, 1, nullptr, 0);
+    finish_params(p, N);
+    return launch_stream(p, dtype == BLR_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  }
+  return pipeline_dense(x, ldx, N, dtype, W, w_layout, I, O, out, ldo, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

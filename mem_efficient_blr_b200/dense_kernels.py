@@ -1,0 +1,32 @@
+"""Dense operators with the reference's names and layouts (triton_funcs/dense_kernels.py).
+
+w is (I, O) (layer.py:267); the result is 2-D (N, O) like the reference's (dense_kernels.py:375-381).
+"""
+from __future__ import annotations
+
+from . import _lib as L
+from . import ops
+
+
+def triton_dense_fp16(x, w, config=None):
+    """Replaces triton_dense_fp16 (dense_kernels.py:375-381)."""
+    i, o = w.shape
+    assert x.shape[-1] == i and w.is_contiguous()
+    return ops.dense_op(ops._flat2d(x), w, L.MMAJOR, i, o)
+
+
+def triton_dense_fp32(x, w):
+    """Replaces triton_dense_fp32 (dense_kernels.py:360-373)."""
+    i, o = w.shape
+    assert x.shape[-1] == i and w.is_contiguous()
+    return ops.dense_f32(ops.flat2d_f32(x), w, L.MMAJOR, i, o)
+
+
+def dense_torch_layout(x, Wt):
+    """torch layout Wt (O, I) (torch_funcs/dense_funcs.py:4-25); batch dims restored."""
+    o, i = Wt.shape
+    return ops.dense_op(ops._flat2d(x), Wt, L.KMAJOR, i, o).reshape(*x.shape[:-1], o)
+
+
+def get_triton_dense_fp16_config():
+    return None

@@ -1,0 +1,204 @@
+"""Torch-facing operators: tensors in, tensors out, arithmetic in libblr_b200.so.
+
+Every operator is registered with ``torch.library.custom_op`` (with a fake kernel), so the reference's
+callers that wrap a model in ``torch.compile(fullgraph=True, mode='reduce-overhead')``
+(models/llama7b.py:65) trace through it; launches go to the current stream, outputs come from torch's
+allocator, and nothing synchronises the host.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from . import _lib as L
+
+
+def _flat2d(x: torch.Tensor) -> torch.Tensor:
+    """(..., I) -> (N, I) view with unit inner stride (copies only if the input forces it)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8 != 0) or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("blr_b200 operators need CUDA tensors: there is no CPU implementation in this package")
+        assert t.is_contiguous() or t.dim() == 2, "factor tensors must be contiguous"
+
+
+def _ws(x: torch.Tensor, n: int, groups: int, width: int):
+    st = L.stream_ptr(x.device)
+    nbytes = L.load().blr_workspace_bytes(n, groups, width)
+    ws = L.workspace(x.device, st, nbytes)
+    return ws, st
+
+
+# ----------------------------------------------------------------------------- BLAST
+@torch.library.custom_op("blr_b200::blast", mutates_args=())
+def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor, u_layout: int, v_layout: int,
+             s_i: int, s_j: int, s_r: int, b: int, P: int, Q: int, R: int, flags: int) -> torch.Tensor:
+    _need_cuda(x, U, V, S)
+    assert U.dtype == x.dtype and V.dtype == x.dtype and S.dtype == x.dtype, "x, U, V, S must share one 16-bit dtype"
+    n = x.shape[0]
+    out = torch.empty((n, b * Q), dtype=x.dtype, device=x.device)
+    ws, st = _ws(x, n, b, R)
+    L.check(L.load().blr_blast(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), U.data_ptr(), u_layout,
+                               V.data_ptr(), v_layout, S.data_ptr(), s_i, s_j, s_r, b, P, Q, R, flags,
+                               out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), st))
+    return out
+
+
+@blast_op.register_fake
+def _(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags):
+    return x.new_empty((x.shape[0], b * Q))
+
+
+@torch.library.custom_op("blr_b200::blast_wq", mutates_args=())
+def blast_wq_op(x: torch.Tensor, Uq: torch.Tensor, u_scale: torch.Tensor, Vq: torch.Tensor, v_scale: torch.Tensor,
+                S: torch.Tensor, s_i: int, s_j: int, s_r: int, bits: int, group: int, b: int, P: int, Q: int,
+                R: int) -> torch.Tensor:
+    _need_cuda(x, Uq, u_scale, Vq, v_scale, S)
+    assert u_scale.dtype == torch.float16 and v_scale.dtype == torch.float16, "scales are fp16"
+    assert S.dtype == x.dtype
+    n = x.shape[0]
+    out = torch.empty((n, b * Q), dtype=x.dtype, device=x.device)
+    ws, st = _ws(x, n, b, R)
+    L.check(L.load().blr_blast_wq(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), Uq.data_ptr(),
+                                  u_scale.data_ptr(), Vq.data_ptr(), v_scale.data_ptr(), S.data_ptr(), s_i, s_j, s_r,
+                                  bits, group, b, P, Q, R, out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), st))
+    return out
+
+
+@blast_wq_op.register_fake
+def _(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
+    return x.new_empty((x.shape[0], b * Q))
+
+
+# ----------------------------------------------------------------------------- Monarch
+@torch.library.custom_op("blr_b200::monarch", mutates_args=())
+def monarch_op(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_layout: int, w1_cols: int, w2_layout: int,
+               b: int, P: int, rank: int, Qs: int, out_order: int) -> torch.Tensor:
+    _need_cuda(x, w1, w2)
+    assert w1.dtype == x.dtype and w2.dtype == x.dtype
+    n = x.shape[0]
+    out = torch.empty((n, b * Qs), dtype=x.dtype, device=x.device)
+    ws, st = _ws(x, n, b, rank)
+    L.check(L.load().blr_monarch(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), w1.data_ptr(), w1_layout,
+                                 w1_cols, w2.data_ptr(), w2_layout, b, P, rank, Qs, out_order, out.data_ptr(),
+                                 out.stride(0), ws.data_ptr(), ws.numel(), st))
+    return out
+
+
+@monarch_op.register_fake
+def _(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
+    return x.new_empty((x.shape[0], b * Qs))
+
+
+# ----------------------------------------------------------------------------- low rank / dense
+@torch.library.custom_op("blr_b200::low_rank", mutates_args=())
+def low_rank_op(x: torch.Tensor, V: torch.Tensor, U: torch.Tensor, v_layout: int, u_layout: int, I: int, R: int,
+                O: int) -> torch.Tensor:
+    _need_cuda(x, V, U)
+    assert V.dtype == x.dtype and U.dtype == x.dtype
+    n = x.shape[0]
+    out = torch.empty((n, O), dtype=x.dtype, device=x.device)
+    ws, st = _ws(x, n, 1, R)
+    L.check(L.load().blr_low_rank(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), V.data_ptr(), v_layout,
+                                  U.data_ptr(), u_layout, I, R, O, out.data_ptr(), out.stride(0), ws.data_ptr(),
+                                  ws.numel(), st))
+    return out
+
+
+@low_rank_op.register_fake
+def _(x, V, U, v_layout, u_layout, I, R, O):
+    return x.new_empty((x.shape[0], O))
+
+
+@torch.library.custom_op("blr_b200::dense", mutates_args=())
+def dense_op(x: torch.Tensor, W: torch.Tensor, w_layout: int, I: int, O: int) -> torch.Tensor:
+    _need_cuda(x, W)
+    assert W.dtype == x.dtype
+    n = x.shape[0]
+    out = torch.empty((n, O), dtype=x.dtype, device=x.device)
+    L.check(L.load().blr_dense(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), W.data_ptr(), w_layout, I, O,
+                               out.data_ptr(), out.stride(0), L.stream_ptr(x.device)))
+    return out
+
+
+@dense_op.register_fake
+def _(x, W, w_layout, I, O):
+    return x.new_empty((x.shape[0], O))
+
+
+# ----------------------------------------------------------------------------- fp32 verification variants
+def _f32(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("blr_b200 operators need CUDA tensors: there is no CPU implementation in this package")
+        assert t.dtype == torch.float32, "the _fp32 entry points take float32 tensors"
+
+
+def blast_f32(x2, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    _f32(x2, U, V, S)
+    n = x2.shape[0]
+    out = torch.empty((n, b * Q), dtype=torch.float32, device=x2.device)
+    z = torch.empty((b, n, R), dtype=torch.float32, device=x2.device)
+    y = torch.empty((b, n, R), dtype=torch.float32, device=x2.device)
+    L.check(L.load().blr_blast_f32(x2.data_ptr(), x2.stride(0), n, U.data_ptr(), u_layout, V.data_ptr(), v_layout,
+                                   S.data_ptr(), s_i, s_j, s_r, b, P, Q, R, out.data_ptr(), out.stride(0),
+                                   z.data_ptr(), y.data_ptr(), L.stream_ptr(x2.device)))
+    return out, z, y
+
+
+def monarch_f32(x2, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
+    _f32(x2, w1, w2)
+    n = x2.shape[0]
+    out = torch.empty((n, b * Qs), dtype=torch.float32, device=x2.device)
+    out1 = torch.empty((b, n, rank), dtype=torch.float32, device=x2.device)
+    L.check(L.load().blr_monarch_f32(x2.data_ptr(), x2.stride(0), n, w1.data_ptr(), w1_layout, w1_cols, w2.data_ptr(),
+                                     w2_layout, b, P, rank, Qs, out_order, out.data_ptr(), out.stride(0),
+                                     out1.data_ptr(), L.stream_ptr(x2.device)))
+    return out, out1
+
+
+def low_rank_f32(x2, V, U, v_layout, u_layout, I, R, O):
+    _f32(x2, V, U)
+    n = x2.shape[0]
+    out = torch.empty((n, O), dtype=torch.float32, device=x2.device)
+    z = torch.empty((n, R), dtype=torch.float32, device=x2.device)
+    L.check(L.load().blr_low_rank_f32(x2.data_ptr(), x2.stride(0), n, V.data_ptr(), v_layout, U.data_ptr(), u_layout,
+                                      I, R, O, out.data_ptr(), out.stride(0), z.data_ptr(), L.stream_ptr(x2.device)))
+    return out, z
+
+
+def dense_f32(x2, W, w_layout, I, O):
+    _f32(x2, W)
+    n = x2.shape[0]
+    out = torch.empty((n, O), dtype=torch.float32, device=x2.device)
+    L.check(L.load().blr_dense_f32(x2.data_ptr(), x2.stride(0), n, W.data_ptr(), w_layout, I, O, out.data_ptr(),
+                                   out.stride(0), L.stream_ptr(x2.device)))
+    return out
+
+
+def flat2d_f32(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    return x2 if x2.stride(-1) == 1 else x2.contiguous()
+
+
+# ----------------------------------------------------------------------------- quantiser
+def quantize_sym(w: torch.Tensor, bits: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-output-channel symmetric quantisation on the device; w (..., K) contiguous 16-bit.
+    Returns (q int8 (..., K) | uint8 (..., K/2), scale fp16 (...))."""
+    _need_cuda(w)
+    assert w.is_contiguous() and bits in (8, 4)
+    K = w.shape[-1]
+    rows = w.numel() // K
+    q = torch.empty((*w.shape[:-1], K if bits == 8 else K // 2), dtype=torch.int8 if bits == 8 else torch.uint8,
+                    device=w.device)
+    scale = torch.empty(w.shape[:-1], dtype=torch.float16, device=w.device)
+    L.check(L.load().blr_quantize_sym(w.data_ptr(), L.dtype_code(w.dtype), rows, K, bits, q.data_ptr(),
+                                      scale.data_ptr(), L.stream_ptr(w.device)))
+    return q, scale

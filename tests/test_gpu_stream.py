@@ -1,0 +1,212 @@
+"""GPU parity of the weight-streaming path (1..16 tokens) against the CPU oracle, through the C ABI.
+
+Tolerance: relative Frobenius error <= 1e-2 against the fp32 oracle evaluated on the same 16-bit
+inputs (the acceptance bound of the headline configuration); typical errors are ~1e-3.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import blr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import mem_efficient_blr_b200.blast_kernels as bk
+    import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
+    import mem_efficient_blr_b200.dense_kernels as dk
+    import mem_efficient_blr_b200.low_rank_kernels as lk
+    import mem_efficient_blr_b200.monarch_kernels as mk
+    from mem_efficient_blr_b200 import _lib
+
+    class NS:
+        pass
+
+    ns = NS()
+    ns.bk, ns.bq, ns.dk, ns.lk, ns.mk, ns.lib = bk, bq, dk, lk, mk, _lib
+    return ns
+
+
+def _cuda(*ts):
+    return [t.to(DEV) for t in ts]
+
+
+def _sync_ok(K):
+    torch.cuda.synchronize()
+    K.lib.workspace_status(torch.device(DEV))
+
+
+BLAST_SHAPES = [
+    # N, I, O, b, R
+    (1, 256, 384, 4, 128),
+    (5, 768, 768, 3, 128),        # the reference's ViT setting b=3
+    (16, 768, 3072, 16, 192),     # P=48, Q=192
+    (8, 4096, 11008, 16, 1024),   # headline layer, Q=688 is not a multiple of 32
+    (16, 4096, 11008, 16, 1024),
+    (1, 11008, 4096, 16, 1488),   # down_proj with the reference's 50%-parameter rank
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", BLAST_SHAPES)
+def test_blast_all_layout_families(K, shape, dtype):
+    N, I, O, b, R = shape
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, dtype, seed=N + R)
+    ref, _, _ = orc.blast(x, U, Vt, S)
+    xd, Ud, Vtd, Sd = _cuda(x, U, Vt, S)
+    got = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+    _sync_ok(K)
+    assert got.shape == ref.shape and got.dtype == dtype
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+    Up, Vp, Sp = _cuda(*orc.blast_to_partial_layout(U, Vt, S))
+    for fn in (K.bk.triton_blast_partial_fp16, K.bk.triton_blast_partial_grouped_fp16,
+               K.bk.triton_blast_partial_grouped_persistent_fp16, K.bk.triton_blast_full_fp16):
+        got = fn(xd, Up, Vp, Sp)
+        _sync_ok(K)
+        assert orc.rel_fro(got.float().cpu(), ref) < TOL, fn.__name__
+    Ub, Vb, Sb = _cuda(*orc.blast_to_bmm_layout(U, Vt, S))
+    got = K.bk.triton_blast_bmm_fp16(xd, Ub, Vb, Sb)
+    _sync_ok(K)
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_blast_reference_golden_vectors(K, golden_dir, tag):
+    g = {k: torch.from_numpy(v) for k, v in np.load(os.path.join(golden_dir, f"blast_{tag}.npz")).items()}
+    x, U, Vt, S = (g[k].to(torch.bfloat16) for k in ("x", "U", "Vt", "S"))
+    ref, _, _ = orc.blast(x, U, Vt, S)
+    got = K.bk.blast_torch_layout(*_cuda(x, U, Vt, S))
+    _sync_ok(K)
+    assert got.shape == g["out"].shape
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+    # and against the reference's own fp32 output: only the bf16 rounding of the inputs separates them
+    assert orc.rel_fro(got.float().cpu(), g["out"]) < 3e-2
+
+
+def test_blast_non_contiguous_x_and_leading_dims(K):
+    x, U, Vt, S = orc.make_blast_inputs(6, 512, 256, 4, 64, torch.float16, seed=9, lead=(2, 3))
+    big = torch.zeros(2, 3, 1024, dtype=torch.float16)
+    big[..., :512] = x
+    xv = big.to(DEV)[..., :512]          # row stride 1024, not contiguous
+    ref, _, _ = orc.blast(x, U, Vt, S)
+    got = K.bk.blast_torch_layout(xv, *_cuda(U, Vt, S))
+    _sync_ok(K)
+    assert got.shape == (2, 3, 256)
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 512, 768, 4, 256), (4, 4096, 11008, 16, 1024), (16, 4096, 11008, 16, 1024),
+                                   (1, 4096, 11008, 16, 1024)])
+def test_blast_weight_quantised(K, shape, dtype, bits):
+    N, I, O, b, R = shape
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, dtype, seed=bits + N)
+    Uq, us = orc.quantize_sym(U, bits)
+    Vq, vs = orc.quantize_sym(Vt, bits)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits)
+    # device quantiser must agree bit for bit with the oracle's
+    dUq, dus, dVq, dvs = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), bits)
+    assert torch.equal(dus.cpu(), us) and torch.equal(dvs.cpu(), vs)
+    assert torch.equal(dUq.cpu(), Uq) and torch.equal(dVq.cpu(), Vq)
+    got = K.bq.blast_wq(x.to(DEV), dUq, dus, dVq, dvs, S.to(DEV), bits)
+    _sync_ok(K)
+    assert got.shape == ref.shape
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+
+
+def test_blast_act_int8_matches_reference_rounding(K):
+    x, U, Vt, S = orc.make_blast_inputs(4, 512, 768, 4, 128, torch.bfloat16, seed=21)
+    x = x * 4  # spread the intermediates over the int8 range
+    ref, z8, y8 = orc.blast_act_int8(x, U, Vt, S)
+    Ub, Vb, Sb = _cuda(*orc.blast_to_bmm_layout(U, Vt, S))
+    got = K.bq.triton_blast_bmm_int8_fp16(x.to(DEV), Ub, Vb, Sb)
+    _sync_ok(K)
+    # rounding ties may flip single intermediates by one unit; the output stays within the bound
+    assert orc.rel_fro(got.float().cpu(), ref) < 3e-2
+
+
+MONARCH_SHAPES = [(1, 256, 512, 4, 64), (7, 768, 3072, 4, 768), (16, 4096, 4096, 16, 1024), (3, 4096, 11008, 16, 1536)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", MONARCH_SHAPES)
+def test_monarch_all_variants(K, shape, dtype):
+    N, I, O, b, rank = shape
+    x, w1_t, w2_t = orc.make_monarch_inputs(N, I, O, b, rank, dtype, seed=N)
+    ref, _, out1, _ = orc.monarch(x, w1_t, w2_t)
+    xd = x.to(DEV)
+    got = K.mk.monarch_torch_layout(xd, w1_t.to(DEV), w2_t.to(DEV))
+    _sync_ok(K)
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+    w1k = orc.monarch_w1_to_kernel_layout(w1_t).to(DEV)
+    got = K.mk.triton_monarch_right_fp16(xd, w1k, w2_t.to(DEV))
+    _sync_ok(K)
+    assert got.shape == ref.shape and orc.rel_fro(got.float().cpu(), ref) < TOL
+    got = K.mk.triton_monarch_right_left_fp16(xd, w1k, orc.monarch_w2_to_left_layout(w2_t).to(DEV))
+    _sync_ok(K)
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+    got = K.mk.triton_monarch_right_ideal_fp16(xd, w1k, w2_t.to(DEV))
+    _sync_ok(K)
+    assert orc.rel_fro(got.float().cpu(), orc.monarch_ideal_order(ref, b)) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 256, 384, 64), (16, 4096, 11008, 1024), (5, 11008, 4096, 1024)])
+def test_low_rank(K, shape, dtype):
+    N, I, O, R = shape
+    x, Vt, Ut = orc.make_low_rank_inputs(N, I, O, R, dtype, seed=N)
+    ref, _ = orc.low_rank(x, Vt, Ut)
+    got = K.lk.low_rank_torch_layout(x.to(DEV), Vt.to(DEV), Ut.to(DEV))
+    _sync_ok(K)
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+    got = K.lk.triton_low_rank_fp16(x.to(DEV), Vt.t().contiguous().to(DEV), Ut.t().contiguous().to(DEV))
+    _sync_ok(K)
+    assert got.shape == (N, O)  # 2-D like the reference
+    assert orc.rel_fro(got.float().cpu(), ref.reshape(N, O)) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 256, 384), (16, 4096, 11008), (3, 11008, 4096)])
+def test_dense(K, shape, dtype):
+    N, I, O = shape
+    x, Wt = orc.make_dense_inputs(N, I, O, dtype, seed=N)
+    ref = orc.dense(x, Wt)
+    got = K.dk.dense_torch_layout(x.to(DEV), Wt.to(DEV))
+    torch.cuda.synchronize()
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL
+    got = K.dk.triton_dense_fp16(x.to(DEV), Wt.t().contiguous().to(DEV))
+    torch.cuda.synchronize()
+    assert got.shape == (N, O) and orc.rel_fro(got.float().cpu(), ref.reshape(N, O)) < TOL
+
+
+def test_repeated_calls_reuse_the_workspace(K):
+    """The grid-barrier words re-arm themselves: 50 back-to-back calls give the same answer."""
+    x, U, Vt, S = orc.make_blast_inputs(16, 1024, 1024, 4, 256, torch.float16, seed=2)
+    ref, _, _ = orc.blast(x, U, Vt, S)
+    args = _cuda(x, U, Vt, S)
+    outs = [K.bk.blast_torch_layout(*args) for _ in range(50)]
+    _sync_ok(K)
+    for o in (outs[0], outs[-1]):
+        assert orc.rel_fro(o.float().cpu(), ref) < TOL
+    assert orc.rel_fro(outs[-1].float().cpu(), outs[0].float().cpu()) < 1e-3
+
+
+def test_argument_errors_are_reported(K):
+    x, U, Vt, S = orc.make_blast_inputs(2, 256, 256, 4, 64, torch.float16, seed=1)
+    with pytest.raises(AssertionError):
+        K.bk.blast_torch_layout(*_cuda(x, U, Vt, S[:, :3].contiguous()))
+    with pytest.raises(RuntimeError):  # CPU tensors: there is no fallback
+        K.bk.blast_torch_layout(x, U, Vt, S)
+    # P = 12 is not a multiple of 8: rejected by the C ABI with a message
+    x, U, Vt, S = orc.make_blast_inputs(2, 48, 64, 4, 64, torch.float16, seed=1)
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        K.bk.blast_torch_layout(*_cuda(x, U, Vt, S))
