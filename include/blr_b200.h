@@ -63,6 +63,12 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int blr_version(void);
 
+/* Profiling aid: with a non-NULL device buffer of 16 * (SM count) uint64, every later streaming-kernel
+ * launch stores per-CTA %globaltimer stamps there (0 start, 1/2 weight loads of phase 0/1 issued,
+ * 3 first stage landed, 4/8 phase 0/1 written, 5 first grid barrier passed, 6 coupling written, 9 end).
+ * NULL switches it off. No reference counterpart. */
+int blr_debug_stream_timeline(void* dev_ptr);
+
 /* Text of the last error on the calling thread. No reference counterpart (the reference raises
  * Python AssertionError, e.g. blast_kernels.py:1951-1955). */
 const char* blr_last_error(void);

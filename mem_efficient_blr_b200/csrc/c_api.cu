@@ -37,33 +37,34 @@ static CUtensorMapDataType dt16(int dtype) {
 // Fills the weight side of a phase.
 static int phase_weights(PhaseDesc& ph, int dtype, const void* W, int layout, int wbits, int G, int M, int K) {
   ph.G = G; ph.M = M; ph.K = K; ph.kmajor = layout == BLR_W_KMAJOR; ph.wbits = wbits;
-  ph.tiles_per_g = (M + kTileRows - 1) / kTileRows;
+  ph.unit_rows = ph.kmajor ? 16 : 32;
+  ph.tiles_per_g = (M + ph.unit_rows - 1) / ph.unit_rows;
   ph.ntiles = G * ph.tiles_per_g;
   ph.a_boxes = 16 / wbits;
-  if (wbits == 16) {
-    if (ph.kmajor) {
-      BLR_REQUIRE(K % 8 == 0, BLR_ERR_SHAPE, "contraction length %d must be a multiple of 8", K);
-      const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)G};
-      const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * K * 2};
-      const uint32_t box[3] = {64, kTileRows, 1};
-      ph.nchunks = (K + 63) / 64;
-      return encode_tmap_3d(&ph.tmW, dt16(dtype), W, dims, str, box, Swz::B128);
-    }
+  if (!ph.kmajor) {
+    BLR_REQUIRE(wbits == 16, BLR_ERR_UNSUPPORTED, "quantised factors must have the contraction index contiguous");
     BLR_REQUIRE(M % 8 == 0, BLR_ERR_SHAPE, "block output width %d must be a multiple of 8", M);
     const uint64_t dims[3] = {(uint64_t)M, (uint64_t)K, (uint64_t)G};
     const uint64_t str[2] = {(uint64_t)M * 2, (uint64_t)M * K * 2};
-    const uint32_t box[3] = {kTileRows, 64, 1};
+    const uint32_t box[3] = {32, 64, 1};
     ph.nchunks = (K + 63) / 64;
-    return encode_tmap_3d(&ph.tmW, dt16(dtype), W, dims, str, box, Swz::B64);
+    return encode_tmap_3d(&ph.tmW[0], dt16(dtype), W, dims, str, box, Swz::B64);
   }
-  BLR_REQUIRE(ph.kmajor, BLR_ERR_UNSUPPORTED, "quantised factors must have the contraction index contiguous");
-  const int kb = wbits == 8 ? K : K / 2;  // bytes per row
-  BLR_REQUIRE(kb % 16 == 0, BLR_ERR_SHAPE, "quantised rows must be multiples of 16 bytes (K=%d, %d bits)", K, wbits);
-  const uint64_t dims[3] = {(uint64_t)kb, (uint64_t)M, (uint64_t)G};
+  // contraction index contiguous: rows of kb bytes, 128 bytes of every row per stage
+  const int kb = wbits == 16 ? K * 2 : (wbits == 8 ? K : K / 2);
+  BLR_REQUIRE(kb % 16 == 0 && (wbits != 4 || K % 2 == 0), BLR_ERR_SHAPE,
+              "weight rows must be multiples of 16 bytes: contraction length %d must be a multiple of 8 (16-bit), 16 (int8) or 32 (int4)", K);
+  const uint64_t inner = wbits == 16 ? (uint64_t)K : (uint64_t)kb;
+  const uint64_t dims[3] = {inner, (uint64_t)M, (uint64_t)G};
   const uint64_t str[2] = {(uint64_t)kb, (uint64_t)M * kb};
-  const uint32_t box[3] = {128, kTileRows, 1};
   ph.nchunks = (kb + 127) / 128;
-  return encode_tmap_3d(&ph.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, dims, str, box, Swz::B128);
+  const CUtensorMapDataType dt = wbits == 16 ? dt16(dtype) : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  for (int h = 1; h <= 8; ++h) {
+    const uint32_t box[3] = {wbits == 16 ? 64u : 128u, (uint32_t)(16 * h), 1};
+    int rc = encode_tmap_3d(&ph.tmW[h - 1], dt, W, dims, str, box, Swz::B128);
+    if (rc) return rc;
+  }
+  return BLR_OK;
 }
 
 // Activation side: A[g][n][k] with element strides (1, ld_n, ld_g).
@@ -84,11 +85,20 @@ static void phase_out(PhaseDesc& ph, void* out, int out_f32, long long os_g, lon
 
 static void finish_params(StreamParams& p, int64_t N) {
   p.N = (int)N;
-  int amax = 1;
-  for (int i = 0; i < p.nphases; ++i) amax = p.ph[i].a_boxes > amax ? p.ph[i].a_boxes : amax;
   const int nb = N <= 8 ? 8 : 16;
-  p.stage_bytes = kBatchTiles * kTileBytes + amax * nb * 128;
-  const int budget = 232448 - 2 * 128 * kRedStride * 4 - 2 * 16 * 8 - 64 - 1024;
+  int wmax = 0, amax = 0;
+  for (int i = 0; i < p.nphases; ++i) {
+    PhaseDesc& ph = p.ph[i];
+    // two K-chunks per ring stage halve the producer/consumer hand-offs; one when K is a single chunk
+    ph.ks = ph.nchunks >= 2 ? 2 : 1;
+    ph.nstage_chunks = (ph.nchunks + ph.ks - 1) / ph.ks;
+    wmax = ph.ks * kSubBytes > wmax ? ph.ks * kSubBytes : wmax;
+    const int a = ph.ks * ph.a_boxes * nb * 128;
+    amax = a > amax ? a : amax;
+  }
+  p.w_bytes = wmax;
+  p.stage_bytes = wmax + amax;
+  const int budget = 232448 - kStreamTailBytes;
   int nst = budget / p.stage_bytes;
   p.nstages = nst > 16 ? 16 : nst;
 }
@@ -113,6 +123,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   int rc = check_common(x, ldx, N, dtype, out, ldo);
   if (rc) return rc;
   BLR_REQUIRE(U && V && S, BLR_ERR_ARG, "factor pointers must not be null");
+  BLR_REQUIRE((reinterpret_cast<uintptr_t>(S) & 15) == 0, BLR_ERR_ALIGN, "S must be 16-byte aligned");
   BLR_REQUIRE(b >= 2, BLR_ERR_SHAPE, "BLAST needs at least 2 blocks per side, got %d (the reference asserts b != 1)", b);
   BLR_REQUIRE(P > 0 && Q > 0 && R > 0, BLR_ERR_SHAPE, "P, Q, R must be positive");
   BLR_REQUIRE(ldx >= (int64_t)b * P && ldo >= (int64_t)b * Q, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
@@ -148,6 +159,10 @@ using namespace blr;
 extern "C" {
 
 int blr_version(void) { return 100; }
+int blr_debug_stream_timeline(void* dev_ptr) {
+  set_stream_timeline(static_cast<unsigned long long*>(dev_ptr));
+  return BLR_OK;
+}
 const char* blr_last_error(void) { return blr::last_error(); }
 
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {

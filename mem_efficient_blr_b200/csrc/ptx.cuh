@@ -11,8 +11,9 @@
 
 namespace blr {
 
-// Budget for any single device-side wait (mbarrier, grid barrier): 2 s of %globaltimer.
-static constexpr unsigned long long kWaitBudgetNs = 2000ull * 1000ull * 1000ull;
+// Budget for any single device-side wait (mbarrier, grid barrier), in SM clock cycles (about 2 s).
+// The SM-local cycle counter is used because reading %globaltimer costs about half a microsecond.
+static constexpr long long kWaitBudgetCycles = 4000ll * 1000ll * 1000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -50,12 +51,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` (shared memory) lets one thread's time-out release the others.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (clock64() - t0 > kWaitBudgetCycles) {
         *abort_flag = 1;
         return false;
       }
@@ -93,12 +94,12 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
 // Bounded poll until *p >= target.
 __device__ __forceinline__ bool wait_counter(const unsigned* p, unsigned target, volatile int* abort_flag) {
   if (ld_acquire_gpu(p) >= target) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (ld_acquire_gpu(p) < target) {
     if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (clock64() - t0 > kWaitBudgetCycles) {
         *abort_flag = 1;
         return false;
       }

@@ -13,22 +13,27 @@
 namespace blr {
 
 static constexpr int kStreamMaxTokens = 16;
-static constexpr int kTileRows = 32;       // weight rows per tile (one TMA box)
-static constexpr int kBatchTiles = 4;      // tiles consumed together (128 rows)
-static constexpr int kTileBytes = 4096;    // 32 rows x 128 B   or   64 k-rows x 64 B
+static constexpr int kBatchRows = 128;      // weight rows consumed together: 16 per consumer warp
+static constexpr int kSubBytes = kBatchRows * 128;  // weight bytes of one K-chunk of a full batch
+static constexpr int kTileBytes = 4096;     // m-contiguous layout: one box = 64 k-rows x 32 m (64 B)
 static constexpr int kConsumerWarps = 8;
 static constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;
-static constexpr int kRedStride = 17;      // fp32 words per reduction-buffer row (16 tokens + pad)
+static constexpr int kStreamTailBytes = 2 * 16 * 8 + 64 + 1024;  // barriers, abort flag, alignment slack
 
 struct alignas(64) PhaseDesc {
-  CUtensorMap tmW;  // weights: K-major dims (K, M, G) box (128 B, 32, 1); M-major dims (M, K, G) box (32, 64, 1)
+  // weights, K-major: dims (K, M, G), tmW[h-1] has box (128 B, 16*h, 1) so that one load brings a whole
+  // batch of h row groups; M-major: dims (M, K, G), only tmW[0] with box (32, 64, 1)
+  CUtensorMap tmW[8];
   CUtensorMap tmA;  // activations: dims (K, N, G) box (64, 8|16, 1)
   int G, M, K;
   int kmajor;       // 1: W[g][m][k] (k contiguous)   0: W[g][k][m] (m contiguous; 16-bit only)
   int wbits;        // 16, 8, 4
-  int tiles_per_g;  // ceil(M / 32)
+  int unit_rows;    // rows per work unit: 16 (K-major) or 32 (M-major)
+  int tiles_per_g;  // work units per block: ceil(M / unit_rows)
   int ntiles;       // G * tiles_per_g
-  int nchunks;      // K-chunks per tile: 128 B of k per row (K-major) or 64 k-rows (M-major)
+  int nchunks;      // K-chunks per unit: 128 B of k per row (K-major) or 64 k-rows (M-major)
+  int ks;           // K-chunks per ring stage (1, 2 or 4)
+  int nstage_chunks;  // ceil(nchunks / ks): ring stages per batch
   int a_boxes;      // 64-wide activation boxes per chunk: 1 (16-bit), 2 (int8), 4 (int4)
   int out_f32;      // 1: out is fp32, 0: out has the activation dtype
   int round_out;    // 1: round to nearest integer and clamp to [-128,127] before storing
@@ -51,10 +56,15 @@ struct alignas(64) StreamParams {
   void* z16;      // [b][N][R] 16-bit scratch (phase 1 activations when mix)
   unsigned* counters;  // [0],[1] grid barriers, [2] exit count, [3] status (0 ok)
   int stage_bytes;
+  int w_bytes;    // weight part of a stage: max over phases of ks * kSubBytes
   int nstages;
+  int debug;  // experiment switches (0 in production)
+  unsigned long long* timeline;  // optional: 16 time stamps per CTA (profiling aid), else nullptr
 };
 
 // Launches the kernel (cooperative launch, one CTA per SM).  is_bf16 selects the 16-bit type.
 int launch_stream(const StreamParams& p, int is_bf16, cudaStream_t stream);
+// Profiling aid: when set, every launch records %globaltimer stamps, 16 slots per CTA, at dev_ptr.
+void set_stream_timeline(unsigned long long* dev_ptr);
 
 }  // namespace blr

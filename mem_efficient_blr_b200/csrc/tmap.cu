@@ -1,6 +1,7 @@
 #include "tmap.h"
 
 #include <mutex>
+#include <unordered_map>
 #include <stdarg.h>
 #include <string.h>
 
@@ -34,8 +35,41 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoding a descriptor costs about a microsecond of host time and a call needs up to 18 of them, while
+// the same weights come back call after call: keep the encoded descriptors, keyed by everything
+// that went into them.
+struct TmapKey {
+  uint64_t v[10];
+  bool operator==(const TmapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < 10; ++i) {
+      h ^= k.v[i];
+      h *= 1099511628211ull;
+    }
+    return (size_t)h;
+  }
+};
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+static std::mutex g_tmap_mu;
+
 int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
                    const uint64_t strides[2], const uint32_t box[3], Swz swz) {
+  int dev = 0;
+  BLR_CUDA_OK(cudaGetDevice(&dev));
+  TmapKey key = {{(uint64_t)reinterpret_cast<uintptr_t>(base), dims[0], dims[1], dims[2], strides[0], strides[1],
+                  ((uint64_t)box[0] << 32) | box[1], ((uint64_t)box[2] << 32) | (uint64_t)dt, (uint64_t)swz,
+                  (uint64_t)dev}};
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *map = it->second;
+      return BLR_OK;
+    }
+  }
   EncodeTiledFn fn = get_encode_fn();
   BLR_REQUIRE(fn != nullptr, BLR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   BLR_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, BLR_ERR_ALIGN, "tensor base %p is not 16-byte aligned", base);
@@ -55,6 +89,11 @@ int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, c
               "cuTensorMapEncodeTiled failed (%d): dims=(%llu,%llu,%llu) strides=(%llu,%llu) box=(%u,%u,%u)", (int)r,
               (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
               (unsigned long long)strides[0], (unsigned long long)strides[1], box[0], box[1], box[2]);
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    if (g_tmap_cache.size() > 16384) g_tmap_cache.clear();
+    g_tmap_cache.emplace(key, *map);
+  }
   return BLR_OK;
 }
 
