@@ -98,7 +98,14 @@ static void finish_params(StreamParams& p, int64_t N) {
   }
   p.w_bytes = wmax;
   p.stage_bytes = wmax + amax;
-  const int budget = 232448 - kStreamTailBytes;
+  p.mix_bytes = 0;
+  if (p.mix) {
+    // the coupling keeps [b][nv] vectors of 8 floats per CTA; nv = its share of the N*R/8 vectors
+    const long long nvec = ((long long)N * p.R) / 8;
+    const long long nv_max = nvec / 128 + 2;  // grids have at least 128 CTAs on the parts this targets
+    p.mix_bytes = (int)(((long long)p.b * nv_max * 32 + 1023) / 1024 * 1024);
+  }
+  const int budget = 232448 - kStreamTailBytes - p.mix_bytes;
   int nst = budget / p.stage_bytes;
   p.nstages = nst > 16 ? 16 : nst;
 }

@@ -199,32 +199,79 @@ __device__ __forceinline__ uint32_t pack16x2(float a, float b) {
 __device__ __forceinline__ float round_clamp_i8(float v) { return fminf(fmaxf(rintf(v), -128.f), 127.f); }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
 
+// Share of the (n, r) plane this CTA couples: [lo, hi) in units of 8 consecutive r.
+__device__ __forceinline__ void couple_range(const StreamParams& p, int& lo, int& hi) {
+  const int nvec = (int)(((long long)p.N * p.R) >> 3);
+  lo = (int)(((long long)nvec * blockIdx.x) / gridDim.x);
+  hi = (int)(((long long)nvec * (blockIdx.x + 1)) / gridDim.x);
+}
+__device__ __forceinline__ bool couple_vectorised(const StreamParams& p) {
+  return p.s_r == 1 && (p.R & 7) == 0 && (p.s_i & 7) == 0 && (p.s_j & 7) == 0 && p.b <= 16;
+}
+// The coupling factors of a thread's first work item: S does not depend on the grid barrier, so they are
+// fetched before the thread waits at it.
+struct CoupleRegs {
+  uint4 s[16];
+};
+__device__ __forceinline__ void couple_item(const StreamParams& p, int e, int nv, int lo, int& i, long long& pt, int& r) {
+  const int v = e % nv;
+  i = e / nv;
+  pt = (long long)(lo + v) << 3;
+  r = (int)(pt % p.R);
+}
+__device__ __forceinline__ void couple_preload(const StreamParams& p, int ctid, CoupleRegs& cr) {
+  if (!couple_vectorised(p)) return;
+  int lo, hi;
+  couple_range(p, lo, hi);
+  const int nv = hi - lo;
+  if (ctid >= nv * p.b) return;
+  int i, r;
+  long long pt;
+  couple_item(p, ctid, nv, lo, i, pt, r);
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    if (j < p.b) cr.s[j] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.S) + i * p.s_i + j * p.s_j + r));
+}
+
 // BLAST coupling z[i][n][r] = sum_j S[i][j][r] * y[j][n][r] for this CTA's share of the (n, r) points.
+// y was written by other CTAs before the grid barrier (the acquire at the barrier makes plain loads see
+// it).  The CTA first copies its slice of y into shared memory (ybuf, [b][nv] vectors of 8 floats), so
+// that the b threads sharing a y vector read it from there, and every global load of the phase is
+// issued in one go.
 template <bool BF16>
-__device__ __forceinline__ void couple(const StreamParams& p, int ctid) {
+__device__ __forceinline__ void couple(const StreamParams& p, int ctid, const CoupleRegs& cr, float4* ybuf) {
   const long long plane = (long long)p.N * p.R;
   const int bb = p.b;
-  if (p.s_r == 1 && (p.R & 7) == 0 && (p.s_i & 7) == 0 && (p.s_j & 7) == 0) {
-    // rank index contiguous in S: one thread per (out block, 8 consecutive r)
-    const int nvec = (int)(plane >> 3);
-    const int lo = (int)(((long long)nvec * blockIdx.x) / gridDim.x);
-    const int hi = (int)(((long long)nvec * (blockIdx.x + 1)) / gridDim.x);
-    const int nv = hi - lo;
+  int lo, hi;
+  couple_range(p, lo, hi);
+  if (couple_vectorised(p) && (long long)bb * (hi - lo) * 32 <= p.mix_bytes) {
+    const int nv = hi - lo, nq = nv * 2;  // float4 per in-block
+    const float* ysrc = p.y32 + ((long long)lo << 3);
+    for (int e = ctid; e < bb * nq; e += kConsumerWarps * 32) {
+      const int j = e / nq, q = e - j * nq;
+      ybuf[e] = *reinterpret_cast<const float4*>(ysrc + j * plane + q * 4);
+    }
+    consumer_bar();
     for (int e = ctid; e < nv * bb; e += kConsumerWarps * 32) {
-      const int v = e % nv, i = e / nv;
-      const long long pt = (long long)(lo + v) << 3;
-      const int r = (int)(pt % p.R);
+      int i, r;
+      long long pt;
+      couple_item(p, e, nv, lo, i, pt, r);
+      const int v = e % nv;
       float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 16
-      for (int j = 0; j < bb; ++j) {
-        const uint4 sv = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.S) + i * p.s_i + j * p.s_j + r));
-        const float4 y0 = __ldcg(reinterpret_cast<const float4*>(p.y32 + j * plane + pt));
-        const float4 y1 = __ldcg(reinterpret_cast<const float4*>(p.y32 + j * plane + pt + 4));
-        const float2 s0 = unpack16x2<BF16>(sv.x), s1 = unpack16x2<BF16>(sv.y), s2 = unpack16x2<BF16>(sv.z), s3 = unpack16x2<BF16>(sv.w);
-        s[0] = fmaf(s0.x, y0.x, s[0]); s[1] = fmaf(s0.y, y0.y, s[1]);
-        s[2] = fmaf(s1.x, y0.z, s[2]); s[3] = fmaf(s1.y, y0.w, s[3]);
-        s[4] = fmaf(s2.x, y1.x, s[4]); s[5] = fmaf(s2.y, y1.y, s[5]);
-        s[6] = fmaf(s3.x, y1.z, s[6]); s[7] = fmaf(s3.y, y1.w, s[7]);
+      const bool pre = e == ctid;  // first item: factors already in registers
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < bb) {
+          uint4 w;
+          if (pre) w = cr.s[j];
+          else w = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.S) + i * p.s_i + j * p.s_j + r));
+          const float4 ya = ybuf[(j * nv + v) * 2], yb = ybuf[(j * nv + v) * 2 + 1];
+          const float2 s0 = unpack16x2<BF16>(w.x), s1 = unpack16x2<BF16>(w.y), s2 = unpack16x2<BF16>(w.z), s3 = unpack16x2<BF16>(w.w);
+          s[0] = fmaf(s0.x, ya.x, s[0]); s[1] = fmaf(s0.y, ya.y, s[1]);
+          s[2] = fmaf(s1.x, ya.z, s[2]); s[3] = fmaf(s1.y, ya.w, s[3]);
+          s[4] = fmaf(s2.x, yb.x, s[4]); s[5] = fmaf(s2.y, yb.y, s[5]);
+          s[6] = fmaf(s3.x, yb.z, s[6]); s[7] = fmaf(s3.y, yb.w, s[7]);
+        }
       }
       if (p.round_z) {
 #pragma unroll
@@ -238,15 +285,15 @@ __device__ __forceinline__ void couple(const StreamParams& p, int ctid) {
   } else {
     // generic strides (e.g. S stored (R, b_out, b_in)): one thread per (point, out block)
     const int NR = (int)plane;
-    const int lo = (int)(((long long)NR * blockIdx.x) / gridDim.x);
-    const int hi = (int)(((long long)NR * (blockIdx.x + 1)) / gridDim.x);
-    const int npts = hi - lo;
+    const int plo = (int)(((long long)NR * blockIdx.x) / gridDim.x);
+    const int phi = (int)(((long long)NR * (blockIdx.x + 1)) / gridDim.x);
+    const int npts = phi - plo;
     for (int e = ctid; e < npts * bb; e += kConsumerWarps * 32) {
-      const int i = e % bb, nr = lo + e / bb, r = nr % p.R;
+      const int i = e % bb, nr = plo + e / bb, r = nr % p.R;
       float s = 0.f;
 #pragma unroll 8
       for (int j = 0; j < bb; ++j)
-        s = fmaf(load16<BF16>(p.S, i * p.s_i + j * p.s_j + r * p.s_r), __ldcg(p.y32 + j * plane + nr), s);
+        s = fmaf(load16<BF16>(p.S, i * p.s_i + j * p.s_j + r * p.s_r), p.y32[j * plane + nr], s);
       if (p.round_z) s = round_clamp_i8(s);
       store16<BF16>(p.z16, i * plane + nr, s);
     }
@@ -261,7 +308,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t NST = p.nstages, stage_bytes = p.stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NST * stage_bytes);  // full[16], empty[16]
+  float4* ybuf = reinterpret_cast<float4*>(smem + (size_t)NST * stage_bytes);                       // coupling scratch
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NST * stage_bytes + p.mix_bytes);  // full[16], empty[16]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * 16);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 16);
 
@@ -448,20 +496,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
       if (phs + 1 < p.nphases) {
         // bar.sync orders the CTA's stores before thread 0; its gpu-scope release is cumulative over them
         consumer_bar();
-        if (ctid == 0) {
-          fence_proxy_async();
-          red_release_gpu_add(p.counters + 0, 1u);
-        }
+        if (ctid == 0) red_release_gpu_add(p.counters + 0, 1u);
         if (p.mix) {
+          CoupleRegs cr;
+          couple_preload(p, ctid, cr);
           if (ctid == 0) {
             if (!wait_counter(p.counters + 0, gridDim.x, abort_flag)) ok = false;
           }
           consumer_bar();
           if (ctid == 0) BLR_STAMP(5);  // grid barrier 0 passed
-          if (!*abort_flag) couple<BF16>(p, ctid);
+          if (!*abort_flag) couple<BF16>(p, ctid, cr, ybuf);
           consumer_bar();
           if (ctid == 0) {
-            fence_proxy_async();
             red_release_gpu_add(p.counters + 1, 1u);
             BLR_STAMP(6);  // coupling written
           }
@@ -501,7 +547,7 @@ static int launch_impl(const StreamParams& p, cudaStream_t stream) {
   int rc = device_info(&di);
   if (rc != BLR_OK) return rc;
   BLR_REQUIRE(di.coop, BLR_ERR_UNSUPPORTED, "device does not support cooperative launch");
-  const size_t smem = (size_t)p.nstages * p.stage_bytes + kStreamTailBytes;
+  const size_t smem = (size_t)p.nstages * p.stage_bytes + p.mix_bytes + kStreamTailBytes;
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
   auto kern = blr_stream_kernel<BF16, NT>;
