@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the structured-matmul hot path on B200.
+
+Headline workload (the configuration the metric is quoted on): symmetric-quantised BLAST decode on the
+Llama-7B gate_proj shape, 4096 -> 11008, b = 16, R = 1024, int8 and packed-int4 factors with fp16
+per-channel scales, token counts 1, 4 and 16.  One *step* runs every (bits, N) point once over a
+rotating set of weight replicas whose total footprint exceeds the L2 cache, so every launch streams
+its weights from HBM.  The metric is algorithmic bytes per second (weights + scales + S + x + out of
+every launch, divided by device time), summed over ranks.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With N > 1 launch under torchrun; every rank runs the same workload on its own GPU (independent
+token batches, replicated weights: weak scaling, no collective in the data path).
+`--impl reference` times the CPU restatement of the reference's torch path on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+I_F, O_F, B_BLK, RANK = 4096, 11008, 16, 1024
+P_BLK, Q_BLK = I_F // B_BLK, O_F // B_BLK
+POINTS = [(8, 1), (8, 4), (8, 16), (4, 1), (4, 4), (4, 16)]  # (bits, tokens)
+L2_BYTES = 126 * 2 ** 20
+
+
+def algorithmic_bytes(bits: int, n: int) -> float:
+    """bytes = wb*R*(I+O) + 2*b^2*R + 2*N*(I+O) + scale bytes, wb = bits/8."""
+    return bits / 8 * RANK * (I_F + O_F) + 2 * B_BLK * B_BLK * RANK + 2 * n * (I_F + O_F) + 2 * (B_BLK * Q_BLK + B_BLK * RANK)
+
+
+def peak_hbm_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+# ------------------------------------------------------------------------------------------ reference arm (CPU)
+def cpu_reference_times(threads: int, iters: int):
+    """Times the CPU restatement of torch_blast_baseline (fp32, dequantised factors) per (bits, N) point."""
+    from oracle import blr_oracle as orc
+    torch.set_num_threads(threads)
+    out = {}
+    x16, U, Vt, S = orc.make_blast_inputs(16, I_F, O_F, B_BLK, RANK, torch.float16, seed=0)
+    for bits in (8, 4):
+        Uq, us = orc.quantize_sym(U, bits)
+        Vq, vs = orc.quantize_sym(Vt, bits)
+        Ud, Vd = orc.dequantize_sym(Uq, us, bits), orc.dequantize_sym(Vq, vs, bits)
+        Sf = S.float()
+        for n in (1, 4, 16):
+            x = x16[:, :n].float()
+            orc.blast(x, Ud, Vd, Sf)
+            ts = []
+            for _ in range(iters):
+                t0 = time.perf_counter()
+                orc.blast(x, Ud, Vd, Sf)
+                ts.append(time.perf_counter() - t0)
+            out[(bits, n)] = statistics.median(ts)
+    return out
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    iters = max(3, min(10, args.steps))
+    # warm-up happens inside cpu_reference_times (one untimed call per point)
+    t0 = time.perf_counter()
+    times = cpu_reference_times(threads, iters)
+    total_bytes = sum(algorithmic_bytes(b, n) for b, n in POINTS)
+    step_s = sum(times[p] for p in POINTS)
+    value = total_bytes / step_s / 1e9
+    line = {
+        "impl": "reference", "metric": "blast_wq_decode_algorithmic_GBps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": iters, "warmup": 1, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(1),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{iters} timed calls per (bits, tokens) point of the CPU restatement of torch_blast_baseline "
+                                   "on dequantised fp32 factors (the reference has no weight-quantised path)"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "us_per_layer": {f"int{b}_n{n}": times[(b, n)] * 1e6 for b, n in POINTS},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(replicas_note):
+    return {"workload": "symmetric-quantised BLAST decode, Llama-7B gate_proj 4096->11008, b=16, R=1024, "
+                        "int8 and packed-int4 factors with fp16 per-channel scales, tokens 1/4/16 (one launch per point per replica)",
+            "in_features": I_F, "out_features": O_F, "blocks": B_BLK, "rank": RANK,
+            "points": [f"int{b}/N={n}" for b, n in POINTS],
+            "l2_policy": "weights rotate over replicas whose footprint exceeds L2 (inputs larger than L2)",
+            "replicas": replicas_note}
+
+
+# ------------------------------------------------------------------------------------------ our arm (GPU)
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
+    from mem_efficient_blr_b200 import _lib
+
+    # ---- synthetic factors with the headline configuration's distributions:
+    # U, Vt ~ N(0, 1/sqrt(fan_in)), S ~ U(0.5, 1.5), x ~ N(0, 1), fp16, seeded per rank
+    g = torch.Generator().manual_seed(rank)
+    U = (torch.randn(B_BLK, Q_BLK, RANK, generator=g) / RANK ** 0.5).half()
+    Vt = (torch.randn(B_BLK, RANK, P_BLK, generator=g) / P_BLK ** 0.5).half()
+    S = (torch.rand(B_BLK, B_BLK, RANK, generator=g) + 0.5).half()
+    x16 = torch.randn(1, 16, I_F, generator=g).half()
+    Ud, Vd, Sd = U.to(dev), Vt.to(dev), S.to(dev)
+    reps = {}
+    for bits in (8, 4):
+        q = bq.quantize_blast_factors(Ud, Vd, bits)
+        per = sum(t.numel() * t.element_size() for t in q)
+        nrep = int(2 * L2_BYTES // per) + 1
+        reps[bits] = [tuple(t.clone() for t in q) for _ in range(nrep)]
+    xs = {n: x16[0, :n].contiguous().to(dev) for n in (1, 4, 16)}
+    xs_host = {n: x16[0, :n].contiguous().pin_memory() for n in (1, 4, 16)}
+    outs_host = {n: torch.empty(n, O_F, dtype=torch.float16).pin_memory() for n in (1, 4, 16)}
+
+    def launch_all():
+        count = 0
+        for bits, n in POINTS:
+            for q in reps[bits]:
+                bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
+                count += 1
+        return count
+
+    if args.ncu_case:
+        # small case for a profiler capture: a few eager launches of one point over distinct replicas
+        bits, n = (int(t) for t in args.ncu_case.split(":"))
+        for q in reps[bits][:6]:
+            bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
+        torch.cuda.synchronize()
+        _lib.workspace_status(dev)
+        print(json.dumps({"ncu_case": args.ncu_case, "launches": 6}))
+        return
+
+    launches_per_step = launch_all()
+    torch.cuda.synchronize()
+    bytes_per_step = sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS)
+
+    # ---- capture one step in a CUDA graph (the per-launch host work would otherwise bound the rate)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        launch_all()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            launch_all()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        barrier()
+    step_ms = e0.elapsed_time(e1) / args.steps
+    _lib.workspace_status(dev)
+    if dist is not None:
+        t = torch.tensor([step_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms = float(t.item())
+    value = world * bytes_per_step / (step_ms * 1e-3) / 1e9
+
+    # ---- per-point detail (separate timed loops, same graph technique)
+    sweep = {}
+    if rank == 0:
+        for bits, n in POINTS:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for q in reps[bits]:
+                        bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
+            torch.cuda.synchronize()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                g.replay()
+            b_.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b_) * 1e3 / (10 * len(reps[bits]))
+            sweep[f"int{bits}_n{n}"] = {"us_per_layer": us, "GBps": algorithmic_bytes(bits, n) / us / 1e3}
+
+    # ---- end to end through the public Python operator, host buffers in and out every launch
+    def e2e_step():
+        for bits, n in POINTS:
+            for q in reps[bits]:
+                xd = xs_host[n].to(dev, non_blocking=True)
+                y = bq.blast_wq(xd, q[0], q[1], q[2], q[3], Sd, bits)
+                outs_host[n].copy_(y, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = sum(2 * n * I_F * len(reps[b]) for b, n in POINTS)
+    d2h = sum(2 * n * O_F * len(reps[b]) for b, n in POINTS)
+
+    if rank == 0:
+        peak, peak_kind = peak_hbm_gbs()
+        achieved = bytes_per_step / (step_ms * 1e-3) / 1e9  # per GPU: algorithmic bytes / launch time
+        cpu = None
+        if world == 1:
+            threads = os.cpu_count() or 1
+            times = cpu_reference_times(threads, 5)
+            cpu_s = sum(times[p] for p in POINTS)
+            cpu = {"value": sum(algorithmic_bytes(b, n) for b, n in POINTS) / cpu_s / 1e9, "unit": "GB/s", "cores": threads,
+                   "kind": "port", "sample": "5 timed calls per (bits, tokens) point of the CPU restatement of "
+                                             "torch_blast_baseline on dequantised fp32 factors"}
+        line = {
+            "metric": "blast_wq_decode_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations, s8/s4 weights, f32 accumulate",
+            "data": "synthetic",
+            "config": workload_config({f"int{b}": len(reps[b]) for b in (8, 4)}),
+            "gpu_launches": launches_per_step * args.steps,
+            "us_per_layer_mean": step_ms * 1e3 / launches_per_step,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": None, "kernel": "blr_stream_kernel"},
+            "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "cpu_baseline": cpu,
+            "clocks": clk.summary(),
+            "sweep": sweep,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager launches of one point and exit (for profiler captures)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
