@@ -34,6 +34,7 @@ I_F, O_F, B_BLK, RANK = 4096, 11008, 16, 1024
 P_BLK, Q_BLK = I_F // B_BLK, O_F // B_BLK
 POINTS = [(8, 1), (8, 4), (8, 16), (4, 1), (4, 4), (4, 16)]  # (bits, tokens)
 L2_BYTES = 126 * 2 ** 20
+NCU_TRAFFIC_INT8_N16 = 16.249e6  # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu)
 
 
 def algorithmic_bytes(bits: int, n: int) -> float:
@@ -306,7 +307,10 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps,
             "us_per_layer_mean": step_ms * 1e3 / launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": None, "kernel": "blr_stream_kernel"},
+                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_INT8_N16, "kernel": "blr_stream_kernel",
+                         "traffic_note": "dram read+write bytes of one int8/N=16 launch from an ncu capture "
+                                         "(profiles/blr_stream_kernel_blast_wq_decode.md); algorithmic bytes of that point: "
+                                         f"{algorithmic_bytes(8, 16):.0f}"},
             "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "cpu_baseline": cpu,
