@@ -1,0 +1,145 @@
+"""GPU parity of the tensor-core pipeline (more than 16 tokens) against the CPU oracle, through the C ABI.
+
+Tolerance: relative Frobenius error <= 1e-2 against the fp32 oracle on the same 16-bit inputs.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import blr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import mem_efficient_blr_b200.blast_kernels as bk
+    import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
+    import mem_efficient_blr_b200.dense_kernels as dk
+    import mem_efficient_blr_b200.low_rank_kernels as lk
+    import mem_efficient_blr_b200.monarch_kernels as mk
+
+    class NS:
+        pass
+
+    ns = NS()
+    ns.bk, ns.bq, ns.dk, ns.lk, ns.mk = bk, bq, dk, lk, mk
+    return ns
+
+
+def _cuda(*ts):
+    return [t.to(DEV) for t in ts]
+
+
+def _err(got, ref):
+    torch.cuda.synchronize()
+    return orc.rel_fro(got.float().cpu(), ref)
+
+
+BLAST_SHAPES = [
+    # N, I, O, b, R
+    (17, 256, 384, 4, 128),
+    (197, 768, 2304, 3, 128),      # the reference's ViT-B setting (b = 3, fused qkv)
+    (197, 768, 3072, 16, 192),
+    (128, 4096, 11008, 16, 1024),  # headline layer, 128 tokens
+    (2048, 4096, 11008, 16, 1024),
+    (129, 11008, 4096, 16, 1488),  # down_proj at the reference's 50 %-parameter rank, ragged token count
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", BLAST_SHAPES)
+def test_blast_prefill_all_layout_families(K, shape, dtype):
+    N, I, O, b, R = shape
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, dtype, seed=N % 97)
+    ref, _, _ = orc.blast(x, U, Vt, S)
+    xd, Ud, Vtd, Sd = _cuda(x, U, Vt, S)
+    got = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+    assert got.shape == ref.shape and got.dtype == dtype
+    assert _err(got, ref) < TOL
+    Up, Vp, Sp = _cuda(*orc.blast_to_partial_layout(U, Vt, S))
+    assert _err(K.bk.triton_blast_partial_grouped_fp16(xd, Up, Vp, Sp), ref) < TOL
+    assert _err(K.bk.triton_blast_full_fp16(xd, Up, Vp, Sp), ref) < TOL
+    Ub, Vb, Sb = _cuda(*orc.blast_to_bmm_layout(U, Vt, S))
+    assert _err(K.bk.triton_blast_bmm_fp16(xd, Ub, Vb, Sb), ref) < TOL
+
+
+def test_blast_reference_golden_vector_17_tokens(K, golden_dir):
+    g = {k: torch.from_numpy(v) for k, v in np.load(os.path.join(golden_dir, "blast_c.npz")).items()}
+    x, U, Vt, S = (g[k].to(torch.bfloat16) for k in ("x", "U", "Vt", "S"))
+    ref, _, _ = orc.blast(x, U, Vt, S)
+    got = K.bk.blast_torch_layout(*_cuda(x, U, Vt, S))
+    assert got.shape == g["out"].shape
+    assert _err(got, ref) < TOL
+    assert _err(got, g["out"]) < 3e-2  # vs the reference's own fp32 output (inputs rounded to bf16 here)
+
+
+def test_blast_act_int8_prefill(K):
+    x, U, Vt, S = orc.make_blast_inputs(64, 512, 768, 4, 128, torch.bfloat16, seed=21)
+    x = x * 4
+    ref, _, _ = orc.blast_act_int8(x, U, Vt, S)
+    Ub, Vb, Sb = _cuda(*orc.blast_to_bmm_layout(U, Vt, S))
+    assert _err(K.bq.triton_blast_bmm_int8_fp16(x.to(DEV), Ub, Vb, Sb), ref) < 3e-2
+
+
+def test_quantised_blast_rejects_more_than_16_tokens(K):
+    x, U, Vt, S = orc.make_blast_inputs(32, 512, 768, 4, 128, torch.float16, seed=2)
+    Uq, us, Vq, vs = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), 8)
+    with pytest.raises(RuntimeError, match="quantised factors"):
+        K.bq.blast_wq(x.to(DEV), Uq, us, Vq, vs, S.to(DEV), 8)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(33, 256, 512, 4, 64), (197, 768, 3072, 4, 768), (128, 4096, 4096, 16, 1024),
+                                   (2048, 4096, 11008, 16, 1536)])
+def test_monarch_prefill_all_variants(K, shape, dtype):
+    N, I, O, b, rank = shape
+    x, w1_t, w2_t = orc.make_monarch_inputs(N, I, O, b, rank, dtype, seed=N % 89)
+    ref = orc.monarch(x, w1_t, w2_t)[0]
+    xd = x.to(DEV)
+    assert _err(K.mk.monarch_torch_layout(xd, w1_t.to(DEV), w2_t.to(DEV)), ref) < TOL
+    w1k = orc.monarch_w1_to_kernel_layout(w1_t).to(DEV)
+    assert _err(K.mk.triton_monarch_right_fp16(xd, w1k, w2_t.to(DEV)), ref) < TOL
+    assert _err(K.mk.triton_monarch_right_left_fp16(xd, w1k, orc.monarch_w2_to_left_layout(w2_t).to(DEV)), ref) < TOL
+    assert _err(K.mk.triton_monarch_right_ideal_fp16(xd, w1k, w2_t.to(DEV)), orc.monarch_ideal_order(ref, b)) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(17, 256, 384, 64), (128, 4096, 11008, 1024), (2048, 11008, 4096, 1024)])
+def test_low_rank_prefill(K, shape, dtype):
+    N, I, O, R = shape
+    x, Vt, Ut = orc.make_low_rank_inputs(N, I, O, R, dtype, seed=N % 83)
+    ref, _ = orc.low_rank(x, Vt, Ut)
+    assert _err(K.lk.low_rank_torch_layout(*_cuda(x, Vt, Ut)), ref) < TOL
+    got = K.lk.triton_low_rank_fp16(x.to(DEV), Vt.t().contiguous().to(DEV), Ut.t().contiguous().to(DEV))
+    assert got.shape == (N, O) and _err(got, ref.reshape(N, O)) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(17, 256, 384), (200, 512, 1000), (2048, 4096, 11008)])
+def test_dense_prefill(K, shape, dtype):
+    N, I, O = shape
+    x, Wt = orc.make_dense_inputs(N, I, O, dtype, seed=N % 79)
+    ref = orc.dense(x, Wt)
+    assert _err(K.dk.dense_torch_layout(*_cuda(x, Wt)), ref) < TOL
+    got = K.dk.triton_dense_fp16(x.to(DEV), Wt.t().contiguous().to(DEV))
+    assert got.shape == (N, O) and _err(got, ref.reshape(N, O)) < TOL
+
+
+def test_linearity_at_full_size(K):
+    """Size-independent property at the headline size: f(a*x1 + x2) = a*f(x1) + f(x2) within rounding."""
+    N, I, O, b, R = 2048, 4096, 11008, 16, 1024
+    x1, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=5)
+    x2 = torch.randn(1, N, I, generator=torch.Generator().manual_seed(6)).half()
+    Ud, Vtd, Sd = _cuda(U, Vt, S)
+    f = lambda t: K.bk.blast_torch_layout(t.to(DEV), Ud, Vtd, Sd).float()
+    lhs = f((0.5 * x1.float() + x2.float()).half())
+    rhs = 0.5 * f(x1) + f(x2)
+    torch.cuda.synchronize()
+    assert orc.rel_fro(lhs.cpu(), rhs.cpu()) < 5e-3
