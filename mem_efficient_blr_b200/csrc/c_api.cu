@@ -16,6 +16,7 @@ struct Workspace {
   unsigned* counters;
   void* region_a;  // 4 bytes per intermediate element
   void* region_b;  // 2 bytes per intermediate element
+  void* region_c;  // expanded coupling factors (only sized for more than 16 tokens)
 };
 
 static int carve(void* ws, size_t ws_bytes, int64_t N, int64_t groups, int64_t width, Workspace* w) {
@@ -27,6 +28,7 @@ static int carve(void* ws, size_t ws_bytes, int64_t N, int64_t groups, int64_t w
   w->counters = reinterpret_cast<unsigned*>(p);
   w->region_a = p + kCtrlBytes;
   w->region_b = p + kCtrlBytes + align256((size_t)groups * N * width * 4);
+  w->region_c = static_cast<uint8_t*>(w->region_b) + align256((size_t)groups * N * width * 2);
   return BLR_OK;
 }
 
@@ -156,7 +158,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   BLR_REQUIRE(u_bits == 16 && v_bits == 16, BLR_ERR_UNSUPPORTED,
               "quantised factors are implemented for up to %d tokens per call", kStreamMaxTokens);
   return pipeline_blast(x, ldx, N, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b, P, Q, R, act8, out, ldo,
-                        w.region_a, w.region_b, stream);
+                        w.region_a, w.region_b, w.region_c, stream);
 }
 
 }  // namespace blr
@@ -175,7 +177,9 @@ const char* blr_last_error(void) { return blr::last_error(); }
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
   if (n_tokens < 0 || groups < 0 || width < 0) return 0;
   const size_t e = (size_t)groups * (size_t)n_tokens * (size_t)width;
-  return kCtrlBytes + align256(e * 4) + align256(e * 2);
+  // above 16 tokens BLAST also keeps its expanded coupling factors: (width / 16) matrices of (16 groups)^2 16-bit values
+  const size_t c = n_tokens > 16 ? (size_t)groups * groups * ((size_t)width + 16) * 32 : 0;
+  return kCtrlBytes + align256(e * 4) + align256(e * 2) + align256(c);
 }
 
 int blr_workspace_init(void* ws, size_t ws_bytes, void* stream) {

@@ -1,5 +1,6 @@
 // Tensor-core pipeline for more than 16 tokens: grouped tcgen05 GEMMs (umma_gemm.cu) chained through
-// 16-bit intermediates, plus the BLAST coupling kernel between the two GEMMs.
+// 16-bit intermediates; the BLAST coupling between the two GEMMs is itself a grouped GEMM (see
+// expand_coupling_kernel).
 #include "pipeline.h"
 
 #include <cuda_bf16.h>
@@ -38,7 +39,7 @@ static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, c
     BLR_REQUIRE(K % 8 == 0, BLR_ERR_SHAPE, "contraction length %d must be a multiple of 8", K);
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)G};
     const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * K * 2};
-    const uint32_t box[3] = {64, 128, 1};
+    const uint32_t box[3] = {64, (uint32_t)umma_w_tile_rows(p), 1};
     rc = encode_tmap_3d(&p.tmW, dt16(dtype), W, dims, str, box, Swz::B128);
   } else {
     BLR_REQUIRE(M % 8 == 0, BLR_ERR_SHAPE, "block output width %d must be a multiple of 8", M);
@@ -52,27 +53,12 @@ static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, c
               (long long)ld_n, (long long)ld_g);
   const uint64_t adims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)G};
   const uint64_t astr[2] = {(uint64_t)ld_n * 2, (uint64_t)(G > 1 ? ld_g : ld_n * N) * 2};
-  const uint32_t abox[3] = {64, (uint32_t)p.bn, 1};
+  const uint32_t abox[3] = {64, (uint32_t)umma_a_tile_rows(p), 1};
   if ((rc = encode_tmap_3d(&p.tmA, dt16(dtype), A, adims, astr, abox, Swz::B128))) return rc;
   return launch_umma_gemm(p, stream);
 }
 
 // ------------------------------------------------------------------------------------------ BLAST coupling
-// z[i][n][r] = sum_j S[i][j][r] * y[j][n][r], y and z 16-bit [b][N][R].
-// A block owns 64 consecutive r and a range of tokens; its slice of S sits in shared memory as fp32-ready
-// 16-bit [i][j][64].  Thread = (8-wide r vector, group of 4 out-blocks, token lane).
-template <typename T>
-__device__ __forceinline__ float2 up2(uint32_t w);
-template <>
-__device__ __forceinline__ float2 up2<__half>(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
-template <>
-__device__ __forceinline__ float2 up2<__nv_bfloat16>(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w)); }
-template <typename T>
-__device__ __forceinline__ uint32_t pk2(float a, float b);
-template <>
-__device__ __forceinline__ uint32_t pk2<__half>(float a, float b) { const __half2 v = __floats2half2_rn(a, b); return *reinterpret_cast<const uint32_t*>(&v); }
-template <>
-__device__ __forceinline__ uint32_t pk2<__nv_bfloat16>(float a, float b) { const __nv_bfloat162 v = __floats2bfloat162_rn(a, b); return *reinterpret_cast<const uint32_t*>(&v); }
 template <typename T>
 __device__ __forceinline__ float ld1(const T* p);
 template <>
@@ -80,62 +66,30 @@ __device__ __forceinline__ float ld1<__half>(const __half* p) { return __half2fl
 template <>
 __device__ __forceinline__ float ld1<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
-template <typename T>
-__global__ void __launch_bounds__(256) blast_couple_kernel(const T* __restrict__ y, const T* __restrict__ S, long long s_i,
-                                                          long long s_j, long long s_r, T* __restrict__ z, int b, int N, int R,
-                                                          int tokens_per_block, int round_z) {
-  extern __shared__ __align__(16) uint8_t sm[];
-  T* sS = reinterpret_cast<T*>(sm);  // [b][b][64]
-  const int r0 = blockIdx.x * 64, n_begin = blockIdx.y * tokens_per_block;
-  const int n_end = min(N, n_begin + tokens_per_block);
-  const int rw = min(64, R - r0);
-  for (int e = threadIdx.x; e < b * b * 64; e += blockDim.x) {
-    const int rr = e & 63, ij = e >> 6, i = ij / b, j = ij - i * b;
-    sS[e] = rr < rw ? S[i * s_i + j * s_j + (long long)(r0 + rr) * s_r] : T(0.f);
-  }
-  __syncthreads();
-  const int IG = (b + 3) / 4;
-  const int vec = threadIdx.x & 7, ig = (threadIdx.x >> 3) % IG, nl = threadIdx.x / (8 * IG);
-  const int n_par = blockDim.x / (8 * IG);
-  if (nl >= n_par || vec * 8 >= rw) return;
-  const long long plane = (long long)N * R;
-  for (int n = n_begin + nl; n < n_end; n += n_par) {
-    float acc[4][8];
+// Expanded coupling factors: for every group of GS consecutive r (GS = 16, or 8 when R is not a multiple of
+// 16), the (GS*b x GS*b) matrix
+//     E[g][(i, r')][(j, r'')] = S[i][j][GS*g + r'] if r' == r'' else 0
+// so that z[i][n][GS*g + r'] = sum_{(j, r'')} E[g][(i, r')][(j, r'')] * y[j][n][GS*g + r''] is one grouped GEMM with
+// K = GS*b on the tensor cores.  All but 1/GS of the products are with zeros; the coupling stays bound by the
+// y / z traffic.  GS = 16 makes every contiguous piece of y' and z a full 32-byte sector.
+template <typename T, int GS>
+__global__ void expand_coupling_kernel(const T* __restrict__ S, long long s_i, long long s_j, long long s_r,
+                                       T* __restrict__ E, int b, int R) {
+  // one thread per row (g, i, r'): b vectors of GS, each with a single non-zero at position r'
+  const int w = GS * b;
+  const long long rows = (long long)(R / GS) * w;
+  const long long row_id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row_id >= rows) return;
+  const int row = (int)(row_id % w), g = (int)(row_id / w), i = row / GS, r1 = row % GS;
+  T* dst = E + row_id * w;
+  const T* src = S + i * s_i + (long long)(GS * g + r1) * s_r;
+  for (int j = 0; j < b; ++j) {
+    alignas(16) T v[GS];
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
+    for (int k = 0; k < GS; ++k) v[k] = T(0.f);
+    v[r1] = src[j * s_j];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[a][k] = 0.f;
-    const T* yp = y + (long long)n * R + r0 + vec * 8;
-    for (int j = 0; j < b; ++j) {
-      const uint4 yv = *reinterpret_cast<const uint4*>(yp + j * plane);
-      const float2 y0 = up2<T>(yv.x), y1 = up2<T>(yv.y), y2 = up2<T>(yv.z), y3 = up2<T>(yv.w);
-#pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        const int i = ig * 4 + a;
-        if (i < b) {
-          const uint4 sv = *reinterpret_cast<const uint4*>(sS + ((i * b + j) << 6) + vec * 8);
-          const float2 s0 = up2<T>(sv.x), s1 = up2<T>(sv.y), s2 = up2<T>(sv.z), s3 = up2<T>(sv.w);
-          acc[a][0] = fmaf(s0.x, y0.x, acc[a][0]); acc[a][1] = fmaf(s0.y, y0.y, acc[a][1]);
-          acc[a][2] = fmaf(s1.x, y1.x, acc[a][2]); acc[a][3] = fmaf(s1.y, y1.y, acc[a][3]);
-          acc[a][4] = fmaf(s2.x, y2.x, acc[a][4]); acc[a][5] = fmaf(s2.y, y2.y, acc[a][5]);
-          acc[a][6] = fmaf(s3.x, y3.x, acc[a][6]); acc[a][7] = fmaf(s3.y, y3.y, acc[a][7]);
-        }
-      }
-    }
-#pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int i = ig * 4 + a;
-      if (i < b) {
-        if (round_z) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[a][k] = fminf(fmaxf(rintf(acc[a][k]), -128.f), 127.f);
-        }
-        uint4 o;
-        o.x = pk2<T>(acc[a][0], acc[a][1]); o.y = pk2<T>(acc[a][2], acc[a][3]);
-        o.z = pk2<T>(acc[a][4], acc[a][5]); o.w = pk2<T>(acc[a][6], acc[a][7]);
-        *reinterpret_cast<uint4*>(z + i * plane + (long long)n * R + r0 + vec * 8) = o;
-      }
-    }
+    for (int k = 0; k < GS / 8; ++k) *reinterpret_cast<uint4*>(dst + GS * j + 8 * k) = *reinterpret_cast<const uint4*>(v + 8 * k);
   }
 }
 
@@ -155,24 +109,23 @@ __global__ void blast_couple_generic_kernel(const T* __restrict__ y, const T* __
 }
 
 template <typename T>
-static int run_couple(const void* y, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* z, int b, int64_t N, int R,
-                      int round_z, cudaStream_t stream) {
-  if (b <= 16 && R % 8 == 0) {
-    const size_t smem = (size_t)b * b * 64 * sizeof(T);
-    // at most 16 * 16 * 64 * 2 = 32 KB: within the default dynamic shared-memory limit
-    const int rblocks = (R + 63) / 64;
-    int tokens_per_block = 128;
-    // enough blocks to fill the machine without shrinking the per-block reuse of S too far
-    while (tokens_per_block > 32 && (long long)rblocks * ((N + tokens_per_block - 1) / tokens_per_block) < 296) tokens_per_block /= 2;
-    dim3 grid(rblocks, (unsigned)((N + tokens_per_block - 1) / tokens_per_block));
-    BLR_REQUIRE(grid.y <= 65535, BLR_ERR_SHAPE, "too many tokens for the coupling kernel");
-    blast_couple_kernel<T><<<grid, 256, smem, stream>>>(static_cast<const T*>(y), static_cast<const T*>(S), s_i, s_j, s_r,
-                                                         static_cast<T*>(z), b, (int)N, R, tokens_per_block, round_z);
-  } else {
-    const long long NR = (long long)N * R;
-    blast_couple_generic_kernel<T><<<(unsigned)((NR + 255) / 256), 256, 0, stream>>>(
-        static_cast<const T*>(y), static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(z), b, NR, R, round_z);
-  }
+static int run_couple_generic(const void* y, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* z, int b, int64_t N,
+                              int R, int round_z, cudaStream_t stream) {
+  const long long NR = (long long)N * R;
+  blast_couple_generic_kernel<T><<<(unsigned)((NR + 255) / 256), 256, 0, stream>>>(
+      static_cast<const T*>(y), static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(z), b, NR, R, round_z);
+  BLR_CUDA_OK(cudaGetLastError());
+  return BLR_OK;
+}
+
+template <typename T>
+static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* E, int b, int R, int gs, cudaStream_t stream) {
+  const long long rows = (long long)(R / gs) * gs * b;
+  const unsigned blocks = (unsigned)((rows + 127) / 128);
+  if (gs == 16)
+    expand_coupling_kernel<T, 16><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, R);
+  else
+    expand_coupling_kernel<T, 8><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, R);
   BLR_CUDA_OK(cudaGetLastError());
   return BLR_OK;
 }
@@ -180,14 +133,29 @@ static int run_couple(const void* y, const void* S, int64_t s_i, int64_t s_j, in
 // ------------------------------------------------------------------------------------------ operators
 int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, const void* V,
                    int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R,
-                   int act_int8, void* out, int64_t ldo, void* y16, void* z16, cudaStream_t stream) {
+                   int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream) {
   const long long plane = (long long)N * R;
-  // y[j][n][r] = sum_p V[j][r][p] x[n][j*P + p]
-  int rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream);
-  if (rc) return rc;
-  rc = dtype == BLR_DTYPE_BF16 ? run_couple<__nv_bfloat16>(y16, S, s_i, s_j, s_r, z16, b, N, R, act_int8, stream)
-                               : run_couple<__half>(y16, S, s_i, s_j, s_r, z16, b, N, R, act_int8, stream);
-  if (rc) return rc;
+  const bool bf = dtype == BLR_DTYPE_BF16;
+  int rc;
+  if (b <= 16 && R % 8 == 0) {
+    // y'[n][r/GS][j][r%GS] = sum_p V[j][r][p] x[n][j*P + p]: the (j, r%GS) index is contiguous, ready to be the
+    // K dimension of the coupling GEMM
+    const int gs = R % 16 == 0 ? 16 : 8, w = gs * b;
+    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, gs, (long long)R * b, w, 1, gs, act_int8}, stream);
+    if (rc) return rc;
+    rc = bf ? run_expand<__nv_bfloat16>(S, s_i, s_j, s_r, e16, b, R, gs, stream) : run_expand<__half>(S, s_i, s_j, s_r, e16, b, R, gs, stream);
+    if (rc) return rc;
+    // z[i][n][GS*g + r'] = sum_k E[g][(i, r')][k] y'[n][g][k]
+    rc = run_gemm(dtype, e16, BLR_W_KMAJOR, R / gs, w, w, y16, N, (int64_t)R * b, w, OutSpec{z16, gs, R, plane, 1, gs, act_int8}, stream);
+    if (rc) return rc;
+  } else {
+    // y[j][n][r] = sum_p V[j][r][p] x[n][j*P + p]
+    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream);
+    if (rc) return rc;
+    rc = bf ? run_couple_generic<__nv_bfloat16>(y16, S, s_i, s_j, s_r, z16, b, N, R, act_int8, stream)
+            : run_couple_generic<__half>(y16, S, s_i, s_j, s_r, z16, b, N, R, act_int8, stream);
+    if (rc) return rc;
+  }
   // out[n][i*Q + q] = sum_r U[i][q][r] z[i][n][r]
   return run_gemm(dtype, U, u_layout, b, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
 }

@@ -237,13 +237,14 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= (uint64_t)2 << 61;  // 128-byte swizzle
   return d;
 }
-// Instruction descriptor, kind::f16: fp32 accumulator, A/B both f16 or both bf16, B always K-major.
-__device__ __forceinline__ uint32_t umma_idesc(bool bf16, bool a_mn_major, uint32_t M, uint32_t N) {
+// Instruction descriptor, kind::f16: fp32 accumulator, A/B both f16 or both bf16.
+__device__ __forceinline__ uint32_t umma_idesc(bool bf16, bool a_mn_major, bool b_mn_major, uint32_t M, uint32_t N) {
   uint32_t d = 0;
   d |= 1u << 4;                       // D format: f32
   d |= (bf16 ? 1u : 0u) << 7;         // A format
   d |= (bf16 ? 1u : 0u) << 10;        // B format
   d |= (a_mn_major ? 1u : 0u) << 15;  // A major
+  d |= (b_mn_major ? 1u : 0u) << 16;  // B major
   d |= (N >> 3) << 17;
   d |= (M >> 4) << 24;
   return d;

@@ -1,10 +1,13 @@
 // tcgen05 / TMEM grouped GEMM (sm_100a).  Persistent, one CTA per SM, warp-specialised:
-//   warp 0   TMA producer: weight tile (128 rows x 64 k, 16 KB) + token tile (bn tokens x 64 k) per stage
-//   warp 1   MMA issuer: one elected thread issues tcgen05.mma (M = 128, N = bn, K = 16) from shared-memory
-//            descriptors, accumulators double-buffered in TMEM (2 x bn columns)
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (one weight row per thread, tokens along the columns),
-//            convert and scatter to the output mapping
+//   warp 0    TMA producer: per stage one 128-row tile (16 KB) of the MMA's row operand and one tile of up to
+//             256 rows of its column operand, both 64 k wide, 128-byte swizzled
+//   warp 1    MMA issuer: one elected thread issues tcgen05.mma (M = 128, N = bn, K = 16) from shared-memory
+//             descriptors; accumulators are double-buffered in TMEM (2 x bn columns of fp32)
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (one MMA row per thread), convert, store
+// Which operand the tokens are is a template parameter (see umma_gemm.h).
 // All waits are bounded; a time-out sets *status and the kernel drains and frees its TMEM.
+#include <stdlib.h>
+
 #include "ptx.cuh"
 #include "tmap.h"
 #include "umma_gemm.h"
@@ -12,9 +15,9 @@
 namespace blr {
 
 static constexpr int kGemmThreads = 192;
-static constexpr int kBM = 128;
+static constexpr int kBM = 128;  // rows of the MMA (TMEM lanes)
 static constexpr int kBK = 64;
-static constexpr int kWTileBytes = kBM * kBK * 2;
+static constexpr int kRowTileBytes = kBM * kBK * 2;
 static constexpr int kMaxStages = 8;
 
 template <bool BF16>
@@ -22,14 +25,28 @@ __device__ __forceinline__ void gemm_store(void* base, long long off, float v) {
   if constexpr (BF16) reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(v);
   else reinterpret_cast<__half*>(base)[off] = __float2half_rn(v);
 }
-
 template <bool BF16>
+__device__ __forceinline__ uint32_t gemm_pack(float a, float b) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+__device__ __forceinline__ float gemm_round(float v, int round_out) {
+  return round_out ? fminf(fmaxf(rintf(v), -128.f), 127.f) : v;
+}
+
+// TR = tokens are the MMA rows (weights its columns); !TR = weights are the rows ("swap-AB").
+template <bool BF16, bool TR>
 __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t a_tile_bytes = (uint32_t)p.bn * kBK * 2;
-  const uint32_t stage_bytes = kWTileBytes + a_tile_bytes;
+  const uint32_t col_tile_bytes = (uint32_t)p.bn * kBK * 2;
+  const uint32_t stage_bytes = kRowTileBytes + col_tile_bytes;
   const uint32_t NST = p.nstages;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NST * stage_bytes);
   // full[8], empty[8], tmem_full[2], tmem_empty[2]
@@ -39,9 +56,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + p.bn - 1) / p.bn;
+  // m_tiles: tiles along the weight rows; n_tiles: tiles along the tokens
+  const int m_tiles = TR ? (p.M + p.bn - 1) / p.bn : (p.M + kBM - 1) / kBM;
+  const int n_tiles = TR ? (p.N + kBM - 1) / kBM : (p.N + p.bn - 1) / p.bn;
   const int tiles = p.G * m_tiles * n_tiles;
   const int kblocks = (p.K + kBK - 1) / kBK;
+  const int w_rows = TR ? p.bn : kBM;    // weight rows per tile
+  const int a_rows = TR ? kBM : p.bn;    // tokens per tile
+  // byte offsets of the two operands inside a stage
+  const uint32_t w_off = TR ? kRowTileBytes : 0u, a_off = TR ? 0u : kRowTileBytes;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -75,12 +98,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
           const uint32_t dst = smem_base + s * stage_bytes, bar = full0 + 8 * s;
           mbar_arrive_expect_tx(bar, stage_bytes);
           if (p.kmajor) {
-            tma_load_3d(dst, &p.tmW, kb * kBK, mt * kBM, g, bar);
+            tma_load_3d(dst + w_off, &p.tmW, kb * kBK, mt * w_rows, g, bar);
           } else {
-            tma_load_3d(dst, &p.tmW, mt * kBM, kb * kBK, g, bar);
-            tma_load_3d(dst + kWTileBytes / 2, &p.tmW, mt * kBM + 64, kb * kBK, g, bar);
+            // output index contiguous: 64-wide column blocks of 64 k-rows, 8 KB each
+            for (int blk = 0; blk < w_rows / 64; ++blk)
+              tma_load_3d(dst + w_off + blk * 8192, &p.tmW, mt * w_rows + blk * 64, kb * kBK, g, bar);
           }
-          tma_load_3d(dst + kWTileBytes, &p.tmA, kb * kBK, nt * p.bn, g, bar);
+          tma_load_3d(dst + a_off, &p.tmA, kb * kBK, nt * a_rows, g, bar);
           if (++s == NST) { s = 0; parity ^= 1u; first = false; }
         }
       }
@@ -88,7 +112,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(BF16, !p.kmajor, kBM, (uint32_t)p.bn);
+      const uint32_t idesc = TR ? umma_idesc(BF16, false, !p.kmajor, kBM, (uint32_t)p.bn)
+                                : umma_idesc(BF16, !p.kmajor, false, kBM, (uint32_t)p.bn);
       uint32_t s = 0, parity = 0;
       uint32_t it = 0;
       bool ok = true;
@@ -101,14 +126,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(full0 + 8 * s, parity, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sW = smem_base + s * stage_bytes, sA = sW + kWTileBytes;
+          const uint32_t st = smem_base + s * stage_bytes, sW = st + w_off, sA = st + a_off;
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) {
-            uint64_t adesc;
-            if (p.kmajor) adesc = umma_smem_desc(sW + kk * 32, 16, 1024);
-            else adesc = umma_smem_desc(sW + kk * 2048, kWTileBytes / 2, 1024);
-            const uint64_t bdesc = umma_smem_desc(sA + kk * 32, 16, 1024);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            // weights: K-major tile advances 32 B per k16 inside the swizzle atom; M-major tile advances 16 k-rows
+            const uint64_t wdesc = p.kmajor ? umma_smem_desc(sW + kk * 32, 16, 1024) : umma_smem_desc(sW + kk * 2048, 8192, 1024);
+            const uint64_t adesc = umma_smem_desc(sA + kk * 32, 16, 1024);
+            if constexpr (TR) umma_f16(d_tmem, adesc, wdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            else umma_f16(d_tmem, wdesc, adesc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
           if (++s == NST) { s = 0; parity ^= 1u; }
@@ -121,30 +146,91 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
     const int q = warp & 3;
     uint32_t it = 0;
     bool ok = true;
+    // 16-byte stores need 8 consecutive outputs contiguous and aligned in memory
+    const bool vec_out = p.os_lo == 1 && (p.per & 7) == 0 && (p.M & 7) == 0 && (p.os_g & 7) == 0 && (p.os_n & 7) == 0 &&
+                         (p.os_hi & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    // 32-byte stores: 16 consecutive outputs contiguous and 32-byte aligned
+    const bool wide_out = vec_out && (p.per & 15) == 0 && (p.os_g & 15) == 0 && (p.os_n & 15) == 0 && (p.os_hi & 15) == 0 &&
+                          (p.bn & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
       const int nt = tile % n_tiles, gm = tile / n_tiles, mt = gm % m_tiles, g = gm / m_tiles;
       const uint32_t buf = it & 1u, use = it >> 1;
       if (ok && !mbar_wait(tfull0 + 8 * buf, use & 1u, abort_flag)) ok = false;
       if (!ok) continue;
       tc_fence_after();
-      const int m = mt * kBM + q * 32 + lane;
-      const bool m_ok = m < p.M;
-      const long long base = m_ok ? (long long)g * p.os_g + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)p.bn;
-      const int n0 = nt * p.bn;
-      for (int c = 0; c < p.bn; c += 16) {
-        if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
-        uint32_t r[16];
-        tmem_ld16(taddr + c, r);
-        tmem_ld_wait();
-        if (m_ok) {
+      const long long gbase = (long long)g * p.os_g;
+      if constexpr (TR) {
+        // thread = token, columns = consecutive weight rows
+        const int n = nt * kBM + q * 32 + lane;
+        const bool n_ok = n < p.N;
+        const long long nbase = gbase + (long long)n * p.os_n;
+        const int m0 = mt * p.bn;
+        int hi = m0 / p.per, lo = m0 - hi * p.per;  // (m / per, m % per) of the chunk start, kept incrementally
+        for (int c0 = 0; c0 < p.bn && m0 + c0 < p.M && !(p.debug & 2); c0 += 64) {
+          // four TMEM loads in flight before the wait: one round covers 64 outputs of this token
+          uint32_t rr[4][16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int n = n0 + c + j;
-            if (n < p.N) {
-              float v = __uint_as_float(r[j]);
-              if (p.round_out) v = fminf(fmaxf(rintf(v), -128.f), 127.f);
-              gemm_store<BF16>(p.out, base + (long long)n * p.os_n, v);
+          for (int u = 0; u < 4; ++u)
+            if (c0 + 16 * u < p.bn && m0 + c0 + 16 * u < p.M) tmem_ld16(taddr + c0 + 16 * u, rr[u]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + 16 * u;
+            if (!(c < p.bn && m0 + c < p.M)) break;
+            uint32_t(&r)[16] = rr[u];
+            if (p.debug & 1) {
+              if (r[0] == 0x12345678u && r[5] == 0x9abcdefu) p.status[0] = 1;  // keeps the loads alive
+            } else if (vec_out) {
+              uint32_t w[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                w[k] = gemm_pack<BF16>(gemm_round(__uint_as_float(r[2 * k]), p.round_out), gemm_round(__uint_as_float(r[2 * k + 1]), p.round_out));
+              uint16_t* o16 = reinterpret_cast<uint16_t*>(p.out);
+              if (wide_out && m0 + c + 16 <= p.M) {
+                // one full 32-byte sector per thread
+                uint16_t* dst = o16 + nbase + (long long)hi * p.os_hi + lo;
+                if (n_ok)
+                  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                lo += 16;
+                if (lo >= p.per) { lo -= p.per; ++hi; }
+              } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  if (n_ok && m0 + c + 8 * h < p.M)
+                    *reinterpret_cast<uint4*>(o16 + nbase + (long long)hi * p.os_hi + lo) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
+                  lo += 8;
+                  if (lo >= p.per) { lo -= p.per; ++hi; }
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (n_ok && m0 + c + j < p.M)
+                  gemm_store<BF16>(p.out, nbase + (long long)hi * p.os_hi + (long long)lo * p.os_lo,
+                                   gemm_round(__uint_as_float(r[j]), p.round_out));
+                if (++lo == p.per) { lo = 0; ++hi; }
+              }
+            }
+          }
+        }
+      } else {
+        // thread = weight row, columns = tokens
+        const int m = mt * kBM + q * 32 + lane;
+        const bool m_ok = m < p.M;
+        const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
+        const int n0 = nt * p.bn;
+        for (int c = 0; c < p.bn; c += 16) {
+          if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
+          uint32_t r[16];
+          tmem_ld16(taddr + c, r);
+          tmem_ld_wait();
+          if (m_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + c + j;
+              if (n < p.N) gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round(__uint_as_float(r[j]), p.round_out));
             }
           }
         }
@@ -167,45 +253,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
 }
 
 void umma_gemm_tiling(GemmParams& p) {
-  int bn = 256;
-  if (p.N <= 256) bn = (p.N + 15) / 16 * 16;
-  if (bn < 16) bn = 16;
-  p.bn = bn;
-  const int stage = kWTileBytes + bn * kBK * 2;
+  if (p.N > 64) {
+    // tokens as MMA rows; weight rows as columns, 256 at a time when the block is tall enough
+    p.tokens_as_rows = 1;
+    int bn = 256;
+    if (p.M <= 192) bn = (p.M + 63) / 64 * 64;  // multiples of 64 keep the M-major boxes whole
+    p.bn = bn;
+  } else {
+    p.tokens_as_rows = 0;
+    p.bn = (p.N + 15) / 16 * 16;
+  }
+  const int stage = kRowTileBytes + p.bn * kBK * 2;
   int nst = (232448 - 1024 - 512) / stage;
   p.nstages = nst > kMaxStages ? kMaxStages : nst;
 }
 
-int launch_umma_gemm(const GemmParams& p, cudaStream_t stream) {
+template <bool BF16, bool TR>
+static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    configured[dev & 63] = true;
+  }
+  blr_umma_gemm_kernel<BF16, TR><<<grid, kGemmThreads, smem, stream>>>(p);
+  BLR_CUDA_OK(cudaGetLastError());
+  return BLR_OK;
+}
+
+int launch_umma_gemm(const GemmParams& p_in, cudaStream_t stream) {
+  GemmParams p = p_in;
+  { static const int dbg = getenv("BLR_GEMM_DEBUG") ? atoi(getenv("BLR_GEMM_DEBUG")) : 0; p.debug = dbg; }
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc != BLR_OK) return rc;
-  const size_t smem = (size_t)p.nstages * (kWTileBytes + p.bn * kBK * 2) + 512 + 1024;
+  const size_t smem = (size_t)p.nstages * (kRowTileBytes + p.bn * kBK * 2) + 512 + 1024;
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
   BLR_REQUIRE(p.bn % 16 == 0 && p.bn >= 16 && p.bn <= 256 && p.nstages >= 2, BLR_ERR_ARG, "bad tile configuration");
+  BLR_REQUIRE(p.kmajor || !p.tokens_as_rows || p.bn % 64 == 0, BLR_ERR_ARG, "bad tile configuration for this weight layout");
   int dev;
   BLR_CUDA_OK(cudaGetDevice(&dev));
-  const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + p.bn - 1) / p.bn;
+  const int m_tiles = p.tokens_as_rows ? (p.M + p.bn - 1) / p.bn : (p.M + kBM - 1) / kBM;
+  const int n_tiles = p.tokens_as_rows ? (p.N + kBM - 1) / kBM : (p.N + p.bn - 1) / p.bn;
   const long long tiles = (long long)p.G * m_tiles * n_tiles;
   const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
   if (p.is_bf16) {
-    static bool configured[64] = {};
-    if (!configured[dev & 63]) {
-      BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
-      configured[dev & 63] = true;
-    }
-    blr_umma_gemm_kernel<true><<<grid, kGemmThreads, smem, stream>>>(p);
-  } else {
-    static bool configured[64] = {};
-    if (!configured[dev & 63]) {
-      BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
-      configured[dev & 63] = true;
-    }
-    blr_umma_gemm_kernel<false><<<grid, kGemmThreads, smem, stream>>>(p);
+    return p.tokens_as_rows ? launch_variant<true, true>(p, grid, smem, dev, di.max_smem_optin, stream)
+                            : launch_variant<true, false>(p, grid, smem, dev, di.max_smem_optin, stream);
   }
-  BLR_CUDA_OK(cudaGetLastError());
-  return BLR_OK;
+  return p.tokens_as_rows ? launch_variant<false, true>(p, grid, smem, dev, di.max_smem_optin, stream)
+                          : launch_variant<false, false>(p, grid, smem, dev, di.max_smem_optin, stream);
 }
 
 }  // namespace blr

@@ -1,7 +1,10 @@
 // Grouped tensor-core GEMM for token counts above the streaming kernel's limit:
 //     out[g][n][m] = sum_k W[g][m][k] * A[g][n][k]
-// with the weights as the 128-row tcgen05 operand ("swap-AB": the tokens are the N dimension of the MMA,
-// so a tile is 128 weight rows x up to 256 tokens), fp32 accumulation in TMEM, 16-bit output.
+// fp32 accumulation in TMEM, 16-bit output.  Two orientations of the tcgen05 tile:
+//   tokens_as_rows = 1: 128 tokens are the MMA's 128 rows, up to 256 weight rows its columns; an epilogue
+//                       thread then owns one token and writes runs of consecutive outputs (16-byte stores);
+//   tokens_as_rows = 0: 128 weight rows are the MMA rows and up to 256 tokens its columns ("swap-AB"),
+//                       which wastes nothing when there are fewer than 128 tokens.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -10,11 +13,12 @@
 namespace blr {
 
 struct alignas(64) GemmParams {
-  CUtensorMap tmW;  // K-major: dims (K, M, G) box (64, 128, 1); M-major: dims (M, K, G) box (64, 64, 1)
-  CUtensorMap tmA;  // dims (K, N, G) box (64, BN, 1)
+  CUtensorMap tmW;  // K-major: dims (K, M, G) box (64, row-tile, 1); M-major: dims (M, K, G) box (64, 64, 1)
+  CUtensorMap tmA;  // dims (K, N, G) box (64, token-tile, 1)
   int G, M, K, N;
-  int kmajor;       // weight layout
-  int bn;           // tokens per tile (multiple of 16, <= 256)
+  int kmajor;          // weight layout
+  int tokens_as_rows;  // orientation (see above)
+  int bn;              // extent of the MMA's column operand: tokens (swap-AB) or weight rows; multiple of 16, <= 256
   int nstages;
   int is_bf16;
   int round_out;    // round to nearest integer, clamp to [-128, 127] before storing
@@ -22,11 +26,16 @@ struct alignas(64) GemmParams {
   long long os_g, os_n, os_hi, os_lo;
   void* out;
   unsigned* status;  // optional: set to 1 when a device-side wait gave up
+  int debug;         // experiment switches (0 in production)
 };
 
 int launch_umma_gemm(const GemmParams& p, cudaStream_t stream);
 
-// Picks the token tile and ring depth for N tokens and fills bn / nstages.
+// Picks orientation, tile extents and ring depth from N, M; fills tokens_as_rows / bn / nstages.
 void umma_gemm_tiling(GemmParams& p);
+
+// Rows of the weight tile and of the token tile implied by the tiling (for the TMA boxes).
+inline int umma_w_tile_rows(const GemmParams& p) { return p.tokens_as_rows ? p.bn : 128; }
+inline int umma_a_tile_rows(const GemmParams& p) { return p.tokens_as_rows ? 128 : p.bn; }
 
 }  // namespace blr

@@ -1,0 +1,89 @@
+"""CPU-side checks of the boundary: the shared library loads, exports every symbol the header declares,
+and the Python operator modules keep the reference's names.  No compute calls (there is no GPU here)."""
+import ctypes
+import importlib
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from mem_efficient_blr_b200 import build as b
+    b.build()  # no-op when the library is newer than its sources
+    from mem_efficient_blr_b200 import _lib
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "blr_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(blr_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    from mem_efficient_blr_b200 import _lib
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/blr_b200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_host_only_entry_points(lib):
+    assert lib.blr_version() >= 100
+    # groups * tokens * width elements: 4-byte + 2-byte regions + 256 control bytes, 256-byte granules
+    assert lib.blr_workspace_bytes(16, 16, 1024) == 256 + 16 * 16 * 1024 * 6
+    assert lib.blr_workspace_bytes(1, 0, 0) == 256
+    big = lib.blr_workspace_bytes(2048, 16, 1024)
+    assert big >= 256 + 2048 * 16 * 1024 * 6 + 16 * 16 * 1024 * 32
+
+
+def test_null_arguments_are_rejected_without_touching_a_device(lib):
+    rc = lib.blr_dense(None, 8, 1, 0, None, 0, 8, 8, None, 8, None)
+    assert rc == -1
+    assert b"null" in lib.blr_last_error()
+    rc = lib.blr_blast_wq(ctypes.c_void_p(16), 64, 1, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), ctypes.c_void_p(16),
+                          ctypes.c_void_p(16), ctypes.c_void_p(16), 1, 1, 1, 3, 0, 4, 16, 16, 16, ctypes.c_void_p(16), 64,
+                          None, 0, None)
+    assert rc == -1 and b"bits" in lib.blr_last_error()
+
+
+REFERENCE_NAMES = {
+    "blast_kernels": ["triton_blast_partial_fp16", "triton_blast_partial_fp32", "triton_blast_partial_grouped_fp16",
+                      "triton_blast_partial_grouped_fp32", "triton_blast_partial_grouped_persistent_fp16",
+                      "triton_blast_partial_grouped_persistent_fp32", "triton_blast_full_fp16", "triton_blast_full_fp32",
+                      "triton_blast_bmm_fp16", "triton_blast_bmm_fp32", "get_triton_blast_partial_fp16_config",
+                      "get_triton_blast_partial_grouped_fp16_config", "get_triton_blast_partial_grouped_persistent_fp16_config",
+                      "get_triton_blast_full_fp16_config", "get_triton_blast_bmm_xv_fp16_config",
+                      "get_triton_blast_bmm_sxv_fp16_config", "get_triton_blast_bmm_usxv_fp16_config"],
+    "blast_sym_quant_kernels": ["triton_blast_bmm_int8_fp16", "get_triton_blast_bmm_xv_int8_fp16_config",
+                                "get_triton_blast_bmm_sxv_int8_fp16_config", "get_triton_blast_bmm_usxv_int8_fp16_config"],
+    "monarch_kernels": ["triton_monarch_right_fp16", "triton_monarch_right_fp32", "triton_monarch_right_ideal_fp16",
+                        "triton_monarch_right_ideal_fp32", "triton_monarch_right_left_fp16", "triton_monarch_right_left_fp32",
+                        "get_triton_monarch_right_fp16_config", "get_triton_monarch_right_ideal_fp16_config",
+                        "get_triton_monarch_right_left_fp16_config"],
+    "low_rank_kernels": ["triton_low_rank_fp16", "triton_low_rank_fp32", "get_triton_low_rank_fp16_config"],
+    "dense_kernels": ["triton_dense_fp16", "triton_dense_fp32", "get_triton_dense_fp16_config"],
+}
+
+
+@pytest.mark.parametrize("module", sorted(REFERENCE_NAMES))
+def test_reference_function_names_exist(module):
+    m = importlib.import_module(f"mem_efficient_blr_b200.{module}")
+    for name in REFERENCE_NAMES[module]:
+        assert callable(getattr(m, name)), name
+        if name.startswith("get_"):
+            import pickle
+            pickle.dumps(getattr(m, name)())  # the reference's harness pickles these (layer.py:310-326)
+
+
+def test_operators_refuse_cpu_tensors():
+    import torch
+    import mem_efficient_blr_b200.dense_kernels as dk
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        dk.dense_torch_layout(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(8, 8, dtype=torch.float16))
