@@ -98,6 +98,16 @@ int blr_blast(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
               int b, int P, int Q, int R, int flags,
               void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
 
+/* blr_blast on a slice of the output blocks, for sharding a layer over GPUs by output block (no reference
+ * counterpart; the reference runs on one GPU): U holds b_out <= b blocks, S element (i, j, r) exists for
+ * i < b_out, out is (N, b_out*Q).  The first stage still covers all b input blocks.  The slices of several
+ * ranks are joined with an all-gather along the feature axis by the caller. */
+int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+                   const void* U, int u_layout, const void* V, int v_layout,
+                   const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                   int b, int b_out, int P, int Q, int R, int flags,
+                   void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
+
 /* BLAST with int8 / packed-int4 factors and fp16 scales.  No reference counterpart (the reference's
  * sym-quant kernels round activations, not weights); the format is: Uq int8 (b,Q,R) or uint8 (b,Q,R/2),
  * Vq int8 (b,R,P) or uint8 (b,R,P/2), contraction index contiguous, two int4 per byte with the even

@@ -29,6 +29,8 @@ SIGNATURES = {
     "blr_workspace_status": (_int, [_vp, _vp]),
     "blr_blast": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
                          _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
+    "blr_blast_rows": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
+                              _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
     "blr_blast_wq": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                             _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
     "blr_monarch": (_int, [_vp, _i64, _i64, _int, _vp, _int, _int, _vp, _int,

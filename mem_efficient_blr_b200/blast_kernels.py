@@ -117,6 +117,17 @@ def blast_torch_layout(x, U, Vt, S, flags=L.FLAG_NONE):
     return out.reshape(*x.shape[:-1], b * q)
 
 
+def blast_output_blocks(x, U_local, Vt, S_local, flags=L.FLAG_NONE):
+    """BLAST restricted to a slice of the output blocks (for sharding a layer over GPUs by output block):
+    U_local (b_out,Q,R), Vt (b,R,P), S_local (b_out,b,R) contiguous; returns (..., b_out*Q)."""
+    b, r, p = Vt.shape
+    bo, q, r2 = U_local.shape
+    assert 1 <= bo <= b and r2 == r and tuple(S_local.shape) == (bo, b, r)
+    assert U_local.is_contiguous() and S_local.is_contiguous()
+    out = ops.blast_op(ops._flat2d(x), U_local, Vt, S_local, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags, bo)
+    return out.reshape(*x.shape[:-1], bo * q)
+
+
 # The reference exposes its autotuner's winning configuration (blast_kernels.py:3068-3086) and pickles
 # it (layer.py:310-326).  Tile shapes here are fixed at build time, so there is nothing to report.
 def get_triton_blast_partial_fp16_config():

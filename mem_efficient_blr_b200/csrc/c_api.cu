@@ -127,7 +127,7 @@ static int check_layout(int layout) {
 // ---------------------------------------------------------------------------------- BLAST (16-bit and quantised)
 static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, const void* S,
-                      int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R, int flags, void* out,
+                      int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
                       int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream) {
   int rc = check_common(x, ldx, N, dtype, out, ldo);
   if (rc) return rc;
@@ -135,7 +135,8 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   BLR_REQUIRE((reinterpret_cast<uintptr_t>(S) & 15) == 0, BLR_ERR_ALIGN, "S must be 16-byte aligned");
   BLR_REQUIRE(b >= 2, BLR_ERR_SHAPE, "BLAST needs at least 2 blocks per side, got %d (the reference asserts b != 1)", b);
   BLR_REQUIRE(P > 0 && Q > 0 && R > 0, BLR_ERR_SHAPE, "P, Q, R must be positive");
-  BLR_REQUIRE(ldx >= (int64_t)b * P && ldo >= (int64_t)b * Q, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
+  BLR_REQUIRE(bo >= 1 && bo <= b, BLR_ERR_SHAPE, "output blocks held by this call (%d) must be in 1..%d", bo, b);
+  BLR_REQUIRE(ldx >= (int64_t)b * P && ldo >= (int64_t)bo * Q, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
   if ((rc = check_layout(u_layout)) || (rc = check_layout(v_layout))) return rc;
   Workspace w;
   if ((rc = carve(ws, ws_bytes, N, b, R, &w))) return rc;
@@ -143,21 +144,21 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
 
   if (N <= kStreamMaxTokens) {
     StreamParams p = {};
-    p.nphases = 2; p.mix = 1; p.b = b; p.R = R; p.round_z = act8;
+    p.nphases = 2; p.mix = 1; p.b = b; p.b_out = bo; p.R = R; p.round_z = act8;
     p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
     p.y32 = static_cast<float*>(w.region_a); p.z16 = w.region_b; p.counters = w.counters;
     if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, v_bits, b, R, P))) return rc;
     if ((rc = phase_acts(p.ph[0], dtype, x, P, N, b, ldx, P))) return rc;
     phase_out(p.ph[0], w.region_a, 1, (long long)N * R, R, R, 0, 1, v_scale, act8);
-    if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, b, Q, R))) return rc;
-    if ((rc = phase_acts(p.ph[1], dtype, w.region_b, R, N, b, R, (int64_t)N * R))) return rc;
+    if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, bo, Q, R))) return rc;
+    if ((rc = phase_acts(p.ph[1], dtype, w.region_b, R, N, bo, R, (int64_t)N * R))) return rc;
     phase_out(p.ph[1], out, 0, Q, ldo, Q, 0, 1, u_scale, 0);
     finish_params(p, N);
     return launch_stream(p, dtype == BLR_DTYPE_BF16, stream);
   }
   BLR_REQUIRE(u_bits == 16 && v_bits == 16, BLR_ERR_UNSUPPORTED,
               "quantised factors are implemented for up to %d tokens per call", kStreamMaxTokens);
-  return pipeline_blast(x, ldx, N, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b, P, Q, R, act8, out, ldo,
+  return pipeline_blast(x, ldx, N, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b, bo, P, Q, R, act8, out, ldo,
                         w.region_a, w.region_b, w.region_c, stream);
 }
 
@@ -203,8 +204,15 @@ int blr_workspace_status(const void* ws, void* stream) {
 int blr_blast(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
               int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R, int flags,
               void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
-  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, P,
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b, P,
                     Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
+                   int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
+                   int flags, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b_out,
+                    P, Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* Uq, const void* u_scale,
@@ -214,7 +222,7 @@ int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
   BLR_REQUIRE(group == 0, BLR_ERR_UNSUPPORTED, "only one scale per output channel (group = 0) is implemented");
   BLR_REQUIRE(u_scale && v_scale, BLR_ERR_ARG, "scale pointers must not be null");
   return blast_impl(x, ldx, n_tokens, dtype, Uq, BLR_W_KMAJOR, bits, u_scale, Vq, BLR_W_KMAJOR, bits, v_scale, S, s_i,
-                    s_j, s_r, b, P, Q, R, BLR_FLAG_NONE, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+                    s_j, s_r, b, b, P, Q, R, BLR_FLAG_NONE, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* w1, int w1_layout, int w1_cols,

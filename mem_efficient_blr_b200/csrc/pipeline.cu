@@ -74,13 +74,13 @@ __device__ __forceinline__ float ld1<__nv_bfloat16>(const __nv_bfloat16* p) { re
 // y / z traffic.  GS = 16 makes every contiguous piece of y' and z a full 32-byte sector.
 template <typename T, int GS>
 __global__ void expand_coupling_kernel(const T* __restrict__ S, long long s_i, long long s_j, long long s_r,
-                                       T* __restrict__ E, int b, int R) {
+                                       T* __restrict__ E, int b, int b_out, int R) {
   // one thread per row (g, i, r'): b vectors of GS, each with a single non-zero at position r'
-  const int w = GS * b;
-  const long long rows = (long long)(R / GS) * w;
+  const int w = GS * b, h = GS * b_out;  // row length, rows per group
+  const long long rows = (long long)(R / GS) * h;
   const long long row_id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (row_id >= rows) return;
-  const int row = (int)(row_id % w), g = (int)(row_id / w), i = row / GS, r1 = row % GS;
+  const int row = (int)(row_id % h), g = (int)(row_id / h), i = row / GS, r1 = row % GS;
   T* dst = E + row_id * w;
   const T* src = S + i * s_i + (long long)(GS * g + r1) * s_r;
   for (int j = 0; j < b; ++j) {
@@ -96,11 +96,11 @@ __global__ void expand_coupling_kernel(const T* __restrict__ S, long long s_i, l
 // Any block count / any strides: one thread per output element.
 template <typename T>
 __global__ void blast_couple_generic_kernel(const T* __restrict__ y, const T* __restrict__ S, long long s_i, long long s_j,
-                                            long long s_r, T* __restrict__ z, int b, long long NR, int R, int round_z) {
+                                            long long s_r, T* __restrict__ z, int b, int b_out, long long NR, int R, int round_z) {
   const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= NR) return;
   const int r = (int)(e % R);
-  for (int i = 0; i < b; ++i) {
+  for (int i = 0; i < b_out; ++i) {
     float s = 0.f;
     for (int j = 0; j < b; ++j) s = fmaf(ld1<T>(S + i * s_i + j * s_j + (long long)r * s_r), ld1<T>(y + j * NR + e), s);
     if (round_z) s = fminf(fmaxf(rintf(s), -128.f), 127.f);
@@ -109,30 +109,31 @@ __global__ void blast_couple_generic_kernel(const T* __restrict__ y, const T* __
 }
 
 template <typename T>
-static int run_couple_generic(const void* y, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* z, int b, int64_t N,
-                              int R, int round_z, cudaStream_t stream) {
+static int run_couple_generic(const void* y, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* z, int b, int b_out,
+                              int64_t N, int R, int round_z, cudaStream_t stream) {
   const long long NR = (long long)N * R;
   blast_couple_generic_kernel<T><<<(unsigned)((NR + 255) / 256), 256, 0, stream>>>(
-      static_cast<const T*>(y), static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(z), b, NR, R, round_z);
+      static_cast<const T*>(y), static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(z), b, b_out, NR, R, round_z);
   BLR_CUDA_OK(cudaGetLastError());
   return BLR_OK;
 }
 
 template <typename T>
-static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* E, int b, int R, int gs, cudaStream_t stream) {
-  const long long rows = (long long)(R / gs) * gs * b;
+static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* E, int b, int b_out, int R, int gs,
+                      cudaStream_t stream) {
+  const long long rows = (long long)(R / gs) * gs * b_out;
   const unsigned blocks = (unsigned)((rows + 127) / 128);
   if (gs == 16)
-    expand_coupling_kernel<T, 16><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, R);
+    expand_coupling_kernel<T, 16><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
   else
-    expand_coupling_kernel<T, 8><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, R);
+    expand_coupling_kernel<T, 8><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
   BLR_CUDA_OK(cudaGetLastError());
   return BLR_OK;
 }
 
 // ------------------------------------------------------------------------------------------ operators
 int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, const void* V,
-                   int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R,
+                   int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
                    int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream) {
   const long long plane = (long long)N * R;
   const bool bf = dtype == BLR_DTYPE_BF16;
@@ -143,21 +144,22 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
     const int gs = R % 16 == 0 ? 16 : 8, w = gs * b;
     rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, gs, (long long)R * b, w, 1, gs, act_int8}, stream);
     if (rc) return rc;
-    rc = bf ? run_expand<__nv_bfloat16>(S, s_i, s_j, s_r, e16, b, R, gs, stream) : run_expand<__half>(S, s_i, s_j, s_r, e16, b, R, gs, stream);
+    rc = bf ? run_expand<__nv_bfloat16>(S, s_i, s_j, s_r, e16, b, b_out, R, gs, stream)
+            : run_expand<__half>(S, s_i, s_j, s_r, e16, b, b_out, R, gs, stream);
     if (rc) return rc;
     // z[i][n][GS*g + r'] = sum_k E[g][(i, r')][k] y'[n][g][k]
-    rc = run_gemm(dtype, e16, BLR_W_KMAJOR, R / gs, w, w, y16, N, (int64_t)R * b, w, OutSpec{z16, gs, R, plane, 1, gs, act_int8}, stream);
+    rc = run_gemm(dtype, e16, BLR_W_KMAJOR, R / gs, gs * b_out, w, y16, N, (int64_t)R * b, w, OutSpec{z16, gs, R, plane, 1, gs, act_int8}, stream);
     if (rc) return rc;
   } else {
     // y[j][n][r] = sum_p V[j][r][p] x[n][j*P + p]
     rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream);
     if (rc) return rc;
-    rc = bf ? run_couple_generic<__nv_bfloat16>(y16, S, s_i, s_j, s_r, z16, b, N, R, act_int8, stream)
-            : run_couple_generic<__half>(y16, S, s_i, s_j, s_r, z16, b, N, R, act_int8, stream);
+    rc = bf ? run_couple_generic<__nv_bfloat16>(y16, S, s_i, s_j, s_r, z16, b, b_out, N, R, act_int8, stream)
+            : run_couple_generic<__half>(y16, S, s_i, s_j, s_r, z16, b, b_out, N, R, act_int8, stream);
     if (rc) return rc;
   }
   // out[n][i*Q + q] = sum_r U[i][q][r] z[i][n][r]
-  return run_gemm(dtype, U, u_layout, b, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
+  return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
 }
 
 int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const void* w1, int w1_layout, int grouped,

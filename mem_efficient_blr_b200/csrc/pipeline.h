@@ -7,7 +7,7 @@
 namespace blr {
 
 int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, const void* V,
-                   int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R,
+                   int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
                    int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream);
 int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const void* w1, int w1_layout, int grouped,
                      const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,

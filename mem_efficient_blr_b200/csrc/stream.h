@@ -48,7 +48,8 @@ struct alignas(64) StreamParams {
   int nphases;
   int N;
   int mix;        // 1: BLAST coupling between phase 0 and phase 1
-  int b, R;       // coupling dimensions
+  int b, R;       // coupling dimensions: in-blocks, rank
+  int b_out;      // out-blocks present in S / z (== b unless the call holds a slice of the output blocks)
   int round_z;    // 1: round/clamp z like round_out
   long long s_i, s_j, s_r;  // element strides of S for (out block, in block, rank)
   const void* S;

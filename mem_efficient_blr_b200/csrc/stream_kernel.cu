@@ -224,7 +224,7 @@ __device__ __forceinline__ void couple_preload(const StreamParams& p, int ctid, 
   int lo, hi;
   couple_range(p, lo, hi);
   const int nv = hi - lo;
-  if (ctid >= nv * p.b) return;
+  if (ctid >= nv * p.b_out) return;
   int i, r;
   long long pt;
   couple_item(p, ctid, nv, lo, i, pt, r);
@@ -252,7 +252,7 @@ __device__ __forceinline__ void couple(const StreamParams& p, int ctid, const Co
       ybuf[e] = *reinterpret_cast<const float4*>(ysrc + j * plane + q * 4);
     }
     consumer_bar();
-    for (int e = ctid; e < nv * bb; e += kConsumerWarps * 32) {
+    for (int e = ctid; e < nv * p.b_out; e += kConsumerWarps * 32) {
       int i, r;
       long long pt;
       couple_item(p, e, nv, lo, i, pt, r);
@@ -288,8 +288,9 @@ __device__ __forceinline__ void couple(const StreamParams& p, int ctid, const Co
     const int plo = (int)(((long long)NR * blockIdx.x) / gridDim.x);
     const int phi = (int)(((long long)NR * (blockIdx.x + 1)) / gridDim.x);
     const int npts = phi - plo;
-    for (int e = ctid; e < npts * bb; e += kConsumerWarps * 32) {
-      const int i = e % bb, nr = plo + e / bb, r = nr % p.R;
+    const int bo = p.b_out;
+    for (int e = ctid; e < npts * bo; e += kConsumerWarps * 32) {
+      const int i = e % bo, nr = plo + e / bo, r = nr % p.R;
       float s = 0.f;
 #pragma unroll 8
       for (int j = 0; j < bb; ++j)

@@ -15,10 +15,17 @@ from . import _lib as L
 
 
 def _flat2d(x: torch.Tensor) -> torch.Tensor:
-    """(..., I) -> (N, I) view with unit inner stride (copies only if the input forces it)."""
-    x2 = x.reshape(-1, x.shape[-1])
+    """(..., I) -> (N, I); a view whenever the leading dims can be merged (traceable by torch.compile)."""
+    return x.reshape(-1, x.shape[-1])
+
+
+def _rows(x2: torch.Tensor) -> torch.Tensor:
+    """Inside an operator: make the (N, I) input fit the TMA rules (unit inner stride, row stride a multiple
+    of 8 elements, 16-byte aligned base); copies only if the input forces it."""
     if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8 != 0) or x2.data_ptr() % 16 != 0:
         x2 = x2.contiguous()
+        if x2.data_ptr() % 16 != 0:
+            x2 = x2.clone()
     return x2
 
 
@@ -39,21 +46,24 @@ def _ws(x: torch.Tensor, n: int, groups: int, width: int):
 # ----------------------------------------------------------------------------- BLAST
 @torch.library.custom_op("blr_b200::blast", mutates_args=())
 def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor, u_layout: int, v_layout: int,
-             s_i: int, s_j: int, s_r: int, b: int, P: int, Q: int, R: int, flags: int) -> torch.Tensor:
+             s_i: int, s_j: int, s_r: int, b: int, P: int, Q: int, R: int, flags: int, b_out: int = -1) -> torch.Tensor:
+    """b_out < b: U and S hold only a slice of the output blocks (sharding by output block)."""
     _need_cuda(x, U, V, S)
+    x = _rows(x)
     assert U.dtype == x.dtype and V.dtype == x.dtype and S.dtype == x.dtype, "x, U, V, S must share one 16-bit dtype"
+    bo = b if b_out < 0 else b_out
     n = x.shape[0]
-    out = torch.empty((n, b * Q), dtype=x.dtype, device=x.device)
+    out = torch.empty((n, bo * Q), dtype=x.dtype, device=x.device)
     ws, st = _ws(x, n, b, R)
-    L.check(L.load().blr_blast(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), U.data_ptr(), u_layout,
-                               V.data_ptr(), v_layout, S.data_ptr(), s_i, s_j, s_r, b, P, Q, R, flags,
-                               out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), st))
+    L.check(L.load().blr_blast_rows(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), U.data_ptr(), u_layout,
+                                    V.data_ptr(), v_layout, S.data_ptr(), s_i, s_j, s_r, b, bo, P, Q, R, flags,
+                                    out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), st))
     return out
 
 
 @blast_op.register_fake
-def _(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags):
-    return x.new_empty((x.shape[0], b * Q))
+def _(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
+    return x.new_empty((x.shape[0], (b if b_out < 0 else b_out) * Q))
 
 
 @torch.library.custom_op("blr_b200::blast_wq", mutates_args=())
@@ -61,6 +71,7 @@ def blast_wq_op(x: torch.Tensor, Uq: torch.Tensor, u_scale: torch.Tensor, Vq: to
                 S: torch.Tensor, s_i: int, s_j: int, s_r: int, bits: int, group: int, b: int, P: int, Q: int,
                 R: int) -> torch.Tensor:
     _need_cuda(x, Uq, u_scale, Vq, v_scale, S)
+    x = _rows(x)
     assert u_scale.dtype == torch.float16 and v_scale.dtype == torch.float16, "scales are fp16"
     assert S.dtype == x.dtype
     n = x.shape[0]
@@ -82,6 +93,7 @@ def _(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
 def monarch_op(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_layout: int, w1_cols: int, w2_layout: int,
                b: int, P: int, rank: int, Qs: int, out_order: int) -> torch.Tensor:
     _need_cuda(x, w1, w2)
+    x = _rows(x)
     assert w1.dtype == x.dtype and w2.dtype == x.dtype
     n = x.shape[0]
     out = torch.empty((n, b * Qs), dtype=x.dtype, device=x.device)
@@ -102,6 +114,7 @@ def _(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
 def low_rank_op(x: torch.Tensor, V: torch.Tensor, U: torch.Tensor, v_layout: int, u_layout: int, I: int, R: int,
                 O: int) -> torch.Tensor:
     _need_cuda(x, V, U)
+    x = _rows(x)
     assert V.dtype == x.dtype and U.dtype == x.dtype
     n = x.shape[0]
     out = torch.empty((n, O), dtype=x.dtype, device=x.device)
@@ -120,6 +133,7 @@ def _(x, V, U, v_layout, u_layout, I, R, O):
 @torch.library.custom_op("blr_b200::dense", mutates_args=())
 def dense_op(x: torch.Tensor, W: torch.Tensor, w_layout: int, I: int, O: int) -> torch.Tensor:
     _need_cuda(x, W)
+    x = _rows(x)
     assert W.dtype == x.dtype
     n = x.shape[0]
     out = torch.empty((n, O), dtype=x.dtype, device=x.device)

@@ -1,0 +1,147 @@
+"""GPU tests of the module-level boundary: wrappers with the reference's constructor signatures, layer swap,
+torch.compile(fullgraph=True) tracing, CUDA-graph capture, and the quantised module."""
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import blr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+PKG = "mem_efficient_blr_b200"
+
+
+@pytest.fixture(scope="module")
+def W():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import mem_efficient_blr_b200.wrappers as w
+    return w
+
+
+def _scaled_(m):
+    """The reference initialises with unscaled randn; scale so that 16-bit outputs stay well conditioned."""
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n != "bias":
+                p.mul_(0.05)
+
+
+@pytest.mark.parametrize("func,N", [("blast_kernels.triton_blast_partial_grouped_fp16", 4),
+                                    ("blast_kernels.triton_blast_bmm_fp16", 4),
+                                    ("blast_kernels.triton_blast_partial_grouped_fp16", 77)])
+def test_blast_linear_matches_oracle_with_bias(W, func, N):
+    torch.manual_seed(0)
+    m = W.BlastLinear(512, 768, 4, 128, f"{PKG}.{func}", DEV, torch.bfloat16, bias=True)
+    _scaled_(m)
+    x = torch.randn(2, N, 512, device=DEV, dtype=torch.bfloat16)
+    out = m(x)
+    assert out.shape == (2, N, 768)
+    U, V, S = m.U.detach().cpu(), m.V.detach().cpu(), m.S.detach().cpu()
+    if "bmm" in func:     # U (b,Q,R), V (b,P,R), S (R,b_out,b_in)
+        ref = orc.blast(x.cpu(), U, V.transpose(1, 2), S.permute(1, 2, 0))[0]
+    else:                 # U (b,R,Q), V (b,P,R), S (b_in,b_out,R)
+        ref = orc.blast(x.cpu(), U.transpose(1, 2), V.transpose(1, 2), S.transpose(0, 1))[0]
+    ref = ref + m.bias.detach().float().cpu()
+    torch.cuda.synchronize()
+    assert orc.rel_fro(out.float().cpu(), ref) < TOL
+
+
+def test_monarch_low_rank_dense_modules(W):
+    torch.manual_seed(1)
+    x = torch.randn(3, 256, device=DEV, dtype=torch.float16)
+    m = W.MonarchLinear(256, 512, 4, 64, f"{PKG}.monarch_kernels.triton_monarch_right_left_fp16", DEV, torch.float16, bias=False)
+    _scaled_(m)
+    w1, w2 = m.w1_bfly.detach().cpu(), m.w2_bfly.detach().cpu()
+    # undo the harness' column regrouping (layer.py:221-224): kernel column l*per + jj is torch column jj*b + l
+    b, P, rank = w1.shape
+    w1_t = w1.view(b, P, b, rank // b).permute(0, 1, 3, 2).reshape(b, P, rank).transpose(1, 2)
+    ref = orc.monarch(x.cpu(), w1_t, w2.transpose(1, 2))[0]
+    assert orc.rel_fro(m(x).float().cpu(), ref) < TOL
+
+    lr = W.LowRankLinear(256, 384, 64, device=DEV, dtype=torch.float16, bias=True)
+    _scaled_(lr)
+    ref = orc.low_rank(x.cpu(), lr.V.detach().cpu().t(), lr.U.detach().cpu().t())[0] + lr.bias.detach().float().cpu()
+    assert orc.rel_fro(lr(x).float().cpu(), ref) < TOL
+
+    d = W.DenseLinear(256, 384, device=DEV, dtype=torch.float16, bias=True)
+    _scaled_(d)
+    ref = orc.dense(x.cpu(), d.W.detach().cpu().t()) + d.bias.detach().float().cpu()
+    assert orc.rel_fro(d(x).float().cpu(), ref) < TOL
+
+
+def test_layer_swap_and_fullgraph_compile(W):
+    torch.manual_seed(2)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up_proj = nn.Linear(256, 512, bias=False)
+            self.down_proj = nn.Linear(512, 256, bias=False)
+            self.other = nn.Linear(256, 256)
+
+        def forward(self, x):
+            return self.other(self.down_proj(torch.nn.functional.silu(self.up_proj(x))))
+
+    blk = Block().to(DEV, torch.bfloat16)
+    n = W.replace_linear_with_custom(
+        blk, "proj", lambda i, o, bias: W.BlastLinear(i, o, 4, 64, device=DEV, dtype=torch.bfloat16, bias=bias))
+    assert n == 2 and isinstance(blk.up_proj, W.BlastLinear) and isinstance(blk.other, nn.Linear)
+    _scaled_(blk.up_proj); _scaled_(blk.down_proj)
+    x = torch.randn(1, 8, 256, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():   # the operators are forward-only (the reference times inference)
+        eager = blk(x)
+        compiled = torch.compile(blk, fullgraph=True)   # the reference compiles its networks this way (models/llama7b.py:65)
+        got = compiled(x)
+    torch.cuda.synchronize()
+    assert orc.rel_fro(got.float().cpu(), eager.float().cpu()) < 1e-3
+
+
+def test_cuda_graph_capture_and_replay(W):
+    x, U, Vt, S = orc.make_blast_inputs(8, 512, 768, 4, 128, torch.float16, seed=4)
+    import mem_efficient_blr_b200.blast_kernels as bk
+    xd, Ud, Vd, Sd = (t.to(DEV) for t in (x, U, Vt, S))
+    ref = orc.blast(x, U, Vt, S)[0]
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        bk.blast_torch_layout(xd, Ud, Vd, Sd)      # warm-up on the capture stream (workspace, descriptors)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            out = bk.blast_torch_layout(xd, Ud, Vd, Sd)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert orc.rel_fro(out.float().cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_quant_blast_linear(W, bits):
+    x, U, Vt, S = orc.make_blast_inputs(4, 1024, 1536, 4, 256, torch.float16, seed=5)
+    m = W.QuantBlastLinear(U.to(DEV), Vt.to(DEV), S.to(DEV), bits)
+    ref = orc.blast_wq(x, m.Uq.cpu(), m.u_scale.cpu(), m.Vq.cpu(), m.v_scale.cpu(), S, bits)[0]
+    out = m(x.to(DEV))
+    torch.cuda.synchronize()
+    assert orc.rel_fro(out.float().cpu(), ref) < TOL
+    full = orc.blast(x, U, Vt, S)[0]          # quantisation error itself: int8 ~1 %, int4 ~15 %
+    assert orc.rel_fro(out.float().cpu(), full) < (0.03 if bits == 8 else 0.3)
+
+
+@pytest.mark.parametrize("N", [4, 200])
+def test_output_block_slices_concatenate_to_the_full_result(W, N):
+    """What each rank of an output-block-sharded layer computes (the all-gather itself is covered on CPU ranks)."""
+    import mem_efficient_blr_b200.blast_kernels as bk
+    from mem_efficient_blr_b200 import dist as bd
+    x, U, Vt, S = orc.make_blast_inputs(N, 1024, 1536, 8, 128, torch.float16, seed=6)
+    xd, Ud, Vd, Sd = (t.to(DEV) for t in (x, U, Vt, S))
+    full = bk.blast_torch_layout(xd, Ud, Vd, Sd)
+    parts = []
+    for rank in range(4):
+        Ul, Sl = bd.shard_blast_factors(Ud, Sd, rank, 4)
+        parts.append(bk.blast_output_blocks(xd, Ul.contiguous(), Vd, Sl.contiguous()))
+    got = torch.cat(parts, dim=-1)
+    torch.cuda.synchronize()
+    assert got.shape == full.shape
+    assert orc.rel_fro(got.float().cpu(), orc.blast(x, U, Vt, S)[0]) < TOL
+    assert orc.rel_fro(got.float().cpu(), full.float().cpu()) < 1e-3
