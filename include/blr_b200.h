@@ -108,6 +108,23 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                    int b, int b_out, int P, int Q, int R, int flags,
                    void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
 
+/* blr_blast for callers that cannot allocate device memory and have no workspace to pass: plug-ins running
+ * inside a host application that owns the device allocator, or latency-critical threads where the implicit
+ * synchronisation of cudaMalloc is not acceptable.  This entry point has
+ * no counterpart in the reference.  Same arguments and results as blr_blast, minus (ws, ws_bytes); 1..16 tokens
+ * only.  Its scratch is a 4 MiB array built into the library's device image, which every GPU that loads the
+ * library holds until exit; calls with blr_workspace_bytes(n_tokens, b, R) > 4 MiB (b * n_tokens * R > 699008)
+ * are rejected with BLR_ERR_WORKSPACE.  The first call on each device looks the array up with
+ * cudaGetSymbolAddress (that device must be current) - make that first call before any stream capture.  It calls
+ * no cudaMalloc / cudaFree or other allocating routine.  All calls on a device share the one array: it keeps the
+ * previous call's contents (the control words are cleared on the stream at the start of every call), and two
+ * calls that overlap on the GPU (different streams) race on it. */
+int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+                     const void* U, int u_layout, const void* V, int v_layout,
+                     const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                     int b, int P, int Q, int R, int flags,
+                     void* out, int64_t ldo, void* stream);
+
 /* BLAST with int8 / packed-int4 factors and fp16 scales.  No reference counterpart (the reference's
  * sym-quant kernels round activations, not weights); the format is: Uq int8 (b,Q,R) or uint8 (b,Q,R/2),
  * Vq int8 (b,R,P) or uint8 (b,R,P/2), contraction index contiguous, two int4 per byte with the even

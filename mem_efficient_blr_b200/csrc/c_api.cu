@@ -2,6 +2,8 @@
 // (N <= 16 tokens) and the tensor-core pipeline (N > 16).
 #include "../../include/blr_b200.h"
 
+#include <mutex>
+
 #include "pipeline.h"
 #include "stream.h"
 #include "tmap.h"
@@ -162,6 +164,32 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
                         w.region_a, w.region_b, w.region_c, stream);
 }
 
+// ---------------------------------------------------------------------------------- fixed scratch for blr_blast_static
+// Scratch of the streaming kernel (control words, fp32 y, 16-bit z) for callers that cannot hand over a
+// workspace.  The array lives in every device's copy of this module from load to exit.
+static constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: b * n_tokens * R <= 699008 elements
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of the array on the current device.  In host code `g_static_scratch` is only a handle
+// for the runtime, not an address a kernel could use, so it is resolved once per device with
+// cudaGetSymbolAddress while that device is current.
+static int static_scratch_ptr(void** out) {
+  static void* ptrs[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  BLR_CUDA_OK(cudaGetDevice(&dev));
+  BLR_REQUIRE(dev >= 0 && dev < 64, BLR_ERR_ARG, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    BLR_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    BLR_REQUIRE(p != nullptr, BLR_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return BLR_OK;
+}
+
 }  // namespace blr
 
 using namespace blr;
@@ -213,6 +241,25 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype, cons
                    int flags, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
   return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b_out,
                     P, Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
+                     int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R,
+                     int flags, void* out, int64_t ldo, void* stream) {
+  BLR_REQUIRE(n_tokens >= 1 && n_tokens <= kStreamMaxTokens, BLR_ERR_UNSUPPORTED,
+              "blr_blast_static handles 1..%d tokens per call, got %lld", kStreamMaxTokens, (long long)n_tokens);
+  BLR_REQUIRE(b >= 2 && R > 0, BLR_ERR_SHAPE, "bad dimensions");
+  const size_t need = blr_workspace_bytes(n_tokens, b, R);
+  BLR_REQUIRE(need <= kStaticScratchBytes, BLR_ERR_WORKSPACE,
+              "blr_blast_static: b * n_tokens * R = %lld needs %zu bytes of scratch, the built-in array holds %zu",
+              (long long)b * n_tokens * R, need, kStaticScratchBytes);
+  void* ws = nullptr;
+  int rc = static_scratch_ptr(&ws);  // first call on a device: resolves the array's address
+  if (rc) return rc;
+  // The array keeps whatever the previous call left; the barrier words must start at zero.
+  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes, static_cast<cudaStream_t>(stream)));
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b, P,
+                    Q, R, flags, out, ldo, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }
 
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* Uq, const void* u_scale,
