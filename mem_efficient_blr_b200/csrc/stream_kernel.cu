@@ -329,6 +329,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
     }
     mbar_init_fence();
   }
+  // Programmatic dependent launch: let the next kernel in the stream begin its own set-up as SMs free up, and
+  // do not touch memory the previous kernel may still be writing (workspace, activations) before it is done.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncthreads();
 
   if (warp == kConsumerWarps) {
@@ -562,6 +566,25 @@ static int launch_impl(const StreamParams& p, cudaStream_t stream) {
   void* args[] = {const_cast<StreamParams*>(&p)};
   // Cooperative launch: the grid barriers need every CTA resident, and this makes the launch fail
   // instead of deadlock when they cannot be.
+  // Programmatic dependent launch on top of it: the next launch in the stream may start its set-up while this
+  // grid drains (see the griddepcontrol pair in the kernel).  BLR_PDL=0 falls back to a plain cooperative launch.
+  static const int pdl = getenv("BLR_PDL") ? atoi(getenv("BLR_PDL")) : 1;
+  if (pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(di.sm_count);
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    at[1].id = cudaLaunchAttributeCooperative;
+    at[1].val.cooperative = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 2;
+    BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)kern, args));
+    return BLR_OK;
+  }
   BLR_CUDA_OK(cudaLaunchCooperativeKernel((const void*)kern, dim3(di.sm_count), dim3(kStreamThreads), args, smem, stream));
   return BLR_OK;
 }
