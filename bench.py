@@ -262,6 +262,58 @@ def run_ours(args):
             us = a.elapsed_time(b_) * 1e3 / (10 * len(reps[bits]))
             sweep[f"int{bits}_n{n}"] = {"us_per_layer": us, "GBps": algorithmic_bytes(bits, n) / us / 1e3}
 
+    # ---- context (not part of the headline): the 16-bit layer at decode and prefill sizes, and the dense fp16
+    # cuBLAS bar of the same layer that the quantised decode is meant to beat
+    context = {}
+    if rank == 0 and not args.no_context:
+        import mem_efficient_blr_b200.blast_kernels as bk
+
+        def graph_time(fns, reps=10):
+            for f in fns:
+                f()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for f in fns:
+                        f()
+            torch.cuda.synchronize()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                g.replay()
+            b_.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b_) * 1e3 / (reps * len(fns))
+
+        peak_hbm, _ = peak_hbm_gbs()
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peak_tf = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            peak_tf = 1590.0
+        nrep16 = 9  # 9 x 31 MB of fp16 factors > 2 x L2
+        Us = [Ud.clone() for _ in range(nrep16)]
+        Vs = [Vd.clone() for _ in range(nrep16)]
+        Ws = [torch.randn(O_F, I_F, device=dev, dtype=torch.float16) / 64 for _ in range(4)]
+        for n in (1, 4, 16, 128, 2048):
+            xn = torch.randn(n, I_F, device=dev, dtype=torch.float16)
+            us = graph_time([(lambda u=u, v=v: bk.blast_torch_layout(xn, u, v, Sd)) for u, v in zip(Us, Vs)])
+            nbytes = 2 * RANK * (I_F + O_F) + 2 * B_BLK * B_BLK * RANK + 2 * n * (I_F + O_F)
+            flops = 2 * n * RANK * (I_F + O_F + B_BLK * B_BLK)
+            roof = max(nbytes / (peak_hbm * 1e9), flops / (peak_tf * 1e12)) * 1e6
+            entry = {"us_per_layer": us, "roofline_us": roof, "frac": roof / us}
+            if n <= 16:
+                entry["dense_fp16_cublas_us"] = graph_time([(lambda w=w: torch.nn.functional.linear(xn, w)) for w in Ws])
+            context[f"blast_fp16_n{n}"] = entry
+        for key, v in sweep.items():
+            n = int(key.split("_n")[1])
+            v["speedup_vs_dense_fp16_cublas"] = context[f"blast_fp16_n{n}"]["dense_fp16_cublas_us"] / v["us_per_layer"]
+        del Us, Vs, Ws
+
     # ---- end to end through the public Python operator, host buffers in and out every launch
     def e2e_step():
         for bits, n in POINTS:
@@ -316,6 +368,7 @@ def run_ours(args):
             "cpu_baseline": cpu,
             "clocks": clk.summary(),
             "sweep": sweep,
+            "context": context,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -328,6 +381,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-context", action="store_true", help="skip the informational 16-bit / cuBLAS measurements")
     ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager launches of one point and exit (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

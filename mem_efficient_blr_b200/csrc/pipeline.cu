@@ -75,22 +75,21 @@ __device__ __forceinline__ float ld1<__nv_bfloat16>(const __nv_bfloat16* p) { re
 template <typename T, int GS>
 __global__ void expand_coupling_kernel(const T* __restrict__ S, long long s_i, long long s_j, long long s_r,
                                        T* __restrict__ E, int b, int b_out, int R) {
-  // one thread per row (g, i, r'): b vectors of GS, each with a single non-zero at position r'
-  const int w = GS * b, h = GS * b_out;  // row length, rows per group
-  const long long rows = (long long)(R / GS) * h;
-  const long long row_id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (row_id >= rows) return;
-  const int row = (int)(row_id % h), g = (int)(row_id / h), i = row / GS, r1 = row % GS;
-  T* dst = E + row_id * w;
-  const T* src = S + i * s_i + (long long)(GS * g + r1) * s_r;
-  for (int j = 0; j < b; ++j) {
-    alignas(16) T v[GS];
+  // one thread per (row (g, i, r'), in-block j): a vector of GS values with a single non-zero at position r';
+  // consecutive threads write consecutive vectors of a row
+  const long long total = (long long)(R / GS) * GS * b_out * b;
+  const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (id >= total) return;
+  const int j = (int)(id % b);
+  const long long row_id = id / b;
+  const int h = GS * b_out, row = (int)(row_id % h), g = (int)(row_id / h), i = row / GS, r1 = row % GS;
+  alignas(16) T v[GS];
 #pragma unroll
-    for (int k = 0; k < GS; ++k) v[k] = T(0.f);
-    v[r1] = src[j * s_j];
+  for (int k = 0; k < GS; ++k) v[k] = T(0.f);
+  v[r1] = S[i * s_i + j * s_j + (long long)(GS * g + r1) * s_r];
+  T* dst = E + id * GS;
 #pragma unroll
-    for (int k = 0; k < GS / 8; ++k) *reinterpret_cast<uint4*>(dst + GS * j + 8 * k) = *reinterpret_cast<const uint4*>(v + 8 * k);
-  }
+  for (int k = 0; k < GS / 8; ++k) *reinterpret_cast<uint4*>(dst + 8 * k) = *reinterpret_cast<const uint4*>(v + 8 * k);
 }
 
 // Any block count / any strides: one thread per output element.
@@ -121,12 +120,12 @@ static int run_couple_generic(const void* y, const void* S, int64_t s_i, int64_t
 template <typename T>
 static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* E, int b, int b_out, int R, int gs,
                       cudaStream_t stream) {
-  const long long rows = (long long)(R / gs) * gs * b_out;
-  const unsigned blocks = (unsigned)((rows + 127) / 128);
+  const long long total = (long long)(R / gs) * gs * b_out * b;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
   if (gs == 16)
-    expand_coupling_kernel<T, 16><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
+    expand_coupling_kernel<T, 16><<<blocks, 256, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
   else
-    expand_coupling_kernel<T, 8><<<blocks, 128, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
+    expand_coupling_kernel<T, 8><<<blocks, 256, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
   BLR_CUDA_OK(cudaGetLastError());
   return BLR_OK;
 }
