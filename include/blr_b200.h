@@ -17,7 +17,8 @@
  *     reference's torch layouts); BLR_W_MMAJOR = [block][k][out_row] (output index contiguous, the
  *     layouts of the reference's Triton entry points).
  *   - Return value: 0 on success, a negative BLR_ERR_* code otherwise; blr_last_error() has the text.
- *     Token counts up to 16 run one weight-streaming kernel; larger counts run the tensor-core pipeline.
+ *     Token counts up to 16 run one weight-streaming kernel (BLAST on up to 8 tokens: a kernel of thread-block
+ *     clusters, one cluster per slice of the rank index); larger counts run the tensor-core pipeline.
  */
 #ifndef BLR_B200_H_
 #define BLR_B200_H_
@@ -69,6 +70,11 @@ int blr_version(void);
  * NULL switches it off. No reference counterpart. */
 int blr_debug_stream_timeline(void* dev_ptr);
 
+/* Test aid: BLAST on 1..8 tokens normally runs on the cluster kernel where the shape allows it;
+ * which = 1 sends those calls to the grid-wide streaming kernel instead (as 9..16 tokens always are),
+ * which = 0 restores the automatic choice. Process-wide. No reference counterpart. */
+int blr_debug_decode_path(int which);
+
 /* Text of the last error on the calling thread. No reference counterpart (the reference raises
  * Python AssertionError, e.g. blast_kernels.py:1951-1955). */
 const char* blr_last_error(void);
@@ -78,8 +84,9 @@ const char* blr_last_error(void);
  * reference allocates its intermediates with torch.empty per call (blast_kernels.py:1967, 2703). */
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width);
 
-/* Zeroes the control words at the start of a workspace.  Required once after allocation and after
- * a call reported BLR_ERR_TIMEOUT through blr_workspace_status. No reference counterpart. */
+/* Zeroes the fixed head of a workspace: 1 KiB of control words and the 2 MiB fp32 accumulation area of the
+ * cluster kernel (the kernels leave both zero again when they finish).  Required once after allocation and
+ * after a call reported BLR_ERR_TIMEOUT through blr_workspace_status. No reference counterpart. */
 int blr_workspace_init(void* ws, size_t ws_bytes, void* stream);
 
 /* Reads the status word of a workspace (synchronises `stream`): 0, or BLR_ERR_TIMEOUT if a kernel
@@ -113,7 +120,7 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
  * synchronisation of cudaMalloc is not acceptable.  This entry point has
  * no counterpart in the reference.  Same arguments and results as blr_blast, minus (ws, ws_bytes); 1..16 tokens
  * only.  Its scratch is a 4 MiB array built into the library's device image, which every GPU that loads the
- * library holds until exit; calls with blr_workspace_bytes(n_tokens, b, R) > 4 MiB (b * n_tokens * R > 699008)
+ * library holds until exit; calls with blr_workspace_bytes(n_tokens, b, R) > 4 MiB (b * n_tokens * R above about 349 000)
  * are rejected with BLR_ERR_WORKSPACE.  The first call on each device looks the array up with
  * cudaGetSymbolAddress (that device must be current) - make that first call before any stream capture.  It calls
  * no cudaMalloc / cudaFree or other allocating routine.  All calls on a device share the one array: it keeps the

@@ -1,0 +1,465 @@
+// BLAST decode kernel built on thread-block clusters (see blast_cluster.h for the decomposition).
+//
+// Per CTA (block index `blk` = rank in the cluster, slice `sl` = cluster index): one producer warp streams, through
+// a ring of TMA stages, first the rows [sl*rs, (sl+1)*rs) of V_blk with the matching boxes of x_blk, then all Q
+// rows of U_blk restricted to the slice's columns; eight consumer warps turn the stages into mma.sync products
+// exactly like the grid-wide streaming kernel (one 16-row group per warp).  Between the two phases the cluster
+// exchanges y through distributed shared memory, guarded by mbarriers that peers arrive on remotely.
+// All waits are bounded; nothing here spins on another cluster.
+#include "blast_cluster.h"
+#include "ptx.cuh"
+#include "stream_device.cuh"
+#include "tmap.h"
+
+namespace blr {
+
+template <bool BF16, int NT>
+__global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(const __grid_constant__ ClusterParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  constexpr int NP = NT * 8;                    // token rows kept everywhere
+  constexpr uint32_t kABoxBytes = NP * 128;     // one [tokens][64 k] activation box
+  const uint32_t NST = p.nstages, stage_bytes = p.stage_bytes;
+  const int rs = p.rs;
+  // [ring][ybuf: NP x rs 16-bit][sbuf: b x rs 16-bit][zbuf: rs/64 boxes][barriers]
+  uint8_t* ybuf = smem + (size_t)NST * stage_bytes;
+  uint8_t* sbuf = ybuf + NP * rs * 2;
+  uint8_t* zbuf = sbuf + 16 * rs * 2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zbuf + (rs / 64) * kABoxBytes);
+  // full[16], empty[16], y_ready, read_done
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 16);
+  const uint32_t y_ready = smem_u32(bars + 32), read_done = smem_u32(bars + 33);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 34);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blk = blockIdx.x, sl = blockIdx.y, part = blockIdx.z, nb = p.b;
+  const int q_lo = part * p.q_part, q_hi = min(p.Q, q_lo + p.q_part);
+  const int r_begin = sl * rs, r_len = min(rs, p.R - r_begin);
+  const PhaseDesc& ph0 = p.ph[0];
+  const PhaseDesc& ph1 = p.ph[1];
+
+  unsigned long long* tl = p.timeline ? p.timeline + (size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 : nullptr;
+#define BLR_STAMP(slot) do { if (tl) tl[slot] = (unsigned long long)clock64(); } while (0)
+  if (threadIdx.x == 0 && tl) { tl[0] = globaltimer_ns(); tl[15] = (unsigned long long)clock64(); }
+  if (warp == kConsumerWarps) {
+    // descriptors this CTA will use: one per batch height for k-contiguous weights (full batches and the last one)
+    const int rows0 = min(rs, p.R - blockIdx.y * rs), rows1 = min(p.Q, (int)(blockIdx.z + 1) * p.q_part) - (int)blockIdx.z * p.q_part;
+    const int hf0 = (min(rows0, kBatchRows) + 15) >> 4, hl0 = (((rows0 - 1) % kBatchRows) + 16) >> 4;
+    const int hf1 = (min(rows1, kBatchRows) + 15) >> 4, hl1 = (((rows1 - 1) % kBatchRows) + 16) >> 4;
+    if (lane == 0) tma_prefetch_desc(&ph0.tmW[ph0.kmajor ? hf0 - 1 : 0]);
+    if (lane == 1) tma_prefetch_desc(&ph0.tmA);
+    if (lane == 2) tma_prefetch_desc(&ph1.tmW[ph1.kmajor ? hf1 - 1 : 0]);
+    if (lane == 3 && ph0.kmajor && hl0 != hf0) tma_prefetch_desc(&ph0.tmW[hl0 - 1]);
+    if (lane == 4 && ph1.kmajor && hl1 != hf1) tma_prefetch_desc(&ph1.tmW[hl1 - 1]);
+  }
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    *last_flag = 0;
+    for (uint32_t s = 0; s < NST; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kConsumerWarps);
+    }
+    mbar_init(y_ready, nb);
+    mbar_init(read_done, nb);
+    mbar_init_fence();
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __syncthreads();
+  // Peers arrive on this CTA's barriers only after their first phase; the cluster barrier that makes the
+  // barriers visible to them is split so that nobody waits for it here.
+  cluster_arrive();
+  if (threadIdx.x == 0) BLR_STAMP(1);
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------ producer (lane 0; for m-contiguous weights lanes 0..7 issue tiles)
+    // One ring stage of phase `phs`: batch of rows at r0, chunk group c.  Weights and activations complete on
+    // the same barrier; they can be issued separately (do_w announces the bytes of both).
+    auto issue = [&](int phs, int r0, int row_hi, int c, uint32_t slot, bool do_w, bool do_x) {
+      const PhaseDesc& ph = p.ph[phs];
+      const int ksub = phs == 0 ? p.ks0 : p.ks1;
+      const int kstep = ph.kmajor ? (ph.wbits == 16 ? 64 : 128) : 64;             // coordinate units per chunk
+      // K range: whole P in phase 0, the slice in phase 1 (coordinates are elements, or bytes for int8 / int4)
+      const int k_base = phs == 0 ? 0 : (ph.kmajor && ph.wbits == 4 ? r_begin / 2 : r_begin);
+      const int rows = min(kBatchRows, row_hi - r0);
+      const int h = (rows + 15) >> 4, tiles = (rows + 31) >> 5;
+      const uint32_t dst = smem_base + slot * stage_bytes, bar = full0 + 8 * slot;
+      const int k0 = k_base + c * ksub * kstep;
+      const uint32_t a_bytes = phs == 0 ? ksub * ph.a_boxes * kABoxBytes : 0u;
+      if (do_w) {
+        if (ph.kmajor) {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(bar, ksub * h * 16 * 128 + a_bytes);
+            for (int sub = 0; sub < ksub; ++sub)
+              tma_load_3d(dst + sub * kSubBytes, &ph.tmW[h - 1], k0 + sub * kstep, r0, blk, bar);
+          }
+        } else {
+          if (lane == 0) mbar_arrive_expect_tx(bar, ksub * tiles * kTileBytes + a_bytes);
+          __syncwarp();
+          if (lane < ksub * 4 && (lane & 3) < tiles)
+            tma_load_3d(dst + (lane >> 2) * kSubBytes + (lane & 3) * kTileBytes, &ph.tmW[0], r0 + (lane & 3) * 32,
+                        k0 + (lane >> 2) * kstep, blk, bar);
+        }
+      }
+      if (do_x && phs == 0 && lane == 0) {
+        const int nbox = ksub * ph.a_boxes, ka = c * nbox * 64;
+        for (int bx = 0; bx < nbox; ++bx) tma_load_3d(dst + p.w_bytes + bx * kABoxBytes, &ph.tmA, ka + bx * 64, 0, blk, bar);
+      }
+    };
+    // The weights do not depend on the kernel before this one in the stream, the activations do: fill the
+    // ring with first-phase weights, wait for the previous kernel, then add the activations.
+    const int nstage0 = (ph0.nchunks + p.ks0 - 1) / p.ks0;
+    int pre = 0;
+    for (int pass = 0; pass < 2; ++pass) {
+      pre = 0;
+      for (int r0 = r_begin; r0 < r_begin + r_len && pre < (int)NST; r0 += kBatchRows)
+        for (int c = 0; c < nstage0 && pre < (int)NST; ++c, ++pre) issue(0, r0, r_begin + r_len, c, pre, pass == 0, pass == 1);
+      if (pass == 0) {
+        if (lane == 0) BLR_STAMP(12);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+      }
+    }
+    if (lane == 0) BLR_STAMP(13);
+    RingPos rp;
+    bool ok = true;
+    int skip = pre;
+    for (int phs = 0; phs < 2 && ok; ++phs) {
+      const int ksub = phs == 0 ? p.ks0 : p.ks1;
+      const int row_lo = phs == 0 ? r_begin : q_lo, row_hi = phs == 0 ? r_begin + r_len : q_hi;
+      const int nstage = phs == 0 ? nstage0 : (p.nchunks1 + ksub - 1) / ksub;
+      for (int r0 = row_lo; r0 < row_hi && ok; r0 += kBatchRows) {
+        for (int c = 0; c < nstage; ++c) {
+          if (skip > 0) {  // issued above
+            --skip;
+            rp.advance(NST);
+            continue;
+          }
+          if (!rp.first_pass) {
+            int w_ok = 1;
+            if (lane == 0) w_ok = mbar_wait(empty0 + 8 * rp.s, rp.use_parity ^ 1u, abort_flag) ? 1 : 0;
+            w_ok = __shfl_sync(0xffffffffu, w_ok, 0);
+            if (!w_ok) { ok = false; break; }
+          }
+          issue(phs, r0, row_hi, c, rp.s, true, true);
+          rp.advance(NST);
+        }
+      }
+    }
+    cluster_wait();
+  } else {
+    // ------------------------------------------------ consumers
+    const int ctid = threadIdx.x;
+    const int row0 = warp * 16, g = lane >> 2, tq = lane & 3;
+    RingPos rp;
+    bool ok = true;
+    // (a) the coupling factors of this CTA's out-block on the slice -> sbuf[j][r], asynchronously
+    const bool s_vec = p.s_r == 1 && ((p.s_i | p.s_j) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.S) & 15) == 0;
+    {
+      const uint16_t* S = reinterpret_cast<const uint16_t*>(p.S);
+      const int nv = rs >> 3;
+      for (int e = ctid; e < nb * nv; e += kConsumerWarps * 32) {
+        const int j = e / nv, v = e - j * nv, r = r_begin + v * 8;
+        const uint32_t dst = smem_u32(sbuf) + (j * rs + v * 8) * 2;
+        if (s_vec && r + 8 <= p.R) {
+          cp_async16(dst, S + blk * p.s_i + j * p.s_j + r);
+        } else {
+          uint16_t* d = reinterpret_cast<uint16_t*>(sbuf) + j * rs + v * 8;
+          for (int k = 0; k < 8; ++k) d[k] = r + k < p.R ? S[blk * p.s_i + j * p.s_j + (long long)(r + k) * p.s_r] : (uint16_t)0;
+        }
+      }
+      // (b) clear the coupled activations (token rows past N and ranks past the slice stay zero)
+      for (int e = ctid; e < (rs / 64) * (int)kABoxBytes / 16; e += kConsumerWarps * 32) reinterpret_cast<uint4*>(zbuf)[e] = make_uint4(0, 0, 0, 0);
+      for (int e = ctid; e < NP * rs * 2 / 16; e += kConsumerWarps * 32) reinterpret_cast<uint4*>(ybuf)[e] = make_uint4(0, 0, 0, 0);
+    }
+    consumer_bar();
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // out32, the counters and x belong to the previous kernel until here
+    if (ctid == 0) BLR_STAMP(14);
+    for (int phs = 0; phs < 2; ++phs) {
+      const PhaseDesc& ph = p.ph[phs];
+      const int ksub = phs == 0 ? p.ks0 : p.ks1, wbits = ph.wbits, kmajor = ph.kmajor;
+      const int row_lo = phs == 0 ? r_begin : q_lo, row_hi = phs == 0 ? r_begin + r_len : q_hi;
+      const int nstage = phs == 0 ? (ph.nchunks + ksub - 1) / ksub : (p.nchunks1 + ksub - 1) / ksub;
+      const uint32_t a_sub = ph.a_boxes * kABoxBytes;
+      for (int r0 = row_lo; r0 < row_hi; r0 += kBatchRows) {
+        const int rows = min(kBatchRows, row_hi - r0);
+        const bool active = row0 < rows;
+        // per-row scales of quantised weights: fetched now, used after the batch's last stage
+        float sc2[2] = {1.f, 1.f};
+        if (phs == 0 && ph.scale && active) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int m = r0 + row0 + g + 8 * h;
+            if (m < row_hi) sc2[h] = __half2float(__ldg(ph.scale + (long long)blk * ph.M + m));
+          }
+        }
+        float acc[4][NT][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[q][n][e] = 0.f;
+        for (int c = 0; c < nstage && ok; ++c) {
+          const uint32_t s = rp.s;
+          if (!mbar_wait(full0 + 8 * s, rp.use_parity, abort_flag)) { ok = false; break; }
+          if (ctid == 0 && c == 0 && r0 == row_lo) BLR_STAMP(9 + phs);
+          if (active) {
+            uint32_t sW = smem_base + s * stage_bytes;
+            uint32_t sA = phs == 0 ? sW + p.w_bytes : smem_u32(zbuf) + c * ksub * a_sub;
+            for (int sub = 0; sub < ksub; ++sub, sW += kSubBytes, sA += a_sub) {
+              if (wbits == 16) {
+                if (kmajor) consume_k16<BF16, NT>(sW, sA, row0, acc, lane);
+                else consume_m16<BF16, NT>(sW + (warp >> 1) * kTileBytes, sA, warp & 1, acc, lane);
+              } else if (wbits == 8) {
+                consume_k8<BF16, NT>(sW, sA, row0, acc, lane);
+              } else {
+                consume_k4<BF16, NT>(sW, sA, row0, acc, lane);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty0 + 8 * s);
+          rp.advance(NST);
+        }
+        if (ctid == 0 && phs == 1 && r0 + kBatchRows >= row_hi) BLR_STAMP(11);
+        if (active) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int m = r0 + row0 + g + 8 * h;
+            if (m < row_hi) {
+              if (phs == 0) {
+                // y_blk[token][r - r_begin] (16-bit) into this CTA's shared memory, for the whole cluster to read
+                const float sc = sc2[h];
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                  for (int e = 0; e < 2; ++e) {
+                    float v = (acc[0][n][2 * h + e] + acc[1][n][2 * h + e] + acc[2][n][2 * h + e] + acc[3][n][2 * h + e]) * sc;
+                    if (p.round_y) v = round_clamp_i8(v);
+                    store16<BF16>(ybuf, (long long)(n * 8 + tq * 2 + e) * rs + (m - r_begin), v);
+                  }
+              } else {
+                // partial out over this slice: fp32 reduction into out32[blk*Q + m][token]
+                float* dst = p.out32 + ((long long)blk * p.Q + m) * NP;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                  const int tok = n * 8 + tq * 2;
+                  if (tok < p.N)
+                    red_add_v2_f32(dst + tok, acc[0][n][2 * h] + acc[1][n][2 * h] + acc[2][n][2 * h] + acc[3][n][2 * h],
+                                   acc[0][n][2 * h + 1] + acc[1][n][2 * h + 1] + acc[2][n][2 * h + 1] + acc[3][n][2 * h + 1]);
+                }
+              }
+            }
+          }
+        }
+      }
+      if (phs == 0) {
+        // ---- exchange y inside the cluster and couple this CTA's out-block on the slice
+        consumer_bar();  // all of y_blk is in ybuf
+        if (ctid == 0) BLR_STAMP(2);
+        cluster_wait();  // every CTA of the cluster has initialised its barriers (long since)
+        if (ctid < nb) mbar_arrive_remote(mapa_shared(y_ready, ctid));
+        if (!mbar_wait_cluster(y_ready, 0, abort_flag)) ok = false;
+        cp_async_wait_all();
+        consumer_bar();  // sbuf complete for every thread
+        if (ctid == 0) BLR_STAMP(3);
+        if (!*abort_flag) {
+          const int nv = rs >> 3;
+          const uint32_t ybase = smem_u32(ybuf), sbase = smem_u32(sbuf);
+          for (int e = ctid; e < p.N * nv; e += kConsumerWarps * 32) {
+            const int n = e / nv, v = e - n * nv;
+            float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            const uint32_t yoff = ybase + (n * rs + v * 8) * 2;
+            for (int j0 = 0; j0 < nb; j0 += 8) {
+              uint4 yv[8];
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj)
+                yv[jj] = j0 + jj < nb ? ld_shared_cluster_v4(mapa_shared(yoff, j0 + jj)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) {
+                if (j0 + jj < nb) {
+                  uint4 sv;
+                  lds128(sbase + ((j0 + jj) * rs + v * 8) * 2, sv.x, sv.y, sv.z, sv.w);
+                  const float2 s0 = unpack16x2<BF16>(sv.x), s1 = unpack16x2<BF16>(sv.y), s2 = unpack16x2<BF16>(sv.z), s3 = unpack16x2<BF16>(sv.w);
+                  const float2 y0 = unpack16x2<BF16>(yv[jj].x), y1 = unpack16x2<BF16>(yv[jj].y), y2 = unpack16x2<BF16>(yv[jj].z), y3 = unpack16x2<BF16>(yv[jj].w);
+                  s[0] = fmaf(s0.x, y0.x, s[0]); s[1] = fmaf(s0.y, y0.y, s[1]);
+                  s[2] = fmaf(s1.x, y1.x, s[2]); s[3] = fmaf(s1.y, y1.y, s[3]);
+                  s[4] = fmaf(s2.x, y2.x, s[4]); s[5] = fmaf(s2.y, y2.y, s[5]);
+                  s[6] = fmaf(s3.x, y3.x, s[6]); s[7] = fmaf(s3.y, y3.y, s[7]);
+                }
+              }
+            }
+            if (p.round_z) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) s[k] = round_clamp_i8(s[k]);
+            }
+            uint4 o;
+            o.x = pack16x2<BF16>(s[0], s[1]); o.y = pack16x2<BF16>(s[2], s[3]);
+            o.z = pack16x2<BF16>(s[4], s[5]); o.w = pack16x2<BF16>(s[6], s[7]);
+            *reinterpret_cast<uint4*>(zbuf + (v >> 3) * kABoxBytes + sw128(n, v & 7)) = o;
+          }
+        }
+        consumer_bar();  // zbuf complete; this CTA no longer reads its peers' ybuf
+        if (ctid == 0) BLR_STAMP(4);
+        if (ctid < nb) mbar_arrive_remote(mapa_shared(read_done, ctid));
+      }
+    }
+    if (ctid == 0) BLR_STAMP(5);
+    // ---- the last slice to finish a block converts it
+    __threadfence();
+    consumer_bar();
+    if (ctid == 0) BLR_STAMP(6);
+    if (ctid == 0) {
+      int last = 0;
+      if (!*abort_flag) {
+        const unsigned prev = atomicAdd(p.counters + part * nb + blk, 1u);
+        last = prev == (unsigned)p.nslices - 1 ? 1 : 0;
+      } else {
+        atomicExch(p.status, 1u);
+      }
+      *last_flag = last;
+    }
+    consumer_bar();
+    if (*last_flag) {
+      __threadfence();
+      // one output row per thread and step, three steps in flight: the fp32 partial sums of a row are NP
+      // consecutive floats, so the loads are whole 32-byte sectors and do not wait on one another
+      const __half* usc = ph1.scale;
+      constexpr int kRowsInFlight = 3, kV4 = NP / 4;
+      for (int q0 = q_lo + ctid; q0 < q_hi; q0 += kRowsInFlight * kConsumerWarps * 32) {
+        float4 v[kRowsInFlight][kV4];
+        float sc[kRowsInFlight];
+#pragma unroll
+        for (int i = 0; i < kRowsInFlight; ++i) {
+          const int q = q0 + i * kConsumerWarps * 32;
+          sc[i] = 1.f;
+          if (q < q_hi) {
+            const float4* src = reinterpret_cast<const float4*>(p.out32 + ((long long)blk * p.Q + q) * NP);
+#pragma unroll
+            for (int k = 0; k < kV4; ++k) v[i][k] = __ldcg(src + k);
+            if (usc) sc[i] = __half2float(__ldg(usc + (long long)blk * p.Q + q));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kRowsInFlight; ++i) {
+          const int q = q0 + i * kConsumerWarps * 32;
+          if (q < q_hi) {
+            float4* src = reinterpret_cast<float4*>(p.out32 + ((long long)blk * p.Q + q) * NP);
+#pragma unroll
+            for (int k = 0; k < kV4; ++k) {
+              src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+              const float e4[4] = {v[i][k].x, v[i][k].y, v[i][k].z, v[i][k].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int n = k * 4 + e;
+                if (n < p.N) store16<BF16>(p.out, (long long)n * p.ldo + (long long)blk * p.Q + q, e4[e] * sc[i]);
+              }
+            }
+          }
+        }
+      }
+      if (ctid == 0) p.counters[part * nb + blk] = 0u;
+    }
+    if (ctid == 0) BLR_STAMP(7);
+    // ---- peers may still be reading this CTA's ybuf: stay until all of them are done
+    mbar_wait_cluster(read_done, 0, abort_flag);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) BLR_STAMP(8);
+#undef BLR_STAMP
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+size_t cluster_smem_bytes(const ClusterParams& p, int np) {
+  return (size_t)p.nstages * p.stage_bytes + (size_t)np * p.rs * 2 + 16 * p.rs * 2 + (p.rs / 64) * np * 128 + 40 * 8 + 1024;
+}
+
+template <bool BF16, int NT>
+static int cluster_capacity_impl(int b, int smem_bytes) {
+  DeviceInfo di;
+  if (device_info(&di) != BLR_OK) return 0;
+  auto kern = blr_blast_cluster_kernel<BF16, NT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin) != cudaSuccess) return 0;
+  if (b > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(b, 1, 1);
+  cfg.blockDim = dim3(kClusterThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = b;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, (const void*)kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+// Resident clusters of b CTAs when every CTA takes smem_bytes of dynamic shared memory; the answer depends on
+// whether one or two CTAs fit an SM, so it is cached for those two classes of size.
+int cluster_capacity(int b, int is_bf16, int n_tokens, int smem_bytes) {
+  static int cache[64][17][2][2];
+  static bool have[64][17][2][2] = {};
+  DeviceInfo di;
+  int dev = 0;
+  if (device_info(&di) != BLR_OK || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || b < 1 || b > 16) return 0;
+  if (n_tokens > kClusterMaxTokens) return 0;
+  const int bf = is_bf16 ? 1 : 0, two = smem_bytes <= kClusterHalfSmem ? 1 : 0;
+  if (!have[dev][b][bf][two]) {
+    const int sm = two ? kClusterHalfSmem : di.max_smem_optin - 1024;
+    cache[dev][b][bf][two] = bf ? cluster_capacity_impl<true, 1>(b, sm) : cluster_capacity_impl<false, 1>(b, sm);
+    have[dev][b][bf][two] = true;
+  }
+  return cache[dev][b][bf][two];
+}
+
+template <bool BF16, int NT>
+static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != BLR_OK) return rc;
+  const size_t smem = cluster_smem_bytes(p, NT * 8);
+  BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
+              smem, di.max_smem_optin);
+  auto kern = blr_blast_cluster_kernel<BF16, NT>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.b, p.nslices, p.qsplit);
+  cfg.blockDim = dim3(kClusterThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = p.b;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 2;
+  void* args[] = {const_cast<ClusterParams*>(&p)};
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)kern, args));
+  return BLR_OK;
+}
+
+extern unsigned long long* g_stream_timeline;
+
+int launch_blast_cluster(const ClusterParams& p_in, int is_bf16, cudaStream_t stream) {
+  ClusterParams p = p_in;
+  p.timeline = g_stream_timeline;
+  BLR_REQUIRE(p.N >= 1 && p.N <= kClusterMaxTokens, BLR_ERR_UNSUPPORTED, "the cluster kernel takes 1..%d tokens", kClusterMaxTokens);
+  return is_bf16 ? launch_cluster_impl<true, 1>(p, stream) : launch_cluster_impl<false, 1>(p, stream);
+}
+
+}  // namespace blr

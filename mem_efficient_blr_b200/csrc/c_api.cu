@@ -4,6 +4,7 @@
 
 #include <mutex>
 
+#include "blast_cluster.h"
 #include "pipeline.h"
 #include "stream.h"
 #include "tmap.h"
@@ -11,7 +12,7 @@
 namespace blr {
 const char* last_error();
 
-static constexpr size_t kCtrlBytes = 256;
+static constexpr size_t kCtrlBytes = 1024;  // words 0..127: grid-wide streaming kernel; 128..254: cluster kernel counters; 255: its status
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct Workspace {
@@ -19,6 +20,7 @@ struct Workspace {
   void* region_a;  // 4 bytes per intermediate element
   void* region_b;  // 2 bytes per intermediate element
   void* region_c;  // expanded coupling factors (only sized for more than 16 tokens)
+  float* out32;    // fp32 accumulation area of the cluster kernel (kClusterOut32Bytes)
 };
 
 static int carve(void* ws, size_t ws_bytes, int64_t N, int64_t groups, int64_t width, Workspace* w) {
@@ -28,6 +30,8 @@ static int carve(void* ws, size_t ws_bytes, int64_t N, int64_t groups, int64_t w
   BLR_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255) == 0, BLR_ERR_ALIGN, "workspace must be 256-byte aligned");
   uint8_t* p = static_cast<uint8_t*>(ws);
   w->counters = reinterpret_cast<unsigned*>(p);
+  w->out32 = reinterpret_cast<float*>(p + kCtrlBytes);  // fixed place and size: it has to stay zero between calls
+  p += kClusterOut32Bytes;
   w->region_a = p + kCtrlBytes;
   w->region_b = p + kCtrlBytes + align256((size_t)groups * N * width * 4);
   w->region_c = static_cast<uint8_t*>(w->region_b) + align256((size_t)groups * N * width * 2);
@@ -127,6 +131,76 @@ static int check_layout(int layout) {
 }
 
 // ---------------------------------------------------------------------------------- BLAST (16-bit and quantised)
+// Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
+static int g_decode_path = 0;  // 0: automatic, 1: grid-wide streaming kernel only (blr_debug_decode_path)
+
+static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
+                         const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, const void* S,
+                         int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
+                         int64_t ldo, const Workspace& w, cudaStream_t stream) {
+  static const bool disabled = getenv("BLR_NO_CLUSTER") != nullptr;
+  // above 8 tokens the exchange through distributed shared memory costs more than the grid barriers it saves
+  const int np = 8;
+  if (disabled || g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
+  if ((long long)b * Q * np * 4 > kClusterOut32Bytes) return 1;
+  const int bf = dtype == BLR_DTYPE_BF16;
+  ClusterParams p = {};
+  int rc;
+  if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, v_bits, b, R, P))) return rc;
+  if ((rc = phase_acts(p.ph[0], dtype, x, P, N, b, ldx, P))) return rc;
+  if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, b, Q, R))) return rc;
+  p.ph[0].scale = static_cast<const __half*>(v_scale);
+  p.ph[1].scale = static_cast<const __half*>(u_scale);
+  DeviceInfo di;
+  if ((rc = device_info(&di))) return rc;
+  // Shape of the launch: ranks per slice (a multiple of what one second-phase chunk covers), row parts of U_i,
+  // and whether two CTAs share an SM.  Measured on the headline layer (b = 16, R = 1024, 16/8/4-bit weights):
+  // wide slices and many row parts win, and two CTAs per SM pay off only when they allow more parts, because
+  // each of them then has half the ring.
+  const int kx = p.ph[1].kmajor ? (u_bits == 16 ? 64 : (u_bits == 8 ? 128 : 256)) : 64;
+  int best_rs = 0, best_parts = 1, best_two = 0;
+  static const char* forced = getenv("BLR_CLUSTER_SHAPE");  // "rs,parts,two": measurement aid
+  if (forced) {
+    if (sscanf(forced, "%d,%d,%d", &best_rs, &best_parts, &best_two) != 3) return 1;
+    if (best_rs % kx != 0 || best_rs < kx || best_rs > kClusterMaxSlice || best_parts < 1 || best_parts > kClusterMaxParts) return 1;
+  } else {
+    const int r_up = (R + kx - 1) / kx * kx;
+    best_rs = r_up < kClusterMaxSlice ? r_up : kClusterMaxSlice / kx * kx;
+    if (best_rs < kx) return 1;
+    const int nsl = (R + best_rs - 1) / best_rs;
+    const int max_parts = Q / kBatchRows < 1 ? 1 : (Q / kBatchRows > kClusterMaxParts ? kClusterMaxParts : Q / kBatchRows);
+    int parts1 = cluster_capacity(b, bf, (int)N, di.max_smem_optin - 1024) / nsl;
+    int parts2 = cluster_capacity(b, bf, (int)N, kClusterHalfSmem) / nsl;
+    if (parts1 > max_parts) parts1 = max_parts;
+    if (parts2 > max_parts) parts2 = max_parts;
+    if (parts1 < 1 && parts2 < 1) return 1;  // more slices than resident clusters: grid-wide kernel
+    best_two = parts2 > parts1 ? 1 : 0;
+    best_parts = best_two ? parts2 : parts1;
+  }
+  const int rs = best_rs;
+  p.N = (int)N; p.b = b; p.R = R; p.Q = Q; p.rs = rs; p.nslices = (R + rs - 1) / rs;
+  p.qsplit = best_parts;
+  p.q_part = ((Q + best_parts - 1) / best_parts + 15) / 16 * 16;
+  p.nchunks1 = rs / kx;
+  // chunks per stage: two where that divides both phases' chunk counts (a chunk past the slice would read the
+  // next slice's columns), else one, so that every stage of the ring carries a full load in both phases
+  p.ks0 = p.ks1 = (p.nchunks1 % 2 == 0 && p.ph[0].nchunks % 2 == 0) ? 2 : 1;
+  p.round_y = act8; p.round_z = act8;
+  p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
+  p.out = out; p.ldo = ldo; p.out32 = w.out32; p.counters = w.counters + 128; p.status = w.counters + 255;
+  p.w_bytes = p.ks0 * kSubBytes;
+  p.stage_bytes = p.w_bytes + p.ks0 * p.ph[0].a_boxes * np * 128;
+  p.nstages = 2;
+  const int extras = (int)cluster_smem_bytes(p, np) - 2 * p.stage_bytes;
+  const int budget = best_two ? kClusterHalfSmem : di.max_smem_optin - 1024;
+  int nst = (budget - extras) / p.stage_bytes;
+  p.nstages = nst > 16 ? 16 : nst;
+  if (p.nstages < 2) return 1;
+  if (forced && p.nslices * p.qsplit > cluster_capacity(b, bf, (int)N, budget)) return 1;
+  rc = launch_blast_cluster(p, bf, stream);
+  return rc;
+}
+
 static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, const void* S,
                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
@@ -145,6 +219,9 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   const int act8 = (flags & BLR_FLAG_ACT_INT8) ? 1 : 0;
 
   if (N <= kStreamMaxTokens) {
+    rc = cluster_blast(x, ldx, N, dtype, U, u_layout, u_bits, u_scale, V, v_layout, v_bits, v_scale, S, s_i, s_j, s_r, b, bo,
+                       P, Q, R, act8, out, ldo, w, stream);
+    if (rc <= 0) return rc;  // 0: launched, < 0: error, 1: not applicable -> grid-wide streaming kernel
     StreamParams p = {};
     p.nphases = 2; p.mix = 1; p.b = b; p.b_out = bo; p.R = R; p.round_z = act8;
     p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
@@ -201,6 +278,11 @@ int blr_debug_stream_timeline(void* dev_ptr) {
   set_stream_timeline(static_cast<unsigned long long*>(dev_ptr));
   return BLR_OK;
 }
+int blr_debug_decode_path(int which) {
+  BLR_REQUIRE(which == 0 || which == 1, BLR_ERR_ARG, "decode path must be 0 (automatic) or 1 (grid-wide kernel)");
+  g_decode_path = which;
+  return BLR_OK;
+}
 const char* blr_last_error(void) { return blr::last_error(); }
 
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
@@ -208,21 +290,21 @@ size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
   const size_t e = (size_t)groups * (size_t)n_tokens * (size_t)width;
   // above 16 tokens BLAST also keeps its expanded coupling factors: (width / 16) matrices of (16 groups)^2 16-bit values
   const size_t c = n_tokens > 16 ? (size_t)groups * groups * ((size_t)width + 16) * 32 : 0;
-  return kCtrlBytes + align256(e * 4) + align256(e * 2) + align256(c);
+  return kCtrlBytes + kClusterOut32Bytes + align256(e * 4) + align256(e * 2) + align256(c);
 }
 
 int blr_workspace_init(void* ws, size_t ws_bytes, void* stream) {
-  BLR_REQUIRE(ws != nullptr && ws_bytes >= kCtrlBytes, BLR_ERR_WORKSPACE, "workspace too small");
-  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes, static_cast<cudaStream_t>(stream)));
+  BLR_REQUIRE(ws != nullptr && ws_bytes >= kCtrlBytes + kClusterOut32Bytes, BLR_ERR_WORKSPACE, "workspace too small");
+  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes + kClusterOut32Bytes, static_cast<cudaStream_t>(stream)));
   return BLR_OK;
 }
 
 int blr_workspace_status(const void* ws, void* stream) {
   BLR_REQUIRE(ws != nullptr, BLR_ERR_WORKSPACE, "workspace is null");
-  unsigned words[4] = {0, 0, 0, 0};
+  unsigned words[256] = {};
   BLR_CUDA_OK(cudaMemcpyAsync(words, ws, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   BLR_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  if (words[3] != 0) {
+  if (words[3] != 0 || words[255] != 0) {
     set_last_error("a kernel gave up on a device-side wait (status word %u)", words[3]);
     return BLR_ERR_TIMEOUT;
   }

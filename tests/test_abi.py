@@ -36,9 +36,10 @@ def test_header_symbols_are_exported(lib):
 
 def test_host_only_entry_points(lib):
     assert lib.blr_version() >= 100
-    # groups * tokens * width elements: 4-byte + 2-byte regions + 256 control bytes, 256-byte granules
-    assert lib.blr_workspace_bytes(16, 16, 1024) == 256 + 16 * 16 * 1024 * 6
-    assert lib.blr_workspace_bytes(1, 0, 0) == 256
+    # groups * tokens * width elements: 4-byte + 2-byte regions, after the fixed part
+    fixed = 1024 + (2 << 20)   # control words + the fp32 accumulation area of the cluster kernel
+    assert lib.blr_workspace_bytes(16, 16, 1024) == fixed + 16 * 16 * 1024 * 6
+    assert lib.blr_workspace_bytes(1, 0, 0) == fixed
     big = lib.blr_workspace_bytes(2048, 16, 1024)
     assert big >= 256 + 2048 * 16 * 1024 * 6 + 16 * 16 * 1024 * 32
 

@@ -123,6 +123,29 @@ def test_blast_weight_quantised(K, shape, dtype, bits):
     assert orc.rel_fro(got.float().cpu(), ref) < TOL
 
 
+def test_small_batches_on_the_grid_wide_kernel(K):
+    """1..8 tokens normally take the cluster kernel; the grid-wide streaming kernel must give the same
+    answers for them (it is what runs when the shape does not fit a cluster)."""
+    lib = K.lib.load()
+    assert lib.blr_debug_decode_path(1) == 0
+    try:
+        for N, I, O, b, R, bits in [(1, 4096, 11008, 16, 1024, 16), (5, 768, 768, 3, 128, 16),
+                                    (4, 4096, 11008, 16, 1024, 8), (1, 4096, 11008, 16, 1024, 4)]:
+            x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=N + bits)
+            if bits == 16:
+                ref, _, _ = orc.blast(x, U, Vt, S)
+                got = K.bk.blast_torch_layout(*_cuda(x, U, Vt, S))
+            else:
+                Uq, us = orc.quantize_sym(U, bits)
+                Vq, vs = orc.quantize_sym(Vt, bits)
+                ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits)
+                got = K.bq.blast_wq(*_cuda(x, Uq, us, Vq, vs, S), bits)
+            _sync_ok(K)
+            assert orc.rel_fro(got.float().cpu(), ref) < TOL, (N, I, O, b, R, bits)
+    finally:
+        assert lib.blr_debug_decode_path(0) == 0
+
+
 def test_blast_act_int8_matches_reference_rounding(K):
     x, U, Vt, S = orc.make_blast_inputs(4, 512, 768, 4, 128, torch.bfloat16, seed=21)
     x = x * 4  # spread the intermediates over the int8 range
