@@ -88,7 +88,9 @@ def dtype_code(dt: torch.dtype) -> int:
 
 
 def stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """The current stream of `device` as an integer handle."""
+    idx = device.index
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device() if idx is None else idx)
 
 
 # ----------------------------------------------------------------------------- workspaces

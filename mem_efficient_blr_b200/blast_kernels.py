@@ -43,7 +43,7 @@ def _dims_bmm(x, U, V, S):
 
 def _partial_fp16(x, U, V, S, flags=L.FLAG_NONE):
     b, p, q, r = _dims_partial(x, U, V, S)
-    out = ops.blast_op(ops._flat2d(x), U, V, S, L.MMAJOR, L.MMAJOR, r, b * r, 1, b, p, q, r, flags)
+    out = ops.blast(ops._flat2d(x), U, V, S, L.MMAJOR, L.MMAJOR, r, b * r, 1, b, p, q, r, flags)
     return out.reshape(*x.shape[:-1], b * q)
 
 
@@ -96,7 +96,7 @@ def triton_blast_full_fp32(x, U, V, S):
 def triton_blast_bmm_fp16(x, U, V, S, config=(None, None, None)):
     """Replaces triton_blast_bmm_fp16 (blast_kernels.py:3043-3065)."""
     b, p, q, r = _dims_bmm(x, U, V, S)
-    out = ops.blast_op(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_NONE)
+    out = ops.blast(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_NONE)
     return out.reshape(*x.shape[:-1], b * q)
 
 
@@ -113,7 +113,7 @@ def blast_torch_layout(x, U, Vt, S, flags=L.FLAG_NONE):
     b, r, p = Vt.shape
     b2, q, r2 = U.shape
     assert b == b2 and b != 1 and r2 == r and tuple(S.shape) == (b2, b, r)
-    out = ops.blast_op(ops._flat2d(x), U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags)
+    out = ops.blast(ops._flat2d(x), U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags)
     return out.reshape(*x.shape[:-1], b * q)
 
 
@@ -124,7 +124,7 @@ def blast_output_blocks(x, U_local, Vt, S_local, flags=L.FLAG_NONE):
     bo, q, r2 = U_local.shape
     assert 1 <= bo <= b and r2 == r and tuple(S_local.shape) == (bo, b, r)
     assert U_local.is_contiguous() and S_local.is_contiguous()
-    out = ops.blast_op(ops._flat2d(x), U_local, Vt, S_local, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags, bo)
+    out = ops.blast(ops._flat2d(x), U_local, Vt, S_local, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags, bo)
     return out.reshape(*x.shape[:-1], bo * q)
 
 

@@ -19,7 +19,7 @@ def triton_blast_bmm_int8_fp16(x, U, V, S, config=(None, None, None)):
     """U (b,Q,R), V (b,P,R), S (R,b_out,b_in), all 16-bit; activations rounded like the reference's kernels
     (blast_sym_quant_kernels.py:105-108, 227-230)."""
     b, p, q, r = _dims_bmm(x, U, V, S)
-    out = ops.blast_op(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_ACT_INT8)
+    out = ops.blast(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_ACT_INT8)
     return out.reshape(*x.shape[:-1], b * q)
 
 
@@ -53,5 +53,5 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     p = Vq.shape[-1] * (1 if bits == 8 else 2)
     assert b == b2 and b != 1 and tuple(S.shape) == (b, b, r)
     assert Uq.shape[-1] * (1 if bits == 8 else 2) == r and x.shape[-1] == b * p
-    out = ops.blast_wq_op(ops._flat2d(x), Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
+    out = ops.blast_wq(ops._flat2d(x), Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
     return out.reshape(*x.shape[:-1], b * q)

@@ -12,7 +12,7 @@ def triton_dense_fp16(x, w, config=None):
     """Replaces triton_dense_fp16 (dense_kernels.py:375-381)."""
     i, o = w.shape
     assert x.shape[-1] == i and w.is_contiguous()
-    return ops.dense_op(ops._flat2d(x), w, L.MMAJOR, i, o)
+    return ops.dense(ops._flat2d(x), w, L.MMAJOR, i, o)
 
 
 def triton_dense_fp32(x, w):
@@ -25,7 +25,7 @@ def triton_dense_fp32(x, w):
 def dense_torch_layout(x, Wt):
     """torch layout Wt (O, I) (torch_funcs/dense_funcs.py:4-25); batch dims restored."""
     o, i = Wt.shape
-    return ops.dense_op(ops._flat2d(x), Wt, L.KMAJOR, i, o).reshape(*x.shape[:-1], o)
+    return ops.dense(ops._flat2d(x), Wt, L.KMAJOR, i, o).reshape(*x.shape[:-1], o)
 
 
 def get_triton_dense_fp16_config():

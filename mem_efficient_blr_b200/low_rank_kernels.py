@@ -20,7 +20,7 @@ def _dims(x, a, b):
 def triton_low_rank_fp16(x, a, b, config=None):
     """Replaces triton_low_rank_fp16 (low_rank_kernels.py:410-417)."""
     i, r, o = _dims(x, a, b)
-    return ops.low_rank_op(ops._flat2d(x), a, b, L.MMAJOR, L.MMAJOR, i, r, o)
+    return ops.low_rank(ops._flat2d(x), a, b, L.MMAJOR, L.MMAJOR, i, r, o)
 
 
 def triton_low_rank_fp32(x, a, b):
@@ -33,7 +33,7 @@ def low_rank_torch_layout(x, Vt, Ut):
     """torch layouts Vt (R, I), Ut (O, R) (torch_funcs/low_rank_funcs.py:4-28); batch dims restored."""
     r, i = Vt.shape
     o, _ = Ut.shape
-    return ops.low_rank_op(ops._flat2d(x), Vt, Ut, L.KMAJOR, L.KMAJOR, i, r, o).reshape(*x.shape[:-1], o)
+    return ops.low_rank(ops._flat2d(x), Vt, Ut, L.KMAJOR, L.KMAJOR, i, r, o).reshape(*x.shape[:-1], o)
 
 
 def get_triton_low_rank_fp16_config():

@@ -27,7 +27,7 @@ def _dims(x, w1, w2, w2_kmajor):
 
 def _run16(x, w1, w2, w2_layout, order):
     b, p, rank, s = _dims(x, w1, w2, w2_layout == L.KMAJOR)
-    out = ops.monarch_op(ops._flat2d(x), w1, w2, L.MMAJOR, L.COLS_GROUPED, w2_layout, b, p, rank, s, order)
+    out = ops.monarch(ops._flat2d(x), w1, w2, L.MMAJOR, L.COLS_GROUPED, w2_layout, b, p, rank, s, order)
     return out.reshape(*x.shape[:-1], b * s)
 
 
@@ -77,7 +77,7 @@ def monarch_torch_layout(x, w1_t, w2_t):
     b, rank, p = w1_t.shape
     l, s, r = w2_t.shape
     assert b == l and r == rank and b * p == x.shape[-1] and rank % b == 0
-    out = ops.monarch_op(ops._flat2d(x), w1_t, w2_t, L.KMAJOR, L.COLS_TORCH, L.KMAJOR, b, p, rank, s, L.OUT_INTERLEAVED)
+    out = ops.monarch(ops._flat2d(x), w1_t, w2_t, L.KMAJOR, L.COLS_TORCH, L.KMAJOR, b, p, rank, s, L.OUT_INTERLEAVED)
     return out.reshape(*x.shape[:-1], b * s)
 
 

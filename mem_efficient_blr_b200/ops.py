@@ -1,9 +1,11 @@
 """Torch-facing operators: tensors in, tensors out, arithmetic in libblr_b200.so.
 
-Every operator is registered with ``torch.library.custom_op`` (with a fake kernel), so the reference's
-callers that wrap a model in ``torch.compile(fullgraph=True, mode='reduce-overhead')``
-(models/llama7b.py:65) trace through it; launches go to the current stream, outputs come from torch's
-allocator, and nothing synchronises the host.
+Every operator exists twice.  ``<name>_op`` is registered with ``torch.library.custom_op`` (with a fake
+kernel), so the reference's callers that wrap a model in ``torch.compile(fullgraph=True,
+mode='reduce-overhead')`` (models/llama7b.py:65) trace through it.  ``<name>`` is what the kernel modules
+call: under a compiler trace it is the registered operator, in eager mode it calls the same implementation
+directly, which saves the dispatcher's ~20 us per call - more than the kernel itself takes on one token.
+Launches go to the current stream, outputs come from torch's allocator, and nothing synchronises the host.
 """
 from __future__ import annotations
 
@@ -36,18 +38,25 @@ def _need_cuda(*ts: torch.Tensor) -> None:
         assert t.is_contiguous() or t.dim() == 2, "factor tensors must be contiguous"
 
 
+def _eager() -> bool:
+    return not torch.compiler.is_compiling()
+
+
+_ws_bytes_cache: dict = {}
+
+
 def _ws(x: torch.Tensor, n: int, groups: int, width: int):
     st = L.stream_ptr(x.device)
-    nbytes = L.load().blr_workspace_bytes(n, groups, width)
+    key = (n, groups, width)
+    nbytes = _ws_bytes_cache.get(key)
+    if nbytes is None:
+        nbytes = _ws_bytes_cache[key] = L.load().blr_workspace_bytes(n, groups, width)
     ws = L.workspace(x.device, st, nbytes)
     return ws, st
 
 
 # ----------------------------------------------------------------------------- BLAST
-@torch.library.custom_op("blr_b200::blast", mutates_args=())
-def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor, u_layout: int, v_layout: int,
-             s_i: int, s_j: int, s_r: int, b: int, P: int, Q: int, R: int, flags: int, b_out: int = -1) -> torch.Tensor:
-    """b_out < b: U and S hold only a slice of the output blocks (sharding by output block)."""
+def _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
     _need_cuda(x, U, V, S)
     x = _rows(x)
     assert U.dtype == x.dtype and V.dtype == x.dtype and S.dtype == x.dtype, "x, U, V, S must share one 16-bit dtype"
@@ -61,15 +70,25 @@ def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor,
     return out
 
 
+@torch.library.custom_op("blr_b200::blast", mutates_args=())
+def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor, u_layout: int, v_layout: int,
+             s_i: int, s_j: int, s_r: int, b: int, P: int, Q: int, R: int, flags: int, b_out: int = -1) -> torch.Tensor:
+    """b_out < b: U and S hold only a slice of the output blocks (sharding by output block)."""
+    return _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
+
+
+def blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
+    if _eager():
+        return _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
+    return blast_op(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
+
+
 @blast_op.register_fake
 def _(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
     return x.new_empty((x.shape[0], (b if b_out < 0 else b_out) * Q))
 
 
-@torch.library.custom_op("blr_b200::blast_wq", mutates_args=())
-def blast_wq_op(x: torch.Tensor, Uq: torch.Tensor, u_scale: torch.Tensor, Vq: torch.Tensor, v_scale: torch.Tensor,
-                S: torch.Tensor, s_i: int, s_j: int, s_r: int, bits: int, group: int, b: int, P: int, Q: int,
-                R: int) -> torch.Tensor:
+def _blast_wq_impl(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
     _need_cuda(x, Uq, u_scale, Vq, v_scale, S)
     x = _rows(x)
     assert u_scale.dtype == torch.float16 and v_scale.dtype == torch.float16, "scales are fp16"
@@ -83,15 +102,26 @@ def blast_wq_op(x: torch.Tensor, Uq: torch.Tensor, u_scale: torch.Tensor, Vq: to
     return out
 
 
+@torch.library.custom_op("blr_b200::blast_wq", mutates_args=())
+def blast_wq_op(x: torch.Tensor, Uq: torch.Tensor, u_scale: torch.Tensor, Vq: torch.Tensor, v_scale: torch.Tensor,
+                S: torch.Tensor, s_i: int, s_j: int, s_r: int, bits: int, group: int, b: int, P: int, Q: int,
+                R: int) -> torch.Tensor:
+    return _blast_wq_impl(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R)
+
+
+def blast_wq(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
+    if _eager():
+        return _blast_wq_impl(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R)
+    return blast_wq_op(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R)
+
+
 @blast_wq_op.register_fake
 def _(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
     return x.new_empty((x.shape[0], b * Q))
 
 
 # ----------------------------------------------------------------------------- Monarch
-@torch.library.custom_op("blr_b200::monarch", mutates_args=())
-def monarch_op(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_layout: int, w1_cols: int, w2_layout: int,
-               b: int, P: int, rank: int, Qs: int, out_order: int) -> torch.Tensor:
+def _monarch_impl(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
     _need_cuda(x, w1, w2)
     x = _rows(x)
     assert w1.dtype == x.dtype and w2.dtype == x.dtype
@@ -104,15 +134,25 @@ def monarch_op(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_layout: i
     return out
 
 
+@torch.library.custom_op("blr_b200::monarch", mutates_args=())
+def monarch_op(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_layout: int, w1_cols: int, w2_layout: int,
+               b: int, P: int, rank: int, Qs: int, out_order: int) -> torch.Tensor:
+    return _monarch_impl(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order)
+
+
+def monarch(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
+    if _eager():
+        return _monarch_impl(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order)
+    return monarch_op(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order)
+
+
 @monarch_op.register_fake
 def _(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
     return x.new_empty((x.shape[0], b * Qs))
 
 
 # ----------------------------------------------------------------------------- low rank / dense
-@torch.library.custom_op("blr_b200::low_rank", mutates_args=())
-def low_rank_op(x: torch.Tensor, V: torch.Tensor, U: torch.Tensor, v_layout: int, u_layout: int, I: int, R: int,
-                O: int) -> torch.Tensor:
+def _low_rank_impl(x, V, U, v_layout, u_layout, I, R, O):
     _need_cuda(x, V, U)
     x = _rows(x)
     assert V.dtype == x.dtype and U.dtype == x.dtype
@@ -125,13 +165,24 @@ def low_rank_op(x: torch.Tensor, V: torch.Tensor, U: torch.Tensor, v_layout: int
     return out
 
 
+@torch.library.custom_op("blr_b200::low_rank", mutates_args=())
+def low_rank_op(x: torch.Tensor, V: torch.Tensor, U: torch.Tensor, v_layout: int, u_layout: int, I: int, R: int,
+                O: int) -> torch.Tensor:
+    return _low_rank_impl(x, V, U, v_layout, u_layout, I, R, O)
+
+
+def low_rank(x, V, U, v_layout, u_layout, I, R, O):
+    if _eager():
+        return _low_rank_impl(x, V, U, v_layout, u_layout, I, R, O)
+    return low_rank_op(x, V, U, v_layout, u_layout, I, R, O)
+
+
 @low_rank_op.register_fake
 def _(x, V, U, v_layout, u_layout, I, R, O):
     return x.new_empty((x.shape[0], O))
 
 
-@torch.library.custom_op("blr_b200::dense", mutates_args=())
-def dense_op(x: torch.Tensor, W: torch.Tensor, w_layout: int, I: int, O: int) -> torch.Tensor:
+def _dense_impl(x, W, w_layout, I, O):
     _need_cuda(x, W)
     x = _rows(x)
     assert W.dtype == x.dtype
@@ -140,6 +191,17 @@ def dense_op(x: torch.Tensor, W: torch.Tensor, w_layout: int, I: int, O: int) ->
     L.check(L.load().blr_dense(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), W.data_ptr(), w_layout, I, O,
                                out.data_ptr(), out.stride(0), L.stream_ptr(x.device)))
     return out
+
+
+@torch.library.custom_op("blr_b200::dense", mutates_args=())
+def dense_op(x: torch.Tensor, W: torch.Tensor, w_layout: int, I: int, O: int) -> torch.Tensor:
+    return _dense_impl(x, W, w_layout, I, O)
+
+
+def dense(x, W, w_layout, I, O):
+    if _eager():
+        return _dense_impl(x, W, w_layout, I, O)
+    return dense_op(x, W, w_layout, I, O)
 
 
 @dense_op.register_fake
