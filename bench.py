@@ -34,7 +34,10 @@ I_F, O_F, B_BLK, RANK = 4096, 11008, 16, 1024
 P_BLK, Q_BLK = I_F // B_BLK, O_F // B_BLK
 POINTS = [(8, 1), (8, 4), (8, 16), (4, 1), (4, 4), (4, 16)]  # (bits, tokens)
 L2_BYTES = 126 * 2 ** 20
-NCU_TRAFFIC_INT8_N16 = 16.249e6  # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch from ncu captures (profiles/): the cluster kernel on
+# int8 factors and 1 token, the grid-wide streaming kernel on int8 factors and 16 tokens
+NCU_TRAFFIC = {"blr_blast_cluster_kernel": (16.474e6, "int8/N=1"), "blr_stream_kernel": (16.249e6, "int8/N=16")}
+CLUSTER_MAX_TOKENS = 8  # calls with up to 8 tokens run blr_blast_cluster_kernel, larger ones blr_stream_kernel
 
 
 def algorithmic_bytes(bits: int, n: int) -> float:
@@ -184,9 +187,16 @@ def run_ours(args):
     xs_host = {n: x16[0, :n].contiguous().pin_memory() for n in (1, 4, 16)}
     outs_host = {n: torch.empty(n, O_F, dtype=torch.float16).pin_memory() for n in (1, 4, 16)}
 
-    def launch_all():
+    def kernel_of(n):
+        return "blr_blast_cluster_kernel" if n <= CLUSTER_MAX_TOKENS else "blr_stream_kernel"
+
+    KERNELS = ["blr_blast_cluster_kernel", "blr_stream_kernel"]
+
+    def launch_points(kernel=None):
         count = 0
         for bits, n in POINTS:
+            if kernel is not None and kernel_of(n) != kernel:
+                continue
             for q in reps[bits]:
                 bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
                 count += 1
@@ -202,18 +212,23 @@ def run_ours(args):
         print(json.dumps({"ncu_case": args.ncu_case, "launches": 6}))
         return
 
-    launches_per_step = launch_all()
+    launches = {k: launch_points(k) for k in KERNELS}
+    launches_per_step = sum(launches.values())
     torch.cuda.synchronize()
-    bytes_per_step = sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS)
+    kbytes = {k: sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS if kernel_of(n) == k) for k in KERNELS}
+    bytes_per_step = sum(kbytes.values())
 
-    # ---- capture one step in a CUDA graph (the per-launch host work would otherwise bound the rate)
+    # ---- capture one step in CUDA graphs (the per-launch host work would otherwise bound the rate): one graph
+    # per kernel, replayed back to back, with an event between them so that each kernel's time is known
     side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
+    graphs = {}
     with torch.cuda.stream(side):
-        launch_all()
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph, stream=side):
-            launch_all()
+        for k in KERNELS:
+            launch_points(k)
+            torch.cuda.synchronize()
+            graphs[k] = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graphs[k], stream=side):
+                launch_points(k)
     torch.cuda.synchronize()
 
     def barrier():
@@ -222,22 +237,27 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        graph.replay()
+        for k in KERNELS:
+            graphs[k].replay()
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(KERNELS) + 1)] for _ in range(args.steps)]
     with ClockSampler(local) as clk:
         barrier()
-        e0.record()
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record()
+        for st in range(args.steps):
+            ev[st][0].record()
+            for i, k in enumerate(KERNELS):
+                graphs[k].replay()
+                ev[st][i + 1].record()
         barrier()
-    step_ms = e0.elapsed_time(e1) / args.steps
+    step_ms = ev[0][0].elapsed_time(ev[-1][-1]) / args.steps
+    kernel_ms = {k: sum(ev[st][i].elapsed_time(ev[st][i + 1]) for st in range(args.steps)) / args.steps
+                 for i, k in enumerate(KERNELS)}
     _lib.workspace_status(dev)
     if dist is not None:
-        t = torch.tensor([step_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([step_ms] + [kernel_ms[k] for k in KERNELS], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_ms = float(t.item())
+        step_ms = float(t[0].item())
+        kernel_ms = {k: float(t[i + 1].item()) for i, k in enumerate(KERNELS)}
     value = world * bytes_per_step / (step_ms * 1e-3) / 1e9
 
     # ---- per-point detail (separate timed loops, same graph technique)
@@ -326,6 +346,7 @@ def run_ours(args):
     for _ in range(2):
         e2e_step()
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
@@ -341,7 +362,16 @@ def run_ours(args):
 
     if rank == 0:
         peak, peak_kind = peak_hbm_gbs()
-        achieved = bytes_per_step / (step_ms * 1e-3) / 1e9  # per GPU: algorithmic bytes / launch time
+        # roofline of the kernel with the largest share of the timed region (per GPU): algorithmic bytes of its
+        # launches / their device time; the other kernel is listed beside it
+        per_kernel = {}
+        for k in KERNELS:
+            ach = kbytes[k] / (kernel_ms[k] * 1e-3) / 1e9
+            per_kernel[k] = {"launches_per_step": launches[k], "share": kernel_ms[k] / sum(kernel_ms.values()),
+                             "us_per_launch": kernel_ms[k] * 1e3 / launches[k],
+                             "algorithmic_bytes_per_launch": kbytes[k] / launches[k], "achieved": ach, "frac": ach / peak}
+        top = max(KERNELS, key=lambda k: kernel_ms[k])
+        achieved = per_kernel[top]["achieved"]
         cpu = None
         if world == 1:
             threads = os.cpu_count() or 1
@@ -359,10 +389,11 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps,
             "us_per_layer_mean": step_ms * 1e3 / launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_INT8_N16, "kernel": "blr_stream_kernel",
-                         "traffic_note": "dram read+write bytes of one int8/N=16 launch from an ncu capture "
-                                         "(profiles/blr_stream_kernel_blast_wq_decode.md); algorithmic bytes of that point: "
-                                         f"{algorithmic_bytes(8, 16):.0f}"},
+                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC[top][0], "kernel": top,
+                         "traffic_note": f"dram read+write bytes of one {NCU_TRAFFIC[top][1]} launch from an ncu capture "
+                                         "(profiles/); algorithmic bytes of that point: "
+                                         f"{algorithmic_bytes(8, 1 if top == 'blr_blast_cluster_kernel' else 16):.0f}",
+                         "kernels": per_kernel},
             "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "cpu_baseline": cpu,
