@@ -135,8 +135,10 @@ int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
 /* BLAST with int8 / packed-int4 factors and fp16 scales.  No reference counterpart (the reference's
  * sym-quant kernels round activations, not weights); the format is: Uq int8 (b,Q,R) or uint8 (b,Q,R/2),
  * Vq int8 (b,R,P) or uint8 (b,R,P/2), contraction index contiguous, two int4 per byte with the even
- * index in the low nibble; u_scale fp16 (b,Q), v_scale fp16 (b,R); weight = q * scale.
- * `group` must be 0 (one scale per output channel). */
+ * index in the low nibble; weight = q * scale.  `group` = 0: one scale per output channel, u_scale fp16 (b,Q),
+ * v_scale fp16 (b,R).  `group` = 128: one scale per 128 consecutive contraction indices, u_scale fp16
+ * (b,Q,R/128), v_scale fp16 (b,R,P/128); P and R must then be multiples of 128.  Other widths are rejected
+ * with BLR_ERR_UNSUPPORTED.  Up to 16 tokens per call. */
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                  const void* Uq, const void* u_scale, const void* Vq, const void* v_scale,
                  const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
@@ -189,7 +191,8 @@ int blr_dense_f32(const float* x, int64_t ldx, int64_t n_tokens,
 
 /* Symmetric weight quantiser (device): w (rows, K) 16-bit, contraction index contiguous ->
  * q int8 (rows, K) or packed uint8 (rows, K/2) and scale fp16 (rows) = max|w| / (127 | 7).
- * No reference counterpart. */
+ * Per-group scales come from the same call on the view (rows * K / group, group): a group is quantised like a
+ * row of its own and the layouts coincide.  No reference counterpart. */
 int blr_quantize_sym(const void* w, int dtype, int64_t rows, int64_t K, int bits,
                      void* q, void* scale, void* stream);
 

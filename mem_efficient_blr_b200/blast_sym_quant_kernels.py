@@ -35,23 +35,29 @@ def get_triton_blast_bmm_usxv_int8_fp16_config():
     return None
 
 
-def quantize_blast_factors(U: torch.Tensor, Vt: torch.Tensor, bits: int):
-    """torch-layout factors U (b,Q,R), Vt (b,R,P) -> (Uq, u_scale (b,Q), Vq, v_scale (b,R)).
-    One fp16 scale per output channel, scale = max|w| / (127 | 7); int4 packed two per byte along the
-    contraction axis, even index in the low nibble."""
-    Uq, us = ops.quantize_sym(U.contiguous(), bits)
-    Vq, vs = ops.quantize_sym(Vt.contiguous(), bits)
+def quantize_blast_factors(U: torch.Tensor, Vt: torch.Tensor, bits: int, group: int = 0):
+    """torch-layout factors U (b,Q,R), Vt (b,R,P) -> (Uq, u_scale, Vq, v_scale).
+    One fp16 scale per output channel (group = 0: u_scale (b,Q), v_scale (b,R)) or per `group` contraction
+    indices (u_scale (b,Q,R/group), v_scale (b,R,P/group); the kernels take group = 128);
+    scale = max|w| / (127 | 7); int4 packed two per byte along the contraction axis, even index in the low nibble."""
+    Uq, us = ops.quantize_sym(U.contiguous(), bits, group)
+    Vq, vs = ops.quantize_sym(Vt.contiguous(), bits, group)
     return Uq, us, Vq, vs
 
 
 def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     """Weight-quantised BLAST. Uq (b,Q,R) int8 or (b,Q,R/2) uint8; Vq (b,R,P) int8 or (b,R,P/2) uint8;
-    scales fp16 (b,Q) / (b,R); S (b_out, b_in, R) in x's dtype."""
+    scales fp16 (b,Q) / (b,R), or (b,Q,R/group) / (b,R,P/group) with per-group scales;
+    S (b_out, b_in, R) in x's dtype."""
     assert bits in (8, 4)
-    b, q = u_scale.shape
-    b2, r = v_scale.shape
+    b, q = u_scale.shape[:2]
+    b2, r = v_scale.shape[:2]
     p = Vq.shape[-1] * (1 if bits == 8 else 2)
     assert b == b2 and b != 1 and tuple(S.shape) == (b, b, r)
     assert Uq.shape[-1] * (1 if bits == 8 else 2) == r and x.shape[-1] == b * p
+    if group == 0:
+        assert u_scale.dim() == 2 and v_scale.dim() == 2, "one scale per output channel expected (group = 0)"
+    else:
+        assert tuple(u_scale.shape) == (b, q, r // group) and tuple(v_scale.shape) == (b, r, p // group)
     out = ops.blast_wq(ops._flat2d(x), Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
     return out.reshape(*x.shape[:-1], b * q)

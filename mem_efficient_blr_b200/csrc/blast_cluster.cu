@@ -13,7 +13,7 @@
 
 namespace blr {
 
-template <bool BF16, int NT>
+template <bool BF16, int NT, bool GS>
 __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(const __grid_constant__ ClusterParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -186,12 +186,26 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
         const bool active = row0 < rows;
         // per-row scales of quantised weights: fetched now, used after the batch's last stage
         float sc2[2] = {1.f, 1.f};
-        if (phs == 0 && ph.scale && active) {
+        if (!GS && phs == 0 && ph.scale && active) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int m = r0 + row0 + g + 8 * h;
             if (m < row_hi) sc2[h] = __half2float(__ldg(ph.scale + (long long)blk * ph.M + m));
           }
+        }
+        // grouped scales: rows of the scale table for this thread's two weight rows, first group of the K range
+        const int ngroups = ph.K / kScaleGroup, gbase = phs == 0 ? 0 : r_begin / kScaleGroup;
+        const __half* srow = nullptr;
+        const __half* srow8 = nullptr;
+        float tot[NT][4];
+        if constexpr (GS) {
+          const int m = r0 + row0 + g;
+          if (active && m < row_hi) srow = ph.scale + ((long long)blk * ph.M + m) * ngroups;
+          if (active && m + 8 < row_hi) srow8 = ph.scale + ((long long)blk * ph.M + m + 8) * ngroups;
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tot[n][e] = 0.f;
         }
         float acc[4][NT][4];
 #pragma unroll
@@ -208,6 +222,8 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
             uint32_t sW = smem_base + s * stage_bytes;
             uint32_t sA = phs == 0 ? sW + p.w_bytes : smem_u32(zbuf) + c * ksub * a_sub;
             for (int sub = 0; sub < ksub; ++sub, sW += kSubBytes, sA += a_sub) {
+              GroupScales gs;
+              if constexpr (GS) gs = load_scale_groups(srow, srow8, gbase + (c * ksub + sub) * (wbits == 8 ? 1 : 2), ngroups, wbits);
               if (wbits == 16) {
                 if (kmajor) consume_k16<BF16, NT>(sW, sA, row0, acc, lane);
                 else consume_m16<BF16, NT>(sW + (warp >> 1) * kTileBytes, sA, warp & 1, acc, lane);
@@ -216,6 +232,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
               } else {
                 consume_k4<BF16, NT>(sW, sA, row0, acc, lane);
               }
+              if constexpr (GS) fold_scale_groups<NT>(acc, tot, gs, wbits);
             }
           }
           __syncwarp();
@@ -235,7 +252,8 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
                   for (int e = 0; e < 2; ++e) {
-                    float v = (acc[0][n][2 * h + e] + acc[1][n][2 * h + e] + acc[2][n][2 * h + e] + acc[3][n][2 * h + e]) * sc;
+                    float v = GS ? tot[n][2 * h + e]
+                                 : (acc[0][n][2 * h + e] + acc[1][n][2 * h + e] + acc[2][n][2 * h + e] + acc[3][n][2 * h + e]) * sc;
                     if (p.round_y) v = round_clamp_i8(v);
                     store16<BF16>(ybuf, (long long)(n * 8 + tq * 2 + e) * rs + (m - r_begin), v);
                   }
@@ -245,9 +263,13 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
                   const int tok = n * 8 + tq * 2;
-                  if (tok < p.N)
-                    red_add_v2_f32(dst + tok, acc[0][n][2 * h] + acc[1][n][2 * h] + acc[2][n][2 * h] + acc[3][n][2 * h],
-                                   acc[0][n][2 * h + 1] + acc[1][n][2 * h + 1] + acc[2][n][2 * h + 1] + acc[3][n][2 * h + 1]);
+                  if (tok < p.N) {
+                    if constexpr (GS)
+                      red_add_v2_f32(dst + tok, tot[n][2 * h], tot[n][2 * h + 1]);
+                    else
+                      red_add_v2_f32(dst + tok, acc[0][n][2 * h] + acc[1][n][2 * h] + acc[2][n][2 * h] + acc[3][n][2 * h],
+                                     acc[0][n][2 * h + 1] + acc[1][n][2 * h + 1] + acc[2][n][2 * h + 1] + acc[3][n][2 * h + 1]);
+                  }
                 }
               }
             }
@@ -325,7 +347,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
       __threadfence();
       // one output row per thread and step, three steps in flight: the fp32 partial sums of a row are NP
       // consecutive floats, so the loads are whole 32-byte sectors and do not wait on one another
-      const __half* usc = ph1.scale;
+      const __half* usc = GS ? nullptr : ph1.scale;  // grouped scales were applied before the reduction
       constexpr int kRowsInFlight = 3, kV4 = NP / 4;
       for (int q0 = q_lo + ctid; q0 < q_hi; q0 += kRowsInFlight * kConsumerWarps * 32) {
         float4 v[kRowsInFlight][kV4];
@@ -378,11 +400,11 @@ size_t cluster_smem_bytes(const ClusterParams& p, int np) {
   return (size_t)p.nstages * p.stage_bytes + (size_t)np * p.rs * 2 + 16 * p.rs * 2 + (p.rs / 64) * np * 128 + 40 * 8 + 1024;
 }
 
-template <bool BF16, int NT>
+template <bool BF16, int NT, bool GS>
 static int cluster_capacity_impl(int b, int smem_bytes) {
   DeviceInfo di;
   if (device_info(&di) != BLR_OK) return 0;
-  auto kern = blr_blast_cluster_kernel<BF16, NT>;
+  auto kern = blr_blast_cluster_kernel<BF16, NT, GS>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin) != cudaSuccess) return 0;
   if (b > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
     cudaGetLastError();
@@ -409,23 +431,26 @@ static int cluster_capacity_impl(int b, int smem_bytes) {
 
 // Resident clusters of b CTAs when every CTA takes smem_bytes of dynamic shared memory; the answer depends on
 // whether one or two CTAs fit an SM, so it is cached for those two classes of size.
-int cluster_capacity(int b, int is_bf16, int n_tokens, int smem_bytes) {
-  static int cache[64][17][2][2];
-  static bool have[64][17][2][2] = {};
+int cluster_capacity(int b, int is_bf16, int grouped, int n_tokens, int smem_bytes) {
+  static int cache[64][17][2][2][2];
+  static bool have[64][17][2][2][2] = {};
   DeviceInfo di;
   int dev = 0;
   if (device_info(&di) != BLR_OK || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || b < 1 || b > 16) return 0;
   if (n_tokens > kClusterMaxTokens) return 0;
-  const int bf = is_bf16 ? 1 : 0, two = smem_bytes <= kClusterHalfSmem ? 1 : 0;
-  if (!have[dev][b][bf][two]) {
+  const int bf = is_bf16 ? 1 : 0, gsi = grouped ? 1 : 0, two = smem_bytes <= kClusterHalfSmem ? 1 : 0;
+  if (!have[dev][b][bf][gsi][two]) {
     const int sm = two ? kClusterHalfSmem : di.max_smem_optin - 1024;
-    cache[dev][b][bf][two] = bf ? cluster_capacity_impl<true, 1>(b, sm) : cluster_capacity_impl<false, 1>(b, sm);
-    have[dev][b][bf][two] = true;
+    int n;
+    if (gsi) n = bf ? cluster_capacity_impl<true, 1, true>(b, sm) : cluster_capacity_impl<false, 1, true>(b, sm);
+    else n = bf ? cluster_capacity_impl<true, 1, false>(b, sm) : cluster_capacity_impl<false, 1, false>(b, sm);
+    cache[dev][b][bf][gsi][two] = n;
+    have[dev][b][bf][gsi][two] = true;
   }
-  return cache[dev][b][bf][two];
+  return cache[dev][b][bf][gsi][two];
 }
 
-template <bool BF16, int NT>
+template <bool BF16, int NT, bool GS>
 static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
@@ -433,7 +458,7 @@ static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   const size_t smem = cluster_smem_bytes(p, NT * 8);
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
-  auto kern = blr_blast_cluster_kernel<BF16, NT>;
+  auto kern = blr_blast_cluster_kernel<BF16, NT, GS>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.b, p.nslices, p.qsplit);
   cfg.blockDim = dim3(kClusterThreads);
@@ -459,7 +484,8 @@ int launch_blast_cluster(const ClusterParams& p_in, int is_bf16, cudaStream_t st
   ClusterParams p = p_in;
   p.timeline = g_stream_timeline;
   BLR_REQUIRE(p.N >= 1 && p.N <= kClusterMaxTokens, BLR_ERR_UNSUPPORTED, "the cluster kernel takes 1..%d tokens", kClusterMaxTokens);
-  return is_bf16 ? launch_cluster_impl<true, 1>(p, stream) : launch_cluster_impl<false, 1>(p, stream);
+  if (p.ph[0].group != 0) return is_bf16 ? launch_cluster_impl<true, 1, true>(p, stream) : launch_cluster_impl<false, 1, true>(p, stream);
+  return is_bf16 ? launch_cluster_impl<true, 1, false>(p, stream) : launch_cluster_impl<false, 1, false>(p, stream);
 }
 
 }  // namespace blr

@@ -39,7 +39,7 @@ struct alignas(64) ClusterParams {
 };
 
 // Largest number of clusters of `b` CTAs that can be resident (0: this cluster shape cannot be launched).
-int cluster_capacity(int b, int is_bf16, int n_tokens, int smem_bytes);
+int cluster_capacity(int b, int is_bf16, int grouped, int n_tokens, int smem_bytes);
 size_t cluster_smem_bytes(const ClusterParams& p, int np);
 int launch_blast_cluster(const ClusterParams& p, int is_bf16, cudaStream_t stream);
 

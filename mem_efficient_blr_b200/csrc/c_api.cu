@@ -135,7 +135,7 @@ static int check_layout(int layout) {
 static int g_decode_path = 0;  // 0: automatic, 1: grid-wide streaming kernel only (blr_debug_decode_path)
 
 static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
-                         const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, const void* S,
+                         const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                          int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
                          int64_t ldo, const Workspace& w, cudaStream_t stream) {
   static const bool disabled = getenv("BLR_NO_CLUSTER") != nullptr;
@@ -151,6 +151,7 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, b, Q, R))) return rc;
   p.ph[0].scale = static_cast<const __half*>(v_scale);
   p.ph[1].scale = static_cast<const __half*>(u_scale);
+  p.ph[0].group = p.ph[1].group = group;
   DeviceInfo di;
   if ((rc = device_info(&di))) return rc;
   // Shape of the launch: ranks per slice (a multiple of what one second-phase chunk covers), row parts of U_i,
@@ -169,8 +170,8 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
     if (best_rs < kx) return 1;
     const int nsl = (R + best_rs - 1) / best_rs;
     const int max_parts = Q / kBatchRows < 1 ? 1 : (Q / kBatchRows > kClusterMaxParts ? kClusterMaxParts : Q / kBatchRows);
-    int parts1 = cluster_capacity(b, bf, (int)N, di.max_smem_optin - 1024) / nsl;
-    int parts2 = cluster_capacity(b, bf, (int)N, kClusterHalfSmem) / nsl;
+    int parts1 = cluster_capacity(b, bf, group, (int)N, di.max_smem_optin - 1024) / nsl;
+    int parts2 = cluster_capacity(b, bf, group, (int)N, kClusterHalfSmem) / nsl;
     if (parts1 > max_parts) parts1 = max_parts;
     if (parts2 > max_parts) parts2 = max_parts;
     if (parts1 < 1 && parts2 < 1) return 1;  // more slices than resident clusters: grid-wide kernel
@@ -196,13 +197,13 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   int nst = (budget - extras) / p.stage_bytes;
   p.nstages = nst > 16 ? 16 : nst;
   if (p.nstages < 2) return 1;
-  if (forced && p.nslices * p.qsplit > cluster_capacity(b, bf, (int)N, budget)) return 1;
+  if (forced && p.nslices * p.qsplit > cluster_capacity(b, bf, group, (int)N, budget)) return 1;
   rc = launch_blast_cluster(p, bf, stream);
   return rc;
 }
 
 static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
-                      const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, const void* S,
+                      const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
                       int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream) {
   int rc = check_common(x, ldx, N, dtype, out, ldo);
@@ -219,7 +220,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   const int act8 = (flags & BLR_FLAG_ACT_INT8) ? 1 : 0;
 
   if (N <= kStreamMaxTokens) {
-    rc = cluster_blast(x, ldx, N, dtype, U, u_layout, u_bits, u_scale, V, v_layout, v_bits, v_scale, S, s_i, s_j, s_r, b, bo,
+    rc = cluster_blast(x, ldx, N, dtype, U, u_layout, u_bits, u_scale, V, v_layout, v_bits, v_scale, group, S, s_i, s_j, s_r, b, bo,
                        P, Q, R, act8, out, ldo, w, stream);
     if (rc <= 0) return rc;  // 0: launched, < 0: error, 1: not applicable -> grid-wide streaming kernel
     StreamParams p = {};
@@ -232,6 +233,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
     if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, bo, Q, R))) return rc;
     if ((rc = phase_acts(p.ph[1], dtype, w.region_b, R, N, bo, R, (int64_t)N * R))) return rc;
     phase_out(p.ph[1], out, 0, Q, ldo, Q, 0, 1, u_scale, 0);
+    p.ph[0].group = p.ph[1].group = group;
     finish_params(p, N);
     return launch_stream(p, dtype == BLR_DTYPE_BF16, stream);
   }
@@ -314,14 +316,14 @@ int blr_workspace_status(const void* ws, void* stream) {
 int blr_blast(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
               int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R, int flags,
               void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
-  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b, P,
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b, P,
                     Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
                    int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
                    int flags, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
-  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b_out,
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b_out,
                     P, Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
@@ -340,7 +342,7 @@ int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype, co
   if (rc) return rc;
   // The array keeps whatever the previous call left; the barrier words must start at zero.
   BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes, static_cast<cudaStream_t>(stream)));
-  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, S, s_i, s_j, s_r, b, b, P,
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b, P,
                     Q, R, flags, out, ldo, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }
 
@@ -348,9 +350,13 @@ int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
                  const void* Vq, const void* v_scale, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int bits,
                  int group, int b, int P, int Q, int R, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
   BLR_REQUIRE(bits == 8 || bits == 4, BLR_ERR_ARG, "bits must be 8 or 4, got %d", bits);
-  BLR_REQUIRE(group == 0, BLR_ERR_UNSUPPORTED, "only one scale per output channel (group = 0) is implemented");
+  BLR_REQUIRE(group == 0 || group == kScaleGroup, BLR_ERR_UNSUPPORTED,
+              "scales per output channel (group = 0) or per %d contraction indices are implemented, got group = %d",
+              kScaleGroup, group);
+  BLR_REQUIRE(group == 0 || (P % kScaleGroup == 0 && R % kScaleGroup == 0), BLR_ERR_SHAPE,
+              "with per-group scales P and R must be multiples of %d", kScaleGroup);
   BLR_REQUIRE(u_scale && v_scale, BLR_ERR_ARG, "scale pointers must not be null");
-  return blast_impl(x, ldx, n_tokens, dtype, Uq, BLR_W_KMAJOR, bits, u_scale, Vq, BLR_W_KMAJOR, bits, v_scale, S, s_i,
+  return blast_impl(x, ldx, n_tokens, dtype, Uq, BLR_W_KMAJOR, bits, u_scale, Vq, BLR_W_KMAJOR, bits, v_scale, group, S, s_i,
                     s_j, s_r, b, b, P, Q, R, BLR_FLAG_NONE, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
 

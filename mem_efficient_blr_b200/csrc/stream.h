@@ -20,6 +20,8 @@ static constexpr int kConsumerWarps = 8;
 static constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;
 static constexpr int kStreamTailBytes = 2 * 16 * 8 + 64 + 1024;  // barriers, abort flag, alignment slack
 
+static constexpr int kScaleGroup = 128;  // the one supported width of a scale group
+
 struct alignas(64) PhaseDesc {
   // weights, K-major: dims (K, M, G), tmW[h-1] has box (128 B, 16*h, 1) so that one load brings a whole
   // batch of h row groups; M-major: dims (M, K, G), only tmW[0] with box (32, 64, 1)
@@ -40,7 +42,8 @@ struct alignas(64) PhaseDesc {
   int per;          // output offset = g*os_g + n*os_n + (m / per)*os_hi + (m % per)*os_lo
   long long os_g, os_n, os_hi, os_lo;
   void* out;
-  const __half* scale;  // per-row dequantisation scale [G*M] or nullptr
+  const __half* scale;  // dequantisation scales: [G*M] (one per row), [G*M][K/group] when group != 0, or nullptr
+  int group;            // 0, or kScaleGroup: contraction indices per scale
 };
 
 struct alignas(64) StreamParams {

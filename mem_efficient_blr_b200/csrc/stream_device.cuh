@@ -136,6 +136,43 @@ __device__ __forceinline__ void consume_k4(uint32_t sWt, uint32_t sA, int row0, 
   }
 }
 
+// Per-group scales (kScaleGroup contraction indices per scale).  One K-chunk is one group of int8 weights or two
+// groups of int4 weights, and the chains acc[0..3] of a chunk are its four 32-byte windows in order, so after a
+// chunk the chains are scaled into `tot` and cleared.  A thread holds rows g and g+8 of its warp's row group:
+// `srow` points at the scales of row g (nullptr: row past M), `srow8` at those of row g+8; `gidx` is the first
+// group of the chunk and `ngroups` the number of groups per row.
+struct GroupScales {
+  float s[2][2];  // [group of the chunk][row g / row g+8]
+};
+// Issued before the chunk is consumed, so that the loads are back when fold_scale_groups needs them.
+__device__ __forceinline__ GroupScales load_scale_groups(const __half* srow, const __half* srow8, int gidx, int ngroups,
+                                                         int wbits) {
+  GroupScales r = {{{0.f, 0.f}, {0.f, 0.f}}};
+  const int per_chunk = wbits == 8 ? 1 : 2;
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+    if (q < per_chunk && gidx + q < ngroups) {
+      if (srow) r.s[q][0] = __half2float(__ldg(srow + gidx + q));
+      if (srow8) r.s[q][1] = __half2float(__ldg(srow8 + gidx + q));
+    }
+  return r;
+}
+template <int NT>
+__device__ __forceinline__ void fold_scale_groups(float (&acc)[4][NT][4], float (&tot)[NT][4], const GroupScales& gs,
+                                                  int wbits) {
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const int q = wbits == 8 ? 0 : (w >> 1);
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        tot[n][e] = fmaf(gs.s[q][e >> 1], acc[w][n][e], tot[n][e]);
+        acc[w][n][e] = 0.f;
+      }
+  }
+}
+
 // ------------------------------------------------------------------ helpers
 template <bool BF16>
 __device__ __forceinline__ void store16(void* base, long long off, float v) {

@@ -146,7 +146,7 @@ __device__ __forceinline__ void couple(const StreamParams& p, int ctid, const Co
 }
 
 // ------------------------------------------------------------------ kernel
-template <bool BF16, int NT>
+template <bool BF16, int NT, bool GS>
 __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __grid_constant__ StreamParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // Carve: [stages][barriers]
@@ -290,6 +290,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[q][n][e] = 0.f;
         const bool active = row0 < b.nt * ph.unit_rows;
+        // grouped scales: rows of the scale table for this thread's two weight rows
+        const int ngroups = ph.K / kScaleGroup;
+        const __half* srow = nullptr;
+        const __half* srow8 = nullptr;
+        float tot[NT][4];
+        if constexpr (GS) {
+          const int m = b.mt0 * ph.unit_rows + row0 + g;
+          if (active && m < ph.M) srow = ph.scale + ((long long)b.g * ph.M + m) * ngroups;
+          if (active && m + 8 < ph.M) srow8 = ph.scale + ((long long)b.g * ph.M + m + 8) * ngroups;
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tot[n][e] = 0.f;
+        }
+        int kc = first_chunk(ph);  // the producers walk the stages of a batch from a rotated start
         for (int c = 0; c < nchunks && ok; ++c) {
           const uint32_t s = rp.s;
           if (!mbar_wait(full0 + 8 * s, rp.use_parity, abort_flag)) { ok = false; break; }
@@ -300,6 +315,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
           if (active && !(p.debug & 4)) {
             uint32_t sW = smem_base + s * stage_bytes, sA = sW + p.w_bytes;
             for (int sub = 0; sub < ksub; ++sub, sW += kSubBytes, sA += a_sub) {
+              GroupScales gs;
+              if constexpr (GS) gs = load_scale_groups(srow, srow8, (kc * ksub + sub) * (wbits == 8 ? 1 : 2), ngroups, wbits);
               if (wbits == 16) {
                 if (kmajor) consume_k16<BF16, NT>(sW, sA, row0, acc, lane);
                 else consume_m16<BF16, NT>(sW + (warp >> 1) * kTileBytes, sA, warp & 1, acc, lane);
@@ -308,11 +325,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
               } else {
                 consume_k4<BF16, NT>(sW, sA, row0, acc, lane);
               }
+              if constexpr (GS) fold_scale_groups<NT>(acc, tot, gs, wbits);
             }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
           rp.advance(NST);
+          if (++kc == nchunks) kc = 0;
         }
         // ---- epilogue straight from the accumulator fragment: rows g / g+8, tokens 2*tq / 2*tq+1 (+8 per n-tile)
         if (active) {
@@ -321,7 +340,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
           for (int h = 0; h < 2; ++h) {
             const int mg = m_lo + 8 * h;
             if (mg < ph.M) {
-              const float sc = ph.scale ? __half2float(ph.scale[(long long)b.g * ph.M + mg]) : 1.f;
+              const float sc = (!GS && ph.scale) ? __half2float(ph.scale[(long long)b.g * ph.M + mg]) : 1.f;
               const long long base = b.g * ph.os_g + (mg / ph.per) * ph.os_hi + (mg % ph.per) * ph.os_lo;
 #pragma unroll
               for (int n = 0; n < NT; ++n)
@@ -329,7 +348,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
                 for (int e = 0; e < 2; ++e) {
                   const int tok = n * 8 + tq * 2 + e;
                   if (tok < p.N) {
-                    float v = (acc[0][n][2 * h + e] + acc[1][n][2 * h + e] + acc[2][n][2 * h + e] + acc[3][n][2 * h + e]) * sc;
+                    float v = GS ? tot[n][2 * h + e]
+                                 : (acc[0][n][2 * h + e] + acc[1][n][2 * h + e] + acc[2][n][2 * h + e] + acc[3][n][2 * h + e]) * sc;
                     if (ph.round_out) v = round_clamp_i8(v);
                     const long long off = base + tok * ph.os_n;
                     if (ph.out_f32) reinterpret_cast<float*>(ph.out)[off] = v;
@@ -390,7 +410,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
 }
 
 // ------------------------------------------------------------------ host launcher
-template <bool BF16, int NT>
+template <bool BF16, int NT, bool GS>
 static int launch_impl(const StreamParams& p, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
@@ -399,7 +419,7 @@ static int launch_impl(const StreamParams& p, cudaStream_t stream) {
   const size_t smem = (size_t)p.nstages * p.stage_bytes + p.mix_bytes + kStreamTailBytes;
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
-  auto kern = blr_stream_kernel<BF16, NT>;
+  auto kern = blr_stream_kernel<BF16, NT, GS>;
   int dev;
   BLR_CUDA_OK(cudaGetDevice(&dev));
   static bool configured[64] = {};  // one flag per device for this template instance
@@ -442,8 +462,12 @@ int launch_stream(const StreamParams& p_in, int is_bf16, cudaStream_t stream) {
   { static const int dbg = getenv("BLR_STREAM_DEBUG") ? atoi(getenv("BLR_STREAM_DEBUG")) : 0; p.debug = dbg; }
   BLR_REQUIRE(p.N >= 1 && p.N <= kStreamMaxTokens, BLR_ERR_ARG, "stream kernel handles 1..%d tokens, got %d",
               kStreamMaxTokens, p.N);
-  if (p.N <= 8) return is_bf16 ? launch_impl<true, 1>(p, stream) : launch_impl<false, 1>(p, stream);
-  return is_bf16 ? launch_impl<true, 2>(p, stream) : launch_impl<false, 2>(p, stream);
+  if (p.ph[0].group != 0) {  // one scale per kScaleGroup contraction indices: its own instantiation
+    if (p.N <= 8) return is_bf16 ? launch_impl<true, 1, true>(p, stream) : launch_impl<false, 1, true>(p, stream);
+    return is_bf16 ? launch_impl<true, 2, true>(p, stream) : launch_impl<false, 2, true>(p, stream);
+  }
+  if (p.N <= 8) return is_bf16 ? launch_impl<true, 1, false>(p, stream) : launch_impl<false, 1, false>(p, stream);
+  return is_bf16 ? launch_impl<true, 2, false>(p, stream) : launch_impl<false, 2, false>(p, stream);
 }
 
 }  // namespace blr

@@ -265,16 +265,20 @@ def flat2d_f32(x: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- quantiser
-def quantize_sym(w: torch.Tensor, bits: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-output-channel symmetric quantisation on the device; w (..., K) contiguous 16-bit.
-    Returns (q int8 (..., K) | uint8 (..., K/2), scale fp16 (...))."""
+def quantize_sym(w: torch.Tensor, bits: int, group: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Symmetric quantisation on the device; w (..., K) contiguous 16-bit.  One fp16 scale per output channel
+    (group = 0) or per `group` consecutive contraction indices.
+    Returns (q int8 (..., K) | uint8 (..., K/2), scale fp16 (...) | (..., K/group))."""
     _need_cuda(w)
     assert w.is_contiguous() and bits in (8, 4)
     K = w.shape[-1]
-    rows = w.numel() // K
+    g = K if group == 0 else group
+    assert K % g == 0 and g % 2 == 0, f"group {group} must divide the contraction length {K}"
+    # a group is quantised exactly like a row of length g, and the layouts coincide
+    rows = w.numel() // g
     q = torch.empty((*w.shape[:-1], K if bits == 8 else K // 2), dtype=torch.int8 if bits == 8 else torch.uint8,
                     device=w.device)
-    scale = torch.empty(w.shape[:-1], dtype=torch.float16, device=w.device)
-    L.check(L.load().blr_quantize_sym(w.data_ptr(), L.dtype_code(w.dtype), rows, K, bits, q.data_ptr(),
+    scale = torch.empty(w.shape[:-1] if group == 0 else (*w.shape[:-1], K // g), dtype=torch.float16, device=w.device)
+    L.check(L.load().blr_quantize_sym(w.data_ptr(), L.dtype_code(w.dtype), rows, g, bits, q.data_ptr(),
                                       scale.data_ptr(), L.stream_ptr(w.device)))
     return q, scale

@@ -147,22 +147,24 @@ class DenseLinear(_Base):
 
 class QuantBlastLinear(_Base):
     """BLAST linear with int8 / packed-int4 factors (up to 16 tokens per call).  Built from torch-layout
-    16-bit factors U (b,Q,R), Vt (b,R,P), S (b,b,R); no counterpart in the reference."""
+    16-bit factors U (b,Q,R), Vt (b,R,P), S (b,b,R); one scale per output channel, or per 128 contraction indices
+    with group = 128; no counterpart in the reference."""
 
-    def __init__(self, U: torch.Tensor, Vt: torch.Tensor, S: torch.Tensor, bits: int = 8, bias: torch.Tensor | None = None):
+    def __init__(self, U: torch.Tensor, Vt: torch.Tensor, S: torch.Tensor, bits: int = 8, bias: torch.Tensor | None = None,
+                 group: int = 0):
         super().__init__()
         from . import blast_sym_quant_kernels as bq
-        self.bits = bits
+        self.bits, self.group = bits, group
         b, Q, R = U.shape
         self.in_features, self.out_features, self.b, self.rank = b * Vt.shape[2], b * Q, b, R
-        Uq, us, Vq, vs = bq.quantize_blast_factors(U, Vt, bits)
+        Uq, us, Vq, vs = bq.quantize_blast_factors(U, Vt, bits, group)
         for name, t in (("Uq", Uq), ("u_scale", us), ("Vq", Vq), ("v_scale", vs), ("S", S.contiguous())):
             self.register_buffer(name, t)
         self.bias = None if bias is None else nn.Parameter(bias)
         self._op = bq.blast_wq
 
     def forward(self, x):
-        return self._finish(x, self._op(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits))
+        return self._finish(x, self._op(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits, self.group))
 
 
 def replace_linear_with_custom(module: nn.Module, key: str, factory) -> int:

@@ -123,6 +123,43 @@ def test_blast_weight_quantised(K, shape, dtype, bits):
     assert orc.rel_fro(got.float().cpu(), ref) < TOL
 
 
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("shape", [(1, 4096, 11008, 16, 1024), (7, 4096, 11008, 16, 1024), (16, 4096, 11008, 16, 1024),
+                                   (3, 1024, 1536, 4, 384), (2, 2048, 1024, 8, 256)])
+def test_blast_weight_quantised_per_group_scales(K, shape, bits):
+    """One scale per 128 contraction indices: device quantiser bit-exact against the oracle's, output against the
+    oracle on the identically dequantised factors; on the cluster kernel (<= 8 tokens) and the grid-wide one."""
+    N, I, O, b, R = shape
+    G = 128
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=100 + bits + N)
+    # spread the magnitudes of the groups so that a per-channel scale would not do
+    U = (U.float() * (1 + 3 * torch.rand(b, O // b, R // G, 1).expand(-1, -1, -1, G).reshape(b, O // b, R))).half()
+    Uq, us = orc.quantize_sym(U, bits, G)
+    Vq, vs = orc.quantize_sym(Vt, bits, G)
+    assert us.shape == (b, O // b, R // G) and vs.shape == (b, R, I // b // G)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits, G)
+    dUq, dus, dVq, dvs = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), bits, G)
+    assert torch.equal(dus.cpu(), us) and torch.equal(dvs.cpu(), vs)
+    assert torch.equal(dUq.cpu(), Uq) and torch.equal(dVq.cpu(), Vq)
+    lib = K.lib.load()
+    try:
+        for path in (0, 1):
+            assert lib.blr_debug_decode_path(path) == 0
+            got = K.bq.blast_wq(x.to(DEV), dUq, dus, dVq, dvs, S.to(DEV), bits, G)
+            _sync_ok(K)
+            assert got.shape == ref.shape
+            assert orc.rel_fro(got.float().cpu(), ref) < TOL, f"path {path}"
+    finally:
+        assert lib.blr_debug_decode_path(0) == 0
+
+
+def test_blast_weight_quantised_rejects_other_group_widths(K):
+    x, U, Vt, S = orc.make_blast_inputs(1, 512, 768, 4, 256, torch.float16, seed=5)
+    q = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), 8, 64)
+    with pytest.raises(RuntimeError, match="group"):
+        K.bq.blast_wq(x.to(DEV), *q, S.to(DEV), 8, 64)
+
+
 def test_small_batches_on_the_grid_wide_kernel(K):
     """1..8 tokens normally take the cluster kernel; the grid-wide streaming kernel must give the same
     answers for them (it is what runs when the shape does not fit a cluster)."""
