@@ -16,6 +16,7 @@
  *   - Weight layouts: BLR_W_KMAJOR = [block][out_row][k] (contraction index contiguous, the
  *     reference's torch layouts); BLR_W_MMAJOR = [block][k][out_row] (output index contiguous, the
  *     layouts of the reference's Triton entry points).
+ *   - n_tokens = 0 is valid for the 16-bit and quantised entry points: they return 0 without touching a pointer.
  *   - Return value: 0 on success, a negative BLR_ERR_* code otherwise; blr_last_error() has the text.
  *     Token counts up to 16 run one weight-streaming kernel (BLAST on up to 8 tokens: a kernel of thread-block
  *     clusters, one cluster per slice of the rank index); larger counts run the tensor-core pipeline.

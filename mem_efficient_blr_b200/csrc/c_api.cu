@@ -118,9 +118,11 @@ static void finish_params(StreamParams& p, int64_t N) {
   p.nstages = nst > 16 ? 16 : nst;
 }
 
+// Returns 1 for an empty batch (nothing to do, not an error), 0 when the call may proceed, < 0 on error.
 static int check_common(const void* x, int64_t ldx, int64_t N, int dtype, const void* out, int64_t ldo) {
+  BLR_REQUIRE(N >= 0, BLR_ERR_ARG, "token count must not be negative, got %lld", (long long)N);
+  if (N == 0) return 1;
   BLR_REQUIRE(x != nullptr && out != nullptr, BLR_ERR_ARG, "x and out must not be null");
-  BLR_REQUIRE(N >= 1, BLR_ERR_ARG, "token count must be positive, got %lld", (long long)N);
   BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
   BLR_REQUIRE(ldx > 0 && ldo > 0, BLR_ERR_ARG, "leading dimensions must be positive");
   return BLR_OK;
@@ -207,7 +209,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
                       int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream) {
   int rc = check_common(x, ldx, N, dtype, out, ldo);
-  if (rc) return rc;
+  if (rc) return rc < 0 ? rc : BLR_OK;
   BLR_REQUIRE(U && V && S, BLR_ERR_ARG, "factor pointers must not be null");
   BLR_REQUIRE((reinterpret_cast<uintptr_t>(S) & 15) == 0, BLR_ERR_ALIGN, "S must be 16-byte aligned");
   BLR_REQUIRE(b >= 2, BLR_ERR_SHAPE, "BLAST needs at least 2 blocks per side, got %d (the reference asserts b != 1)", b);
@@ -365,7 +367,7 @@ int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const v
                 void* ws, size_t ws_bytes, void* stream) {
   const int64_t N = n_tokens;
   int rc = check_common(x, ldx, N, dtype, out, ldo);
-  if (rc) return rc;
+  if (rc) return rc < 0 ? rc : BLR_OK;
   BLR_REQUIRE(w1 && w2, BLR_ERR_ARG, "factor pointers must not be null");
   BLR_REQUIRE(b >= 1 && P > 0 && rank > 0 && Qs > 0, BLR_ERR_SHAPE, "b, P, rank, Qs must be positive");
   BLR_REQUIRE(rank % b == 0, BLR_ERR_SHAPE, "rank %d must be a multiple of the block count %d (wrappers.py:14)", rank, b);
@@ -401,7 +403,7 @@ int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
                  int u_layout, int I, int R, int O, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
   const int64_t N = n_tokens;
   int rc = check_common(x, ldx, N, dtype, out, ldo);
-  if (rc) return rc;
+  if (rc) return rc < 0 ? rc : BLR_OK;
   BLR_REQUIRE(V && U, BLR_ERR_ARG, "factor pointers must not be null");
   BLR_REQUIRE(I > 0 && R > 0 && O > 0, BLR_ERR_SHAPE, "I, R, O must be positive");
   BLR_REQUIRE(ldx >= I && ldo >= O, BLR_ERR_SHAPE, "leading dimensions shorter than a row");
@@ -428,7 +430,7 @@ int blr_dense(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const voi
               void* out, int64_t ldo, void* stream) {
   const int64_t N = n_tokens;
   int rc = check_common(x, ldx, N, dtype, out, ldo);
-  if (rc) return rc;
+  if (rc) return rc < 0 ? rc : BLR_OK;
   BLR_REQUIRE(W, BLR_ERR_ARG, "weight pointer must not be null");
   BLR_REQUIRE(I > 0 && O > 0, BLR_ERR_SHAPE, "I, O must be positive");
   BLR_REQUIRE(ldx >= I && ldo >= O, BLR_ERR_SHAPE, "leading dimensions shorter than a row");

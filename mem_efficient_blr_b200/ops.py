@@ -58,6 +58,8 @@ def _ws(x: torch.Tensor, n: int, groups: int, width: int):
 # ----------------------------------------------------------------------------- BLAST
 def _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
     _need_cuda(x, U, V, S)
+    if x.shape[0] == 0:  # an empty batch (e.g. a rank without tokens) is valid and needs no launch
+        return x.new_empty((0, (b if b_out < 0 else b_out) * Q))
     x = _rows(x)
     assert U.dtype == x.dtype and V.dtype == x.dtype and S.dtype == x.dtype, "x, U, V, S must share one 16-bit dtype"
     bo = b if b_out < 0 else b_out
@@ -90,6 +92,8 @@ def _(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1
 
 def _blast_wq_impl(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
     _need_cuda(x, Uq, u_scale, Vq, v_scale, S)
+    if x.shape[0] == 0:
+        return x.new_empty((0, b * Q))
     x = _rows(x)
     assert u_scale.dtype == torch.float16 and v_scale.dtype == torch.float16, "scales are fp16"
     assert S.dtype == x.dtype
@@ -123,6 +127,8 @@ def _(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
 # ----------------------------------------------------------------------------- Monarch
 def _monarch_impl(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
     _need_cuda(x, w1, w2)
+    if x.shape[0] == 0:
+        return x.new_empty((0, b * Qs))
     x = _rows(x)
     assert w1.dtype == x.dtype and w2.dtype == x.dtype
     n = x.shape[0]
@@ -154,6 +160,8 @@ def _(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
 # ----------------------------------------------------------------------------- low rank / dense
 def _low_rank_impl(x, V, U, v_layout, u_layout, I, R, O):
     _need_cuda(x, V, U)
+    if x.shape[0] == 0:
+        return x.new_empty((0, O))
     x = _rows(x)
     assert V.dtype == x.dtype and U.dtype == x.dtype
     n = x.shape[0]
@@ -184,6 +192,8 @@ def _(x, V, U, v_layout, u_layout, I, R, O):
 
 def _dense_impl(x, W, w_layout, I, O):
     _need_cuda(x, W)
+    if x.shape[0] == 0:
+        return x.new_empty((0, O))
     x = _rows(x)
     assert W.dtype == x.dtype
     n = x.shape[0]

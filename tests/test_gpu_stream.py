@@ -248,6 +248,21 @@ def test_dense(K, shape, dtype):
     assert got.shape == (N, O) and orc.rel_fro(got.float().cpu(), ref.reshape(N, O)) < TOL
 
 
+def test_empty_batches_return_empty_outputs(K):
+    """Zero tokens (a rank whose token slice is empty) is valid on every operator family and through the C ABI."""
+    _, U, Vt, S = orc.make_blast_inputs(1, 512, 768, 4, 128, torch.float16, seed=1)
+    x0 = torch.empty(0, 512, dtype=torch.float16, device=DEV)
+    assert K.bk.blast_torch_layout(x0, *_cuda(U, Vt, S)).shape == (0, 768)
+    q = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), 8)
+    assert K.bq.blast_wq(x0, *q, S.to(DEV), 8).shape == (0, 768)
+    Wt = torch.randn(768, 512, dtype=torch.float16, device=DEV)
+    assert K.dk.dense_torch_layout(x0, Wt).shape == (0, 768)
+    lib = K.lib.load()
+    assert lib.blr_dense(None, 512, 0, 0, Wt.data_ptr(), 0, 512, 768, None, 768, None) == 0
+    assert lib.blr_blast(None, 512, 0, 0, U.to(DEV).data_ptr(), 0, Vt.to(DEV).data_ptr(), 0, S.to(DEV).data_ptr(), 4 * 128,
+                         128, 1, 4, 128, 192, 128, 0, None, 768, None, 0, None) == 0
+
+
 def test_repeated_calls_reuse_the_workspace(K):
     """The grid-barrier words re-arm themselves: 50 back-to-back calls give the same answer."""
     x, U, Vt, S = orc.make_blast_inputs(16, 1024, 1024, 4, 256, torch.float16, seed=2)
