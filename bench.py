@@ -334,6 +334,44 @@ def run_ours(args):
             v["speedup_vs_dense_fp16_cublas"] = context[f"blast_fp16_n{n}"]["dense_fp16_cublas_us"] / v["us_per_layer"]
         del Us, Vs, Ws
 
+        # Network-level context: the 224 structured linears of one Llama-7B-BLAST decode step (32 layers x
+        # q/k/v/o 4096->4096 R=1024 and gate/up/down R=1488, b=16, as in the reference's
+        # configs/networks/llama7b.yaml), every layer with its own random factors (6.6 GB in fp16, far beyond L2),
+        # chained in one CUDA graph.  Attention, norms and the SwiGLU product are not part of the path and not run.
+        def linear_chain(bits):
+            shapes = [(4096, 4096, 1024)] * 4 + [(4096, 11008, 1488)] * 2 + [(11008, 4096, 1488)]
+            layers, nbytes = [], 0
+            for _ in range(32):
+                for (i_f, o_f, r) in shapes:
+                    p_, q_ = i_f // B_BLK, o_f // B_BLK
+                    u = torch.randn(B_BLK, q_, r, device=dev, dtype=torch.float16) / r ** 0.5
+                    v = torch.randn(B_BLK, r, p_, device=dev, dtype=torch.float16) / p_ ** 0.5
+                    s_ = torch.rand(B_BLK, B_BLK, r, device=dev, dtype=torch.float16) + 0.5
+                    wb = 2 if bits == 16 else bits / 8
+                    nbytes += wb * r * (i_f + o_f) + 2 * B_BLK * B_BLK * r + 2 * (i_f + o_f)
+                    if bits == 16:
+                        layers.append((i_f, (u, v, s_)))
+                    else:
+                        layers.append((i_f, (*bq.quantize_blast_factors(u, v, bits), s_)))
+                        del u, v
+            xin = {4096: torch.randn(1, 4096, device=dev, dtype=torch.float16),
+                   11008: torch.randn(1, 11008, device=dev, dtype=torch.float16)}
+
+            def step():
+                for i_f, f in layers:
+                    if bits == 16:
+                        bk.blast_torch_layout(xin[i_f], *f)
+                    else:
+                        bq.blast_wq(xin[i_f], f[0], f[1], f[2], f[3], f[4], bits)
+            us = graph_time([step], reps=5)
+            floor = nbytes / (peak_hbm * 1e9) * 1e6
+            return {"us_per_token_step": us, "tokens_per_s_batch1": 1e6 / us, "linears": len(layers),
+                    "weight_streaming_floor_us": floor, "frac": floor / us}
+
+        context["llama7b_blast_linears_decode_fp16"] = linear_chain(16)
+        context["llama7b_blast_linears_decode_int8"] = linear_chain(8)
+        torch.cuda.empty_cache()
+
     # ---- end to end through the public Python operator, host buffers in and out every launch
     def e2e_step():
         for bits, n in POINTS:
