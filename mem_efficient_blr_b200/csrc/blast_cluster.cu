@@ -287,39 +287,45 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
         consumer_bar();  // sbuf complete for every thread
         if (ctid == 0) BLR_STAMP(3);
         if (!*abort_flag) {
-          const int nv = rs >> 3;
+          // One item = 8 ranks of one token; two neighbouring lanes share an item, each gathers eight of the
+          // (up to) sixteen in-blocks with all its remote loads in flight at once, then the halves are added.
+          const int nv = rs >> 3, items = p.N * nv * 2;
           const uint32_t ybase = smem_u32(ybuf), sbase = smem_u32(sbuf);
-          for (int e = ctid; e < p.N * nv; e += kConsumerWarps * 32) {
-            const int n = e / nv, v = e - n * nv;
+          for (int base = 0; base < items; base += kConsumerWarps * 32) {
+            const int e = base + ctid, pe = e >> 1, j0 = (e & 1) * 8;
+            const bool valid = e < items;
+            const int n = valid ? pe / nv : 0, v = valid ? pe - n * nv : 0;
             float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             const uint32_t yoff = ybase + (n * rs + v * 8) * 2;
-            for (int j0 = 0; j0 < nb; j0 += 8) {
-              uint4 yv[8];
+            uint4 yv[8];
 #pragma unroll
-              for (int jj = 0; jj < 8; ++jj)
-                yv[jj] = j0 + jj < nb ? ld_shared_cluster_v4(mapa_shared(yoff, j0 + jj)) : make_uint4(0, 0, 0, 0);
+            for (int jj = 0; jj < 8; ++jj)
+              yv[jj] = (valid && j0 + jj < nb) ? ld_shared_cluster_v4(mapa_shared(yoff, j0 + jj)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-              for (int jj = 0; jj < 8; ++jj) {
-                if (j0 + jj < nb) {
-                  uint4 sv;
-                  lds128(sbase + ((j0 + jj) * rs + v * 8) * 2, sv.x, sv.y, sv.z, sv.w);
-                  const float2 s0 = unpack16x2<BF16>(sv.x), s1 = unpack16x2<BF16>(sv.y), s2 = unpack16x2<BF16>(sv.z), s3 = unpack16x2<BF16>(sv.w);
-                  const float2 y0 = unpack16x2<BF16>(yv[jj].x), y1 = unpack16x2<BF16>(yv[jj].y), y2 = unpack16x2<BF16>(yv[jj].z), y3 = unpack16x2<BF16>(yv[jj].w);
-                  s[0] = fmaf(s0.x, y0.x, s[0]); s[1] = fmaf(s0.y, y0.y, s[1]);
-                  s[2] = fmaf(s1.x, y1.x, s[2]); s[3] = fmaf(s1.y, y1.y, s[3]);
-                  s[4] = fmaf(s2.x, y2.x, s[4]); s[5] = fmaf(s2.y, y2.y, s[5]);
-                  s[6] = fmaf(s3.x, y3.x, s[6]); s[7] = fmaf(s3.y, y3.y, s[7]);
-                }
+            for (int jj = 0; jj < 8; ++jj) {
+              if (valid && j0 + jj < nb) {
+                uint4 sv;
+                lds128(sbase + ((j0 + jj) * rs + v * 8) * 2, sv.x, sv.y, sv.z, sv.w);
+                const float2 s0 = unpack16x2<BF16>(sv.x), s1 = unpack16x2<BF16>(sv.y), s2 = unpack16x2<BF16>(sv.z), s3 = unpack16x2<BF16>(sv.w);
+                const float2 y0 = unpack16x2<BF16>(yv[jj].x), y1 = unpack16x2<BF16>(yv[jj].y), y2 = unpack16x2<BF16>(yv[jj].z), y3 = unpack16x2<BF16>(yv[jj].w);
+                s[0] = fmaf(s0.x, y0.x, s[0]); s[1] = fmaf(s0.y, y0.y, s[1]);
+                s[2] = fmaf(s1.x, y1.x, s[2]); s[3] = fmaf(s1.y, y1.y, s[3]);
+                s[4] = fmaf(s2.x, y2.x, s[4]); s[5] = fmaf(s2.y, y2.y, s[5]);
+                s[6] = fmaf(s3.x, y3.x, s[6]); s[7] = fmaf(s3.y, y3.y, s[7]);
               }
             }
-            if (p.round_z) {
 #pragma unroll
-              for (int k = 0; k < 8; ++k) s[k] = round_clamp_i8(s[k]);
+            for (int k = 0; k < 8; ++k) s[k] += __shfl_xor_sync(0xffffffffu, s[k], 1);
+            if (valid && (e & 1) == 0) {
+              if (p.round_z) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) s[k] = round_clamp_i8(s[k]);
+              }
+              uint4 o;
+              o.x = pack16x2<BF16>(s[0], s[1]); o.y = pack16x2<BF16>(s[2], s[3]);
+              o.z = pack16x2<BF16>(s[4], s[5]); o.w = pack16x2<BF16>(s[6], s[7]);
+              *reinterpret_cast<uint4*>(zbuf + (v >> 3) * kABoxBytes + sw128(n, v & 7)) = o;
             }
-            uint4 o;
-            o.x = pack16x2<BF16>(s[0], s[1]); o.y = pack16x2<BF16>(s[2], s[3]);
-            o.z = pack16x2<BF16>(s[4], s[5]); o.w = pack16x2<BF16>(s[6], s[7]);
-            *reinterpret_cast<uint4*>(zbuf + (v >> 3) * kABoxBytes + sw128(n, v & 7)) = o;
           }
         }
         consumer_bar();  // zbuf complete; this CTA no longer reads its peers' ybuf
