@@ -125,7 +125,8 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
  * are rejected with BLR_ERR_WORKSPACE.  The first call on each device looks the array up with
  * cudaGetSymbolAddress (that device must be current) - make that first call before any stream capture.  It calls
  * no cudaMalloc / cudaFree or other allocating routine.  All calls on a device share the one array: it keeps the
- * previous call's contents (the control words are cleared on the stream at the start of every call), and two
+ * previous call's contents (the control words and the accumulation area the shape can touch are cleared on the
+ * stream at the start of every call), and two
  * calls that overlap on the GPU (different streams) race on it. */
 int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                      const void* U, int u_layout, const void* V, int v_layout,

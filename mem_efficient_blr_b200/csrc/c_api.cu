@@ -140,10 +140,9 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
                          const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                          int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
                          int64_t ldo, const Workspace& w, cudaStream_t stream) {
-  static const bool disabled = getenv("BLR_NO_CLUSTER") != nullptr;
   // above 8 tokens the exchange through distributed shared memory costs more than the grid barriers it saves
   const int np = 8;
-  if (disabled || g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
+  if (g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
   if ((long long)b * Q * np * 4 > kClusterOut32Bytes) return 1;
   const int bf = dtype == BLR_DTYPE_BF16;
   ClusterParams p = {};
@@ -342,8 +341,12 @@ int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype, co
   void* ws = nullptr;
   int rc = static_scratch_ptr(&ws);  // first call on a device: resolves the array's address
   if (rc) return rc;
-  // The array keeps whatever the previous call left; the barrier words must start at zero.
-  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes, static_cast<cudaStream_t>(stream)));
+  // The array keeps whatever the previous call left.  The control words and the part of the fp32 accumulation
+  // area this shape can touch must start at zero; the kernels leave them zero, but a call that gave up on a wait
+  // does not, and this entry point has no separate init call.
+  size_t head = (size_t)b * Q * 16 * sizeof(float);
+  if (head > (size_t)kClusterOut32Bytes) head = kClusterOut32Bytes;
+  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes + head, static_cast<cudaStream_t>(stream)));
   return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b, P,
                     Q, R, flags, out, ldo, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }

@@ -63,7 +63,6 @@ struct alignas(64) StreamParams {
   int w_bytes;    // weight part of a stage: max over phases of ks * kSubBytes
   int nstages;
   int mix_bytes;  // shared memory for the coupling's copy of y (0 when mix == 0)
-  int debug;  // experiment switches (0 in production)
   unsigned long long* timeline;  // optional: 16 time stamps per CTA (profiling aid), else nullptr
 };
 

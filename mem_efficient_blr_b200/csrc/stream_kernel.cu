@@ -209,12 +209,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
           // sub-chunks past the end of K read out-of-range coordinates: zero fill, no memory traffic
           if (kmajor) {
             if (lane == 0) {
-              if (p.debug & 2) mbar_arrive(bar);
-              else {
-                mbar_arrive_expect_tx(bar, ksub * b.nt * 16 * 128);
-                for (int sub = 0; sub < ksub; ++sub)
-                  tma_load_3d(dst + sub * kSubBytes, &ph.tmW[b.nt - 1], k0 + sub * kstep, b.mt0 * 16, b.g, bar);
-              }
+              mbar_arrive_expect_tx(bar, ksub * b.nt * 16 * 128);
+              for (int sub = 0; sub < ksub; ++sub)
+                tma_load_3d(dst + sub * kSubBytes, &ph.tmW[b.nt - 1], k0 + sub * kstep, b.mt0 * 16, b.g, bar);
             }
           } else {
             if (lane == 0) mbar_arrive_expect_tx(bar, ksub * b.nt * kTileBytes);
@@ -253,13 +250,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
           for (int c = 0; c < nchunks; ++c) {
             if (!rp.first_pass && !mbar_wait(empty0 + 8 * rp.s, rp.use_parity ^ 1u, abort_flag)) { ok = false; break; }
             const uint32_t dst = smem_base + rp.s * stage_bytes + p.w_bytes, bar = full0 + 8 * rp.s;
-            if (p.debug & 1) {
-              mbar_arrive(bar);
-            } else {
-              const int k0 = kc * a_boxes * 64;
-              mbar_arrive_expect_tx(bar, a_boxes * kABoxBytes);
-              for (int bx = 0; bx < a_boxes; ++bx) tma_load_3d(dst + bx * kABoxBytes, &ph.tmA, k0 + bx * 64, 0, b.g, bar);
-            }
+            const int k0 = kc * a_boxes * 64;
+            mbar_arrive_expect_tx(bar, a_boxes * kABoxBytes);
+            for (int bx = 0; bx < a_boxes; ++bx) tma_load_3d(dst + bx * kABoxBytes, &ph.tmA, k0 + bx * 64, 0, b.g, bar);
             rp.advance(NST);
             if (++kc == nchunks) kc = 0;
           }
@@ -312,7 +305,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
             first_stage = false;
             if (ctid == 0) BLR_STAMP(3);  // first stage landed
           }
-          if (active && !(p.debug & 4)) {
+          if (active) {
             uint32_t sW = smem_base + s * stage_bytes, sA = sW + p.w_bytes;
             for (int sub = 0; sub < ksub; ++sub, sW += kSubBytes, sA += a_sub) {
               GroupScales gs;
@@ -459,7 +452,6 @@ void set_stream_timeline(unsigned long long* dev_ptr) { g_stream_timeline = dev_
 int launch_stream(const StreamParams& p_in, int is_bf16, cudaStream_t stream) {
   StreamParams p = p_in;
   p.timeline = g_stream_timeline;
-  { static const int dbg = getenv("BLR_STREAM_DEBUG") ? atoi(getenv("BLR_STREAM_DEBUG")) : 0; p.debug = dbg; }
   BLR_REQUIRE(p.N >= 1 && p.N <= kStreamMaxTokens, BLR_ERR_ARG, "stream kernel handles 1..%d tokens, got %d",
               kStreamMaxTokens, p.N);
   if (p.ph[0].group != 0) {  // one scale per kScaleGroup contraction indices: its own instantiation

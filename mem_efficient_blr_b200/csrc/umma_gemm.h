@@ -26,7 +26,6 @@ struct alignas(64) GemmParams {
   long long os_g, os_n, os_hi, os_lo;
   void* out;
   unsigned* status;  // optional: set to 1 when a device-side wait gave up
-  int debug;         // experiment switches (0 in production)
 };
 
 int launch_umma_gemm(const GemmParams& p, cudaStream_t stream);
