@@ -50,6 +50,8 @@ BLAST_SHAPES = [
     (128, 4096, 11008, 16, 1024),  # headline layer, 128 tokens
     (2048, 4096, 11008, 16, 1024),
     (129, 11008, 4096, 16, 1488),  # down_proj at the reference's 50 %-parameter rank, ragged token count
+    (65, 1152, 2304, 6, 192),      # six and nine blocks
+    (197, 2304, 3456, 9, 384),
 ]
 
 

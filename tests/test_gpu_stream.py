@@ -52,6 +52,9 @@ BLAST_SHAPES = [
     (8, 4096, 11008, 16, 1024),   # headline layer, Q=688 is not a multiple of 32
     (16, 4096, 11008, 16, 1024),
     (1, 11008, 4096, 16, 1488),   # down_proj with the reference's 50%-parameter rank
+    (3, 1152, 2304, 6, 192),      # six blocks: a cluster of 6 CTAs
+    (16, 2304, 3456, 9, 384),     # nine blocks, beyond the portable cluster size
+    (2, 3456, 1152, 9, 256),
 ]
 
 
