@@ -44,13 +44,13 @@ def _dims_bmm(x, U, V, S):
 def _partial_fp16(x, U, V, S, flags=L.FLAG_NONE):
     b, p, q, r = _dims_partial(x, U, V, S)
     out = ops.blast(ops._flat2d(x), U, V, S, L.MMAJOR, L.MMAJOR, r, b * r, 1, b, p, q, r, flags)
-    return out.reshape(*x.shape[:-1], b * q)
+    return ops._like_input(out, x)
 
 
 def _partial_fp32(x, U, V, S):
     b, p, q, r = _dims_partial(x, U, V, S)
     out, z, y = ops.blast_f32(ops.flat2d_f32(x), U, V, S, L.MMAJOR, L.MMAJOR, r, b * r, 1, b, p, q, r)
-    return out.reshape(*x.shape[:-1], b * q), z, y
+    return ops._like_input(out, x), z, y
 
 
 def triton_blast_partial_fp16(x, U, V, S, config=None):
@@ -97,14 +97,14 @@ def triton_blast_bmm_fp16(x, U, V, S, config=(None, None, None)):
     """Replaces triton_blast_bmm_fp16 (blast_kernels.py:3043-3065)."""
     b, p, q, r = _dims_bmm(x, U, V, S)
     out = ops.blast(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_NONE)
-    return out.reshape(*x.shape[:-1], b * q)
+    return ops._like_input(out, x)
 
 
 def triton_blast_bmm_fp32(x, U, V, S):
     """Replaces triton_blast_bmm_fp32 (blast_kernels.py:2998-3041): (out, z (b,R,N), y (R,b,N))."""
     b, p, q, r = _dims_bmm(x, U, V, S)
     out, z, y = ops.blast_f32(ops.flat2d_f32(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r)
-    return out.reshape(*x.shape[:-1], b * q), z.transpose(1, 2), y.permute(2, 0, 1)
+    return ops._like_input(out, x), z.transpose(1, 2), y.permute(2, 0, 1)
 
 
 def blast_torch_layout(x, U, Vt, S, flags=L.FLAG_NONE):
@@ -114,7 +114,7 @@ def blast_torch_layout(x, U, Vt, S, flags=L.FLAG_NONE):
     b2, q, r2 = U.shape
     assert b == b2 and b != 1 and r2 == r and tuple(S.shape) == (b2, b, r)
     out = ops.blast(ops._flat2d(x), U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags)
-    return out.reshape(*x.shape[:-1], b * q)
+    return ops._like_input(out, x)
 
 
 def blast_output_blocks(x, U_local, Vt, S_local, flags=L.FLAG_NONE):
@@ -125,7 +125,7 @@ def blast_output_blocks(x, U_local, Vt, S_local, flags=L.FLAG_NONE):
     assert 1 <= bo <= b and r2 == r and tuple(S_local.shape) == (bo, b, r)
     assert U_local.is_contiguous() and S_local.is_contiguous()
     out = ops.blast(ops._flat2d(x), U_local, Vt, S_local, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, flags, bo)
-    return out.reshape(*x.shape[:-1], bo * q)
+    return ops._like_input(out, x)
 
 
 # The reference exposes its autotuner's winning configuration (blast_kernels.py:3068-3086) and pickles

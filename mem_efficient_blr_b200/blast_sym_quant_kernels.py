@@ -20,7 +20,7 @@ def triton_blast_bmm_int8_fp16(x, U, V, S, config=(None, None, None)):
     (blast_sym_quant_kernels.py:105-108, 227-230)."""
     b, p, q, r = _dims_bmm(x, U, V, S)
     out = ops.blast(ops._flat2d(x), U, V, S, L.KMAJOR, L.MMAJOR, b, 1, b * b, b, p, q, r, L.FLAG_ACT_INT8)
-    return out.reshape(*x.shape[:-1], b * q)
+    return ops._like_input(out, x)
 
 
 def get_triton_blast_bmm_xv_int8_fp16_config():
@@ -50,14 +50,13 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     scales fp16 (b,Q) / (b,R), or (b,Q,R/group) / (b,R,P/group) with per-group scales;
     S (b_out, b_in, R) in x's dtype."""
     assert bits in (8, 4)
-    b, q = u_scale.shape[:2]
-    b2, r = v_scale.shape[:2]
-    p = Vq.shape[-1] * (1 if bits == 8 else 2)
-    assert b == b2 and b != 1 and tuple(S.shape) == (b, b, r)
-    assert Uq.shape[-1] * (1 if bits == 8 else 2) == r and x.shape[-1] == b * p
+    per = 1 if bits == 8 else 2
+    b, q, r, p = u_scale.size(0), u_scale.size(1), v_scale.size(1), Vq.size(-1) * per
+    assert v_scale.size(0) == b and b != 1 and S.size(0) == b and S.size(1) == b and S.size(2) == r
+    assert Uq.size(-1) * per == r and x.size(-1) == b * p
     if group == 0:
         assert u_scale.dim() == 2 and v_scale.dim() == 2, "one scale per output channel expected (group = 0)"
     else:
         assert tuple(u_scale.shape) == (b, q, r // group) and tuple(v_scale.shape) == (b, r, p // group)
     out = ops.blast_wq(ops._flat2d(x), Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
-    return out.reshape(*x.shape[:-1], b * q)
+    return ops._like_input(out, x)

@@ -25,7 +25,7 @@ def triton_dense_fp32(x, w):
 def dense_torch_layout(x, Wt):
     """torch layout Wt (O, I) (torch_funcs/dense_funcs.py:4-25); batch dims restored."""
     o, i = Wt.shape
-    return ops.dense(ops._flat2d(x), Wt, L.KMAJOR, i, o).reshape(*x.shape[:-1], o)
+    return ops._like_input(ops.dense(ops._flat2d(x), Wt, L.KMAJOR, i, o), x)
 
 
 def get_triton_dense_fp16_config():

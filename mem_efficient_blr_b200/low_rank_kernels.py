@@ -33,7 +33,7 @@ def low_rank_torch_layout(x, Vt, Ut):
     """torch layouts Vt (R, I), Ut (O, R) (torch_funcs/low_rank_funcs.py:4-28); batch dims restored."""
     r, i = Vt.shape
     o, _ = Ut.shape
-    return ops.low_rank(ops._flat2d(x), Vt, Ut, L.KMAJOR, L.KMAJOR, i, r, o).reshape(*x.shape[:-1], o)
+    return ops._like_input(ops.low_rank(ops._flat2d(x), Vt, Ut, L.KMAJOR, L.KMAJOR, i, r, o), x)
 
 
 def get_triton_low_rank_fp16_config():

@@ -28,13 +28,13 @@ def _dims(x, w1, w2, w2_kmajor):
 def _run16(x, w1, w2, w2_layout, order):
     b, p, rank, s = _dims(x, w1, w2, w2_layout == L.KMAJOR)
     out = ops.monarch(ops._flat2d(x), w1, w2, L.MMAJOR, L.COLS_GROUPED, w2_layout, b, p, rank, s, order)
-    return out.reshape(*x.shape[:-1], b * s)
+    return ops._like_input(out, x)
 
 
 def _run32(x, w1, w2, w2_layout, order):
     b, p, rank, s = _dims(x, w1, w2, w2_layout == L.KMAJOR)
     out, out1 = ops.monarch_f32(ops.flat2d_f32(x), w1, w2, L.MMAJOR, L.COLS_GROUPED, w2_layout, b, p, rank, s, order)
-    return out.reshape(*x.shape[:-1], b * s), out1
+    return ops._like_input(out, x), out1
 
 
 def triton_monarch_right_fp16(x, w1_bfly, w2_bfly_t, config=None):
@@ -78,7 +78,7 @@ def monarch_torch_layout(x, w1_t, w2_t):
     l, s, r = w2_t.shape
     assert b == l and r == rank and b * p == x.shape[-1] and rank % b == 0
     out = ops.monarch(ops._flat2d(x), w1_t, w2_t, L.KMAJOR, L.COLS_TORCH, L.KMAJOR, b, p, rank, s, L.OUT_INTERLEAVED)
-    return out.reshape(*x.shape[:-1], b * s)
+    return ops._like_input(out, x)
 
 
 def get_triton_monarch_right_fp16_config():

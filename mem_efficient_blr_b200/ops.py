@@ -17,8 +17,14 @@ from . import _lib as L
 
 
 def _flat2d(x: torch.Tensor) -> torch.Tensor:
-    """(..., I) -> (N, I); a view whenever the leading dims can be merged (traceable by torch.compile)."""
-    return x.reshape(-1, x.shape[-1])
+    """(..., I) -> (N, I); a view whenever the leading dims can be merged (traceable by torch.compile).
+    A 2-D input is returned as it is: a reshape costs more host time than some of the kernels run."""
+    return x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+
+
+def _like_input(out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """(N, W) -> (..., W) with the leading dims of x."""
+    return out if x.dim() == 2 else out.reshape(*x.shape[:-1], out.shape[-1])
 
 
 def _rows(x2: torch.Tensor) -> torch.Tensor:
