@@ -368,6 +368,53 @@ def run_ours(args):
             return {"us_per_token_step": us, "tokens_per_s_batch1": 1e6 / us, "linears": len(layers),
                     "weight_streaming_floor_us": floor, "frac": floor / us}
 
+        # Layer sweep: every operator family at the three Llama-7B linear shapes, 1 token and 2048 tokens, fp16,
+        # ranks from the reference's 50 %-parameter configurations; roofline = max(bytes / HBM, flops / tensor).
+        import mem_efficient_blr_b200.dense_kernels as dk
+        import mem_efficient_blr_b200.low_rank_kernels as lk
+        import mem_efficient_blr_b200.monarch_kernels as mk
+
+        def sweep_point(kind, i_f, o_f, r, n):
+            xn = torch.randn(n, i_f, device=dev, dtype=torch.float16)
+            h = lambda *shape, fan: torch.randn(*shape, device=dev, dtype=torch.float16) / fan ** 0.5
+            if kind == "blast":
+                wbytes = 2 * r * (i_f + o_f) + 2 * B_BLK * B_BLK * r
+                flops = 2 * n * r * (i_f + o_f + B_BLK * B_BLK)
+                mk_one = lambda: (h(B_BLK, o_f // B_BLK, r, fan=r), h(B_BLK, r, i_f // B_BLK, fan=i_f // B_BLK),
+                                  torch.rand(B_BLK, B_BLK, r, device=dev, dtype=torch.float16) + 0.5)
+                call = lambda f: bk.blast_torch_layout(xn, *f)
+            elif kind == "monarch":
+                wbytes = 2 * r * (i_f + o_f)
+                flops = 2 * n * r * (i_f + o_f)
+                mk_one = lambda: (h(B_BLK, r, i_f // B_BLK, fan=i_f // B_BLK), h(B_BLK, o_f // B_BLK, r, fan=r))
+                call = lambda f: mk.monarch_torch_layout(xn, *f)
+            elif kind == "low_rank":
+                wbytes = 2 * r * (i_f + o_f)
+                flops = 2 * n * r * (i_f + o_f)
+                mk_one = lambda: (h(r, i_f, fan=i_f), h(o_f, r, fan=r))
+                call = lambda f: lk.low_rank_torch_layout(xn, *f)
+            else:
+                wbytes = 2 * i_f * o_f
+                flops = 2 * n * i_f * o_f
+                mk_one = lambda: (h(o_f, i_f, fan=i_f),)
+                call = lambda f: dk.dense_torch_layout(xn, *f)
+            nrep = int(2 * L2_BYTES // wbytes) + 1
+            sets = [mk_one() for _ in range(nrep)]
+            us = graph_time([(lambda f=f: call(f)) for f in sets], reps=5)
+            nbytes = wbytes + 2 * n * (i_f + o_f)
+            roof = max(nbytes / (peak_hbm * 1e9), flops / (peak_tf * 1e12)) * 1e6
+            return {"us_per_layer": us, "roofline_us": roof, "frac": roof / us}
+
+        layer_sweep = {}
+        for lname, i_f, o_f, ranks in (("qkvo_4096x4096", 4096, 4096, {"blast": 1024, "monarch": 1024, "low_rank": 1024}),
+                                       ("gate_4096x11008", 4096, 11008, {"blast": 1488, "monarch": 1536, "low_rank": 1024}),
+                                       ("down_11008x4096", 11008, 4096, {"blast": 1488, "monarch": 1536, "low_rank": 1024})):
+            for kind in ("blast", "monarch", "low_rank", "dense"):
+                for n in (1, 2048):
+                    layer_sweep[f"{lname}/{kind}/n{n}"] = sweep_point(kind, i_f, o_f, ranks.get(kind, 0), n)
+                    torch.cuda.empty_cache()
+        context["layer_sweep_fp16"] = layer_sweep
+
         context["llama7b_blast_linears_decode_fp16"] = linear_chain(16)
         context["llama7b_blast_linears_decode_int8"] = linear_chain(8)
         torch.cuda.empty_cache()

@@ -399,7 +399,7 @@ int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const v
     return launch_stream(p, dtype == BLR_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   }
   return pipeline_monarch(x, ldx, N, dtype, w1, w1_layout, grouped, w2, w2_layout, b, P, rank, Qs,
-                          out_order == BLR_OUT_INTERLEAVED, out, ldo, w.region_b, static_cast<cudaStream_t>(stream));
+                          out_order == BLR_OUT_INTERLEAVED, out, ldo, w.region_b, w.region_a, static_cast<cudaStream_t>(stream));
 }
 
 int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* V, int v_layout, const void* U,

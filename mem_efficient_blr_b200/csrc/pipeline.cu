@@ -161,16 +161,117 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
   return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
 }
 
+// Transposes small matrices: in[a][c] (A x C, contiguous) -> out[c * out_c + a], kRowsPerCta matrices per CTA.
+// Matrix (g, r), r < rows, is read at g * in_g + r * A * C and written at g * out_g + r * out_r.
+// A GEMM that would scatter 2-byte stores across planes (Monarch's middle permutation on the torch layout) or across
+// 32-byte sectors (Monarch's interleaved output) writes its natural layout instead, and this pass re-orders it:
+// 16-byte global loads, element-wise through shared memory (pitch C + 2: the transposed reads touch all banks),
+// 16-byte global stores where eight consecutive outputs are contiguous and aligned.
+static constexpr int kRowsPerCta = 4;
+
+__global__ void __launch_bounds__(256) transpose_rows_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out,
+                                                             int A, int C, long long rows, long long in_g, long long out_g,
+                                                             long long out_r, long long out_c, int vec_out) {
+  extern __shared__ uint16_t tile[];  // [kRowsPerCta][A][C + 2]
+  const long long chunks = (rows + kRowsPerCta - 1) / kRowsPerCta;
+  const long long g = blockIdx.x / chunks, r0 = (blockIdx.x - g * chunks) * kRowsPerCta;
+  const int nr = (int)(rows - r0 < kRowsPerCta ? rows - r0 : kRowsPerCta);
+  const int pitch = C + 2, mat = A * C, total = nr * mat, step = blockDim.x * 8;
+  const uint16_t* src = in + g * in_g + r0 * mat;
+  {  // linear read of nr contiguous matrices, eight elements per thread and step (mat is a multiple of 8)
+    for (int e = threadIdx.x * 8; e < total; e += step) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src + e);
+      const uint16_t* h = reinterpret_cast<const uint16_t*>(&v);
+      const int r = e / mat, em = e - r * mat;
+      int a = em / C, c = em - a * C;
+      uint16_t* t = tile + r * A * pitch;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        t[a * pitch + c] = h[k];
+        if (++c == C) { c = 0; ++a; }
+      }
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < nr; ++r) {
+    const uint16_t* t = tile + r * A * pitch;
+    uint16_t* dst = out + g * out_g + (r0 + r) * out_r;
+    if (vec_out) {  // A % 8 == 0 and every run of A outputs starts 16-byte aligned
+      for (int e = threadIdx.x * 8; e < mat; e += step) {
+        const int c = e / A, a = e - c * A;
+        uint4 v;
+        uint16_t* h = reinterpret_cast<uint16_t*>(&v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) h[k] = t[(a + k) * pitch + c];
+        *reinterpret_cast<uint4*>(dst + c * out_c + a) = v;
+      }
+    } else {
+      for (int e = threadIdx.x; e < mat; e += blockDim.x) {
+        const int c = e / A, a = e - c * A;
+        dst[c * out_c + a] = t[a * pitch + c];
+      }
+    }
+  }
+}
+
+static int transpose_rows(const void* in, void* out, int A, int C, long long groups, long long rows, long long in_g,
+                          long long out_g, long long out_r, long long out_c, cudaStream_t stream) {
+  const size_t smem = (size_t)kRowsPerCta * A * (C + 2) * 2;
+  BLR_REQUIRE((A * C) % 8 == 0, BLR_ERR_SHAPE, "re-ordering needs matrices of a multiple of 8 elements, got %d x %d", A, C);
+  const long long chunks = (rows + kRowsPerCta - 1) / kRowsPerCta;
+  BLR_REQUIRE(groups * chunks < (1ll << 31), BLR_ERR_SHAPE, "too many rows to re-order");
+  static bool configured[64] = {};
+  int dev = 0;
+  BLR_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    BLR_CUDA_OK(cudaFuncSetAttribute(transpose_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    configured[dev & 63] = true;
+  }
+  const int vec_out = A % 8 == 0 && out_c % 8 == 0 && out_g % 8 == 0 && out_r % 8 == 0 &&
+                      (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  transpose_rows_kernel<<<(unsigned)(groups * chunks), 256, smem, stream>>>(static_cast<const uint16_t*>(in),
+                                                                             static_cast<uint16_t*>(out), A, C, rows, in_g,
+                                                                             out_g, out_r, out_c, vec_out);
+  BLR_CUDA_OK(cudaGetLastError());
+  return BLR_OK;
+}
+
+// Shared memory the re-ordering pass needs for A x C matrices.
+static size_t transpose_smem(int A, int C) { return (size_t)kRowsPerCta * A * (C + 2) * 2; }
+
+// scratch: at least 4 * b * N * rank bytes (the fp32-sized region of a workspace), z16: 2 * b * N * rank bytes.
 int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const void* w1, int w1_layout, int grouped,
                      const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,
-                     int64_t ldo, void* z16, cudaStream_t stream) {
+                     int64_t ldo, void* z16, void* scratch, cudaStream_t stream) {
   const int per = rank / b;
   const long long plane = (long long)N * rank;
-  const OutSpec o1 = grouped ? OutSpec{z16, per, rank, plane, 1, per, 0} : OutSpec{z16, per, rank, 1, plane, b, 0};
-  int rc = run_gemm(dtype, w1, w1_layout, b, rank, P, x, N, ldx, P, o1, stream);
-  if (rc) return rc;
-  const OutSpec o2 = interleaved ? OutSpec{out, 1, ldo, 0, b, Qs, 0} : OutSpec{out, Qs, ldo, 0, 1, Qs, 0};
-  return run_gemm(dtype, w2, w2_layout, b, Qs, rank, z16, N, rank, plane, o2, stream);
+  int rc;
+  if (grouped) {
+    // columns already grouped by destination block: column l*per + jj of block k goes to Z[l][n][k*per + jj]
+    rc = run_gemm(dtype, w1, w1_layout, b, rank, P, x, N, ldx, P, OutSpec{z16, per, rank, plane, 1, per, 0}, stream);
+    if (rc) return rc;
+  } else if (rank % 8 == 0 && transpose_smem(per, b) <= 160 * 1024) {
+    // torch layout: column jj*b + l of block k goes to Z[l][n][k*per + jj].  Written directly that is one 2-byte
+    // store per plane; instead the GEMM writes pre[k][n][q] and a pass transposes every (k, n) row (per x b).
+    rc = run_gemm(dtype, w1, w1_layout, b, rank, P, x, N, ldx, P, OutSpec{scratch, plane, rank, 0, 1, rank, 0}, stream);
+    if (rc) return rc;
+    rc = transpose_rows(scratch, z16, per, b, b, N, plane, per, rank, plane, stream);
+    if (rc) return rc;
+  } else {
+    rc = run_gemm(dtype, w1, w1_layout, b, rank, P, x, N, ldx, P, OutSpec{z16, per, rank, 1, plane, b, 0}, stream);
+    if (rc) return rc;
+  }
+  if (!interleaved) return run_gemm(dtype, w2, w2_layout, b, Qs, rank, z16, N, rank, plane, OutSpec{out, Qs, ldo, 0, 1, Qs, 0}, stream);
+  // interleaved output, feature s*b + l: written directly, neighbouring outputs of a block are b elements apart
+  // (one sector per 2-byte store).  When the scratch region can hold the block-major result, write that and
+  // transpose every token's (b x Qs) row.
+  if (Qs <= 2 * rank && (b * Qs) % 8 == 0 && transpose_smem(b, Qs) <= 160 * 1024) {
+    rc = run_gemm(dtype, w2, w2_layout, b, Qs, rank, z16, N, rank, plane,
+                  OutSpec{scratch, Qs, (long long)b * Qs, 0, 1, Qs, 0}, stream);
+    if (rc) return rc;
+    return transpose_rows(scratch, out, b, Qs, 1, N, 0, 0, ldo, b, stream);
+  }
+  return run_gemm(dtype, w2, w2_layout, b, Qs, rank, z16, N, rank, plane, OutSpec{out, 1, ldo, 0, b, Qs, 0}, stream);
 }
 
 int pipeline_low_rank(const void* x, int64_t ldx, int64_t N, int dtype, const void* V, int v_layout, const void* U,

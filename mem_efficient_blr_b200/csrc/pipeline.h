@@ -11,7 +11,7 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
                    int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream);
 int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const void* w1, int w1_layout, int grouped,
                      const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,
-                     int64_t ldo, void* z16, cudaStream_t stream);
+                     int64_t ldo, void* z16, void* scratch, cudaStream_t stream);
 int pipeline_low_rank(const void* x, int64_t ldx, int64_t N, int dtype, const void* V, int v_layout, const void* U,
                       int u_layout, int I, int R, int O, void* out, int64_t ldo, void* z16, cudaStream_t stream);
 int pipeline_dense(const void* x, int64_t ldx, int64_t N, int dtype, const void* W, int w_layout, int I, int O,
