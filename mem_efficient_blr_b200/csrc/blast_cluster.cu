@@ -161,7 +161,10 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
       for (int e = ctid; e < nb * nv; e += kConsumerWarps * 32) {
         const int j = e / nv, v = e - j * nv, r = r_begin + v * 8;
         const uint32_t dst = smem_u32(sbuf) + (j * rs + v * 8) * 2;
-        if (s_vec && r + 8 <= p.R) {
+        if (S == nullptr) {  // no coupling factors: all ones (a plain sum over the in-blocks), zero past R
+          uint16_t* d = reinterpret_cast<uint16_t*>(sbuf) + j * rs + v * 8;
+          for (int k = 0; k < 8; ++k) d[k] = r + k < p.R ? (BF16 ? (uint16_t)0x3F80 : (uint16_t)0x3C00) : (uint16_t)0;
+        } else if (s_vec && r + 8 <= p.R) {
           cp_async16(dst, S + blk * p.s_i + j * p.s_j + r);
         } else {
           uint16_t* d = reinterpret_cast<uint16_t*>(sbuf) + j * rs + v * 8;

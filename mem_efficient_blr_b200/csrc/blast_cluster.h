@@ -28,7 +28,7 @@ struct alignas(64) ClusterParams {
   int nchunks1;        // chunks of the second phase inside one slice
   int round_y, round_z;
   long long s_i, s_j, s_r;
-  const void* S;
+  const void* S;       // coupling factors, or nullptr for all ones
   void* out;
   long long ldo;
   float* out32;        // [b*Q][8 or 16] fp32, zero between calls

@@ -42,8 +42,11 @@ static CUtensorMapDataType dt16(int dtype) {
   return dtype == BLR_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 }
 
-// Fills the weight side of a phase.
-static int phase_weights(PhaseDesc& ph, int dtype, const void* W, int layout, int wbits, int G, int M, int K) {
+// Fills the weight side of a phase.  row_stride / grp_stride (elements; 0 = packed) describe blocks that are
+// column or row slices of a larger matrix: the distance between consecutive rows of a block (K-major: output
+// rows; M-major: contraction rows) and between blocks.
+static int phase_weights(PhaseDesc& ph, int dtype, const void* W, int layout, int wbits, int G, int M, int K,
+                         int64_t row_stride = 0, int64_t grp_stride = 0) {
   ph.G = G; ph.M = M; ph.K = K; ph.kmajor = layout == BLR_W_KMAJOR; ph.wbits = wbits;
   ph.unit_rows = ph.kmajor ? 16 : 32;
   ph.tiles_per_g = (M + ph.unit_rows - 1) / ph.unit_rows;
@@ -53,7 +56,7 @@ static int phase_weights(PhaseDesc& ph, int dtype, const void* W, int layout, in
     BLR_REQUIRE(wbits == 16, BLR_ERR_UNSUPPORTED, "quantised factors must have the contraction index contiguous");
     BLR_REQUIRE(M % 8 == 0, BLR_ERR_SHAPE, "block output width %d must be a multiple of 8", M);
     const uint64_t dims[3] = {(uint64_t)M, (uint64_t)K, (uint64_t)G};
-    const uint64_t str[2] = {(uint64_t)M * 2, (uint64_t)M * K * 2};
+    const uint64_t str[2] = {(uint64_t)(row_stride ? row_stride : M) * 2, (uint64_t)(grp_stride ? grp_stride : (int64_t)M * K) * 2};
     const uint32_t box[3] = {32, 64, 1};
     ph.nchunks = (K + 63) / 64;
     return encode_tmap_3d(&ph.tmW[0], dt16(dtype), W, dims, str, box, Swz::B64);
@@ -64,7 +67,9 @@ static int phase_weights(PhaseDesc& ph, int dtype, const void* W, int layout, in
               "weight rows must be multiples of 16 bytes: contraction length %d must be a multiple of 8 (16-bit), 16 (int8) or 32 (int4)", K);
   const uint64_t inner = wbits == 16 ? (uint64_t)K : (uint64_t)kb;
   const uint64_t dims[3] = {inner, (uint64_t)M, (uint64_t)G};
-  const uint64_t str[2] = {(uint64_t)kb, (uint64_t)M * kb};
+  BLR_REQUIRE((row_stride == 0 && grp_stride == 0) || wbits == 16, BLR_ERR_UNSUPPORTED, "strided blocks are 16-bit only");
+  const uint64_t str[2] = {row_stride ? (uint64_t)row_stride * 2 : (uint64_t)kb,
+                           grp_stride ? (uint64_t)grp_stride * 2 : (uint64_t)M * kb};
   ph.nchunks = (kb + 127) / 128;
   const CUtensorMapDataType dt = wbits == 16 ? dt16(dtype) : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   for (int h = 1; h <= 8; ++h) {
@@ -139,7 +144,8 @@ static int g_decode_path = 0;  // 0: automatic, 1: grid-wide streaming kernel on
 static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                          const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                          int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
-                         int64_t ldo, const Workspace& w, cudaStream_t stream) {
+                         int64_t ldo, const Workspace& w, cudaStream_t stream, int64_t v_row = 0, int64_t v_grp = 0,
+                         int64_t u_row = 0, int64_t u_grp = 0) {
   // above 8 tokens the exchange through distributed shared memory costs more than the grid barriers it saves
   const int np = 8;
   if (g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
@@ -147,18 +153,19 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   const int bf = dtype == BLR_DTYPE_BF16;
   ClusterParams p = {};
   int rc;
-  if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, v_bits, b, R, P))) return rc;
+  if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, v_bits, b, R, P, v_row, v_grp))) return rc;
   if ((rc = phase_acts(p.ph[0], dtype, x, P, N, b, ldx, P))) return rc;
-  if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, b, Q, R))) return rc;
+  if ((rc = phase_weights(p.ph[1], dtype, U, u_layout, u_bits, b, Q, R, u_row, u_grp))) return rc;
   p.ph[0].scale = static_cast<const __half*>(v_scale);
   p.ph[1].scale = static_cast<const __half*>(u_scale);
   p.ph[0].group = p.ph[1].group = group;
   DeviceInfo di;
   if ((rc = device_info(&di))) return rc;
   // Shape of the launch: ranks per slice (a multiple of what one second-phase chunk covers), row parts of U_i,
-  // and whether two CTAs share an SM.  Measured on the headline layer (b = 16, R = 1024, 16/8/4-bit weights):
-  // wide slices and many row parts win, and two CTAs per SM pay off only when they allow more parts, because
-  // each of them then has half the ring.
+  // and whether two CTAs share an SM.  All clusters must be resident at once.  Among the shapes that are, a cost
+  // fitted to measurements on the headline layer picks one: weight bytes per CTA (a part repeats the first phase,
+  // so that term does not shrink with the parts), 20 % off when a CTA has an SM and the whole ring to itself,
+  // plus the equivalent of 20 KB per slice for the reductions and the finaliser's wait.
   const int kx = p.ph[1].kmajor ? (u_bits == 16 ? 64 : (u_bits == 8 ? 128 : 256)) : 64;
   int best_rs = 0, best_parts = 1, best_two = 0;
   static const char* forced = getenv("BLR_CLUSTER_SHAPE");  // "rs,parts,two": measurement aid
@@ -166,18 +173,24 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
     if (sscanf(forced, "%d,%d,%d", &best_rs, &best_parts, &best_two) != 3) return 1;
     if (best_rs % kx != 0 || best_rs < kx || best_rs > kClusterMaxSlice || best_parts < 1 || best_parts > kClusterMaxParts) return 1;
   } else {
-    const int r_up = (R + kx - 1) / kx * kx;
-    best_rs = r_up < kClusterMaxSlice ? r_up : kClusterMaxSlice / kx * kx;
-    if (best_rs < kx) return 1;
-    const int nsl = (R + best_rs - 1) / best_rs;
+    const int cap[2] = {cluster_capacity(b, bf, group, (int)N, di.max_smem_optin - 1024),
+                        cluster_capacity(b, bf, group, (int)N, kClusterHalfSmem)};
     const int max_parts = Q / kBatchRows < 1 ? 1 : (Q / kBatchRows > kClusterMaxParts ? kClusterMaxParts : Q / kBatchRows);
-    int parts1 = cluster_capacity(b, bf, group, (int)N, di.max_smem_optin - 1024) / nsl;
-    int parts2 = cluster_capacity(b, bf, group, (int)N, kClusterHalfSmem) / nsl;
-    if (parts1 > max_parts) parts1 = max_parts;
-    if (parts2 > max_parts) parts2 = max_parts;
-    if (parts1 < 1 && parts2 < 1) return 1;  // more slices than resident clusters: grid-wide kernel
-    best_two = parts2 > parts1 ? 1 : 0;
-    best_parts = best_two ? parts2 : parts1;
+    const int r_up = (R + kx - 1) / kx * kx;
+    double best = -1.;
+    for (int rs = kx; rs <= kClusterMaxSlice && rs <= r_up; rs += kx) {
+      if (group != 0 && rs % kScaleGroup != 0) continue;
+      const int nsl = (R + rs - 1) / rs;
+      if ((long long)nsl * rs - R >= kx) continue;  // a last slice that is mostly padding only delays the others
+      for (int two = 0; two < 2; ++two)
+        for (int parts = 1; parts <= max_parts && nsl * parts <= cap[two]; ++parts) {
+          const int qp = ((Q + parts - 1) / parts + 15) / 16 * 16;
+          const double kb = ((double)rs * P + (double)qp * rs) * u_bits / 8. / 1024.;
+          const double cost = kb * (two ? 1.0 : 0.8) + 20. * nsl;
+          if (best < 0. || cost < best) { best = cost; best_rs = rs; best_parts = parts; best_two = two; }
+        }
+    }
+    if (best < 0.) return 1;  // more slices than resident clusters at every width: grid-wide kernel
   }
   const int rs = best_rs;
   p.N = (int)N; p.b = b; p.R = R; p.Q = Q; p.rs = rs; p.nslices = (R + rs - 1) / rs;
@@ -414,6 +427,19 @@ int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
   Workspace w;
   if ((rc = carve(ws, ws_bytes, N, 1, R, &w))) return rc;
   if (N <= kStreamMaxTokens) {
+    // Low rank is BLAST with an all-ones coupling: cut the I columns of V into b blocks (y_j = V[:, block j] x_j,
+    // z = sum_j y_j) and the O rows of U into b blocks (out_i = U[block i] z).  That puts it on the cluster kernel,
+    // which splits the long contraction of the first stage over b CTAs instead of leaving it to R / 16 of them.
+    for (int bb = 16; bb >= 2; bb >>= 1) {
+      if (I % (bb * 8) != 0 || O % (bb * 8) != 0) continue;
+      const int Pb = I / bb, Qb = O / bb;
+      const bool vk = v_layout == BLR_W_KMAJOR, uk = u_layout == BLR_W_KMAJOR;
+      rc = cluster_blast(x, ldx, N, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, nullptr, 0, 0, 0, bb, bb, Pb,
+                         Qb, R, 0, out, ldo, w, static_cast<cudaStream_t>(stream), vk ? I : 0, vk ? Pb : 0, uk ? 0 : O,
+                         uk ? 0 : Qb);
+      if (rc <= 0) return rc;
+      break;  // not applicable: the grid-wide kernel below
+    }
     StreamParams p = {};
     p.nphases = 2; p.mix = 0; p.counters = w.counters;
     if ((rc = phase_weights(p.ph[0], dtype, V, v_layout, 16, 1, R, I))) return rc;
