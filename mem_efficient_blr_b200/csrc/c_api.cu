@@ -99,13 +99,27 @@ static void phase_out(PhaseDesc& ph, void* out, int out_f32, long long os_g, lon
 static void finish_params(StreamParams& p, int64_t N) {
   p.N = (int)N;
   const int nb = N <= 8 ? 8 : 16;
+  DeviceInfo di;
+  const int grid = device_info(&di) == BLR_OK && di.sm_count > 0 ? di.sm_count : 148;
   int wmax = 0, amax = 0;
   for (int i = 0; i < p.nphases; ++i) {
     PhaseDesc& ph = p.ph[i];
     // two K-chunks per ring stage halve the producer/consumer hand-offs; one when K is a single chunk
     ph.ks = ph.nchunks >= 2 ? 2 : 1;
+    ph.sub_bytes = kSubBytes;
+    if (ph.kmajor) {
+      // A CTA with few 16-row groups per batch (few output rows, long contraction) would move 2 KB per group and
+      // chunk: pack the chunks of a stage densely and take more of them, up to about 32 KB of weights per stage,
+      // as long as the activation producer does not have to issue more than 8 boxes per stage.
+      int per_cta = (ph.ntiles + grid - 1) / grid;
+      if (per_cta > ph.tiles_per_g) per_cta = ph.tiles_per_g;
+      if (per_cta > kBatchRows / 16) per_cta = kBatchRows / 16;
+      if (per_cta < 1) per_cta = 1;
+      ph.sub_bytes = per_cta * 16 * 128;
+      while (ph.ks < 8 && ph.ks * 2 <= ph.nchunks && ph.ks * 2 * ph.sub_bytes <= 32768 && ph.ks * 2 * ph.a_boxes <= 8) ph.ks *= 2;
+    }
     ph.nstage_chunks = (ph.nchunks + ph.ks - 1) / ph.ks;
-    wmax = ph.ks * kSubBytes > wmax ? ph.ks * kSubBytes : wmax;
+    wmax = ph.ks * ph.sub_bytes > wmax ? ph.ks * ph.sub_bytes : wmax;
     const int a = ph.ks * ph.a_boxes * nb * 128;
     amax = a > amax ? a : amax;
   }

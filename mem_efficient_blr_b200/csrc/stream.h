@@ -34,7 +34,9 @@ struct alignas(64) PhaseDesc {
   int tiles_per_g;  // work units per block: ceil(M / unit_rows)
   int ntiles;       // G * tiles_per_g
   int nchunks;      // K-chunks per unit: 128 B of k per row (K-major) or 64 k-rows (M-major)
-  int ks;           // K-chunks per ring stage (1, 2 or 4)
+  int ks;           // K-chunks per ring stage (1, 2, 4 or 8)
+  int sub_bytes;    // distance between the K-chunks of a stage: the weight bytes of one chunk of the largest batch
+                    // a CTA gets in this phase (kSubBytes for a full batch of 128 rows)
   int nstage_chunks;  // ceil(nchunks / ks): ring stages per batch
   int a_boxes;      // 64-wide activation boxes per chunk: 1 (16-bit), 2 (int8), 4 (int4)
   int out_f32;      // 1: out is fp32, 0: out has the activation dtype
@@ -60,7 +62,7 @@ struct alignas(64) StreamParams {
   void* z16;      // [b][N][R] 16-bit scratch (phase 1 activations when mix)
   unsigned* counters;  // [0],[1] grid barriers, [2] exit count, [3] status (0 ok)
   int stage_bytes;
-  int w_bytes;    // weight part of a stage: max over phases of ks * kSubBytes
+  int w_bytes;    // weight part of a stage: max over phases of ks * sub_bytes
   int nstages;
   int mix_bytes;  // shared memory for the coupling's copy of y (0 when mix == 0)
   unsigned long long* timeline;  // optional: 16 time stamps per CTA (profiling aid), else nullptr

@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
             if (lane == 0) {
               mbar_arrive_expect_tx(bar, ksub * b.nt * 16 * 128);
               for (int sub = 0; sub < ksub; ++sub)
-                tma_load_3d(dst + sub * kSubBytes, &ph.tmW[b.nt - 1], k0 + sub * kstep, b.mt0 * 16, b.g, bar);
+                tma_load_3d(dst + sub * ph.sub_bytes, &ph.tmW[b.nt - 1], k0 + sub * kstep, b.mt0 * 16, b.g, bar);
             }
           } else {
             if (lane == 0) mbar_arrive_expect_tx(bar, ksub * b.nt * kTileBytes);
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
       tile_range(ph, t, t_hi);
       Batch b;
       const int nchunks = ph.nstage_chunks, wbits = ph.wbits, kmajor = ph.kmajor, ksub = ph.ks;
-      const uint32_t a_sub = ph.a_boxes * kABoxBytes;
+      const uint32_t a_sub = ph.a_boxes * kABoxBytes, sub_bytes = ph.sub_bytes;
       while (next_batch(ph, t, t_hi, b)) {
         float acc[4][NT][4];  // four independent accumulation chains (one per k16 step / window of a chunk)
 #pragma unroll
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
           }
           if (active) {
             uint32_t sW = smem_base + s * stage_bytes, sA = sW + p.w_bytes;
-            for (int sub = 0; sub < ksub; ++sub, sW += kSubBytes, sA += a_sub) {
+            for (int sub = 0; sub < ksub; ++sub, sW += sub_bytes, sA += a_sub) {
               GroupScales gs;
               if constexpr (GS) gs = load_scale_groups(srow, srow8, (kc * ksub + sub) * (wbits == 8 ? 1 : 2), ngroups, wbits);
               if (wbits == 16) {
