@@ -140,7 +140,8 @@ int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
  * index in the low nibble; weight = q * scale.  `group` = 0: one scale per output channel, u_scale fp16 (b,Q),
  * v_scale fp16 (b,R).  `group` = 128: one scale per 128 consecutive contraction indices, u_scale fp16
  * (b,Q,R/128), v_scale fp16 (b,R,P/128); P and R must then be multiples of 128.  Other widths are rejected
- * with BLR_ERR_UNSUPPORTED.  Up to 16 tokens per call. */
+ * with BLR_ERR_UNSUPPORTED.  Up to 16 tokens per call (BLR_ERR_UNSUPPORTED above: dequantise with
+ * blr_dequantize_sym and call blr_blast, as the Python layer does). */
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                  const void* Uq, const void* u_scale, const void* Vq, const void* v_scale,
                  const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
@@ -197,6 +198,13 @@ int blr_dense_f32(const float* x, int64_t ldx, int64_t n_tokens,
  * row of its own and the layouts coincide.  No reference counterpart. */
 int blr_quantize_sym(const void* w, int dtype, int64_t rows, int64_t K, int bits,
                      void* q, void* scale, void* stream);
+
+/* Inverse of blr_quantize_sym: w (rows, K) in the 16-bit `dtype` = q * scale, rounded to that type.
+ * `group` = 0 for one scale per row, else the number of consecutive contraction indices per scale.
+ * K and the group width must be multiples of 16.  Used for quantised layers on more than 16 tokens, where the
+ * tensor-core pipeline takes 16-bit factors.  No reference counterpart. */
+int blr_dequantize_sym(const void* q, const void* scale, int64_t rows, int64_t K, int bits, int64_t group,
+                       int dtype, void* w, void* stream);
 
 #ifdef __cplusplus
 }

@@ -48,6 +48,7 @@ SIGNATURES = {
     "blr_low_rank_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _int, _int, _int, _int, _vp, _i64, _vp, _vp]),
     "blr_dense_f32": (_int, [_vp, _i64, _i64, _vp, _int, _int, _int, _vp, _i64, _vp]),
     "blr_quantize_sym": (_int, [_vp, _int, _i64, _i64, _int, _vp, _vp, _vp]),
+    "blr_dequantize_sym": (_int, [_vp, _vp, _i64, _i64, _int, _i64, _int, _vp, _vp]),
 }
 
 _lib = None

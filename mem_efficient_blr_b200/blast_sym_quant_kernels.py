@@ -48,7 +48,8 @@ def quantize_blast_factors(U: torch.Tensor, Vt: torch.Tensor, bits: int, group: 
 def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     """Weight-quantised BLAST. Uq (b,Q,R) int8 or (b,Q,R/2) uint8; Vq (b,R,P) int8 or (b,R,P/2) uint8;
     scales fp16 (b,Q) / (b,R), or (b,Q,R/group) / (b,R,P/group) with per-group scales;
-    S (b_out, b_in, R) in x's dtype."""
+    S (b_out, b_in, R) in x's dtype.  Any token count: up to 16 tokens the factors stay quantised all the way to
+    the MMA, above that they are widened to x's dtype for the call."""
     assert bits in (8, 4)
     per = 1 if bits == 8 else 2
     b, q, r, p = u_scale.size(0), u_scale.size(1), v_scale.size(1), Vq.size(-1) * per
@@ -58,5 +59,13 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
         assert u_scale.dim() == 2 and v_scale.dim() == 2, "one scale per output channel expected (group = 0)"
     else:
         assert tuple(u_scale.shape) == (b, q, r // group) and tuple(v_scale.shape) == (b, r, p // group)
-    out = ops.blast_wq(ops._flat2d(x), Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
+    x2 = ops._flat2d(x)
+    if x2.shape[0] > 16:
+        # more than 16 tokens run on the tensor-core pipeline, which takes 16-bit factors: widen them for this call
+        # (about 10 us at the headline shape against 120 us of GEMMs; nothing is cached, the layer keeps its footprint)
+        U = ops.dequantize_sym(Uq, u_scale, bits, group, x.dtype)
+        Vt = ops.dequantize_sym(Vq, v_scale, bits, group, x.dtype)
+        out = ops.blast(x2, U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, L.FLAG_NONE)
+    else:
+        out = ops.blast_wq(x2, Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
     return ops._like_input(out, x)

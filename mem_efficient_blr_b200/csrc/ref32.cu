@@ -118,6 +118,44 @@ __global__ void quantize_kernel(const T* __restrict__ w, long long K, int bits, 
   }
 }
 
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Inverse of the quantiser: 16 consecutive weights per thread, w = q * scale rounded to the 16-bit type.
+// `group` consecutive weights share a scale (the row length for per-channel scales); it is a multiple of 16.
+template <typename T>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ q, const __half* __restrict__ scale,
+                                                         long long total, long long group, int bits, T* __restrict__ out) {
+  const long long e0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+  if (e0 >= total) return;
+  const float sc = __half2float(scale[e0 / group]);
+  float v[16];
+  if (bits == 8) {
+    const uint4 w = *reinterpret_cast<const uint4*>(q + e0);
+    const int8_t* b = reinterpret_cast<const int8_t*>(&w);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = (float)b[k] * sc;
+  } else {
+    const uint2 w = *reinterpret_cast<const uint2*>(q + e0 / 2);
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(&w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int lo = b[k] & 0xF, hi = b[k] >> 4;
+      v[2 * k] = (float)(lo > 7 ? lo - 16 : lo) * sc;
+      v[2 * k + 1] = (float)(hi > 7 ? hi - 16 : hi) * sc;
+    }
+  }
+  __align__(16) T o[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) o[k] = from_f32<T>(v[k]);
+  reinterpret_cast<uint4*>(out + e0)[0] = reinterpret_cast<const uint4*>(o)[0];
+  reinterpret_cast<uint4*>(out + e0)[1] = reinterpret_cast<const uint4*>(o)[1];
+}
+
 }  // namespace blr
 
 using namespace blr;
@@ -184,6 +222,32 @@ int blr_quantize_sym(const void* w, int dtype, int64_t rows, int64_t K, int bits
     quantize_kernel<__half><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __half*>(w), K, bits,
                                                            static_cast<int8_t*>(q), static_cast<uint8_t*>(q),
                                                            static_cast<__half*>(scale));
+  else
+    BLR_REQUIRE(false, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  BLR_CUDA_OK(cudaGetLastError());
+  return BLR_OK;
+}
+
+int blr_dequantize_sym(const void* q, const void* scale, int64_t rows, int64_t K, int bits, int64_t group, int dtype,
+                       void* w, void* stream) {
+  BLR_REQUIRE(q && scale && w, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(bits == 8 || bits == 4, BLR_ERR_ARG, "bits must be 8 or 4");
+  const int64_t g = group == 0 ? K : group;
+  BLR_REQUIRE(rows >= 1 && K >= 16 && K % 16 == 0 && g % 16 == 0 && K % g == 0, BLR_ERR_SHAPE,
+              "row length %lld and scale group %lld must be multiples of 16, the group a divisor of the row", (long long)K,
+              (long long)g);
+  BLR_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, BLR_ERR_ALIGN,
+              "q and w must be 16-byte aligned");
+  const long long total = rows * K;
+  const long long blocks = (total / 16 + 255) / 256;
+  BLR_REQUIRE(blocks < (1ll << 31), BLR_ERR_SHAPE, "too many weights");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == BLR_DTYPE_BF16)
+    dequantize_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(q), static_cast<const __half*>(scale),
+                                                                      total, g, bits, static_cast<__nv_bfloat16*>(w));
+  else if (dtype == BLR_DTYPE_F16)
+    dequantize_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint8_t*>(q), static_cast<const __half*>(scale), total,
+                                                               g, bits, static_cast<__half*>(w));
   else
     BLR_REQUIRE(false, BLR_ERR_ARG, "unknown dtype %d", dtype);
   BLR_CUDA_OK(cudaGetLastError());

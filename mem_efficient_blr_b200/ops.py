@@ -298,3 +298,15 @@ def quantize_sym(w: torch.Tensor, bits: int, group: int = 0) -> Tuple[torch.Tens
     L.check(L.load().blr_quantize_sym(w.data_ptr(), L.dtype_code(w.dtype), rows, g, bits, q.data_ptr(),
                                       scale.data_ptr(), L.stream_ptr(w.device)))
     return q, scale
+
+
+def dequantize_sym(q: torch.Tensor, scale: torch.Tensor, bits: int, group: int, dtype: torch.dtype) -> torch.Tensor:
+    """16-bit weights q * scale for factors made by quantize_sym (same shapes and group convention)."""
+    _need_cuda(q, scale)
+    assert q.is_contiguous() and scale.is_contiguous() and bits in (8, 4)
+    K = q.shape[-1] * (1 if bits == 8 else 2)
+    rows = q.numel() // q.shape[-1]
+    w = torch.empty((*q.shape[:-1], K), dtype=dtype, device=q.device)
+    L.check(L.load().blr_dequantize_sym(q.data_ptr(), scale.data_ptr(), rows, K, bits, group, L.dtype_code(dtype),
+                                        w.data_ptr(), L.stream_ptr(q.device)))
+    return w

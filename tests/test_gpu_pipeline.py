@@ -90,11 +90,14 @@ def test_blast_act_int8_prefill(K):
     assert _err(K.bq.triton_blast_bmm_int8_fp16(x.to(DEV), Ub, Vb, Sb), ref) < 3e-2
 
 
-def test_quantised_blast_rejects_more_than_16_tokens(K):
+def test_quantised_entry_point_rejects_more_than_16_tokens(K):
+    """The C entry point keeps quantised factors all the way to the MMA and takes up to 16 tokens; the Python
+    operator widens the factors above that (test_weight_quantised_blast_above_16_tokens)."""
+    from mem_efficient_blr_b200 import ops
     x, U, Vt, S = orc.make_blast_inputs(32, 512, 768, 4, 128, torch.float16, seed=2)
     Uq, us, Vq, vs = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), 8)
     with pytest.raises(RuntimeError, match="quantised factors"):
-        K.bq.blast_wq(x.to(DEV), Uq, us, Vq, vs, S.to(DEV), 8)
+        ops.blast_wq(x.to(DEV)[0], Uq, us, Vq, vs, S.to(DEV), 4 * 128, 128, 1, 8, 0, 4, 128, 192, 128)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -145,3 +148,24 @@ def test_linearity_at_full_size(K):
     rhs = 0.5 * f(x1) + f(x2)
     torch.cuda.synchronize()
     assert orc.rel_fro(lhs.cpu(), rhs.cpu()) < 5e-3
+
+
+@pytest.mark.parametrize("bits,group", [(8, 0), (4, 0), (8, 128), (4, 128)])
+def test_weight_quantised_blast_above_16_tokens(K, bits, group):
+    """Quantised layers on prefill sizes: factors widened to 16 bits for the call, then the tensor-core pipeline.
+    The widening rounds q * scale to the 16-bit type, which the oracle (fp32 dequantisation) does not; the bound
+    is the same 1e-2."""
+    N, I, O, b, R = 197, 4096, 11008, 16, 1024
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=bits + group)
+    Uq, us = orc.quantize_sym(U, bits, group)
+    Vq, vs = orc.quantize_sym(Vt, bits, group)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits, group)
+    import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
+    from mem_efficient_blr_b200 import ops
+    # the widening itself is exact up to the rounding to fp16
+    Ud = ops.dequantize_sym(Uq.to(DEV), us.to(DEV), bits, group, torch.float16)
+    want = orc.dequantize_sym(Uq, us, bits, group).half()
+    assert torch.equal(Ud.cpu(), want)
+    got = bq.blast_wq(x.to(DEV), Uq.to(DEV), us.to(DEV), Vq.to(DEV), vs.to(DEV), S.to(DEV), bits, group)
+    assert got.shape == ref.shape
+    assert _err(got, ref) < TOL
