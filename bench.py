@@ -419,18 +419,25 @@ def run_ours(args):
         context["llama7b_blast_linears_decode_int8"] = linear_chain(8)
         torch.cuda.empty_cache()
 
-    # ---- end to end through the public Python operator, host buffers in and out every launch
+    # ---- end to end through the public host-buffer operator: x in pinned host memory, result back in pinned host
+    # memory, every launch (one library call enqueues copy-in, kernel and copy-out; its copy streams let consecutive
+    # calls overlap).  The step ends when the last result has arrived in host memory.
     def e2e_step():
         for bits, n in POINTS:
             for q in reps[bits]:
-                xd = xs_host[n].to(dev, non_blocking=True)
-                y = bq.blast_wq(xd, q[0], q[1], q[2], q[3], Sd, bits)
-                outs_host[n].copy_(y, non_blocking=True)
+                bq.blast_wq_host(xs_host[n], q[0], q[1], q[2], q[3], Sd, bits, out=outs_host[n])
+        bq.host_flush(dev)
 
     e2e_steps = max(2, min(args.steps, 5))
     for _ in range(2):
         e2e_step()
     barrier()
+    # the host path must deliver what the device path computes (last call of a step: int4, 16 tokens, last replica)
+    q = reps[4][-1]
+    want = bq.blast_wq(xs[16], q[0], q[1], q[2], q[3], Sd, 4).float().cpu()
+    err = float((outs_host[16].float() - want).norm() / want.norm())
+    if not err < 1e-3:
+        raise SystemExit(f"host-buffer path disagrees with the device path: relative error {err}")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):

@@ -148,6 +148,31 @@ int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                  int bits, int group, int b, int P, int Q, int R,
                  void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
 
+/* Host-buffer forms of blr_blast and blr_blast_wq: x_host (N, ldx) and out_host (N, ldo) are host memory (pinned
+ * memory makes the copies asynchronous), the factors are device memory.  The call enqueues the copy of x, the
+ * kernels and the copy of the result and returns.  The copies run on two streams the library keeps per (device,
+ * `stream`), ordered against `stream` with events, and `staging` is used as a ring of four slots, so that
+ * consecutive calls overlap: copy-in of the next call and copy-out of the previous one run beside the kernel.
+ * out_host is valid after blr_host_flush(stream) has been called and `stream` has been synchronised.
+ * `staging` is caller-owned device memory of blr_host_staging_bytes(n_tokens, b*P, b*Q) bytes, 256-byte aligned,
+ * used with one stream like the workspace and, from its first use on, always passed with the same size (the
+ * slots are cut from that size); size it for the largest call.  No reference counterpart (the reference's operators take device tensors). */
+size_t blr_host_staging_bytes(int64_t n_tokens, int64_t in_features, int64_t out_features);
+/* Makes `stream` wait for every copy-out that host-buffer calls on it have enqueued so far. */
+int blr_host_flush(void* stream);
+int blr_blast_host(const void* x_host, int64_t ldx, int64_t n_tokens, int dtype,
+                   const void* U, int u_layout, const void* V, int v_layout,
+                   const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                   int b, int P, int Q, int R, int flags,
+                   void* out_host, int64_t ldo, void* staging, size_t staging_bytes,
+                   void* ws, size_t ws_bytes, void* stream);
+int blr_blast_wq_host(const void* x_host, int64_t ldx, int64_t n_tokens, int dtype,
+                      const void* Uq, const void* u_scale, const void* Vq, const void* v_scale,
+                      const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                      int bits, int group, int b, int P, int Q, int R,
+                      void* out_host, int64_t ldo, void* staging, size_t staging_bytes,
+                      void* ws, size_t ws_bytes, void* stream);
+
 /* Monarch: block-diagonal w1, permutation, block-diagonal w2.
  * Replaces torch_monarch_baseline (torch_funcs/monarch_funcs.py:4-45) and
  * triton_monarch_{right,right_ideal,right_left}_fp16 (triton_funcs/monarch_kernels.py:869-909,

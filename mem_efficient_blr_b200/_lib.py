@@ -47,6 +47,12 @@ SIGNATURES = {
                                _int, _int, _int, _int, _int, _vp, _i64, _vp, _vp]),
     "blr_low_rank_f32": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _int, _int, _int, _int, _vp, _i64, _vp, _vp]),
     "blr_dense_f32": (_int, [_vp, _i64, _i64, _vp, _int, _int, _int, _vp, _i64, _vp]),
+    "blr_host_staging_bytes": (_sz, [_i64, _i64, _i64]),
+    "blr_host_flush": (_int, [_vp]),
+    "blr_blast_host": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
+                              _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp, _sz, _vp]),
+    "blr_blast_wq_host": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                 _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp, _sz, _vp]),
     "blr_quantize_sym": (_int, [_vp, _int, _i64, _i64, _int, _vp, _vp, _vp]),
     "blr_dequantize_sym": (_int, [_vp, _vp, _i64, _i64, _int, _i64, _int, _vp, _vp]),
 }
@@ -110,6 +116,22 @@ def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
         check(load().blr_workspace_init(ws.data_ptr(), ws.numel(), stream))
         _workspaces[key] = ws
     return ws
+
+
+_stagings: dict = {}
+
+
+def staging(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Device buffer that the host-buffer entry points copy x into and the result out of; one per (device, stream)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    st = _stagings.get(key)
+    if st is None or st.numel() < nbytes:
+        if st is not None:
+            # the ring's slots are cut from the buffer's size: drain the copies in flight before it changes
+            torch.cuda.synchronize(device)
+        st = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _stagings[key] = st
+    return st
 
 
 def workspace_status(device: torch.device) -> None:

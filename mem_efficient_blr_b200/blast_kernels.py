@@ -128,6 +128,38 @@ def blast_output_blocks(x, U_local, Vt, S_local, flags=L.FLAG_NONE):
     return ops._like_input(out, x)
 
 
+def blast_torch_layout_host(x_host, U, Vt, S, out=None, flags=L.FLAG_NONE):
+    """blast_torch_layout for activations in host memory: x_host (N, b*P) 16-bit CPU tensor (pinned for asynchronous
+    copies), factors on the device.  One library call enqueues copy-in, the kernels and copy-out; the copies run on
+    streams of the library so that consecutive calls overlap.  Returns the (pinned) host tensor `out` (N, b*Q),
+    valid after host_flush() and a synchronisation of the current stream."""
+    assert not x_host.is_cuda and x_host.dim() == 2 and x_host.stride(1) == 1
+    dev = U.device
+    b, r, p = Vt.shape
+    b2, q, r2 = U.shape
+    n = x_host.size(0)
+    assert b == b2 and b != 1 and r2 == r and tuple(S.shape) == (b2, b, r) and x_host.size(1) == b * p
+    assert U.dtype == x_host.dtype and Vt.dtype == x_host.dtype and S.dtype == x_host.dtype
+    assert U.is_contiguous() and Vt.is_contiguous() and S.is_contiguous()
+    if out is None:
+        out = torch.empty((n, b * q), dtype=x_host.dtype, pin_memory=True)
+    assert not out.is_cuda and out.stride(1) == 1 and tuple(out.shape) == (n, b * q) and out.dtype == x_host.dtype
+    lib = L.load()
+    st = L.stream_ptr(dev)
+    ws = L.workspace(dev, st, lib.blr_workspace_bytes(n, b, r))
+    sg = L.staging(dev, st, lib.blr_host_staging_bytes(max(n, 16), b * p, b * q))
+    L.check(lib.blr_blast_host(x_host.data_ptr(), x_host.stride(0), n, L.dtype_code(x_host.dtype), U.data_ptr(), L.KMAJOR,
+                               Vt.data_ptr(), L.KMAJOR, S.data_ptr(), b * r, r, 1, b, p, q, r, flags, out.data_ptr(),
+                               out.stride(0), sg.data_ptr(), sg.numel(), ws.data_ptr(), ws.numel(), st))
+    return out
+
+
+def host_flush(device=None) -> None:
+    """Makes the current stream of `device` wait for the copy-outs of all host-buffer calls issued on it."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    L.check(L.load().blr_host_flush(L.stream_ptr(dev)))
+
+
 # The reference exposes its autotuner's winning configuration (blast_kernels.py:3068-3086) and pickles
 # it (layer.py:310-326).  Tile shapes here are fixed at build time, so there is nothing to report.
 def get_triton_blast_partial_fp16_config():

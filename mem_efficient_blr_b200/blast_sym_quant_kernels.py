@@ -69,3 +69,40 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     else:
         out = ops.blast_wq(x2, Uq, u_scale, Vq, v_scale, S, b * r, r, 1, bits, group, b, p, q, r)
     return ops._like_input(out, x)
+
+
+def blast_wq_host(x_host, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0, out=None):
+    """blast_wq for activations in host memory: x_host (N, b*P) 16-bit CPU tensor (pinned for asynchronous copies),
+    factors on the device.  One library call enqueues copy-in, the kernel and copy-out on the device's current
+    stream and two copy streams of the library, so that consecutive calls overlap their copies with each other's
+    kernels; returns the (pinned) host tensor `out` (N, b*Q), valid after host_flush() and a synchronisation of
+    the current stream.  Up to 16 tokens per call; larger batches go through blast_wq on device tensors."""
+    assert not x_host.is_cuda and x_host.dim() == 2 and x_host.stride(1) == 1 and bits in (8, 4)
+    dev = Uq.device
+    per = 1 if bits == 8 else 2
+    b, q, r, p = u_scale.size(0), u_scale.size(1), v_scale.size(1), Vq.size(-1) * per
+    n = x_host.size(0)
+    assert x_host.size(1) == b * p and S.size(0) == b and S.size(1) == b and S.size(2) == r
+    if n > 16:
+        y = blast_wq(x_host.to(dev, non_blocking=True), Uq, u_scale, Vq, v_scale, S, bits, group)
+        if out is None:
+            out = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+        return out.copy_(y, non_blocking=True)
+    if out is None:
+        out = torch.empty((n, b * q), dtype=x_host.dtype, pin_memory=True)
+    assert not out.is_cuda and out.stride(1) == 1 and tuple(out.shape) == (n, b * q) and out.dtype == x_host.dtype
+    lib = L.load()
+    st = L.stream_ptr(dev)
+    ws = L.workspace(dev, st, lib.blr_workspace_bytes(n, b, r))
+    sg = L.staging(dev, st, lib.blr_host_staging_bytes(16, b * p, b * q))  # one size for every token count
+    L.check(lib.blr_blast_wq_host(x_host.data_ptr(), x_host.stride(0), n, L.dtype_code(x_host.dtype), Uq.data_ptr(),
+                                  u_scale.data_ptr(), Vq.data_ptr(), v_scale.data_ptr(), S.data_ptr(), b * r, r, 1, bits,
+                                  group, b, p, q, r, out.data_ptr(), out.stride(0), sg.data_ptr(), sg.numel(),
+                                  ws.data_ptr(), ws.numel(), st))
+    return out
+
+
+def host_flush(device=None) -> None:
+    """Makes the current stream of `device` wait for the copy-outs of all blast_wq_host calls issued on it."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    L.check(L.load().blr_host_flush(L.stream_ptr(dev)))

@@ -3,6 +3,7 @@
 #include "../../include/blr_b200.h"
 
 #include <mutex>
+#include <unordered_map>
 
 #include "blast_cluster.h"
 #include "pipeline.h"
@@ -390,6 +391,137 @@ int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
   BLR_REQUIRE(u_scale && v_scale, BLR_ERR_ARG, "scale pointers must not be null");
   return blast_impl(x, ldx, n_tokens, dtype, Uq, BLR_W_KMAJOR, bits, u_scale, Vq, BLR_W_KMAJOR, bits, v_scale, group, S, s_i,
                     s_j, s_r, b, b, P, Q, R, BLR_FLAG_NONE, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------- host-buffer entry points
+// x and out live in host memory (pinned for truly asynchronous copies); the factors stay resident on the device.
+// A call enqueues copy-in, the kernels and copy-out and returns.  The copies run on two streams the library owns
+// per (device, caller stream), tied to the caller's stream with events, and the staging buffer is a ring of
+// kHostSlots slots: the copy-in of call k+1 and the copy-out of call k-1 overlap the kernel of call k.
+// out_host is valid once blr_host_flush has been enqueued on the caller's stream and that stream synchronised.
+static constexpr int kHostSlots = 4;
+
+struct HostPipe {
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[kHostSlots] = {}, ev_k[kHostSlots] = {}, ev_out[kHostSlots] = {};
+  bool used[kHostSlots] = {};
+  unsigned next = 0;
+};
+
+static int host_pipe(cudaStream_t user, HostPipe** out) {
+  static std::mutex mu;
+  static std::unordered_map<unsigned long long, HostPipe*> pipes;
+  int dev = 0;
+  BLR_CUDA_OK(cudaGetDevice(&dev));
+  const unsigned long long key = (unsigned long long)reinterpret_cast<uintptr_t>(user) * 64ull + (unsigned)dev;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = pipes.find(key);
+  if (it == pipes.end()) {
+    HostPipe* hp = new HostPipe();
+    BLR_CUDA_OK(cudaStreamCreateWithFlags(&hp->s_in, cudaStreamNonBlocking));
+    BLR_CUDA_OK(cudaStreamCreateWithFlags(&hp->s_out, cudaStreamNonBlocking));
+    for (int i = 0; i < kHostSlots; ++i) {
+      BLR_CUDA_OK(cudaEventCreateWithFlags(&hp->ev_in[i], cudaEventDisableTiming));
+      BLR_CUDA_OK(cudaEventCreateWithFlags(&hp->ev_k[i], cudaEventDisableTiming));
+      BLR_CUDA_OK(cudaEventCreateWithFlags(&hp->ev_out[i], cudaEventDisableTiming));
+    }
+    it = pipes.emplace(key, hp).first;
+  }
+  *out = it->second;
+  return BLR_OK;
+}
+
+struct HostCall {
+  HostPipe* hp;
+  int slot;
+  void *x_dev, *out_dev;
+};
+
+// Copy-in on the library's stream into the next ring slot; the caller's stream then waits for it and for the
+// copy-out that last used the slot.
+static int stage_in(const void* x_host, int64_t ldx, int64_t N, int64_t I, int64_t O, void* staging, size_t staging_bytes,
+                    cudaStream_t user, HostCall* hc) {
+  BLR_REQUIRE(x_host != nullptr && staging != nullptr, BLR_ERR_ARG, "x_host and staging must not be null");
+  const size_t need = blr_host_staging_bytes(N, I, O);
+  BLR_REQUIRE(staging_bytes >= need, BLR_ERR_WORKSPACE, "staging buffer of %zu bytes needed, got %zu", need, staging_bytes);
+  BLR_REQUIRE((reinterpret_cast<uintptr_t>(staging) & 255) == 0, BLR_ERR_ALIGN, "staging buffer must be 256-byte aligned");
+  BLR_REQUIRE(ldx >= I, BLR_ERR_SHAPE, "leading dimension shorter than a row");
+  int rc = host_pipe(user, &hc->hp);
+  if (rc) return rc;
+  HostPipe* hp = hc->hp;
+  const int slot = hc->slot = (int)(hp->next++ % kHostSlots);
+  // slots are cut from the buffer's own size, so calls of different sizes on one buffer agree on where they are
+  const size_t per = staging_bytes / kHostSlots / 256 * 256;
+  hc->x_dev = static_cast<uint8_t*>(staging) + per * slot;
+  hc->out_dev = static_cast<uint8_t*>(hc->x_dev) + align256((size_t)N * I * 2);
+  if (hp->used[slot]) {
+    BLR_CUDA_OK(cudaStreamWaitEvent(hp->s_in, hp->ev_k[slot], 0));   // the kernel that read this slot's x is done
+    BLR_CUDA_OK(cudaStreamWaitEvent(user, hp->ev_out[slot], 0));     // the copy-out of this slot's result is done
+  }
+  if (ldx == I) BLR_CUDA_OK(cudaMemcpyAsync(hc->x_dev, x_host, (size_t)N * I * 2, cudaMemcpyHostToDevice, hp->s_in));
+  else BLR_CUDA_OK(cudaMemcpy2DAsync(hc->x_dev, (size_t)I * 2, x_host, (size_t)ldx * 2, (size_t)I * 2, (size_t)N,
+                                     cudaMemcpyHostToDevice, hp->s_in));
+  BLR_CUDA_OK(cudaEventRecord(hp->ev_in[slot], hp->s_in));
+  BLR_CUDA_OK(cudaStreamWaitEvent(user, hp->ev_in[slot], 0));
+  return BLR_OK;
+}
+static int stage_out(void* out_host, int64_t ldo, int64_t N, int64_t O, cudaStream_t user, HostCall* hc) {
+  HostPipe* hp = hc->hp;
+  const int slot = hc->slot;
+  BLR_CUDA_OK(cudaEventRecord(hp->ev_k[slot], user));
+  BLR_CUDA_OK(cudaStreamWaitEvent(hp->s_out, hp->ev_k[slot], 0));
+  if (ldo == O) BLR_CUDA_OK(cudaMemcpyAsync(out_host, hc->out_dev, (size_t)N * O * 2, cudaMemcpyDeviceToHost, hp->s_out));
+  else BLR_CUDA_OK(cudaMemcpy2DAsync(out_host, (size_t)ldo * 2, hc->out_dev, (size_t)O * 2, (size_t)O * 2, (size_t)N,
+                                     cudaMemcpyDeviceToHost, hp->s_out));
+  BLR_CUDA_OK(cudaEventRecord(hp->ev_out[slot], hp->s_out));
+  hp->used[slot] = true;
+  return BLR_OK;
+}
+
+size_t blr_host_staging_bytes(int64_t n_tokens, int64_t in_features, int64_t out_features) {
+  if (n_tokens < 0 || in_features < 0 || out_features < 0) return 0;
+  return kHostSlots * (align256((size_t)n_tokens * in_features * 2) + align256((size_t)n_tokens * out_features * 2));
+}
+
+int blr_host_flush(void* stream) {
+  cudaStream_t user = static_cast<cudaStream_t>(stream);
+  HostPipe* hp;
+  int rc = host_pipe(user, &hp);
+  if (rc) return rc;
+  for (int i = 0; i < kHostSlots; ++i)
+    if (hp->used[i]) BLR_CUDA_OK(cudaStreamWaitEvent(user, hp->ev_out[i], 0));
+  return BLR_OK;
+}
+
+int blr_blast_host(const void* x_host, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
+                   int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int P, int Q, int R, int flags,
+                   void* out_host, int64_t ldo, void* staging, size_t staging_bytes, void* ws, size_t ws_bytes, void* stream) {
+  if (n_tokens == 0) return BLR_OK;
+  BLR_REQUIRE(out_host != nullptr && b >= 1 && P > 0 && Q > 0 && ldo >= (int64_t)b * Q, BLR_ERR_ARG, "bad output arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  HostCall hc;
+  int rc = stage_in(x_host, ldx, n_tokens, (int64_t)b * P, (int64_t)b * Q, staging, staging_bytes, st, &hc);
+  if (rc) return rc;
+  rc = blast_impl(hc.x_dev, (int64_t)b * P, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j,
+                  s_r, b, b, P, Q, R, flags, hc.out_dev, (int64_t)b * Q, ws, ws_bytes, st);
+  if (rc) return rc;
+  return stage_out(out_host, ldo, n_tokens, (int64_t)b * Q, st, &hc);
+}
+
+int blr_blast_wq_host(const void* x_host, int64_t ldx, int64_t n_tokens, int dtype, const void* Uq, const void* u_scale,
+                      const void* Vq, const void* v_scale, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int bits,
+                      int group, int b, int P, int Q, int R, void* out_host, int64_t ldo, void* staging, size_t staging_bytes,
+                      void* ws, size_t ws_bytes, void* stream) {
+  if (n_tokens == 0) return BLR_OK;
+  BLR_REQUIRE(out_host != nullptr && b >= 1 && P > 0 && Q > 0 && ldo >= (int64_t)b * Q, BLR_ERR_ARG, "bad output arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  HostCall hc;
+  int rc = stage_in(x_host, ldx, n_tokens, (int64_t)b * P, (int64_t)b * Q, staging, staging_bytes, st, &hc);
+  if (rc) return rc;
+  rc = blr_blast_wq(hc.x_dev, (int64_t)b * P, n_tokens, dtype, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R,
+                    hc.out_dev, (int64_t)b * Q, ws, ws_bytes, stream);
+  if (rc) return rc;
+  return stage_out(out_host, ldo, n_tokens, (int64_t)b * Q, st, &hc);
 }
 
 int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* w1, int w1_layout, int w1_cols,

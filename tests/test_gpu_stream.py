@@ -266,6 +266,50 @@ def test_empty_batches_return_empty_outputs(K):
                          128, 1, 4, 128, 192, 128, 0, None, 768, None, 0, None) == 0
 
 
+@pytest.mark.parametrize("bits", [8, 4])
+def test_host_buffer_entry_point(K, bits):
+    """x and out in pinned host memory, factors on the device: one call copies in, computes and copies out."""
+    N, I, O, b, R = 5, 4096, 11008, 16, 1024
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=40 + bits)
+    Uq, us = orc.quantize_sym(U, bits)
+    Vq, vs = orc.quantize_sym(Vt, bits)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits)
+    xh = x.reshape(N, I).pin_memory()
+    dq = _cuda(Uq, us, Vq, vs, S)
+    out = K.bq.blast_wq_host(xh, *dq, bits)
+    K.bq.host_flush()
+    _sync_ok(K)
+    assert not out.is_cuda and out.shape == (N, O)
+    assert orc.rel_fro(out.float(), ref.reshape(N, O)) < TOL
+    # a strided host view (rows 2*I apart) and a caller-provided output
+    wide = torch.zeros(N, 2 * I, dtype=torch.float16).pin_memory()
+    wide[:, :I] = xh
+    out2 = torch.empty(N, O, dtype=torch.float16).pin_memory()
+    got = K.bq.blast_wq_host(wide[:, :I], *dq, bits, out=out2)
+    K.bq.host_flush()
+    _sync_ok(K)
+    # the slices' partial sums meet in fp32 atomics, whose order varies from run to run: equal up to the last bit
+    assert got is out2 and orc.rel_fro(out2.float(), out.float()) < 1e-3
+    # a burst of calls with changing token counts through the ring of staging slots
+    outs = [torch.empty(n, O, dtype=torch.float16).pin_memory() for n in (1, 5, 3, 5, 1, 2, 5, 4, 5)]
+    for o in outs:
+        K.bq.blast_wq_host(xh[: o.shape[0]], *dq, bits, out=o)
+    K.bq.host_flush()
+    _sync_ok(K)
+    for o in outs:
+        assert orc.rel_fro(o.float(), out[: o.shape[0]].float()) < 1e-3
+
+
+def test_host_buffer_entry_point_16_bit(K):
+    for N in (3, 40):  # streaming / cluster kernel, and the tensor-core pipeline
+        x, U, Vt, S = orc.make_blast_inputs(N, 768, 3072, 4, 192, torch.bfloat16, seed=N)
+        ref, _, _ = orc.blast(x, U, Vt, S)
+        out = K.bk.blast_torch_layout_host(x.reshape(N, 768).pin_memory(), *_cuda(U, Vt, S))
+        K.bk.host_flush()
+        _sync_ok(K)
+        assert orc.rel_fro(out.float(), ref.reshape(N, 3072)) < TOL
+
+
 def test_repeated_calls_reuse_the_workspace(K):
     """The grid-barrier words re-arm themselves: 50 back-to-back calls give the same answer."""
     x, U, Vt, S = orc.make_blast_inputs(16, 1024, 1024, 4, 256, torch.float16, seed=2)
