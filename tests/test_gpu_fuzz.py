@@ -90,3 +90,29 @@ def test_low_rank_and_monarch_random_shapes(case):
     got = mk.monarch_torch_layout(x.to(DEV), w1_t.to(DEV), w2_t.to(DEV))
     torch.cuda.synchronize()
     assert orc.rel_fro(got.float().cpu(), ref) < TOL, (case, rank)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_grouped_scales_and_block_slices_random(seed):
+    import mem_efficient_blr_b200.blast_kernels as bk
+    import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
+    rng = random.Random(100 + seed)
+    b = rng.choice([2, 4, 8, 16])
+    P, R = 128 * rng.randrange(1, 3), 128 * rng.randrange(1, 5)
+    Q = rng.randrange(8, 200, 8)
+    N = rng.choice([1, 6, 8, 10, 16])
+    bits = rng.choice([8, 4])
+    x, U, Vt, S = orc.make_blast_inputs(N, b * P, b * Q, b, R, torch.float16, seed=seed)
+    Uq, us = orc.quantize_sym(U, bits, 128)
+    Vq, vs = orc.quantize_sym(Vt, bits, 128)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits, 128)
+    got = bq.blast_wq(x.to(DEV), Uq.to(DEV), us.to(DEV), Vq.to(DEV), vs.to(DEV), S.to(DEV), bits, 128)
+    torch.cuda.synchronize()
+    assert orc.rel_fro(got.float().cpu(), ref) < TOL, (N, b, P, Q, R, bits)
+    # a slice of the output blocks (what one rank of a block-sharded layer computes)
+    lo = rng.randrange(0, b)
+    hi = rng.randrange(lo + 1, b + 1)
+    full, _, _ = orc.blast(x, U, Vt, S)
+    got = bk.blast_output_blocks(x.to(DEV), U[lo:hi].contiguous().to(DEV), Vt.to(DEV), S[lo:hi].contiguous().to(DEV))
+    torch.cuda.synchronize()
+    assert orc.rel_fro(got.float().cpu(), full[..., lo * Q:hi * Q]) < TOL, (N, b, lo, hi)
