@@ -13,7 +13,7 @@
 
 namespace blr {
 
-template <bool BF16, int NT, bool GS>
+template <bool BF16, int NT, bool GS, bool MON>
 __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(const __grid_constant__ ClusterParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -37,6 +37,10 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
   const int blk = blockIdx.x, sl = blockIdx.y, part = blockIdx.z, nb = p.b;
   const int q_lo = part * p.q_part, q_hi = min(p.Q, q_lo + p.q_part);
   const int r_begin = sl * rs, r_len = min(rs, p.R - r_begin);
+  // first phase: weight/activation block and row range of this CTA (BLAST: its own block, the slice's ranks;
+  // Monarch: a share of the rows of one of the first-stage blocks that feed the slice)
+  const int blk0 = MON ? sl * p.mblk + blk / p.cpb : blk;
+  const int r_begin0 = MON ? (blk % p.cpb) * rs : r_begin, r_len0 = MON ? rs : r_len;
   const PhaseDesc& ph0 = p.ph[0];
   const PhaseDesc& ph1 = p.ph[1];
 
@@ -45,7 +49,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
   if (threadIdx.x == 0 && tl) { tl[0] = globaltimer_ns(); tl[15] = (unsigned long long)clock64(); }
   if (warp == kConsumerWarps) {
     // descriptors this CTA will use: one per batch height for k-contiguous weights (full batches and the last one)
-    const int rows0 = min(rs, p.R - blockIdx.y * rs), rows1 = min(p.Q, (int)(blockIdx.z + 1) * p.q_part) - (int)blockIdx.z * p.q_part;
+    const int rows0 = r_len0, rows1 = min(p.Q, (int)(blockIdx.z + 1) * p.q_part) - (int)blockIdx.z * p.q_part;
     const int hf0 = (min(rows0, kBatchRows) + 15) >> 4, hl0 = (((rows0 - 1) % kBatchRows) + 16) >> 4;
     const int hf1 = (min(rows1, kBatchRows) + 15) >> 4, hl1 = (((rows1 - 1) % kBatchRows) + 16) >> 4;
     if (lane == 0) tma_prefetch_desc(&ph0.tmW[ph0.kmajor ? hf0 - 1 : 0]);
@@ -82,7 +86,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
       const int kstep = ph.kmajor ? (ph.wbits == 16 ? 64 : 128) : 64;             // coordinate units per chunk
       // K range: whole P in phase 0, the slice in phase 1 (coordinates are elements, or bytes for int8 / int4)
       const int k_base = phs == 0 ? 0 : (ph.kmajor && ph.wbits == 4 ? r_begin / 2 : r_begin);
-      const int rows = min(kBatchRows, row_hi - r0);
+      const int rows = min(kBatchRows, row_hi - r0), wblk = phs == 0 ? blk0 : blk;
       const int h = (rows + 15) >> 4, tiles = (rows + 31) >> 5;
       const uint32_t dst = smem_base + slot * stage_bytes, bar = full0 + 8 * slot;
       const int k0 = k_base + c * ksub * kstep;
@@ -92,19 +96,19 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
           if (lane == 0) {
             mbar_arrive_expect_tx(bar, ksub * h * 16 * 128 + a_bytes);
             for (int sub = 0; sub < ksub; ++sub)
-              tma_load_3d(dst + sub * kSubBytes, &ph.tmW[h - 1], k0 + sub * kstep, r0, blk, bar);
+              tma_load_3d(dst + sub * kSubBytes, &ph.tmW[h - 1], k0 + sub * kstep, r0, wblk, bar);
           }
         } else {
           if (lane == 0) mbar_arrive_expect_tx(bar, ksub * tiles * kTileBytes + a_bytes);
           __syncwarp();
           if (lane < ksub * 4 && (lane & 3) < tiles)
             tma_load_3d(dst + (lane >> 2) * kSubBytes + (lane & 3) * kTileBytes, &ph.tmW[0], r0 + (lane & 3) * 32,
-                        k0 + (lane >> 2) * kstep, blk, bar);
+                        k0 + (lane >> 2) * kstep, wblk, bar);
         }
       }
       if (do_x && phs == 0 && lane == 0) {
         const int nbox = ksub * ph.a_boxes, ka = c * nbox * 64;
-        for (int bx = 0; bx < nbox; ++bx) tma_load_3d(dst + p.w_bytes + bx * kABoxBytes, &ph.tmA, ka + bx * 64, 0, blk, bar);
+        for (int bx = 0; bx < nbox; ++bx) tma_load_3d(dst + p.w_bytes + bx * kABoxBytes, &ph.tmA, ka + bx * 64, 0, blk0, bar);
       }
     };
     // The weights do not depend on the kernel before this one in the stream, the activations do: fill the
@@ -113,8 +117,8 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
     int pre = 0;
     for (int pass = 0; pass < 2; ++pass) {
       pre = 0;
-      for (int r0 = r_begin; r0 < r_begin + r_len && pre < (int)NST; r0 += kBatchRows)
-        for (int c = 0; c < nstage0 && pre < (int)NST; ++c, ++pre) issue(0, r0, r_begin + r_len, c, pre, pass == 0, pass == 1);
+      for (int r0 = r_begin0; r0 < r_begin0 + r_len0 && pre < (int)NST; r0 += kBatchRows)
+        for (int c = 0; c < nstage0 && pre < (int)NST; ++c, ++pre) issue(0, r0, r_begin0 + r_len0, c, pre, pass == 0, pass == 1);
       if (pass == 0) {
         if (lane == 0) BLR_STAMP(12);
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
     int skip = pre;
     for (int phs = 0; phs < 2 && ok; ++phs) {
       const int ksub = phs == 0 ? p.ks0 : p.ks1;
-      const int row_lo = phs == 0 ? r_begin : q_lo, row_hi = phs == 0 ? r_begin + r_len : q_hi;
+      const int row_lo = phs == 0 ? r_begin0 : q_lo, row_hi = phs == 0 ? r_begin0 + r_len0 : q_hi;
       const int nstage = phs == 0 ? nstage0 : (p.nchunks1 + ksub - 1) / ksub;
       for (int r0 = row_lo; r0 < row_hi && ok; r0 += kBatchRows) {
         for (int c = 0; c < nstage; ++c) {
@@ -158,7 +162,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
     {
       const uint16_t* S = reinterpret_cast<const uint16_t*>(p.S);
       const int nv = rs >> 3;
-      for (int e = ctid; e < nb * nv; e += kConsumerWarps * 32) {
+      for (int e = ctid; e < (MON ? 0 : nb * nv); e += kConsumerWarps * 32) {  // Monarch has no factors
         const int j = e / nv, v = e - j * nv, r = r_begin + v * 8;
         const uint32_t dst = smem_u32(sbuf) + (j * rs + v * 8) * 2;
         if (S == nullptr) {  // no coupling factors: all ones (a plain sum over the in-blocks), zero past R
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
     for (int phs = 0; phs < 2; ++phs) {
       const PhaseDesc& ph = p.ph[phs];
       const int ksub = phs == 0 ? p.ks0 : p.ks1, wbits = ph.wbits, kmajor = ph.kmajor;
-      const int row_lo = phs == 0 ? r_begin : q_lo, row_hi = phs == 0 ? r_begin + r_len : q_hi;
+      const int row_lo = phs == 0 ? r_begin0 : q_lo, row_hi = phs == 0 ? r_begin0 + r_len0 : q_hi;
       const int nstage = phs == 0 ? (ph.nchunks + ksub - 1) / ksub : (p.nchunks1 + ksub - 1) / ksub;
       const uint32_t a_sub = ph.a_boxes * kABoxBytes;
       for (int r0 = row_lo; r0 < row_hi; r0 += kBatchRows) {
@@ -193,7 +197,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int m = r0 + row0 + g + 8 * h;
-            if (m < row_hi) sc2[h] = __half2float(__ldg(ph.scale + (long long)blk * ph.M + m));
+            if (m < row_hi) sc2[h] = __half2float(__ldg(ph.scale + (long long)blk0 * ph.M + m));
           }
         }
         // grouped scales: rows of the scale table for this thread's two weight rows, first group of the K range
@@ -203,8 +207,9 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
         float tot[NT][4];
         if constexpr (GS) {
           const int m = r0 + row0 + g;
-          if (active && m < row_hi) srow = ph.scale + ((long long)blk * ph.M + m) * ngroups;
-          if (active && m + 8 < row_hi) srow8 = ph.scale + ((long long)blk * ph.M + m + 8) * ngroups;
+          const int sblk = phs == 0 ? blk0 : blk;
+          if (active && m < row_hi) srow = ph.scale + ((long long)sblk * ph.M + m) * ngroups;
+          if (active && m + 8 < row_hi) srow8 = ph.scale + ((long long)sblk * ph.M + m + 8) * ngroups;
 #pragma unroll
           for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -258,7 +263,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
                     float v = GS ? tot[n][2 * h + e]
                                  : (acc[0][n][2 * h + e] + acc[1][n][2 * h + e] + acc[2][n][2 * h + e] + acc[3][n][2 * h + e]) * sc;
                     if (p.round_y) v = round_clamp_i8(v);
-                    store16<BF16>(ybuf, (long long)(n * 8 + tq * 2 + e) * rs + (m - r_begin), v);
+                    store16<BF16>(ybuf, (long long)(n * 8 + tq * 2 + e) * rs + (m - r_begin0), v);
                   }
               } else {
                 // partial out over this slice: fp32 reduction into out32[blk*Q + m][token]
@@ -289,7 +294,20 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
         cp_async_wait_all();
         consumer_bar();  // sbuf complete for every thread
         if (ctid == 0) BLR_STAMP(3);
-        if (!*abort_flag) {
+        if (MON && !*abort_flag) {
+          // Monarch: the exchange is the permutation.  Element t of this CTA's slice of z_l is the first-stage output
+          // (block sl*mblk + t / per, column q); that column was computed by CTA (t / per)*cpb + q / rs as its local
+          // row q % rs.
+          const uint32_t ybase = smem_u32(ybuf);
+          for (int e = ctid; e < p.N * rs; e += kConsumerWarps * 32) {
+            const int n = e / rs, t = e - n * rs;
+            const int kk = t / p.per, jj = t - kk * p.per;
+            const int q = p.w1_grouped ? blk * p.per + jj : jj * nb + blk;
+            const int c = kk * p.cpb + q / rs, loc = q % rs;
+            const uint16_t v = ld_shared_cluster_u16(mapa_shared(ybase + (n * rs + loc) * 2, c));
+            *reinterpret_cast<uint16_t*>(zbuf + (t >> 6) * kABoxBytes + sw128(n, (t & 63) >> 3) + (t & 7) * 2) = v;
+          }
+        } else if (!*abort_flag) {
           // One item = 8 ranks of one token; two neighbouring lanes share an item, each gathers eight of the
           // (up to) sixteen in-blocks with all its remote loads in flight at once, then the halves are added.
           const int nv = rs >> 3, items = p.N * nv * 2;
@@ -384,7 +402,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int n = k * 4 + e;
-                if (n < p.N) store16<BF16>(p.out, (long long)n * p.ldo + (long long)blk * p.Q + q, e4[e] * sc[i]);
+                if (n < p.N) store16<BF16>(p.out, (long long)n * p.ldo + blk * p.out_blk + q * p.out_q, e4[e] * sc[i]);
               }
             }
           }
@@ -409,11 +427,11 @@ size_t cluster_smem_bytes(const ClusterParams& p, int np) {
   return (size_t)p.nstages * p.stage_bytes + (size_t)np * p.rs * 2 + 16 * p.rs * 2 + (p.rs / 64) * np * 128 + 40 * 8 + 1024;
 }
 
-template <bool BF16, int NT, bool GS>
+template <bool BF16, int NT, bool GS, bool MON>
 static int cluster_capacity_impl(int b, int smem_bytes) {
   DeviceInfo di;
   if (device_info(&di) != BLR_OK) return 0;
-  auto kern = blr_blast_cluster_kernel<BF16, NT, GS>;
+  auto kern = blr_blast_cluster_kernel<BF16, NT, GS, MON>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin) != cudaSuccess) return 0;
   if (b > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
     cudaGetLastError();
@@ -440,26 +458,28 @@ static int cluster_capacity_impl(int b, int smem_bytes) {
 
 // Resident clusters of b CTAs when every CTA takes smem_bytes of dynamic shared memory; the answer depends on
 // whether one or two CTAs fit an SM, so it is cached for those two classes of size.
-int cluster_capacity(int b, int is_bf16, int grouped, int n_tokens, int smem_bytes) {
-  static int cache[64][17][2][2][2];
-  static bool have[64][17][2][2][2] = {};
+int cluster_capacity(int b, int is_bf16, int variant, int n_tokens, int smem_bytes) {
+  static int cache[64][17][2][3][2];
+  static bool have[64][17][2][3][2] = {};
   DeviceInfo di;
   int dev = 0;
   if (device_info(&di) != BLR_OK || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || b < 1 || b > 16) return 0;
   if (n_tokens > kClusterMaxTokens) return 0;
-  const int bf = is_bf16 ? 1 : 0, gsi = grouped ? 1 : 0, two = smem_bytes <= kClusterHalfSmem ? 1 : 0;
+  // variant: 0 BLAST with per-channel scales or none, a scale-group width, kClusterVariantMonarch
+  const int bf = is_bf16 ? 1 : 0, gsi = variant == kClusterVariantMonarch ? 2 : (variant ? 1 : 0), two = smem_bytes <= kClusterHalfSmem ? 1 : 0;
   if (!have[dev][b][bf][gsi][two]) {
     const int sm = two ? kClusterHalfSmem : di.max_smem_optin - 1024;
     int n;
-    if (gsi) n = bf ? cluster_capacity_impl<true, 1, true>(b, sm) : cluster_capacity_impl<false, 1, true>(b, sm);
-    else n = bf ? cluster_capacity_impl<true, 1, false>(b, sm) : cluster_capacity_impl<false, 1, false>(b, sm);
+    if (gsi == 2) n = bf ? cluster_capacity_impl<true, 1, false, true>(b, sm) : cluster_capacity_impl<false, 1, false, true>(b, sm);
+    else if (gsi) n = bf ? cluster_capacity_impl<true, 1, true, false>(b, sm) : cluster_capacity_impl<false, 1, true, false>(b, sm);
+    else n = bf ? cluster_capacity_impl<true, 1, false, false>(b, sm) : cluster_capacity_impl<false, 1, false, false>(b, sm);
     cache[dev][b][bf][gsi][two] = n;
     have[dev][b][bf][gsi][two] = true;
   }
   return cache[dev][b][bf][gsi][two];
 }
 
-template <bool BF16, int NT, bool GS>
+template <bool BF16, int NT, bool GS, bool MON>
 static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
@@ -467,7 +487,7 @@ static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   const size_t smem = cluster_smem_bytes(p, NT * 8);
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
-  auto kern = blr_blast_cluster_kernel<BF16, NT, GS>;
+  auto kern = blr_blast_cluster_kernel<BF16, NT, GS, MON>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.b, p.nslices, p.qsplit);
   cfg.blockDim = dim3(kClusterThreads);
@@ -493,8 +513,9 @@ int launch_blast_cluster(const ClusterParams& p_in, int is_bf16, cudaStream_t st
   ClusterParams p = p_in;
   p.timeline = g_stream_timeline;
   BLR_REQUIRE(p.N >= 1 && p.N <= kClusterMaxTokens, BLR_ERR_UNSUPPORTED, "the cluster kernel takes 1..%d tokens", kClusterMaxTokens);
-  if (p.ph[0].group != 0) return is_bf16 ? launch_cluster_impl<true, 1, true>(p, stream) : launch_cluster_impl<false, 1, true>(p, stream);
-  return is_bf16 ? launch_cluster_impl<true, 1, false>(p, stream) : launch_cluster_impl<false, 1, false>(p, stream);
+  if (p.monarch) return is_bf16 ? launch_cluster_impl<true, 1, false, true>(p, stream) : launch_cluster_impl<false, 1, false, true>(p, stream);
+  if (p.ph[0].group != 0) return is_bf16 ? launch_cluster_impl<true, 1, true, false>(p, stream) : launch_cluster_impl<false, 1, true, false>(p, stream);
+  return is_bf16 ? launch_cluster_impl<true, 1, false, false>(p, stream) : launch_cluster_impl<false, 1, false, false>(p, stream);
 }
 
 }  // namespace blr

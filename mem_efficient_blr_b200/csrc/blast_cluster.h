@@ -27,6 +27,11 @@ struct alignas(64) ClusterParams {
   int ks0, ks1;        // K-chunks per ring stage in the two phases
   int nchunks1;        // chunks of the second phase inside one slice
   int round_y, round_z;
+  // Monarch (monarch = 1): no coupling factors; the first phase of slice sl covers the mblk first-stage blocks
+  // sl*mblk .. whose outputs feed the slice, cpb = b / mblk CTAs per block with rs rows each, and the exchange is
+  // the permutation: z_l[t] = pre[k][q], k = sl*mblk + t / per, q = (t % per)*b + l (w1_grouped: l*per + t % per)
+  int monarch, mblk, cpb, per, w1_grouped;
+  long long out_blk, out_q;  // output feature of (block, row) = block * out_blk + row * out_q
   long long s_i, s_j, s_r;
   const void* S;       // coupling factors, or nullptr for all ones
   void* out;
@@ -39,7 +44,9 @@ struct alignas(64) ClusterParams {
 };
 
 // Largest number of clusters of `b` CTAs that can be resident (0: this cluster shape cannot be launched).
-int cluster_capacity(int b, int is_bf16, int grouped, int n_tokens, int smem_bytes);
+// variant: 0 (BLAST, per-channel scales or none), kScaleGroup (BLAST with per-group scales), kClusterVariantMonarch
+static constexpr int kClusterVariantMonarch = -1;
+int cluster_capacity(int b, int is_bf16, int variant, int n_tokens, int smem_bytes);
 size_t cluster_smem_bytes(const ClusterParams& p, int np);
 int launch_blast_cluster(const ClusterParams& p, int is_bf16, cudaStream_t stream);
 

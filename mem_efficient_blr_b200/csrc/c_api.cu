@@ -218,6 +218,7 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   p.round_y = act8; p.round_z = act8;
   p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
   p.out = out; p.ldo = ldo; p.out32 = w.out32; p.counters = w.counters + 128; p.status = w.counters + 255;
+  p.out_blk = Q; p.out_q = 1;
   p.w_bytes = p.ks0 * kSubBytes;
   p.stage_bytes = p.w_bytes + p.ks0 * p.ph[0].a_boxes * np * 128;
   p.nstages = 2;
@@ -229,6 +230,65 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   if (forced && p.nslices * p.qsplit > cluster_capacity(b, bf, group, (int)N, budget)) return 1;
   rc = launch_blast_cluster(p, bf, stream);
   return rc;
+}
+
+// Monarch for 1..8 tokens on the cluster kernel: the first stage's blocks that feed a slice of the second stage's
+// contraction index are shared out over the cluster's CTAs, the permutation between the stages is the exchange
+// through distributed shared memory, and the second stage runs like BLAST's.  Returns 0 / 1 / < 0 like cluster_blast.
+static int cluster_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const void* w1, int w1_layout, int grouped,
+                           const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,
+                           int64_t ldo, const Workspace& w, cudaStream_t stream) {
+  const int np = 8;
+  if (g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;
+  if ((long long)b * Qs * np * 4 > kClusterOut32Bytes) return 1;
+  const int per = rank / b, bf = dtype == BLR_DTYPE_BF16;
+  DeviceInfo di;
+  int rc;
+  if ((rc = device_info(&di))) return rc;
+  ClusterParams p = {};
+  if ((rc = phase_weights(p.ph[0], dtype, w1, w1_layout, 16, b, rank, P))) return rc;
+  if ((rc = phase_acts(p.ph[0], dtype, x, P, N, b, ldx, P))) return rc;
+  if ((rc = phase_weights(p.ph[1], dtype, w2, w2_layout, 16, b, Qs, rank))) return rc;
+  // slice = mblk whole first-stage blocks (mblk divides b), rs = mblk * per ranks, a multiple of the 64-wide K-chunk
+  const int cap[2] = {cluster_capacity(b, bf, kClusterVariantMonarch, (int)N, di.max_smem_optin - 1024),
+                      cluster_capacity(b, bf, kClusterVariantMonarch, (int)N, kClusterHalfSmem)};
+  const int max_parts = Qs / kBatchRows < 1 ? 1 : (Qs / kBatchRows > kClusterMaxParts ? kClusterMaxParts : Qs / kBatchRows);
+  int best_m = 0, best_parts = 1, best_two = 0;
+  double best = -1.;
+  for (int m = 1; m <= b; ++m) {
+    if (b % m != 0) continue;
+    const int rs = m * per;
+    if (rs % 64 != 0 || rs > kClusterMaxSlice) continue;
+    const int nsl = b / m;
+    for (int two = 0; two < 2; ++two)
+      for (int parts = 1; parts <= max_parts && nsl * parts <= cap[two]; ++parts) {
+        const int qp = ((Qs + parts - 1) / parts + 15) / 16 * 16;
+        const double kb = ((double)rs * P + (double)qp * rs) * 2. / 1024.;
+        // beyond about 300 KB of weights per CTA the grid-wide kernel (all SMs, one barrier for Monarch) is as fast
+        if (kb > 300.) continue;
+        const double cost = kb * (two ? 1.0 : 0.8) + 20. * nsl;
+        if (best < 0. || cost < best) { best = cost; best_m = m; best_parts = parts; best_two = two; }
+      }
+  }
+  if (best < 0.) return 1;
+  const int rs = best_m * per;
+  p.N = (int)N; p.b = b; p.R = rank; p.Q = Qs; p.rs = rs; p.nslices = b / best_m;
+  p.qsplit = best_parts;
+  p.q_part = ((Qs + best_parts - 1) / best_parts + 15) / 16 * 16;
+  p.nchunks1 = rs / 64;
+  p.ks0 = p.ks1 = (p.nchunks1 % 2 == 0 && p.ph[0].nchunks % 2 == 0) ? 2 : 1;
+  p.monarch = 1; p.mblk = best_m; p.cpb = b / best_m; p.per = per; p.w1_grouped = grouped;
+  p.out_blk = interleaved ? 1 : Qs; p.out_q = interleaved ? b : 1;
+  p.out = out; p.ldo = ldo; p.out32 = w.out32; p.counters = w.counters + 128; p.status = w.counters + 255;
+  p.w_bytes = p.ks0 * kSubBytes;
+  p.stage_bytes = p.w_bytes + p.ks0 * p.ph[0].a_boxes * np * 128;
+  p.nstages = 2;
+  const int extras = (int)cluster_smem_bytes(p, np) - 2 * p.stage_bytes;
+  const int budget = best_two ? kClusterHalfSmem : di.max_smem_optin - 1024;
+  int nst = (budget - extras) / p.stage_bytes;
+  p.nstages = nst > 16 ? 16 : nst;
+  if (p.nstages < 2) return 1;
+  return launch_blast_cluster(p, bf, stream);
 }
 
 static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
@@ -544,6 +604,9 @@ int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const v
   const long long zplane = (long long)N * rank;
   const int grouped = w1_cols == BLR_MONARCH_COLS_GROUPED;
   if (N <= kStreamMaxTokens) {
+    rc = cluster_monarch(x, ldx, N, dtype, w1, w1_layout, grouped, w2, w2_layout, b, P, rank, Qs, out_order == BLR_OUT_INTERLEAVED,
+                         out, ldo, w, static_cast<cudaStream_t>(stream));
+    if (rc <= 0) return rc;  // 1: not applicable -> grid-wide streaming kernel
     StreamParams p = {};
     p.nphases = 2; p.mix = 0; p.counters = w.counters;
     if ((rc = phase_weights(p.ph[0], dtype, w1, w1_layout, 16, b, rank, P))) return rc;

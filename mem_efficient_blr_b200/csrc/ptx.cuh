@@ -114,6 +114,12 @@ __device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(cluster_addr) : "memory");
   return v;
 }
+// One 16-bit element of a peer CTA's shared memory.
+__device__ __forceinline__ uint16_t ld_shared_cluster_u16(uint32_t cluster_addr) {
+  uint16_t v;
+  asm volatile("ld.shared::cluster.u16 %0, [%1];" : "=h"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
