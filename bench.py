@@ -37,7 +37,7 @@ L2_BYTES = 126 * 2 ** 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from ncu captures (profiles/): the cluster kernel on
 # int8 factors and 1 token, the grid-wide streaming kernel on int8 factors and 16 tokens
 NCU_TRAFFIC = {"blr_blast_cluster_kernel": (16.474e6, "int8/N=1"), "blr_stream_kernel": (16.249e6, "int8/N=16")}
-CLUSTER_MAX_TOKENS = 8  # calls with up to 8 tokens run blr_blast_cluster_kernel, larger ones blr_stream_kernel
+CLUSTER_MAX_TOKENS = 16  # BLAST calls with up to 16 tokens run blr_blast_cluster_kernel on this layer's shape
 
 
 def algorithmic_bytes(bits: int, n: int) -> float:
@@ -190,7 +190,7 @@ def run_ours(args):
     def kernel_of(n):
         return "blr_blast_cluster_kernel" if n <= CLUSTER_MAX_TOKENS else "blr_stream_kernel"
 
-    KERNELS = ["blr_blast_cluster_kernel", "blr_stream_kernel"]
+    KERNELS = sorted({kernel_of(n) for _, n in POINTS})
 
     def launch_points(kernel=None):
         count = 0

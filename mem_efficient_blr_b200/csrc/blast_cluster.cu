@@ -13,8 +13,11 @@
 
 namespace blr {
 
-template <bool BF16, int NT, bool GS, bool MON>
+// XCH: how the cluster turns the first phase's outputs into the second phase's activations -
+// kXchPull (every CTA pulls all of every y_j), kXchSubslice (coupling by rank sub-slice), kXchMonarch (permutation).
+template <bool BF16, int NT, bool GS, int XCH>
 __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(const __grid_constant__ ClusterParams p) {
+  constexpr bool MON = XCH == kXchMonarch, SUB = XCH == kXchSubslice;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -22,14 +25,15 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
   constexpr uint32_t kABoxBytes = NP * 128;     // one [tokens][64 k] activation box
   const uint32_t NST = p.nstages, stage_bytes = p.stage_bytes;
   const int rs = p.rs;
-  // [ring][ybuf: NP x rs 16-bit][sbuf: b x rs 16-bit][zbuf: rs/64 boxes][barriers]
+  // [ring][ybuf: NP x rs 16-bit][sbuf: b x rs 16-bit][gbuf: NP x rs 16-bit][zbuf: rs/64 boxes][barriers]
   uint8_t* ybuf = smem + (size_t)NST * stage_bytes;
   uint8_t* sbuf = ybuf + NP * rs * 2;
-  uint8_t* zbuf = sbuf + 16 * rs * 2;
+  uint8_t* gbuf = sbuf + 16 * rs * 2;  // sub-slice coupling: y_j[token][this CTA's w ranks] of every in-block j
+  uint8_t* zbuf = gbuf + NP * rs * 2;
   uint64_t* bars = reinterpret_cast<uint64_t*>(zbuf + (rs / 64) * kABoxBytes);
   // full[16], empty[16], y_ready, read_done
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 16);
-  const uint32_t y_ready = smem_u32(bars + 32), read_done = smem_u32(bars + 33);
+  const uint32_t y_ready = smem_u32(bars + 32), read_done = smem_u32(bars + 33), z_ready = smem_u32(bars + 35);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 34);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
 
@@ -67,6 +71,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
     }
     mbar_init(y_ready, nb);
     mbar_init(read_done, nb);
+    mbar_init(z_ready, nb);
     mbar_init_fence();
   }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -162,7 +167,20 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
     {
       const uint16_t* S = reinterpret_cast<const uint16_t*>(p.S);
       const int nv = rs >> 3;
-      for (int e = ctid; e < (MON ? 0 : nb * nv); e += kConsumerWarps * 32) {  // Monarch has no factors
+      const int w = rs / nb, wv = w >> 3;  // sub-slice coupling: ranks and 8-rank vectors per CTA
+      for (int e = ctid; e < (SUB ? nb * nb * wv : 0); e += kConsumerWarps * 32) {
+        // sbuf[i][j][t] = S[i][j][r_begin + blk*w + t]: the factors of every (out, in) pair on this CTA's ranks
+        const int ij = e / wv, v = e - ij * wv, i = ij / nb, j = ij - i * nb, r = r_begin + blk * w + v * 8;
+        uint16_t* d = reinterpret_cast<uint16_t*>(sbuf) + ij * w + v * 8;
+        if (S == nullptr) {
+          for (int k = 0; k < 8; ++k) d[k] = r + k < p.R ? (BF16 ? (uint16_t)0x3F80 : (uint16_t)0x3C00) : (uint16_t)0;
+        } else if (s_vec && r + 8 <= p.R) {
+          cp_async16(smem_u32(d), S + i * p.s_i + j * p.s_j + r);
+        } else {
+          for (int k = 0; k < 8; ++k) d[k] = r + k < p.R ? S[i * p.s_i + j * p.s_j + (long long)(r + k) * p.s_r] : (uint16_t)0;
+        }
+      }
+      for (int e = ctid; e < (XCH == kXchPull ? nb * nv : 0); e += kConsumerWarps * 32) {  // Monarch has no factors
         const int j = e / nv, v = e - j * nv, r = r_begin + v * 8;
         const uint32_t dst = smem_u32(sbuf) + (j * rs + v * 8) * 2;
         if (S == nullptr) {  // no coupling factors: all ones (a plain sum over the in-blocks), zero past R
@@ -307,7 +325,47 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
             const uint16_t v = ld_shared_cluster_u16(mapa_shared(ybase + (n * rs + loc) * 2, c));
             *reinterpret_cast<uint16_t*>(zbuf + (t >> 6) * kABoxBytes + sw128(n, (t & 63) >> 3) + (t & 7) * 2) = v;
           }
-        } else if (!*abort_flag) {
+        } else if (SUB && !*abort_flag) {
+          // Coupling by rank sub-slice.  This CTA takes ranks [blk*w, (blk+1)*w) of the slice for every pair of blocks:
+          // (1) gather those ranks of every y_j, (2) z_i = sum_j S_ij . y_j on them for every out-block i,
+          // (3) write z_i's piece into CTA i's zbuf.  Traffic through distributed shared memory: 2 N rs values per CTA.
+          const int w = rs / nb, wv = w >> 3;
+          const uint32_t ybase = smem_u32(ybuf), gbase = smem_u32(gbuf), sbase = smem_u32(sbuf), zbase = smem_u32(zbuf);
+          for (int e = ctid; e < nb * p.N * wv; e += kConsumerWarps * 32) {
+            const int j = e / (p.N * wv), rem = e - j * (p.N * wv), n = rem / wv, v = rem - n * wv;
+            const uint4 yv = ld_shared_cluster_v4(mapa_shared(ybase + (n * rs + blk * w + v * 8) * 2, j));
+            *reinterpret_cast<uint4*>(gbuf + ((j * NP + n) * w + v * 8) * 2) = yv;
+          }
+          consumer_bar();  // gbuf complete; this CTA no longer reads its peers' ybuf
+          if (ctid < nb) mbar_arrive_remote(mapa_shared(read_done, ctid));
+          for (int e = ctid; e < nb * p.N * wv; e += kConsumerWarps * 32) {
+            const int i = e / (p.N * wv), rem = e - i * (p.N * wv), n = rem / wv, v = rem - n * wv;
+            float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < nb; ++j) {
+              uint4 sv, yv;
+              lds128(sbase + ((i * nb + j) * w + v * 8) * 2, sv.x, sv.y, sv.z, sv.w);
+              lds128(gbase + ((j * NP + n) * w + v * 8) * 2, yv.x, yv.y, yv.z, yv.w);
+              const float2 s0 = unpack16x2<BF16>(sv.x), s1 = unpack16x2<BF16>(sv.y), s2 = unpack16x2<BF16>(sv.z), s3 = unpack16x2<BF16>(sv.w);
+              const float2 y0 = unpack16x2<BF16>(yv.x), y1 = unpack16x2<BF16>(yv.y), y2 = unpack16x2<BF16>(yv.z), y3 = unpack16x2<BF16>(yv.w);
+              s[0] = fmaf(s0.x, y0.x, s[0]); s[1] = fmaf(s0.y, y0.y, s[1]);
+              s[2] = fmaf(s1.x, y1.x, s[2]); s[3] = fmaf(s1.y, y1.y, s[3]);
+              s[4] = fmaf(s2.x, y2.x, s[4]); s[5] = fmaf(s2.y, y2.y, s[5]);
+              s[6] = fmaf(s3.x, y3.x, s[6]); s[7] = fmaf(s3.y, y3.y, s[7]);
+            }
+            if (p.round_z) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) s[k] = round_clamp_i8(s[k]);
+            }
+            uint4 o;
+            o.x = pack16x2<BF16>(s[0], s[1]); o.y = pack16x2<BF16>(s[2], s[3]);
+            o.z = pack16x2<BF16>(s[4], s[5]); o.w = pack16x2<BF16>(s[6], s[7]);
+            const int col = blk * w + v * 8;  // column of the slice, a multiple of 8
+            st_shared_cluster_v4(mapa_shared(zbase + (col >> 6) * kABoxBytes + sw128(n, (col & 63) >> 3), i), o);
+          }
+          consumer_bar();  // this CTA's pieces are written (the arrive below releases them to the cluster)
+          if (ctid < nb) mbar_arrive_remote(mapa_shared(z_ready, ctid));
+          if (!mbar_wait_cluster(z_ready, 0, abort_flag)) ok = false;  // every CTA's pieces of z_blk are here
+        } else if (XCH == kXchPull && !*abort_flag) {
           // One item = 8 ranks of one token; two neighbouring lanes share an item, each gathers eight of the
           // (up to) sixteen in-blocks with all its remote loads in flight at once, then the halves are added.
           const int nv = rs >> 3, items = p.N * nv * 2;
@@ -351,7 +409,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
         }
         consumer_bar();  // zbuf complete; this CTA no longer reads its peers' ybuf
         if (ctid == 0) BLR_STAMP(4);
-        if (ctid < nb) mbar_arrive_remote(mapa_shared(read_done, ctid));
+        if (ctid < nb && !SUB) mbar_arrive_remote(mapa_shared(read_done, ctid));  // (sub-slice: done above)
       }
     }
     if (ctid == 0) BLR_STAMP(5);
@@ -424,14 +482,14 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
 
 // ------------------------------------------------------------------ host side
 size_t cluster_smem_bytes(const ClusterParams& p, int np) {
-  return (size_t)p.nstages * p.stage_bytes + (size_t)np * p.rs * 2 + 16 * p.rs * 2 + (p.rs / 64) * np * 128 + 40 * 8 + 1024;
+  return (size_t)p.nstages * p.stage_bytes + (size_t)np * p.rs * 2 + 16 * p.rs * 2 + (size_t)np * p.rs * 2 + (p.rs / 64) * np * 128 + 40 * 8 + 1024;
 }
 
-template <bool BF16, int NT, bool GS, bool MON>
+template <bool BF16, int NT, bool GS, int XCH>
 static int cluster_capacity_impl(int b, int smem_bytes) {
   DeviceInfo di;
   if (device_info(&di) != BLR_OK) return 0;
-  auto kern = blr_blast_cluster_kernel<BF16, NT, GS, MON>;
+  auto kern = blr_blast_cluster_kernel<BF16, NT, GS, XCH>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin) != cudaSuccess) return 0;
   if (b > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
     cudaGetLastError();
@@ -470,16 +528,18 @@ int cluster_capacity(int b, int is_bf16, int variant, int n_tokens, int smem_byt
   if (!have[dev][b][bf][gsi][two]) {
     const int sm = two ? kClusterHalfSmem : di.max_smem_optin - 1024;
     int n;
-    if (gsi == 2) n = bf ? cluster_capacity_impl<true, 1, false, true>(b, sm) : cluster_capacity_impl<false, 1, false, true>(b, sm);
-    else if (gsi) n = bf ? cluster_capacity_impl<true, 1, true, false>(b, sm) : cluster_capacity_impl<false, 1, true, false>(b, sm);
-    else n = bf ? cluster_capacity_impl<true, 1, false, false>(b, sm) : cluster_capacity_impl<false, 1, false, false>(b, sm);
+    // all instantiations of a variant have the same launch bounds and take the shared memory they are given, so
+    // the one-tile pull form stands for the others
+    if (gsi == 2) n = bf ? cluster_capacity_impl<true, 1, false, kXchMonarch>(b, sm) : cluster_capacity_impl<false, 1, false, kXchMonarch>(b, sm);
+    else if (gsi) n = bf ? cluster_capacity_impl<true, 1, true, kXchPull>(b, sm) : cluster_capacity_impl<false, 1, true, kXchPull>(b, sm);
+    else n = bf ? cluster_capacity_impl<true, 1, false, kXchPull>(b, sm) : cluster_capacity_impl<false, 1, false, kXchPull>(b, sm);
     cache[dev][b][bf][gsi][two] = n;
     have[dev][b][bf][gsi][two] = true;
   }
   return cache[dev][b][bf][gsi][two];
 }
 
-template <bool BF16, int NT, bool GS, bool MON>
+template <bool BF16, int NT, bool GS, int XCH>
 static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
@@ -487,7 +547,21 @@ static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   const size_t smem = cluster_smem_bytes(p, NT * 8);
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
-  auto kern = blr_blast_cluster_kernel<BF16, NT, GS, MON>;
+  auto kern = blr_blast_cluster_kernel<BF16, NT, GS, XCH>;
+  {
+    // the occupancy query configured only the instantiation that stands for this one's resource class
+    int dev = 0;
+    BLR_CUDA_OK(cudaGetDevice(&dev));
+    static bool configured[64] = {}, big_clusters[64] = {};  // per template instance
+    if (!configured[dev & 63]) {
+      BLR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+      configured[dev & 63] = true;
+    }
+    if (p.b > 8 && !big_clusters[dev & 63]) {  // clusters of more than 8 CTAs need the function's consent
+      BLR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+      big_clusters[dev & 63] = true;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.b, p.nslices, p.qsplit);
   cfg.blockDim = dim3(kClusterThreads);
@@ -513,9 +587,21 @@ int launch_blast_cluster(const ClusterParams& p_in, int is_bf16, cudaStream_t st
   ClusterParams p = p_in;
   p.timeline = g_stream_timeline;
   BLR_REQUIRE(p.N >= 1 && p.N <= kClusterMaxTokens, BLR_ERR_UNSUPPORTED, "the cluster kernel takes 1..%d tokens", kClusterMaxTokens);
-  if (p.monarch) return is_bf16 ? launch_cluster_impl<true, 1, false, true>(p, stream) : launch_cluster_impl<false, 1, false, true>(p, stream);
-  if (p.ph[0].group != 0) return is_bf16 ? launch_cluster_impl<true, 1, true, false>(p, stream) : launch_cluster_impl<false, 1, true, false>(p, stream);
-  return is_bf16 ? launch_cluster_impl<true, 1, false, false>(p, stream) : launch_cluster_impl<false, 1, false, false>(p, stream);
+  const bool gs = p.ph[0].group != 0;
+#define BLR_CL(BF, NTV, GSV, X) launch_cluster_impl<BF, NTV, GSV, X>(p, stream)
+  if (p.monarch) return is_bf16 ? BLR_CL(true, 1, false, kXchMonarch) : BLR_CL(false, 1, false, kXchMonarch);
+  if (p.N > 8) {  // two token tiles: sub-slice coupling only (the caller has checked that it applies)
+    BLR_REQUIRE(p.subslice, BLR_ERR_UNSUPPORTED, "more than 8 tokens need the sub-slice coupling");
+    if (gs) return is_bf16 ? BLR_CL(true, 2, true, kXchSubslice) : BLR_CL(false, 2, true, kXchSubslice);
+    return is_bf16 ? BLR_CL(true, 2, false, kXchSubslice) : BLR_CL(false, 2, false, kXchSubslice);
+  }
+  if (p.subslice) {
+    if (gs) return is_bf16 ? BLR_CL(true, 1, true, kXchSubslice) : BLR_CL(false, 1, true, kXchSubslice);
+    return is_bf16 ? BLR_CL(true, 1, false, kXchSubslice) : BLR_CL(false, 1, false, kXchSubslice);
+  }
+  if (gs) return is_bf16 ? BLR_CL(true, 1, true, kXchPull) : BLR_CL(false, 1, true, kXchPull);
+  return is_bf16 ? BLR_CL(true, 1, false, kXchPull) : BLR_CL(false, 1, false, kXchPull);
+#undef BLR_CL
 }
 
 }  // namespace blr

@@ -12,7 +12,8 @@ namespace blr {
 
 static constexpr int kClusterThreads = (kConsumerWarps + 1) * 32;
 static constexpr int kClusterOut32Bytes = 2 << 20;   // fixed fp32 accumulation area at the start of a workspace
-static constexpr int kClusterMaxTokens = 8;           // tokens per call this kernel is used for
+static constexpr int kXchPull = 0, kXchSubslice = 1, kXchMonarch = 2;  // exchange forms (template parameter)
+static constexpr int kClusterMaxTokens = 16;          // tokens per call this kernel is used for
 static constexpr int kClusterMaxSlice = 256;         // ranks per slice
 static constexpr int kClusterHalfSmem = 115712;      // dynamic shared memory per CTA that lets two CTAs share an SM
 static constexpr int kClusterMaxParts = 7;           // row parts of U_i (counters: parts * 16 words)
@@ -27,6 +28,9 @@ struct alignas(64) ClusterParams {
   int ks0, ks1;        // K-chunks per ring stage in the two phases
   int nchunks1;        // chunks of the second phase inside one slice
   int round_y, round_z;
+  int subslice;        // 1: coupling by rank sub-slice (needs rs % (8 b) == 0): CTA c gathers ranks [c w, (c+1) w), w = rs / b,
+                       // of every y_j, couples them for every out-block i and scatters z_i's piece to CTA i; the
+                       // distributed-shared-memory traffic is 2 N rs values per CTA instead of b N rs
   // Monarch (monarch = 1): no coupling factors; the first phase of slice sl covers the mblk first-stage blocks
   // sl*mblk .. whose outputs feed the slice, cpb = b / mblk CTAs per block with rs rows each, and the exchange is
   // the permutation: z_l[t] = pre[k][q], k = sl*mblk + t / per, q = (t % per)*b + l (w1_grouped: l*per + t % per)

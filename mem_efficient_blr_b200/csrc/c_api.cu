@@ -154,6 +154,7 @@ static int check_layout(int layout) {
 
 // ---------------------------------------------------------------------------------- BLAST (16-bit and quantised)
 // Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
+static constexpr int kSubsliceMinTokens = 4;
 static int g_decode_path = 0;  // 0: automatic, 1: grid-wide streaming kernel only (blr_debug_decode_path)
 
 static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
@@ -161,8 +162,7 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
                          int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
                          int64_t ldo, const Workspace& w, cudaStream_t stream, int64_t v_row = 0, int64_t v_grp = 0,
                          int64_t u_row = 0, int64_t u_grp = 0) {
-  // above 8 tokens the exchange through distributed shared memory costs more than the grid barriers it saves
-  const int np = 8;
+  const int np = N <= 8 ? 8 : 16;
   if (g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
   if ((long long)b * Q * np * 4 > kClusterOut32Bytes) return 1;
   const int bf = dtype == BLR_DTYPE_BF16;
@@ -219,14 +219,22 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
   p.out = out; p.ldo = ldo; p.out32 = w.out32; p.counters = w.counters + 128; p.status = w.counters + 255;
   p.out_blk = Q; p.out_q = 1;
-  p.w_bytes = p.ks0 * kSubBytes;
-  p.stage_bytes = p.w_bytes + p.ks0 * p.ph[0].a_boxes * np * 128;
-  p.nstages = 2;
-  const int extras = (int)cluster_smem_bytes(p, np) - 2 * p.stage_bytes;
+  // Coupling by rank sub-slice moves 2 N rs values per CTA through distributed shared memory instead of b N rs, at
+  // the price of a second exchange step: it wins from about 4 tokens on, and is the only form for two token tiles.
+  p.subslice = rs % (8 * b) == 0 && N >= kSubsliceMinTokens;
+  if (N > 8 && !p.subslice) return 1;
   const int budget = best_two ? kClusterHalfSmem : di.max_smem_optin - 1024;
-  int nst = (budget - extras) / p.stage_bytes;
-  p.nstages = nst > 16 ? 16 : nst;
-  if (p.nstages < 2) return 1;
+  for (;;) {
+    p.w_bytes = p.ks0 * kSubBytes;
+    p.stage_bytes = p.w_bytes + p.ks0 * p.ph[0].a_boxes * np * 128;
+    p.nstages = 2;
+    const int extras = (int)cluster_smem_bytes(p, np) - 2 * p.stage_bytes;
+    const int nst = (budget - extras) / p.stage_bytes;
+    p.nstages = nst > 16 ? 16 : nst;
+    if (p.nstages >= 2) break;
+    if (p.ks0 == 1) return 1;
+    p.ks0 = p.ks1 = 1;  // two chunks per stage leave no room for a second stage: one chunk per stage
+  }
   if (forced && p.nslices * p.qsplit > cluster_capacity(b, bf, group, (int)N, budget)) return 1;
   rc = launch_blast_cluster(p, bf, stream);
   return rc;
@@ -239,7 +247,7 @@ static int cluster_monarch(const void* x, int64_t ldx, int64_t N, int dtype, con
                            const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,
                            int64_t ldo, const Workspace& w, cudaStream_t stream) {
   const int np = 8;
-  if (g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;
+  if (g_decode_path == 1 || N > 8 || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;  // one token tile only
   if ((long long)b * Qs * np * 4 > kClusterOut32Bytes) return 1;
   const int per = rank / b, bf = dtype == BLR_DTYPE_BF16;
   DeviceInfo di;

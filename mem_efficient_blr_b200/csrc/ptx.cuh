@@ -114,6 +114,9 @@ __device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(cluster_addr) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, const uint4& v) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 // One 16-bit element of a peer CTA's shared memory.
 __device__ __forceinline__ uint16_t ld_shared_cluster_u16(uint32_t cluster_addr) {
   uint16_t v;

@@ -164,13 +164,14 @@ def test_blast_weight_quantised_rejects_other_group_widths(K):
 
 
 def test_small_batches_on_the_grid_wide_kernel(K):
-    """1..8 tokens normally take the cluster kernel; the grid-wide streaming kernel must give the same
-    answers for them (it is what runs when the shape does not fit a cluster)."""
+    """BLAST on 1..16 tokens normally takes the cluster kernel; the grid-wide streaming kernel must give the same
+    answers (it is what runs when the shape does not fit a cluster)."""
     lib = K.lib.load()
     assert lib.blr_debug_decode_path(1) == 0
     try:
         for N, I, O, b, R, bits in [(1, 4096, 11008, 16, 1024, 16), (5, 768, 768, 3, 128, 16),
-                                    (4, 4096, 11008, 16, 1024, 8), (1, 4096, 11008, 16, 1024, 4)]:
+                                    (4, 4096, 11008, 16, 1024, 8), (1, 4096, 11008, 16, 1024, 4),
+                                    (16, 4096, 11008, 16, 1024, 8), (12, 768, 3072, 4, 192, 16)]:
             x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=N + bits)
             if bits == 16:
                 ref, _, _ = orc.blast(x, U, Vt, S)
