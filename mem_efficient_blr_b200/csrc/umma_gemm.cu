@@ -256,6 +256,10 @@ void umma_gemm_tiling(GemmParams& p) {
     p.tokens_as_rows = 1;
     int bn = 256;
     if (p.M <= 192) bn = (p.M + 63) / 64 * 64;  // multiples of 64 keep the M-major boxes whole
+    // few token tiles: narrower weight tiles until there is about one tile per SM (a 128 x 256 tile of a short
+    // contraction is over in a microsecond; half of the SMs idle costs more than the smaller MMA shape)
+    const long long n_tiles = (p.N + kBM - 1) / kBM;
+    while (bn % 128 == 0 && (long long)p.G * ((p.M + bn - 1) / bn) * n_tiles < 132) bn /= 2;  // 256 -> 128 -> 64
     p.bn = bn;
   } else {
     p.tokens_as_rows = 0;
