@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
   // byte offsets of the two operands inside a stage
   const uint32_t w_off = TR ? kRowTileBytes : 0u, a_off = TR ? 0u : kRowTileBytes;
 
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (uint32_t s = 0; s < NST; ++s) {
@@ -83,6 +84,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above overlaps the tail of the previous kernel in the stream; its
+  // results (this kernel's activations) and the buffers it may still be reading (this kernel's output) are
+  // touched only after it has completed.  Every thread waits, so this grid completes after its predecessor.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------ producer
@@ -277,8 +282,18 @@ static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, i
     BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     configured[dev & 63] = true;
   }
-  blr_umma_gemm_kernel<BF16, TR><<<grid, kGemmThreads, smem, stream>>>(p);
-  BLR_CUDA_OK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  void* args[] = {const_cast<GemmParams*>(&p)};
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR>, args));
   return BLR_OK;
 }
 
