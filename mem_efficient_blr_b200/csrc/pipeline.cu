@@ -77,9 +77,13 @@ __global__ void expand_coupling_kernel(const T* __restrict__ S, long long s_i, l
                                        T* __restrict__ E, int b, int b_out, int R) {
   // one thread per (row (g, i, r'), in-block j): a vector of GS values with a single non-zero at position r';
   // consecutive threads write consecutive vectors of a row
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long total = (long long)(R / GS) * GS * b_out * b;
   const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (id >= total) return;
+  if (id >= total) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // every thread waits: the grid must not complete before its predecessor
+    return;
+  }
   const int j = (int)(id % b);
   const long long row_id = id / b;
   const int h = GS * b_out, row = (int)(row_id % h), g = (int)(row_id / h), i = row / GS, r1 = row % GS;
@@ -87,6 +91,9 @@ __global__ void expand_coupling_kernel(const T* __restrict__ S, long long s_i, l
 #pragma unroll
   for (int k = 0; k < GS; ++k) v[k] = T(0.f);
   v[r1] = S[i * s_i + j * s_j + (long long)(GS * g + r1) * s_r];
+  // the factors do not depend on the previous kernel; E may still be read by it (the coupling GEMM of the previous
+  // call on this workspace), so the stores wait for its completion
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   T* dst = E + id * GS;
 #pragma unroll
   for (int k = 0; k < GS / 8; ++k) *reinterpret_cast<uint4*>(dst + 8 * k) = *reinterpret_cast<const uint4*>(v + 8 * k);
@@ -122,11 +129,20 @@ static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void
                       cudaStream_t stream) {
   const long long total = (long long)(R / gs) * gs * b_out * b;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (gs == 16)
-    expand_coupling_kernel<T, 16><<<blocks, 256, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
-  else
-    expand_coupling_kernel<T, 8><<<blocks, 256, 0, stream>>>(static_cast<const T*>(S), s_i, s_j, s_r, static_cast<T*>(E), b, b_out, R);
-  BLR_CUDA_OK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  const T* Sp = static_cast<const T*>(S);
+  T* Ep = static_cast<T*>(E);
+  void* args[] = {&Sp, &s_i, &s_j, &s_r, &Ep, &b, &b_out, &R};
+  if (gs == 16) BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)expand_coupling_kernel<T, 16>, args));
+  else BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)expand_coupling_kernel<T, 8>, args));
   return BLR_OK;
 }
 
