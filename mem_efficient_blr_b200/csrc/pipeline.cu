@@ -15,6 +15,8 @@ static CUtensorMapDataType dt16(int dtype) {
   return dtype == BLR_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 }
 
+static constexpr int kCoupleTileMaxTokens = 256;  // above: coupling as a grouped GEMM over expanded factors
+
 struct OutSpec {
   void* out;
   long long os_g, os_n, os_hi, os_lo;
@@ -124,6 +126,95 @@ static int run_couple_generic(const void* y, const void* S, int64_t s_i, int64_t
   return BLR_OK;
 }
 
+// Coupling on the CUDA cores for a few hundred tokens, where building and multiplying the expanded factors costs more
+// than the coupling itself: a block takes 64 consecutive ranks, stages S[i][j][64 ranks] for all pairs of blocks in
+// shared memory once, and walks its share of the tokens; a thread owns 8 ranks of one token, holds the b vectors
+// y_j in registers and produces the b_out vectors z_i.  y, z: [block][token][R], S with unit rank stride.
+template <typename T, int B>
+__global__ void __launch_bounds__(256) blast_couple_tile_kernel(const T* __restrict__ y, const T* __restrict__ S, long long s_i,
+                                                                long long s_j, T* __restrict__ z, int b_out, long long N, int R,
+                                                                int round_z, int tok_groups) {
+  extern __shared__ __align__(16) unsigned char couple_smem[];
+  T* sS = reinterpret_cast<T*>(couple_smem);  // [b_out][B][64]
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int rt = blockIdx.x / tok_groups, tg = blockIdx.x - rt * tok_groups, r0 = rt * 64;
+  for (int e = threadIdx.x; e < b_out * B * 8; e += 256) {
+    const int ij = e >> 3, v = e & 7, i = ij / B, j = ij - i * B;
+    uint4 w = make_uint4(0, 0, 0, 0);
+    if (r0 + v * 8 < R) w = __ldg(reinterpret_cast<const uint4*>(S + i * s_i + j * s_j + r0 + v * 8));
+    reinterpret_cast<uint4*>(sS)[e] = w;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // y comes from the previous kernel; z may still be read by an earlier one
+  __syncthreads();
+  const int v = threadIdx.x & 7, nl = threadIdx.x >> 3;  // 8 rank vectors x 32 tokens per pass
+  const long long plane = N * R;
+  if (r0 + v * 8 >= R) return;
+  for (long long n = (long long)tg * 32 + nl; n < N; n += (long long)tok_groups * 32) {
+    float yv[B][8];
+#pragma unroll
+    for (int j = 0; j < B; ++j) {
+      const uint4 w = *reinterpret_cast<const uint4*>(y + j * plane + n * R + r0 + v * 8);
+      const T* h = reinterpret_cast<const T*>(&w);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) yv[j][k] = (float)h[k];
+    }
+    for (int i = 0; i < b_out; ++i) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < B; ++j) {
+        const uint4 w = reinterpret_cast<const uint4*>(sS)[(i * B + j) * 8 + v];
+        const T* h = reinterpret_cast<const T*>(&w);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = fmaf((float)h[k], yv[j][k], acc[k]);
+      }
+      alignas(16) T o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = T(round_z ? fminf(fmaxf(rintf(acc[k]), -128.f), 127.f) : acc[k]);
+      *reinterpret_cast<uint4*>(z + i * plane + n * R + r0 + v * 8) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+}
+
+template <typename T>
+static int run_couple_tile(const void* y, const void* S, int64_t s_i, int64_t s_j, void* z, int b, int b_out, int64_t N, int R,
+                           int round_z, cudaStream_t stream) {
+  const int r_tiles = (R + 63) / 64;
+  int tok_groups = (int)((N + 31) / 32);
+  const int want = (2 * 148 + r_tiles - 1) / r_tiles;  // about two blocks per SM
+  if (tok_groups > want) tok_groups = want;
+  const size_t smem = (size_t)b_out * b * 64 * sizeof(T);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(r_tiles * tok_groups));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  const T* yp = static_cast<const T*>(y);
+  const T* Sp = static_cast<const T*>(S);
+  T* zp = static_cast<T*>(z);
+  long long si = s_i, sj = s_j, n = N;
+  void* args[] = {&yp, &Sp, &si, &sj, &zp, &b_out, &n, &R, &round_z, &tok_groups};
+  const void* kern = nullptr;
+  switch (b) {
+    case 2: kern = (const void*)blast_couple_tile_kernel<T, 2>; break;
+    case 3: kern = (const void*)blast_couple_tile_kernel<T, 3>; break;
+    case 4: kern = (const void*)blast_couple_tile_kernel<T, 4>; break;
+    case 6: kern = (const void*)blast_couple_tile_kernel<T, 6>; break;
+    case 8: kern = (const void*)blast_couple_tile_kernel<T, 8>; break;
+    case 9: kern = (const void*)blast_couple_tile_kernel<T, 9>; break;
+    case 12: kern = (const void*)blast_couple_tile_kernel<T, 12>; break;
+    case 16: kern = (const void*)blast_couple_tile_kernel<T, 16>; break;
+    default: return 1;  // no instantiation for this block count
+  }
+  if (smem > 48 * 1024) BLR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, kern, args));
+  return BLR_OK;
+}
+
 template <typename T>
 static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void* E, int b, int b_out, int R, int gs,
                       cudaStream_t stream) {
@@ -153,6 +244,18 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
   const long long plane = (long long)N * R;
   const bool bf = dtype == BLR_DTYPE_BF16;
   int rc;
+  // Up to a few hundred tokens the coupling is cheaper on the CUDA cores (one kernel, factors staged in shared
+  // memory) than as a GEMM over expanded factors (two kernels, 16x the products).
+  const bool s_vec = s_r == 1 && (s_i & 7) == 0 && (s_j & 7) == 0 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
+  if (N <= kCoupleTileMaxTokens && R % 8 == 0 && s_vec && b <= 16) {
+    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream);
+    if (rc) return rc;
+    rc = bf ? run_couple_tile<__nv_bfloat16>(y16, S, s_i, s_j, z16, b, b_out, N, R, act_int8, stream)
+            : run_couple_tile<__half>(y16, S, s_i, s_j, z16, b, b_out, N, R, act_int8, stream);
+    if (rc < 0) return rc;
+    if (rc == 0) return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
+    // rc == 1: no instantiation for this block count; y16 is overwritten below in the layout that path wants
+  }
   if (b <= 16 && R % 8 == 0) {
     // y'[n][r/GS][j][r%GS] = sum_p V[j][r][p] x[n][j*P + p]: the (j, r%GS) index is contiguous, ready to be the
     // K dimension of the coupling GEMM
