@@ -247,7 +247,9 @@ static int cluster_monarch(const void* x, int64_t ldx, int64_t N, int dtype, con
                            const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,
                            int64_t ldo, const Workspace& w, cudaStream_t stream) {
   const int np = 8;
-  if (g_decode_path == 1 || N > 8 || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;  // one token tile only
+  // one token tile; the permutation is gathered element by element, which for the torch layout (stride b between a
+  // CTA's elements) overtakes the grid-wide kernel's barrier from about 6 tokens on
+  if (g_decode_path == 1 || N > (grouped ? 8 : 5) || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;
   if ((long long)b * Qs * np * 4 > kClusterOut32Bytes) return 1;
   const int per = rank / b, bf = dtype == BLR_DTYPE_BF16;
   DeviceInfo di;
