@@ -18,7 +18,7 @@
  *     layouts of the reference's Triton entry points).
  *   - n_tokens = 0 is valid for the 16-bit and quantised entry points: they return 0 without touching a pointer.
  *   - Return value: 0 on success, a negative BLR_ERR_* code otherwise; blr_last_error() has the text.
- *     Token counts up to 16 run one weight-streaming kernel (BLAST, and Monarch / low-rank on up to 8 tokens:
+ *     Token counts up to 16 run one weight-streaming kernel (BLAST and low-rank, and Monarch on up to 8 tokens:
  *     a kernel of thread-block clusters, one cluster per slice of the rank index); larger counts run the
  *     tensor-core pipeline.
  */
@@ -72,7 +72,7 @@ int blr_version(void);
  * NULL switches it off. No reference counterpart. */
 int blr_debug_stream_timeline(void* dev_ptr);
 
-/* Test aid: BLAST on 1..16 tokens (Monarch and low-rank: 1..8) normally runs on the cluster kernel where the shape
+/* Test aid: BLAST and low-rank on 1..16 tokens (Monarch: 1..8) normally run on the cluster kernel where the shape
  * allows it; which = 1 sends those calls to the grid-wide streaming kernel instead,
  * which = 0 restores the automatic choice. Process-wide. No reference counterpart. */
 int blr_debug_decode_path(int which);
