@@ -1,10 +1,12 @@
-// BLAST decode kernel built on thread-block clusters (see blast_cluster.h for the decomposition).
+// Two-stage decode kernel built on thread-block clusters (see blast_cluster.h for the decomposition): BLAST,
+// low-rank (BLAST with an all-ones coupling) and Monarch.
 //
-// Per CTA (block index `blk` = rank in the cluster, slice `sl` = cluster index): one producer warp streams, through
-// a ring of TMA stages, first the rows [sl*rs, (sl+1)*rs) of V_blk with the matching boxes of x_blk, then all Q
-// rows of U_blk restricted to the slice's columns; eight consumer warps turn the stages into mma.sync products
-// exactly like the grid-wide streaming kernel (one 16-row group per warp).  Between the two phases the cluster
-// exchanges y through distributed shared memory, guarded by mbarriers that peers arrive on remotely.
+// Per CTA (block index `blk` = rank in the cluster, slice `sl` = blockIdx.y, row part = blockIdx.z): one producer
+// warp streams, through a ring of TMA stages, first its first-stage rows (BLAST: rows [sl*rs, (sl+1)*rs) of V_blk)
+// with the matching boxes of x, then its part of the rows of U_blk restricted to the slice's columns; eight
+// consumer warps turn the stages into mma.sync products exactly like the grid-wide streaming kernel (one 16-row
+// group per warp).  Between the two phases the cluster exchanges the first stage's outputs through distributed
+// shared memory, guarded by mbarriers that peers arrive on remotely, in one of three forms (template parameter).
 // All waits are bounded; nothing here spins on another cluster.
 #include "blast_cluster.h"
 #include "ptx.cuh"

@@ -2,7 +2,9 @@
 // per slice, one CTA of the cluster per block index.  CTA j computes y_j on the slice, the cluster exchanges y
 // through distributed shared memory, CTA i couples z_i on the slice and multiplies it with the matching columns
 // of U_i; the partial outputs of the slices are summed with fp32 reductions in global memory and the last CTA to
-// finish a block converts it.  Every weight byte is read once and nothing waits on another cluster.
+// finish a block converts it.  Nothing waits on another cluster.  The rows of U_i can be cut into parts (one
+// cluster per slice and part; the parts of a slice repeat its first stage and coupling).  Monarch runs on the same
+// kernel with the permutation between its stages as the exchange.
 #pragma once
 #include <cuda_runtime.h>
 
