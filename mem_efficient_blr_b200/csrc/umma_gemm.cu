@@ -264,7 +264,8 @@ void umma_gemm_tiling(GemmParams& p) {
     // few token tiles: narrower weight tiles until there is about one tile per SM (a 128 x 256 tile of a short
     // contraction is over in a microsecond; half of the SMs idle costs more than the smaller MMA shape)
     const long long n_tiles = (p.N + kBM - 1) / kBM;
-    while (bn % 128 == 0 && (long long)p.G * ((p.M + bn - 1) / bn) * n_tiles < 132) bn /= 2;  // 256 -> 128 -> 64
+    // (long contractions keep the wide tile: there the loads per flop decide, and they grow as the tile narrows)
+    while (p.K <= 512 && bn % 128 == 0 && (long long)p.G * ((p.M + bn - 1) / bn) * n_tiles < 132) bn /= 2;  // 256 -> 128 -> 64
     p.bn = bn;
   } else {
     p.tokens_as_rows = 0;
