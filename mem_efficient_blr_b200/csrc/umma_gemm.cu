@@ -266,6 +266,8 @@ void umma_gemm_tiling(GemmParams& p) {
     const long long n_tiles = (p.N + kBM - 1) / kBM;
     // (long contractions keep the wide tile: there the loads per flop decide, and they grow as the tile narrows)
     while (p.K <= 512 && bn % 128 == 0 && (long long)p.G * ((p.M + bn - 1) / bn) * n_tiles < 132) bn /= 2;  // 256 -> 128 -> 64
+    // long contraction: narrower only while the tiles still fit one wave (then a narrower tile is a shorter wave)
+    while (p.K > 512 && bn % 128 == 0 && (long long)p.G * ((p.M + bn / 2 - 1) / (bn / 2)) * n_tiles <= 148) bn /= 2;
     p.bn = bn;
   } else {
     p.tokens_as_rows = 0;
