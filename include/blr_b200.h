@@ -157,7 +157,8 @@ int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
  * out_host is valid after blr_host_flush(stream) has been called and `stream` has been synchronised.
  * `staging` is caller-owned device memory of blr_host_staging_bytes(n_tokens, b*P, b*Q) bytes, 256-byte aligned,
  * used with one stream like the workspace and, from its first use on, always passed with the same size (the
- * slots are cut from that size); size it for the largest call.  No reference counterpart (the reference's operators take device tensors). */
+ * slots are cut from that size); size it for the largest call.  Not for use while `stream` is being captured into a
+ * CUDA graph: the copy streams are not part of the capture.  No reference counterpart (the reference's operators take device tensors). */
 size_t blr_host_staging_bytes(int64_t n_tokens, int64_t in_features, int64_t out_features);
 /* Makes `stream` wait for every copy-out that host-buffer calls on it have enqueued so far. */
 int blr_host_flush(void* stream);
