@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
             *reinterpret_cast<uint4*>(gbuf + ((j * NP + n) * w + v * 8) * 2) = yv;
           }
           consumer_bar();  // gbuf complete; this CTA no longer reads its peers' ybuf
-          if (ctid < nb) mbar_arrive_remote(mapa_shared(read_done, ctid));
+          if (ctid < nb) mbar_arrive_remote_relaxed(mapa_shared(read_done, ctid));
           for (int e = ctid; e < nb * p.N * wv; e += kConsumerWarps * 32) {
             const int i = e / (p.N * wv), rem = e - i * (p.N * wv), n = rem / wv, v = rem - n * wv;
             float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
         }
         consumer_bar();  // zbuf complete; this CTA no longer reads its peers' ybuf
         if (ctid == 0) BLR_STAMP(4);
-        if (ctid < nb && !SUB) mbar_arrive_remote(mapa_shared(read_done, ctid));  // (sub-slice: done above)
+        if (ctid < nb && !SUB) mbar_arrive_remote_relaxed(mapa_shared(read_done, ctid));  // (sub-slice: done above)
       }
     }
     if (ctid == 0) BLR_STAMP(5);
