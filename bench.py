@@ -202,6 +202,17 @@ def run_ours(args):
                 count += 1
         return count
 
+    if args.ncu_case.startswith("p16:"):
+        # small case for a profiler capture of the tensor-core pipeline: the 16-bit layer on N tokens, three calls
+        import mem_efficient_blr_b200.blast_kernels as bk
+        n = int(args.ncu_case.split(":")[1])
+        xn = torch.randn(n, I_F, device=dev, dtype=torch.float16)
+        for _ in range(3):
+            bk.blast_torch_layout(xn, Ud, Vd, Sd)
+        torch.cuda.synchronize()
+        _lib.workspace_status(dev)
+        print(json.dumps({"ncu_case": args.ncu_case, "calls": 3}))
+        return
     if args.ncu_case:
         # small case for a profiler capture: a few eager launches of one point over distinct replicas
         bits, n = (int(t) for t in args.ncu_case.split(":"))
@@ -505,7 +516,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-context", action="store_true", help="skip the informational 16-bit / cuBLAS measurements")
-    ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager launches of one point and exit (for profiler captures)")
+    ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager launches of one point and exit (for profiler captures); "
+                                                  "p16:TOKENS - three calls of the 16-bit layer on that many tokens")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
