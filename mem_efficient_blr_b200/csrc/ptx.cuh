@@ -295,6 +295,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Ties the registers of a tmem_ld16 to the wait that precedes this call: uses of r[] cannot move above it.
+__device__ __forceinline__ void tmem_regs_ready(uint32_t (&r)[16]) {
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]));
+  asm volatile("" : "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]));
+}
 
 // Shared-memory operand descriptor for 128-byte-swizzled tiles (the layout TMA writes with SWIZZLE_128B).
 //   K-major operand  ([rows][64 k]):  lbo unused, sbo = 1024 (8 rows x 128 B)

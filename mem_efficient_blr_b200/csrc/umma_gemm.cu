@@ -3,7 +3,8 @@
 //             256 rows of its column operand, both 64 k wide, 128-byte swizzled
 //   warp 1    MMA issuer: one elected thread issues tcgen05.mma (M = 128, N = bn, K = 16) from shared-memory
 //             descriptors; accumulators are double-buffered in TMEM (2 x bn columns of fp32)
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (one MMA row per thread), convert, store
+//   warps 2-9 epilogue: tcgen05.ld the accumulator (one MMA row per thread, two warps per 32 rows taking
+//             alternate 64-column chunks, loads of the next chunk in flight), convert, store
 // Which operand the tokens are is a template parameter (see umma_gemm.h).
 // All waits are bounded; a time-out sets *status and the kernel drains and frees its TMEM.
 #include <stdlib.h>
@@ -14,7 +15,7 @@
 
 namespace blr {
 
-static constexpr int kGemmThreads = 192;
+static constexpr int kGemmThreads = 320;
 static constexpr int kBM = 128;  // rows of the MMA (TMEM lanes)
 static constexpr int kBK = 64;
 static constexpr int kRowTileBytes = kBM * kBK * 2;
@@ -35,9 +36,15 @@ __device__ __forceinline__ uint32_t gemm_pack(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&v);
   }
 }
-__device__ __forceinline__ float gemm_round(float v, int round_out) {
-  return round_out ? fminf(fmaxf(rintf(v), -128.f), 127.f) : v;
+template <bool RND>
+__device__ __forceinline__ float gemm_round(float v) {
+  if constexpr (RND) return fminf(fmaxf(rintf(v), -128.f), 127.f);
+  else return v;
 }
+template <bool V>
+struct RoundTag {
+  static constexpr bool value = V;
+};
 
 // TR = tokens are the MMA rows (weights its columns); !TR = weights are the rows ("swap-AB").
 template <bool BF16, bool TR>
@@ -75,7 +82,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
-      mbar_init(tempty0 + 8 * b, 4);  // one arrival per epilogue warp
+      mbar_init(tempty0 + 8 * b, 8);  // one arrival per epilogue warp
     }
     mbar_init_fence();
   }
@@ -147,8 +154,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
       }
     }
   } else {
-    // ------------------------------------------------ epilogue: warp w reads TMEM lanes 32*(w%4)..+31
-    const int q = warp & 3;
+    // ------------------------------------------------ epilogue: warp w reads TMEM lanes 32*(w%4)..+31; the two
+    // warps of a lane quarter take alternate column chunks of the accumulator
+    const int q = warp & 3, half = (warp - 2) >> 2;
     uint32_t it = 0;
     bool ok = true;
     // 16-byte stores need 8 consecutive outputs contiguous and aligned in memory
@@ -157,91 +165,114 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
     // 32-byte stores: 16 consecutive outputs contiguous and 32-byte aligned
     const bool wide_out = vec_out && (p.per & 15) == 0 && (p.os_g & 15) == 0 && (p.os_n & 15) == 0 && (p.os_hi & 15) == 0 &&
                           (p.bn & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-      const int nt = tile % n_tiles, gm = tile / n_tiles, mt = gm % m_tiles, g = gm / m_tiles;
-      const uint32_t buf = it & 1u, use = it >> 1;
-      if (ok && !mbar_wait(tfull0 + 8 * buf, use & 1u, abort_flag)) ok = false;
-      if (!ok) continue;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)p.bn;
-      const long long gbase = (long long)g * p.os_g;
-      if constexpr (TR) {
-        // thread = token, columns = consecutive weight rows
-        const int n = nt * kBM + q * 32 + lane;
-        const bool n_ok = n < p.N;
-        const long long nbase = gbase + (long long)n * p.os_n;
-        const int m0 = mt * p.bn;
-        int hi = m0 / p.per, lo = m0 - hi * p.per;  // (m / per, m % per) of the chunk start, kept incrementally
-        for (int c0 = 0; c0 < p.bn && m0 + c0 < p.M; c0 += 64) {
-          // four TMEM loads in flight before the wait: one round covers 64 outputs of this token
-          uint32_t rr[4][16];
+    // the body is instantiated with and without the rounding to int8 steps (a round-to-integer per value is a
+    // quarter-rate instruction that the common case must not pay for)
+    auto run = [&](auto rnd_tag) {
+      constexpr bool RND = decltype(rnd_tag)::value;
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+        const int nt = tile % n_tiles, gm = tile / n_tiles, mt = gm % m_tiles, g = gm / m_tiles;
+        const uint32_t buf = it & 1u, use = it >> 1;
+        if (ok && !mbar_wait(tfull0 + 8 * buf, use & 1u, abort_flag)) ok = false;
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)p.bn;
+        const long long gbase = (long long)g * p.os_g;
+        if constexpr (TR) {
+          // thread = token, columns = consecutive weight rows, 64 per round; the loads of the next round are in
+          // flight while this one is converted and stored
+          const int n = nt * kBM + q * 32 + lane;
+          const bool n_ok = n < p.N;
+          const long long nbase = gbase + (long long)n * p.os_n;
+          const int m0 = mt * p.bn;
+          const int cend = min(p.bn, p.M - m0);  // columns of this tile that exist
+          auto issue = [&](int c0, uint32_t(&rr)[4][16]) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (c0 + 16 * u < p.bn && m0 + c0 + 16 * u < p.M) tmem_ld16(taddr + c0 + 16 * u, rr[u]);
-          tmem_ld_wait();
+            for (int u = 0; u < 4; ++u)
+              if (c0 + 16 * u < cend) tmem_ld16(taddr + c0 + 16 * u, rr[u]);
+          };
+          auto drain = [&](int c0, uint32_t(&rr)[4][16]) {
+            int hi = (m0 + c0) / p.per, lo = (m0 + c0) - hi * p.per;  // (m / per, m % per), kept incrementally
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + 16 * u;
-            if (!(c < p.bn && m0 + c < p.M)) break;
-            uint32_t(&r)[16] = rr[u];
-            if (vec_out) {
-              uint32_t w[8];
+            for (int u = 0; u < 4; ++u) {
+              const int c = c0 + 16 * u;
+              if (c >= cend) break;
+              uint32_t(&r)[16] = rr[u];
+              tmem_regs_ready(r);
+              if (vec_out) {
+                uint32_t w[8];
 #pragma unroll
-              for (int k = 0; k < 8; ++k)
-                w[k] = gemm_pack<BF16>(gemm_round(__uint_as_float(r[2 * k]), p.round_out), gemm_round(__uint_as_float(r[2 * k + 1]), p.round_out));
-              uint16_t* o16 = reinterpret_cast<uint16_t*>(p.out);
-              if (wide_out && m0 + c + 16 <= p.M) {
-                // one full 32-byte sector per thread
-                uint16_t* dst = o16 + nbase + (long long)hi * p.os_hi + lo;
-                if (n_ok)
-                  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-                lo += 16;
-                if (lo >= p.per) { lo -= p.per; ++hi; }
+                for (int k = 0; k < 8; ++k)
+                  w[k] = gemm_pack<BF16>(gemm_round<RND>(__uint_as_float(r[2 * k])), gemm_round<RND>(__uint_as_float(r[2 * k + 1])));
+                uint16_t* o16 = reinterpret_cast<uint16_t*>(p.out);
+                if (wide_out && m0 + c + 16 <= p.M) {
+                  // one full 32-byte sector per thread
+                  uint16_t* dst = o16 + nbase + (long long)hi * p.os_hi + lo;
+                  if (n_ok)
+                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                  lo += 16;
+                  if (lo >= p.per) { lo -= p.per; ++hi; }
+                } else {
+#pragma unroll
+                  for (int h = 0; h < 2; ++h) {
+                    if (n_ok && m0 + c + 8 * h < p.M)
+                      *reinterpret_cast<uint4*>(o16 + nbase + (long long)hi * p.os_hi + lo) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
+                    lo += 8;
+                    if (lo >= p.per) { lo -= p.per; ++hi; }
+                  }
+                }
               } else {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  if (n_ok && m0 + c + 8 * h < p.M)
-                    *reinterpret_cast<uint4*>(o16 + nbase + (long long)hi * p.os_hi + lo) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
-                  lo += 8;
-                  if (lo >= p.per) { lo -= p.per; ++hi; }
+                for (int j = 0; j < 16; ++j) {
+                  if (n_ok && m0 + c + j < p.M)
+                    gemm_store<BF16>(p.out, nbase + (long long)hi * p.os_hi + (long long)lo * p.os_lo, gemm_round<RND>(__uint_as_float(r[j])));
+                  if (++lo == p.per) { lo = 0; ++hi; }
                 }
               }
-            } else {
+            }
+          };
+          uint32_t ra[4][16], rb[4][16];
+          int c0 = 64 * half;
+          if (c0 < cend) issue(c0, ra);
+          while (c0 < cend) {
+            tmem_ld_wait();
+            if (c0 + 128 < cend) issue(c0 + 128, rb);
+            drain(c0, ra);
+            c0 += 128;
+            if (c0 >= cend) break;
+            tmem_ld_wait();
+            if (c0 + 128 < cend) issue(c0 + 128, ra);
+            drain(c0, rb);
+            c0 += 128;
+          }
+        } else {
+          // thread = weight row, columns = tokens
+          const int m = mt * kBM + q * 32 + lane;
+          const bool m_ok = m < p.M;
+          const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
+          const int n0 = nt * p.bn;
+          for (int c = 16 * half; c < p.bn; c += 32) {
+            if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
+            uint32_t r[16];
+            tmem_ld16(taddr + c, r);
+            tmem_ld_wait();
+            tmem_regs_ready(r);
+            if (m_ok) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                if (n_ok && m0 + c + j < p.M)
-                  gemm_store<BF16>(p.out, nbase + (long long)hi * p.os_hi + (long long)lo * p.os_lo,
-                                   gemm_round(__uint_as_float(r[j]), p.round_out));
-                if (++lo == p.per) { lo = 0; ++hi; }
+                const int n = n0 + c + j;
+                if (n < p.N) gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round<RND>(__uint_as_float(r[j])));
               }
             }
           }
         }
-      } else {
-        // thread = weight row, columns = tokens
-        const int m = mt * kBM + q * 32 + lane;
-        const bool m_ok = m < p.M;
-        const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
-        const int n0 = nt * p.bn;
-        for (int c = 0; c < p.bn; c += 16) {
-          if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
-          uint32_t r[16];
-          tmem_ld16(taddr + c, r);
-          tmem_ld_wait();
-          if (m_ok) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int n = n0 + c + j;
-              if (n < p.N) gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round(__uint_as_float(r[j]), p.round_out));
-            }
-          }
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
-    }
+    };
+    if (p.round_out) run(RoundTag<true>{});
+    else run(RoundTag<false>{});
   }
   tc_fence_before();
   __syncthreads();
