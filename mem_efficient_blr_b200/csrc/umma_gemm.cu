@@ -41,13 +41,90 @@ __device__ __forceinline__ float gemm_round(float v) {
   if constexpr (RND) return fminf(fmaxf(rintf(v), -128.f), 127.f);
   else return v;
 }
-template <bool V>
-struct RoundTag {
-  static constexpr bool value = V;
+
+// Epilogue of one tile when tokens are the MMA rows: this thread's token, its columns = consecutive weight rows.
+struct EpiRow {
+  void* out;
+  long long nbase, os_hi, os_lo;  // element offset of the token; strides of (m / per) and (m % per)
+  int per, M, m0, cend;           // first weight row of the tile, columns of the tile that exist
+  bool n_ok;                      // token exists
 };
 
+// MODE 2: 32-byte stores (16 consecutive outputs contiguous and aligned, no ragged tile edge), 1: 16-byte stores,
+// 0: element stores.  The mode is a template parameter so that a chunk executes only its own variant.
+template <bool BF16, bool RND, int MODE>
+__device__ __forceinline__ void epilogue_store32(const EpiRow& e, int c0, uint32_t (&rr)[2][16]) {
+  int hi = (e.m0 + c0) / e.per, lo = (e.m0 + c0) - hi * e.per;  // (m / per, m % per), kept incrementally
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int c = c0 + 16 * u;
+    if (c >= e.cend) break;
+    uint32_t(&r)[16] = rr[u];
+    tmem_regs_ready(r);
+    if constexpr (MODE > 0) {
+      uint32_t w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        w[k] = gemm_pack<BF16>(gemm_round<RND>(__uint_as_float(r[2 * k])), gemm_round<RND>(__uint_as_float(r[2 * k + 1])));
+      uint16_t* o16 = reinterpret_cast<uint16_t*>(e.out);
+      if constexpr (MODE == 2) {
+        // one full 32-byte sector per thread
+        uint16_t* dst = o16 + e.nbase + (long long)hi * e.os_hi + lo;
+        if (e.n_ok)
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                       "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+        lo += 16;
+        if (lo >= e.per) { lo -= e.per; ++hi; }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (e.n_ok && e.m0 + c + 8 * h < e.M)
+            *reinterpret_cast<uint4*>(o16 + e.nbase + (long long)hi * e.os_hi + lo) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
+          lo += 8;
+          if (lo >= e.per) { lo -= e.per; ++hi; }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (e.n_ok && e.m0 + c + j < e.M)
+          gemm_store<BF16>(e.out, e.nbase + (long long)hi * e.os_hi + (long long)lo * e.os_lo, gemm_round<RND>(__uint_as_float(r[j])));
+        if (++lo == e.per) { lo = 0; ++hi; }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void epilogue_load32(uint32_t taddr, uint32_t (&rr)[2][16]) {
+#pragma unroll
+  for (int u = 0; u < 2; ++u) tmem_ld16(taddr + 16 * u, rr[u]);
+}
+
+// Columns c_first, c_first + 64, ... of the tile, 32 per round; the loads of the next round are in flight while
+// this one is converted and stored.  (A round always loads 32 columns: the allocation has room behind the last
+// tile column.)
+template <bool BF16, bool RND, int MODE>
+__device__ __forceinline__ void epilogue_rows(const EpiRow& e, uint32_t taddr, int c_first) {
+  uint32_t ra[2][16], rb[2][16];
+  int c0 = c_first;
+  if (c0 < e.cend) epilogue_load32(taddr + c0, ra);
+  while (c0 < e.cend) {
+    tmem_ld_wait();
+    if (c0 + 64 < e.cend) epilogue_load32(taddr + c0 + 64, rb);
+    epilogue_store32<BF16, RND, MODE>(e, c0, ra);
+    c0 += 64;
+    if (c0 >= e.cend) break;
+    tmem_ld_wait();
+    if (c0 + 64 < e.cend) epilogue_load32(taddr + c0 + 64, ra);
+    epilogue_store32<BF16, RND, MODE>(e, c0, rb);
+    c0 += 64;
+  }
+}
+
 // TR = tokens are the MMA rows (weights its columns); !TR = weights are the rows ("swap-AB").
-template <bool BF16, bool TR>
+// MODE = store width of the TR epilogue (see epilogue_store32), RND = round the outputs to int8 steps; both are
+// chosen by the host from the parameters, so that the epilogue holds exactly one variant.
+template <bool BF16, bool TR, int MODE, bool RND>
 __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -159,120 +236,51 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
     const int q = warp & 3, half = (warp - 2) >> 2;
     uint32_t it = 0;
     bool ok = true;
-    // 16-byte stores need 8 consecutive outputs contiguous and aligned in memory
-    const bool vec_out = p.os_lo == 1 && (p.per & 7) == 0 && (p.M & 7) == 0 && (p.os_g & 7) == 0 && (p.os_n & 7) == 0 &&
-                         (p.os_hi & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
-    // 32-byte stores: 16 consecutive outputs contiguous and 32-byte aligned
-    const bool wide_out = vec_out && (p.per & 15) == 0 && (p.os_g & 15) == 0 && (p.os_n & 15) == 0 && (p.os_hi & 15) == 0 &&
-                          (p.bn & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
-    // the body is instantiated with and without the rounding to int8 steps (a round-to-integer per value is a
-    // quarter-rate instruction that the common case must not pay for)
-    auto run = [&](auto rnd_tag) {
-      constexpr bool RND = decltype(rnd_tag)::value;
-      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-        const int nt = tile % n_tiles, gm = tile / n_tiles, mt = gm % m_tiles, g = gm / m_tiles;
-        const uint32_t buf = it & 1u, use = it >> 1;
-        if (ok && !mbar_wait(tfull0 + 8 * buf, use & 1u, abort_flag)) ok = false;
-        if (!ok) continue;
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)p.bn;
-        const long long gbase = (long long)g * p.os_g;
-        if constexpr (TR) {
-          // thread = token, columns = consecutive weight rows, 64 per round; the loads of the next round are in
-          // flight while this one is converted and stored
-          const int n = nt * kBM + q * 32 + lane;
-          const bool n_ok = n < p.N;
-          const long long nbase = gbase + (long long)n * p.os_n;
-          const int m0 = mt * p.bn;
-          const int cend = min(p.bn, p.M - m0);  // columns of this tile that exist
-          auto issue = [&](int c0, uint32_t(&rr)[4][16]) {
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+      const int nt = tile % n_tiles, gm = tile / n_tiles, mt = gm % m_tiles, g = gm / m_tiles;
+      const uint32_t buf = it & 1u, use = it >> 1;
+      if (ok && !mbar_wait(tfull0 + 8 * buf, use & 1u, abort_flag)) ok = false;
+      if (!ok) continue;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)p.bn;
+      const long long gbase = (long long)g * p.os_g;
+      if constexpr (TR) {
+        EpiRow e;
+        e.out = p.out;
+        const int n = nt * kBM + q * 32 + lane;
+        e.n_ok = n < p.N;
+        e.nbase = gbase + (long long)n * p.os_n;
+        e.os_hi = p.os_hi, e.os_lo = p.os_lo, e.per = p.per, e.M = p.M, e.m0 = mt * p.bn;
+        e.cend = min(p.bn, p.M - e.m0);
+        epilogue_rows<BF16, RND, MODE>(e, taddr, 32 * half);
+      } else {
+        // thread = weight row, columns = tokens
+        const int m = mt * kBM + q * 32 + lane;
+        const bool m_ok = m < p.M;
+        const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
+        const int n0 = nt * p.bn;
+        for (int c = 16 * half; c < p.bn; c += 32) {
+          if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
+          uint32_t r[16];
+          tmem_ld16(taddr + c, r);
+          tmem_ld_wait();
+          tmem_regs_ready(r);
+          if (m_ok) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (c0 + 16 * u < cend) tmem_ld16(taddr + c0 + 16 * u, rr[u]);
-          };
-          auto drain = [&](int c0, uint32_t(&rr)[4][16]) {
-            int hi = (m0 + c0) / p.per, lo = (m0 + c0) - hi * p.per;  // (m / per, m % per), kept incrementally
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int c = c0 + 16 * u;
-              if (c >= cend) break;
-              uint32_t(&r)[16] = rr[u];
-              tmem_regs_ready(r);
-              if (vec_out) {
-                uint32_t w[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                  w[k] = gemm_pack<BF16>(gemm_round<RND>(__uint_as_float(r[2 * k])), gemm_round<RND>(__uint_as_float(r[2 * k + 1])));
-                uint16_t* o16 = reinterpret_cast<uint16_t*>(p.out);
-                if (wide_out && m0 + c + 16 <= p.M) {
-                  // one full 32-byte sector per thread
-                  uint16_t* dst = o16 + nbase + (long long)hi * p.os_hi + lo;
-                  if (n_ok)
-                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-                  lo += 16;
-                  if (lo >= p.per) { lo -= p.per; ++hi; }
-                } else {
-#pragma unroll
-                  for (int h = 0; h < 2; ++h) {
-                    if (n_ok && m0 + c + 8 * h < p.M)
-                      *reinterpret_cast<uint4*>(o16 + nbase + (long long)hi * p.os_hi + lo) = make_uint4(w[4 * h], w[4 * h + 1], w[4 * h + 2], w[4 * h + 3]);
-                    lo += 8;
-                    if (lo >= p.per) { lo -= p.per; ++hi; }
-                  }
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  if (n_ok && m0 + c + j < p.M)
-                    gemm_store<BF16>(p.out, nbase + (long long)hi * p.os_hi + (long long)lo * p.os_lo, gemm_round<RND>(__uint_as_float(r[j])));
-                  if (++lo == p.per) { lo = 0; ++hi; }
-                }
-              }
-            }
-          };
-          uint32_t ra[4][16], rb[4][16];
-          int c0 = 64 * half;
-          if (c0 < cend) issue(c0, ra);
-          while (c0 < cend) {
-            tmem_ld_wait();
-            if (c0 + 128 < cend) issue(c0 + 128, rb);
-            drain(c0, ra);
-            c0 += 128;
-            if (c0 >= cend) break;
-            tmem_ld_wait();
-            if (c0 + 128 < cend) issue(c0 + 128, ra);
-            drain(c0, rb);
-            c0 += 128;
-          }
-        } else {
-          // thread = weight row, columns = tokens
-          const int m = mt * kBM + q * 32 + lane;
-          const bool m_ok = m < p.M;
-          const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
-          const int n0 = nt * p.bn;
-          for (int c = 16 * half; c < p.bn; c += 32) {
-            if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
-            uint32_t r[16];
-            tmem_ld16(taddr + c, r);
-            tmem_ld_wait();
-            tmem_regs_ready(r);
-            if (m_ok) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int n = n0 + c + j;
-                if (n < p.N) gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round<RND>(__uint_as_float(r[j])));
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + c + j;
+              if (n < p.N) {
+                const float v = __uint_as_float(r[j]);
+                gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round<RND>(v));
               }
             }
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
       }
-    };
-    if (p.round_out) run(RoundTag<true>{});
-    else run(RoundTag<false>{});
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -309,11 +317,11 @@ void umma_gemm_tiling(GemmParams& p) {
   p.nstages = nst > kMaxStages ? kMaxStages : nst;
 }
 
-template <bool BF16, bool TR>
+template <bool BF16, bool TR, int MODE, bool RND>
 static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
-    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR, MODE, RND>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     configured[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -327,8 +335,24 @@ static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, i
   cfg.attrs = at;
   cfg.numAttrs = 1;
   void* args[] = {const_cast<GemmParams*>(&p)};
-  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR>, args));
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR, MODE, RND>, args));
   return BLR_OK;
+}
+
+template <bool BF16>
+static int launch_dtype(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
+  if (!p.tokens_as_rows) {
+    return p.round_out ? launch_variant<BF16, false, 0, true>(p, grid, smem, dev, max_smem, stream)
+                       : launch_variant<BF16, false, 0, false>(p, grid, smem, dev, max_smem, stream);
+  }
+  if (p.round_out) {
+    if (mode == 2) return launch_variant<BF16, true, 2, true>(p, grid, smem, dev, max_smem, stream);
+    if (mode == 1) return launch_variant<BF16, true, 1, true>(p, grid, smem, dev, max_smem, stream);
+    return launch_variant<BF16, true, 0, true>(p, grid, smem, dev, max_smem, stream);
+  }
+  if (mode == 2) return launch_variant<BF16, true, 2, false>(p, grid, smem, dev, max_smem, stream);
+  if (mode == 1) return launch_variant<BF16, true, 1, false>(p, grid, smem, dev, max_smem, stream);
+  return launch_variant<BF16, true, 0, false>(p, grid, smem, dev, max_smem, stream);
 }
 
 int launch_umma_gemm(const GemmParams& p_in, cudaStream_t stream) {
@@ -347,12 +371,15 @@ int launch_umma_gemm(const GemmParams& p_in, cudaStream_t stream) {
   const int n_tiles = p.tokens_as_rows ? (p.N + kBM - 1) / kBM : (p.N + p.bn - 1) / p.bn;
   const long long tiles = (long long)p.G * m_tiles * n_tiles;
   const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-  if (p.is_bf16) {
-    return p.tokens_as_rows ? launch_variant<true, true>(p, grid, smem, dev, di.max_smem_optin, stream)
-                            : launch_variant<true, false>(p, grid, smem, dev, di.max_smem_optin, stream);
-  }
-  return p.tokens_as_rows ? launch_variant<false, true>(p, grid, smem, dev, di.max_smem_optin, stream)
-                          : launch_variant<false, false>(p, grid, smem, dev, di.max_smem_optin, stream);
+  // store width of the epilogue when tokens are the MMA rows: 16-byte stores need 8 consecutive outputs contiguous
+  // and aligned in memory; 32-byte stores 16 of them, 32-byte aligned, and no ragged tile edge
+  const bool vec_out = p.os_lo == 1 && (p.per & 7) == 0 && (p.M & 7) == 0 && (p.os_g & 7) == 0 && (p.os_n & 7) == 0 &&
+                       (p.os_hi & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+  const bool wide_out = vec_out && (p.per & 15) == 0 && (p.M & 15) == 0 && (p.os_g & 15) == 0 && (p.os_n & 15) == 0 &&
+                        (p.os_hi & 15) == 0 && (p.bn & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+  const int mode = wide_out ? 2 : vec_out ? 1 : 0;
+  return p.is_bf16 ? launch_dtype<true>(p, mode, grid, smem, dev, di.max_smem_optin, stream)
+                   : launch_dtype<false>(p, mode, grid, smem, dev, di.max_smem_optin, stream);
 }
 
 }  // namespace blr
