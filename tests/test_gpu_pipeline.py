@@ -52,6 +52,7 @@ BLAST_SHAPES = [
     (129, 11008, 4096, 16, 1488),  # down_proj at the reference's 50 %-parameter rank, ragged token count
     (65, 1152, 2304, 6, 192),      # six and nine blocks
     (197, 2304, 3456, 9, 384),
+    (100, 512, 288, 4, 64),        # Q = 72: 16-byte but not 32-byte output pieces
 ]
 
 
@@ -127,7 +128,7 @@ def test_low_rank_prefill(K, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(17, 256, 384), (200, 512, 1000), (2048, 4096, 11008)])
+@pytest.mark.parametrize("shape", [(17, 256, 384), (200, 512, 1000), (130, 264, 1001), (2048, 4096, 11008)])
 def test_dense_prefill(K, shape, dtype):
     N, I, O = shape
     x, Wt = orc.make_dense_inputs(N, I, O, dtype, seed=N % 79)
