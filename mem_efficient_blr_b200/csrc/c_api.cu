@@ -507,8 +507,8 @@ struct HostCall {
   void *x_dev, *out_dev;
 };
 
-// Copy-in on the library's stream into the next ring slot; the caller's stream then waits for it and for the
-// copy-out that last used the slot.
+// Copy-in on the library's stream into the next ring slot, after the copy-out that last used the slot; the caller's
+// stream then waits for the copy-in.
 static int stage_in(const void* x_host, int64_t ldx, int64_t N, int64_t I, int64_t O, void* staging, size_t staging_bytes,
                     cudaStream_t user, HostCall* hc) {
   BLR_REQUIRE(x_host != nullptr && staging != nullptr, BLR_ERR_ARG, "x_host and staging must not be null");
@@ -524,10 +524,9 @@ static int stage_in(const void* x_host, int64_t ldx, int64_t N, int64_t I, int64
   const size_t per = staging_bytes / kHostSlots / 256 * 256;
   hc->x_dev = static_cast<uint8_t*>(staging) + per * slot;
   hc->out_dev = static_cast<uint8_t*>(hc->x_dev) + align256((size_t)N * I * 2);
-  if (hp->used[slot]) {
-    BLR_CUDA_OK(cudaStreamWaitEvent(hp->s_in, hp->ev_k[slot], 0));   // the kernel that read this slot's x is done
-    BLR_CUDA_OK(cudaStreamWaitEvent(user, hp->ev_out[slot], 0));     // the copy-out of this slot's result is done
-  }
+  // the copy-out that last used the slot is done, and with it the kernel that read the slot's x (the copy-out waited
+  // for that kernel); the caller's stream inherits both through ev_in and so carries one wait per call
+  if (hp->used[slot]) BLR_CUDA_OK(cudaStreamWaitEvent(hp->s_in, hp->ev_out[slot], 0));
   if (ldx == I) BLR_CUDA_OK(cudaMemcpyAsync(hc->x_dev, x_host, (size_t)N * I * 2, cudaMemcpyHostToDevice, hp->s_in));
   else BLR_CUDA_OK(cudaMemcpy2DAsync(hc->x_dev, (size_t)I * 2, x_host, (size_t)ldx * 2, (size_t)I * 2, (size_t)N,
                                      cudaMemcpyHostToDevice, hp->s_in));

@@ -299,6 +299,17 @@ def test_host_buffer_entry_point(K, bits):
     _sync_ok(K)
     for o in outs:
         assert orc.rel_fro(o.float(), out[: o.shape[0]].float()) < 1e-3
+    # the prepared call: same entry point, arguments converted once
+    call = K.bq.BlastWqHostCall(*dq, bits)
+    outs = [torch.empty(n, O, dtype=torch.float16).pin_memory() for n in (5, 1, 4)]
+    for o in outs:
+        assert call(xh[: o.shape[0]], o) is o
+    K.bq.host_flush()
+    _sync_ok(K)
+    for o in outs:
+        assert orc.rel_fro(o.float(), out[: o.shape[0]].float()) < 1e-3
+    with pytest.raises(AssertionError):
+        call(xh[:, : I // 2], outs[0])
 
 
 def test_host_buffer_entry_point_16_bit(K):
