@@ -333,13 +333,79 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
           // (3) write z_i's piece into CTA i's zbuf.  Traffic through distributed shared memory: 2 N rs values per CTA.
           const int w = rs / nb, wv = w >> 3;
           const uint32_t ybase = smem_u32(ybuf), gbase = smem_u32(gbuf), sbase = smem_u32(sbuf), zbase = smem_u32(zbuf);
-          for (int e = ctid; e < nb * p.N * wv; e += kConsumerWarps * 32) {
-            const int j = e / (p.N * wv), rem = e - j * (p.N * wv), n = rem / wv, v = rem - n * wv;
-            const uint4 yv = ld_shared_cluster_v4(mapa_shared(ybase + (n * rs + blk * w + v * 8) * 2, j));
-            *reinterpret_cast<uint4*>(gbuf + ((j * NP + n) * w + v * 8) * 2) = yv;
+          // (two remote loads in flight per thread: their latency is what this step costs)
+          for (int e0 = ctid; e0 < nb * p.N * wv; e0 += 2 * kConsumerWarps * 32) {
+            const int e1 = e0 + kConsumerWarps * 32;
+            const bool two = e1 < nb * p.N * wv;
+            const int j0 = e0 / (p.N * wv), rem0 = e0 - j0 * (p.N * wv), n0 = rem0 / wv, v0 = rem0 - n0 * wv;
+            const int ee = two ? e1 : e0;
+            const int j1 = ee / (p.N * wv), rem1 = ee - j1 * (p.N * wv), n1 = rem1 / wv, v1 = rem1 - n1 * wv;
+            const uint4 ya = ld_shared_cluster_v4(mapa_shared(ybase + (n0 * rs + blk * w + v0 * 8) * 2, j0));
+            uint4 yb = ya;
+            if (two) yb = ld_shared_cluster_v4(mapa_shared(ybase + (n1 * rs + blk * w + v1 * 8) * 2, j1));
+            *reinterpret_cast<uint4*>(gbuf + ((j0 * NP + n0) * w + v0 * 8) * 2) = ya;
+            if (two) *reinterpret_cast<uint4*>(gbuf + ((j1 * NP + n1) * w + v1 * 8) * 2) = yb;
           }
           consumer_bar();  // gbuf complete; this CTA no longer reads its peers' ybuf
           if (ctid < nb) mbar_arrive_remote_relaxed(mapa_shared(read_done, ctid));
+          if constexpr (NT == 2) {
+            // 9..16 tokens: one thread couples two out-blocks x two tokens (n, n + 8) on 8 ranks, so that every
+            // unpacked factor and activation feeds two products
+            const int ipairs = (nb + 1) >> 1;
+            for (int e = ctid; e < ipairs * 8 * wv; e += kConsumerWarps * 32) {
+              const int ip = e / (8 * wv), rem = e - ip * (8 * wv), n0 = rem / wv, v = rem - n0 * wv;
+              const int i0 = 2 * ip, i1 = i0 + 1 < nb ? i0 + 1 : i0, n1 = n0 + 8;  // (clamped: the extra result is dropped)
+              float a[2][2][8];
+#pragma unroll
+              for (int x = 0; x < 2; ++x)
+#pragma unroll
+                for (int y = 0; y < 2; ++y)
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) a[x][y][k] = 0.f;
+              for (int j = 0; j < nb; ++j) {
+                uint4 sv[2], yv[2];
+                lds128(sbase + ((i0 * nb + j) * w + v * 8) * 2, sv[0].x, sv[0].y, sv[0].z, sv[0].w);
+                lds128(sbase + ((i1 * nb + j) * w + v * 8) * 2, sv[1].x, sv[1].y, sv[1].z, sv[1].w);
+                lds128(gbase + ((j * NP + n0) * w + v * 8) * 2, yv[0].x, yv[0].y, yv[0].z, yv[0].w);
+                lds128(gbase + ((j * NP + n1) * w + v * 8) * 2, yv[1].x, yv[1].y, yv[1].z, yv[1].w);
+                float sf[2][8], yf[2][8];
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                  const uint32_t sw[4] = {sv[x].x, sv[x].y, sv[x].z, sv[x].w}, yw[4] = {yv[x].x, yv[x].y, yv[x].z, yv[x].w};
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    const float2 fs = unpack16x2<BF16>(sw[k]), fy = unpack16x2<BF16>(yw[k]);
+                    sf[x][2 * k] = fs.x, sf[x][2 * k + 1] = fs.y, yf[x][2 * k] = fy.x, yf[x][2 * k + 1] = fy.y;
+                  }
+                }
+#pragma unroll
+                for (int x = 0; x < 2; ++x)
+#pragma unroll
+                  for (int y = 0; y < 2; ++y)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) a[x][y][k] = fmaf(sf[x][k], yf[y][k], a[x][y][k]);
+              }
+              const int col = blk * w + v * 8;  // column of the slice, a multiple of 8
+#pragma unroll
+              for (int x = 0; x < 2; ++x) {
+                if (x == 1 && i0 + 1 >= nb) break;
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {
+                  const int n = y ? n1 : n0;
+                  if (n >= p.N) continue;
+                  float* r = a[x][y];
+                  if (p.round_z) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) r[k] = round_clamp_i8(r[k]);
+                  }
+                  uint4 o;
+                  o.x = pack16x2<BF16>(r[0], r[1]); o.y = pack16x2<BF16>(r[2], r[3]);
+                  o.z = pack16x2<BF16>(r[4], r[5]); o.w = pack16x2<BF16>(r[6], r[7]);
+                  st_shared_cluster_v4(mapa_shared(zbase + (col >> 6) * kABoxBytes + sw128(n, (col & 63) >> 3), x ? i1 : i0), o);
+                }
+              }
+            }
+          } else
           for (int e = ctid; e < nb * p.N * wv; e += kConsumerWarps * 32) {
             const int i = e / (p.N * wv), rem = e - i * (p.N * wv), n = rem / wv, v = rem - n * wv;
             float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
