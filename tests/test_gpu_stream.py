@@ -55,6 +55,8 @@ BLAST_SHAPES = [
     (3, 1152, 2304, 6, 192),      # six blocks: a cluster of 6 CTAs
     (16, 2304, 3456, 9, 384),     # nine blocks, beyond the portable cluster size
     (2, 3456, 1152, 9, 256),
+    (13, 768, 1152, 3, 384),      # odd block count with two token tiles and a ragged second tile
+    (11, 1152, 2304, 6, 384),
 ]
 
 
