@@ -72,9 +72,10 @@ int blr_version(void);
  * NULL switches it off. No reference counterpart. */
 int blr_debug_stream_timeline(void* dev_ptr);
 
-/* Test aid: BLAST and low-rank on 1..16 tokens (Monarch: 1..8) normally run on the cluster kernel where the shape
- * allows it; which = 1 sends those calls to the grid-wide streaming kernel instead,
- * which = 0 restores the automatic choice. Process-wide. No reference counterpart. */
+/* Test aid: which kernel serves 1..16 tokens.  0: automatic (BLAST with contraction-contiguous factors: the two-launch
+ * path; other BLAST layouts, low-rank, Monarch on up to 8 tokens: the cluster kernel; the rest: the grid-wide streaming
+ * kernel).  1: the grid-wide streaming kernel for everything.  2: automatic without the two-launch path.
+ * Process-wide (an atomic). No reference counterpart. */
 int blr_debug_decode_path(int which);
 
 /* Text of the last error on the calling thread. No reference counterpart (the reference raises
@@ -134,6 +135,11 @@ int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                      const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
                      int b, int P, int Q, int R, int flags,
                      void* out, int64_t ldo, void* stream);
+/* Status of the built-in scratch array on the current device (synchronises `stream`, allocates nothing): 0, or
+ * BLR_ERR_TIMEOUT if a blr_blast_static call since the last query gave up on a device-side wait, in which case that
+ * call's output is not valid.  A time-out stays recorded across later calls until this function has reported it
+ * once.  No reference counterpart. */
+int blr_blast_static_status(void* stream);
 
 /* BLAST with int8 / packed-int4 factors and fp16 scales.  No reference counterpart (the reference's
  * sym-quant kernels round activations, not weights); the format is: Uq int8 (b,Q,R) or uint8 (b,Q,R/2),

@@ -34,6 +34,7 @@ SIGNATURES = {
                               _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
     "blr_blast_static": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
                                 _int, _int, _int, _int, _int, _vp, _i64, _vp]),
+    "blr_blast_static_status": (_int, [_vp]),
     "blr_blast_wq": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                             _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
     "blr_monarch": (_int, [_vp, _i64, _i64, _int, _vp, _int, _int, _vp, _int,

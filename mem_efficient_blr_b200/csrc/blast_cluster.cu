@@ -543,9 +543,9 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
   __syncthreads();
   if (threadIdx.x == 0) BLR_STAMP(8);
 #undef BLR_STAMP
-  if (*abort_flag) {
-    for (int i = 0; i < 200; ++i) __nanosleep(1000);
-  }
+  // No CTA leaves while a peer may still read its ybuf, write its zbuf or arrive on its barriers: every wait above
+  // is bounded, so every thread of the cluster gets here, also after a time-out.
+  cluster_sync_all();
 }
 
 // ------------------------------------------------------------------ host side

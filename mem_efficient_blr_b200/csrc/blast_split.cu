@@ -1,0 +1,932 @@
+// BLAST on 1..16 tokens as two dependent launches (see blast_split.h for the decomposition).
+//
+// Weights sit in shared memory as 128-byte-swizzled boxes of rows x 128 B written by TMA (the layout of the other
+// weight-streaming kernels).  What happens to them depends on their width:
+//
+//   16-bit factors   mma.sync m16n8k16 on 16-bit activations, which are staged as boxes of [token][64 k] with
+//                    128-byte rows swizzled by token; a box holds exactly N token rows (fragment loads of rows N..
+//                    run into the next box: those rows only feed output columns that are dropped).
+//   int8 / int4      integer mma.sync m16n8k32 straight on the stored bytes - no widening instruction per weight,
+//                    which is what bounds a conversion-based path once everything is in shared memory.  The
+//                    activations of a token row are turned into 16-bit fixed point, q = rint(a / s) with
+//                    s = max|a| / 32512, and split into a signed high byte and an unsigned low byte
+//                    (q = 256 hi + lo); sum_k w_k a_k = s (256 sum_k w_k hi_k + sum_k w_k lo_k) with exact integer
+//                    sums, and the weight scales apply to the result.  The rounding of a to 16 bits of the row
+//                    maximum is finer in norm than the 11-bit mantissa the activations arrive with.
+//
+// After the wait on the kernel ahead everything is in shared memory and the time goes to latencies, not bandwidth:
+// sixteen consumer warps per CTA keep independent work in flight.  Registers are capped (launch bounds) so that a
+// front CTA and a back CTA of neighbouring launches fit one SM together - that is what lets a launch fetch its
+// weights while the launch before it computes.
+#include "blast_split.h"
+
+#include <stdlib.h>
+
+#include "ptx.cuh"
+#include "stream_device.cuh"
+#include "tmap.h"
+
+namespace blr {
+
+// Profiling builds (-DBLR_TIMELINE) record %globaltimer stamps per CTA: 16 slots per CTA, 256 CTAs per launch,
+// launches numbered by the host in order.  Off in the shipped library.
+#ifdef BLR_TIMELINE
+unsigned long long* g_split_timeline = nullptr;
+int g_split_timeline_launches = 0, g_split_timeline_next = 0;
+#define BLR_TL(slot)                                                                                              \
+  do {                                                                                                            \
+    if (p.timeline && threadIdx.x == 0 && blockIdx.x < 256) p.timeline[(size_t)blockIdx.x * 16 + (slot)] = globaltimer_ns(); \
+  } while (0)
+#define BLR_TLV(slot, val)                                                                                        \
+  do {                                                                                                            \
+    if (p.timeline && blockIdx.x < 256) p.timeline[(size_t)blockIdx.x * 16 + (slot)] = (unsigned long long)(val);  \
+  } while (0)
+#else
+#define BLR_TL(slot) do { } while (0)
+#define BLR_TLV(slot, val) do { } while (0)
+#endif
+
+static constexpr int kW = kSplitWarps;  // consumer warps per CTA
+
+// ---------------------------------------------------------------------------------------------------- shared-memory maps
+struct FrontLayout {
+  uint32_t w, xs, sx, s, vs, ypart, ybuf, bar, total;
+};
+struct BackLayout {
+  uint32_t ring, zs, sz, part, us, bars, total;
+};
+__host__ __device__ static inline uint32_t up16(uint32_t v) { return (v + 15u) & ~15u; }
+// Bytes of one token row of fixed-point activations over K contraction indices (2 bytes per index), padded so
+// that the 16-byte fragment loads of neighbouring token rows fall into different banks.
+__host__ __device__ static inline uint32_t fx_pitch(int K, int wbits) {
+  const uint32_t body = wbits == 8 ? ((uint32_t)(K + 31) / 32) * 64 : ((uint32_t)(K + 63) / 64) * 128;
+  return ((body + 127u) & ~127u) + (wbits == 8 ? 64u : 16u);
+}
+
+__host__ __device__ static inline FrontLayout front_layout(const SplitParams& p) {
+  const uint32_t np = p.N <= 8 ? 8 : 16;
+  const uint32_t abox = 16 / p.wbits, nbx = p.nch0 * abox, sl = p.nch0 < kW ? p.nch0 : kW;
+  FrontLayout L;
+  uint32_t o = 0;
+  L.w = o; o += (uint32_t)p.nch0 * p.b * 1024 + 1024;   // [chunk][in-block][8 rows][128 B] + one slab of slack
+  L.xs = o;                                             // activations of every (in-block, token) row
+  if (p.wbits == 16) o += (uint32_t)p.b * nbx * p.N * 128 + 2048;  // [in-block][box][token][128 B] + slack for rows N..15
+  else o += (uint32_t)p.b * p.N * fx_pitch(p.P, p.wbits);          // [in-block][token][fixed-point row]
+  L.sx = o; o += up16((uint32_t)p.b * p.N * 4);           // fixed-point scale of every (in-block, token) row
+  L.s = o; o += up16((uint32_t)p.bo * (p.b * 16 + 16));   // [out-block][in-block][8 ranks] 16-bit, padded rows
+  L.vs = o; o += (uint32_t)p.b * 8 * 4;                   // per-channel scales of the slice's rows
+  L.ypart = o; o += (uint32_t)p.b * sl * 8 * np * 4;      // [in-block][chunk slot][8 ranks][np tokens] fp32
+  L.ybuf = o; o += (uint32_t)p.b * p.N * 8 * 4;           // [in-block][token][8 ranks] fp32
+  L.bar = o; o += 16;
+  L.total = o + 1024;  // room to align the base to 1 KiB
+  return L;
+}
+
+__host__ __device__ static inline BackLayout back_layout(const SplitParams& p) {
+  const uint32_t np = p.N <= 8 ? 8 : 16;
+  const uint32_t abox = 16 / p.wbits, nbz = p.nch1 * abox, sl = p.nch1 < kW ? p.nch1 : kW;
+  BackLayout L;
+  uint32_t o = 0;
+  L.ring = o; o += (uint32_t)p.nstages * kSplitStageBytes;
+  L.zs = o;
+  if (p.wbits == 16) o += nbz * p.N * 128 + 2048;         // [box][token][128 B] + slack
+  else o += (uint32_t)p.N * fx_pitch(p.R, p.wbits);       // [token][fixed-point row]
+  L.sz = o; o += 32 * 4;                                  // fixed-point scale per token, then per-warp maxima
+  L.part = o; o += (uint32_t)p.gpc * sl * 16 * np * 4;    // [group][chunk slot][16 rows][np tokens] fp32
+  L.us = o; o += (uint32_t)p.gpc * 16 * 4;                // per-channel scales of the CTA's rows
+  L.bars = o; o += (2 * (uint32_t)p.nstages + 2) * 8;
+  L.total = o + 1024;
+  return L;
+}
+
+size_t split_front_smem(const SplitParams& p) { return front_layout(p).total; }
+size_t split_back_smem(const SplitParams& p) { return back_layout(p).total; }
+
+// ---------------------------------------------------------------------------------------------------- small helpers
+__device__ __forceinline__ void cp_async16_zfill(uint32_t smem_dst, const void* gsrc, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void named_bar(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ uint4 ld_global_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// D (s32) += A (s8, 16 x 32) * B (32 x 8): B signed or unsigned bytes.
+__device__ __forceinline__ void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------------------------------- fixed-point activations
+// Byte position, inside a token row, of the first of the 8 consecutive contraction indices k0 .. k0+7 (k0 a multiple
+// of 8), and how the 8 values spread over 32-bit words.  The order inside a row is the order in which the integer
+// MMA's B fragment wants them, so that a thread fetches a step's fragments of both planes with one 16-byte load:
+//   int8 weights  block of 32 k = 64 B: [tq 0..3][plane hi|lo][half 0|1][4 B]   k = 32 blk + 16 half + 4 tq + e
+//   int4 weights  block of 64 k = 128 B: [tq][parity][plane][half][4 B]          k = 64 blk + 2 (16 half + 4 tq + e) + parity
+//                 (a stored byte holds indices 2B and 2B+1; the low nibbles of a word form one MMA operand, the high
+//                 nibbles another, so even and odd indices are kept apart)
+// Values 0..3 and 4..7 of the run go to two words per plane (int8: tq and tq + 1; int4: even and odd indices).
+template <int WB>
+__device__ __forceinline__ void fx_store8(uint32_t row_addr, int k0, const int (&q)[8]) {
+  // byte 0 of q is the low plane (unsigned), byte 1 the high plane (signed): |q| <= 32512 < 2^15
+  if constexpr (WB == 8) {
+    const uint32_t blk = (uint32_t)k0 >> 5, o = (uint32_t)k0 & 31u, half = o >> 4, tq = (o & 15u) >> 2;  // tq is 0 or 2
+    const uint32_t base = row_addr + blk * 64u + tq * 16u + half * 4u;
+    sts32(base, prmt(prmt(q[0], q[1], 0x0051u), prmt(q[2], q[3], 0x0051u), 0x5410u));            // hi, tq
+    sts32(base + 8u, prmt(prmt(q[0], q[1], 0x0040u), prmt(q[2], q[3], 0x0040u), 0x5410u));       // lo, tq
+    sts32(base + 16u, prmt(prmt(q[4], q[5], 0x0051u), prmt(q[6], q[7], 0x0051u), 0x5410u));      // hi, tq + 1
+    sts32(base + 24u, prmt(prmt(q[4], q[5], 0x0040u), prmt(q[6], q[7], 0x0040u), 0x5410u));      // lo, tq + 1
+  } else {
+    const uint32_t blk = (uint32_t)k0 >> 6, B = ((uint32_t)k0 & 63u) >> 1, half = B >> 4, tq = (B & 15u) >> 2;
+    const uint32_t base = row_addr + blk * 128u + tq * 32u + half * 4u;
+    sts32(base, prmt(prmt(q[0], q[2], 0x0051u), prmt(q[4], q[6], 0x0051u), 0x5410u));            // even k, hi
+    sts32(base + 8u, prmt(prmt(q[0], q[2], 0x0040u), prmt(q[4], q[6], 0x0040u), 0x5410u));       // even k, lo
+    sts32(base + 16u, prmt(prmt(q[1], q[3], 0x0051u), prmt(q[5], q[7], 0x0051u), 0x5410u));      // odd k, hi
+    sts32(base + 24u, prmt(prmt(q[1], q[3], 0x0040u), prmt(q[5], q[7], 0x0040u), 0x5410u));      // odd k, lo
+  }
+}
+
+// rint(a * inv) for |a * inv| < 2^22, as the low bits of a float sum: 1.5 * 2^23 + q has q (two's complement) in its
+// low mantissa bits, and fx_store8 only takes bytes 0 and 1.  One FMA instead of a multiply and a conversion.
+__device__ __forceinline__ int fx_round(float a, float inv) { return __float_as_int(fmaf(a, inv, 12582912.f)); }
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack16x2<BF16>(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// A warp turns token rows of K 16-bit values (global memory, 16-byte aligned, rows `row_stride` elements apart in the
+// order given by row_src) into fixed-point rows in shared memory and their scales.  PPL = 16-byte pieces per lane and
+// row (K <= 256 PPL); 8 / PPL rows are loaded together so that their global-memory latencies overlap.
+template <bool BF16, int WB, int PPL, typename RowSrc>
+__device__ __forceinline__ void fx_quantize_rows(int first, int nrows, int step, RowSrc row_src, int K, uint32_t dst0, uint32_t pitch,
+                                                 float* scales, int lane) {
+  constexpr int RB = 8 / PPL;
+  const int pieces = K >> 3;
+  for (int r0 = first; r0 < nrows; r0 += step * RB) {
+    uint4 v[RB][PPL];
+#pragma unroll
+    for (int rb = 0; rb < RB; ++rb) {
+      const int r = r0 + rb * step;
+#pragma unroll
+      for (int i = 0; i < PPL; ++i) {
+        const int pc = i * 32 + lane;
+        v[rb][i] = make_uint4(0, 0, 0, 0);
+        if (r < nrows && pc < pieces) v[rb][i] = ld_global_cg_v4(row_src(r) + pc * 8);
+      }
+    }
+#pragma unroll
+    for (int rb = 0; rb < RB; ++rb) {
+      const int r = r0 + rb * step;
+      if (r >= nrows) break;  // warp-uniform
+      float m = 0.f;
+#pragma unroll
+      for (int i = 0; i < PPL; ++i) {
+        float f[8];
+        unpack8<BF16>(v[rb][i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const bool fin = m > 0.f && m < 3.0e38f;  // (an infinite or NaN row has no fixed-point form: it yields zeros)
+      const float inv = fin ? 32512.f / m : 0.f;
+      if (lane == 0) scales[r] = fin ? m / 32512.f : 0.f;
+      const uint32_t row_addr = dst0 + (uint32_t)r * pitch;
+#pragma unroll
+      for (int i = 0; i < PPL; ++i) {
+        const int pc = i * 32 + lane;
+        if (pc < pieces) {
+          float f[8];
+          int q[8];
+          unpack8<BF16>(v[rb][i], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) q[e] = fx_round(f[e], inv);
+          fx_store8<WB>(row_addr, pc * 8, q);
+        }
+      }
+    }
+  }
+}
+
+template <bool BF16, int WB, typename RowSrc>
+__device__ __forceinline__ void fx_quantize(int first, int nrows, int step, RowSrc row_src, int K, uint32_t dst0, uint32_t pitch,
+                                            float* scales, int lane) {
+  const int ppl = ((K >> 3) + 31) >> 5;
+  if (ppl <= 1) fx_quantize_rows<BF16, WB, 1>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
+  else if (ppl <= 2) fx_quantize_rows<BF16, WB, 2>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
+  else if (ppl <= 4) fx_quantize_rows<BF16, WB, 4>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
+  else fx_quantize_rows<BF16, WB, 8>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
+}
+
+// ---------------------------------------------------------------------------------------------------- chunk consumers
+// One 128-byte K-chunk of a 16-row weight group (rows 0..15 of the box at sW).  The shared-memory loads of a batch of
+// 32-byte windows are issued before the first use, so that their latencies overlap.
+// 16-bit weights: activation boxes at sA (one 64-wide box per chunk).
+template <bool BF16, int NT>
+__device__ __forceinline__ void sp_k16(uint32_t sW, uint32_t sA, float (&acc)[4][NT][4], int lane) {
+  const uint32_t jm = lane >> 3, l7 = lane & 7;
+  const uint32_t row = l7 + (jm & 1) * 8;
+  uint32_t a[4][4], bf[4][NT][2];
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    ldsm_x4(sW + sw128(row, ks * 2 + (jm >> 1)), a[ks][0], a[ks][1], a[ks][2], a[ks][3]);
+    load_bfrag<NT>(sA, ks, lane, bf[ks]);
+  }
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+    for (int n = 0; n < NT; ++n) mma_16816<BF16>(acc[ks][n], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bf[ks][n][0], bf[ks][n][1]);
+}
+
+// int8 weights, 128 k per chunk: four 32-byte windows = four m16n8k32 steps per plane.  sA: fixed-point row of token
+// 0 at the chunk's first index, rows `pitch` bytes apart; token rows past N read as zero.
+template <int NT>
+__device__ __forceinline__ void iq_k8(uint32_t sW, uint32_t sA, uint32_t pitch, int N, int (&hi)[NT][4], int (&lo)[NT][4], int lane) {
+  const uint32_t jm = lane >> 3, l7 = lane & 7, g = lane >> 2, tq = lane & 3;
+  const uint32_t row = l7 + (jm & 1) * 8;
+  // token rows past N read token 0's row: their output columns are never looked at, and integers have no NaN
+  uint32_t arow[NT];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) arow[n] = sA + ((int)(n * 8 + g) < N ? (n * 8 + g) : 0u) * pitch + tq * 16;
+  constexpr int WBATCH = NT == 1 ? 4 : 2;
+#pragma unroll
+  for (int w0 = 0; w0 < 4; w0 += WBATCH) {
+    uint32_t a[WBATCH][4], b[WBATCH][NT][4];
+#pragma unroll
+    for (int i = 0; i < WBATCH; ++i) {
+      const int win = w0 + i;
+      ldsm_x4(sW + sw128(row, win * 2 + (jm >> 1)), a[i][0], a[i][1], a[i][2], a[i][3]);
+#pragma unroll
+      for (int n = 0; n < NT; ++n) lds128(arow[n] + win * 64, b[i][n][0], b[i][n][1], b[i][n][2], b[i][n][3]);
+    }
+#pragma unroll
+    for (int i = 0; i < WBATCH; ++i)
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        imma_s8s8(hi[n], a[i][0], a[i][1], a[i][2], a[i][3], b[i][n][0], b[i][n][1]);
+        imma_s8u8(lo[n], a[i][0], a[i][1], a[i][2], a[i][3], b[i][n][2], b[i][n][3]);
+      }
+  }
+}
+
+// Packed int4 weights, 256 k per chunk: a 32-byte window holds 64 indices; the low nibbles of its words (shifted into
+// the high half of each byte: 16 v as a signed byte) multiply the even indices, the high nibbles the odd ones.  The
+// factor 16 is divided out with the scales.
+template <int NT, int WLO, int WHI>
+__device__ __forceinline__ void iq_k4_win(uint32_t sW, uint32_t sA, uint32_t pitch, int N, int (&hi)[NT][4], int (&lo)[NT][4], int lane) {
+  const uint32_t jm = lane >> 3, l7 = lane & 7, g = lane >> 2, tq = lane & 3;
+  const uint32_t row = l7 + (jm & 1) * 8;
+  uint32_t arow[NT];  // (token rows past N read token 0's row, see iq_k8)
+#pragma unroll
+  for (int n = 0; n < NT; ++n) arow[n] = sA + ((int)(n * 8 + g) < N ? (n * 8 + g) : 0u) * pitch + tq * 32;
+  constexpr int WBATCH = NT == 1 ? 2 : 1;
+#pragma unroll
+  for (int w0 = WLO; w0 < WHI; w0 += WBATCH) {
+    uint32_t r[WBATCH][4], be[WBATCH][NT][4], bo[WBATCH][NT][4];
+#pragma unroll
+    for (int i = 0; i < WBATCH; ++i) {
+      const int win = w0 + i;
+      ldsm_x4(sW + sw128(row, win * 2 + (jm >> 1)), r[i][0], r[i][1], r[i][2], r[i][3]);
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        lds128(arow[n] + win * 128, be[i][n][0], be[i][n][1], be[i][n][2], be[i][n][3]);
+        lds128(arow[n] + win * 128 + 16, bo[i][n][0], bo[i][n][1], bo[i][n][2], bo[i][n][3]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < WBATCH; ++i) {
+      uint32_t ae[4], ao[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ae[e] = (r[i][e] << 4) & 0xF0F0F0F0u;
+        ao[e] = r[i][e] & 0xF0F0F0F0u;
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        imma_s8s8(hi[n], ae[0], ae[1], ae[2], ae[3], be[i][n][0], be[i][n][1]);
+        imma_s8u8(lo[n], ae[0], ae[1], ae[2], ae[3], be[i][n][2], be[i][n][3]);
+        imma_s8s8(hi[n], ao[0], ao[1], ao[2], ao[3], bo[i][n][0], bo[i][n][1]);
+        imma_s8u8(lo[n], ao[0], ao[1], ao[2], ao[3], bo[i][n][2], bo[i][n][3]);
+      }
+    }
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void iq_k4(uint32_t sW, uint32_t sA, uint32_t pitch, int N, int (&hi)[NT][4], int (&lo)[NT][4], int lane) {
+  iq_k4_win<NT, 0, 4>(sW, sA, pitch, N, hi, lo, lane);
+}
+// Windows first .. first + 1 of the chunk: one scale group of 128 indices (first is 0 or 2).
+template <int NT>
+__device__ __forceinline__ void iq_k4_half(uint32_t sW, uint32_t sA, uint32_t pitch, int N, int (&hi)[NT][4], int (&lo)[NT][4], int lane,
+                                           int first) {
+  if (first == 0) iq_k4_win<NT, 0, 2>(sW, sA, pitch, N, hi, lo, lane);
+  else iq_k4_win<NT, 2, 4>(sW, sA, pitch, N, hi, lo, lane);
+}
+
+// Accumulators of one work item: fp32 chains for 16-bit weights, integer planes for quantised weights, and the
+// running fp32 total that per-group scales fold into.
+template <int NT, int WB>
+struct ItemAcc {
+  float acc[WB == 16 ? 4 : 1][NT][4];
+  int hi[NT][4], lo[NT][4];
+  float tot[NT][4];
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        tot[n][e] = 0.f;
+        hi[n][e] = lo[n][e] = 0;
+#pragma unroll
+        for (int q = 0; q < (WB == 16 ? 4 : 1); ++q) acc[q][n][e] = 0.f;
+      }
+  }
+  // integer planes -> tot, scaled by the two rows' group scales, and cleared (per-group scales)
+  __device__ __forceinline__ void fold(float s_row, float s_row8) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        tot[n][e] = fmaf(e < 2 ? s_row : s_row8, (float)(hi[n][e] * 256 + lo[n][e]), tot[n][e]);
+        hi[n][e] = lo[n][e] = 0;
+      }
+  }
+  // value of accumulator element (n, e) before the per-channel and activation scales
+  __device__ __forceinline__ float value(int n, int e, bool grouped) const {
+    if constexpr (WB == 16) return acc[0][n][e] + acc[1][n][e] + acc[2][n][e] + acc[3][n][e];
+    else return grouped ? tot[n][e] : (float)(hi[n][e] * 256 + lo[n][e]);  // < 2^31: one chunk of at most 256 indices per accumulator
+  }
+};
+
+// ---------------------------------------------------------------------------------------------------- front
+// Quotient by a small runtime divisor without a division: magic = ceil(2^32 / d), exact for t < 65536 (d = 1: magic 0).
+__device__ __forceinline__ uint32_t fastdiv(uint32_t t, uint32_t d, uint32_t magic) { return d == 1u ? t : __umulhi(t, magic); }
+
+// Clock stamps of profiling builds (thread 0, cycles since `tck`).
+#ifdef BLR_TIMELINE
+#define BLR_CK(slot) do { if (threadIdx.x == 0) BLR_TLV(slot, clock64() - tck); } while (0)
+#else
+#define BLR_CK(slot) do { } while (0)
+#endif
+
+template <bool BF16, int NT, bool GS, int WB>
+__global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(const __grid_constant__ SplitParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  constexpr int NP = NT * 8;
+  constexpr int wbits = WB, abox = 16 / WB;
+  constexpr bool FX = WB != 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, nb = p.b, bo = p.bo, nch = p.nch0, R = p.R;
+  const int nbx = nch * abox, SL = nch < kW ? nch : kW;
+  const int r0 = blockIdx.x * kSplitRanks;
+  const uint32_t xbox = (uint32_t)N * 128u, xpitch = FX ? fx_pitch(p.P, WB) : 0u;
+  const FrontLayout L = front_layout(p);
+  const uint32_t bar = smem_base + L.bar;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.bar + 8);
+  float* vs = reinterpret_cast<float*>(smem + L.vs);
+  float* sx = reinterpret_cast<float*>(smem + L.sx);
+  float* ypart = reinterpret_cast<float*>(smem + L.ypart);
+  float* ybuf = reinterpret_cast<float*>(smem + L.ybuf);
+#ifdef BLR_TIMELINE
+  long long tck = 0;
+#endif
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar, 1);
+    mbar_init_fence();
+  }
+  BLR_TL(0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __syncthreads();
+  // ---- everything that does not depend on the kernel ahead: the slice's rows of every V_j, its coupling factors, scales
+  if (tid == 0) {
+    mbar_arrive_expect_tx(bar, (uint32_t)nch * nb * 1024u);
+    constexpr int kstep = wbits == 16 ? 64 : 128;
+    for (int c = 0; c < nch; ++c) tma_load_3d(smem_base + L.w + (uint32_t)c * nb * 1024u, &p.tmV, c * kstep, r0, 0, bar);
+  }
+  {
+    const uint16_t* S = reinterpret_cast<const uint16_t*>(p.S);
+    const bool s_vec = S != nullptr && p.s_r == 1 && ((p.s_i | p.s_j) & 7) == 0 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
+    const uint32_t pitch = (uint32_t)nb * 16u + 16u;
+    for (int i = warp; i < bo; i += kW)
+      for (int j = lane; j < nb; j += 32) {
+        uint16_t* d = reinterpret_cast<uint16_t*>(smem + L.s + i * pitch + j * 16);
+        if (S == nullptr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] = BF16 ? (uint16_t)0x3F80 : (uint16_t)0x3C00;
+        } else if (s_vec) {
+          cp_async16(smem_u32(d), S + i * p.s_i + j * p.s_j + r0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] = S[i * p.s_i + j * p.s_j + (long long)(r0 + k) * p.s_r];
+        }
+      }
+    if (tid < nb * 8) {
+      float v = (!GS && p.v_scale != nullptr) ? __half2float(__ldg(p.v_scale + (long long)(tid >> 3) * R + r0 + (tid & 7))) : 1.f;
+      if (WB == 4) v *= 0.0625f;  // the int4 operands are 16 v
+      vs[tid] = v;
+    }
+  }
+  BLR_TL(1);
+  // One warp waits for the kernel ahead; the others sleep at the barrier.
+  if (warp == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+  __syncthreads();
+  BLR_TL(2);
+#ifdef BLR_TIMELINE
+  tck = clock64();
+#endif
+  // ---- x, all of it, one (in-block, token) row per warp and turn
+  {
+    const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
+    const int nrows = nb * N;
+    if constexpr (FX) {
+      const long long ldx = p.ldx;
+      const int P = p.P;
+      const uint32_t mN = p.magic_N;
+      auto row_src = [&](int r) {
+        const int j = (int)fastdiv((uint32_t)r, (uint32_t)N, mN), n = r - j * N;
+        return x + (long long)n * ldx + (long long)j * P;
+      };
+      fx_quantize<BF16, WB>(warp, nrows, kW, row_src, P, smem_base + L.xs, xpitch, sx, lane);
+    } else {
+      // [in-block][64-wide box][token][128 B], zero past P
+      const int cpr = nbx * 8;  // 16-byte pieces per row
+      for (int rowi = warp; rowi < nrows; rowi += kW) {
+        const int j = (int)fastdiv((uint32_t)rowi, (uint32_t)N, p.magic_N), n = rowi - j * N;
+        const uint16_t* src = x + (long long)n * p.ldx + (long long)j * p.P;
+        const uint32_t dst0 = smem_base + L.xs + (uint32_t)(j * nbx * N + n) * 128u;
+        for (int ch = lane; ch < cpr; ch += 32) {
+          const int kb = ch >> 3, c16 = ch & 7, k = ch * 8;
+          const bool in = k < p.P;
+          cp_async16_zfill(dst0 + (uint32_t)kb * xbox + (uint32_t)((c16 ^ (n & 7)) << 4), src + (in ? k : 0), in ? 16u : 0u);
+        }
+      }
+    }
+  }
+  cp_async_wait_all();
+  BLR_CK(7);
+  bool ok = mbar_wait(bar, 0, abort_flag);
+  if (__syncthreads_or(ok ? 0 : 1)) {
+    if (tid == 0) atomicExch(p.status, 1u);
+    return;
+  }
+  BLR_CK(8);
+  // ---- y_j on the slice.  Work item = (in-block j, chunk c), numbered t = j*nch + c; warp w takes t = w, w + 16, ...
+  // Consecutive items of a warp that belong to one j (only with more than 16 chunks per row) share an accumulator,
+  // which goes to the partial-sum slot (j, first chunk % 16).  Rows 8..15 of the MMA are the next block's rows (or
+  // slack) against the wrong activations: never read back.
+  {
+    const int g = lane >> 2, tq = lane & 3;
+    const int ngroups = GS ? p.P / kScaleGroup : 0;
+    constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;  // fixed-point bytes of one chunk's indices in a token row
+    const int nitems = nb * nch;
+    ItemAcc<NT, WB> A;
+    int jcur = -1, cfirst = 0;
+    auto flush = [&]() {
+      float* slot = ypart + ((jcur * SL + (cfirst & (kW - 1))) * 8 + g) * NP;
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        *reinterpret_cast<float2*>(slot + n * 8 + tq * 2) = make_float2(A.value(n, 0, GS), A.value(n, 1, GS));
+    };
+#pragma unroll 1
+    for (int t = warp; t < nitems; t += kW) {
+      const int j = (int)fastdiv((uint32_t)t, (uint32_t)nch, p.magic_nch0), c = t - j * nch;
+      if (j != jcur) {
+        if (jcur >= 0) flush();
+        A.clear();
+        jcur = j;
+        cfirst = c;
+      }
+      const uint32_t sW = smem_base + L.w + (uint32_t)(c * nb + j) * 1024u;
+      if constexpr (WB == 16) {
+        sp_k16<BF16, NT>(sW, smem_base + L.xs + (uint32_t)(j * nbx + c) * xbox, A.acc, lane);
+      } else {
+        const uint32_t sA = smem_base + L.xs + (uint32_t)(j * N) * xpitch + (uint32_t)c * kChunkAct;
+        float gsc = 0.f, gsc2 = 0.f;
+        if constexpr (GS) {
+          const __half* srow = p.v_scale + ((long long)j * R + r0 + g) * ngroups;
+          const int gi = c * (WB == 8 ? 1 : 2);
+          gsc = __half2float(__ldg(srow + gi));
+          if (WB == 4 && gi + 1 < ngroups) gsc2 = __half2float(__ldg(srow + gi + 1));
+        }
+        if constexpr (WB == 8) {
+          iq_k8<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
+          if constexpr (GS) A.fold(gsc, 0.f);
+        } else if constexpr (!GS) {
+          iq_k4<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
+        } else {
+          // two scale groups per chunk: the first two windows, then the last two
+          iq_k4_half<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane, 0);
+          A.fold(gsc, 0.f);
+          iq_k4_half<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane, 2);
+          A.fold(gsc2, 0.f);
+        }
+      }
+    }
+    if (jcur >= 0) flush();
+  }
+  BLR_CK(9);
+  __syncthreads();
+  BLR_CK(10);
+  BLR_TL(5);
+  // ---- y[j][n][r] = scales * sum of the chunk slots (fixed order)
+  for (int e = tid; e < nb * N * 8; e += kSplitFrontThreads) {
+    const int gg = e & 7, t = e >> 3, j = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - j * N;
+    const float* yp = ypart + (j * SL * 8 + gg) * NP + n;
+    float y = yp[0];
+    for (int cm = 1; cm < SL; ++cm) y += yp[cm * 8 * NP];
+    y *= vs[j * 8 + gg];
+    if constexpr (FX) y *= sx[t];
+    if (p.round_y) y = round_clamp_i8(y);
+    ybuf[t * 8 + gg] = y;
+  }
+  __syncthreads();
+  // ---- z[i][n][r] = sum_j S[i][j][r] y[j][n][r]: four partial sums per point (terms j = q mod 4), added in a fixed order
+  {
+    const uint32_t pitch = (uint32_t)nb * 16u + 16u;
+    for (int e = tid; e < bo * N * 8; e += kSplitFrontThreads) {
+      const int gg = e & 7, t = e >> 3, i = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - i * N;
+      const uint8_t* srow = smem + L.s + i * pitch + gg * 2;
+      const float* yp = ybuf + n * 8 + gg;
+      float a4[4] = {0.f, 0.f, 0.f, 0.f};
+      int j = 0;
+      for (; j + 4 <= nb; j += 4) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) a4[q] = fmaf(load16<BF16>(srow + (j + q) * 16, 0), yp[(j + q) * N * 8], a4[q]);
+      }
+      for (; j < nb; ++j) a4[0] = fmaf(load16<BF16>(srow + j * 16, 0), yp[j * N * 8], a4[0]);
+      float a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+      if (p.round_z) a = round_clamp_i8(a);
+      store16<BF16>(p.z, (long long)t * R + r0 + gg, a);
+    }
+  }
+  BLR_CK(11);
+  BLR_TL(6);
+}
+
+// ---------------------------------------------------------------------------------------------------- back
+template <bool BF16, int NT, bool GS, int WB>
+__global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(const __grid_constant__ SplitParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  constexpr int NP = NT * 8;
+  constexpr int wbits = WB, abox = 16 / WB;
+  constexpr bool FX = WB != 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, nch = p.nch1, R = p.R, Q = p.Q;
+  const int nbz = nch * abox, SL = nch < kW ? nch : kW;
+  const int nseg = (nch + kSplitStageChunks - 1) / kSplitStageChunks;
+  const int NST = p.nstages;
+  const int blk = blockIdx.x / p.cpb, part = blockIdx.x - blk * p.cpb;
+  const int gpb = (Q + 15) >> 4;
+  const int g_lo = part * p.gpc, g_hi = min(gpb, g_lo + p.gpc), ng = g_hi - g_lo;
+  const uint32_t zbox = (uint32_t)N * 128u, zpitch = FX ? fx_pitch(R, WB) : 0u;
+  const BackLayout L = back_layout(p);
+  const uint32_t full0 = smem_base + L.bars, empty0 = full0 + 8u * NST;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.bars + 16 * NST);
+  float* partial = reinterpret_cast<float*>(smem + L.part);
+  float* us = reinterpret_cast<float*>(smem + L.us);
+  float* sz = reinterpret_cast<float*>(smem + L.sz);
+  const bool resident = NST >= ng * nseg;  // the CTA's whole share has a stage of its own: no stage is reused
+#ifdef BLR_TIMELINE
+  long long tck = 0;
+#endif
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kW);
+    }
+    mbar_init_fence();
+  }
+  BLR_TL(0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __syncthreads();
+  if (ng <= 0) return;
+
+  if (warp == kW) {
+    // ------------------------------------------------ producer: the CTA's rows, one 16-row group x up to 8 chunks per stage.
+    // The ring is as long as the CTA's whole share where that fits, so the loads below all leave before anything is
+    // consumed, i.e. while the kernel ahead in the stream is still running.
+    constexpr int kstep = wbits == 16 ? 64 : 128;
+    RingPos rp;
+    bool ok = true;
+    for (int g = g_lo; g < g_hi && ok; ++g)
+      for (int seg = 0; seg < nseg; ++seg) {
+        if (!rp.first_pass) {
+          int w_ok = 1;
+          if (lane == 0) w_ok = mbar_wait(empty0 + 8 * rp.s, rp.use_parity ^ 1u, abort_flag) ? 1 : 0;
+          w_ok = __shfl_sync(0xffffffffu, w_ok, 0);
+          if (!w_ok) { ok = false; break; }
+        }
+        const int c_lo = seg * kSplitStageChunks, nc = min(kSplitStageChunks, nch - c_lo);
+        const uint32_t dst = smem_base + L.ring + rp.s * kSplitStageBytes, fb = full0 + 8 * rp.s;
+        if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)nc * kSplitChunkBytes);
+        __syncwarp();
+        if (lane < nc) tma_load_3d(dst + lane * kSplitChunkBytes, &p.tmU, (c_lo + lane) * kstep, g * 16, blk, fb);
+        rp.advance(NST);
+      }
+    return;
+  }
+  // ------------------------------------------------ consumers
+  const int ctid = tid;
+  constexpr int kCT = kW * 32;
+  const int gq = lane >> 2, tq = lane & 3;
+  for (int e = ctid; e < ng * 16; e += kCT) {
+    const int q = g_lo * 16 + e;
+    float v = (!GS && p.u_scale != nullptr && q < Q) ? __half2float(__ldg(p.u_scale + (long long)blk * Q + q)) : 1.f;
+    if (WB == 4) v *= 0.0625f;
+    us[e] = v;
+  }
+  if (ctid < 16) sz[16 + ctid] = 0.f;  // row maxima of the fixed-point conversion
+  BLR_TL(1);
+  if (warp == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+  named_bar(1, kCT);
+  BLR_TL(2);
+#ifdef BLR_TIMELINE
+  tck = clock64();
+#endif
+  // ---- z of this out-block
+  {
+    const uint16_t* z = reinterpret_cast<const uint16_t*>(p.z) + (long long)blk * N * R;
+    if constexpr (FX) {
+      // Every token row is shared out over wpr = 16 / N warps (at least one): each thread takes its 16-byte pieces,
+      // the warps' maxima meet in shared memory, then every thread converts its own pieces.
+      const int wpr = N >= kW ? 1 : kW / N, n = warp / wpr, wl = warp - n * wpr;
+      const int pieces = R >> 3;
+      float* pm = sz + 16;  // per-warp maxima (16 floats after the 16 row scales)
+      uint4 v[8];
+      float m = 0.f;
+      const bool have_row = n < N;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int pc = (i * wpr + wl) * 32 + lane;
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (have_row && pc < pieces) {
+          v[i] = ld_global_cg_v4(z + (long long)n * R + pc * 8);
+          float f[8];
+          unpack8<BF16>(v[i], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      // non-negative floats order like their bit patterns (a NaN would come out as the largest: the row then reads as zeros)
+      if (lane == 0 && have_row) atomicMax(reinterpret_cast<int*>(pm) + n, __float_as_int(m));
+      named_bar(1, kCT);
+      if (have_row) {
+        const float rm = pm[n];
+        const bool fin = rm > 0.f && rm < 3.0e38f;
+        const float inv = fin ? 32512.f / rm : 0.f;
+        if (wl == 0 && lane == 0) sz[n] = fin ? rm / 32512.f : 0.f;
+        const uint32_t row_addr = smem_base + L.zs + (uint32_t)n * zpitch;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int pc = (i * wpr + wl) * 32 + lane;
+          if (pc < pieces) {
+            float f[8];
+            int q[8];
+            unpack8<BF16>(v[i], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) q[e] = fx_round(f[e], inv);
+            fx_store8<WB>(row_addr, pc * 8, q);
+          }
+        }
+      }
+    } else {
+      // [64-wide box][token][128 B], zero past R.  A warp per run of 32 pieces of a token row.
+      const int cpr = nbz * 8, upr = (cpr + 31) >> 5;  // 16-byte pieces and warp-wide runs per row
+      for (int u = warp; u < N * upr; u += kW) {
+        const int n = u / upr, ch = (u - n * upr) * 32 + lane;
+        if (ch < cpr) {
+          const int kb = ch >> 3, c16 = ch & 7, k = ch * 8;
+          const bool in = k < R;
+          cp_async16_zfill(smem_base + L.zs + (uint32_t)(kb * N + n) * 128u + (uint32_t)((c16 ^ (n & 7)) << 4),
+                           z + (long long)n * R + (in ? k : 0), in ? 16u : 0u);
+        }
+      }
+    }
+  }
+  cp_async_wait_all();
+  named_bar(1, kCT);
+  BLR_CK(7);
+  BLR_TL(3);
+  // ---- products.  Work item = (group gl, chunk c), numbered t = gl*nch + c; warp w takes t = w, w + 16, ...; the
+  // items of a warp that belong to one group (more than 16 chunks per row) share an accumulator, which goes to the
+  // partial-sum slot (gl, first chunk % 16).  Stage of an item: gl*nseg + c / 8.  When the CTA's whole share is
+  // resident a warp only looks at the stages it reads; with a shorter ring every warp walks every stage in order and
+  // frees it, used or not.
+  bool ok = true;
+  const int ngroups = GS ? R / kScaleGroup : 0;
+  constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;
+  {
+    ItemAcc<NT, WB> A;
+    int gcur = -1, cfirst = 0;
+    auto flush = [&]() {
+      float* slot = partial + (size_t)(gcur * SL + (cfirst & (kW - 1))) * 16 * NP;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+          *reinterpret_cast<float2*>(slot + (gq + 8 * h) * NP + n * 8 + tq * 2) =
+              make_float2(A.value(n, 2 * h, GS), A.value(n, 2 * h + 1, GS));
+    };
+    auto item = [&](int gl, int c, uint32_t s) {
+      if (gl != gcur) {
+        if (gcur >= 0) flush();
+        A.clear();
+        gcur = gl;
+        cfirst = c;
+      }
+      const int g = g_lo + gl;
+      const uint32_t sW = smem_base + L.ring + s * kSplitStageBytes + (c & (kSplitStageChunks - 1)) * kSplitChunkBytes;
+      if constexpr (WB == 16) {
+        sp_k16<BF16, NT>(sW, smem_base + L.zs + (uint32_t)c * zbox, A.acc, lane);
+      } else {
+        const uint32_t sA = smem_base + L.zs + (uint32_t)c * kChunkAct;
+        float ga = 0.f, ga8 = 0.f, gb = 0.f, gb8 = 0.f;
+        if constexpr (GS) {
+          const int m = g * 16 + gq, gi = c * (WB == 8 ? 1 : 2);
+          const __half* srow = p.u_scale + ((long long)blk * Q + m) * ngroups;
+          if (m < Q) ga = __half2float(__ldg(srow + gi));
+          if (m + 8 < Q) ga8 = __half2float(__ldg(srow + 8 * ngroups + gi));
+          if (WB == 4 && gi + 1 < ngroups) {
+            if (m < Q) gb = __half2float(__ldg(srow + gi + 1));
+            if (m + 8 < Q) gb8 = __half2float(__ldg(srow + 8 * ngroups + gi + 1));
+          }
+        }
+        if constexpr (WB == 8) {
+          iq_k8<NT>(sW, sA, zpitch, N, A.hi, A.lo, lane);
+          if constexpr (GS) A.fold(ga, ga8);
+        } else if constexpr (!GS) {
+          iq_k4<NT>(sW, sA, zpitch, N, A.hi, A.lo, lane);
+        } else {
+          iq_k4_half<NT>(sW, sA, zpitch, N, A.hi, A.lo, lane, 0);
+          A.fold(ga, ga8);
+          iq_k4_half<NT>(sW, sA, zpitch, N, A.hi, A.lo, lane, 2);
+          A.fold(gb, gb8);
+        }
+      }
+    };
+    if (resident) {
+      const int nitems = ng * nch;
+#pragma unroll 1
+      for (int t = warp; t < nitems && ok; t += kW) {
+        const int gl = (int)fastdiv((uint32_t)t, (uint32_t)nch, p.magic_nch1), c = t - gl * nch;
+        const uint32_t s = (uint32_t)(gl * nseg + (c >> 3));
+        if (!mbar_wait(full0 + 8 * s, 0, abort_flag)) { ok = false; break; }
+        item(gl, c, s);
+      }
+    } else {
+      RingPos rp;
+#pragma unroll 1
+      for (int gl = 0; gl < ng && ok; ++gl) {
+        const int c0 = (warp - gl * nch) & (kW - 1);  // this warp's first chunk of the group (none if >= nch)
+#pragma unroll 1
+        for (int seg = 0; seg < nseg; ++seg) {
+          const uint32_t s = rp.s;
+          // chunk of this warp inside the stage: c = c0 + 16 m with seg*8 <= c < seg*8 + 8
+          const int ci = (c0 - seg * kSplitStageChunks) & (kW - 1), c = seg * kSplitStageChunks + ci;
+          if (!mbar_wait(full0 + 8 * s, rp.use_parity, abort_flag)) { ok = false; break; }
+          if (ci < kSplitStageChunks && c < nch) item(gl, c, s);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty0 + 8 * s);
+          rp.advance(NST);
+        }
+      }
+    }
+    if (gcur >= 0) flush();
+  }
+  BLR_CK(8);
+  named_bar(1, kCT);
+  BLR_CK(9);
+  BLR_TL(5);
+  if (*abort_flag) {
+    if (ctid == 0) atomicExch(p.status, 1u);
+    return;
+  }
+  // ---- out[n][blk*Q + q] = scales * sum over the chunk slots of the row (fixed order), consecutive threads on consecutive rows
+  {
+    const int rows = ng * 16;
+    for (int e = ctid; e < rows * N; e += kCT) {
+      const int n = e / rows, lr = e - n * rows, gl = lr >> 4, row = lr & 15;
+      const int q = (g_lo + gl) * 16 + row;
+      if (q >= Q) continue;
+      const float* sp = partial + (size_t)(gl * SL) * 16 * NP + row * NP + n;
+      float s = 0.f;
+      for (int cs = 0; cs < SL; ++cs) s += sp[cs * 16 * NP];
+      s *= us[lr];
+      if constexpr (FX) s *= sz[n];
+      store16<BF16>(p.out, (long long)n * p.ldo + (long long)blk * Q + q, s);
+    }
+  }
+  BLR_CK(10);
+  BLR_TL(6);
+}
+
+// ---------------------------------------------------------------------------------------------------- host side
+template <bool BF16, int NT, bool GS, int WB>
+static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != BLR_OK) return rc;
+  const size_t fs = split_front_smem(p), bs = split_back_smem(p);
+  BLR_REQUIRE((int)fs <= di.max_smem_optin && (int)bs <= di.max_smem_optin, BLR_ERR_UNSUPPORTED,
+              "needs %zu / %zu bytes of shared memory, device offers %d", fs, bs, di.max_smem_optin);
+  auto front = blr_blast_front_kernel<BF16, NT, GS, WB>;
+  auto back = blr_blast_back_kernel<BF16, NT, GS, WB>;
+  {
+    int dev = 0;
+    BLR_CUDA_OK(cudaGetDevice(&dev));
+    static bool configured[64] = {};  // per template instance
+    if (!configured[dev & 63]) {
+      BLR_CUDA_OK(cudaFuncSetAttribute(front, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+      BLR_CUDA_OK(cudaFuncSetAttribute(back, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
+      configured[dev & 63] = true;
+    }
+  }
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+#ifdef BLR_TIMELINE
+  SplitParams pf = p, pb = p;
+  pf.timeline = pb.timeline = nullptr;
+  if (g_split_timeline && g_split_timeline_next + 2 <= g_split_timeline_launches) {
+    pf.timeline = g_split_timeline + (size_t)(g_split_timeline_next++) * 256 * 16;
+    pb.timeline = g_split_timeline + (size_t)(g_split_timeline_next++) * 256 * 16;
+  }
+  void* args[] = {&pf};
+  void* args_b[] = {&pb};
+#else
+  void* args[] = {const_cast<SplitParams*>(&p)};
+  void** args_b = args;
+#endif
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = stream;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+#ifdef BLR_TIMELINE
+  if (getenv("BLR_NO_PDL")) cfg.numAttrs = 0;  // profiling builds only: launches fully serialised
+#endif
+  cfg.gridDim = dim3(p.R / kSplitRanks);
+  cfg.blockDim = dim3(kSplitFrontThreads);
+  cfg.dynamicSmemBytes = fs;
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)front, args));
+  cfg.gridDim = dim3(p.bo * p.cpb);
+  cfg.blockDim = dim3(kSplitBackThreads);
+  cfg.dynamicSmemBytes = bs;
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)back, args_b));
+  return BLR_OK;
+}
+
+int launch_blast_split(const SplitParams& p, int is_bf16, cudaStream_t stream) {
+  BLR_REQUIRE(p.N >= 1 && p.N <= kStreamMaxTokens, BLR_ERR_UNSUPPORTED, "the two-launch decode path takes 1..%d tokens", kStreamMaxTokens);
+  const bool gs = p.group != 0;
+#define BLR_SP(BF, NTV, GSV)                                                        \
+  (p.wbits == 16 ? launch_split_impl<BF, NTV, false, 16>(p, stream)                 \
+                 : (p.wbits == 8 ? launch_split_impl<BF, NTV, GSV, 8>(p, stream) : launch_split_impl<BF, NTV, GSV, 4>(p, stream)))
+  if (p.N <= 8) {
+    if (gs) return is_bf16 ? BLR_SP(true, 1, true) : BLR_SP(false, 1, true);
+    return is_bf16 ? BLR_SP(true, 1, false) : BLR_SP(false, 1, false);
+  }
+  if (gs) return is_bf16 ? BLR_SP(true, 2, true) : BLR_SP(false, 2, true);
+  return is_bf16 ? BLR_SP(true, 2, false) : BLR_SP(false, 2, false);
+#undef BLR_SP
+}
+
+}  // namespace blr
+
+#ifdef BLR_TIMELINE
+extern "C" int blr_debug_split_timeline(void* dev_ptr, int launches) {
+  blr::g_split_timeline = static_cast<unsigned long long*>(dev_ptr);
+  blr::g_split_timeline_launches = launches;
+  blr::g_split_timeline_next = 0;
+  return 0;
+}
+#endif

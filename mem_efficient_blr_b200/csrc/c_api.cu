@@ -2,10 +2,12 @@
 // (N <= 16 tokens) and the tensor-core pipeline (N > 16).
 #include "../../include/blr_b200.h"
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
 #include "blast_cluster.h"
+#include "blast_split.h"
 #include "pipeline.h"
 #include "stream.h"
 #include "tmap.h"
@@ -155,7 +157,75 @@ static int check_layout(int layout) {
 // ---------------------------------------------------------------------------------- BLAST (16-bit and quantised)
 // Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
 static constexpr int kSubsliceMinTokens = 4;
-static int g_decode_path = 0;  // 0: automatic, 1: grid-wide streaming kernel only (blr_debug_decode_path)
+// 0: automatic, 1: grid-wide streaming kernel only, 2: no two-launch path (cluster kernel where it applies)
+static std::atomic<int> g_decode_path{0};
+
+// Two-launch path (blast_split.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
+static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
+                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
+                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
+                       int64_t ldo, const Workspace& w, cudaStream_t stream) {
+  // Measured crossover against the cluster kernel on the Llama-7B shapes: the two-launch path wins up to 4 tokens
+  // with quantised factors (its fixed-point conversion of the activations grows with the token count) and up to
+  // 8 tokens with 16-bit factors.
+  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > (u_bits == 16 ? 8 : 4)) return 1;
+  if (u_layout != BLR_W_KMAJOR || v_layout != BLR_W_KMAJOR || u_bits != v_bits || b > kSplitMaxBlocks) return 1;
+  const int wb = u_bits;
+  const long long kbV = (long long)P * wb / 8, kbU = (long long)R * wb / 8;
+  if (R % kSplitRanks != 0 || P % 8 != 0 || kbV % 16 != 0 || kbU % 16 != 0 || (wb == 4 && ((P | R) & 1))) return 1;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ldx % 8 != 0) return 1;
+  if (group != 0 && (group != kScaleGroup || P % kScaleGroup != 0 || R % kScaleGroup != 0)) return 1;
+  if (wb != 16 && (P > 2048 || R > 2048)) return 1;  // a warp holds a whole activation row in registers while it scales it
+  DeviceInfo di;
+  int rc;
+  if ((rc = device_info(&di))) return rc;
+  SplitParams p = {};
+  p.x = x; p.S = S; p.v_scale = static_cast<const __half*>(v_scale); p.u_scale = static_cast<const __half*>(u_scale);
+  p.z = w.region_b; p.out = out; p.status = w.counters + 255;
+  p.ldx = ldx; p.ldo = ldo; p.s_i = s_i; p.s_j = s_j; p.s_r = s_r;
+  p.N = (int)N; p.b = b; p.bo = bo; p.P = P; p.Q = Q; p.R = R;
+  p.wbits = wb; p.group = group; p.round_y = act8; p.round_z = act8;
+  p.nch0 = (int)((kbV + 127) / 128);
+  p.nch1 = (int)((kbU + 127) / 128);
+  // back kernel: every CTA a run of 16-row groups of one out-block, about one CTA per SM
+  const int gpb = (Q + 15) / 16;
+  int cpb = di.sm_count / bo;
+  if (cpb < 1) cpb = 1;
+  if (cpb > gpb) cpb = gpb;
+  p.gpc = (gpb + cpb - 1) / cpb;
+  p.cpb = (gpb + p.gpc - 1) / p.gpc;
+  auto magic = [](int d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d); };
+  p.magic_N = magic((int)N); p.magic_nch0 = magic(p.nch0); p.magic_nch1 = magic(p.nch1);
+  if ((long long)b * p.nch0 >= 65536 || (long long)p.gpc * p.nch1 >= 65536) return 1;
+  p.nstages = 2;
+  const int fs = (int)split_front_smem(p);
+  if (fs > di.max_smem_optin) return 1;
+  // ring of the back kernel: the CTA's whole share if it fits beside a front CTA of the next call on the same SM
+  // (228 KB per SM, 1 KB of it reserved per CTA), else what fits, but never fewer than 4 stages
+  const int nseg = (p.nch1 + kSplitStageChunks - 1) / kSplitStageChunks, total = p.gpc * nseg;
+  const int other = (int)split_back_smem(p) - 2 * kSplitStageBytes;
+  int nst = (228 * 1024 - 2048 - fs - other) / kSplitStageBytes;
+  if (nst < 4) nst = 4;
+  if (nst > total) nst = total;
+  if (nst > (di.max_smem_optin - other) / kSplitStageBytes) nst = (di.max_smem_optin - other) / kSplitStageBytes;
+  if (nst < 1 || (nst < 2 && total > 1)) return 1;
+  p.nstages = nst;
+  const CUtensorMapDataType dt = wb == 16 ? dt16(dtype) : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const uint32_t inner_box = wb == 16 ? 64u : 128u;
+  {
+    const uint64_t dims[3] = {wb == 16 ? (uint64_t)P : (uint64_t)kbV, (uint64_t)R, (uint64_t)b};
+    const uint64_t str[2] = {(uint64_t)kbV, (uint64_t)R * kbV};
+    const uint32_t box[3] = {inner_box, (uint32_t)kSplitRanks, (uint32_t)b};
+    if ((rc = encode_tmap_3d(&p.tmV, dt, V, dims, str, box, Swz::B128))) return rc;
+  }
+  {
+    const uint64_t dims[3] = {wb == 16 ? (uint64_t)R : (uint64_t)kbU, (uint64_t)Q, (uint64_t)bo};
+    const uint64_t str[2] = {(uint64_t)kbU, (uint64_t)Q * kbU};
+    const uint32_t box[3] = {inner_box, 16u, 1u};
+    if ((rc = encode_tmap_3d(&p.tmU, dt, U, dims, str, box, Swz::B128))) return rc;
+  }
+  return launch_blast_split(p, dtype == BLR_DTYPE_BF16, stream);
+}
 
 static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                          const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
@@ -163,7 +233,7 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
                          int64_t ldo, const Workspace& w, cudaStream_t stream, int64_t v_row = 0, int64_t v_grp = 0,
                          int64_t u_row = 0, int64_t u_grp = 0) {
   const int np = N <= 8 ? 8 : 16;
-  if (g_decode_path == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
+  if (g_decode_path.load(std::memory_order_relaxed) == 1 || N > kClusterMaxTokens || b > 16 || bo != b || u_bits != v_bits || R % 8 != 0) return 1;
   if ((long long)b * Q * np * 4 > kClusterOut32Bytes) return 1;
   const int bf = dtype == BLR_DTYPE_BF16;
   ClusterParams p = {};
@@ -249,7 +319,7 @@ static int cluster_monarch(const void* x, int64_t ldx, int64_t N, int dtype, con
   const int np = 8;
   // one token tile; the permutation is gathered element by element, which for the torch layout (stride b between a
   // CTA's elements) overtakes the grid-wide kernel's barrier from about 6 tokens on
-  if (g_decode_path == 1 || N > (grouped ? 8 : 5) || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;
+  if (g_decode_path.load(std::memory_order_relaxed) == 1 || N > (grouped ? 8 : 5) || b > 16 || b < 2 || rank % b != 0 || rank % 8 != 0) return 1;
   if ((long long)b * Qs * np * 4 > kClusterOut32Bytes) return 1;
   const int per = rank / b, bf = dtype == BLR_DTYPE_BF16;
   DeviceInfo di;
@@ -319,9 +389,12 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   const int act8 = (flags & BLR_FLAG_ACT_INT8) ? 1 : 0;
 
   if (N <= kStreamMaxTokens) {
+    rc = split_blast(x, ldx, N, dtype, U, u_layout, u_bits, u_scale, V, v_layout, v_bits, v_scale, group, S, s_i, s_j, s_r, b, bo,
+                     P, Q, R, act8, out, ldo, w, stream);
+    if (rc <= 0) return rc;  // 0: launched, < 0: error, 1: not applicable -> cluster kernel
     rc = cluster_blast(x, ldx, N, dtype, U, u_layout, u_bits, u_scale, V, v_layout, v_bits, v_scale, group, S, s_i, s_j, s_r, b, bo,
                        P, Q, R, act8, out, ldo, w, stream);
-    if (rc <= 0) return rc;  // 0: launched, < 0: error, 1: not applicable -> grid-wide streaming kernel
+    if (rc <= 0) return rc;  // 1: not applicable -> grid-wide streaming kernel
     StreamParams p = {};
     p.nphases = 2; p.mix = 1; p.b = b; p.b_out = bo; p.R = R; p.round_z = act8;
     p.s_i = s_i; p.s_j = s_j; p.s_r = s_r; p.S = S;
@@ -345,7 +418,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
 // ---------------------------------------------------------------------------------- fixed scratch for blr_blast_static
 // Scratch of the streaming kernel (control words, fp32 y, 16-bit z) for callers that cannot hand over a
 // workspace.  The array lives in every device's copy of this module from load to exit.
-static constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB: b * n_tokens * R <= 699008 elements
+static constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB, 2 MiB + 1 KiB of it the fixed head: b * n_tokens * R up to about 349 000
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // Device address of the array on the current device.  In host code `g_static_scratch` is only a handle
@@ -380,8 +453,9 @@ int blr_debug_stream_timeline(void* dev_ptr) {
   return BLR_OK;
 }
 int blr_debug_decode_path(int which) {
-  BLR_REQUIRE(which == 0 || which == 1, BLR_ERR_ARG, "decode path must be 0 (automatic) or 1 (grid-wide kernel)");
-  g_decode_path = which;
+  BLR_REQUIRE(which >= 0 && which <= 2, BLR_ERR_ARG,
+              "decode path must be 0 (automatic), 1 (grid-wide kernel) or 2 (cluster kernel before the grid-wide one)");
+  g_decode_path.store(which, std::memory_order_relaxed);
   return BLR_OK;
 }
 const char* blr_last_error(void) { return blr::last_error(); }
@@ -442,11 +516,32 @@ int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype, co
   // The array keeps whatever the previous call left.  The control words and the part of the fp32 accumulation
   // area this shape can touch must start at zero; the kernels leave them zero, but a call that gave up on a wait
   // does not, and this entry point has no separate init call.
+  // The two status words (3 and 255) are left alone: they keep a time-out until blr_blast_static_status reads it.
   size_t head = (size_t)b * Q * 16 * sizeof(float);
   if (head > (size_t)kClusterOut32Bytes) head = kClusterOut32Bytes;
-  BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes + head, static_cast<cudaStream_t>(stream)));
+  uint8_t* wp = static_cast<uint8_t*>(ws);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BLR_CUDA_OK(cudaMemsetAsync(wp, 0, 3 * sizeof(unsigned), st));
+  BLR_CUDA_OK(cudaMemsetAsync(wp + 4 * sizeof(unsigned), 0, 251 * sizeof(unsigned), st));
+  BLR_CUDA_OK(cudaMemsetAsync(wp + kCtrlBytes, 0, head, st));
   return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b, P,
                     Q, R, flags, out, ldo, ws, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+}
+
+int blr_blast_static_status(void* stream) {
+  void* ws = nullptr;
+  int rc = static_scratch_ptr(&ws);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned words[256] = {};
+  BLR_CUDA_OK(cudaMemcpyAsync(words, ws, sizeof(words), cudaMemcpyDeviceToHost, st));
+  BLR_CUDA_OK(cudaStreamSynchronize(st));
+  if (words[3] == 0 && words[255] == 0) return BLR_OK;
+  uint8_t* wp = static_cast<uint8_t*>(ws);
+  BLR_CUDA_OK(cudaMemsetAsync(wp + 3 * sizeof(unsigned), 0, sizeof(unsigned), st));
+  BLR_CUDA_OK(cudaMemsetAsync(wp + 255 * sizeof(unsigned), 0, sizeof(unsigned), st));
+  set_last_error("a blr_blast_static call gave up on a device-side wait (status words %u, %u)", words[3], words[255]);
+  return BLR_ERR_TIMEOUT;
 }
 
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* Uq, const void* u_scale,

@@ -70,10 +70,11 @@ __device__ __forceinline__ void consume_m16(uint32_t sWt, uint32_t sA, int rg, f
 
 // int8 weights, k contiguous: box of rows x 128 k.  A thread's ldmatrix word holds k = 4t..4t+3 of a
 // 16-wide window, so the matching activation fragment is the 8 contiguous bytes at the same k.
+// kABox: distance between the two activation boxes of the chunk (a box of NT * 8 token rows by default).
 template <bool BF16, int NT>
-__device__ __forceinline__ void consume_k8(uint32_t sWt, uint32_t sA, int row0, float (&acc)[4][NT][4], int lane) {
+__device__ __forceinline__ void consume_k8(uint32_t sWt, uint32_t sA, int row0, float (&acc)[4][NT][4], int lane,
+                                           const uint32_t kABox = NT * 8 * 128) {
   const uint32_t jm = lane >> 3, l7 = lane & 7, g = lane >> 2, tq = lane & 3;
-  constexpr uint32_t kABox = NT * 8 * 128;
   const uint32_t row = row0 + l7 + (jm & 1) * 8;
 #pragma unroll
   for (int win = 0; win < 4; ++win) {  // 32-byte windows of the 128-byte row
@@ -101,10 +102,11 @@ __device__ __forceinline__ void consume_k8(uint32_t sWt, uint32_t sA, int row0, 
 // Packed int4 weights, k contiguous: box of rows x 256 k (128 bytes per row).  A thread's ldmatrix word
 // holds k = 8t..8t+7 of a 32-wide window as nibbles; nibbles (e, e+4) convert together, so the
 // activation pairs are permuted to (k_e, k_{e+4}) with prmt.
+// kABox: distance between the four activation boxes of the chunk.
 template <bool BF16, int NT>
-__device__ __forceinline__ void consume_k4(uint32_t sWt, uint32_t sA, int row0, float (&acc)[4][NT][4], int lane) {
+__device__ __forceinline__ void consume_k4(uint32_t sWt, uint32_t sA, int row0, float (&acc)[4][NT][4], int lane,
+                                           const uint32_t kABox = NT * 8 * 128) {
   const uint32_t jm = lane >> 3, l7 = lane & 7, g = lane >> 2, tq = lane & 3;
-  constexpr uint32_t kABox = NT * 8 * 128;
   const uint32_t row = row0 + l7 + (jm & 1) * 8;
 #pragma unroll
   for (int win = 0; win < 4; ++win) {  // 32-byte windows = 64 k = one activation box

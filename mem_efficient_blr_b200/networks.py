@@ -1,0 +1,292 @@
+"""Network-level glue around the structured linears: a Llama-7B-shaped decoder and a ViT-B/16-shaped encoder.
+
+The reference times whole HuggingFace models whose nn.Linear layers were swapped for its structured modules
+(models/llama7b.py:24-92, models/vit_b_patch16_224.py:69-131, utils.py:46-116).  No checkpoint or tokenizer can be
+fetched here, so the networks are built from the shapes alone with random weights: the same layer list, the same
+linears swapped (Llama: q/k/v/o and gate/up/down of every layer, lm_head stays dense; ViT: fused qkv, intermediate
+and output of every layer, the attention output projection stays dense), and around them plain PyTorch - RMSNorm /
+LayerNorm, rotary embedding, `scaled_dot_product_attention`, SwiGLU / GELU.  Those surrounding pieces are
+placeholders for what a serving stack would fuse; the structured linears are what this package is about.
+
+Decode runs against a static key/value cache (one write position per step, attention over the whole cache), so a
+step has fixed shapes and can be captured in a CUDA graph (`GraphedCall`).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import blast_kernels as bk
+from . import blast_sym_quant_kernels as bq
+
+
+# ------------------------------------------------------------------------------------------------ structured linears
+class BlastTorchLinear(nn.Module):
+    """BLAST linear on the torch layouts U (b,Q,R), Vt (b,R,P), S (b,b,R) (torch_funcs/blast_funcs.py:3-47), with a
+    variance-preserving random init: x ~ N(0,1) gives out ~ N(0,1) (Vt ~ N(0,1/P), S ~ U(0.5,1.5), U ~ N(0,1/(R b E[S^2])))."""
+
+    def __init__(self, in_features, out_features, b, rank, bias=False, device="cuda", dtype=torch.float16, generator=None):
+        super().__init__()
+        assert in_features % b == 0 and out_features % b == 0
+        self.in_features, self.out_features, self.b, self.rank = in_features, out_features, b, rank
+        P, Q = in_features // b, out_features // b
+        g = generator
+        rn = lambda *s: torch.randn(*s, generator=g)
+        self.U = nn.Parameter((rn(b, Q, rank) / math.sqrt(rank * b * 13.0 / 12.0)).to(device=device, dtype=dtype), requires_grad=False)
+        self.Vt = nn.Parameter((rn(b, rank, P) / math.sqrt(P)).to(device=device, dtype=dtype), requires_grad=False)
+        self.S = nn.Parameter((torch.rand(b, b, rank, generator=g) + 0.5).to(device=device, dtype=dtype), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype), requires_grad=False) if bias else None
+
+    def forward(self, x):
+        out = bk.blast_torch_layout(x, self.U, self.Vt, self.S)
+        if self.bias is not None:
+            out += self.bias
+        return out
+
+    def quantized(self, bits: int, group: int = 0) -> "BlastQuantLinear":
+        return BlastQuantLinear(self, bits, group)
+
+
+class BlastQuantLinear(nn.Module):
+    """The same layer with int8 / packed-int4 factors and fp16 scales (the format of blr_blast_wq)."""
+
+    def __init__(self, src: BlastTorchLinear, bits: int, group: int = 0):
+        super().__init__()
+        self.in_features, self.out_features, self.b, self.rank = src.in_features, src.out_features, src.b, src.rank
+        self.bits, self.group = bits, group
+        Uq, us, Vq, vs = bq.quantize_blast_factors(src.U.data, src.Vt.data, bits, group)
+        for name, t in (("Uq", Uq), ("u_scale", us), ("Vq", Vq), ("v_scale", vs), ("S", src.S.data)):
+            self.register_buffer(name, t)
+        self.bias = src.bias
+
+    def forward(self, x):
+        out = bq.blast_wq(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits, self.group)
+        if self.bias is not None:
+            out += self.bias
+        return out
+
+
+def make_linear(method: str, in_features: int, out_features: int, b: int, rank: int, bias: bool, device, dtype, generator):
+    """method: 'blast' (16-bit factors), 'blast_int8', 'blast_int4', or 'dense' (nn.Linear, the unstructured bar)."""
+    if method == "dense":
+        lin = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=dtype)
+        with torch.no_grad():
+            lin.weight.copy_((torch.randn(out_features, in_features, generator=generator) / math.sqrt(in_features)).to(dtype))
+            if bias:
+                lin.bias.zero_()
+        return lin.requires_grad_(False)
+    base = BlastTorchLinear(in_features, out_features, b, rank, bias, device, dtype, generator)
+    if method == "blast":
+        return base
+    if method in ("blast_int8", "blast_int4"):
+        return base.quantized(8 if method == "blast_int8" else 4)
+    raise ValueError(f"unknown method {method!r}")
+
+
+# ------------------------------------------------------------------------------------------------ Llama-shaped decoder
+@dataclass
+class LlamaShape:
+    """Llama-7B: 32 layers, d = 4096, 32 heads, FFN 11008 (SwiGLU), vocabulary 32000; BLAST b = 16 with the ranks of
+    the reference's configs/networks/llama7b.yaml (q/k/v/o 1024, gate/up/down 1488: 50 % of the dense parameters)."""
+    layers: int = 32
+    d: int = 4096
+    heads: int = 32
+    ffn: int = 11008
+    vocab: int = 32000
+    b: int = 16
+    rank_attn: int = 1024
+    rank_mlp: int = 1488
+    rope_theta: float = 10000.0
+    eps: float = 1e-6
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, d, eps, device, dtype):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(d, device=device, dtype=dtype), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x):
+        v = x.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (v * self.weight.float()).to(x.dtype)
+
+
+def _rope(q, k, cos, sin):
+    """q, k (B, H, T, hd); cos, sin (T, hd/2): rotate pairs (first half, second half) like HF's Llama."""
+    def rot(t):
+        t1, t2 = t.float().chunk(2, dim=-1)
+        return torch.cat((t1 * cos - t2 * sin, t2 * cos + t1 * sin), dim=-1).to(t.dtype)
+    return rot(q), rot(k)
+
+
+class LlamaLayer(nn.Module):
+    def __init__(self, shape: LlamaShape, method: str, device, dtype, generator):
+        super().__init__()
+        s, mk = shape, lambda i, o, r: make_linear(method, i, o, shape.b, r, False, device, dtype, generator)
+        self.heads, self.hd = s.heads, s.d // s.heads
+        self.q_proj, self.k_proj, self.v_proj, self.o_proj = (mk(s.d, s.d, s.rank_attn) for _ in range(4))
+        self.gate_proj, self.up_proj = mk(s.d, s.ffn, s.rank_mlp), mk(s.d, s.ffn, s.rank_mlp)
+        self.down_proj = mk(s.ffn, s.d, s.rank_mlp)
+        self.input_layernorm = RMSNorm(s.d, s.eps, device, dtype)
+        self.post_attention_layernorm = RMSNorm(s.d, s.eps, device, dtype)
+
+    def structured(self):
+        return [self.q_proj, self.k_proj, self.v_proj, self.o_proj, self.gate_proj, self.up_proj, self.down_proj]
+
+    def forward(self, x, cos, sin, kc, vc, pos, causal: bool):
+        """x (B, T, d); kc, vc (B, H, S, hd) static cache; pos (T,) int64 cache slots of these tokens.
+        causal: the T tokens are the whole sequence so far (prefill); else they attend to the whole cache."""
+        B, T, _ = x.shape
+        h = self.input_layernorm(x)
+        q = self.q_proj(h).view(B, T, self.heads, self.hd).transpose(1, 2)
+        k = self.k_proj(h).view(B, T, self.heads, self.hd).transpose(1, 2)
+        v = self.v_proj(h).view(B, T, self.heads, self.hd).transpose(1, 2)
+        q, k = _rope(q, k, cos, sin)
+        kc.index_copy_(2, pos, k)
+        vc.index_copy_(2, pos, v)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True) if causal else F.scaled_dot_product_attention(q, kc, vc)
+        x = x + self.o_proj(a.transpose(1, 2).reshape(B, T, -1))
+        h = self.post_attention_layernorm(x)
+        return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h))
+
+
+class LlamaDecoder(nn.Module):
+    """Decoder of the shape above with a static cache for `cache_len` positions and `batch` sequences."""
+
+    def __init__(self, shape: LlamaShape, method: str, batch: int, cache_len: int, device="cuda", dtype=torch.float16, seed=0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.shape, self.method, self.batch, self.cache_len = shape, method, batch, cache_len
+        self.embed_tokens = nn.Embedding(shape.vocab, shape.d, device=device, dtype=dtype)
+        with torch.no_grad():
+            self.embed_tokens.weight.copy_(torch.randn(shape.vocab, shape.d, generator=g).to(dtype))
+        self.embed_tokens.requires_grad_(False)
+        self.layers = nn.ModuleList(LlamaLayer(shape, method, device, dtype, g) for _ in range(shape.layers))
+        self.norm = RMSNorm(shape.d, shape.eps, device, dtype)
+        self.lm_head = make_linear("dense", shape.d, shape.vocab, 0, 0, False, device, dtype, g)
+        hd = shape.d // shape.heads
+        inv = 1.0 / (shape.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+        ang = torch.outer(torch.arange(cache_len, dtype=torch.float32), inv)
+        self.register_buffer("cos", ang.cos().to(device), persistent=False)
+        self.register_buffer("sin", ang.sin().to(device), persistent=False)
+        self.kcache = [torch.zeros(batch, shape.heads, cache_len, hd, device=device, dtype=dtype) for _ in range(shape.layers)]
+        self.vcache = [torch.zeros(batch, shape.heads, cache_len, hd, device=device, dtype=dtype) for _ in range(shape.layers)]
+
+    def structured_linears(self):
+        return [m for layer in self.layers for m in layer.structured()]
+
+    def _run(self, ids, pos, causal):
+        x = self.embed_tokens(ids)
+        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+        for i, layer in enumerate(self.layers):
+            x = layer(x, cos, sin, self.kcache[i], self.vcache[i], pos, causal)
+        return self.lm_head(self.norm(x[:, -1]))
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids (B, T), T <= cache_len: fills cache slots 0..T-1, returns the logits of the last position (B, vocab)."""
+        pos = torch.arange(ids.shape[1], device=ids.device)
+        return self._run(ids, pos, True)
+
+    @torch.no_grad()
+    def decode_step(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """ids (B, 1): one new token per sequence, written to cache slot pos (1,) and attending to the whole cache
+        (slots beyond the sequence's length must hold real keys: the benchmark decodes at a full cache)."""
+        return self._run(ids, pos, False)
+
+
+# ------------------------------------------------------------------------------------------------ ViT-shaped encoder
+@dataclass
+class ViTShape:
+    """ViT-B/16 at 224 x 224: 12 layers, d = 768, 12 heads, MLP 3072, 196 patches + class token = 197 tokens.
+    BLAST b = 16 with ranks for 50 % of the dense parameters: R (I + O + b^2) = I O / 2."""
+    layers: int = 12
+    d: int = 768
+    heads: int = 12
+    mlp: int = 3072
+    image: int = 224
+    patch: int = 16
+    b: int = 16
+    eps: float = 1e-12
+    ranks: dict = field(default_factory=lambda: {"qkv": 256, "intermediate": 288, "output": 288})
+
+
+class ViTLayer(nn.Module):
+    def __init__(self, shape: ViTShape, method: str, device, dtype, generator):
+        super().__init__()
+        s = shape
+        mk = lambda i, o, r: make_linear(method, i, o, s.b, r, True, device, dtype, generator)
+        self.heads = s.heads
+        self.qkv = mk(s.d, 3 * s.d, s.ranks["qkv"])                 # fused like fuse_qkv_in_vit (vit_b_patch16_224.py:14-66)
+        self.attn_out = make_linear("dense", s.d, s.d, 0, 0, True, device, dtype, generator)  # skipped by the reference's swap
+        self.intermediate = mk(s.d, s.mlp, s.ranks["intermediate"])
+        self.output = mk(s.mlp, s.d, s.ranks["output"])
+        self.ln1 = nn.LayerNorm(s.d, eps=s.eps, device=device, dtype=dtype).requires_grad_(False)
+        self.ln2 = nn.LayerNorm(s.d, eps=s.eps, device=device, dtype=dtype).requires_grad_(False)
+
+    def structured(self):
+        return [self.qkv, self.intermediate, self.output]
+
+    def forward(self, x):
+        B, T, d = x.shape
+        q, k, v = self.qkv(self.ln1(x)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v)
+        x = x + self.attn_out(a.transpose(1, 2).reshape(B, T, d))
+        return x + self.output(F.gelu(self.intermediate(self.ln2(x))))
+
+
+class ViTEncoder(nn.Module):
+    def __init__(self, shape: ViTShape, method: str, device="cuda", dtype=torch.float16, seed=0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        s = shape
+        self.shape, self.method = shape, method
+        self.patch = nn.Conv2d(3, s.d, s.patch, s.patch, device=device, dtype=dtype).requires_grad_(False)
+        ntok = (s.image // s.patch) ** 2 + 1
+        self.cls = nn.Parameter((torch.randn(1, 1, s.d, generator=g) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
+        self.posemb = nn.Parameter((torch.randn(1, ntok, s.d, generator=g) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
+        self.layers = nn.ModuleList(ViTLayer(s, method, device, dtype, g) for _ in range(s.layers))
+        self.ln = nn.LayerNorm(s.d, eps=s.eps, device=device, dtype=dtype).requires_grad_(False)
+
+    def structured_linears(self):
+        return [m for layer in self.layers for m in layer.structured()]
+
+    @torch.no_grad()
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        """images (B, 3, 224, 224) -> features (B, 197, d)."""
+        x = self.patch(images).flatten(2).transpose(1, 2)
+        x = torch.cat((self.cls.expand(x.shape[0], -1, -1), x), dim=1) + self.posemb
+        for layer in self.layers:
+            x = layer(x)
+        return self.ln(x)
+
+
+# ------------------------------------------------------------------------------------------------ CUDA-graph replay
+class GraphedCall:
+    """Captures `fn(*static_inputs)` once in a CUDA graph and replays it; inputs are updated by copying into the
+    static tensors.  The structured operators launch on the current stream from caller-provided tensors and their
+    per-stream workspace exists after the warm-up calls, so a capture contains no allocation of theirs."""
+
+    def __init__(self, fn, *static_inputs, warmup: int = 2):
+        self.fn, self.inputs = fn, static_inputs
+        self.stream = torch.cuda.Stream()
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            for _ in range(warmup):
+                self.out = fn(*static_inputs)
+            self.stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                self.out = fn(*static_inputs)
+        torch.cuda.current_stream().wait_stream(self.stream)
+
+    def __call__(self, *new_inputs):
+        for dst, src in zip(self.inputs, new_inputs):
+            dst.copy_(src)
+        self.graph.replay()
+        return self.out

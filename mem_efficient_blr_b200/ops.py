@@ -37,11 +37,19 @@ def _rows(x2: torch.Tensor) -> torch.Tensor:
     return x2
 
 
-def _need_cuda(*ts: torch.Tensor) -> None:
-    for t in ts:
+def _need_cuda(x: torch.Tensor, *factors: torch.Tensor) -> None:
+    """x may be any strided (N, I) view (it is repaired by _rows); factors go to the library as packed arrays, so a
+    transposed or sliced view would be read with the wrong strides: refuse it, as the reference's kernels do
+    (blast_kernels.py:1951-1952, low_rank_kernels.py:283-285)."""
+    for t in (x, *factors):
         if not t.is_cuda:
             raise RuntimeError("blr_b200 operators need CUDA tensors: there is no CPU implementation in this package")
-        assert t.is_contiguous() or t.dim() == 2, "factor tensors must be contiguous"
+    for t in factors:
+        assert t.is_contiguous(), "factor tensors must be contiguous"
+        assert t.device == x.device, "x and the factors must live on one device"
+    # the library launches on the current device (its descriptor cache and device attributes are per device)
+    assert x.device.index is None or x.device.index == torch.cuda.current_device(), \
+        f"tensors are on {x.device} but the current CUDA device is {torch.cuda.current_device()}: wrap the call in torch.cuda.device"
 
 
 def _eager() -> bool:

@@ -148,7 +148,7 @@ def test_blast_weight_quantised_per_group_scales(K, shape, bits):
     assert torch.equal(dUq.cpu(), Uq) and torch.equal(dVq.cpu(), Vq)
     lib = K.lib.load()
     try:
-        for path in (0, 1):
+        for path in (0, 1, 2):   # automatic (two-launch path up to 4 tokens), grid-wide kernel, cluster kernel
             assert lib.blr_debug_decode_path(path) == 0
             got = K.bq.blast_wq(x.to(DEV), dUq, dus, dVq, dvs, S.to(DEV), bits, G)
             _sync_ok(K)
@@ -165,11 +165,13 @@ def test_blast_weight_quantised_rejects_other_group_widths(K):
         K.bq.blast_wq(x.to(DEV), *q, S.to(DEV), 8, 64)
 
 
-def test_small_batches_on_the_grid_wide_kernel(K):
-    """BLAST on 1..16 tokens normally takes the cluster kernel; the grid-wide streaming kernel must give the same
-    answers (it is what runs when the shape does not fit a cluster)."""
+@pytest.mark.parametrize("path", [1, 2])
+def test_small_batches_on_the_other_decode_kernels(K, path):
+    """BLAST on few tokens normally takes the two-launch path; the cluster kernel (path 2: what runs for the layouts
+    and token counts that path does not take) and the grid-wide streaming kernel (path 1: what runs when a shape does
+    not fit a cluster) must give the same answers."""
     lib = K.lib.load()
-    assert lib.blr_debug_decode_path(1) == 0
+    assert lib.blr_debug_decode_path(path) == 0
     try:
         for N, I, O, b, R, bits in [(1, 4096, 11008, 16, 1024, 16), (5, 768, 768, 3, 128, 16),
                                     (4, 4096, 11008, 16, 1024, 8), (1, 4096, 11008, 16, 1024, 4),
@@ -200,7 +202,37 @@ def test_blast_act_int8_matches_reference_rounding(K):
     assert orc.rel_fro(got.float().cpu(), ref) < 3e-2
 
 
-MONARCH_SHAPES = [(1, 256, 512, 4, 64), (7, 768, 3072, 4, 768), (16, 4096, 4096, 16, 1024), (3, 4096, 11008, 16, 1536)]
+@pytest.mark.parametrize("N", [1, 4, 16])
+def test_blast_act_int8_intermediates_on_the_headline_layer(K, N):
+    """The reference's activation rounding (blast_sym_quant_kernels.py:105-108, 227-230) on the 4096 -> 11008 layer.
+    z is read back from the operator's workspace where the kernel leaves it (two-launch path and tensor-core pipeline
+    keep it as (block, token, rank) 16-bit values): it must hold integers in [-128, 127] that equal the oracle's
+    except where a product landed within rounding distance of a half-integer.  One unit of y moves z by S_ij <= 1.5, so
+    z may differ by up to 2 at such points; they must stay rare.  The output bound follows from the share of moved
+    intermediates measured here (a unit error in about 1 % of them is a relative error of about 0.1 / 37 per entry)."""
+    I, O, b, R = 4096, 11008, 16, 1024
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.bfloat16, seed=77 + N)
+    x = x * 2
+    ref, z8, y8 = orc.blast_act_int8(x, U, Vt, S)
+    from mem_efficient_blr_b200 import _lib as L
+    got = K.bk.blast_torch_layout(*_cuda(x, U, Vt, S), flags=L.FLAG_ACT_INT8)
+    _sync_ok(K)
+    err = orc.rel_fro(got.float().cpu(), ref)
+    assert err < 1e-2, err
+    if N <= 8:  # the two-launch path: z sits at the start of the 2-byte region of the workspace
+        lib = K.lib.load()
+        dev = torch.device(DEV)
+        ws = L.workspace(dev, L.stream_ptr(dev), lib.blr_workspace_bytes(N, b, R))
+        off = 1024 + (2 << 20) + ((b * N * R * 4 + 255) // 256) * 256
+        z = ws[off: off + b * N * R * 2].view(torch.bfloat16).reshape(b, N, R).float().cpu()
+        assert torch.equal(z, z.round()) and z.abs().max() <= 128
+        d = (z - z8.float().reshape(b, N, R)).abs()
+        assert d.max() <= 2 and (d > 0).float().mean() < 0.02, (float(d.max()), float((d > 0).float().mean()))
+
+
+MONARCH_SHAPES = [(1, 256, 512, 4, 64), (7, 768, 3072, 4, 768), (16, 4096, 4096, 16, 1024), (3, 4096, 11008, 16, 1536),
+                  # four blocks on the Llama-7B projections (ranks for about half of the dense parameters)
+                  (1, 4096, 4096, 4, 1024), (16, 4096, 11008, 4, 1536), (1, 11008, 4096, 4, 1536)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -334,6 +366,61 @@ def test_repeated_calls_reuse_the_workspace(K):
     for o in (outs[0], outs[-1]):
         assert orc.rel_fro(o.float().cpu(), ref) < TOL
     assert orc.rel_fro(outs[-1].float().cpu(), outs[0].float().cpu()) < 1e-3
+
+
+def test_two_launch_path_is_bitwise_reproducible(K):
+    """Up to 4 tokens (8 with 16-bit factors) every sum has a fixed order: repeated calls agree bit for bit."""
+    for bits, N in ((16, 1), (16, 8), (8, 1), (8, 4), (4, 3)):
+        x, U, Vt, S = orc.make_blast_inputs(N, 4096, 11008, 16, 1024, torch.float16, seed=N)
+        if bits == 16:
+            args = _cuda(x, U, Vt, S)
+            outs = [K.bk.blast_torch_layout(*args) for _ in range(4)]
+        else:
+            q = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), bits)
+            xd, Sd = _cuda(x, S)
+            outs = [K.bq.blast_wq(xd, *q, Sd, bits) for _ in range(4)]
+        _sync_ok(K)
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0]), (bits, N)
+
+
+def test_timeout_status_is_reported_and_cleared(K):
+    """A kernel that gives up on a device-side wait leaves a non-zero status word in the workspace.  No wait is made
+    to run out here: the word is written from the host, as a kernel would have left it, and the host side must
+    report BLR_ERR_TIMEOUT, and after blr_workspace_init report success and compute correctly again."""
+    from mem_efficient_blr_b200 import _lib as L
+    x, U, Vt, S = orc.make_blast_inputs(2, 512, 768, 4, 128, torch.float16, seed=8)
+    args = _cuda(x, U, Vt, S)
+    K.bk.blast_torch_layout(*args)
+    _sync_ok(K)
+    dev = torch.device(DEV)
+    st = L.stream_ptr(dev)
+    lib = K.lib.load()
+    ws = L.workspace(dev, st, lib.blr_workspace_bytes(2, 4, 128))
+    for word in (3, 255):   # grid-wide kernel's status, cluster / two-launch kernels' status
+        ws[4 * word: 4 * word + 4].copy_(torch.tensor([1, 0, 0, 0], dtype=torch.uint8))
+        torch.cuda.synchronize()
+        assert lib.blr_workspace_status(ws.data_ptr(), st) == -7
+        assert b"gave up" in lib.blr_last_error()
+        with pytest.raises(RuntimeError):
+            ws[4 * word: 4 * word + 4].copy_(torch.tensor([1, 0, 0, 0], dtype=torch.uint8))
+            torch.cuda.synchronize()
+            L.workspace_status(dev)      # raises and re-initialises the workspace
+        assert lib.blr_workspace_status(ws.data_ptr(), st) == 0
+        got = K.bk.blast_torch_layout(*args)
+        _sync_ok(K)
+        assert orc.rel_fro(got.float().cpu(), orc.blast(x, U, Vt, S)[0]) < TOL
+
+
+def test_non_contiguous_factors_are_refused(K):
+    """A transposed view has the right shape but the wrong strides for the packed layouts the library reads."""
+    x, Wt = orc.make_dense_inputs(3, 256, 256, torch.float16, seed=3)
+    xd, Wd = _cuda(x, Wt)
+    with pytest.raises(AssertionError, match="contiguous"):
+        K.dk.dense_torch_layout(xd, Wd.t())
+    x, Vt, Ut = orc.make_low_rank_inputs(3, 256, 256, 64, torch.float16, seed=3)
+    with pytest.raises(AssertionError, match="contiguous"):
+        K.lk.low_rank_torch_layout(x.to(DEV), Vt.to(DEV), Ut.to(DEV).t().contiguous().t())
 
 
 def test_argument_errors_are_reported(K):

@@ -39,12 +39,19 @@ def test_static_scratch_entry_matches_workspace_entry_twice(shape):
     want = bk.blast_torch_layout(xd, Ud, Vd, Sd).reshape(N, O).float()
     ref, _, _ = orc.blast(x, U, Vt, S)
     x2 = xd.reshape(N, I)
-    for attempt in range(2):
-        rc, got = _call_static(lib, L, x2, Ud, Vd, Sd, b, P, Q, R)
-        assert rc == 0, lib.blr_last_error()
-        torch.cuda.synchronize()
-        assert orc.rel_fro(got.float().cpu(), want.cpu()) < TOL, f"call {attempt}"
-        assert orc.rel_fro(got.float().cpu(), ref.reshape(N, O)) < TOL, f"call {attempt}"
+    # every decode kernel on the built-in array in turn: the two-launch path (0), the grid-wide kernel (1), the cluster
+    # kernel (2); the second call of each finds the leftovers of the call before it
+    try:
+        for path in (0, 1, 2):
+            assert lib.blr_debug_decode_path(path) == 0
+            for attempt in range(2):
+                rc, got = _call_static(lib, L, x2, Ud, Vd, Sd, b, P, Q, R)
+                assert rc == 0, lib.blr_last_error()
+                assert lib.blr_blast_static_status(L.stream_ptr(xd.device)) == 0, lib.blr_last_error()
+                assert orc.rel_fro(got.float().cpu(), want.cpu()) < TOL, f"path {path} call {attempt}"
+                assert orc.rel_fro(got.float().cpu(), ref.reshape(N, O)) < TOL, f"path {path} call {attempt}"
+    finally:
+        assert lib.blr_debug_decode_path(0) == 0
 
 
 def test_static_scratch_entry_rejects_oversized_problems():
