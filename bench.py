@@ -3,16 +3,24 @@
 
 Headline workload (the configuration the metric is quoted on): symmetric-quantised BLAST decode on the
 Llama-7B gate_proj shape, 4096 -> 11008, b = 16, R = 1024, int8 and packed-int4 factors with fp16
-per-channel scales, token counts 1, 4 and 16.  One *step* runs every (bits, N) point once over a
+per-channel scales, token counts 1, 4 and 16.  One *pass* runs every (bits, N) point once over a
 rotating set of weight replicas whose total footprint exceeds the L2 cache, so every launch streams
-its weights from HBM.  The metric is algorithmic bytes per second (weights + scales + S + x + out of
-every launch, divided by device time), summed over ranks.
+its weights from HBM; one *step* is PASSES_PER_STEP passes (so that the timed region lasts about a second
+and the clock sampler sees it).  The metric is algorithmic bytes per second (weights + scales + S + x + out
+of every launch, divided by device time), summed over ranks.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+Beside the headline the same JSON line carries, in top-level keys: the per-point times with the dense fp16
+cuBLAS bar (`sweep`), the layer sweep over all Llama-7B projections and operator families (`layer_sweep`), a
+Llama-7B-shaped decoder with BLAST linears - prefill at 2048 tokens and decode at batch 1/4/16/64 against a
+2048-token cache, 16-bit and int8 factors - and a ViT-B/16-shaped encoder (`llama7b_blast`, `vit_b16_blast`),
+and, on more than one GPU, BLAST sharded by output block with an all-gather (`row_block_sharding`).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
 
 With N > 1 launch under torchrun; every rank runs the same workload on its own GPU (independent
-token batches, replicated weights: weak scaling, no collective in the data path).
-`--impl reference` times the CPU restatement of the reference's torch path on the host cores.
+token batches, replicated weights: weak scaling, no collective in the data path of the headline).
+`--impl reference` times the reference's own torch path (torch_funcs/blast_funcs.py, copied unmodified under
+oracle/_ref/ by oracle/make_ref.py; the oracle's restatement if that copy is absent) on the host cores.
 """
 from __future__ import annotations
 
@@ -34,10 +42,14 @@ I_F, O_F, B_BLK, RANK = 4096, 11008, 16, 1024
 P_BLK, Q_BLK = I_F // B_BLK, O_F // B_BLK
 POINTS = [(8, 1), (8, 4), (8, 16), (4, 1), (4, 4), (4, 16)]  # (bits, tokens)
 L2_BYTES = 126 * 2 ** 20
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch from ncu captures (profiles/): the cluster kernel on
-# int8 factors and 1 token, the grid-wide streaming kernel on int8 factors and 16 tokens
-NCU_TRAFFIC = {"blr_blast_cluster_kernel": (16.474e6, "int8/N=1"), "blr_stream_kernel": (16.249e6, "int8/N=16")}
-CLUSTER_MAX_TOKENS = 16  # BLAST calls with up to 16 tokens run blr_blast_cluster_kernel on this layer's shape
+PASSES_PER_STEP = 25
+# Which kernels serve a point of the headline workload (the library's dispatch for this layer): up to 4 tokens the
+# two-launch path (two kernels per call), above it the cluster kernel (one).
+GROUPS = {"two_launch": ("blr_blast_front_kernel+blr_blast_back_kernel", 2), "cluster": ("blr_blast_cluster_kernel", 1)}
+
+
+def group_of(n: int) -> str:
+    return "two_launch" if n <= 4 else "cluster"
 
 
 def algorithmic_bytes(bits: int, n: int) -> float:
@@ -45,13 +57,23 @@ def algorithmic_bytes(bits: int, n: int) -> float:
     return bits / 8 * RANK * (I_F + O_F) + 2 * B_BLK * B_BLK * RANK + 2 * n * (I_F + O_F) + 2 * (B_BLK * Q_BLK + B_BLK * RANK)
 
 
-def peak_hbm_gbs():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def measured_peaks():
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
     except Exception:
-        return 6650.0, "fallback"
+        return 6650.0, 1590.0, "fallback"
+
+
+def ncu_traffic(group: str):
+    """dram read + write bytes of one call of the group from the ncu capture summarised under profiles/ (None if absent)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            d = json.load(f)[group]
+        return float(d["bytes_per_call"]), d["note"]
+    except Exception:
+        return None, "no capture on file"
 
 
 class ClockSampler:
@@ -91,28 +113,56 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.rows)}
 
 
+def workload_config():
+    return {"workload": "symmetric-quantised BLAST decode, Llama-7B gate_proj 4096->11008, b=16, R=1024, "
+                        "int8 and packed-int4 factors with fp16 per-channel scales, tokens 1/4/16 (one launch per point per replica)",
+            "in_features": I_F, "out_features": O_F, "blocks": B_BLK, "rank": RANK,
+            "points": [f"int{b}/N={n}" for b, n in POINTS],
+            "passes_per_step": PASSES_PER_STEP,
+            "l2_policy": "weights rotate over replicas whose footprint exceeds L2 (inputs larger than L2)"}
+
+
 # ------------------------------------------------------------------------------------------ reference arm (CPU)
-def cpu_reference_times(threads: int, iters: int):
-    """Times the CPU restatement of torch_blast_baseline (fp32, dequantised factors) per (bits, N) point."""
+def cpu_blast_function():
+    """The reference's torch_blast_baseline from the unmodified copy under oracle/_ref/ ("reference"), else the oracle's
+    restatement of it ("port")."""
+    from oracle import make_ref
+    if make_ref.available():
+        sys.path.insert(0, make_ref.import_path())
+        try:
+            from torch_funcs.blast_funcs import torch_blast_baseline
+            return torch_blast_baseline, "reference"
+        finally:
+            sys.path.pop(0)
     from oracle import blr_oracle as orc
-    torch.set_num_threads(threads)
-    out = {}
-    x16, U, Vt, S = orc.make_blast_inputs(16, I_F, O_F, B_BLK, RANK, torch.float16, seed=0)
-    for bits in (8, 4):
-        Uq, us = orc.quantize_sym(U, bits)
-        Vq, vs = orc.quantize_sym(Vt, bits)
-        Ud, Vd = orc.dequantize_sym(Uq, us, bits), orc.dequantize_sym(Vq, vs, bits)
-        Sf = S.float()
-        for n in (1, 4, 16):
-            x = x16[:, :n].float()
-            orc.blast(x, Ud, Vd, Sf)
-            ts = []
-            for _ in range(iters):
-                t0 = time.perf_counter()
-                orc.blast(x, Ud, Vd, Sf)
-                ts.append(time.perf_counter() - t0)
-            out[(bits, n)] = statistics.median(ts)
-    return out
+    return orc.blast, "port"
+
+
+class CpuWorkload:
+    """The headline points on dequantised fp32 factors for the CPU function (the reference has no weight-quantised path)."""
+
+    def __init__(self, threads: int):
+        from oracle import blr_oracle as orc
+        torch.set_num_threads(threads)
+        self.fn, self.kind = cpu_blast_function()
+        x16, U, Vt, S = orc.make_blast_inputs(16, I_F, O_F, B_BLK, RANK, torch.float16, seed=0)
+        self.S = S.float()
+        self.x = {n: x16[:, :n].float() for n in (1, 4, 16)}
+        self.f = {}
+        for bits in (8, 4):
+            Uq, us = orc.quantize_sym(U, bits)
+            Vq, vs = orc.quantize_sym(Vt, bits)
+            self.f[bits] = (orc.dequantize_sym(Uq, us, bits), orc.dequantize_sym(Vq, vs, bits))
+
+    def step(self):
+        """One call per (bits, tokens) point; returns seconds per point."""
+        t = {}
+        for bits, n in POINTS:
+            Ud, Vd = self.f[bits]
+            t0 = time.perf_counter()
+            self.fn(self.x[n], Ud, Vd, self.S)
+            t[(bits, n)] = time.perf_counter() - t0
+        return t
 
 
 def run_reference(args):
@@ -120,35 +170,232 @@ def run_reference(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    iters = max(3, min(10, args.steps))
-    # warm-up happens inside cpu_reference_times (one untimed call per point)
     t0 = time.perf_counter()
-    times = cpu_reference_times(threads, iters)
+    wl = CpuWorkload(threads)
+    for _ in range(args.warmup):
+        wl.step()
+    steps = [wl.step() for _ in range(args.steps)]
+    per_point = {p: statistics.median(s[p] for s in steps) for p in POINTS}
+    step_s = sum(sum(s.values()) for s in steps) / len(steps)
     total_bytes = sum(algorithmic_bytes(b, n) for b, n in POINTS)
-    step_s = sum(times[p] for p in POINTS)
     value = total_bytes / step_s / 1e9
     line = {
         "impl": "reference", "metric": "blast_wq_decode_algorithmic_GBps", "value": value, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": iters, "warmup": 1, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(1),
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": f"{iters} timed calls per (bits, tokens) point of the CPU restatement of torch_blast_baseline "
-                                   "on dequantised fp32 factors (the reference has no weight-quantised path)"},
+        "config": workload_config(),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": wl.kind,
+                         "sample": "a step = one call per (bits, tokens) point of torch_blast_baseline "
+                                   "(torch_funcs/blast_funcs.py:3-47) on dequantised fp32 factors, all host cores"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "us_per_layer": {f"int{b}_n{n}": times[(b, n)] * 1e6 for b, n in POINTS},
+        "us_per_layer": {f"int{b}_n{n}": per_point[(b, n)] * 1e6 for b, n in POINTS},
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(replicas_note):
-    return {"workload": "symmetric-quantised BLAST decode, Llama-7B gate_proj 4096->11008, b=16, R=1024, "
-                        "int8 and packed-int4 factors with fp16 per-channel scales, tokens 1/4/16 (one launch per point per replica)",
-            "in_features": I_F, "out_features": O_F, "blocks": B_BLK, "rank": RANK,
-            "points": [f"int{b}/N={n}" for b, n in POINTS],
-            "l2_policy": "weights rotate over replicas whose footprint exceeds L2 (inputs larger than L2)",
-            "replicas": replicas_note}
+# ------------------------------------------------------------------------------------------ GPU helpers
+class GraphTimer:
+    def __init__(self):
+        self.side = torch.cuda.Stream()
+
+    def capture(self, fn):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(self.side):
+            with torch.cuda.graph(g, stream=self.side):
+                fn()
+        torch.cuda.synchronize()
+        return g
+
+    def us_per_call(self, fns, reps=10):
+        """Mean device time of one call of a list of callables captured back to back in one graph."""
+        g = self.capture(lambda: [f() for f in fns])
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b_.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b_) * 1e3 / (reps * len(fns))
+
+
+def time_ms(fn, reps, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b_.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b_) / reps
+
+
+def max_over_ranks(dist, dev, values):
+    if dist is None:
+        return values
+    t = torch.tensor(values, device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+# ------------------------------------------------------------------------------------------ network level
+def llama_leg(dev, rank, world, dist, quick):
+    """Llama-7B-shaped decoder, every attention / MLP linear a BLAST linear (b = 16, ranks 1024 / 1488): prefill at 2048
+    tokens (16-bit factors) and decode at batch 1/4/16/64 against a full 2048-token cache (16-bit and int8 factors),
+    each decode step replayed from a CUDA graph.  Token batches are independent per rank (data parallel): tokens/s
+    are summed over ranks, times are the maximum over ranks."""
+    from mem_efficient_blr_b200 import networks as nw
+    shape = nw.LlamaShape(layers=4) if quick else nw.LlamaShape()
+    batches = (1, 16) if quick else (1, 4, 16, 64)
+    cache = 2048
+    peak_hbm, _, _ = measured_peaks()
+    out = {"shape": {"layers": shape.layers, "d": shape.d, "heads": shape.heads, "ffn": shape.ffn, "vocab": shape.vocab,
+                     "blast_b": shape.b, "rank_attn": shape.rank_attn, "rank_mlp": shape.rank_mlp},
+           "kv_cache_tokens": cache, "dtype": "f16", "parallelism": f"dp{world} (token batches per rank)"}
+    gt = GraphTimer()
+    for method in ("blast", "blast_int8"):
+        torch.cuda.empty_cache()
+        model = nw.LlamaDecoder(shape, method, batch=max(batches), cache_len=cache, device=dev, dtype=torch.float16,
+                                seed=rank, init_on_device=True)
+        for kc, vc in zip(model.kcache, model.vcache):
+            kc.normal_(0, 0.5)
+            vc.normal_(0, 0.5)
+        wbytes = sum(p.numel() * p.element_size() for m in model.structured_linears() for p in list(m.parameters()) + list(m.buffers()))
+        res = {"structured_weight_bytes": wbytes, "weight_streaming_floor_ms": wbytes / (peak_hbm * 1e9) * 1e3, "decode": {}}
+        lin = model.structured_linears()
+        for B in batches:
+            ids = torch.randint(0, shape.vocab, (B, 1), device=dev)
+            pos = torch.tensor([cache - 1], device=dev)
+            step = nw.GraphedCall(model.decode_step, ids, pos)
+            ms = time_ms(step.graph.replay, 10, warm=3)
+            # the structured linears of the same step alone, same graph technique: their share of the step
+            xin = {m.in_features: torch.randn(B, m.in_features, device=dev, dtype=torch.float16) for m in lin}
+            g = gt.capture(lambda: [m(xin[m.in_features]) for m in lin])
+            ms_lin = time_ms(g.replay, 10, warm=3)
+            ms, ms_lin = max_over_ranks(dist, dev, [ms, ms_lin])
+            res["decode"][f"batch{B}"] = {"ms_per_token_step": ms, "tokens_per_s": world * B / (ms * 1e-3),
+                                          "structured_linears_ms": ms_lin, "structured_linears_share": ms_lin / ms}
+            del step, g
+        if method == "blast":
+            T = 512 if quick else 2048
+            ids = torch.randint(0, shape.vocab, (1, T), device=dev)
+            ms = time_ms(lambda: model.prefill(ids), 3, warm=2)
+            xin = {m.in_features: torch.randn(T, m.in_features, device=dev, dtype=torch.float16) for m in lin}
+            ms_lin = time_ms(lambda: [m(xin[m.in_features]) for m in lin], 3, warm=2)
+            ms, ms_lin = max_over_ranks(dist, dev, [ms, ms_lin])
+            res["prefill"] = {"tokens": T, "ms": ms, "tokens_per_s": world * T / (ms * 1e-3), "structured_linears_ms": ms_lin,
+                              "structured_linears_share": ms_lin / ms}
+        out[method] = res
+        del model, lin
+    torch.cuda.empty_cache()
+    return out
+
+
+def vit_leg(dev, rank, world, dist, quick):
+    """ViT-B/16-shaped encoder (197 tokens per image), fused qkv / intermediate / output linears as BLAST b = 16 with
+    about half of the dense parameters; images per second at several batch sizes, independent batches per rank."""
+    from mem_efficient_blr_b200 import networks as nw
+    shape = nw.ViTShape()
+    model = nw.ViTEncoder(shape, "blast", device=dev, dtype=torch.float16, seed=rank, init_on_device=True)
+    out = {"shape": {"layers": shape.layers, "d": shape.d, "heads": shape.heads, "mlp": shape.mlp, "tokens": 197,
+                     "blast_b": shape.b, "ranks": shape.ranks}, "dtype": "f16", "parallelism": f"dp{world} (image batches per rank)"}
+    for B in ((1, 32) if quick else (1, 16, 64, 256)):
+        img = torch.randn(B, 3, shape.image, shape.image, device=dev, dtype=torch.float16)
+        ms = time_ms(lambda: model(img), 5, warm=2)
+        (ms,) = max_over_ranks(dist, dev, [ms])
+        out[f"batch{B}"] = {"ms": ms, "images_per_s": world * B / (ms * 1e-3), "tokens_per_s": world * B * 197 / (ms * 1e-3)}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def sharding_leg(dev, rank, world, dist):
+    """BLAST sharded by output block over the ranks (gate_proj shape with the 50 %-parameter rank): every rank holds
+    b / world blocks of U and S and all of V, computes its columns, and one NCCL all_gather along the feature axis
+    assembles the row.  Microseconds per layer including the gather, against the whole layer on one GPU; the gathered
+    result is checked against the unsharded one on every rank."""
+    import mem_efficient_blr_b200.blast_kernels as bk
+    from mem_efficient_blr_b200 import dist as bd
+    R = 1488
+    g = torch.Generator(device=dev).manual_seed(7)   # same factors on every rank
+    U = (torch.randn(B_BLK, Q_BLK, R, generator=g, device=dev) / R ** 0.5).half()
+    Vt = (torch.randn(B_BLK, R, P_BLK, generator=g, device=dev) / P_BLK ** 0.5).half()
+    S = (torch.rand(B_BLK, B_BLK, R, generator=g, device=dev) + 0.5).half()
+    Ul, Sl = (t.contiguous() for t in bd.shard_blast_factors(U, S, rank, world))
+    out = {"layer": f"BLAST {I_F}->{O_F}, b={B_BLK}, R={R}, fp16", "ranks": world, "blocks_per_rank": B_BLK // world}
+    for n in (1, 16, 2048):
+        x = torch.randn(n, I_F, generator=g, device=dev).half()
+        full = bk.blast_torch_layout(x, U, Vt, S)
+        got = bd.blast_row_block_parallel(x, Ul, Vt, Sl, bk.blast_output_blocks)
+        torch.cuda.synchronize()
+        err = float((got.float() - full.float()).norm() / full.float().norm())
+        if not err < 1e-3:
+            raise SystemExit(f"rank {rank}: row-block sharding disagrees with the unsharded layer at {n} tokens: {err}")
+        dist.barrier()
+        us_full = time_ms(lambda: bk.blast_torch_layout(x, U, Vt, S), 50, warm=5) * 1e3
+        us_local = time_ms(lambda: bk.blast_output_blocks(x, Ul, Vt, Sl), 50, warm=5) * 1e3
+        dist.barrier()
+        us_shard = time_ms(lambda: bd.blast_row_block_parallel(x, Ul, Vt, Sl, bk.blast_output_blocks), 50, warm=5) * 1e3
+        us_full, us_local, us_shard = max_over_ranks(dist, dev, [us_full, us_local, us_shard])
+        out[f"n{n}"] = {"us_one_gpu": us_full, "us_local_part": us_local, "us_sharded_with_gather": us_shard,
+                        "speedup": us_full / us_shard, "efficiency": us_full / us_shard / world, "rel_err_vs_unsharded": err}
+    return out
+
+
+def layer_sweep(dev, quick):
+    """Every operator family at the three Llama-7B linear shapes (Monarch with 4 blocks, BLAST with 16), fp16, tokens
+    1 / 16 / 128 / 2048, ranks for about half of the dense parameters; roofline = max(bytes / HBM, flops / tensor)."""
+    import mem_efficient_blr_b200.blast_kernels as bk
+    import mem_efficient_blr_b200.dense_kernels as dk
+    import mem_efficient_blr_b200.low_rank_kernels as lk
+    import mem_efficient_blr_b200.monarch_kernels as mk
+    peak_hbm, peak_tf, _ = measured_peaks()
+    gt = GraphTimer()
+
+    def point(kind, i_f, o_f, r, n):
+        xn = torch.randn(n, i_f, device=dev, dtype=torch.float16)
+        h = lambda *shape, fan: torch.randn(*shape, device=dev, dtype=torch.float16) / fan ** 0.5
+        if kind == "blast":
+            wbytes, flops = 2 * r * (i_f + o_f) + 2 * B_BLK * B_BLK * r, 2 * n * r * (i_f + o_f + B_BLK * B_BLK)
+            mk_one = lambda: (h(B_BLK, o_f // B_BLK, r, fan=r), h(B_BLK, r, i_f // B_BLK, fan=i_f // B_BLK),
+                              torch.rand(B_BLK, B_BLK, r, device=dev, dtype=torch.float16) + 0.5)
+            call = lambda f: bk.blast_torch_layout(xn, *f)
+        elif kind == "monarch":
+            wbytes, flops = 2 * r * (i_f + o_f), 2 * n * r * (i_f + o_f)
+            mk_one = lambda: (h(4, r, i_f // 4, fan=i_f // 4), h(4, o_f // 4, r, fan=r))
+            call = lambda f: mk.monarch_torch_layout(xn, *f)
+        elif kind == "low_rank":
+            wbytes, flops = 2 * r * (i_f + o_f), 2 * n * r * (i_f + o_f)
+            mk_one = lambda: (h(r, i_f, fan=i_f), h(o_f, r, fan=r))
+            call = lambda f: lk.low_rank_torch_layout(xn, *f)
+        else:
+            wbytes, flops = 2 * i_f * o_f, 2 * n * i_f * o_f
+            mk_one = lambda: (h(o_f, i_f, fan=i_f),)
+            call = lambda f: dk.dense_torch_layout(xn, *f)
+        nrep = int(2 * L2_BYTES // wbytes) + 1
+        sets = [mk_one() for _ in range(nrep)]
+        us = gt.us_per_call([(lambda f=f: call(f)) for f in sets], reps=5)
+        nbytes = wbytes + 2 * n * (i_f + o_f)
+        roof = max(nbytes / (peak_hbm * 1e9), flops / (peak_tf * 1e12)) * 1e6
+        return {"us_per_layer": round(us, 2), "roofline_us": round(roof, 2), "frac": round(roof / us, 3)}
+
+    res = {}
+    tokens = (1, 2048) if quick else (1, 16, 128, 2048)
+    for lname, i_f, o_f, ranks in (("qkvo_4096x4096", 4096, 4096, {"blast": 1024, "monarch": 1024, "low_rank": 1024}),
+                                   ("gate_4096x11008", 4096, 11008, {"blast": 1488, "monarch": 1536, "low_rank": 1024}),
+                                   ("down_11008x4096", 11008, 4096, {"blast": 1488, "monarch": 1536, "low_rank": 1024})):
+        for kind in ("blast", "monarch", "low_rank", "dense"):
+            for n in tokens:
+                res[f"{lname}/{kind}/n{n}"] = point(kind, i_f, o_f, ranks.get(kind, 0), n)
+                torch.cuda.empty_cache()
+    return res
 
 
 # ------------------------------------------------------------------------------------------ our arm (GPU)
@@ -166,6 +413,7 @@ def run_ours(args):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
+    import mem_efficient_blr_b200.blast_kernels as bk
     import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
     from mem_efficient_blr_b200 import _lib
 
@@ -187,24 +435,18 @@ def run_ours(args):
     xs_host = {n: x16[0, :n].contiguous().pin_memory() for n in (1, 4, 16)}
     outs_host = {n: torch.empty(n, O_F, dtype=torch.float16).pin_memory() for n in (1, 4, 16)}
 
-    def kernel_of(n):
-        return "blr_blast_cluster_kernel" if n <= CLUSTER_MAX_TOKENS else "blr_stream_kernel"
-
-    KERNELS = sorted({kernel_of(n) for _, n in POINTS})
-
-    def launch_points(kernel=None):
-        count = 0
+    def launch_points(group=None):
+        calls = 0
         for bits, n in POINTS:
-            if kernel is not None and kernel_of(n) != kernel:
+            if group is not None and group_of(n) != group:
                 continue
             for q in reps[bits]:
                 bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
-                count += 1
-        return count
+                calls += 1
+        return calls
 
     if args.ncu_case.startswith("p16:"):
         # small case for a profiler capture of the tensor-core pipeline: the 16-bit layer on N tokens, three calls
-        import mem_efficient_blr_b200.blast_kernels as bk
         n = int(args.ncu_case.split(":")[1])
         xn = torch.randn(n, I_F, device=dev, dtype=torch.float16)
         for _ in range(3):
@@ -214,238 +456,110 @@ def run_ours(args):
         print(json.dumps({"ncu_case": args.ncu_case, "calls": 3}))
         return
     if args.ncu_case:
-        # small case for a profiler capture: a few eager launches of one point over distinct replicas
+        # small case for a profiler capture: a few eager calls of one point over distinct replicas
         bits, n = (int(t) for t in args.ncu_case.split(":"))
         for q in reps[bits][:6]:
             bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
         torch.cuda.synchronize()
         _lib.workspace_status(dev)
-        print(json.dumps({"ncu_case": args.ncu_case, "launches": 6}))
+        print(json.dumps({"ncu_case": args.ncu_case, "calls": 6}))
         return
 
-    launches = {k: launch_points(k) for k in KERNELS}
-    launches_per_step = sum(launches.values())
+    groups = sorted({group_of(n) for _, n in POINTS})
+    calls = {k: launch_points(k) for k in groups}
     torch.cuda.synchronize()
-    kbytes = {k: sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS if kernel_of(n) == k) for k in KERNELS}
-    bytes_per_step = sum(kbytes.values())
+    kbytes = {k: sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS if group_of(n) == k) for k in groups}
+    bytes_per_pass = sum(kbytes.values())
+    launches_per_pass = sum(calls[k] * GROUPS[k][1] for k in groups)
 
-    # ---- capture one step in CUDA graphs (the per-launch host work would otherwise bound the rate): one graph
-    # per kernel, replayed back to back, with an event between them so that each kernel's time is known
-    side = torch.cuda.Stream()
-    graphs = {}
-    with torch.cuda.stream(side):
-        for k in KERNELS:
-            launch_points(k)
-            torch.cuda.synchronize()
-            graphs[k] = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graphs[k], stream=side):
-                launch_points(k)
-    torch.cuda.synchronize()
+    # ---- capture one pass in CUDA graphs (the per-launch host work would otherwise bound the rate): one graph per
+    # kernel group, replayed back to back, with an event between them so that each group's time is known
+    gt = GraphTimer()
+    graphs = {k: gt.capture(lambda k=k: launch_points(k)) for k in groups}
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def one_step(ev=None):
+        for ps in range(PASSES_PER_STEP):
+            for i, k in enumerate(groups):
+                if ev is not None and ps == 0:
+                    ev[i].record()
+                graphs[k].replay()
+            if ev is not None and ps == 0:
+                ev[len(groups)].record()
+
     for _ in range(max(args.warmup, 3)):
-        for k in KERNELS:
-            graphs[k].replay()
+        one_step()
     barrier()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(KERNELS) + 1)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(groups) + 1)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
         barrier()
+        t_begin.record()
         for st in range(args.steps):
-            ev[st][0].record()
-            for i, k in enumerate(KERNELS):
-                graphs[k].replay()
-                ev[st][i + 1].record()
+            one_step(ev[st])
+        t_end.record()
         barrier()
-    step_ms = ev[0][0].elapsed_time(ev[-1][-1]) / args.steps
-    kernel_ms = {k: sum(ev[st][i].elapsed_time(ev[st][i + 1]) for st in range(args.steps)) / args.steps
-                 for i, k in enumerate(KERNELS)}
+    step_ms = t_begin.elapsed_time(t_end) / args.steps
+    # time of each group inside the first pass of every step (events on the launching stream)
+    group_ms = {k: sum(ev[st][i].elapsed_time(ev[st][i + 1]) for st in range(args.steps)) / args.steps for i, k in enumerate(groups)}
     _lib.workspace_status(dev)
-    if dist is not None:
-        t = torch.tensor([step_ms] + [kernel_ms[k] for k in KERNELS], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_ms = float(t[0].item())
-        kernel_ms = {k: float(t[i + 1].item()) for i, k in enumerate(KERNELS)}
-    value = world * bytes_per_step / (step_ms * 1e-3) / 1e9
+    vals = max_over_ranks(dist, dev, [step_ms] + [group_ms[k] for k in groups])
+    step_ms, group_ms = vals[0], {k: vals[i + 1] for i, k in enumerate(groups)}
+    value = world * bytes_per_pass * PASSES_PER_STEP / (step_ms * 1e-3) / 1e9
 
-    # ---- per-point detail (separate timed loops, same graph technique)
+    peak_hbm, peak_tf, peak_kind = measured_peaks()
+    # ---- per-point detail (separate timed loops, same graph technique) with the dense fp16 cuBLAS bar of the layer
     sweep = {}
     if rank == 0:
-        for bits, n in POINTS:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                with torch.cuda.graph(g, stream=side):
-                    for q in reps[bits]:
-                        bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
-            torch.cuda.synchronize()
-            for _ in range(3):
-                g.replay()
-            torch.cuda.synchronize()
-            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(10):
-                g.replay()
-            b_.record()
-            torch.cuda.synchronize()
-            us = a.elapsed_time(b_) * 1e3 / (10 * len(reps[bits]))
-            sweep[f"int{bits}_n{n}"] = {"us_per_layer": us, "GBps": algorithmic_bytes(bits, n) / us / 1e3}
-
-    # ---- context (not part of the headline): the 16-bit layer at decode and prefill sizes, and the dense fp16
-    # cuBLAS bar of the same layer that the quantised decode is meant to beat
-    context = {}
-    if rank == 0 and not args.no_context:
-        import mem_efficient_blr_b200.blast_kernels as bk
-
-        def graph_time(fns, reps=10):
-            for f in fns:
-                f()
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                with torch.cuda.graph(g, stream=side):
-                    for f in fns:
-                        f()
-            torch.cuda.synchronize()
-            for _ in range(3):
-                g.replay()
-            torch.cuda.synchronize()
-            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(reps):
-                g.replay()
-            b_.record()
-            torch.cuda.synchronize()
-            return a.elapsed_time(b_) * 1e3 / (reps * len(fns))
-
-        peak_hbm, _ = peak_hbm_gbs()
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peak_tf = float(json.load(f)["bf16_tflops"])
-        except Exception:
-            peak_tf = 1590.0
-        nrep16 = 9  # 9 x 31 MB of fp16 factors > 2 x L2
-        Us = [Ud.clone() for _ in range(nrep16)]
-        Vs = [Vd.clone() for _ in range(nrep16)]
         Ws = [torch.randn(O_F, I_F, device=dev, dtype=torch.float16) / 64 for _ in range(4)]
+        dense_us = {}
+        for n in (1, 4, 16):
+            xn = xs[n]
+            dense_us[n] = gt.us_per_call([(lambda w=w: torch.nn.functional.linear(xn, w)) for w in Ws])
+        del Ws
+        for bits, n in POINTS:
+            us = gt.us_per_call([(lambda q=q: bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)) for q in reps[bits]])
+            nb = algorithmic_bytes(bits, n)
+            sweep[f"int{bits}_n{n}"] = {"us_per_layer": us, "GBps": nb / us / 1e3, "roofline_us": nb / (peak_hbm * 1e3),
+                                        "frac": nb / (peak_hbm * 1e3) / us, "dense_fp16_cublas_us": dense_us[n],
+                                        "speedup_vs_dense_fp16_cublas": dense_us[n] / us,
+                                        "speedup_target": 3.9 if bits == 8 else 7.6}
+        # the 16-bit layer at decode and prefill sizes
+        Us = [Ud.clone() for _ in range(9)]  # 9 x 31 MB of fp16 factors > 2 x L2
+        Vs = [Vd.clone() for _ in range(9)]
         for n in (1, 4, 16, 128, 2048):
             xn = torch.randn(n, I_F, device=dev, dtype=torch.float16)
-            us = graph_time([(lambda u=u, v=v: bk.blast_torch_layout(xn, u, v, Sd)) for u, v in zip(Us, Vs)])
+            us = gt.us_per_call([(lambda u=u, v=v: bk.blast_torch_layout(xn, u, v, Sd)) for u, v in zip(Us, Vs)])
             nbytes = 2 * RANK * (I_F + O_F) + 2 * B_BLK * B_BLK * RANK + 2 * n * (I_F + O_F)
             flops = 2 * n * RANK * (I_F + O_F + B_BLK * B_BLK)
             roof = max(nbytes / (peak_hbm * 1e9), flops / (peak_tf * 1e12)) * 1e6
-            entry = {"us_per_layer": us, "roofline_us": roof, "frac": roof / us}
-            if n <= 16:
-                entry["dense_fp16_cublas_us"] = graph_time([(lambda w=w: torch.nn.functional.linear(xn, w)) for w in Ws])
-            context[f"blast_fp16_n{n}"] = entry
-        for key, v in sweep.items():
-            n = int(key.split("_n")[1])
-            v["speedup_vs_dense_fp16_cublas"] = context[f"blast_fp16_n{n}"]["dense_fp16_cublas_us"] / v["us_per_layer"]
-        del Us, Vs, Ws
-
-        # Network-level context: the 224 structured linears of one Llama-7B-BLAST decode step (32 layers x
-        # q/k/v/o 4096->4096 R=1024 and gate/up/down R=1488, b=16, as in the reference's
-        # configs/networks/llama7b.yaml), every layer with its own random factors (6.6 GB in fp16, far beyond L2),
-        # chained in one CUDA graph.  Attention, norms and the SwiGLU product are not part of the path and not run.
-        def linear_chain(bits):
-            shapes = [(4096, 4096, 1024)] * 4 + [(4096, 11008, 1488)] * 2 + [(11008, 4096, 1488)]
-            layers, nbytes = [], 0
-            for _ in range(32):
-                for (i_f, o_f, r) in shapes:
-                    p_, q_ = i_f // B_BLK, o_f // B_BLK
-                    u = torch.randn(B_BLK, q_, r, device=dev, dtype=torch.float16) / r ** 0.5
-                    v = torch.randn(B_BLK, r, p_, device=dev, dtype=torch.float16) / p_ ** 0.5
-                    s_ = torch.rand(B_BLK, B_BLK, r, device=dev, dtype=torch.float16) + 0.5
-                    wb = 2 if bits == 16 else bits / 8
-                    nbytes += wb * r * (i_f + o_f) + 2 * B_BLK * B_BLK * r + 2 * (i_f + o_f)
-                    if bits == 16:
-                        layers.append((i_f, (u, v, s_)))
-                    else:
-                        layers.append((i_f, (*bq.quantize_blast_factors(u, v, bits), s_)))
-                        del u, v
-            xin = {4096: torch.randn(1, 4096, device=dev, dtype=torch.float16),
-                   11008: torch.randn(1, 11008, device=dev, dtype=torch.float16)}
-
-            def step():
-                for i_f, f in layers:
-                    if bits == 16:
-                        bk.blast_torch_layout(xin[i_f], *f)
-                    else:
-                        bq.blast_wq(xin[i_f], f[0], f[1], f[2], f[3], f[4], bits)
-            us = graph_time([step], reps=5)
-            floor = nbytes / (peak_hbm * 1e9) * 1e6
-            return {"us_per_token_step": us, "tokens_per_s_batch1": 1e6 / us, "linears": len(layers),
-                    "weight_streaming_floor_us": floor, "frac": floor / us}
-
-        # Layer sweep: every operator family at the three Llama-7B linear shapes, 1 token and 2048 tokens, fp16,
-        # ranks from the reference's 50 %-parameter configurations; roofline = max(bytes / HBM, flops / tensor).
-        import mem_efficient_blr_b200.dense_kernels as dk
-        import mem_efficient_blr_b200.low_rank_kernels as lk
-        import mem_efficient_blr_b200.monarch_kernels as mk
-
-        def sweep_point(kind, i_f, o_f, r, n):
-            xn = torch.randn(n, i_f, device=dev, dtype=torch.float16)
-            h = lambda *shape, fan: torch.randn(*shape, device=dev, dtype=torch.float16) / fan ** 0.5
-            if kind == "blast":
-                wbytes = 2 * r * (i_f + o_f) + 2 * B_BLK * B_BLK * r
-                flops = 2 * n * r * (i_f + o_f + B_BLK * B_BLK)
-                mk_one = lambda: (h(B_BLK, o_f // B_BLK, r, fan=r), h(B_BLK, r, i_f // B_BLK, fan=i_f // B_BLK),
-                                  torch.rand(B_BLK, B_BLK, r, device=dev, dtype=torch.float16) + 0.5)
-                call = lambda f: bk.blast_torch_layout(xn, *f)
-            elif kind == "monarch":
-                wbytes = 2 * r * (i_f + o_f)
-                flops = 2 * n * r * (i_f + o_f)
-                mk_one = lambda: (h(B_BLK, r, i_f // B_BLK, fan=i_f // B_BLK), h(B_BLK, o_f // B_BLK, r, fan=r))
-                call = lambda f: mk.monarch_torch_layout(xn, *f)
-            elif kind == "low_rank":
-                wbytes = 2 * r * (i_f + o_f)
-                flops = 2 * n * r * (i_f + o_f)
-                mk_one = lambda: (h(r, i_f, fan=i_f), h(o_f, r, fan=r))
-                call = lambda f: lk.low_rank_torch_layout(xn, *f)
-            else:
-                wbytes = 2 * i_f * o_f
-                flops = 2 * n * i_f * o_f
-                mk_one = lambda: (h(o_f, i_f, fan=i_f),)
-                call = lambda f: dk.dense_torch_layout(xn, *f)
-            nrep = int(2 * L2_BYTES // wbytes) + 1
-            sets = [mk_one() for _ in range(nrep)]
-            us = graph_time([(lambda f=f: call(f)) for f in sets], reps=5)
-            nbytes = wbytes + 2 * n * (i_f + o_f)
-            roof = max(nbytes / (peak_hbm * 1e9), flops / (peak_tf * 1e12)) * 1e6
-            return {"us_per_layer": us, "roofline_us": roof, "frac": roof / us}
-
-        layer_sweep = {}
-        for lname, i_f, o_f, ranks in (("qkvo_4096x4096", 4096, 4096, {"blast": 1024, "monarch": 1024, "low_rank": 1024}),
-                                       ("gate_4096x11008", 4096, 11008, {"blast": 1488, "monarch": 1536, "low_rank": 1024}),
-                                       ("down_11008x4096", 11008, 4096, {"blast": 1488, "monarch": 1536, "low_rank": 1024})):
-            for kind in ("blast", "monarch", "low_rank", "dense"):
-                for n in (1, 2048):
-                    layer_sweep[f"{lname}/{kind}/n{n}"] = sweep_point(kind, i_f, o_f, ranks.get(kind, 0), n)
-                    torch.cuda.empty_cache()
-        context["layer_sweep_fp16"] = layer_sweep
-
-        context["llama7b_blast_linears_decode_fp16"] = linear_chain(16)
-        context["llama7b_blast_linears_decode_int8"] = linear_chain(8)
+            sweep[f"fp16_n{n}"] = {"us_per_layer": us, "roofline_us": roof, "frac": roof / us,
+                                   "TFLOPs": flops / us / 1e6, "GBps": nbytes / us / 1e3}
+        del Us, Vs
         torch.cuda.empty_cache()
 
+    lsweep = layer_sweep(dev, args.quick) if rank == 0 and not args.no_context else None
+
     # ---- end to end through the public host-buffer operator: x in pinned host memory, result back in pinned host
-    # memory, every launch (one library call enqueues copy-in, kernel and copy-out; its copy streams let consecutive
+    # memory, every call (one library call enqueues copy-in, kernel and copy-out; its copy streams let consecutive
     # calls overlap).  The step ends when the last result has arrived in host memory.
     host_calls = {bits: [bq.BlastWqHostCall(q[0], q[1], q[2], q[3], Sd, bits) for q in reps[bits]] for bits in reps}
 
-    def e2e_step():
+    def e2e_pass():
         for bits, n in POINTS:
             for call in host_calls[bits]:
                 call(xs_host[n], outs_host[n])
         bq.host_flush(dev)
 
-    e2e_steps = max(2, min(args.steps, 5))
+    e2e_passes = 5
     for _ in range(2):
-        e2e_step()
+        e2e_pass()
     barrier()
-    # the host path must deliver what the device path computes (last call of a step: int4, 16 tokens, last replica)
+    # the host path must deliver what the device path computes (last call of a pass: int4, 16 tokens, last replica)
     q = reps[4][-1]
     want = bq.blast_wq(xs[16], q[0], q[1], q[2], q[3], Sd, 4).float().cpu()
     err = float((outs_host[16].float() - want).norm() / want.norm())
@@ -453,58 +567,63 @@ def run_ours(args):
         raise SystemExit(f"host-buffer path disagrees with the device path: relative error {err}")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    for _ in range(e2e_passes):
+        e2e_pass()
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    h2d = sum(2 * n * I_F * len(reps[b]) for b, n in POINTS)
-    d2h = sum(2 * n * O_F * len(reps[b]) for b, n in POINTS)
+    (e2e_ms,) = max_over_ranks(dist, dev, [e0.elapsed_time(e1) / e2e_passes])
+    h2d = sum(2 * n * I_F * len(reps[b]) for b, n in POINTS) * PASSES_PER_STEP
+    d2h = sum(2 * n * O_F * len(reps[b]) for b, n in POINTS) * PASSES_PER_STEP
+    del host_calls, reps
+    torch.cuda.empty_cache()
+
+    # ---- network level and sharding (all ranks take part; rank 0 reports)
+    llama = vit = shard = None
+    if not args.no_context:
+        llama = llama_leg(dev, rank, world, dist, args.quick)
+        vit = vit_leg(dev, rank, world, dist, args.quick)
+        if world > 1 and B_BLK % world == 0:
+            shard = sharding_leg(dev, rank, world, dist)
 
     if rank == 0:
-        peak, peak_kind = peak_hbm_gbs()
-        # roofline of the kernel with the largest share of the timed region (per GPU): algorithmic bytes of its
-        # launches / their device time; the other kernel is listed beside it
-        per_kernel = {}
-        for k in KERNELS:
-            ach = kbytes[k] / (kernel_ms[k] * 1e-3) / 1e9
-            per_kernel[k] = {"launches_per_step": launches[k], "share": kernel_ms[k] / sum(kernel_ms.values()),
-                             "us_per_launch": kernel_ms[k] * 1e3 / launches[k],
-                             "algorithmic_bytes_per_launch": kbytes[k] / launches[k], "achieved": ach, "frac": ach / peak}
-        top = max(KERNELS, key=lambda k: kernel_ms[k])
-        achieved = per_kernel[top]["achieved"]
+        per_group = {}
+        for k in groups:
+            ach = kbytes[k] / (group_ms[k] * 1e-3) / 1e9
+            per_group[k] = {"kernels": GROUPS[k][0], "calls_per_pass": calls[k], "launches_per_call": GROUPS[k][1],
+                            "share": group_ms[k] / sum(group_ms.values()), "us_per_call": group_ms[k] * 1e3 / calls[k],
+                            "algorithmic_bytes_per_call": kbytes[k] / calls[k], "achieved": ach, "frac": ach / peak_hbm}
+        top = max(groups, key=lambda k: group_ms[k])
+        traffic, traffic_note = ncu_traffic(top)
         cpu = None
         if world == 1:
             threads = os.cpu_count() or 1
-            times = cpu_reference_times(threads, 5)
-            cpu_s = sum(times[p] for p in POINTS)
+            wl = CpuWorkload(threads)
+            wl.step()
+            steps = [wl.step() for _ in range(5)]
+            cpu_s = sum(sum(s.values()) for s in steps) / len(steps)
             cpu = {"value": sum(algorithmic_bytes(b, n) for b, n in POINTS) / cpu_s / 1e9, "unit": "GB/s", "cores": threads,
-                   "kind": "port", "sample": "5 timed calls per (bits, tokens) point of the CPU restatement of "
-                                             "torch_blast_baseline on dequantised fp32 factors"}
+                   "kind": wl.kind, "sample": "5 timed calls per (bits, tokens) point of torch_blast_baseline "
+                                              "(torch_funcs/blast_funcs.py:3-47) on dequantised fp32 factors, all host cores"}
         line = {
             "metric": "blast_wq_decode_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations, s8/s4 weights, f32 accumulate",
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations, s8/s4 weights, s32/f32 accumulate",
             "data": "synthetic",
-            "config": workload_config({f"int{b}": len(reps[b]) for b in (8, 4)}),
-            "gpu_launches": launches_per_step * args.steps,
-            "us_per_layer_mean": step_ms * 1e3 / launches_per_step,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC[top][0], "kernel": top,
-                         "traffic_note": f"dram read+write bytes of one {NCU_TRAFFIC[top][1]} launch from an ncu capture "
-                                         "(profiles/); algorithmic bytes of that point: "
-                                         f"{algorithmic_bytes(8, 1 if top == 'blr_blast_cluster_kernel' else 16):.0f}",
-                         "kernels": per_kernel},
-            "e2e": {"value": world * bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "config": workload_config(),
+            "gpu_launches": launches_per_pass * PASSES_PER_STEP * args.steps,
+            "us_per_layer_mean": step_ms * 1e3 / (sum(calls.values()) * PASSES_PER_STEP),
+            "roofline": {"bound": "hbm", "achieved": per_group[top]["achieved"], "peak": peak_hbm, "unit": "GB/s",
+                         "frac": per_group[top]["frac"], "peak_kind": peak_kind, "traffic": traffic, "traffic_note": traffic_note,
+                         "kernel": GROUPS[top][0], "whole_step_frac": value / world / peak_hbm, "groups": per_group},
+            "e2e": {"value": world * bytes_per_pass / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms * PASSES_PER_STEP},
             "cpu_baseline": cpu,
             "clocks": clk.summary(),
             "sweep": sweep,
-            "context": context,
+            "llama7b_blast": llama,
+            "vit_b16_blast": vit,
+            "row_block_sharding": shard,
+            "layer_sweep": lsweep,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -514,11 +633,12 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-context", action="store_true", help="skip the informational 16-bit / cuBLAS measurements")
-    ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager launches of one point and exit (for profiler captures); "
+    ap.add_argument("--no-context", action="store_true", help="headline only: skip the layer sweep, the networks and the sharding leg")
+    ap.add_argument("--quick", action="store_true", help="smaller network legs (4 decoder layers, fewer batch sizes) and a two-point layer sweep")
+    ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager calls of one point and exit (for profiler captures); "
                                                   "p16:TOKENS - three calls of the 16-bit layer on that many tokens")
     args = ap.parse_args()
     if args.impl == "reference":

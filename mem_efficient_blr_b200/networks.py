@@ -35,10 +35,11 @@ class BlastTorchLinear(nn.Module):
         self.in_features, self.out_features, self.b, self.rank = in_features, out_features, b, rank
         P, Q = in_features // b, out_features // b
         g = generator
-        rn = lambda *s: torch.randn(*s, generator=g)
+        gd = g.device if g is not None else "cpu"   # a CUDA generator fills the factors on the device (large models)
+        rn = lambda *s: torch.randn(*s, generator=g, device=gd)
         self.U = nn.Parameter((rn(b, Q, rank) / math.sqrt(rank * b * 13.0 / 12.0)).to(device=device, dtype=dtype), requires_grad=False)
         self.Vt = nn.Parameter((rn(b, rank, P) / math.sqrt(P)).to(device=device, dtype=dtype), requires_grad=False)
-        self.S = nn.Parameter((torch.rand(b, b, rank, generator=g) + 0.5).to(device=device, dtype=dtype), requires_grad=False)
+        self.S = nn.Parameter((torch.rand(b, b, rank, generator=g, device=gd) + 0.5).to(device=device, dtype=dtype), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype), requires_grad=False) if bias else None
 
     def forward(self, x):
@@ -74,8 +75,9 @@ def make_linear(method: str, in_features: int, out_features: int, b: int, rank: 
     """method: 'blast' (16-bit factors), 'blast_int8', 'blast_int4', or 'dense' (nn.Linear, the unstructured bar)."""
     if method == "dense":
         lin = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=dtype)
+        gd = generator.device if generator is not None else "cpu"
         with torch.no_grad():
-            lin.weight.copy_((torch.randn(out_features, in_features, generator=generator) / math.sqrt(in_features)).to(dtype))
+            lin.weight.copy_((torch.randn(out_features, in_features, generator=generator, device=gd) / math.sqrt(in_features)).to(dtype))
             if bias:
                 lin.bias.zero_()
         return lin.requires_grad_(False)
@@ -158,13 +160,14 @@ class LlamaLayer(nn.Module):
 class LlamaDecoder(nn.Module):
     """Decoder of the shape above with a static cache for `cache_len` positions and `batch` sequences."""
 
-    def __init__(self, shape: LlamaShape, method: str, batch: int, cache_len: int, device="cuda", dtype=torch.float16, seed=0):
+    def __init__(self, shape: LlamaShape, method: str, batch: int, cache_len: int, device="cuda", dtype=torch.float16, seed=0,
+                 init_on_device: bool = False):
         super().__init__()
-        g = torch.Generator().manual_seed(seed)
+        g = torch.Generator(device=device if init_on_device else "cpu").manual_seed(seed)
         self.shape, self.method, self.batch, self.cache_len = shape, method, batch, cache_len
         self.embed_tokens = nn.Embedding(shape.vocab, shape.d, device=device, dtype=dtype)
         with torch.no_grad():
-            self.embed_tokens.weight.copy_(torch.randn(shape.vocab, shape.d, generator=g).to(dtype))
+            self.embed_tokens.weight.copy_(torch.randn(shape.vocab, shape.d, generator=g, device=g.device).to(dtype))
         self.embed_tokens.requires_grad_(False)
         self.layers = nn.ModuleList(LlamaLayer(shape, method, device, dtype, g) for _ in range(shape.layers))
         self.norm = RMSNorm(shape.d, shape.eps, device, dtype)
@@ -182,9 +185,10 @@ class LlamaDecoder(nn.Module):
 
     def _run(self, ids, pos, causal):
         x = self.embed_tokens(ids)
+        B = ids.shape[0]   # a smaller batch than the cache was built for uses the first B sequences' slots
         cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
         for i, layer in enumerate(self.layers):
-            x = layer(x, cos, sin, self.kcache[i], self.vcache[i], pos, causal)
+            x = layer(x, cos, sin, self.kcache[i][:B], self.vcache[i][:B], pos, causal)
         return self.lm_head(self.norm(x[:, -1]))
 
     @torch.no_grad()
@@ -241,15 +245,15 @@ class ViTLayer(nn.Module):
 
 
 class ViTEncoder(nn.Module):
-    def __init__(self, shape: ViTShape, method: str, device="cuda", dtype=torch.float16, seed=0):
+    def __init__(self, shape: ViTShape, method: str, device="cuda", dtype=torch.float16, seed=0, init_on_device: bool = False):
         super().__init__()
-        g = torch.Generator().manual_seed(seed)
+        g = torch.Generator(device=device if init_on_device else "cpu").manual_seed(seed)
         s = shape
         self.shape, self.method = shape, method
         self.patch = nn.Conv2d(3, s.d, s.patch, s.patch, device=device, dtype=dtype).requires_grad_(False)
         ntok = (s.image // s.patch) ** 2 + 1
-        self.cls = nn.Parameter((torch.randn(1, 1, s.d, generator=g) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
-        self.posemb = nn.Parameter((torch.randn(1, ntok, s.d, generator=g) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
+        self.cls = nn.Parameter((torch.randn(1, 1, s.d, generator=g, device=g.device) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
+        self.posemb = nn.Parameter((torch.randn(1, ntok, s.d, generator=g, device=g.device) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
         self.layers = nn.ModuleList(ViTLayer(s, method, device, dtype, g) for _ in range(s.layers))
         self.ln = nn.LayerNorm(s.d, eps=s.eps, device=device, dtype=dtype).requires_grad_(False)
 

@@ -1,0 +1,77 @@
+"""Network level on the GPU: a small Llama-shaped decoder and a small ViT-shaped encoder whose structured linears run
+this package's kernels, against the same networks on CPU in fp32 whose structured linears call the oracle
+(same seeds, same 16-bit-rounded parameters).  Bound: relative Frobenius error of the logits / features <= 1e-2."""
+import pytest
+import torch
+
+from oracle import blr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+
+
+def _round_params_like(model, dtype):
+    """fp32 twin: every parameter rounded through the 16-bit type the GPU model stores."""
+    with torch.no_grad():
+        for p in list(model.parameters()) + list(model.buffers()):
+            if p.is_floating_point():
+                p.copy_(p.to(dtype).float())
+
+
+def _oracle_linears(nw, model, bits):
+    """Swaps the forward of every structured linear of the CPU twin for the oracle's BLAST."""
+    for m in model.structured_linears():
+        assert isinstance(m, nw.BlastTorchLinear)
+        if bits == 16:
+            m.forward = (lambda x, m=m: orc.blast(x, m.U, m.Vt, m.S)[0] + (0 if m.bias is None else m.bias))
+        else:
+            Uq, us = orc.quantize_sym(m.U.data.half(), bits)
+            Vq, vs = orc.quantize_sym(m.Vt.data.half(), bits)
+            m.forward = (lambda x, m=m, q=(Uq, us, Vq, vs): orc.blast_wq(x, *q, m.S, bits)[0] + (0 if m.bias is None else m.bias))
+
+
+@pytest.mark.parametrize("method,bits", [("blast", 16), ("blast_int8", 8)])
+def test_llama_shaped_decoder_matches_oracle_backed_twin(method, bits):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from mem_efficient_blr_b200 import networks as nw
+    shape = nw.LlamaShape(layers=2, d=512, heads=8, ffn=1024, vocab=384, b=16, rank_attn=64, rank_mlp=96)
+    B, T = 3, 12
+    ids = torch.randint(0, shape.vocab, (B, T), generator=torch.Generator().manual_seed(5))
+    gpu = nw.LlamaDecoder(shape, method, batch=B, cache_len=T, device=DEV, dtype=torch.float16, seed=11)
+    cpu = nw.LlamaDecoder(shape, "blast", batch=B, cache_len=T, device="cpu", dtype=torch.float32, seed=11)
+    _round_params_like(cpu, torch.float16)
+    _oracle_linears(nw, cpu, bits)
+    # prefill of T - 1 tokens (tensor-core pipeline: 33 rows per linear), then one decode step (3 rows: decode kernels)
+    want_p, got_p = cpu.prefill(ids[:, :T - 1]), gpu.prefill(ids[:, :T - 1].to(DEV))
+    want_d = cpu.decode_step(ids[:, T - 1:], torch.tensor([T - 1]))
+    got_d = gpu.decode_step(ids[:, T - 1:].to(DEV), torch.tensor([T - 1], device=DEV))
+    torch.cuda.synchronize()
+    assert orc.rel_fro(got_p.float().cpu(), want_p) < TOL
+    assert orc.rel_fro(got_d.float().cpu(), want_d) < TOL
+    # the decode step replayed from a CUDA graph gives the same logits
+    step = nw.GraphedCall(gpu.decode_step, ids[:, T - 1:].to(DEV), torch.tensor([T - 1], device=DEV))
+    again = step(ids[:, T - 1:].to(DEV), torch.tensor([T - 1], device=DEV))
+    torch.cuda.synchronize()
+    assert orc.rel_fro(again.float().cpu(), got_d.float().cpu()) < 1e-3
+
+
+def test_vit_shaped_encoder_matches_oracle_backed_twin():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from mem_efficient_blr_b200 import networks as nw
+    shape = nw.ViTShape(layers=2, d=256, heads=4, mlp=512, image=64, patch=16, b=16,
+                        ranks={"qkv": 32, "intermediate": 48, "output": 48})
+    img = torch.randn(2, 3, 64, 64, generator=torch.Generator().manual_seed(2))
+    gpu = nw.ViTEncoder(shape, "blast", device=DEV, dtype=torch.float16, seed=4)
+    cpu = nw.ViTEncoder(shape, "blast", device="cpu", dtype=torch.float32, seed=4)
+    # the twin's unseeded pieces (patch convolution, layer norms) take the GPU model's values
+    cpu.load_state_dict({k: v.float().cpu() for k, v in gpu.state_dict().items()})
+    _round_params_like(cpu, torch.float16)
+    _oracle_linears(nw, cpu, 16)
+    got = gpu(img.to(DEV, torch.float16))
+    torch.cuda.synchronize()
+    want = cpu(img.half().float())
+    assert got.shape == (2, 17, 256)
+    assert orc.rel_fro(got.float().cpu(), want) < TOL
