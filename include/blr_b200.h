@@ -87,6 +87,13 @@ const char* blr_last_error(void);
  * reference allocates its intermediates with torch.empty per call (blast_kernels.py:1967, 2703). */
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width);
 
+/* Device memory for a workspace or staging buffer straight from cudaMalloc / back to cudaFree, for host layers whose
+ * own allocator is not a safe home for a long-lived scratch buffer (PyTorch routes allocations made while it records a
+ * CUDA graph, or warms one up, into that graph's private pool).  Not to be called while a stream capture is under
+ * way.  Returns NULL on failure (blr_last_error has the text).  No reference counterpart. */
+void* blr_scratch_alloc(size_t bytes);
+int blr_scratch_free(void* ptr);
+
 /* Zeroes the fixed head of a workspace: 1 KiB of control words and the 2 MiB fp32 accumulation area of the
  * cluster kernel (the kernels leave both zero again when they finish).  Required once after allocation and
  * after a call reported BLR_ERR_TIMEOUT through blr_workspace_status. No reference counterpart. */

@@ -26,6 +26,8 @@ SIGNATURES = {
     "blr_debug_decode_path": (_int, [_int]),
     "blr_last_error": (C.c_char_p, []),
     "blr_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "blr_scratch_alloc": (_vp, [_sz]),
+    "blr_scratch_free": (_int, [_vp]),
     "blr_workspace_init": (_int, [_vp, _sz, _vp]),
     "blr_workspace_status": (_int, [_vp, _vp]),
     "blr_blast": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
@@ -106,6 +108,40 @@ def stream_ptr(device: torch.device) -> int:
 _workspaces: dict = {}
 
 
+class _RawBuffer:
+    """Device memory from blr_scratch_alloc, exposed through the CUDA array interface so that torch can view it."""
+
+    def __init__(self, nbytes: int):
+        self.ptr = load().blr_scratch_alloc(nbytes)
+        if not self.ptr:
+            raise RuntimeError("blr_b200: " + load().blr_last_error().decode("utf-8", "replace"))
+        self.nbytes = nbytes
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (self.ptr, False), "version": 3}
+
+    def __del__(self):
+        try:
+            if self.ptr:
+                load().blr_scratch_free(self.ptr)
+        except Exception:
+            pass
+
+
+def _alloc_outside_graph_pools(nbytes: int, device: torch.device) -> torch.Tensor:
+    """A long-lived scratch buffer must not come from a CUDA-graph memory pool: torch.compile's CUDA-graph trees
+    (mode='reduce-overhead', what the reference's network harness uses, models/llama7b.py:65) route every allocation
+    of the thread that warms up or records a graph into the graph's private pool and then insist that nothing but
+    the graph's outputs lives there.  So the buffer comes from cudaMalloc through the library and torch only views
+    it.  While a capture is under way cudaMalloc is not allowed: the buffer then comes from the capture's pool (a
+    caller that captures without a warm-up call owns that choice)."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        raw = _RawBuffer(nbytes)
+        t = torch.as_tensor(raw, device=device)
+    t._blr_owner = raw  # the view keeps the allocation alive
+    return t
+
+
 def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
     ws = _workspaces.get(key)
@@ -113,7 +149,7 @@ def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
         cap = max(nbytes, 1 << 20)
         if ws is not None:
             cap = max(cap, 2 * ws.numel())
-        ws = torch.empty(cap, dtype=torch.uint8, device=device)
+        ws = _alloc_outside_graph_pools(cap, device)
         check(load().blr_workspace_init(ws.data_ptr(), ws.numel(), stream))
         _workspaces[key] = ws
     return ws

@@ -468,6 +468,21 @@ size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
   return kCtrlBytes + kClusterOut32Bytes + align256(e * 4) + align256(e * 2) + align256(c);
 }
 
+void* blr_scratch_alloc(size_t bytes) {
+  void* p = nullptr;
+  const cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    set_last_error("cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    return nullptr;
+  }
+  return p;
+}
+
+int blr_scratch_free(void* p) {
+  BLR_CUDA_OK(cudaFree(p));
+  return BLR_OK;
+}
+
 int blr_workspace_init(void* ws, size_t ws_bytes, void* stream) {
   BLR_REQUIRE(ws != nullptr && ws_bytes >= kCtrlBytes + kClusterOut32Bytes, BLR_ERR_WORKSPACE, "workspace too small");
   BLR_CUDA_OK(cudaMemsetAsync(ws, 0, kCtrlBytes + kClusterOut32Bytes, static_cast<cudaStream_t>(stream)));

@@ -167,9 +167,9 @@ class QuantBlastLinear(_Base):
         return self._finish(x, self._op(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits, self.group))
 
 
-def replace_linear_with_custom(module: nn.Module, key: str, factory) -> int:
-    """Swaps every nn.Linear whose qualified name contains `key` for `factory(in_features, out_features, bias)`;
-    the substring rule of the reference's utils.replace_linear_with_custom (utils.py:46-116).  Returns the count."""
+def replace_linear_with_factory(module: nn.Module, key: str, factory) -> int:
+    """Swaps every nn.Linear whose qualified name contains `key` for `factory(in_features, out_features, bias)`.
+    Returns the count."""
     n = 0
     for name, child in list(module.named_modules()):
         if key in name and isinstance(child, nn.Linear):
@@ -180,3 +180,50 @@ def replace_linear_with_custom(module: nn.Module, key: str, factory) -> int:
             setattr(parent, parts[-1], factory(child.in_features, child.out_features, child.bias is not None))
             n += 1
     return n
+
+
+def _conv1d_type():
+    try:  # HuggingFace's GPT-2 style linear (weight stored transposed); optional
+        from transformers.pytorch_utils import Conv1D
+        return Conv1D
+    except Exception:
+        return ()
+
+
+def replace_linear_with_custom(model: nn.Module, layer_configs: dict, method: str, skip_keys=None) -> int:
+    """Mirror of utils.replace_linear_with_custom (utils.py:46-116), same arguments: for every (key, config) of
+    `layer_configs`, each nn.Linear (or HF Conv1D) whose qualified name contains `key` - and none of `skip_keys` -
+    becomes the structured module of `method` ("blast", "blast_sym_quant", "monarch", "low_rank", "dense") built from
+    config["b"], config["rank"], config["func"] (dotted path of the operator function) and config.get("compile").
+    Device, dtype and the presence of a bias follow the replaced layer.  Returns the number of layers replaced."""
+    conv1d = _conv1d_type()
+    skip_keys = skip_keys or []
+    count = 0
+    for name, module in list(model.named_modules()):
+        is_lin, is_c1d = isinstance(module, nn.Linear), bool(conv1d) and isinstance(module, conv1d)
+        if not (is_lin or is_c1d):
+            continue
+        for key, config in layer_configs.items():
+            if key not in name or any(skip in name for skip in skip_keys):
+                continue
+            i_f, o_f = (module.in_features, module.out_features) if is_lin else (module.nx, module.nf)
+            common = dict(func_path=config["func"], device=module.weight.device, dtype=module.weight.dtype,
+                          bias=module.bias is not None, is_compiled=config.get("compile", False))
+            if method in ("blast", "blast_sym_quant"):
+                new_layer = BlastLinear(i_f, o_f, config["b"], config["rank"], **common)
+            elif method == "monarch":
+                new_layer = MonarchLinear(i_f, o_f, config["b"], config["rank"], **common)
+            elif method == "low_rank":
+                new_layer = LowRankLinear(i_f, o_f, config["rank"], **common)
+            elif method == "dense":
+                new_layer = DenseLinear(i_f, o_f, **common)
+            else:
+                raise ValueError(f"unknown method {method!r}")
+            parent = model
+            parts = name.split(".")
+            for p in parts[:-1]:
+                parent = getattr(parent, p)
+            setattr(parent, parts[-1], new_layer)
+            count += 1
+            break
+    return count

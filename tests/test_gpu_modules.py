@@ -85,14 +85,19 @@ def test_layer_swap_and_fullgraph_compile(W):
             return self.other(self.down_proj(torch.nn.functional.silu(self.up_proj(x))))
 
     blk = Block().to(DEV, torch.bfloat16)
-    n = W.replace_linear_with_custom(
-        blk, "proj", lambda i, o, bias: W.BlastLinear(i, o, 4, 64, device=DEV, dtype=torch.bfloat16, bias=bias))
+    # the reference's call form (utils.py:46): substring keys, per-key config, method name
+    cfg = {"func": "mem_efficient_blr_b200.blast_kernels.triton_blast_partial_grouped_fp16", "b": 4, "rank": 64}
+    n = W.replace_linear_with_custom(blk, {"up_proj": cfg, "down_proj": cfg, "other": cfg}, "blast", skip_keys=["other"])
     assert n == 2 and isinstance(blk.up_proj, W.BlastLinear) and isinstance(blk.other, nn.Linear)
+    assert blk.up_proj.U.dtype == torch.bfloat16 and blk.up_proj.bias is None
     _scaled_(blk.up_proj); _scaled_(blk.down_proj)
     x = torch.randn(1, 8, 256, device=DEV, dtype=torch.bfloat16)
     with torch.no_grad():   # the operators are forward-only (the reference times inference)
         eager = blk(x)
-        compiled = torch.compile(blk, fullgraph=True)   # the reference compiles its networks this way (models/llama7b.py:65)
+        # the reference compiles its networks this way (models/llama7b.py:65): one graph, replayed from CUDA graphs
+        compiled = torch.compile(blk, fullgraph=True, mode="reduce-overhead")
+        for _ in range(3):   # the first calls record and warm the CUDA-graph tree
+            compiled(x)
         got = compiled(x)
     torch.cuda.synchronize()
     assert orc.rel_fro(got.float().cpu(), eager.float().cpu()) < 1e-3
