@@ -343,9 +343,22 @@ def sharding_leg(dev, rank, world, dist):
         us_local = time_ms(lambda: bk.blast_output_blocks(x, Ul, Vt, Sl), 50, warm=5) * 1e3
         dist.barrier()
         us_shard = time_ms(lambda: bd.blast_row_block_parallel(x, Ul, Vt, Sl, bk.blast_output_blocks), 50, warm=5) * 1e3
-        us_full, us_local, us_shard = max_over_ranks(dist, dev, [us_full, us_local, us_shard])
+        # the same call replayed from a CUDA graph (kernels and the NCCL collective captured together): what a
+        # decode step that is itself a graph pays, without the host's launch work
+        us_graph = None
+        try:
+            dist.barrier()
+            gcall = GraphTimer().capture(lambda: bd.blast_row_block_parallel(x, Ul, Vt, Sl, bk.blast_output_blocks))
+            dist.barrier()
+            us_graph = time_ms(gcall.replay, 50, warm=5) * 1e3
+        except Exception as e:   # a collective that cannot be captured on this stack: report the eager figure only
+            us_graph = float("nan")
+            out.setdefault("graph_capture_error", repr(e)[:200])
+        us_full, us_local, us_shard, us_graph = max_over_ranks(dist, dev, [us_full, us_local, us_shard, us_graph])
+        best = us_graph if us_graph == us_graph else us_shard
         out[f"n{n}"] = {"us_one_gpu": us_full, "us_local_part": us_local, "us_sharded_with_gather": us_shard,
-                        "speedup": us_full / us_shard, "efficiency": us_full / us_shard / world, "rel_err_vs_unsharded": err}
+                        "us_sharded_with_gather_graph": us_graph, "speedup": us_full / best,
+                        "efficiency": us_full / best / world, "rel_err_vs_unsharded": err}
     return out
 
 

@@ -66,12 +66,6 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int blr_version(void);
 
-/* Profiling aid: with a non-NULL device buffer of 16 * (SM count) uint64, every later streaming-kernel
- * launch stores per-CTA %globaltimer stamps there (0 start, 1/2 weight loads of phase 0/1 issued,
- * 3 first stage landed, 4/8 phase 0/1 written, 5 first grid barrier passed, 6 coupling written, 9 end).
- * NULL switches it off. No reference counterpart. */
-int blr_debug_stream_timeline(void* dev_ptr);
-
 /* Test aid: which kernel serves 1..16 tokens.  0: automatic (BLAST with contraction-contiguous factors: the two-launch
  * path; other BLAST layouts, low-rank, Monarch on up to 8 tokens: the cluster kernel; the rest: the grid-wide streaming
  * kernel).  1: the grid-wide streaming kernel for everything.  2: automatic without the two-launch path.

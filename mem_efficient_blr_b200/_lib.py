@@ -22,7 +22,6 @@ _i64, _int, _vp, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
 # name -> (restype, argtypes); must list every symbol include/blr_b200.h declares
 SIGNATURES = {
     "blr_version": (_int, []),
-    "blr_debug_stream_timeline": (_int, [_vp]),
     "blr_debug_decode_path": (_int, [_int]),
     "blr_last_error": (C.c_char_p, []),
     "blr_workspace_bytes": (_sz, [_i64, _i64, _i64]),

@@ -50,9 +50,13 @@ __global__ void __launch_bounds__(kClusterThreads, 2) blr_blast_cluster_kernel(c
   const PhaseDesc& ph0 = p.ph[0];
   const PhaseDesc& ph1 = p.ph[1];
 
+#ifdef BLR_TIMELINE  // profiling builds only: 16 cycle stamps per CTA
   unsigned long long* tl = p.timeline ? p.timeline + (size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 : nullptr;
 #define BLR_STAMP(slot) do { if (tl) tl[slot] = (unsigned long long)clock64(); } while (0)
   if (threadIdx.x == 0 && tl) { tl[0] = globaltimer_ns(); tl[15] = (unsigned long long)clock64(); }
+#else
+#define BLR_STAMP(slot) do { } while (0)
+#endif
   if (warp == kConsumerWarps) {
     // descriptors this CTA will use: one per batch height for k-contiguous weights (full batches and the last one)
     const int rows0 = r_len0, rows1 = min(p.Q, (int)(blockIdx.z + 1) * p.q_part) - (int)blockIdx.z * p.q_part;
@@ -649,11 +653,15 @@ static int launch_cluster_impl(const ClusterParams& p, cudaStream_t stream) {
   return BLR_OK;
 }
 
+#ifdef BLR_TIMELINE
 extern unsigned long long* g_stream_timeline;
+#endif
 
 int launch_blast_cluster(const ClusterParams& p_in, int is_bf16, cudaStream_t stream) {
   ClusterParams p = p_in;
+#ifdef BLR_TIMELINE
   p.timeline = g_stream_timeline;
+#endif
   BLR_REQUIRE(p.N >= 1 && p.N <= kClusterMaxTokens, BLR_ERR_UNSUPPORTED, "the cluster kernel takes 1..%d tokens", kClusterMaxTokens);
   const bool gs = p.ph[0].group != 0;
 #define BLR_CL(BF, NTV, GSV, X) launch_cluster_impl<BF, NTV, GSV, X>(p, stream)

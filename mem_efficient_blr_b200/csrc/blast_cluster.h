@@ -46,7 +46,9 @@ struct alignas(64) ClusterParams {
   unsigned* counters;  // [qsplit][b] slices finished per (part, block), zero between calls
   unsigned* status;    // set to 1 when a wait ran out
   int stage_bytes, w_bytes, nstages;
-  unsigned long long* timeline;  // optional profiling stamps, 16 per CTA (see blr_debug_stream_timeline)
+#ifdef BLR_TIMELINE
+  unsigned long long* timeline;  // profiling builds: 16 stamps per CTA
+#endif
 };
 
 // Largest number of clusters of `b` CTAs that can be resident (0: this cluster shape cannot be launched).

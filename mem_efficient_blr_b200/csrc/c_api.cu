@@ -253,7 +253,11 @@ static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const
   // plus the equivalent of 20 KB per slice for the reductions and the finaliser's wait.
   const int kx = p.ph[1].kmajor ? (u_bits == 16 ? 64 : (u_bits == 8 ? 128 : 256)) : 64;
   int best_rs = 0, best_parts = 1, best_two = 0;
-  static const char* forced = getenv("BLR_CLUSTER_SHAPE");  // "rs,parts,two": measurement aid
+#ifdef BLR_TIMELINE
+  static const char* forced = getenv("BLR_CLUSTER_SHAPE");  // profiling builds only: "rs,parts,two"
+#else
+  const char* forced = nullptr;
+#endif
   if (forced) {
     if (sscanf(forced, "%d,%d,%d", &best_rs, &best_parts, &best_two) != 3) return 1;
     if (best_rs % kx != 0 || best_rs < kx || best_rs > kClusterMaxSlice || best_parts < 1 || best_parts > kClusterMaxParts) return 1;
@@ -448,10 +452,12 @@ using namespace blr;
 extern "C" {
 
 int blr_version(void) { return 100; }
-int blr_debug_stream_timeline(void* dev_ptr) {
+#ifdef BLR_TIMELINE
+int blr_debug_stream_timeline(void* dev_ptr) {  // profiling builds only, not part of the shipped ABI
   set_stream_timeline(static_cast<unsigned long long*>(dev_ptr));
   return BLR_OK;
 }
+#endif
 int blr_debug_decode_path(int which) {
   BLR_REQUIRE(which >= 0 && which <= 2, BLR_ERR_ARG,
               "decode path must be 0 (automatic), 1 (grid-wide kernel) or 2 (cluster kernel before the grid-wide one)");

@@ -65,12 +65,16 @@ struct alignas(64) StreamParams {
   int w_bytes;    // weight part of a stage: max over phases of ks * sub_bytes
   int nstages;
   int mix_bytes;  // shared memory for the coupling's copy of y (0 when mix == 0)
-  unsigned long long* timeline;  // optional: 16 time stamps per CTA (profiling aid), else nullptr
+#ifdef BLR_TIMELINE
+  unsigned long long* timeline;  // profiling builds: 16 time stamps per CTA
+#endif
 };
 
 // Launches the kernel (cooperative launch, one CTA per SM).  is_bf16 selects the 16-bit type.
 int launch_stream(const StreamParams& p, int is_bf16, cudaStream_t stream);
-// Profiling aid: when set, every launch records %globaltimer stamps, 16 slots per CTA, at dev_ptr.
+#ifdef BLR_TIMELINE
+// Profiling builds: when set, every launch records %globaltimer stamps, 16 slots per CTA, at dev_ptr.
 void set_stream_timeline(unsigned long long* dev_ptr);
+#endif
 
 }  // namespace blr

@@ -161,8 +161,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) blr_stream_kernel(const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t kABoxBytes = NT * 8 * 128;
   // optional per-CTA time stamps (16 slots per CTA) for profiling runs
+#ifdef BLR_TIMELINE  // profiling builds only: 16 time stamps per CTA
   unsigned long long* tl = p.timeline ? p.timeline + (size_t)blockIdx.x * 16 : nullptr;
 #define BLR_STAMP(slot) do { if (tl) tl[slot] = globaltimer_ns(); } while (0)
+#else
+#define BLR_STAMP(slot) do { } while (0)
+#endif
   if (threadIdx.x == 0) BLR_STAMP(0);
 
   if (threadIdx.x == 0) {
@@ -424,34 +428,33 @@ static int launch_impl(const StreamParams& p, cudaStream_t stream) {
   // Cooperative launch: the grid barriers need every CTA resident, and this makes the launch fail
   // instead of deadlock when they cannot be.
   // Programmatic dependent launch on top of it: the next launch in the stream may start its set-up while this
-  // grid drains (see the griddepcontrol pair in the kernel).  BLR_PDL=0 falls back to a plain cooperative launch.
-  static const int pdl = getenv("BLR_PDL") ? atoi(getenv("BLR_PDL")) : 1;
-  if (pdl) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(di.sm_count);
-    cfg.blockDim = dim3(kStreamThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute at[2];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    at[1].id = cudaLaunchAttributeCooperative;
-    at[1].val.cooperative = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 2;
-    BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)kern, args));
-    return BLR_OK;
-  }
-  BLR_CUDA_OK(cudaLaunchCooperativeKernel((const void*)kern, dim3(di.sm_count), dim3(kStreamThreads), args, smem, stream));
+  // grid drains (see the griddepcontrol pair in the kernel).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(di.sm_count);
+  cfg.blockDim = dim3(kStreamThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  at[1].id = cudaLaunchAttributeCooperative;
+  at[1].val.cooperative = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 2;
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)kern, args));
   return BLR_OK;
 }
 
+#ifdef BLR_TIMELINE
 unsigned long long* g_stream_timeline = nullptr;
 void set_stream_timeline(unsigned long long* dev_ptr) { g_stream_timeline = dev_ptr; }
+#endif
 
 int launch_stream(const StreamParams& p_in, int is_bf16, cudaStream_t stream) {
   StreamParams p = p_in;
+#ifdef BLR_TIMELINE
   p.timeline = g_stream_timeline;
+#endif
   BLR_REQUIRE(p.N >= 1 && p.N <= kStreamMaxTokens, BLR_ERR_ARG, "stream kernel handles 1..%d tokens, got %d",
               kStreamMaxTokens, p.N);
   if (p.ph[0].group != 0) {  // one scale per kScaleGroup contraction indices: its own instantiation

@@ -47,9 +47,17 @@ def blast_row_block_parallel(x: torch.Tensor, U_local: torch.Tensor, Vt: torch.T
     local = compute(x, U_local, Vt, S_local).contiguous()
     if world == 1:
         return local
-    parts = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(parts, local, group=group)
-    return torch.cat(parts, dim=-1)
+    # one collective into a (world, N, width) buffer; rank g's columns are out[:, g*width:(g+1)*width]
+    lead, width = local.shape[:-1], local.shape[-1]
+    flat = local.reshape(-1, width)
+    gathered = torch.empty((world, flat.shape[0], width), dtype=local.dtype, device=local.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(gathered, flat, group=group)
+    else:  # gloo (CPU ranks in the tests) gathers into a list of views of the same buffer
+        dist.all_gather(list(gathered.unbind(0)), flat, group=group)
+    if flat.shape[0] == 1:   # one token: the gathered buffer already is the row
+        return gathered.reshape(*lead, world * width)
+    return gathered.permute(1, 0, 2).reshape(*lead, world * width)
 
 
 def data_parallel_apply(x: torch.Tensor, fn: Callable, group=None, gather: bool = False) -> torch.Tensor:
