@@ -119,6 +119,36 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                    int b, int b_out, int P, int Q, int R, int flags,
                    void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
 
+/* Several BLAST layers that share their input and shapes in one pair of launches, with the element-wise work around
+ * them folded in (no counterpart in the reference, whose modules call one operator per layer and add the bias and
+ * the activation with separate torch kernels, models/wrappers.py:171-177):
+ *   - q / k / v projections of an attention block, or gate / up projections of an MLP: n_problems layers, one x;
+ *   - `bias` (b*Q values) and `residual` ((N, b*Q), row stride ldr) are added to a layer's result before it is stored;
+ *   - act = BLR_ACT_SILU_MUL: the input is silu(x) * x_mul (x_mul like x, same row stride): a down projection that
+ *     takes the gate and up results directly.
+ * Factors are contraction-contiguous: U (b,Q,R), V (b,R,P) in the 16-bit dtype (bits = 16: scales ignored) or quantised
+ * as for blr_blast_wq (bits = 8 | 4).  S element (i, j, r) of every layer at i*s_i + j*s_j + r*s_r.
+ * Scratch: blr_workspace_bytes(n_tokens, n_problems * b, R).  Serves the token counts of the two-launch decode path
+ * (up to 8 tokens with 16-bit factors, 4 with quantised ones); BLR_ERR_UNSUPPORTED otherwise - run the layers one by one. */
+#define BLR_ACT_NONE 0
+#define BLR_ACT_SILU_MUL 1
+typedef struct blr_blast_problem {
+  const void* U;
+  const void* V;
+  const void* S;
+  const void* u_scale; /* NULL with 16-bit factors */
+  const void* v_scale;
+  const void* bias;     /* NULL or b*Q values of the 16-bit dtype */
+  const void* residual; /* NULL or (N, b*Q) of the 16-bit dtype */
+  int64_t ldr;
+  void* out;
+  int64_t ldo;
+} blr_blast_problem;
+int blr_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int64_t n_tokens, int dtype,
+                    int n_problems, const blr_blast_problem* problems,
+                    int64_t s_i, int64_t s_j, int64_t s_r, int bits, int group, int b, int P, int Q, int R,
+                    void* ws, size_t ws_bytes, void* stream);
+
 /* blr_blast for callers that cannot allocate device memory and have no workspace to pass: plug-ins running
  * inside a host application that owns the device allocator, or latency-critical threads where the implicit
  * synchronisation of cudaMalloc is not acceptable.  This entry point has
@@ -239,6 +269,15 @@ int blr_quantize_sym(const void* w, int dtype, int64_t rows, int64_t K, int bits
  * tensor-core pipeline takes 16-bit factors.  No reference counterpart. */
 int blr_dequantize_sym(const void* q, const void* scale, int64_t rows, int64_t K, int bits, int64_t group,
                        int dtype, void* w, void* stream);
+
+/* Load / store probe: reads the operand arrays a, b, c once (any of them may have 0 bytes) and writes
+ * out[n][o] = o / tile (tile > 0) or 0 (tile = 0): the memory traffic of an operator without its arithmetic.
+ * Replaces triton_low_rank_load_store_fp16/_fp32 (triton_funcs/low_rank_kernels.py:419-449; kernels :163-236 store
+ * the index of the 64-wide output tile) and triton_dense_load_store_fp16/_fp32 (dense_kernels.py:383-411; kernels
+ * :190-227 store zeros).  out_kind: 0 fp16, 1 bf16, 2 fp32. */
+int blr_load_store_probe(const void* a, size_t a_bytes, const void* b, size_t b_bytes, const void* c, size_t c_bytes,
+                         int out_kind, void* out, int64_t n_tokens, int64_t out_features, int64_t ldo, int tile,
+                         void* stream);
 
 #ifdef __cplusplus
 }

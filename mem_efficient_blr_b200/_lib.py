@@ -19,12 +19,22 @@ STREAM_MAX_TOKENS = 16
 
 _i64, _int, _vp, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
 
+
+class BlastProblem(C.Structure):
+    """blr_blast_problem of include/blr_b200.h."""
+    _fields_ = [("U", _vp), ("V", _vp), ("S", _vp), ("u_scale", _vp), ("v_scale", _vp), ("bias", _vp), ("residual", _vp),
+                ("ldr", _i64), ("out", _vp), ("ldo", _i64)]
+
+
+ACT_NONE, ACT_SILU_MUL = 0, 1
+
 # name -> (restype, argtypes); must list every symbol include/blr_b200.h declares
 SIGNATURES = {
     "blr_version": (_int, []),
     "blr_debug_decode_path": (_int, [_int]),
     "blr_last_error": (C.c_char_p, []),
     "blr_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "blr_load_store_probe": (_int, [_vp, _sz, _vp, _sz, _vp, _sz, _int, _vp, _i64, _i64, _i64, _int, _vp]),
     "blr_scratch_alloc": (_vp, [_sz]),
     "blr_scratch_free": (_int, [_vp]),
     "blr_workspace_init": (_int, [_vp, _sz, _vp]),
@@ -33,6 +43,8 @@ SIGNATURES = {
                          _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
     "blr_blast_rows": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
                               _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
+    "blr_blast_multi": (_int, [_vp, _i64, _vp, _int, _i64, _int, _int, C.POINTER(BlastProblem), _i64, _i64, _i64,
+                               _int, _int, _int, _int, _int, _int, _vp, _sz, _vp]),
     "blr_blast_static": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
                                 _int, _int, _int, _int, _int, _vp, _i64, _vp]),
     "blr_blast_static_status": (_int, [_vp]),

@@ -71,6 +71,30 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     return ops._like_input(out, x)
 
 
+def blast_wq_multi(x, layers, bits: int, group: int = 0, x_mul=None, biases=None, residuals=None):
+    """blast_wq for several layers on one input: layers = [(Uq, u_scale, Vq, v_scale, S), ...] with equal shapes; the
+    options of blast_kernels.blast_multi_torch_layout.  One pair of launches up to 4 tokens, else layer by layer."""
+    assert bits in (8, 4)
+    per = 1 if bits == 8 else 2
+    Uq0, us0, Vq0, vs0, S0 = layers[0]
+    b, q, r, p = us0.size(0), us0.size(1), vs0.size(1), Vq0.size(-1) * per
+    x2 = ops._flat2d(x)
+    xm2 = None if x_mul is None else ops._flat2d(x_mul)
+    res2 = None if residuals is None else [None if t is None else ops._flat2d(t) for t in residuals]
+    outs = ops.blast_multi(x2, layers, bits, group, b, p, q, r, xm2, biases, res2) if 1 <= len(layers) <= 3 else None
+    if outs is None:
+        xe = x2 if xm2 is None else torch.nn.functional.silu(x2) * xm2
+        outs = []
+        for i, (Uq, us, Vq, vs, S) in enumerate(layers):
+            o = ops._flat2d(blast_wq(xe, Uq, us, Vq, vs, S, bits, group))
+            if biases is not None and biases[i] is not None:
+                o += biases[i]
+            if res2 is not None and res2[i] is not None:
+                o += res2[i]
+            outs.append(o)
+    return [ops._like_input(o, x) for o in outs]
+
+
 def blast_wq_host(x_host, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0, out=None):
     """blast_wq for activations in host memory: x_host (N, b*P) 16-bit CPU tensor (pinned for asynchronous copies),
     factors on the device.  One library call enqueues copy-in, the kernel and copy-out on the device's current

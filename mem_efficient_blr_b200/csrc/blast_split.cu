@@ -176,9 +176,22 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 // A warp turns token rows of K 16-bit values (global memory, 16-byte aligned, rows `row_stride` elements apart in the
 // order given by row_src) into fixed-point rows in shared memory and their scales.  PPL = 16-byte pieces per lane and
 // row (K <= 256 PPL); 8 / PPL rows are loaded together so that their global-memory latencies overlap.
-template <bool BF16, int WB, int PPL, typename RowSrc>
-__device__ __forceinline__ void fx_quantize_rows(int first, int nrows, int step, RowSrc row_src, int K, uint32_t dst0, uint32_t pitch,
-                                                 float* scales, int lane) {
+// 8 packed 16-bit values: a := silu(a) * m, rounded back to the 16-bit type (what the unfused product would hold).
+template <bool BF16>
+__device__ __forceinline__ void silu_mul8(uint4& a, const uint4& m) {
+  float fa[8], fm[8];
+  unpack8<BF16>(a, fa);
+  unpack8<BF16>(m, fm);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) fa[e] = fa[e] / (1.f + __expf(-fa[e])) * fm[e];
+  a.x = pack16x2<BF16>(fa[0], fa[1]); a.y = pack16x2<BF16>(fa[2], fa[3]);
+  a.z = pack16x2<BF16>(fa[4], fa[5]); a.w = pack16x2<BF16>(fa[6], fa[7]);
+}
+
+// ACT: the rows are silu(row_src) * row_mul (row_mul(r) gives the second operand's row).
+template <bool BF16, int WB, int PPL, bool ACT, typename RowSrc, typename RowMul>
+__device__ __forceinline__ void fx_quantize_rows(int first, int nrows, int step, RowSrc row_src, RowMul row_mul, int K, uint32_t dst0,
+                                                 uint32_t pitch, float* scales, int lane) {
   constexpr int RB = 8 / PPL;
   const int pieces = K >> 3;
   for (int r0 = first; r0 < nrows; r0 += step * RB) {
@@ -190,7 +203,10 @@ __device__ __forceinline__ void fx_quantize_rows(int first, int nrows, int step,
       for (int i = 0; i < PPL; ++i) {
         const int pc = i * 32 + lane;
         v[rb][i] = make_uint4(0, 0, 0, 0);
-        if (r < nrows && pc < pieces) v[rb][i] = ld_global_cg_v4(row_src(r) + pc * 8);
+        if (r < nrows && pc < pieces) {
+          v[rb][i] = ld_global_cg_v4(row_src(r) + pc * 8);
+          if constexpr (ACT) silu_mul8<BF16>(v[rb][i], ld_global_cg_v4(row_mul(r) + pc * 8));
+        }
       }
     }
 #pragma unroll
@@ -227,14 +243,14 @@ __device__ __forceinline__ void fx_quantize_rows(int first, int nrows, int step,
   }
 }
 
-template <bool BF16, int WB, typename RowSrc>
-__device__ __forceinline__ void fx_quantize(int first, int nrows, int step, RowSrc row_src, int K, uint32_t dst0, uint32_t pitch,
-                                            float* scales, int lane) {
+template <bool BF16, int WB, bool ACT, typename RowSrc, typename RowMul>
+__device__ __forceinline__ void fx_quantize(int first, int nrows, int step, RowSrc row_src, RowMul row_mul, int K, uint32_t dst0,
+                                            uint32_t pitch, float* scales, int lane) {
   const int ppl = ((K >> 3) + 31) >> 5;
-  if (ppl <= 1) fx_quantize_rows<BF16, WB, 1>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
-  else if (ppl <= 2) fx_quantize_rows<BF16, WB, 2>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
-  else if (ppl <= 4) fx_quantize_rows<BF16, WB, 4>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
-  else fx_quantize_rows<BF16, WB, 8>(first, nrows, step, row_src, K, dst0, pitch, scales, lane);
+  if (ppl <= 1) fx_quantize_rows<BF16, WB, 1, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
+  else if (ppl <= 2) fx_quantize_rows<BF16, WB, 2, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
+  else if (ppl <= 4) fx_quantize_rows<BF16, WB, 4, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
+  else fx_quantize_rows<BF16, WB, 8, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
 }
 
 // ---------------------------------------------------------------------------------------------------- chunk consumers
@@ -401,6 +417,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   const int N = p.N, nb = p.b, bo = p.bo, nch = p.nch0, R = p.R;
   const int nbx = nch * abox, SL = nch < kW ? nch : kW;
   const int r0 = blockIdx.x * kSplitRanks;
+  const SplitProblem& q = p.pr[blockIdx.y];
   const uint32_t xbox = (uint32_t)N * 128u, xpitch = FX ? fx_pitch(p.P, WB) : 0u;
   const FrontLayout L = front_layout(p);
   const uint32_t bar = smem_base + L.bar;
@@ -425,10 +442,10 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   if (tid == 0) {
     mbar_arrive_expect_tx(bar, (uint32_t)nch * nb * 1024u);
     constexpr int kstep = wbits == 16 ? 64 : 128;
-    for (int c = 0; c < nch; ++c) tma_load_3d(smem_base + L.w + (uint32_t)c * nb * 1024u, &p.tmV, c * kstep, r0, 0, bar);
+    for (int c = 0; c < nch; ++c) tma_load_3d(smem_base + L.w + (uint32_t)c * nb * 1024u, &q.tmV, c * kstep, r0, 0, bar);
   }
   {
-    const uint16_t* S = reinterpret_cast<const uint16_t*>(p.S);
+    const uint16_t* S = reinterpret_cast<const uint16_t*>(q.S);
     const bool s_vec = S != nullptr && p.s_r == 1 && ((p.s_i | p.s_j) & 7) == 0 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
     const uint32_t pitch = (uint32_t)nb * 16u + 16u;
     for (int i = warp; i < bo; i += kW)
@@ -445,7 +462,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
         }
       }
     if (tid < nb * 8) {
-      float v = (!GS && p.v_scale != nullptr) ? __half2float(__ldg(p.v_scale + (long long)(tid >> 3) * R + r0 + (tid & 7))) : 1.f;
+      float v = (!GS && q.v_scale != nullptr) ? __half2float(__ldg(q.v_scale + (long long)(tid >> 3) * R + r0 + (tid & 7))) : 1.f;
       if (WB == 4) v *= 0.0625f;  // the int4 operands are 16 v
       vs[tid] = v;
     }
@@ -461,16 +478,39 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   // ---- x, all of it, one (in-block, token) row per warp and turn
   {
     const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
+    const uint16_t* xm = reinterpret_cast<const uint16_t*>(p.x_mul);
+    const bool act = p.act == kSplitActSiluMul;
     const int nrows = nb * N;
     if constexpr (FX) {
       const long long ldx = p.ldx;
       const int P = p.P;
       const uint32_t mN = p.magic_N;
-      auto row_src = [&](int r) {
+      auto row_off = [&](int r) {
         const int j = (int)fastdiv((uint32_t)r, (uint32_t)N, mN), n = r - j * N;
-        return x + (long long)n * ldx + (long long)j * P;
+        return (long long)n * ldx + (long long)j * P;
       };
-      fx_quantize<BF16, WB>(warp, nrows, kW, row_src, P, smem_base + L.xs, xpitch, sx, lane);
+      auto row_src = [&](int r) { return x + row_off(r); };
+      auto row_mul = [&](int r) { return xm + row_off(r); };
+      if (act) fx_quantize<BF16, WB, true>(warp, nrows, kW, row_src, row_mul, P, smem_base + L.xs, xpitch, sx, lane);
+      else fx_quantize<BF16, WB, false>(warp, nrows, kW, row_src, row_mul, P, smem_base + L.xs, xpitch, sx, lane);
+    } else if (act) {
+      // silu(x) * x_mul through registers into the same [in-block][64-wide box][token][128 B] layout, zero past P
+      const int cpr = nbx * 8;
+      for (int rowi = warp; rowi < nrows; rowi += kW) {
+        const int j = (int)fastdiv((uint32_t)rowi, (uint32_t)N, p.magic_N), n = rowi - j * N;
+        const long long off = (long long)n * p.ldx + (long long)j * p.P;
+        const uint32_t dst0 = smem_base + L.xs + (uint32_t)(j * nbx * N + n) * 128u;
+        for (int ch = lane; ch < cpr; ch += 32) {
+          const int kb = ch >> 3, c16 = ch & 7, k = ch * 8;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (k < p.P) {
+            v = ld_global_cg_v4(x + off + k);
+            silu_mul8<BF16>(v, ld_global_cg_v4(xm + off + k));
+          }
+          const uint32_t d = dst0 + (uint32_t)kb * xbox + (uint32_t)((c16 ^ (n & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(d), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+      }
     } else {
       // [in-block][64-wide box][token][128 B], zero past P
       const int cpr = nbx * 8;  // 16-byte pieces per row
@@ -527,7 +567,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
         const uint32_t sA = smem_base + L.xs + (uint32_t)(j * N) * xpitch + (uint32_t)c * kChunkAct;
         float gsc = 0.f, gsc2 = 0.f;
         if constexpr (GS) {
-          const __half* srow = p.v_scale + ((long long)j * R + r0 + g) * ngroups;
+          const __half* srow = q.v_scale + ((long long)j * R + r0 + g) * ngroups;
           const int gi = c * (WB == 8 ? 1 : 2);
           gsc = __half2float(__ldg(srow + gi));
           if (WB == 4 && gi + 1 < ngroups) gsc2 = __half2float(__ldg(srow + gi + 1));
@@ -580,7 +620,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
       for (; j < nb; ++j) a4[0] = fmaf(load16<BF16>(srow + j * 16, 0), yp[j * N * 8], a4[0]);
       float a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
       if (p.round_z) a = round_clamp_i8(a);
-      store16<BF16>(p.z, (long long)t * R + r0 + gg, a);
+      store16<BF16>(q.z, (long long)t * R + r0 + gg, a);
     }
   }
   BLR_CK(11);
@@ -602,6 +642,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   const int nseg = (nch + kSplitStageChunks - 1) / kSplitStageChunks;
   const int NST = p.nstages;
   const int blk = blockIdx.x / p.cpb, part = blockIdx.x - blk * p.cpb;
+  const SplitProblem& q = p.pr[blockIdx.y];
   const int gpb = (Q + 15) >> 4;
   const int g_lo = part * p.gpc, g_hi = min(gpb, g_lo + p.gpc), ng = g_hi - g_lo;
   const uint32_t zbox = (uint32_t)N * 128u, zpitch = FX ? fx_pitch(R, WB) : 0u;
@@ -648,7 +689,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
         const uint32_t dst = smem_base + L.ring + rp.s * kSplitStageBytes, fb = full0 + 8 * rp.s;
         if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)nc * kSplitChunkBytes);
         __syncwarp();
-        if (lane < nc) tma_load_3d(dst + lane * kSplitChunkBytes, &p.tmU, (c_lo + lane) * kstep, g * 16, blk, fb);
+        if (lane < nc) tma_load_3d(dst + lane * kSplitChunkBytes, &q.tmU, (c_lo + lane) * kstep, g * 16, blk, fb);
         rp.advance(NST);
       }
     return;
@@ -658,8 +699,8 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   constexpr int kCT = kW * 32;
   const int gq = lane >> 2, tq = lane & 3;
   for (int e = ctid; e < ng * 16; e += kCT) {
-    const int q = g_lo * 16 + e;
-    float v = (!GS && p.u_scale != nullptr && q < Q) ? __half2float(__ldg(p.u_scale + (long long)blk * Q + q)) : 1.f;
+    const int qq = g_lo * 16 + e;
+    float v = (!GS && q.u_scale != nullptr && qq < Q) ? __half2float(__ldg(q.u_scale + (long long)blk * Q + qq)) : 1.f;
     if (WB == 4) v *= 0.0625f;
     us[e] = v;
   }
@@ -673,7 +714,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
 #endif
   // ---- z of this out-block
   {
-    const uint16_t* z = reinterpret_cast<const uint16_t*>(p.z) + (long long)blk * N * R;
+    const uint16_t* z = reinterpret_cast<const uint16_t*>(q.z) + (long long)blk * N * R;
     if constexpr (FX) {
       // Every token row is shared out over wpr = 16 / N warps (at least one): each thread takes its 16-byte pieces,
       // the warps' maxima meet in shared memory, then every thread converts its own pieces.
@@ -773,7 +814,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
         float ga = 0.f, ga8 = 0.f, gb = 0.f, gb8 = 0.f;
         if constexpr (GS) {
           const int m = g * 16 + gq, gi = c * (WB == 8 ? 1 : 2);
-          const __half* srow = p.u_scale + ((long long)blk * Q + m) * ngroups;
+          const __half* srow = q.u_scale + ((long long)blk * Q + m) * ngroups;
           if (m < Q) ga = __half2float(__ldg(srow + gi));
           if (m + 8 < Q) ga8 = __half2float(__ldg(srow + 8 * ngroups + gi));
           if (WB == 4 && gi + 1 < ngroups) {
@@ -836,14 +877,17 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     const int rows = ng * 16;
     for (int e = ctid; e < rows * N; e += kCT) {
       const int n = e / rows, lr = e - n * rows, gl = lr >> 4, row = lr & 15;
-      const int q = (g_lo + gl) * 16 + row;
-      if (q >= Q) continue;
+      const int qq = (g_lo + gl) * 16 + row;
+      if (qq >= Q) continue;
       const float* sp = partial + (size_t)(gl * SL) * 16 * NP + row * NP + n;
       float s = 0.f;
       for (int cs = 0; cs < SL; ++cs) s += sp[cs * 16 * NP];
       s *= us[lr];
       if constexpr (FX) s *= sz[n];
-      store16<BF16>(p.out, (long long)n * p.ldo + (long long)blk * Q + q, s);
+      const long long col = (long long)blk * Q + qq;
+      if (q.bias != nullptr) s += load16<BF16>(q.bias, col);
+      if (q.residual != nullptr) s += load16<BF16>(q.residual, (long long)n * q.ldr + col);
+      store16<BF16>(q.out, (long long)n * q.ldo + col, s);
     }
   }
   BLR_CK(10);
@@ -894,11 +938,11 @@ static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
 #ifdef BLR_TIMELINE
   if (getenv("BLR_NO_PDL")) cfg.numAttrs = 0;  // profiling builds only: launches fully serialised
 #endif
-  cfg.gridDim = dim3(p.R / kSplitRanks);
+  cfg.gridDim = dim3(p.R / kSplitRanks, p.nprob);
   cfg.blockDim = dim3(kSplitFrontThreads);
   cfg.dynamicSmemBytes = fs;
   BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)front, args));
-  cfg.gridDim = dim3(p.bo * p.cpb);
+  cfg.gridDim = dim3(p.bo * p.cpb, p.nprob);
   cfg.blockDim = dim3(kSplitBackThreads);
   cfg.dynamicSmemBytes = bs;
   BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)back, args_b));

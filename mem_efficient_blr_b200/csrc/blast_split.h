@@ -30,17 +30,32 @@ static constexpr int kSplitChunkBytes = 16 * 128;
 static constexpr int kSplitStageBytes = kSplitStageChunks * kSplitChunkBytes;
 static constexpr int kSplitMaxBlocks = 32;
 
-struct alignas(64) SplitParams {
+static constexpr int kSplitMaxProblems = 3;  // layers that share x and their shapes, run by one pair of launches
+
+// Input transform applied while x is staged: none, or x := silu(x) * x_mul (the SwiGLU product in front of a
+// down projection; models the reference's `down_proj(act_fn(gate_proj(h)) * up_proj(h))`).
+static constexpr int kSplitActNone = 0, kSplitActSiluMul = 1;
+
+struct SplitProblem {
   CUtensorMap tmV;  // dims (P | row bytes, R, b), box (128 B, 8, b), 128-byte swizzle
   CUtensorMap tmU;  // dims (R | row bytes, Q, b_out), box (128 B, 16, 1), 128-byte swizzle
-  const void* x;
   const void* S;           // coupling factors or nullptr (all ones)
   const __half* v_scale;   // (b, R) or (b, R, P / group) or nullptr
   const __half* u_scale;   // (b_out, Q) or (b_out, Q, R / group) or nullptr
   void* z;                 // (b_out, N, R) 16-bit, written by the front kernel, read by the back kernel
-  void* out;
+  void* out;               // (N, b_out * Q), row stride ldo
+  const void* bias;        // (b_out * Q) 16-bit added to every row, or nullptr
+  const void* residual;    // (N, b_out * Q) 16-bit added to the result (row stride ldr), or nullptr
+  long long ldo, ldr;
+};
+
+struct alignas(64) SplitParams {
+  SplitProblem pr[kSplitMaxProblems];  // blockIdx.y picks the problem; all share x, the shapes and the strides of S
+  const void* x;
+  const void* x_mul;       // second input of the input transform (same shape and row stride as x), or nullptr
   unsigned* status;        // set to 1 when a wait ran out
-  long long ldx, ldo, s_i, s_j, s_r;
+  long long ldx, s_i, s_j, s_r;
+  int nprob, act;
   int N, b, bo, P, Q, R;
   int wbits, group;
   int round_y, round_z;
@@ -49,7 +64,7 @@ struct alignas(64) SplitParams {
   int nstages;             // back kernel: ring stages
   unsigned magic_N, magic_nch0, magic_nch1;  // ceil(2^32 / d) for d = N, nch0, nch1 (0 for d = 1): division-free quotients
 #ifdef BLR_TIMELINE
-  unsigned long long* timeline;  // profiling builds: 8 stamps per CTA of this launch
+  unsigned long long* timeline;  // profiling builds: 16 stamps per CTA of this launch
 #endif
 };
 

@@ -155,41 +155,47 @@ static int check_layout(int layout) {
 }
 
 // ---------------------------------------------------------------------------------- BLAST (16-bit and quantised)
-// Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
 static constexpr int kSubsliceMinTokens = 4;
 // 0: automatic, 1: grid-wide streaming kernel only, 2: no two-launch path (cluster kernel where it applies)
 static std::atomic<int> g_decode_path{0};
 
+// One layer of a two-launch call (all layers of a call share x, the shapes and the strides of S).
+struct SplitLayer {
+  const void *U, *u_scale, *V, *v_scale, *S, *bias, *residual;
+  void* out;
+  int64_t ldo, ldr;
+};
+
 // Two-launch path (blast_split.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
-static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
-                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
-                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
-                       int64_t ldo, const Workspace& w, cudaStream_t stream) {
+// `zbase` is 16-bit scratch for nprob * bo * N * R values.
+static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int64_t N, int dtype, int nprob,
+                             const SplitLayer* layers, int u_layout, int v_layout, int wb, int group, int64_t s_i, int64_t s_j,
+                             int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* zbase, unsigned* status,
+                             cudaStream_t stream) {
   // Measured crossover against the cluster kernel on the Llama-7B shapes: the two-launch path wins up to 4 tokens
   // with quantised factors (its fixed-point conversion of the activations grows with the token count) and up to
   // 8 tokens with 16-bit factors.
-  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > (u_bits == 16 ? 8 : 4)) return 1;
-  if (u_layout != BLR_W_KMAJOR || v_layout != BLR_W_KMAJOR || u_bits != v_bits || b > kSplitMaxBlocks) return 1;
-  const int wb = u_bits;
+  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > (wb == 16 ? 8 : 4)) return 1;
+  if (u_layout != BLR_W_KMAJOR || v_layout != BLR_W_KMAJOR || b > kSplitMaxBlocks || nprob < 1 || nprob > kSplitMaxProblems) return 1;
   const long long kbV = (long long)P * wb / 8, kbU = (long long)R * wb / 8;
   if (R % kSplitRanks != 0 || P % 8 != 0 || kbV % 16 != 0 || kbU % 16 != 0 || (wb == 4 && ((P | R) & 1))) return 1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ldx % 8 != 0) return 1;
+  if (act != kSplitActNone && (x_mul == nullptr || (reinterpret_cast<uintptr_t>(x_mul) & 15) != 0)) return 1;
   if (group != 0 && (group != kScaleGroup || P % kScaleGroup != 0 || R % kScaleGroup != 0)) return 1;
   if (wb != 16 && (P > 2048 || R > 2048)) return 1;  // a warp holds a whole activation row in registers while it scales it
   DeviceInfo di;
   int rc;
   if ((rc = device_info(&di))) return rc;
   SplitParams p = {};
-  p.x = x; p.S = S; p.v_scale = static_cast<const __half*>(v_scale); p.u_scale = static_cast<const __half*>(u_scale);
-  p.z = w.region_b; p.out = out; p.status = w.counters + 255;
-  p.ldx = ldx; p.ldo = ldo; p.s_i = s_i; p.s_j = s_j; p.s_r = s_r;
+  p.x = x; p.x_mul = x_mul; p.act = act; p.nprob = nprob; p.status = status;
+  p.ldx = ldx; p.s_i = s_i; p.s_j = s_j; p.s_r = s_r;
   p.N = (int)N; p.b = b; p.bo = bo; p.P = P; p.Q = Q; p.R = R;
   p.wbits = wb; p.group = group; p.round_y = act8; p.round_z = act8;
   p.nch0 = (int)((kbV + 127) / 128);
   p.nch1 = (int)((kbU + 127) / 128);
-  // back kernel: every CTA a run of 16-row groups of one out-block, about one CTA per SM
+  // back kernel: every CTA a run of 16-row groups of one out-block, about one CTA per SM over all layers of the call
   const int gpb = (Q + 15) / 16;
-  int cpb = di.sm_count / bo;
+  int cpb = di.sm_count / (bo * nprob);
   if (cpb < 1) cpb = 1;
   if (cpb > gpb) cpb = gpb;
   p.gpc = (gpb + cpb - 1) / cpb;
@@ -212,21 +218,39 @@ static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const v
   p.nstages = nst;
   const CUtensorMapDataType dt = wb == 16 ? dt16(dtype) : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const uint32_t inner_box = wb == 16 ? 64u : 128u;
-  {
-    const uint64_t dims[3] = {wb == 16 ? (uint64_t)P : (uint64_t)kbV, (uint64_t)R, (uint64_t)b};
-    const uint64_t str[2] = {(uint64_t)kbV, (uint64_t)R * kbV};
-    const uint32_t box[3] = {inner_box, (uint32_t)kSplitRanks, (uint32_t)b};
-    if ((rc = encode_tmap_3d(&p.tmV, dt, V, dims, str, box, Swz::B128))) return rc;
-  }
-  {
-    const uint64_t dims[3] = {wb == 16 ? (uint64_t)R : (uint64_t)kbU, (uint64_t)Q, (uint64_t)bo};
-    const uint64_t str[2] = {(uint64_t)kbU, (uint64_t)Q * kbU};
-    const uint32_t box[3] = {inner_box, 16u, 1u};
-    if ((rc = encode_tmap_3d(&p.tmU, dt, U, dims, str, box, Swz::B128))) return rc;
+  for (int i = 0; i < nprob; ++i) {
+    const SplitLayer& l = layers[i];
+    SplitProblem& q = p.pr[i];
+    q.S = l.S; q.v_scale = static_cast<const __half*>(l.v_scale); q.u_scale = static_cast<const __half*>(l.u_scale);
+    q.z = static_cast<uint8_t*>(zbase) + (size_t)i * align256((size_t)bo * N * R * 2);
+    q.out = l.out; q.ldo = l.ldo; q.bias = l.bias; q.residual = l.residual; q.ldr = l.ldr;
+    {
+      const uint64_t dims[3] = {wb == 16 ? (uint64_t)P : (uint64_t)kbV, (uint64_t)R, (uint64_t)b};
+      const uint64_t str[2] = {(uint64_t)kbV, (uint64_t)R * kbV};
+      const uint32_t box[3] = {inner_box, (uint32_t)kSplitRanks, (uint32_t)b};
+      if ((rc = encode_tmap_3d(&q.tmV, dt, l.V, dims, str, box, Swz::B128))) return rc;
+    }
+    {
+      const uint64_t dims[3] = {wb == 16 ? (uint64_t)R : (uint64_t)kbU, (uint64_t)Q, (uint64_t)bo};
+      const uint64_t str[2] = {(uint64_t)kbU, (uint64_t)Q * kbU};
+      const uint32_t box[3] = {inner_box, 16u, 1u};
+      if ((rc = encode_tmap_3d(&q.tmU, dt, l.U, dims, str, box, Swz::B128))) return rc;
+    }
   }
   return launch_blast_split(p, dtype == BLR_DTYPE_BF16, stream);
 }
 
+static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
+                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
+                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
+                       int64_t ldo, const Workspace& w, cudaStream_t stream) {
+  if (u_bits != v_bits) return 1;
+  const SplitLayer l = {U, u_scale, V, v_scale, S, nullptr, nullptr, out, ldo, 0};
+  return split_blast_multi(x, ldx, nullptr, kSplitActNone, N, dtype, 1, &l, u_layout, v_layout, u_bits, group, s_i, s_j, s_r, b, bo,
+                           P, Q, R, act8, w.region_b, w.counters + 255, stream);
+}
+
+// Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
 static int cluster_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                          const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                          int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* out,
@@ -563,6 +587,40 @@ int blr_blast_static_status(void* stream) {
   BLR_CUDA_OK(cudaMemsetAsync(wp + 255 * sizeof(unsigned), 0, sizeof(unsigned), st));
   set_last_error("a blr_blast_static call gave up on a device-side wait (status words %u, %u)", words[3], words[255]);
   return BLR_ERR_TIMEOUT;
+}
+
+int blr_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int64_t n_tokens, int dtype, int n_problems,
+                    const blr_blast_problem* problems, int64_t s_i, int64_t s_j, int64_t s_r, int bits, int group, int b, int P,
+                    int Q, int R, void* ws, size_t ws_bytes, void* stream) {
+  const int64_t N = n_tokens;
+  BLR_REQUIRE(N >= 0, BLR_ERR_ARG, "token count must not be negative");
+  if (N == 0) return BLR_OK;
+  BLR_REQUIRE(x != nullptr && problems != nullptr, BLR_ERR_ARG, "x and problems must not be null");
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  BLR_REQUIRE(n_problems >= 1 && n_problems <= kSplitMaxProblems, BLR_ERR_UNSUPPORTED, "1..%d layers per call, got %d",
+              kSplitMaxProblems, n_problems);
+  BLR_REQUIRE(bits == 16 || bits == 8 || bits == 4, BLR_ERR_ARG, "bits must be 16, 8 or 4, got %d", bits);
+  BLR_REQUIRE(act == BLR_ACT_NONE || act == BLR_ACT_SILU_MUL, BLR_ERR_ARG, "unknown input transform %d", act);
+  BLR_REQUIRE(act == BLR_ACT_NONE || x_mul != nullptr, BLR_ERR_ARG, "the silu-mul transform needs x_mul");
+  BLR_REQUIRE(b >= 2 && P > 0 && Q > 0 && R > 0 && ldx >= (int64_t)b * P, BLR_ERR_SHAPE, "bad dimensions");
+  SplitLayer layers[kSplitMaxProblems];
+  for (int i = 0; i < n_problems; ++i) {
+    const blr_blast_problem& q = problems[i];
+    BLR_REQUIRE(q.U && q.V && q.S && q.out && q.ldo >= (int64_t)b * Q, BLR_ERR_ARG, "layer %d: null factor / output or short row", i);
+    BLR_REQUIRE(bits == 16 || (q.u_scale && q.v_scale), BLR_ERR_ARG, "layer %d: quantised factors need scales", i);
+    BLR_REQUIRE(q.residual == nullptr || q.ldr >= (int64_t)b * Q, BLR_ERR_SHAPE, "layer %d: residual rows shorter than the output", i);
+    layers[i] = {q.U, bits == 16 ? nullptr : q.u_scale, q.V, bits == 16 ? nullptr : q.v_scale, q.S, q.bias, q.residual, q.out, q.ldo, q.ldr};
+  }
+  Workspace w;
+  int rc = carve(ws, ws_bytes, N, (int64_t)n_problems * b, R, &w);
+  if (rc) return rc;
+  rc = split_blast_multi(x, ldx, x_mul, act == BLR_ACT_SILU_MUL ? kSplitActSiluMul : kSplitActNone, N, dtype, n_problems, layers,
+                         BLR_W_KMAJOR, BLR_W_KMAJOR, bits, group, s_i, s_j, s_r, b, b, P, Q, R, 0, w.region_b, w.counters + 255,
+                         static_cast<cudaStream_t>(stream));
+  BLR_REQUIRE(rc != 1, BLR_ERR_UNSUPPORTED,
+              "the fused call serves up to 8 tokens with 16-bit factors and 4 with quantised ones, contraction-contiguous "
+              "factors and shapes the two-launch path takes: run the layers one by one instead");
+  return rc;
 }
 
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* Uq, const void* u_scale,

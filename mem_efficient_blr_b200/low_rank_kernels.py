@@ -29,6 +29,22 @@ def triton_low_rank_fp32(x, a, b):
     return ops.low_rank_f32(ops.flat2d_f32(x), a, b, L.MMAJOR, L.MMAJOR, i, r, o)
 
 
+def triton_low_rank_load_store_fp16(x, a, b):
+    """Replaces triton_low_rank_load_store_fp16 (low_rank_kernels.py:435-449): a bandwidth probe that reads x, a and b
+    and writes y (N, O) with the index of the 64-wide output tile in every element (the reference kernel's default
+    BLOCK_SIZE_O, low_rank_kernels.py:229-234), no arithmetic."""
+    i, r, o = _dims(x, a, b)
+    x2 = ops._flat2d(x).contiguous()
+    return ops.load_store_probe((x2, a, b), x2.shape[0], o, x.dtype, 64)
+
+
+def triton_low_rank_load_store_fp32(x, a, b):
+    """Replaces triton_low_rank_load_store_fp32 (low_rank_kernels.py:419-433); float32 tensors."""
+    i, r, o = _dims(x, a, b)
+    x2 = ops.flat2d_f32(x).contiguous()
+    return ops.load_store_probe((x2, a, b), x2.shape[0], o, x.dtype, 64)
+
+
 def low_rank_torch_layout(x, Vt, Ut):
     """torch layouts Vt (R, I), Ut (O, R) (torch_funcs/low_rank_funcs.py:4-28); batch dims restored."""
     r, i = Vt.shape

@@ -318,3 +318,73 @@ def dequantize_sym(q: torch.Tensor, scale: torch.Tensor, bits: int, group: int, 
     L.check(L.load().blr_dequantize_sym(q.data_ptr(), scale.data_ptr(), rows, K, bits, group, L.dtype_code(dtype),
                                         w.data_ptr(), L.stream_ptr(q.device)))
     return w
+
+
+# ----------------------------------------------------------------------------- load / store probe
+def load_store_probe(operands, n: int, out_features: int, dtype: torch.dtype, tile: int) -> torch.Tensor:
+    """Streams up to three contiguous operand tensors once and returns out (n, out_features) with out[:, o] = o // tile
+    (zeros for tile = 0): the traffic of an operator without its arithmetic."""
+    assert 1 <= len(operands) <= 3
+    _need_cuda(operands[0], *operands[1:])
+    for t in operands:
+        assert t.is_contiguous() and (t.numel() * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
+    dev = operands[0].device
+    out = torch.empty((n, out_features), dtype=dtype, device=dev)
+    kind = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dtype]
+    args = []
+    for t in list(operands) + [None] * (3 - len(operands)):
+        args += [0, 0] if t is None else [t.data_ptr(), t.numel() * t.element_size()]
+    L.check(L.load().blr_load_store_probe(*args, kind, out.data_ptr(), n, out_features, out.stride(0) if n else out_features,
+                                          tile, L.stream_ptr(dev)))
+    return out
+
+
+# ----------------------------------------------------------------------------- several layers in one pair of launches
+def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int, x_mul=None, biases=None, residuals=None):
+    """Up to three BLAST layers that share x (N, b*P) and their shapes, through blr_blast_multi.
+    layers: tuples (U, Vt, S) of 16-bit factors (bits = 16) or (Uq, u_scale, Vq, v_scale, S) (bits = 8 | 4), torch
+    layouts.  x_mul: the input becomes silu(x) * x_mul.  biases / residuals: per layer, None or a tensor added to the
+    layer's result ((b*Q,) / (N, b*Q)).  Returns the list of outputs, or None when the fused call does not apply
+    (token count or shape outside the two-launch decode path): the caller then runs the layers one by one."""
+    n = x.shape[0]
+    if n == 0 or n > (8 if bits == 16 else 4) or torch.compiler.is_compiling():
+        return None
+    x = _rows(x)
+    if x_mul is not None:
+        x_mul = _rows(x_mul)
+        assert x_mul.shape == x.shape and x_mul.dtype == x.dtype
+        if x_mul.stride(0) != x.stride(0):
+            x, x_mul = x.contiguous(), x_mul.contiguous()
+    k = len(layers)
+    arr = (L.BlastProblem * k)()
+    outs, keep = [], []
+    for i, lay in enumerate(layers):
+        if bits == 16:
+            U, Vt, S = lay
+            us = vs = None
+        else:
+            U, us, Vt, vs, S = lay
+        _need_cuda(x, U, Vt, S)
+        out = torch.empty((n, b * Q), dtype=x.dtype, device=x.device)
+        bias = None if biases is None else biases[i]
+        res = None if residuals is None else residuals[i]
+        if res is not None:
+            res = _rows(res)
+            assert res.shape == out.shape and res.dtype == x.dtype
+        arr[i].U, arr[i].V, arr[i].S = U.data_ptr(), Vt.data_ptr(), S.data_ptr()
+        arr[i].u_scale = 0 if us is None else us.data_ptr()
+        arr[i].v_scale = 0 if vs is None else vs.data_ptr()
+        arr[i].bias = 0 if bias is None else bias.data_ptr()
+        arr[i].residual = 0 if res is None else res.data_ptr()
+        arr[i].ldr = 0 if res is None else res.stride(0)
+        arr[i].out, arr[i].ldo = out.data_ptr(), out.stride(0)
+        outs.append(out)
+        keep.append((bias, res))
+    ws, st = _ws(x, n, k * b, R)
+    rc = L.load().blr_blast_multi(x.data_ptr(), x.stride(0), 0 if x_mul is None else x_mul.data_ptr(),
+                                  L.ACT_NONE if x_mul is None else L.ACT_SILU_MUL, n, L.dtype_code(x.dtype), k, arr,
+                                  b * R, R, 1, bits, group, b, P, Q, R, ws.data_ptr(), ws.numel(), st)
+    if rc == -6:   # BLR_ERR_UNSUPPORTED: shape outside the fused path
+        return None
+    L.check(rc)
+    return outs

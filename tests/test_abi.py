@@ -54,6 +54,15 @@ def test_null_arguments_are_rejected_without_touching_a_device(lib):
     assert rc == -1 and b"bits" in lib.blr_last_error()
 
 
+def test_reference_probe_names_exist():
+    import mem_efficient_blr_b200.dense_kernels as dk
+    import mem_efficient_blr_b200.low_rank_kernels as lk
+    for m, names in ((lk, ("triton_low_rank_load_store_fp16", "triton_low_rank_load_store_fp32")),
+                     (dk, ("triton_dense_load_store_fp16", "triton_dense_load_store_fp32"))):
+        for n in names:
+            assert callable(getattr(m, n))
+
+
 REFERENCE_NAMES = {
     "blast_kernels": ["triton_blast_partial_fp16", "triton_blast_partial_fp32", "triton_blast_partial_grouped_fp16",
                       "triton_blast_partial_grouped_fp32", "triton_blast_partial_grouped_persistent_fp16",

@@ -75,3 +75,25 @@ def test_low_rank_and_dense_fp32(K):
     _close(y, ref.reshape(5, 56)); _close(zz, z.reshape(5, 24))
     x, Wt = orc.make_dense_inputs(5, 72, 56, torch.float32, seed=3)
     _close(K.dk.triton_dense_fp32(x.to(DEV), Wt.t().contiguous().to(DEV)), orc.dense(x, Wt).reshape(5, 56))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_load_store_probes_write_what_the_reference_probes_write(dtype):
+    """triton_low_rank_load_store_* stores the index of the 64-wide output tile (low_rank_kernels.py:229-234),
+    triton_dense_load_store_* stores zeros (dense_kernels.py:222-227); both return the 2-D (N, O) shape."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import mem_efficient_blr_b200.dense_kernels as dk
+    import mem_efficient_blr_b200.low_rank_kernels as lk
+    x = torch.randn(2, 5, 256, device="cuda:0", dtype=dtype)
+    a, b = torch.randn(256, 64, device="cuda:0", dtype=dtype), torch.randn(64, 200, device="cuda:0", dtype=dtype)
+    f = lk.triton_low_rank_load_store_fp32 if dtype == torch.float32 else lk.triton_low_rank_load_store_fp16
+    y = f(x, a, b)
+    torch.cuda.synchronize()
+    assert y.shape == (10, 200) and y.dtype == dtype
+    assert torch.equal(y.float().cpu(), (torch.arange(200) // 64).float().expand(10, 200))
+    w = torch.randn(256, 200, device="cuda:0", dtype=dtype)
+    g = dk.triton_dense_load_store_fp32 if dtype == torch.float32 else dk.triton_dense_load_store_fp16
+    y = g(x, w)
+    torch.cuda.synchronize()
+    assert y.shape == (10, 200) and float(y.abs().max()) == 0.0

@@ -433,3 +433,50 @@ def test_argument_errors_are_reported(K):
     x, U, Vt, S = orc.make_blast_inputs(2, 48, 64, 4, 64, torch.float16, seed=1)
     with pytest.raises(RuntimeError, match="multiple of 8"):
         K.bk.blast_torch_layout(*_cuda(x, U, Vt, S))
+
+
+@pytest.mark.parametrize("bits", [16, 8, 4])
+@pytest.mark.parametrize("N", [1, 3, 12])
+def test_fused_layers_bias_residual_and_swiglu_input(K, bits, N):
+    """blr_blast_multi: q/k/v-style layers on one input with bias and residual in the epilogue, and a down projection
+    fed with silu(gate) * up, against the oracle composition (N = 12 takes the layer-by-layer route)."""
+    I, O, b, R = 1024, 1536, 8, 256
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=200 + N)
+    sets = [(U, Vt, S)]
+    for s in (1, 2):
+        _, U2, Vt2, S2 = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=300 + s)
+        sets.append((U2, Vt2, S2))
+    g = torch.Generator().manual_seed(N)
+    biases = [torch.randn(O, generator=g).half() for _ in sets]
+    res = torch.randn(1, N, O, generator=g).half()
+    xm = torch.randn(1, N, I, generator=g).half()
+    xe = torch.nn.functional.silu(x.float()) * xm.float()
+
+    def ref_one(inp, f, bias, residual):
+        if bits == 16:
+            o = orc.blast(inp, *f)[0]
+        else:
+            Uq, us = orc.quantize_sym(f[0], bits)
+            Vq, vs = orc.quantize_sym(f[1], bits)
+            o = orc.blast_wq(inp, Uq, us, Vq, vs, f[2], bits)[0]
+        return o + bias.float() + residual.float()
+
+    if bits == 16:
+        dev_sets = [tuple(_cuda(*f)) for f in sets]
+        call = lambda inp, ls, **kw: K.bk.blast_multi_torch_layout(inp, ls, **kw)
+    else:
+        dev_sets = []
+        for f in sets:
+            Uq, us, Vq, vs = K.bq.quantize_blast_factors(f[0].to(DEV), f[1].to(DEV), bits)
+            dev_sets.append((Uq, us, Vq, vs, f[2].to(DEV)))
+        call = lambda inp, ls, **kw: K.bq.blast_wq_multi(inp, ls, bits, **kw)
+    # three layers, one input
+    got = call(x.to(DEV), dev_sets, biases=[t.to(DEV) for t in biases], residuals=[res.to(DEV)] * 3)
+    _sync_ok(K)
+    for o, f, bias in zip(got, sets, biases):
+        assert o.shape == (1, N, O)
+        assert orc.rel_fro(o.float().cpu(), ref_one(x, f, bias, res)) < TOL
+    # one layer on silu(x) * x_mul (the activations are rounded to 16 bits once, like the unfused product)
+    (got,) = call(x.to(DEV), dev_sets[:1], x_mul=xm.to(DEV), residuals=[res.to(DEV)])
+    _sync_ok(K)
+    assert orc.rel_fro(got.float().cpu(), ref_one(xe.half(), sets[0], torch.zeros(O), res)) < TOL
