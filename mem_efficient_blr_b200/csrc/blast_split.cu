@@ -56,6 +56,9 @@ struct BackLayout {
   uint32_t ring, zs, sz, part, us, bars, total;
 };
 __host__ __device__ static inline uint32_t up16(uint32_t v) { return (v + 15u) & ~15u; }
+// Warps that share one accumulation (an in-block of the front kernel, a 16-row group of the back kernel) when a CTA
+// has fewer of those than warps: each takes every share-th chunk of the contraction.
+__host__ __device__ static inline int split_share(int units) { return units >= kW ? 1 : kW / units; }
 // Bytes of one token row of fixed-point activations over K contraction indices (2 bytes per index), padded so
 // that the 16-byte fragment loads of neighbouring token rows fall into different banks.
 __host__ __device__ static inline uint32_t fx_pitch(int K, int wbits) {
@@ -65,7 +68,7 @@ __host__ __device__ static inline uint32_t fx_pitch(int K, int wbits) {
 
 __host__ __device__ static inline FrontLayout front_layout(const SplitParams& p) {
   const uint32_t np = p.N <= 8 ? 8 : 16;
-  const uint32_t abox = 16 / p.wbits, nbx = p.nch0 * abox, sl = p.nch0 < kW ? p.nch0 : kW;
+  const uint32_t abox = 16 / p.wbits, nbx = p.nch0 * abox, sl = split_share(p.b);
   FrontLayout L;
   uint32_t o = 0;
   L.w = o; o += (uint32_t)p.nch0 * p.b * 1024 + 1024;   // [chunk][in-block][8 rows][128 B] + one slab of slack
@@ -75,7 +78,7 @@ __host__ __device__ static inline FrontLayout front_layout(const SplitParams& p)
   L.sx = o; o += up16((uint32_t)p.b * p.N * 4);           // fixed-point scale of every (in-block, token) row
   L.s = o; o += up16((uint32_t)p.bo * (p.b * 16 + 16));   // [out-block][in-block][8 ranks] 16-bit, padded rows
   L.vs = o; o += (uint32_t)p.b * 8 * 4;                   // per-channel scales of the slice's rows
-  L.ypart = o; o += (uint32_t)p.b * sl * 8 * np * 4;      // [in-block][chunk slot][8 ranks][np tokens] fp32
+  L.ypart = o; o += sl > 1 ? (uint32_t)p.b * sl * 8 * np * 4 : 0u;  // [in-block][sharing warp][8 ranks][np tokens] fp32
   L.ybuf = o; o += (uint32_t)p.b * p.N * 8 * 4;           // [in-block][token][8 ranks] fp32
   L.bar = o; o += 16;
   L.total = o + 1024;  // room to align the base to 1 KiB
@@ -84,7 +87,7 @@ __host__ __device__ static inline FrontLayout front_layout(const SplitParams& p)
 
 __host__ __device__ static inline BackLayout back_layout(const SplitParams& p) {
   const uint32_t np = p.N <= 8 ? 8 : 16;
-  const uint32_t abox = 16 / p.wbits, nbz = p.nch1 * abox, sl = p.nch1 < kW ? p.nch1 : kW;
+  const uint32_t abox = 16 / p.wbits, nbz = p.nch1 * abox, sl = split_share(p.gpc);
   BackLayout L;
   uint32_t o = 0;
   L.ring = o; o += (uint32_t)p.nstages * kSplitStageBytes;
@@ -92,7 +95,7 @@ __host__ __device__ static inline BackLayout back_layout(const SplitParams& p) {
   if (p.wbits == 16) o += nbz * p.N * 128 + 2048;         // [box][token][128 B] + slack
   else o += (uint32_t)p.N * fx_pitch(p.R, p.wbits);       // [token][fixed-point row]
   L.sz = o; o += 32 * 4;                                  // fixed-point scale per token, then per-warp maxima
-  L.part = o; o += (uint32_t)p.gpc * sl * 16 * np * 4;    // [group][chunk slot][16 rows][np tokens] fp32
+  L.part = o; o += (uint32_t)p.gpc * sl * 16 * np * 4;    // [group][sharing warp][16 rows][np tokens] fp32
   L.us = o; o += (uint32_t)p.gpc * 16 * 4;                // per-channel scales of the CTA's rows
   L.bars = o; o += (2 * (uint32_t)p.nstages + 2) * 8;
   L.total = o + 1024;
@@ -173,9 +176,6 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   }
 }
 
-// A warp turns token rows of K 16-bit values (global memory, 16-byte aligned, rows `row_stride` elements apart in the
-// order given by row_src) into fixed-point rows in shared memory and their scales.  PPL = 16-byte pieces per lane and
-// row (K <= 256 PPL); 8 / PPL rows are loaded together so that their global-memory latencies overlap.
 // 8 packed 16-bit values: a := silu(a) * m, rounded back to the 16-bit type (what the unfused product would hold).
 template <bool BF16>
 __device__ __forceinline__ void silu_mul8(uint4& a, const uint4& m) {
@@ -188,69 +188,67 @@ __device__ __forceinline__ void silu_mul8(uint4& a, const uint4& m) {
   a.z = pack16x2<BF16>(fa[4], fa[5]); a.w = pack16x2<BF16>(fa[6], fa[7]);
 }
 
-// ACT: the rows are silu(row_src) * row_mul (row_mul(r) gives the second operand's row).
-template <bool BF16, int WB, int PPL, bool ACT, typename RowSrc, typename RowMul>
-__device__ __forceinline__ void fx_quantize_rows(int first, int nrows, int step, RowSrc row_src, RowMul row_mul, int K, uint32_t dst0,
-                                                 uint32_t pitch, float* scales, int lane) {
-  constexpr int RB = 8 / PPL;
-  const int pieces = K >> 3;
-  for (int r0 = first; r0 < nrows; r0 += step * RB) {
-    uint4 v[RB][PPL];
-#pragma unroll
-    for (int rb = 0; rb < RB; ++rb) {
-      const int r = r0 + rb * step;
-#pragma unroll
-      for (int i = 0; i < PPL; ++i) {
-        const int pc = i * 32 + lane;
-        v[rb][i] = make_uint4(0, 0, 0, 0);
-        if (r < nrows && pc < pieces) {
-          v[rb][i] = ld_global_cg_v4(row_src(r) + pc * 8);
-          if constexpr (ACT) silu_mul8<BF16>(v[rb][i], ld_global_cg_v4(row_mul(r) + pc * 8));
-        }
-      }
-    }
-#pragma unroll
-    for (int rb = 0; rb < RB; ++rb) {
-      const int r = r0 + rb * step;
-      if (r >= nrows) break;  // warp-uniform
-      float m = 0.f;
-#pragma unroll
-      for (int i = 0; i < PPL; ++i) {
-        float f[8];
-        unpack8<BF16>(v[rb][i], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      const bool fin = m > 0.f && m < 3.0e38f;  // (an infinite or NaN row has no fixed-point form: it yields zeros)
-      const float inv = fin ? 32512.f / m : 0.f;
-      if (lane == 0) scales[r] = fin ? m / 32512.f : 0.f;
-      const uint32_t row_addr = dst0 + (uint32_t)r * pitch;
-#pragma unroll
-      for (int i = 0; i < PPL; ++i) {
-        const int pc = i * 32 + lane;
-        if (pc < pieces) {
-          float f[8];
-          int q[8];
-          unpack8<BF16>(v[rb][i], f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) q[e] = fx_round(f[e], inv);
-          fx_store8<WB>(row_addr, pc * 8, q);
-        }
-      }
-    }
+// The fixed-point conversion works in place on rows that lie as plain 16-bit values at the start of their fixed-point
+// rows in shared memory: a 32-index block of int8 rows (64-index block of int4 rows) covers the same bytes before and
+// after, and the 4 (8) lanes that hold its 16-byte pieces all read before any of them writes.  The loops are rolled on
+// purpose: this code runs once per launch, so that its size (instruction fetches) counts for more than its ILP.
+// A warp's pieces of a row are base + lane for base = base0, base0 + step, ... (multiples of 32).
+template <bool BF16>
+__device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 r = __hmax2(__habs2(*reinterpret_cast<const __nv_bfloat162*>(&w)), *reinterpret_cast<const __nv_bfloat162*>(&m));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  } else {
+    const __half2 r = __hmax2(__habs2(*reinterpret_cast<const __half2*>(&w)), *reinterpret_cast<const __half2*>(&m));
+    return *reinterpret_cast<const uint32_t*>(&r);
   }
 }
 
-template <bool BF16, int WB, bool ACT, typename RowSrc, typename RowMul>
-__device__ __forceinline__ void fx_quantize(int first, int nrows, int step, RowSrc row_src, RowMul row_mul, int K, uint32_t dst0,
-                                            uint32_t pitch, float* scales, int lane) {
-  const int ppl = ((K >> 3) + 31) >> 5;
-  if (ppl <= 1) fx_quantize_rows<BF16, WB, 1, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
-  else if (ppl <= 2) fx_quantize_rows<BF16, WB, 2, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
-  else if (ppl <= 4) fx_quantize_rows<BF16, WB, 4, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
-  else fx_quantize_rows<BF16, WB, 8, ACT>(first, nrows, step, row_src, row_mul, K, dst0, pitch, scales, lane);
+// Largest magnitude over the warp's pieces of a row (NaNs do not count), the same value in every lane.
+template <bool BF16>
+__device__ __forceinline__ float fx_row_absmax(uint32_t row_addr, int base0, int step, int pieces, int lane) {
+  uint32_t m2 = 0;
+#pragma unroll 1
+  for (int base = base0; base < pieces; base += step) {
+    const int pc = base + lane;
+    if (pc < pieces) {
+      uint32_t a, b, c, d;
+      lds128(row_addr + (uint32_t)pc * 16u, a, b, c, d);
+      m2 = absmax2<BF16>(absmax2<BF16>(m2, a), b);
+      m2 = absmax2<BF16>(absmax2<BF16>(m2, c), d);
+    }
+  }
+  const float2 t = unpack16x2<BF16>(m2);
+  float m = fmaxf(t.x, t.y);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  return m;
+}
+
+// Scale of a row with largest magnitude m, and its inverse (an all-zero, infinite or NaN row reads as zeros).
+__device__ __forceinline__ float fx_scale(float m, float& inv) {
+  const bool fin = m > 0.f && m < 3.0e38f;
+  inv = fin ? __fdividef(32512.f, m) : 0.f;
+  return fin ? m * (1.f / 32512.f) : 0.f;
+}
+
+template <bool BF16, int WB>
+__device__ __forceinline__ void fx_row_convert(uint32_t row_addr, int base0, int step, int pieces, float inv, int lane) {
+#pragma unroll 1
+  for (int base = base0; base < pieces; base += step) {  // warp-uniform bounds
+    const int pc = base + lane;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (pc < pieces) lds128(row_addr + (uint32_t)pc * 16u, v.x, v.y, v.z, v.w);
+    __syncwarp();
+    if (pc < pieces) {
+      float f[8];
+      int q[8];
+      unpack8<BF16>(v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[e] = fx_round(f[e], inv);
+      fx_store8<WB>(row_addr, pc * 8, q);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------- chunk consumers
@@ -383,14 +381,14 @@ struct ItemAcc {
     for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        tot[n][e] = fmaf(e < 2 ? s_row : s_row8, (float)(hi[n][e] * 256 + lo[n][e]), tot[n][e]);
+        tot[n][e] = fmaf(e < 2 ? s_row : s_row8, fmaf((float)hi[n][e], 256.f, (float)lo[n][e]), tot[n][e]);
         hi[n][e] = lo[n][e] = 0;
       }
   }
   // value of accumulator element (n, e) before the per-channel and activation scales
   __device__ __forceinline__ float value(int n, int e, bool grouped) const {
     if constexpr (WB == 16) return acc[0][n][e] + acc[1][n][e] + acc[2][n][e] + acc[3][n][e];
-    else return grouped ? tot[n][e] : (float)(hi[n][e] * 256 + lo[n][e]);  // < 2^31: one chunk of at most 256 indices per accumulator
+    else return grouped ? tot[n][e] : fmaf((float)hi[n][e], 256.f, (float)lo[n][e]);
   }
 };
 
@@ -405,7 +403,7 @@ __device__ __forceinline__ uint32_t fastdiv(uint32_t t, uint32_t d, uint32_t mag
 #define BLR_CK(slot) do { } while (0)
 #endif
 
-template <bool BF16, int NT, bool GS, int WB>
+template <bool BF16, int NT, bool GS, int WB, bool ACT>
 __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(const __grid_constant__ SplitParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -415,7 +413,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   constexpr bool FX = WB != 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, nb = p.b, bo = p.bo, nch = p.nch0, R = p.R;
-  const int nbx = nch * abox, SL = nch < kW ? nch : kW;
+  const int nbx = nch * abox;
   const int r0 = blockIdx.x * kSplitRanks;
   const SplitProblem& q = p.pr[blockIdx.y];
   const uint32_t xbox = (uint32_t)N * 128u, xpitch = FX ? fx_pitch(p.P, WB) : 0u;
@@ -442,13 +440,16 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   if (tid == 0) {
     mbar_arrive_expect_tx(bar, (uint32_t)nch * nb * 1024u);
     constexpr int kstep = wbits == 16 ? 64 : 128;
+#pragma unroll 1
     for (int c = 0; c < nch; ++c) tma_load_3d(smem_base + L.w + (uint32_t)c * nb * 1024u, &q.tmV, c * kstep, r0, 0, bar);
   }
   {
     const uint16_t* S = reinterpret_cast<const uint16_t*>(q.S);
     const bool s_vec = S != nullptr && p.s_r == 1 && ((p.s_i | p.s_j) & 7) == 0 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
     const uint32_t pitch = (uint32_t)nb * 16u + 16u;
+#pragma unroll 1
     for (int i = warp; i < bo; i += kW)
+#pragma unroll 1
       for (int j = lane; j < nb; j += 32) {
         uint16_t* d = reinterpret_cast<uint16_t*>(smem + L.s + i * pitch + j * 16);
         if (S == nullptr) {
@@ -479,21 +480,61 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   {
     const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
     const uint16_t* xm = reinterpret_cast<const uint16_t*>(p.x_mul);
-    const bool act = p.act == kSplitActSiluMul;
+    constexpr bool act = ACT;
     const int nrows = nb * N;
     if constexpr (FX) {
+      // raw rows into the fixed-point rows (asynchronously, all of the warp's rows in flight), then in place: the
+      // input transform where asked for, the row maximum, the conversion
       const long long ldx = p.ldx;
-      const int P = p.P;
+      const int P = p.P, pieces = P >> 3;
       const uint32_t mN = p.magic_N;
       auto row_off = [&](int r) {
         const int j = (int)fastdiv((uint32_t)r, (uint32_t)N, mN), n = r - j * N;
         return (long long)n * ldx + (long long)j * P;
       };
-      auto row_src = [&](int r) { return x + row_off(r); };
-      auto row_mul = [&](int r) { return xm + row_off(r); };
-      if (act) fx_quantize<BF16, WB, true>(warp, nrows, kW, row_src, row_mul, P, smem_base + L.xs, xpitch, sx, lane);
-      else fx_quantize<BF16, WB, false>(warp, nrows, kW, row_src, row_mul, P, smem_base + L.xs, xpitch, sx, lane);
-    } else if (act) {
+#pragma unroll 1
+      for (int r = warp; r < nrows; r += kW) {
+        const uint16_t* src = x + row_off(r);
+        const uint32_t row_addr = smem_base + L.xs + (uint32_t)r * xpitch;
+#pragma unroll 1
+        for (int pc = lane; pc < pieces; pc += 32) cp_async16(row_addr + (uint32_t)pc * 16u, src + pc * 8);
+      }
+      if constexpr (ACT) {
+        // the second operand straight from global memory, one piece ahead of its use
+        int r = warp, base = 0;
+        uint4 nxt = make_uint4(0, 0, 0, 0);
+        if (r < nrows && lane < pieces) nxt = ld_global_cg_v4(xm + row_off(r) + lane * 8);
+        cp_async_wait_all();
+        __syncwarp();
+#pragma unroll 1
+        while (r < nrows) {
+          const uint4 cur = nxt;
+          int r2 = r, b2 = base + 32;
+          if (b2 >= pieces) { b2 = 0; r2 += kW; }
+          if (r2 < nrows && b2 + lane < pieces) nxt = ld_global_cg_v4(xm + row_off(r2) + (b2 + lane) * 8);
+          if (base + lane < pieces) {
+            const uint32_t a = smem_base + L.xs + (uint32_t)r * xpitch + (uint32_t)(base + lane) * 16u;
+            uint4 v;
+            lds128(a, v.x, v.y, v.z, v.w);
+            silu_mul8<BF16>(v, cur);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+          }
+          r = r2;
+          base = b2;
+        }
+      } else {
+        cp_async_wait_all();
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int r = warp; r < nrows; r += kW) {
+        const uint32_t row_addr = smem_base + L.xs + (uint32_t)r * xpitch;
+        float inv;
+        const float sc = fx_scale(fx_row_absmax<BF16>(row_addr, 0, 32, pieces, lane), inv);
+        if (lane == 0) sx[r] = sc;
+        fx_row_convert<BF16, WB>(row_addr, 0, 32, pieces, inv, lane);
+      }
+    } else if constexpr (act) {
       // silu(x) * x_mul through registers into the same [in-block][64-wide box][token][128 B] layout, zero past P
       const int cpr = nbx * 8;
       for (int rowi = warp; rowi < nrows; rowi += kW) {
@@ -534,89 +575,106 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
     return;
   }
   BLR_CK(8);
-  // ---- y_j on the slice.  Work item = (in-block j, chunk c), numbered t = j*nch + c; warp w takes t = w, w + 16, ...
-  // Consecutive items of a warp that belong to one j (only with more than 16 chunks per row) share an accumulator,
-  // which goes to the partial-sum slot (j, first chunk % 16).  Rows 8..15 of the MMA are the next block's rows (or
-  // slack) against the wrong activations: never read back.
+  // ---- y_j on the slice.  A warp owns an in-block (warps w, w + 16, ... beyond 16 in-blocks) and runs down its
+  // chunks with one accumulator, then scales and stores y[j][n][r].  With fewer than 9 in-blocks `share` warps split
+  // the chunks of one in-block and their sums meet in shared memory, added in a fixed order.  Rows 8..15 of the MMA are
+  // the next block's rows (or slack) against the wrong activations: never read back.
   {
     const int g = lane >> 2, tq = lane & 3;
     const int ngroups = GS ? p.P / kScaleGroup : 0;
     constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;  // fixed-point bytes of one chunk's indices in a token row
-    const int nitems = nb * nch;
+    const int share = split_share(nb);
+    const int jw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - jw * share;
     ItemAcc<NT, WB> A;
-    int jcur = -1, cfirst = 0;
-    auto flush = [&]() {
-      float* slot = ypart + ((jcur * SL + (cfirst & (kW - 1))) * 8 + g) * NP;
-#pragma unroll
-      for (int n = 0; n < NT; ++n)
-        *reinterpret_cast<float2*>(slot + n * 8 + tq * 2) = make_float2(A.value(n, 0, GS), A.value(n, 1, GS));
-    };
 #pragma unroll 1
-    for (int t = warp; t < nitems; t += kW) {
-      const int j = (int)fastdiv((uint32_t)t, (uint32_t)nch, p.magic_nch0), c = t - j * nch;
-      if (j != jcur) {
-        if (jcur >= 0) flush();
-        A.clear();
-        jcur = j;
-        cfirst = c;
-      }
-      const uint32_t sW = smem_base + L.w + (uint32_t)(c * nb + j) * 1024u;
-      if constexpr (WB == 16) {
-        sp_k16<BF16, NT>(sW, smem_base + L.xs + (uint32_t)(j * nbx + c) * xbox, A.acc, lane);
-      } else {
-        const uint32_t sA = smem_base + L.xs + (uint32_t)(j * N) * xpitch + (uint32_t)c * kChunkAct;
-        float gsc = 0.f, gsc2 = 0.f;
-        if constexpr (GS) {
-          const __half* srow = q.v_scale + ((long long)j * R + r0 + g) * ngroups;
-          const int gi = c * (WB == 8 ? 1 : 2);
-          gsc = __half2float(__ldg(srow + gi));
-          if (WB == 4 && gi + 1 < ngroups) gsc2 = __half2float(__ldg(srow + gi + 1));
-        }
-        if constexpr (WB == 8) {
-          iq_k8<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
-          if constexpr (GS) A.fold(gsc, 0.f);
-        } else if constexpr (!GS) {
-          iq_k4<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
+    for (int j = jw; j < nb; j += kW) {
+      A.clear();
+#pragma unroll 1
+      for (int c = ws; c < nch; c += share) {
+        const uint32_t sW = smem_base + L.w + (uint32_t)(c * nb + j) * 1024u;
+        if constexpr (WB == 16) {
+          sp_k16<BF16, NT>(sW, smem_base + L.xs + (uint32_t)(j * nbx + c) * xbox, A.acc, lane);
         } else {
-          // two scale groups per chunk: the first two windows, then the last two
-          iq_k4_half<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane, 0);
-          A.fold(gsc, 0.f);
-          iq_k4_half<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane, 2);
-          A.fold(gsc2, 0.f);
+          const uint32_t sA = smem_base + L.xs + (uint32_t)(j * N) * xpitch + (uint32_t)c * kChunkAct;
+          float gsc = 0.f, gsc2 = 0.f;
+          if constexpr (GS) {
+            const __half* srow = q.v_scale + ((long long)j * R + r0 + g) * ngroups;
+            const int gi = c * (WB == 8 ? 1 : 2);
+            gsc = __half2float(__ldg(srow + gi));
+            if (WB == 4 && gi + 1 < ngroups) gsc2 = __half2float(__ldg(srow + gi + 1));
+          }
+          if constexpr (WB == 8) {
+            iq_k8<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
+            if constexpr (GS) A.fold(gsc, 0.f);
+          } else if constexpr (!GS) {
+            iq_k4<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
+          } else {
+            // two scale groups per chunk: the first two windows, then the last two
+            iq_k4_half<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane, 0);
+            A.fold(gsc, 0.f);
+            iq_k4_half<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane, 2);
+            A.fold(gsc2, 0.f);
+          }
         }
+      }
+      if (share == 1) {
+        const float vsc = vs[j * 8 + g];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int tok = n * 8 + tq * 2 + e;
+            if (tok < N) {
+              float y = A.value(n, e, GS) * vsc;
+              if constexpr (FX) y *= sx[j * N + tok];
+              if (p.round_y) y = round_clamp_i8(y);
+              ybuf[(j * N + tok) * 8 + g] = y;
+            }
+          }
+      } else {
+        float* slot = ypart + ((j * share + ws) * 8 + g) * NP;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+          *reinterpret_cast<float2*>(slot + n * 8 + tq * 2) = make_float2(A.value(n, 0, GS), A.value(n, 1, GS));
       }
     }
-    if (jcur >= 0) flush();
+    BLR_CK(9);
+    __syncthreads();
+    BLR_CK(10);
+    BLR_TL(5);
+    if (share > 1) {
+      // y[j][n][r] = scales * sum of the sharing warps' slots (fixed order)
+#pragma unroll 1
+      for (int e = tid; e < nb * N * 8; e += kSplitFrontThreads) {
+        const int gg = e & 7, t = e >> 3, j = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - j * N;
+        const float* yp = ypart + (j * share * 8 + gg) * NP + n;
+        float y = yp[0];
+#pragma unroll 1
+        for (int cm = 1; cm < share; ++cm) y += yp[cm * 8 * NP];
+        y *= vs[j * 8 + gg];
+        if constexpr (FX) y *= sx[t];
+        if (p.round_y) y = round_clamp_i8(y);
+        ybuf[t * 8 + gg] = y;
+      }
+      __syncthreads();
+    }
   }
-  BLR_CK(9);
-  __syncthreads();
-  BLR_CK(10);
-  BLR_TL(5);
-  // ---- y[j][n][r] = scales * sum of the chunk slots (fixed order)
-  for (int e = tid; e < nb * N * 8; e += kSplitFrontThreads) {
-    const int gg = e & 7, t = e >> 3, j = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - j * N;
-    const float* yp = ypart + (j * SL * 8 + gg) * NP + n;
-    float y = yp[0];
-    for (int cm = 1; cm < SL; ++cm) y += yp[cm * 8 * NP];
-    y *= vs[j * 8 + gg];
-    if constexpr (FX) y *= sx[t];
-    if (p.round_y) y = round_clamp_i8(y);
-    ybuf[t * 8 + gg] = y;
-  }
-  __syncthreads();
   // ---- z[i][n][r] = sum_j S[i][j][r] y[j][n][r]: four partial sums per point (terms j = q mod 4), added in a fixed order
   {
     const uint32_t pitch = (uint32_t)nb * 16u + 16u;
+#pragma unroll 1
     for (int e = tid; e < bo * N * 8; e += kSplitFrontThreads) {
       const int gg = e & 7, t = e >> 3, i = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - i * N;
       const uint8_t* srow = smem + L.s + i * pitch + gg * 2;
       const float* yp = ybuf + n * 8 + gg;
       float a4[4] = {0.f, 0.f, 0.f, 0.f};
       int j = 0;
+#pragma unroll 1
       for (; j + 4 <= nb; j += 4) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) a4[q] = fmaf(load16<BF16>(srow + (j + q) * 16, 0), yp[(j + q) * N * 8], a4[q]);
       }
+#pragma unroll 1
       for (; j < nb; ++j) a4[0] = fmaf(load16<BF16>(srow + j * 16, 0), yp[j * N * 8], a4[0]);
       float a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
       if (p.round_z) a = round_clamp_i8(a);
@@ -638,7 +696,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   constexpr bool FX = WB != 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = p.N, nch = p.nch1, R = p.R, Q = p.Q;
-  const int nbz = nch * abox, SL = nch < kW ? nch : kW;
+  const int nbz = nch * abox;
   const int nseg = (nch + kSplitStageChunks - 1) / kSplitStageChunks;
   const int NST = p.nstages;
   const int blk = blockIdx.x / p.cpb, part = blockIdx.x - blk * p.cpb;
@@ -677,7 +735,9 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     constexpr int kstep = wbits == 16 ? 64 : 128;
     RingPos rp;
     bool ok = true;
+#pragma unroll 1
     for (int g = g_lo; g < g_hi && ok; ++g)
+#pragma unroll 1
       for (int seg = 0; seg < nseg; ++seg) {
         if (!rp.first_pass) {
           int w_ok = 1;
@@ -698,6 +758,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   const int ctid = tid;
   constexpr int kCT = kW * 32;
   const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll 1
   for (int e = ctid; e < ng * 16; e += kCT) {
     const int qq = g_lo * 16 + e;
     float v = (!GS && q.u_scale != nullptr && qq < Q) ? __half2float(__ldg(q.u_scale + (long long)blk * Q + qq)) : 1.f;
@@ -719,46 +780,28 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
       // Every token row is shared out over wpr = 16 / N warps (at least one): each thread takes its 16-byte pieces,
       // the warps' maxima meet in shared memory, then every thread converts its own pieces.
       const int wpr = N >= kW ? 1 : kW / N, n = warp / wpr, wl = warp - n * wpr;
-      const int pieces = R >> 3;
-      float* pm = sz + 16;  // per-warp maxima (16 floats after the 16 row scales)
-      uint4 v[8];
-      float m = 0.f;
+      const int pieces = R >> 3, base0 = wl * 32, step = wpr * 32;
+      float* pm = sz + 16;  // per-row maxima (16 floats after the 16 row scales)
       const bool have_row = n < N;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int pc = (i * wpr + wl) * 32 + lane;
-        v[i] = make_uint4(0, 0, 0, 0);
-        if (have_row && pc < pieces) {
-          v[i] = ld_global_cg_v4(z + (long long)n * R + pc * 8);
-          float f[8];
-          unpack8<BF16>(v[i], f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
-        }
+      const uint32_t row_addr = smem_base + L.zs + (uint32_t)n * zpitch;
+      if (have_row) {
+#pragma unroll 1
+        for (int base = base0; base < pieces; base += step)
+          if (base + lane < pieces) cp_async16(row_addr + (uint32_t)(base + lane) * 16u, z + (long long)n * R + (base + lane) * 8);
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      // non-negative floats order like their bit patterns (a NaN would come out as the largest: the row then reads as zeros)
-      if (lane == 0 && have_row) atomicMax(reinterpret_cast<int*>(pm) + n, __float_as_int(m));
+      cp_async_wait_all();
+      __syncwarp();
+      if (have_row) {
+        const float m = fx_row_absmax<BF16>(row_addr, base0, step, pieces, lane);
+        // non-negative floats order like their bit patterns
+        if (lane == 0) atomicMax(reinterpret_cast<int*>(pm) + n, __float_as_int(m));
+      }
       named_bar(1, kCT);
       if (have_row) {
-        const float rm = pm[n];
-        const bool fin = rm > 0.f && rm < 3.0e38f;
-        const float inv = fin ? 32512.f / rm : 0.f;
-        if (wl == 0 && lane == 0) sz[n] = fin ? rm / 32512.f : 0.f;
-        const uint32_t row_addr = smem_base + L.zs + (uint32_t)n * zpitch;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int pc = (i * wpr + wl) * 32 + lane;
-          if (pc < pieces) {
-            float f[8];
-            int q[8];
-            unpack8<BF16>(v[i], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) q[e] = fx_round(f[e], inv);
-            fx_store8<WB>(row_addr, pc * 8, q);
-          }
-        }
+        float inv;
+        const float sc = fx_scale(pm[n], inv);
+        if (wl == 0 && lane == 0) sz[n] = sc;
+        fx_row_convert<BF16, WB>(row_addr, base0, step, pieces, inv, lane);
       }
     } else {
       // [64-wide box][token][128 B], zero past R.  A warp per run of 32 pieces of a token row.
@@ -778,19 +821,20 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   named_bar(1, kCT);
   BLR_CK(7);
   BLR_TL(3);
-  // ---- products.  Work item = (group gl, chunk c), numbered t = gl*nch + c; warp w takes t = w, w + 16, ...; the
-  // items of a warp that belong to one group (more than 16 chunks per row) share an accumulator, which goes to the
-  // partial-sum slot (gl, first chunk % 16).  Stage of an item: gl*nseg + c / 8.  When the CTA's whole share is
-  // resident a warp only looks at the stages it reads; with a shorter ring every warp walks every stage in order and
-  // frees it, used or not.
+  // ---- products.  A warp owns a 16-row group (groups w, w + 16, ... when the CTA has more than 16) and runs down
+  // its chunks with one accumulator; a CTA with fewer than 9 groups lets `share` warps split the chunks of a group.
+  // Every warp leaves its sum in its own slot; the slots of a group are added in a fixed order below.  Stage of
+  // chunk c of group gl: gl*nseg + c / 8.  When the CTA's whole share is resident a warp only looks at the stages it
+  // reads; with a shorter ring every warp walks every stage in order and frees it, used or not.
   bool ok = true;
   const int ngroups = GS ? R / kScaleGroup : 0;
   constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;
+  const int share = split_share(p.gpc);
   {
+    const int gw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - gw * share;
     ItemAcc<NT, WB> A;
-    int gcur = -1, cfirst = 0;
-    auto flush = [&]() {
-      float* slot = partial + (size_t)(gcur * SL + (cfirst & (kW - 1))) * 16 * NP;
+    auto flush = [&](int gl) {
+      float* slot = partial + (size_t)(gl * share + ws) * 16 * NP;
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -798,13 +842,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
           *reinterpret_cast<float2*>(slot + (gq + 8 * h) * NP + n * 8 + tq * 2) =
               make_float2(A.value(n, 2 * h, GS), A.value(n, 2 * h + 1, GS));
     };
-    auto item = [&](int gl, int c, uint32_t s) {
-      if (gl != gcur) {
-        if (gcur >= 0) flush();
-        A.clear();
-        gcur = gl;
-        cfirst = c;
-      }
+    auto chunk = [&](int gl, int c, uint32_t s) {
       const int g = g_lo + gl;
       const uint32_t sW = smem_base + L.ring + s * kSplitStageBytes + (c & (kSplitStageChunks - 1)) * kSplitChunkBytes;
       if constexpr (WB == 16) {
@@ -836,33 +874,44 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
       }
     };
     if (resident) {
-      const int nitems = ng * nch;
 #pragma unroll 1
-      for (int t = warp; t < nitems && ok; t += kW) {
-        const int gl = (int)fastdiv((uint32_t)t, (uint32_t)nch, p.magic_nch1), c = t - gl * nch;
-        const uint32_t s = (uint32_t)(gl * nseg + (c >> 3));
-        if (!mbar_wait(full0 + 8 * s, 0, abort_flag)) { ok = false; break; }
-        item(gl, c, s);
+      for (int gl = gw; gl < ng && ok; gl += kW) {
+        A.clear();
+        int s_seen = -1;
+#pragma unroll 1
+        for (int c = ws; c < nch; c += share) {
+          const int s = gl * nseg + (c >> 3);
+          if (s != s_seen) {
+            if (!mbar_wait(full0 + 8 * s, 0, abort_flag)) { ok = false; break; }
+            s_seen = s;
+          }
+          chunk(gl, c, (uint32_t)s);
+        }
+        flush(gl);
       }
     } else {
       RingPos rp;
 #pragma unroll 1
       for (int gl = 0; gl < ng && ok; ++gl) {
-        const int c0 = (warp - gl * nch) & (kW - 1);  // this warp's first chunk of the group (none if >= nch)
+        const bool mine = share == 1 ? (gl & (kW - 1)) == warp : gl == gw;
+        int c = ws;  // this warp's next chunk of the group
+        if (mine) A.clear();
 #pragma unroll 1
         for (int seg = 0; seg < nseg; ++seg) {
           const uint32_t s = rp.s;
-          // chunk of this warp inside the stage: c = c0 + 16 m with seg*8 <= c < seg*8 + 8
-          const int ci = (c0 - seg * kSplitStageChunks) & (kW - 1), c = seg * kSplitStageChunks + ci;
           if (!mbar_wait(full0 + 8 * s, rp.use_parity, abort_flag)) { ok = false; break; }
-          if (ci < kSplitStageChunks && c < nch) item(gl, c, s);
+          if (mine) {
+            const int c_end = min(nch, (seg + 1) * kSplitStageChunks);
+#pragma unroll 1
+            for (; c < c_end; c += share) chunk(gl, c, s);
+          }
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
           rp.advance(NST);
         }
+        if (mine && ok) flush(gl);
       }
     }
-    if (gcur >= 0) flush();
   }
   BLR_CK(8);
   named_bar(1, kCT);
@@ -872,16 +921,18 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     if (ctid == 0) atomicExch(p.status, 1u);
     return;
   }
-  // ---- out[n][blk*Q + q] = scales * sum over the chunk slots of the row (fixed order), consecutive threads on consecutive rows
+  // ---- out[n][blk*Q + q] = scales * sum over the sharing warps' slots (fixed order), consecutive threads on consecutive rows
   {
-    const int rows = ng * 16;
-    for (int e = ctid; e < rows * N; e += kCT) {
-      const int n = e / rows, lr = e - n * rows, gl = lr >> 4, row = lr & 15;
-      const int qq = (g_lo + gl) * 16 + row;
-      if (qq >= Q) continue;
-      const float* sp = partial + (size_t)(gl * SL) * 16 * NP + row * NP + n;
-      float s = 0.f;
-      for (int cs = 0; cs < SL; ++cs) s += sp[cs * 16 * NP];
+    const int rows_full = p.gpc * 16, rows = ng * 16;
+#pragma unroll 1
+    for (int e = ctid; e < rows_full * N; e += kCT) {
+      const int n = (int)fastdiv((uint32_t)e, (uint32_t)rows_full, p.magic_rows), lr = e - n * rows_full;
+      const int gl = lr >> 4, row = lr & 15, qq = g_lo * 16 + lr;
+      if (lr >= rows || qq >= Q) continue;
+      const float* sp = partial + (size_t)(gl * share) * 16 * NP + row * NP + n;
+      float s = sp[0];
+#pragma unroll 1
+      for (int cs = 1; cs < share; ++cs) s += sp[cs * 16 * NP];
       s *= us[lr];
       if constexpr (FX) s *= sz[n];
       const long long col = (long long)blk * Q + qq;
@@ -903,16 +954,17 @@ static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
   const size_t fs = split_front_smem(p), bs = split_back_smem(p);
   BLR_REQUIRE((int)fs <= di.max_smem_optin && (int)bs <= di.max_smem_optin, BLR_ERR_UNSUPPORTED,
               "needs %zu / %zu bytes of shared memory, device offers %d", fs, bs, di.max_smem_optin);
-  auto front = blr_blast_front_kernel<BF16, NT, GS, WB>;
+  auto front = p.act == kSplitActSiluMul ? blr_blast_front_kernel<BF16, NT, GS, WB, true> : blr_blast_front_kernel<BF16, NT, GS, WB, false>;
   auto back = blr_blast_back_kernel<BF16, NT, GS, WB>;
   {
     int dev = 0;
     BLR_CUDA_OK(cudaGetDevice(&dev));
-    static bool configured[64] = {};  // per template instance
-    if (!configured[dev & 63]) {
+    static bool configured[2][64] = {};  // per template instance and front variant
+    bool& done = configured[p.act == kSplitActSiluMul][dev & 63];
+    if (!done) {
       BLR_CUDA_OK(cudaFuncSetAttribute(front, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
       BLR_CUDA_OK(cudaFuncSetAttribute(back, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
-      configured[dev & 63] = true;
+      done = true;
     }
   }
   cudaLaunchAttribute at[1];

@@ -201,8 +201,8 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   p.gpc = (gpb + cpb - 1) / cpb;
   p.cpb = (gpb + p.gpc - 1) / p.gpc;
   auto magic = [](int d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d); };
-  p.magic_N = magic((int)N); p.magic_nch0 = magic(p.nch0); p.magic_nch1 = magic(p.nch1);
-  if ((long long)b * p.nch0 >= 65536 || (long long)p.gpc * p.nch1 >= 65536) return 1;
+  p.magic_N = magic((int)N); p.magic_rows = magic(p.gpc * 16);
+  if ((long long)b * N >= 65536 || (long long)p.gpc * 16 * N >= 65536) return 1;
   p.nstages = 2;
   const int fs = (int)split_front_smem(p);
   if (fs > di.max_smem_optin) return 1;
