@@ -48,8 +48,9 @@ PASSES_PER_STEP = 25
 GROUPS = {"two_launch": ("blr_blast_front_kernel+blr_blast_back_kernel", 2), "cluster": ("blr_blast_cluster_kernel", 1)}
 
 
-def group_of(n: int) -> str:
-    return "two_launch" if n <= 4 else "cluster"
+def group_of(bits: int, n: int) -> str:
+    """Kernel group the library's dispatch picks for a point (packed int4 above 8 tokens goes to the cluster kernel)."""
+    return "cluster" if bits == 4 and n > 8 else "two_launch"
 
 
 def algorithmic_bytes(bits: int, n: int) -> float:
@@ -451,7 +452,7 @@ def run_ours(args):
     def launch_points(group=None):
         calls = 0
         for bits, n in POINTS:
-            if group is not None and group_of(n) != group:
+            if group is not None and group_of(bits, n) != group:
                 continue
             for q in reps[bits]:
                 bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
@@ -478,10 +479,10 @@ def run_ours(args):
         print(json.dumps({"ncu_case": args.ncu_case, "calls": 6}))
         return
 
-    groups = sorted({group_of(n) for _, n in POINTS})
+    groups = sorted({group_of(b, n) for b, n in POINTS})
     calls = {k: launch_points(k) for k in groups}
     torch.cuda.synchronize()
-    kbytes = {k: sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS if group_of(n) == k) for k in groups}
+    kbytes = {k: sum(algorithmic_bytes(b, n) * len(reps[b]) for b, n in POINTS if group_of(b, n) == k) for k in groups}
     bytes_per_pass = sum(kbytes.values())
     launches_per_pass = sum(calls[k] * GROUPS[k][1] for k in groups)
 

@@ -251,6 +251,47 @@ __device__ __forceinline__ void fx_row_convert(uint32_t row_addr, int base0, int
   }
 }
 
+// Short rows (at most 32 pieces: one per lane), four rows of the warp at a time so that their dependent chains
+// (load, maximum, shuffles, scale, conversion) overlap.  Rows rb .. rb + 3 with rb = 4 (warp + 16 it).
+template <bool BF16, int WB>
+__device__ __forceinline__ void fx_rows4(int nrows, int pieces, uint32_t rows0, uint32_t pitch, float* scales, int warp, int lane) {
+  const bool have = lane < pieces;
+#pragma unroll 1
+  for (int rb = warp * 4; rb < nrows; rb += kW * 4) {
+    uint4 v[4];
+    float m[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (have && rb + i < nrows) lds128(rows0 + (uint32_t)(rb + i) * pitch + (uint32_t)lane * 16u, v[i].x, v[i].y, v[i].z, v[i].w);
+      const uint32_t m2 = absmax2<BF16>(absmax2<BF16>(absmax2<BF16>(absmax2<BF16>(0u, v[i].x), v[i].y), v[i].z), v[i].w);
+      const float2 t = unpack16x2<BF16>(m2);
+      m[i] = fmaxf(t.x, t.y);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], __shfl_xor_sync(0xffffffffu, m[i], o));
+    __syncwarp();  // every lane has read its pieces: the stores below land on other lanes' pieces of the same block
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (rb + i < nrows) {  // warp-uniform
+        float inv;
+        const float sc = fx_scale(m[i], inv);
+        if (lane == 0) scales[rb + i] = sc;
+        if (have) {
+          float f[8];
+          int q[8];
+          unpack8<BF16>(v[i], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) q[e] = fx_round(f[e], inv);
+          fx_store8<WB>(rows0 + (uint32_t)(rb + i) * pitch, lane * 8, q);
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------- chunk consumers
 // One 128-byte K-chunk of a 16-row weight group (rows 0..15 of the box at sW).  The shared-memory loads of a batch of
 // 32-byte windows are issued before the first use, so that their latencies overlap.
@@ -484,7 +525,8 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
     const int nrows = nb * N;
     if constexpr (FX) {
       // raw rows into the fixed-point rows (asynchronously, all of the warp's rows in flight), then in place: the
-      // input transform where asked for, the row maximum, the conversion
+      // input transform where asked for, the row maximum, the conversion.  The warp's rows come in runs of rr:
+      // rows rb .. rb + rr - 1 with rb = rr (warp + 16 it); short rows (one piece per lane) go four at a time.
       const long long ldx = p.ldx;
       const int P = p.P, pieces = P >> 3;
       const uint32_t mN = p.magic_N;
@@ -492,16 +534,27 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
         const int j = (int)fastdiv((uint32_t)r, (uint32_t)N, mN), n = r - j * N;
         return (long long)n * ldx + (long long)j * P;
       };
+      const bool short_rows = pieces <= 32 && nrows > kW;  // (with at most one row per warp there is nothing to overlap)
+      const int rr = short_rows ? 4 : 1;
 #pragma unroll 1
-      for (int r = warp; r < nrows; r += kW) {
-        const uint16_t* src = x + row_off(r);
-        const uint32_t row_addr = smem_base + L.xs + (uint32_t)r * xpitch;
+      for (int rb = warp * rr; rb < nrows; rb += kW * rr)
 #pragma unroll 1
-        for (int pc = lane; pc < pieces; pc += 32) cp_async16(row_addr + (uint32_t)pc * 16u, src + pc * 8);
-      }
+        for (int r = rb; r < rb + rr && r < nrows; ++r) {
+          const uint16_t* src = x + row_off(r);
+          const uint32_t row_addr = smem_base + L.xs + (uint32_t)r * xpitch;
+#pragma unroll 1
+          for (int pc = lane; pc < pieces; pc += 32) cp_async16(row_addr + (uint32_t)pc * 16u, src + pc * 8);
+        }
       if constexpr (ACT) {
         // the second operand straight from global memory, one piece ahead of its use
-        int r = warp, base = 0;
+        int rb = warp * rr, r = rb, base = 0;
+        auto advance = [&](int& rb_, int& r_, int& base_) {
+          base_ += 32;
+          if (base_ >= pieces) {
+            base_ = 0;
+            if (++r_ >= rb_ + rr || r_ >= nrows) r_ = rb_ += kW * rr;
+          }
+        };
         uint4 nxt = make_uint4(0, 0, 0, 0);
         if (r < nrows && lane < pieces) nxt = ld_global_cg_v4(xm + row_off(r) + lane * 8);
         cp_async_wait_all();
@@ -509,8 +562,8 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
 #pragma unroll 1
         while (r < nrows) {
           const uint4 cur = nxt;
-          int r2 = r, b2 = base + 32;
-          if (b2 >= pieces) { b2 = 0; r2 += kW; }
+          int rb2 = rb, r2 = r, b2 = base;
+          advance(rb2, r2, b2);
           if (r2 < nrows && b2 + lane < pieces) nxt = ld_global_cg_v4(xm + row_off(r2) + (b2 + lane) * 8);
           if (base + lane < pieces) {
             const uint32_t a = smem_base + L.xs + (uint32_t)r * xpitch + (uint32_t)(base + lane) * 16u;
@@ -519,6 +572,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
             silu_mul8<BF16>(v, cur);
             asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
           }
+          rb = rb2;
           r = r2;
           base = b2;
         }
@@ -526,13 +580,17 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
         cp_async_wait_all();
       }
       __syncwarp();
+      if (short_rows) {
+        fx_rows4<BF16, WB>(nrows, pieces, smem_base + L.xs, xpitch, sx, warp, lane);
+      } else {
 #pragma unroll 1
-      for (int r = warp; r < nrows; r += kW) {
-        const uint32_t row_addr = smem_base + L.xs + (uint32_t)r * xpitch;
-        float inv;
-        const float sc = fx_scale(fx_row_absmax<BF16>(row_addr, 0, 32, pieces, lane), inv);
-        if (lane == 0) sx[r] = sc;
-        fx_row_convert<BF16, WB>(row_addr, 0, 32, pieces, inv, lane);
+        for (int r = warp; r < nrows; r += kW) {
+          const uint32_t row_addr = smem_base + L.xs + (uint32_t)r * xpitch;
+          float inv;
+          const float sc = fx_scale(fx_row_absmax<BF16>(row_addr, 0, 32, pieces, lane), inv);
+          if (lane == 0) sx[r] = sc;
+          fx_row_convert<BF16, WB>(row_addr, 0, 32, pieces, inv, lane);
+        }
       }
     } else if constexpr (act) {
       // silu(x) * x_mul through registers into the same [in-block][64-wide box][token][128 B] layout, zero past P
@@ -659,8 +717,9 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
       __syncthreads();
     }
   }
-  // ---- z[i][n][r] = sum_j S[i][j][r] y[j][n][r]: four partial sums per point (terms j = q mod 4), added in a fixed order
-  {
+  // ---- z[i][n][r] = sum_j S[i][j][r] y[j][n][r].  Few points (fewer than threads): a thread per point with four
+  // partial sums (terms j = q mod 4), added in a fixed order.
+  if (bo * N * 8 <= kSplitFrontThreads / 2) {
     const uint32_t pitch = (uint32_t)nb * 16u + 16u;
 #pragma unroll 1
     for (int e = tid; e < bo * N * 8; e += kSplitFrontThreads) {
@@ -679,6 +738,40 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
       float a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
       if (p.round_z) a = round_clamp_i8(a);
       store16<BF16>(q.z, (long long)t * R + r0 + gg, a);
+    }
+  }
+  else {  // more points: four ranks per thread, the terms in rising j
+    const uint32_t pitch = (uint32_t)nb * 16u + 16u;
+#pragma unroll 1
+    for (int e = tid; e < bo * N * 2; e += kSplitFrontThreads) {
+      const int g4 = (e & 1) * 4, t = e >> 1, i = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - i * N;
+      const uint32_t srow = smem_base + L.s + (uint32_t)i * pitch + (uint32_t)g4 * 2u;
+      const float* yp = ybuf + n * 8 + g4;
+      float a[4] = {0.f, 0.f, 0.f, 0.f};
+      auto term = [&](int j) {
+        uint32_t s01, s23;
+        asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(s01), "=r"(s23) : "r"(srow + (uint32_t)j * 16u));
+        const float4 y = *reinterpret_cast<const float4*>(yp + j * N * 8);
+        const float2 sa = unpack16x2<BF16>(s01), sb = unpack16x2<BF16>(s23);
+        a[0] = fmaf(sa.x, y.x, a[0]);
+        a[1] = fmaf(sa.y, y.y, a[1]);
+        a[2] = fmaf(sb.x, y.z, a[2]);
+        a[3] = fmaf(sb.y, y.w, a[3]);
+      };
+      int j = 0;
+#pragma unroll 1
+      for (; j + 4 <= nb; j += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) term(j + u);
+      }
+#pragma unroll 1
+      for (; j < nb; ++j) term(j);
+      if (p.round_z) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) a[c] = round_clamp_i8(a[c]);
+      }
+      uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(q.z) + (long long)t * R + r0 + g4);
+      asm volatile("st.global.v2.b32 [%0], {%1,%2};" ::"l"(dst), "r"(pack16x2<BF16>(a[0], a[1])), "r"(pack16x2<BF16>(a[2], a[3])) : "memory");
     }
   }
   BLR_CK(11);
@@ -921,24 +1014,45 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     if (ctid == 0) atomicExch(p.status, 1u);
     return;
   }
-  // ---- out[n][blk*Q + q] = scales * sum over the sharing warps' slots (fixed order), consecutive threads on consecutive rows
+  // ---- out[n][blk*Q + q] = scales * sum over the sharing warps' slots (fixed order); a thread takes two
+  // neighbouring rows of a token, consecutive threads consecutive pairs
   {
-    const int rows_full = p.gpc * 16, rows = ng * 16;
+    const int pairs_full = p.gpc * 8, rows = ng * 16;
+    uint16_t* outp = reinterpret_cast<uint16_t*>(q.out);
 #pragma unroll 1
-    for (int e = ctid; e < rows_full * N; e += kCT) {
-      const int n = (int)fastdiv((uint32_t)e, (uint32_t)rows_full, p.magic_rows), lr = e - n * rows_full;
+    for (int e = ctid; e < pairs_full * N; e += kCT) {
+      const int n = (int)fastdiv((uint32_t)e, (uint32_t)pairs_full, p.magic_rows), lr = (e - n * pairs_full) * 2;
       const int gl = lr >> 4, row = lr & 15, qq = g_lo * 16 + lr;
       if (lr >= rows || qq >= Q) continue;
       const float* sp = partial + (size_t)(gl * share) * 16 * NP + row * NP + n;
-      float s = sp[0];
+      float s0 = sp[0], s1 = sp[NP];
 #pragma unroll 1
-      for (int cs = 1; cs < share; ++cs) s += sp[cs * 16 * NP];
-      s *= us[lr];
-      if constexpr (FX) s *= sz[n];
-      const long long col = (long long)blk * Q + qq;
-      if (q.bias != nullptr) s += load16<BF16>(q.bias, col);
-      if (q.residual != nullptr) s += load16<BF16>(q.residual, (long long)n * q.ldr + col);
-      store16<BF16>(q.out, (long long)n * q.ldo + col, s);
+      for (int cs = 1; cs < share; ++cs) {
+        s0 += sp[cs * 16 * NP];
+        s1 += sp[cs * 16 * NP + NP];
+      }
+      s0 *= us[lr];
+      s1 *= us[lr + 1];
+      if constexpr (FX) {
+        s0 *= sz[n];
+        s1 *= sz[n];
+      }
+      const long long col = (long long)blk * Q + qq, o = (long long)n * q.ldo + col;
+      const bool two = qq + 1 < Q;
+      if (q.bias != nullptr) {
+        s0 += load16<BF16>(q.bias, col);
+        if (two) s1 += load16<BF16>(q.bias, col + 1);
+      }
+      if (q.residual != nullptr) {
+        s0 += load16<BF16>(q.residual, (long long)n * q.ldr + col);
+        if (two) s1 += load16<BF16>(q.residual, (long long)n * q.ldr + col + 1);
+      }
+      if (two && (o & 1) == 0) {
+        *reinterpret_cast<uint32_t*>(outp + o) = pack16x2<BF16>(s0, s1);
+      } else {
+        store16<BF16>(q.out, o, s0);
+        if (two) store16<BF16>(q.out, o + 1, s1);
+      }
     }
   }
   BLR_CK(10);

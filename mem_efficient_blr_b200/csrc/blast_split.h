@@ -62,7 +62,7 @@ struct alignas(64) SplitParams {
   int nch0, nch1;          // 128-byte chunks per row of V / of U
   int cpb, gpc;            // back kernel: CTAs per out-block, 16-row groups per CTA
   int nstages;             // back kernel: ring stages
-  unsigned magic_N, magic_rows;  // ceil(2^32 / d) for d = N, 16 gpc (0 for d = 1): division-free quotients
+  unsigned magic_N, magic_rows;  // ceil(2^32 / d) for d = N, 8 gpc (0 for d = 1): division-free quotients
 #ifdef BLR_TIMELINE
   unsigned long long* timeline;  // profiling builds: 16 stamps per CTA of this launch
 #endif

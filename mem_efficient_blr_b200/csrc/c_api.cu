@@ -172,10 +172,10 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
                              const SplitLayer* layers, int u_layout, int v_layout, int wb, int group, int64_t s_i, int64_t s_j,
                              int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* zbase, unsigned* status,
                              cudaStream_t stream) {
-  // Measured crossover against the cluster kernel on the Llama-7B shapes: the two-launch path wins up to 4 tokens
-  // with quantised factors (its fixed-point conversion of the activations grows with the token count) and up to
-  // 8 tokens with 16-bit factors.
-  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > (wb == 16 ? 8 : 4)) return 1;
+  // Measured crossover against the cluster kernel on the Llama-7B shapes: the two-launch path wins at every token
+  // count it takes with 16-bit and int8 factors, and up to 8 tokens with packed int4 factors (whose integer MMAs and
+  // fixed-point activations double per chunk).
+  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > (wb == 4 ? 8 : kStreamMaxTokens)) return 1;
   if (u_layout != BLR_W_KMAJOR || v_layout != BLR_W_KMAJOR || b > kSplitMaxBlocks || nprob < 1 || nprob > kSplitMaxProblems) return 1;
   const long long kbV = (long long)P * wb / 8, kbU = (long long)R * wb / 8;
   if (R % kSplitRanks != 0 || P % 8 != 0 || kbV % 16 != 0 || kbU % 16 != 0 || (wb == 4 && ((P | R) & 1))) return 1;
@@ -201,7 +201,7 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   p.gpc = (gpb + cpb - 1) / cpb;
   p.cpb = (gpb + p.gpc - 1) / p.gpc;
   auto magic = [](int d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d); };
-  p.magic_N = magic((int)N); p.magic_rows = magic(p.gpc * 16);
+  p.magic_N = magic((int)N); p.magic_rows = magic(p.gpc * 8);
   if ((long long)b * N >= 65536 || (long long)p.gpc * 16 * N >= 65536) return 1;
   p.nstages = 2;
   const int fs = (int)split_front_smem(p);
