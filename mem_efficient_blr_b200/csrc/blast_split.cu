@@ -95,7 +95,7 @@ __host__ __device__ static inline BackLayout back_layout(const SplitParams& p) {
   if (p.wbits == 16) o += nbz * p.N * 128 + 2048;         // [box][token][128 B] + slack
   else o += (uint32_t)p.N * fx_pitch(p.R, p.wbits);       // [token][fixed-point row]
   L.sz = o; o += 32 * 4;                                  // fixed-point scale per token, then per-warp maxima
-  L.part = o; o += (uint32_t)p.gpc * sl * 16 * np * 4;    // [group][sharing warp][16 rows][np tokens] fp32
+  L.part = o; o += (uint32_t)p.gpc * sl * 16 * np * 4;    // [group][sharing warp][np tokens][16 rows] fp32
   L.us = o; o += (uint32_t)p.gpc * 16 * 4;                // per-channel scales of the CTA's rows
   L.bars = o; o += (2 * (uint32_t)p.nstages + 2) * 8;
   L.total = o + 1024;
@@ -927,13 +927,14 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     const int gw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - gw * share;
     ItemAcc<NT, WB> A;
     auto flush = [&](int gl) {
+      // [token][16 rows]: the sums below read neighbouring rows of a token from neighbouring banks
       float* slot = partial + (size_t)(gl * share + ws) * 16 * NP;
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int n = 0; n < NT; ++n)
-          *reinterpret_cast<float2*>(slot + (gq + 8 * h) * NP + n * 8 + tq * 2) =
-              make_float2(A.value(n, 2 * h, GS), A.value(n, 2 * h + 1, GS));
+#pragma unroll
+          for (int e = 0; e < 2; ++e) slot[(n * 8 + tq * 2 + e) * 16 + gq + 8 * h] = A.value(n, 2 * h + e, GS);
     };
     auto chunk = [&](int gl, int c, uint32_t s) {
       const int g = g_lo + gl;
@@ -1024,12 +1025,13 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
       const int n = (int)fastdiv((uint32_t)e, (uint32_t)pairs_full, p.magic_rows), lr = (e - n * pairs_full) * 2;
       const int gl = lr >> 4, row = lr & 15, qq = g_lo * 16 + lr;
       if (lr >= rows || qq >= Q) continue;
-      const float* sp = partial + (size_t)(gl * share) * 16 * NP + row * NP + n;
-      float s0 = sp[0], s1 = sp[NP];
+      const float2* sp = reinterpret_cast<const float2*>(partial + (size_t)(gl * share) * 16 * NP + n * 16 + row);
+      float s0 = sp[0].x, s1 = sp[0].y;
 #pragma unroll 1
       for (int cs = 1; cs < share; ++cs) {
-        s0 += sp[cs * 16 * NP];
-        s1 += sp[cs * 16 * NP + NP];
+        const float2 v = sp[cs * 8 * NP];
+        s0 += v.x;
+        s1 += v.y;
       }
       s0 *= us[lr];
       s1 *= us[lr + 1];
