@@ -1,4 +1,6 @@
-"""ctypes binding of libblr_b200.so (the C ABI in include/blr_b200.h) plus workspace handling."""
+"""Loads libblr_b200.so (the C ABI in include/blr_b200.h): the ctypes binding, the thin PyTorch C++ extension
+_blr_torch.so over the same ABI (TORCH_LIBRARY ops `blr_b200_ext::*`, the route of the hot operators), and the
+workspace handling they share."""
 from __future__ import annotations
 
 import ctypes as C
@@ -9,6 +11,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libblr_b200.so")
+EXT_PATH = os.path.join(HERE, "_blr_torch.so")
 
 F16, BF16 = 0, 1
 KMAJOR, MMAJOR = 0, 1
@@ -72,7 +75,7 @@ SIGNATURES = {
 }
 
 _lib = None
-_lock = threading.Lock()
+_lock = threading.RLock()
 
 
 def load() -> C.CDLL:
@@ -86,12 +89,32 @@ def load() -> C.CDLL:
                 raise RuntimeError(
                     f"{LIB_PATH} is missing: build it with `python -m mem_efficient_blr_b200.build` "
                     "(needs nvcc); this package has no CPU or Triton fallback")
-            lib = C.CDLL(LIB_PATH)
+            lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)  # (the torch extension links against it by soname)
             for name, (res, args) in SIGNATURES.items():
                 fn = getattr(lib, name)
                 fn.restype, fn.argtypes = res, args
             _lib = lib
     return _lib
+
+
+_ext = None
+_ext_tried = False
+
+
+def ext():
+    """torch.ops.blr_b200_ext once _blr_torch.so is loaded, None where it has not been built (the operators then go
+    through ctypes: same kernels, more host time per call).  Setting BLR_B200_NO_TORCH_EXT=1 keeps it unloaded."""
+    global _ext, _ext_tried
+    if _ext_tried:
+        return _ext
+    with _lock:
+        if not _ext_tried:
+            if os.path.exists(EXT_PATH) and LIB_PATH.endswith("libblr_b200.so") and not os.environ.get("BLR_B200_NO_TORCH_EXT"):
+                load()
+                torch.ops.load_library(EXT_PATH)
+                _ext = torch.ops.blr_b200_ext
+            _ext_tried = True
+    return _ext
 
 
 def check(rc: int) -> None:
@@ -153,8 +176,27 @@ def _alloc_outside_graph_pools(nbytes: int, device: torch.device) -> torch.Tenso
     return t
 
 
+class _RawView:
+    """Device memory owned elsewhere (the torch extension's workspace registry), viewable by torch."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+_ext_views: dict = {}
+
+
 def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    e = ext()
+    if e is not None:
+        # one registry for both routes: the extension owns the buffers, this layer views them
+        ptr, cap = e.workspace(key[0], stream, nbytes)
+        v = _ext_views.get(key)
+        if v is None or v.data_ptr() != ptr or v.numel() != cap:
+            with torch.cuda.device(key[0]):
+                v = _ext_views[key] = torch.as_tensor(_RawView(ptr, cap), device=torch.device("cuda", key[0]))
+        return v
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         cap = max(nbytes, 1 << 20)
@@ -167,11 +209,20 @@ def workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
 
 
 _stagings: dict = {}
+_ext_staging_views: dict = {}
 
 
 def staging(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     """Device buffer that the host-buffer entry points copy x into and the result out of; one per (device, stream)."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    e = ext()
+    if e is not None:
+        ptr, cap = e.staging(key[0], stream, nbytes)
+        v = _ext_staging_views.get(key)
+        if v is None or v.data_ptr() != ptr or v.numel() != cap:
+            with torch.cuda.device(key[0]):
+                v = _ext_staging_views[key] = torch.as_tensor(_RawView(ptr, cap), device=torch.device("cuda", key[0]))
+        return v
     st = _stagings.get(key)
     if st is None or st.numel() < nbytes:
         if st is not None:
@@ -186,6 +237,10 @@ def workspace_status(device: torch.device) -> None:
     """Raises if a kernel that used this device's current-stream workspace reported a timed-out wait."""
     st = stream_ptr(device)
     key = (device.index if device.index is not None else torch.cuda.current_device(), st)
+    e = ext()
+    if e is not None:
+        check(e.workspace_status(key[0], st))  # (re-initialises the workspace after an error)
+        return
     ws = _workspaces.get(key)
     if ws is not None:
         rc = load().blr_workspace_status(ws.data_ptr(), st)

@@ -115,6 +115,10 @@ def blast_wq_host(x_host, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0
     if out is None:
         out = torch.empty((n, b * q), dtype=x_host.dtype, pin_memory=True)
     assert not out.is_cuda and out.stride(1) == 1 and tuple(out.shape) == (n, b * q) and out.dtype == x_host.dtype
+    e = L.ext()
+    if e is not None:
+        e.blast_wq_host(x_host, out, Uq, u_scale, Vq, v_scale, S, bits, group)
+        return out
     lib = L.load()
     st = L.stream_ptr(dev)
     ws = L.workspace(dev, st, lib.blr_workspace_bytes(n, b, r))
@@ -154,8 +158,13 @@ class BlastWqHostCall:
         self._sg_bytes = lib.blr_host_staging_bytes(16, b * p, b * q)
         self._dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._scratch = {}  # stream -> (workspace, staging)
+        self._ext = L.ext()
+        self._bits, self._group = bits, group
 
     def __call__(self, x_host, out):
+        if self._ext is not None:  # the C++ operator checks the shapes itself
+            self._ext.blast_wq_host(x_host, out, *self._keep, self._bits, self._group)
+            return out
         n = x_host.size(0)
         if not (n <= 16 and x_host.size(1) == self.in_features and out.size(0) == n and out.size(1) == self.out_features
                 and x_host.dtype == self.dtype and out.dtype == self.dtype and not x_host.is_cuda and not out.is_cuda

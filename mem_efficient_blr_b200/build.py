@@ -1,4 +1,5 @@
-"""Builds libblr_b200.so in-tree with nvcc for sm_100a (no JIT cache, no torch headers needed)."""
+"""Builds libblr_b200.so in-tree with nvcc for sm_100a (no JIT cache, no torch headers needed), and the thin PyTorch
+C++ extension _blr_torch.so over its C ABI (g++ against the torch headers, also in-tree)."""
 from __future__ import annotations
 
 import os
@@ -51,7 +52,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
         objs.append(obj)
-    link = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart"]
+    # the soname lets the torch extension's DT_NEEDED entry resolve to the copy the Python layer has already loaded
+    link = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart", "-Xlinker", "-soname=libblr_b200.so"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")
@@ -62,5 +64,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+EXT = os.path.join(HERE, "_blr_torch.so")
+
+
+def ext_needs_build() -> bool:
+    if not os.path.exists(EXT):
+        return True
+    t = os.path.getmtime(EXT)
+    deps = [os.path.join(CSRC, "torch_ext.cpp"), os.path.join(HERE, "..", "include", "blr_b200.h")]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build_torch_ext(force: bool = False, verbose: bool = False) -> str:
+    """Compiles csrc/torch_ext.cpp (TORCH_LIBRARY ops over the C ABI) against the installed torch and links it to
+    libblr_b200.so; the result is copied next to it.  Needs libblr_b200.so built first."""
+    if not force and not ext_needs_build():
+        return EXT
+    from torch.utils import cpp_extension as ce
+    bdir = os.path.join(HERE, "build", "torch_ext")
+    os.makedirs(bdir, exist_ok=True)
+    ce.load(name="_blr_torch", sources=[os.path.join(CSRC, "torch_ext.cpp")], extra_cflags=["-O2", "-std=c++17"],
+            extra_include_paths=[os.path.join(HERE, "..", "include")], extra_ldflags=[f"-L{HERE}", "-lblr_b200"],
+            build_directory=bdir, with_cuda=True, is_python_module=False, verbose=verbose)
+    shutil.copyfile(os.path.join(bdir, "_blr_torch.so"), EXT)
+    return EXT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_torch_ext(force="--force" in sys.argv, verbose="-v" in sys.argv))

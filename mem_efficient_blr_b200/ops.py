@@ -1,10 +1,11 @@
 """Torch-facing operators: tensors in, tensors out, arithmetic in libblr_b200.so.
 
-Every operator exists twice.  ``<name>_op`` is registered with ``torch.library.custom_op`` (with a fake
-kernel), so the reference's callers that wrap a model in ``torch.compile(fullgraph=True,
-mode='reduce-overhead')`` (models/llama7b.py:65) trace through it.  ``<name>`` is what the kernel modules
-call: under a compiler trace it is the registered operator, in eager mode it calls the same implementation
-directly, which saves the dispatcher's ~20 us per call - more than the kernel itself takes on one token.
+The hot operators (BLAST, quantised BLAST, Monarch, low-rank, dense on 16-bit tensors) are TORCH_LIBRARY ops of the
+thin C++ extension (csrc/torch_ext.cpp, ``torch.ops.blr_b200_ext.*``, CUDA + Meta kernels): an eager call costs a
+dispatcher hop, and the reference's callers that wrap a model in ``torch.compile(fullgraph=True,
+mode='reduce-overhead')`` (models/llama7b.py:65) trace through them.  Where the extension has not been built the
+same operators run through ctypes: ``<name>_op`` is then a ``torch.library.custom_op`` with a fake kernel for
+tracing, and in eager mode ``<name>`` calls the implementation directly.
 Launches go to the current stream, outputs come from torch's allocator, and nothing synchronises the host.
 """
 from __future__ import annotations
@@ -94,6 +95,9 @@ def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor,
 
 
 def blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
+    e = L.ext()
+    if e is not None:
+        return e.blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
     if _eager():
         return _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
     return blast_op(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
@@ -128,6 +132,9 @@ def blast_wq_op(x: torch.Tensor, Uq: torch.Tensor, u_scale: torch.Tensor, Vq: to
 
 
 def blast_wq(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R):
+    e = L.ext()
+    if e is not None:
+        return e.blast_wq(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R)
     if _eager():
         return _blast_wq_impl(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R)
     return blast_wq_op(x, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R)
@@ -161,6 +168,9 @@ def monarch_op(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_layout: i
 
 
 def monarch(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order):
+    e = L.ext()
+    if e is not None:
+        return e.monarch(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order)
     if _eager():
         return _monarch_impl(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order)
     return monarch_op(x, w1, w2, w1_layout, w1_cols, w2_layout, b, P, rank, Qs, out_order)
@@ -194,6 +204,9 @@ def low_rank_op(x: torch.Tensor, V: torch.Tensor, U: torch.Tensor, v_layout: int
 
 
 def low_rank(x, V, U, v_layout, u_layout, I, R, O):
+    e = L.ext()
+    if e is not None:
+        return e.low_rank(x, V, U, v_layout, u_layout, I, R, O)
     if _eager():
         return _low_rank_impl(x, V, U, v_layout, u_layout, I, R, O)
     return low_rank_op(x, V, U, v_layout, u_layout, I, R, O)
@@ -223,6 +236,9 @@ def dense_op(x: torch.Tensor, W: torch.Tensor, w_layout: int, I: int, O: int) ->
 
 
 def dense(x, W, w_layout, I, O):
+    e = L.ext()
+    if e is not None:
+        return e.dense(x, W, w_layout, I, O)
     if _eager():
         return _dense_impl(x, W, w_layout, I, O)
     return dense_op(x, W, w_layout, I, O)

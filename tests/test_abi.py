@@ -97,3 +97,24 @@ def test_operators_refuse_cpu_tensors():
     import mem_efficient_blr_b200.dense_kernels as dk
     with pytest.raises(RuntimeError, match="no CPU implementation"):
         dk.dense_torch_layout(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(8, 8, dtype=torch.float16))
+
+
+def test_torch_extension_loads_and_declares_the_operators():
+    """The thin C++ extension over the C ABI: built in-tree, loads without a GPU, declares every hot operator with a
+    Meta kernel (shape inference for torch.compile) and refuses CPU tensors like the rest of the package."""
+    import torch
+    from mem_efficient_blr_b200 import _lib
+    e = _lib.ext()
+    assert e is not None, "mem_efficient_blr_b200/_blr_torch.so is missing: python -m mem_efficient_blr_b200.build"
+    for name in ("blast", "blast_wq", "monarch", "low_rank", "dense", "blast_wq_host", "host_flush", "workspace",
+                 "staging", "workspace_status"):
+        assert hasattr(e, name), name
+    x = torch.empty(5, 64, device="meta", dtype=torch.bfloat16)
+    w = torch.empty(48, 64, device="meta", dtype=torch.bfloat16)
+    assert e.dense(x, w, _lib.KMAJOR, 64, 48).shape == (5, 48)
+    u = torch.empty(4, 12, 32, device="meta", dtype=torch.bfloat16)
+    v = torch.empty(4, 32, 16, device="meta", dtype=torch.bfloat16)
+    s_ = torch.empty(4, 4, 32, device="meta", dtype=torch.bfloat16)
+    assert e.blast(x, u, v, s_, _lib.KMAJOR, _lib.KMAJOR, 128, 32, 1, 4, 16, 12, 32, 0).shape == (5, 48)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        e.dense(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(8, 8, dtype=torch.float16), _lib.KMAJOR, 8, 8)

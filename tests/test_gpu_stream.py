@@ -342,7 +342,7 @@ def test_host_buffer_entry_point(K, bits):
     _sync_ok(K)
     for o in outs:
         assert orc.rel_fro(o.float(), out[: o.shape[0]].float()) < 1e-3
-    with pytest.raises(AssertionError):
+    with pytest.raises((AssertionError, RuntimeError)):  # (the C++ operator reports a RuntimeError)
         call(xh[:, : I // 2], outs[0])
 
 
@@ -416,10 +416,10 @@ def test_non_contiguous_factors_are_refused(K):
     """A transposed view has the right shape but the wrong strides for the packed layouts the library reads."""
     x, Wt = orc.make_dense_inputs(3, 256, 256, torch.float16, seed=3)
     xd, Wd = _cuda(x, Wt)
-    with pytest.raises(AssertionError, match="contiguous"):
+    with pytest.raises((AssertionError, RuntimeError), match="contiguous"):
         K.dk.dense_torch_layout(xd, Wd.t())
     x, Vt, Ut = orc.make_low_rank_inputs(3, 256, 256, 64, torch.float16, seed=3)
-    with pytest.raises(AssertionError, match="contiguous"):
+    with pytest.raises((AssertionError, RuntimeError), match="contiguous"):
         K.lk.low_rank_torch_layout(x.to(DEV), Vt.to(DEV), Ut.to(DEV).t().contiguous().t())
 
 
