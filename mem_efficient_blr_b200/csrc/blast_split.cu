@@ -9,8 +9,8 @@
 //   int8 / int4      integer mma.sync m16n8k32 straight on the stored bytes - no widening instruction per weight,
 //                    which is what bounds a conversion-based path once everything is in shared memory.  The
 //                    activations of a token row are turned into 16-bit fixed point, q = rint(a / s) with
-//                    s = max|a| / 32512, and split into a signed high byte and an unsigned low byte
-//                    (q = 256 hi + lo); sum_k w_k a_k = s (256 sum_k w_k hi_k + sum_k w_k lo_k) with exact integer
+//                    s = max|a| / 32512, and split into two signed bytes
+//                    (q = 256 hi + lo, lo in [-128, 127]); sum_k w_k a_k = s (256 sum_k w_k hi_k + sum_k w_k lo_k) with exact integer
 //                    sums, and the weight scales apply to the result.  The rounding of a to 16 bits of the row
 //                    maximum is finer in norm than the 11-bit mantissa the activations arrive with.
 //
@@ -120,17 +120,13 @@ __device__ __forceinline__ uint4 ld_global_cg_v4(const void* p) {
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
-// D (s32) += A (s8, 16 x 32) * B (32 x 8): B signed or unsigned bytes.
+// D (s32) += A (s8, 16 x 32) * B (s8, 32 x 8).
 __device__ __forceinline__ void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void imma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
+
 
 // ---------------------------------------------------------------------------------------------------- fixed-point activations
 // Byte position, inside a token row, of the first of the 8 consecutive contraction indices k0 .. k0+7 (k0 a multiple
@@ -143,27 +139,30 @@ __device__ __forceinline__ void imma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1,
 // Values 0..3 and 4..7 of the run go to two words per plane (int8: tq and tq + 1; int4: even and odd indices).
 template <int WB>
 __device__ __forceinline__ void fx_store8(uint32_t row_addr, int k0, const int (&q)[8]) {
-  // byte 0 of q is the low plane (unsigned), byte 1 the high plane (signed): |q| <= 32512 < 2^15
+  // q holds the fixed-point value + 128: byte 1 is the high plane, byte 0 with its top bit flipped the low plane, both
+  // signed (value = 256 hi + lo, lo in [-128, 127], |hi| <= 127)
+  constexpr uint32_t kFlip = 0x80808080u;
   if constexpr (WB == 8) {
     const uint32_t blk = (uint32_t)k0 >> 5, o = (uint32_t)k0 & 31u, half = o >> 4, tq = (o & 15u) >> 2;  // tq is 0 or 2
     const uint32_t base = row_addr + blk * 64u + tq * 16u + half * 4u;
     sts32(base, prmt(prmt(q[0], q[1], 0x0051u), prmt(q[2], q[3], 0x0051u), 0x5410u));            // hi, tq
-    sts32(base + 8u, prmt(prmt(q[0], q[1], 0x0040u), prmt(q[2], q[3], 0x0040u), 0x5410u));       // lo, tq
+    sts32(base + 8u, prmt(prmt(q[0], q[1], 0x0040u), prmt(q[2], q[3], 0x0040u), 0x5410u) ^ kFlip);       // lo, tq
     sts32(base + 16u, prmt(prmt(q[4], q[5], 0x0051u), prmt(q[6], q[7], 0x0051u), 0x5410u));      // hi, tq + 1
-    sts32(base + 24u, prmt(prmt(q[4], q[5], 0x0040u), prmt(q[6], q[7], 0x0040u), 0x5410u));      // lo, tq + 1
+    sts32(base + 24u, prmt(prmt(q[4], q[5], 0x0040u), prmt(q[6], q[7], 0x0040u), 0x5410u) ^ kFlip);      // lo, tq + 1
   } else {
     const uint32_t blk = (uint32_t)k0 >> 6, B = ((uint32_t)k0 & 63u) >> 1, half = B >> 4, tq = (B & 15u) >> 2;
     const uint32_t base = row_addr + blk * 128u + tq * 32u + half * 4u;
     sts32(base, prmt(prmt(q[0], q[2], 0x0051u), prmt(q[4], q[6], 0x0051u), 0x5410u));            // even k, hi
-    sts32(base + 8u, prmt(prmt(q[0], q[2], 0x0040u), prmt(q[4], q[6], 0x0040u), 0x5410u));       // even k, lo
+    sts32(base + 8u, prmt(prmt(q[0], q[2], 0x0040u), prmt(q[4], q[6], 0x0040u), 0x5410u) ^ kFlip);       // even k, lo
     sts32(base + 16u, prmt(prmt(q[1], q[3], 0x0051u), prmt(q[5], q[7], 0x0051u), 0x5410u));      // odd k, hi
-    sts32(base + 24u, prmt(prmt(q[1], q[3], 0x0040u), prmt(q[5], q[7], 0x0040u), 0x5410u));      // odd k, lo
+    sts32(base + 24u, prmt(prmt(q[1], q[3], 0x0040u), prmt(q[5], q[7], 0x0040u), 0x5410u) ^ kFlip);      // odd k, lo
   }
 }
 
-// rint(a * inv) for |a * inv| < 2^22, as the low bits of a float sum: 1.5 * 2^23 + q has q (two's complement) in its
-// low mantissa bits, and fx_store8 only takes bytes 0 and 1.  One FMA instead of a multiply and a conversion.
-__device__ __forceinline__ int fx_round(float a, float inv) { return __float_as_int(fmaf(a, inv, 12582912.f)); }
+// rint(a * inv) + 128 for |a * inv| < 2^22, as the low bits of a float sum: 1.5 * 2^23 + 128 + q has q + 128 (two's
+// complement) in its low mantissa bits, and fx_store8 only takes bytes 0 and 1.  One FMA instead of a multiply and a
+// conversion.
+__device__ __forceinline__ int fx_round(float a, float inv) { return __float_as_int(fmaf(a, inv, 12582912.f + 128.f)); }
 
 template <bool BF16>
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -204,6 +203,14 @@ __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w) {
   }
 }
 
+// Largest of the 64 packed non-negative 16-bit floats a warp holds in m2, as a float in every lane: non-negative
+// floats order like their bit patterns, so one integer warp reduction does it.
+template <bool BF16>
+__device__ __forceinline__ float warp_max16(uint32_t m2) {
+  const uint32_t m = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
+  return unpack16x2<BF16>(m).x;
+}
+
 // Largest magnitude over the warp's pieces of a row (NaNs do not count), the same value in every lane.
 template <bool BF16>
 __device__ __forceinline__ float fx_row_absmax(uint32_t row_addr, int base0, int step, int pieces, int lane) {
@@ -218,11 +225,7 @@ __device__ __forceinline__ float fx_row_absmax(uint32_t row_addr, int base0, int
       m2 = absmax2<BF16>(absmax2<BF16>(m2, c), d);
     }
   }
-  const float2 t = unpack16x2<BF16>(m2);
-  float m = fmaxf(t.x, t.y);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  return m;
+  return warp_max16<BF16>(m2);
 }
 
 // Scale of a row with largest magnitude m, and its inverse (an all-zero, infinite or NaN row reads as zeros).
@@ -264,14 +267,8 @@ __device__ __forceinline__ void fx_rows4(int nrows, int pieces, uint32_t rows0, 
     for (int i = 0; i < 4; ++i) {
       v[i] = make_uint4(0, 0, 0, 0);
       if (have && rb + i < nrows) lds128(rows0 + (uint32_t)(rb + i) * pitch + (uint32_t)lane * 16u, v[i].x, v[i].y, v[i].z, v[i].w);
-      const uint32_t m2 = absmax2<BF16>(absmax2<BF16>(absmax2<BF16>(absmax2<BF16>(0u, v[i].x), v[i].y), v[i].z), v[i].w);
-      const float2 t = unpack16x2<BF16>(m2);
-      m[i] = fmaxf(t.x, t.y);
+      m[i] = warp_max16<BF16>(absmax2<BF16>(absmax2<BF16>(absmax2<BF16>(absmax2<BF16>(0u, v[i].x), v[i].y), v[i].z), v[i].w));
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], __shfl_xor_sync(0xffffffffu, m[i], o));
     __syncwarp();  // every lane has read its pieces: the stores below land on other lanes' pieces of the same block
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -338,7 +335,7 @@ __device__ __forceinline__ void iq_k8(uint32_t sW, uint32_t sA, uint32_t pitch, 
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
         imma_s8s8(hi[n], a[i][0], a[i][1], a[i][2], a[i][3], b[i][n][0], b[i][n][1]);
-        imma_s8u8(lo[n], a[i][0], a[i][1], a[i][2], a[i][3], b[i][n][2], b[i][n][3]);
+        imma_s8s8(lo[n], a[i][0], a[i][1], a[i][2], a[i][3], b[i][n][2], b[i][n][3]);
       }
   }
 }
@@ -378,9 +375,9 @@ __device__ __forceinline__ void iq_k4_win(uint32_t sW, uint32_t sA, uint32_t pit
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
         imma_s8s8(hi[n], ae[0], ae[1], ae[2], ae[3], be[i][n][0], be[i][n][1]);
-        imma_s8u8(lo[n], ae[0], ae[1], ae[2], ae[3], be[i][n][2], be[i][n][3]);
+        imma_s8s8(lo[n], ae[0], ae[1], ae[2], ae[3], be[i][n][2], be[i][n][3]);
         imma_s8s8(hi[n], ao[0], ao[1], ao[2], ao[3], bo[i][n][0], bo[i][n][1]);
-        imma_s8u8(lo[n], ao[0], ao[1], ao[2], ao[3], bo[i][n][2], bo[i][n][3]);
+        imma_s8s8(lo[n], ao[0], ao[1], ao[2], ao[3], bo[i][n][2], bo[i][n][3]);
       }
     }
   }
@@ -398,12 +395,62 @@ __device__ __forceinline__ void iq_k4_half(uint32_t sW, uint32_t sA, uint32_t pi
   else iq_k4_win<NT, 2, 4>(sW, sA, pitch, N, hi, lo, lane);
 }
 
+// Up to 4 tokens, both planes in one MMA: output column c of the 8 holds token c % 4, plane c / 4 (high planes
+// first), so lane (g, tq) fetches the 8 bytes of its plane of token g % 4 per window.  Half the MMAs and half the
+// activation bytes of the two-MMA form.
+template <int WLO, int WHI>
+__device__ __forceinline__ void iq_k8_merged(uint32_t sW, uint32_t sA, uint32_t pitch, int N, int (&acc)[4], int lane) {
+  const uint32_t jm = lane >> 3, l7 = lane & 7, g = lane >> 2, tq = lane & 3;
+  const uint32_t row = l7 + (jm & 1) * 8;
+  const uint32_t arow = sA + ((int)(g & 3) < N ? (g & 3) : 0u) * pitch + tq * 16 + (g >> 2) * 8;
+  uint32_t a[WHI - WLO][4], b[WHI - WLO][2];
+#pragma unroll
+  for (int i = 0; i < WHI - WLO; ++i) {
+    const int win = WLO + i;
+    ldsm_x4(sW + sw128(row, win * 2 + (jm >> 1)), a[i][0], a[i][1], a[i][2], a[i][3]);
+    lds64(arow + win * 64, b[i][0], b[i][1]);
+  }
+#pragma unroll
+  for (int i = 0; i < WHI - WLO; ++i) imma_s8s8(acc, a[i][0], a[i][1], a[i][2], a[i][3], b[i][0], b[i][1]);
+}
+template <int WLO, int WHI>
+__device__ __forceinline__ void iq_k4_merged(uint32_t sW, uint32_t sA, uint32_t pitch, int N, int (&acc)[4], int lane) {
+  const uint32_t jm = lane >> 3, l7 = lane & 7, g = lane >> 2, tq = lane & 3;
+  const uint32_t row = l7 + (jm & 1) * 8;
+  const uint32_t arow = sA + ((int)(g & 3) < N ? (g & 3) : 0u) * pitch + tq * 32 + (g >> 2) * 8;
+#pragma unroll
+  for (int w0 = WLO; w0 < WHI; w0 += 2) {
+    uint32_t r[2][4], be[2][2], bo[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int win = w0 + i;
+      ldsm_x4(sW + sw128(row, win * 2 + (jm >> 1)), r[i][0], r[i][1], r[i][2], r[i][3]);
+      lds64(arow + win * 128, be[i][0], be[i][1]);
+      lds64(arow + win * 128 + 16, bo[i][0], bo[i][1]);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t ae[4], ao[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ae[e] = (r[i][e] << 4) & 0xF0F0F0F0u;
+        ao[e] = r[i][e] & 0xF0F0F0F0u;
+      }
+      imma_s8s8(acc, ae[0], ae[1], ae[2], ae[3], be[i][0], be[i][1]);
+      imma_s8s8(acc, ao[0], ao[1], ao[2], ao[3], bo[i][0], bo[i][1]);
+    }
+  }
+}
+
 // Accumulators of one work item: fp32 chains for 16-bit weights, integer planes for quantised weights, and the
-// running fp32 total that per-group scales fold into.
-template <int NT, int WB>
+// running fp32 total that per-group scales fold into.  MG (quantised weights, up to 4 tokens): one integer
+// accumulator whose columns are (token, plane); finish() brings the planes of a token together (they sit two lanes
+// apart), after which lanes with tq < 2 hold tokens 2 tq and 2 tq + 1 like the other forms and the other lanes'
+// values belong to token columns 4..7, which nobody reads.
+template <int NT, int WB, bool MG>
 struct ItemAcc {
   float acc[WB == 16 ? 4 : 1][NT][4];
-  int hi[NT][4], lo[NT][4];
+  int hi[NT][4], lo[MG ? 1 : NT][4];
   float tot[NT][4];
   __device__ __forceinline__ void clear() {
 #pragma unroll
@@ -411,7 +458,8 @@ struct ItemAcc {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         tot[n][e] = 0.f;
-        hi[n][e] = lo[n][e] = 0;
+        hi[n][e] = 0;
+        if constexpr (!MG) lo[n][e] = 0;
 #pragma unroll
         for (int q = 0; q < (WB == 16 ? 4 : 1); ++q) acc[q][n][e] = 0.f;
       }
@@ -422,13 +470,27 @@ struct ItemAcc {
     for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        tot[n][e] = fmaf(e < 2 ? s_row : s_row8, fmaf((float)hi[n][e], 256.f, (float)lo[n][e]), tot[n][e]);
-        hi[n][e] = lo[n][e] = 0;
+        const float v = MG ? (float)hi[n][e] : fmaf((float)hi[n][e], 256.f, (float)lo[MG ? 0 : n][e]);
+        tot[n][e] = fmaf(e < 2 ? s_row : s_row8, v, tot[n][e]);
+        hi[n][e] = 0;
+        if constexpr (!MG) lo[n][e] = 0;
       }
+  }
+  // once, after the last chunk and before value(): every lane of the warp
+  __device__ __forceinline__ void finish(bool grouped) {
+    if constexpr (MG) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mine = grouped ? tot[0][e] : (float)hi[0][e];
+        const float other = __shfl_xor_sync(0xffffffffu, mine, 2);  // the low plane of lanes tq < 2
+        tot[0][e] = fmaf(mine, 256.f, other);
+      }
+    }
   }
   // value of accumulator element (n, e) before the per-channel and activation scales
   __device__ __forceinline__ float value(int n, int e, bool grouped) const {
     if constexpr (WB == 16) return acc[0][n][e] + acc[1][n][e] + acc[2][n][e] + acc[3][n][e];
+    else if constexpr (MG) return tot[0][e];
     else return grouped ? tot[n][e] : fmaf((float)hi[n][e], 256.f, (float)lo[n][e]);
   }
 };
@@ -444,7 +506,7 @@ __device__ __forceinline__ uint32_t fastdiv(uint32_t t, uint32_t d, uint32_t mag
 #define BLR_CK(slot) do { } while (0)
 #endif
 
-template <bool BF16, int NT, bool GS, int WB, bool ACT>
+template <bool BF16, int NT, bool GS, int WB, bool ACT, bool MG>
 __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(const __grid_constant__ SplitParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -643,7 +705,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
     constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;  // fixed-point bytes of one chunk's indices in a token row
     const int share = split_share(nb);
     const int jw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - jw * share;
-    ItemAcc<NT, WB> A;
+    ItemAcc<NT, WB, MG> A;
 #pragma unroll 1
     for (int j = jw; j < nb; j += kW) {
       A.clear();
@@ -661,7 +723,17 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
             gsc = __half2float(__ldg(srow + gi));
             if (WB == 4 && gi + 1 < ngroups) gsc2 = __half2float(__ldg(srow + gi + 1));
           }
-          if constexpr (WB == 8) {
+          if constexpr (MG && WB == 8) {
+            iq_k8_merged<0, 4>(sW, sA, xpitch, N, A.hi[0], lane);
+            if constexpr (GS) A.fold(gsc, 0.f);
+          } else if constexpr (MG && !GS) {
+            iq_k4_merged<0, 4>(sW, sA, xpitch, N, A.hi[0], lane);
+          } else if constexpr (MG) {
+            iq_k4_merged<0, 2>(sW, sA, xpitch, N, A.hi[0], lane);
+            A.fold(gsc, 0.f);
+            iq_k4_merged<2, 4>(sW, sA, xpitch, N, A.hi[0], lane);
+            A.fold(gsc2, 0.f);
+          } else if constexpr (WB == 8) {
             iq_k8<NT>(sW, sA, xpitch, N, A.hi, A.lo, lane);
             if constexpr (GS) A.fold(gsc, 0.f);
           } else if constexpr (!GS) {
@@ -675,6 +747,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
           }
         }
       }
+      A.finish(GS);
       if (share == 1) {
         const float vsc = vs[j * 8 + g];
 #pragma unroll
@@ -779,7 +852,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------- back
-template <bool BF16, int NT, bool GS, int WB>
+template <bool BF16, int NT, bool GS, int WB, bool MG>
 __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(const __grid_constant__ SplitParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -925,8 +998,9 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   const int share = split_share(p.gpc);
   {
     const int gw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - gw * share;
-    ItemAcc<NT, WB> A;
+    ItemAcc<NT, WB, MG> A;
     auto flush = [&](int gl) {
+      A.finish(GS);
       // [token][16 rows]: the sums below read neighbouring rows of a token from neighbouring banks
       float* slot = partial + (size_t)(gl * share + ws) * 16 * NP;
 #pragma unroll
@@ -954,7 +1028,17 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
             if (m + 8 < Q) gb8 = __half2float(__ldg(srow + 8 * ngroups + gi + 1));
           }
         }
-        if constexpr (WB == 8) {
+        if constexpr (MG && WB == 8) {
+          iq_k8_merged<0, 4>(sW, sA, zpitch, N, A.hi[0], lane);
+          if constexpr (GS) A.fold(ga, ga8);
+        } else if constexpr (MG && !GS) {
+          iq_k4_merged<0, 4>(sW, sA, zpitch, N, A.hi[0], lane);
+        } else if constexpr (MG) {
+          iq_k4_merged<0, 2>(sW, sA, zpitch, N, A.hi[0], lane);
+          A.fold(ga, ga8);
+          iq_k4_merged<2, 4>(sW, sA, zpitch, N, A.hi[0], lane);
+          A.fold(gb, gb8);
+        } else if constexpr (WB == 8) {
           iq_k8<NT>(sW, sA, zpitch, N, A.hi, A.lo, lane);
           if constexpr (GS) A.fold(ga, ga8);
         } else if constexpr (!GS) {
@@ -1062,7 +1146,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-template <bool BF16, int NT, bool GS, int WB>
+template <bool BF16, int NT, bool GS, int WB, bool MG = false>
 static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
@@ -1070,8 +1154,8 @@ static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
   const size_t fs = split_front_smem(p), bs = split_back_smem(p);
   BLR_REQUIRE((int)fs <= di.max_smem_optin && (int)bs <= di.max_smem_optin, BLR_ERR_UNSUPPORTED,
               "needs %zu / %zu bytes of shared memory, device offers %d", fs, bs, di.max_smem_optin);
-  auto front = p.act == kSplitActSiluMul ? blr_blast_front_kernel<BF16, NT, GS, WB, true> : blr_blast_front_kernel<BF16, NT, GS, WB, false>;
-  auto back = blr_blast_back_kernel<BF16, NT, GS, WB>;
+  auto front = p.act == kSplitActSiluMul ? blr_blast_front_kernel<BF16, NT, GS, WB, true, MG> : blr_blast_front_kernel<BF16, NT, GS, WB, false, MG>;
+  auto back = blr_blast_back_kernel<BF16, NT, GS, WB, MG>;
   {
     int dev = 0;
     BLR_CUDA_OK(cudaGetDevice(&dev));
@@ -1123,6 +1207,13 @@ int launch_blast_split(const SplitParams& p, int is_bf16, cudaStream_t stream) {
 #define BLR_SP(BF, NTV, GSV)                                                        \
   (p.wbits == 16 ? launch_split_impl<BF, NTV, false, 16>(p, stream)                 \
                  : (p.wbits == 8 ? launch_split_impl<BF, NTV, GSV, 8>(p, stream) : launch_split_impl<BF, NTV, GSV, 4>(p, stream)))
+  if (p.N <= 4 && p.wbits != 16) {
+    // quantised factors, up to 4 tokens: both planes of the fixed-point activations in one integer MMA
+#define BLR_SPM(BF, GSV) (p.wbits == 8 ? launch_split_impl<BF, 1, GSV, 8, true>(p, stream) : launch_split_impl<BF, 1, GSV, 4, true>(p, stream))
+    if (gs) return is_bf16 ? BLR_SPM(true, true) : BLR_SPM(false, true);
+    return is_bf16 ? BLR_SPM(true, false) : BLR_SPM(false, false);
+#undef BLR_SPM
+  }
   if (p.N <= 8) {
     if (gs) return is_bf16 ? BLR_SP(true, 1, true) : BLR_SP(false, 1, true);
     return is_bf16 ? BLR_SP(true, 1, false) : BLR_SP(false, 1, false);
