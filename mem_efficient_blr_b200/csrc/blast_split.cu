@@ -571,6 +571,9 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
       vs[tid] = v;
     }
   }
+  // (divisions of the product phase, done here where nothing waits for them)
+  const int share = split_share(nb);
+  const int jw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - jw * share;
   BLR_TL(1);
   // One warp waits for the kernel ahead; the others sleep at the barrier.
   if (warp == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -703,8 +706,6 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
     const int g = lane >> 2, tq = lane & 3;
     const int ngroups = GS ? p.P / kScaleGroup : 0;
     constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;  // fixed-point bytes of one chunk's indices in a token row
-    const int share = split_share(nb);
-    const int jw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - jw * share;
     ItemAcc<NT, WB, MG> A;
 #pragma unroll 1
     for (int j = jw; j < nb; j += kW) {
@@ -932,6 +933,10 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     us[e] = v;
   }
   if (ctid < 16) sz[16 + ctid] = 0.f;  // row maxima of the fixed-point conversion
+  // (divisions of the later phases, done here where nothing waits for them)
+  const int share = split_share(p.gpc);
+  const int gw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - gw * share;
+  const int wpr = N >= kW ? 1 : kW / N, zn = warp / wpr, zwl = warp - zn * wpr;
   BLR_TL(1);
   if (warp == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
   named_bar(1, kCT);
@@ -945,7 +950,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
     if constexpr (FX) {
       // Every token row is shared out over wpr = 16 / N warps (at least one): each thread takes its 16-byte pieces,
       // the warps' maxima meet in shared memory, then every thread converts its own pieces.
-      const int wpr = N >= kW ? 1 : kW / N, n = warp / wpr, wl = warp - n * wpr;
+      const int n = zn, wl = zwl;
       const int pieces = R >> 3, base0 = wl * 32, step = wpr * 32;
       float* pm = sz + 16;  // per-row maxima (16 floats after the 16 row scales)
       const bool have_row = n < N;
@@ -995,9 +1000,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   bool ok = true;
   const int ngroups = GS ? R / kScaleGroup : 0;
   constexpr uint32_t kChunkAct = WB == 8 ? 256u : 512u;
-  const int share = split_share(p.gpc);
   {
-    const int gw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - gw * share;
     ItemAcc<NT, WB, MG> A;
     auto flush = [&](int gl) {
       A.finish(GS);
