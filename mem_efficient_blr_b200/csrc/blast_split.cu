@@ -937,6 +937,8 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
   const int share = split_share(p.gpc);
   const int gw = share == 1 ? warp : warp / share, ws = share == 1 ? 0 : warp - gw * share;
   const int wpr = N >= kW ? 1 : kW / N, zn = warp / wpr, zwl = warp - zn * wpr;
+  const int cpr = nbz * 8, upr = (cpr + 31) >> 5;  // 16-bit path: 16-byte pieces and warp-wide runs per row of z
+  const int un0 = warp / upr, ur0 = warp - un0 * upr, udn = kW / upr, udr = kW - udn * upr;
   BLR_TL(1);
   if (warp == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
   named_bar(1, kCT);
@@ -976,10 +978,20 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
       }
     } else {
       // [64-wide box][token][128 B], zero past R.  A warp per run of 32 pieces of a token row.
-      const int cpr = nbz * 8, upr = (cpr + 31) >> 5;  // 16-byte pieces and warp-wide runs per row
+      // unit u = warp, warp + 16, ...: token u / upr, run u % upr, stepped without divisions
+      int n = un0, run = ur0;
+#pragma unroll 1
       for (int u = warp; u < N * upr; u += kW) {
-        const int n = u / upr, ch = (u - n * upr) * 32 + lane;
+        const int ch = run * 32 + lane;
+        run += udr;
+        const int n_now = n;
+        n += udn;
+        if (run >= upr) {
+          run -= upr;
+          ++n;
+        }
         if (ch < cpr) {
+          const int n = n_now;
           const int kb = ch >> 3, c16 = ch & 7, k = ch * 8;
           const bool in = k < R;
           cp_async16_zfill(smem_base + L.zs + (uint32_t)(kb * N + n) * 128u + (uint32_t)((c16 ^ (n & 7)) << 4),
