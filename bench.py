@@ -49,8 +49,8 @@ GROUPS = {"two_launch": ("blr_blast_front_kernel+blr_blast_back_kernel", 2), "cl
 
 
 def group_of(bits: int, n: int) -> str:
-    """Kernel group the library's dispatch picks for a point (packed int4 above 8 tokens goes to the cluster kernel)."""
-    return "cluster" if bits == 4 and n > 8 else "two_launch"
+    """Kernel group the library's dispatch picks for a point: every point of the workload takes the two-launch path."""
+    return "two_launch"
 
 
 def algorithmic_bytes(bits: int, n: int) -> float:

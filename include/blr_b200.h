@@ -129,7 +129,7 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
  * Factors are contraction-contiguous: U (b,Q,R), V (b,R,P) in the 16-bit dtype (bits = 16: scales ignored) or quantised
  * as for blr_blast_wq (bits = 8 | 4).  S element (i, j, r) of every layer at i*s_i + j*s_j + r*s_r.
  * Scratch: blr_workspace_bytes(n_tokens, n_problems * b, R).  Serves the token counts of the two-launch decode path
- * (up to 8 tokens with 16-bit factors, 4 with quantised ones); BLR_ERR_UNSUPPORTED otherwise - run the layers one by one. */
+ * (1..16 tokens, K-major factors); BLR_ERR_UNSUPPORTED otherwise - run the layers one by one. */
 #define BLR_ACT_NONE 0
 #define BLR_ACT_SILU_MUL 1
 typedef struct blr_blast_problem {

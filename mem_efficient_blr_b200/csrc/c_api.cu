@@ -172,10 +172,9 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
                              const SplitLayer* layers, int u_layout, int v_layout, int wb, int group, int64_t s_i, int64_t s_j,
                              int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* zbase, unsigned* status,
                              cudaStream_t stream) {
-  // Measured crossover against the cluster kernel on the Llama-7B shapes: the two-launch path wins at every token
-  // count it takes with 16-bit and int8 factors, and up to 8 tokens with packed int4 factors (whose integer MMAs and
-  // fixed-point activations double per chunk).
-  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > (wb == 4 ? 8 : kStreamMaxTokens)) return 1;
+  // Measured against the cluster kernel on the Llama-7B shapes, the two-launch path wins at every token count it
+  // takes (1..16) with 16-bit, int8 and packed int4 factors.
+  if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > kStreamMaxTokens) return 1;
   if (u_layout != BLR_W_KMAJOR || v_layout != BLR_W_KMAJOR || b > kSplitMaxBlocks || nprob < 1 || nprob > kSplitMaxProblems) return 1;
   const long long kbV = (long long)P * wb / 8, kbU = (long long)R * wb / 8;
   if (R % kSplitRanks != 0 || P % 8 != 0 || kbV % 16 != 0 || kbU % 16 != 0 || (wb == 4 && ((P | R) & 1))) return 1;

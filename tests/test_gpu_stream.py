@@ -436,10 +436,10 @@ def test_argument_errors_are_reported(K):
 
 
 @pytest.mark.parametrize("bits", [16, 8, 4])
-@pytest.mark.parametrize("N", [1, 3, 12])
+@pytest.mark.parametrize("N", [1, 3, 12, 20])
 def test_fused_layers_bias_residual_and_swiglu_input(K, bits, N):
     """blr_blast_multi: q/k/v-style layers on one input with bias and residual in the epilogue, and a down projection
-    fed with silu(gate) * up, against the oracle composition (N = 12 takes the layer-by-layer route)."""
+    fed with silu(gate) * up, against the oracle composition (N = 20 takes the layer-by-layer route)."""
     I, O, b, R = 1024, 1536, 8, 256
     x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=200 + N)
     sets = [(U, Vt, S)]
