@@ -279,6 +279,34 @@ int blr_load_store_probe(const void* a, size_t a_bytes, const void* b, size_t b_
                          int out_kind, void* out, int64_t n_tokens, int64_t out_features, int64_t ldo, int tile,
                          void* stream);
 
+/* ---- The small kernels of a Llama-style decode step around the structured linears.  No counterpart among the
+ * reference's operator files: its network harness runs HuggingFace's modules for them (models/llama7b.py,
+ * network.py:60-94).  16-bit tensors of `dtype`, fp32 arithmetic, one rounding on the way out. */
+
+/* out[r][:] = x[r][:] * rsqrt(mean(x[r][:]^2) + eps) * weight[:] for `rows` rows of d values (d, ldx, ldo multiples
+ * of 8; pointers 16-byte aligned).  Models LlamaRMSNorm. */
+int blr_rmsnorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, float eps, int dtype,
+                void* out, int64_t ldo, void* stream);
+
+/* Rotary embedding and append to a static KV cache.  q, k, v: n_seq * n_tok rows (sequence-major) of heads * head_dim
+ * values, row strides ldq / ldk / ldv.  Token t takes cache slot pos[t] (device int64) and the rotation angle of that
+ * slot from cos_table / sin_table ((slots, head_dim / 2) fp32; pairs (i, i + head_dim / 2) rotate, as in HF's Llama).
+ * q is rotated in place; rotated k and v are written to k_cache / v_cache [seq][head][pos[t]][:] (caches of
+ * (n_seq, heads, slots, head_dim)). */
+int blr_rope_append(void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                    const float* cos_table, const float* sin_table, const int64_t* pos,
+                    int64_t n_seq, int n_tok, int heads, int head_dim, int slots, int dtype,
+                    void* k_cache, void* v_cache, void* stream);
+
+/* Attention of one query token per sequence over the first n_keys slots of the cache:
+ * out[seq][head*head_dim + :] = softmax(scale * q . K^T) V, q (n_seq, heads * head_dim) with row stride ldq.
+ * The keys of a head are split over up to 8 CTAs whose partial results a second kernel merges; `scratch` holds the
+ * partials (blr_attention_decode_scratch_bytes). */
+size_t blr_attention_decode_scratch_bytes(int64_t n_seq, int heads, int head_dim, int n_keys);
+int blr_attention_decode(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                         int64_t n_seq, int heads, int head_dim, int slots, int n_keys, float scale, int dtype,
+                         void* out, int64_t ldo, void* scratch, size_t scratch_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

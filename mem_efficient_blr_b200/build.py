@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libblr_b200.so")
-SOURCES = ["tmap.cu", "stream_kernel.cu", "blast_cluster.cu", "blast_split.cu", "umma_gemm.cu", "pipeline.cu", "ref32.cu", "c_api.cu"]
+SOURCES = ["tmap.cu", "stream_kernel.cu", "blast_cluster.cu", "blast_split.cu", "umma_gemm.cu", "pipeline.cu", "ref32.cu", "decoder_kernels.cu", "c_api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",

@@ -1,0 +1,359 @@
+// The small kernels of a Llama-style decode step around the structured linears: RMSNorm, rotary embedding with the
+// append to a static KV cache, and attention of one new token per sequence over the cache.  None of them has a
+// counterpart among the reference's operator files: its network harness runs HuggingFace's modules for these
+// (models/llama7b.py builds the model, network.py:60-94 times it), a dozen element-wise launches per layer each.
+// Here a decoder layer is four structured-linear calls plus these four launches.
+//
+// All arithmetic is fp32 on 16-bit inputs, rounded once on the way out, like the PyTorch modules they stand in for.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/blr_b200.h"
+#include "tmap.h"
+
+namespace blr {
+
+template <bool BF16>
+__device__ __forceinline__ float2 up2(uint32_t w) {
+  if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t down2(float a, float b) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&r);
+  } else {
+    const __half2 r = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_maxf(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------ RMSNorm
+// out[r][:] = x[r][:] * rsqrt(mean(x[r][:]^2) + eps) * w[:].  One CTA per row, 16-byte accesses (d % 8 == 0).
+template <bool BF16>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict__ x, long long ldx, const uint16_t* __restrict__ w,
+                                                      float eps, int d, uint16_t* __restrict__ out, long long ldo) {
+  __shared__ float red[8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint16_t* xr = x + (long long)blockIdx.x * ldx;
+  uint16_t* orow = out + (long long)blockIdx.x * ldo;
+  const int pieces = d >> 3;
+  float ss = 0.f;
+  for (int p = threadIdx.x; p < pieces; p += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + p * 8);
+    const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = up2<BF16>(ws[i]);
+      ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)d + eps);
+  for (int p = threadIdx.x; p < pieces; p += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + p * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(w + p * 8);
+    const uint32_t vs[4] = {v.x, v.y, v.z, v.w}, gs[4] = {g.x, g.y, g.z, g.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = up2<BF16>(vs[i]), s = up2<BF16>(gs[i]);
+      o[i] = down2<BF16>(f.x * inv * s.x, f.y * inv * s.y);
+    }
+    *reinterpret_cast<uint4*>(orow + p * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ rotary embedding + cache append
+// Row r = (sequence b, token t) of q, k, v (rows of H * hd values, row strides ldq / ldk / ldv).  Pairs (i, i + hd/2) of
+// every head of q and k are rotated by the angle of cache slot pos[t] (cos, sin tables (slots, hd/2), fp32); q is
+// rewritten in place, the rotated k and v go to kc / vc [b][h][pos[t]][:] (caches (B, H, slots, hd)).
+template <bool BF16>
+__global__ void __launch_bounds__(256) rope_append_kernel(uint16_t* __restrict__ q, long long ldq, const uint16_t* __restrict__ k,
+                                                          long long ldk, const uint16_t* __restrict__ v, long long ldv,
+                                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                          const long long* __restrict__ pos, int T, int H, int hd, int slots,
+                                                          uint16_t* __restrict__ kc, uint16_t* __restrict__ vc) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int r = blockIdx.x, b = r / T, t = r - b * T, half = hd >> 1;
+  const long long slot = pos[t];
+  const float* cs = cos_t + slot * half;
+  const float* sn = sin_t + slot * half;
+  uint16_t* qr = q + (long long)r * ldq;
+  const uint16_t* kr = k + (long long)r * ldk;
+  const uint16_t* vr = v + (long long)r * ldv;
+  // two values per thread and step: pair index i = 2 u, 2 u + 1 of head h
+  const int per_head = half >> 1;
+  for (int e = threadIdx.x; e < H * per_head; e += 256) {
+    const int h = e / per_head, i = (e - h * per_head) * 2;
+    const float c0 = cs[i], c1 = cs[i + 1], s0 = sn[i], s1 = sn[i + 1];
+    const long long o1 = (long long)h * hd + i, o2 = o1 + half;
+    const long long dst = (((long long)b * H + h) * slots + slot) * hd;
+    {
+      const float2 a = up2<BF16>(*reinterpret_cast<const uint32_t*>(qr + o1)), bb = up2<BF16>(*reinterpret_cast<const uint32_t*>(qr + o2));
+      *reinterpret_cast<uint32_t*>(qr + o1) = down2<BF16>(a.x * c0 - bb.x * s0, a.y * c1 - bb.y * s1);
+      *reinterpret_cast<uint32_t*>(qr + o2) = down2<BF16>(bb.x * c0 + a.x * s0, bb.y * c1 + a.y * s1);
+    }
+    {
+      const float2 a = up2<BF16>(*reinterpret_cast<const uint32_t*>(kr + o1)), bb = up2<BF16>(*reinterpret_cast<const uint32_t*>(kr + o2));
+      *reinterpret_cast<uint32_t*>(kc + dst + i) = down2<BF16>(a.x * c0 - bb.x * s0, a.y * c1 - bb.y * s1);
+      *reinterpret_cast<uint32_t*>(kc + dst + half + i) = down2<BF16>(bb.x * c0 + a.x * s0, bb.y * c1 + a.y * s1);
+    }
+    *reinterpret_cast<uint32_t*>(vc + dst + i) = *reinterpret_cast<const uint32_t*>(vr + o1);
+    *reinterpret_cast<uint32_t*>(vc + dst + half + i) = *reinterpret_cast<const uint32_t*>(vr + o2);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ attention of one token over the cache
+// CTA (split, head, sequence): keys [k0, k0 + ks) of the head's cache.  Phase A: a thread per key, dot product with q
+// (shared memory, fp32) over hd in 16-byte pieces; block maximum and sum of exp.  Phase B: threads own pairs of
+// output dimensions and stride over the keys.  Partial result (unnormalised output, maximum, sum) per split; the
+// combine kernel merges the splits of a head.
+static constexpr int kAttnThreads = 256;
+
+template <bool BF16>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(const uint16_t* __restrict__ q, long long ldq,
+                                                                         const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
+                                                                         int H, int hd, int slots, int n_keys, int ks, float scale,
+                                                                         float* __restrict__ part) {
+  extern __shared__ float sm[];  // q[hd] | p[ks] | red[16] | acc[4][hd]
+  float* qs = sm;
+  float* ps = qs + hd;
+  float* red = ps + ks;
+  float* accs = red + 16;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int k0 = split * ks, nk = min(ks, n_keys - k0);
+  const uint16_t* kh = kc + (((long long)b * H + h) * slots + k0) * hd;
+  const uint16_t* vh = vc + (((long long)b * H + h) * slots + k0) * hd;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = tid; i < hd / 2; i += kAttnThreads) {
+    const float2 f = up2<BF16>(*reinterpret_cast<const uint32_t*>(q + (long long)b * ldq + (long long)h * hd + 2 * i));
+    qs[2 * i] = f.x;
+    qs[2 * i + 1] = f.y;
+  }
+  __syncthreads();
+  // ---- scores
+  float m = -3.0e38f;
+  for (int j = tid; j < nk; j += kAttnThreads) {
+    const uint16_t* kr = kh + (long long)j * hd;
+    float s = 0.f;
+    for (int p = 0; p < hd; p += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(kr + p);
+      const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = up2<BF16>(ws[i]);
+        s = fmaf(f.x, qs[p + 2 * i], fmaf(f.y, qs[p + 2 * i + 1], s));
+      }
+    }
+    s *= scale;
+    ps[j] = s;
+    m = fmaxf(m, s);
+  }
+  m = warp_maxf(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int i = 1; i < kAttnThreads / 32; ++i) m = fmaxf(m, red[i]);
+  float l = 0.f;
+  for (int j = tid; j < nk; j += kAttnThreads) {
+    const float p = __expf(ps[j] - m);
+    ps[j] = p;
+    l += p;
+  }
+  l = warp_sum(l);
+  __syncthreads();  // (everyone has read red[] as maxima)
+  if (lane == 0) red[8 + warp] = l;
+  __syncthreads();
+  // ---- weighted sum of the values: thread (group g of 4, dimension pair dp)
+  const int npair = hd >> 1, groups = kAttnThreads / npair >= 4 ? 4 : (kAttnThreads / npair > 0 ? kAttnThreads / npair : 1);
+  if (tid < groups * npair) {
+    const int g = tid / npair, dp = tid - g * npair;
+    float ax = 0.f, ay = 0.f;
+    for (int j = g; j < nk; j += groups) {
+      const float2 f = up2<BF16>(*reinterpret_cast<const uint32_t*>(vh + (long long)j * hd + 2 * dp));
+      const float p = ps[j];
+      ax = fmaf(p, f.x, ax);
+      ay = fmaf(p, f.y, ay);
+    }
+    accs[g * hd + 2 * dp] = ax;
+    accs[g * hd + 2 * dp + 1] = ay;
+  }
+  __syncthreads();
+  float* dst = part + (((long long)b * H + h) * gridDim.x + split) * (hd + 2);
+  for (int d = tid; d < hd; d += kAttnThreads) {
+    float o = accs[d];
+    for (int g = 1; g < groups; ++g) o += accs[g * hd + d];
+    dst[d] = o;
+  }
+  if (tid == 0) {
+    float lt = 0.f;
+#pragma unroll
+    for (int i = 0; i < kAttnThreads / 32; ++i) lt += red[8 + i];
+    dst[hd] = m;
+    dst[hd + 1] = lt;
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const float* __restrict__ part, int nsplit, int hd, uint16_t* __restrict__ out,
+                                                                  long long ldo, int H) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* p0 = part + (((long long)b * H + h) * nsplit) * (hd + 2);
+  float m = -3.0e38f;
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, p0[s * (hd + 2) + hd]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) L += p0[s * (hd + 2) + hd + 1] * __expf(p0[s * (hd + 2) + hd] - m);
+  const float invL = 1.f / L;
+  for (int dp = threadIdx.x; dp < hd / 2; dp += 128) {
+    float ox = 0.f, oy = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float w = __expf(p0[s * (hd + 2) + hd] - m);
+      ox = fmaf(w, p0[s * (hd + 2) + 2 * dp], ox);
+      oy = fmaf(w, p0[s * (hd + 2) + 2 * dp + 1], oy);
+    }
+    *reinterpret_cast<uint32_t*>(out + (long long)b * ldo + (long long)h * hd + 2 * dp) = down2<BF16>(ox * invL, oy * invL);
+  }
+}
+
+template <typename K, typename... A>
+static int launch_pdl(K kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  BLR_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, args...));
+  return BLR_OK;
+}
+
+static int attn_splits(int64_t B, int H, int n_keys) {
+  int ns = (int)((2 * 148 + B * H - 1) / (B * H));
+  if (ns > 8) ns = 8;
+  while (ns > 1 && (n_keys + ns - 1) / ns < 64) --ns;
+  return ns < 1 ? 1 : ns;
+}
+
+}  // namespace blr
+
+using namespace blr;
+
+extern "C" {
+
+int blr_rmsnorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, float eps, int dtype, void* out, int64_t ldo,
+                void* stream) {
+  BLR_REQUIRE(rows >= 0 && d > 0 && d % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0, BLR_ERR_ARG,
+              "rmsnorm needs d, ldx and ldo to be multiples of 8 (d = %d)", d);
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  if (rows == 0) return BLR_OK;
+  BLR_REQUIRE(x != nullptr && weight != nullptr && out != nullptr, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15) == 0, BLR_ERR_ARG,
+              "rmsnorm needs 16-byte aligned pointers");
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const uint16_t* wp = static_cast<const uint16_t*>(weight);
+  uint16_t* op = static_cast<uint16_t*>(out);
+  const long long lx = ldx, lo = ldo;
+  if (dtype == BLR_DTYPE_BF16) return launch_pdl(rmsnorm_kernel<true>, dim3((unsigned)rows), dim3(256), 0, st, xp, lx, wp, eps, d, op, lo);
+  return launch_pdl(rmsnorm_kernel<false>, dim3((unsigned)rows), dim3(256), 0, st, xp, lx, wp, eps, d, op, lo);
+}
+
+int blr_rope_append(void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const float* cos_table,
+                    const float* sin_table, const int64_t* pos, int64_t n_seq, int n_tok, int heads, int head_dim, int slots, int dtype,
+                    void* k_cache, void* v_cache, void* stream) {
+  BLR_REQUIRE(n_seq >= 0 && n_tok > 0 && heads > 0 && head_dim > 0 && head_dim % 4 == 0 && slots > 0, BLR_ERR_ARG,
+              "rope_append: head_dim must be a multiple of 4 (got %d)", head_dim);
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  BLR_REQUIRE(ldq % 2 == 0 && ldk % 2 == 0 && ldv % 2 == 0, BLR_ERR_ARG, "rope_append: row strides must be even");
+  if (n_seq == 0) return BLR_OK;
+  BLR_REQUIRE(q && k && v && cos_table && sin_table && pos && k_cache && v_cache, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 3) == 0, BLR_ERR_ARG,
+              "rope_append needs 4-byte aligned pointers");
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint16_t* qp = static_cast<uint16_t*>(q);
+  const uint16_t* kp = static_cast<const uint16_t*>(k);
+  const uint16_t* vp = static_cast<const uint16_t*>(v);
+  uint16_t* kcp = static_cast<uint16_t*>(k_cache);
+  uint16_t* vcp = static_cast<uint16_t*>(v_cache);
+  const long long lq = ldq, lk = ldk, lv = ldv;
+  const long long* pp = reinterpret_cast<const long long*>(pos);
+  const dim3 grid((unsigned)(n_seq * n_tok));
+  if (dtype == BLR_DTYPE_BF16)
+    return launch_pdl(rope_append_kernel<true>, grid, dim3(256), 0, st, qp, lq, kp, lk, vp, lv, cos_table, sin_table, pp, n_tok, heads, head_dim, slots, kcp, vcp);
+  return launch_pdl(rope_append_kernel<false>, grid, dim3(256), 0, st, qp, lq, kp, lk, vp, lv, cos_table, sin_table, pp, n_tok, heads, head_dim, slots, kcp, vcp);
+}
+
+size_t blr_attention_decode_scratch_bytes(int64_t n_seq, int heads, int head_dim, int n_keys) {
+  if (n_seq <= 0 || heads <= 0 || head_dim <= 0 || n_keys <= 0) return 0;
+  return (size_t)n_seq * heads * attn_splits(n_seq, heads, n_keys) * (head_dim + 2) * sizeof(float);
+}
+
+int blr_attention_decode(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, int64_t n_seq, int heads, int head_dim,
+                         int slots, int n_keys, float scale, int dtype, void* out, int64_t ldo, void* scratch, size_t scratch_bytes,
+                         void* stream) {
+  BLR_REQUIRE(n_seq >= 0 && heads > 0 && head_dim >= 8 && head_dim % 8 == 0 && head_dim <= 256 && slots > 0 && n_keys > 0 && n_keys <= slots,
+              BLR_ERR_ARG, "attention_decode: head_dim must be a multiple of 8 up to 256 and 1 <= n_keys <= slots");
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  BLR_REQUIRE(ldq % 2 == 0 && ldo % 2 == 0, BLR_ERR_ARG, "attention_decode: row strides must be even");
+  if (n_seq == 0) return BLR_OK;
+  BLR_REQUIRE(q && k_cache && v_cache && out && scratch, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(scratch_bytes >= blr_attention_decode_scratch_bytes(n_seq, heads, head_dim, n_keys), BLR_ERR_WORKSPACE,
+              "attention_decode: scratch of %zu bytes is too small", scratch_bytes);
+  BLR_REQUIRE(((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0 &&
+                  ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 3) == 0, BLR_ERR_ARG,
+              "attention_decode needs 16-byte aligned caches and 4-byte aligned q and out");
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int ns = attn_splits(n_seq, heads, n_keys), ks = (n_keys + ns - 1) / ns;
+  const size_t smem = (size_t)(head_dim + ks + 16 + 4 * head_dim) * sizeof(float);
+  BLR_REQUIRE(smem <= 200 * 1024, BLR_ERR_UNSUPPORTED, "attention_decode: %d keys per CTA need %zu bytes of shared memory", ks, smem);
+  const uint16_t* qp = static_cast<const uint16_t*>(q);
+  const uint16_t* kp = static_cast<const uint16_t*>(k_cache);
+  const uint16_t* vp = static_cast<const uint16_t*>(v_cache);
+  uint16_t* op = static_cast<uint16_t*>(out);
+  float* part = static_cast<float*>(scratch);
+  const long long lq = ldq, lo = ldo;
+  const dim3 grid((unsigned)ns, (unsigned)heads, (unsigned)n_seq);
+  int rc;
+  if (dtype == BLR_DTYPE_BF16) {
+    if (smem > 48 * 1024) BLR_CUDA_OK(cudaFuncSetAttribute(attn_decode_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rc = launch_pdl(attn_decode_partial_kernel<true>, grid, dim3(kAttnThreads), smem, st, qp, lq, kp, vp, heads, head_dim, slots, n_keys, ks, scale, part);
+    if (rc) return rc;
+    return launch_pdl(attn_decode_combine_kernel<true>, dim3((unsigned)heads, (unsigned)n_seq), dim3(128), 0, st, (const float*)part, ns, head_dim, op, lo, heads);
+  }
+  if (smem > 48 * 1024) BLR_CUDA_OK(cudaFuncSetAttribute(attn_decode_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  rc = launch_pdl(attn_decode_partial_kernel<false>, grid, dim3(kAttnThreads), smem, st, qp, lq, kp, vp, heads, head_dim, slots, n_keys, ks, scale, part);
+  if (rc) return rc;
+  return launch_pdl(attn_decode_combine_kernel<false>, dim3((unsigned)heads, (unsigned)n_seq), dim3(128), 0, st, (const float*)part, ns, head_dim, op, lo, heads);
+}
+
+}  // extern "C"

@@ -135,6 +135,9 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
+        if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.shape[-1] % 8 == 0:
+            from . import ops
+            return ops.rmsnorm(x, self.weight, self.eps)   # one kernel instead of five element-wise ones
         v = x.float()
         v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
         return (v * self.weight.float()).to(x.dtype)
@@ -162,10 +165,28 @@ class LlamaLayer(nn.Module):
     def structured(self):
         return [self.q_proj, self.k_proj, self.v_proj, self.o_proj, self.gate_proj, self.up_proj, self.down_proj]
 
-    def forward(self, x, cos, sin, kc, vc, pos, causal: bool):
-        """x (B, T, d); kc, vc (B, H, S, hd) static cache; pos (T,) int64 cache slots of these tokens.
-        causal: the T tokens are the whole sequence so far (prefill); else they attend to the whole cache."""
+    def _decode_fused(self, x, cos_table, sin_table, kc, vc, pos):
+        """One new token per sequence on the GPU: four structured-linear calls and four small kernels (two norms,
+        rotary embedding + cache append, attention over the cache) instead of some thirty element-wise launches."""
+        from . import ops
+        B, _, d = x.shape
+        h = self.input_layernorm(x)
+        q, k, v = (t.view(B, d) for t in structured_multi([self.q_proj, self.k_proj, self.v_proj], h))
+        ops.rope_append(q, k, v, cos_table, sin_table, pos, kc, vc, 1)
+        a = ops.attention_decode(q, kc, vc)
+        (x,) = structured_multi([self.o_proj], a.view(B, 1, d), residual=x)
+        h = self.post_attention_layernorm(x)
+        g, u = structured_multi([self.gate_proj, self.up_proj], h)
+        (x,) = structured_multi([self.down_proj], g, x_mul=u, residual=x)
+        return x
+
+    def forward(self, x, cos, sin, kc, vc, pos, causal: bool, tables=None):
+        """x (B, T, d); kc, vc (B, H, S, hd) static cache; pos (T,) int64 cache slots of these tokens; cos, sin (T, hd/2)
+        the angles of those slots.  causal: the T tokens are the whole sequence so far (prefill); else they attend to
+        the whole cache.  tables: the full (S, hd/2) cos / sin tables, which selects the fused decode path."""
         B, T, _ = x.shape
+        if tables is not None:
+            return self._decode_fused(x, tables[0], tables[1], kc, vc, pos)
         h = self.input_layernorm(x)
         q, k, v = (t.view(B, T, self.heads, self.hd).transpose(1, 2) for t in
                    structured_multi([self.q_proj, self.k_proj, self.v_proj], h))
@@ -188,6 +209,7 @@ class LlamaDecoder(nn.Module):
         super().__init__()
         g = torch.Generator(device=device if init_on_device else "cpu").manual_seed(seed)
         self.shape, self.method, self.batch, self.cache_len = shape, method, batch, cache_len
+        self.fused_decode = True   # False: the decode step runs the same torch modules as the prefill
         self.embed_tokens = nn.Embedding(shape.vocab, shape.d, device=device, dtype=dtype)
         with torch.no_grad():
             self.embed_tokens.weight.copy_(torch.randn(shape.vocab, shape.d, generator=g, device=g.device).to(dtype))
@@ -209,9 +231,14 @@ class LlamaDecoder(nn.Module):
     def _run(self, ids, pos, causal):
         x = self.embed_tokens(ids)
         B = ids.shape[0]   # a smaller batch than the cache was built for uses the first B sequences' slots
-        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+        # one new token per sequence on the GPU with 16-bit activations takes the fused decode path
+        hd = self.shape.d // self.shape.heads
+        fused = (not causal and ids.shape[1] == 1 and x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and hd % 8 == 0
+                 and self.fused_decode)
+        tables = (self.cos, self.sin) if fused else None
+        cos, sin = (None, None) if fused else (self.cos.index_select(0, pos), self.sin.index_select(0, pos))
         for i, layer in enumerate(self.layers):
-            x = layer(x, cos, sin, self.kcache[i][:B], self.vcache[i][:B], pos, causal)
+            x = layer(x, cos, sin, self.kcache[i][:B], self.vcache[i][:B], pos, causal, tables)
         return self.lm_head(self.norm(x[:, -1]))
 
     @torch.no_grad()

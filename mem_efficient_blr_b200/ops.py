@@ -404,3 +404,51 @@ def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int
         return None
     L.check(rc)
     return outs
+
+
+# ----------------------------------------------------------------------------- decoder kernels around the linears
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x (..., d) 16-bit CUDA tensor -> x * rsqrt(mean(x^2) + eps) * weight, fp32 arithmetic, one rounding (LlamaRMSNorm)."""
+    _need_cuda(x, weight)
+    d = x.shape[-1]
+    x2 = x if x.dim() == 2 else x.reshape(-1, d)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+    L.check(L.load().blr_rmsnorm(x2.data_ptr(), x2.stride(0), x2.shape[0], d, weight.data_ptr(), float(eps), L.dtype_code(x.dtype),
+                                 out.data_ptr(), out.stride(0), L.stream_ptr(x.device)))
+    return out if x.dim() == 2 else out.reshape(*x.shape[:-1], d)
+
+
+def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,
+                pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_tok: int) -> torch.Tensor:
+    """q, k, v (n_seq * n_tok, heads * head_dim) rows (sequence-major); caches (n_seq, heads, slots, head_dim); cos / sin
+    tables (slots, head_dim / 2) fp32; pos (n_tok,) int64 cache slots.  Rotates q in place (returned), writes the
+    rotated k and v into the caches at the tokens' slots."""
+    _need_cuda(q, k_cache, v_cache)
+    n_seq, heads, slots, hd = k_cache.shape
+    assert q.dim() == 2 and q.shape == k.shape == v.shape and q.shape[0] == n_seq * n_tok and q.shape[1] == heads * hd
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and v_cache.shape == k_cache.shape
+    assert cos_table.dtype == torch.float32 and sin_table.dtype == torch.float32 and cos_table.is_contiguous() and sin_table.is_contiguous()
+    assert tuple(cos_table.shape) == (slots, hd // 2) and pos.dtype == torch.int64 and pos.numel() == n_tok and pos.is_cuda
+    L.check(L.load().blr_rope_append(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                                     cos_table.data_ptr(), sin_table.data_ptr(), pos.data_ptr(), n_seq, n_tok, heads, hd, slots,
+                                     L.dtype_code(q.dtype), k_cache.data_ptr(), v_cache.data_ptr(), L.stream_ptr(q.device)))
+    return q
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_keys: int = -1, scale: float = 0.0) -> torch.Tensor:
+    """One query token per sequence over the first n_keys slots of the cache (all by default): q (n_seq, heads * head_dim),
+    caches (n_seq, heads, slots, head_dim) -> (n_seq, heads * head_dim); scale defaults to head_dim ** -0.5."""
+    _need_cuda(q, k_cache, v_cache)
+    n_seq, heads, slots, hd = k_cache.shape
+    assert q.dim() == 2 and tuple(q.shape) == (n_seq, heads * hd) and q.stride(1) == 1 and v_cache.shape == k_cache.shape
+    n_keys = slots if n_keys < 0 else n_keys
+    lib = L.load()
+    out = torch.empty((n_seq, heads * hd), dtype=q.dtype, device=q.device)
+    nbytes = lib.blr_attention_decode_scratch_bytes(n_seq, heads, hd, n_keys)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    L.check(lib.blr_attention_decode(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), n_seq, heads, hd, slots,
+                                     n_keys, float(scale) if scale else hd ** -0.5, L.dtype_code(q.dtype), out.data_ptr(),
+                                     out.stride(0), scratch.data_ptr(), nbytes, L.stream_ptr(q.device)))
+    return out
