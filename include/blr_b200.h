@@ -299,7 +299,8 @@ int blr_rope_append(void* q, int64_t ldq, const void* k, int64_t ldk, const void
                     void* k_cache, void* v_cache, void* stream);
 
 /* Attention of one query token per sequence over the first n_keys slots of the cache:
- * out[seq][head*head_dim + :] = softmax(scale * q . K^T) V, q (n_seq, heads * head_dim) with row stride ldq.
+ * out[seq][head*head_dim + :] = softmax(scale * q . K^T) V, q (n_seq, heads * head_dim) with row stride ldq
+ * (a multiple of 8, q 16-byte aligned); head_dim a power of two from 8 to 256.
  * The keys of a head are split over up to 8 CTAs whose partial results a second kernel merges; `scratch` holds the
  * partials (blr_attention_decode_scratch_bytes). */
 size_t blr_attention_decode_scratch_bytes(int64_t n_seq, int heads, int head_dim, int n_keys);

@@ -125,10 +125,12 @@ __global__ void __launch_bounds__(256) rope_append_kernel(uint16_t* __restrict__
 }
 
 // ------------------------------------------------------------------------------------------------ attention of one token over the cache
-// CTA (split, head, sequence): keys [k0, k0 + ks) of the head's cache.  Phase A: a thread per key, dot product with q
-// (shared memory, fp32) over hd in 16-byte pieces; block maximum and sum of exp.  Phase B: threads own pairs of
-// output dimensions and stride over the keys.  Partial result (unnormalised output, maximum, sum) per split; the
-// combine kernel merges the splits of a head.
+// CTA (split, head, sequence): keys [k0, k0 + ks) of the head's cache.  A key (and value) row of hd 16-bit values is
+// read by hd / 8 neighbouring lanes, 16 bytes each, so a warp's load covers whole rows back to back; a lane keeps its
+// 8 values of q in registers.  Phase A: dot products (reduced over a row's lanes by shuffles), block maximum, exp and
+// sum.  Phase B: every lane accumulates its 8 output dimensions over the keys of its row slot; the slots' sums meet
+// in shared memory.  Partial result (unnormalised output, maximum, sum) per split; the combine kernel merges the
+// splits of a head.  hd / 8 must divide 32 (hd = 8, 16, 32, 64, 128 or 256).
 static constexpr int kAttnThreads = 256;
 
 template <bool BF16>
@@ -136,40 +138,48 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(const
                                                                          const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                                                                          int H, int hd, int slots, int n_keys, int ks, float scale,
                                                                          float* __restrict__ part) {
-  extern __shared__ float sm[];  // q[hd] | p[ks] | red[16] | acc[4][hd]
-  float* qs = sm;
-  float* ps = qs + hd;
-  float* red = ps + ks;
+  extern __shared__ float sm[];  // p[ks] | red[16] | acc[256][8]
+  float* ps = sm;
+  float* red = ps + ((ks + 3) & ~3);  // (keeps the float4 stores into acc[] 16-byte aligned)
   float* accs = red + 16;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int k0 = split * ks, nk = min(ks, n_keys - k0);
-  const uint16_t* kh = kc + (((long long)b * H + h) * slots + k0) * hd;
-  const uint16_t* vh = vc + (((long long)b * H + h) * slots + k0) * hd;
+  const int lpk = hd >> 3, kpw = 32 / lpk, sub = lane / lpk, piece = lane - sub * lpk;
+  const int k0 = split * ks, nk = min(ks, n_keys - k0), kstep = (kAttnThreads / 32) * kpw;
+  const uint16_t* kh = kc + (((long long)b * H + h) * slots + k0) * hd + piece * 8;
+  const uint16_t* vh = vc + (((long long)b * H + h) * slots + k0) * hd + piece * 8;
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  for (int i = tid; i < hd / 2; i += kAttnThreads) {
-    const float2 f = up2<BF16>(*reinterpret_cast<const uint32_t*>(q + (long long)b * ldq + (long long)h * hd + 2 * i));
-    qs[2 * i] = f.x;
-    qs[2 * i + 1] = f.y;
+  float qf[8];
+  {
+    const uint4 v = *reinterpret_cast<const uint4*>(q + (long long)b * ldq + (long long)h * hd + piece * 8);
+    const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = up2<BF16>(ws[i]);
+      qf[2 * i] = f.x * scale;
+      qf[2 * i + 1] = f.y * scale;
+    }
   }
-  __syncthreads();
   // ---- scores
   float m = -3.0e38f;
-  for (int j = tid; j < nk; j += kAttnThreads) {
-    const uint16_t* kr = kh + (long long)j * hd;
+#pragma unroll 4
+  for (int j0 = warp * kpw; j0 < nk; j0 += kstep) {  // warp-uniform bounds
+    const int j = j0 + sub;
     float s = 0.f;
-    for (int p = 0; p < hd; p += 8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(kr + p);
+    if (j < nk) {
+      const uint4 v = *reinterpret_cast<const uint4*>(kh + (long long)j * hd);
       const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = up2<BF16>(ws[i]);
-        s = fmaf(f.x, qs[p + 2 * i], fmaf(f.y, qs[p + 2 * i + 1], s));
+        s = fmaf(f.x, qf[2 * i], fmaf(f.y, qf[2 * i + 1], s));
       }
     }
-    s *= scale;
-    ps[j] = s;
-    m = fmaxf(m, s);
+    for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (j < nk) {
+      if (piece == 0) ps[j] = s;
+      m = fmaxf(m, s);
+    }
   }
   m = warp_maxf(m);
   if (lane == 0) red[warp] = m;
@@ -184,28 +194,37 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(const
     l += p;
   }
   l = warp_sum(l);
-  __syncthreads();  // (everyone has read red[] as maxima)
   if (lane == 0) red[8 + warp] = l;
   __syncthreads();
-  // ---- weighted sum of the values: thread (group g of 4, dimension pair dp)
-  const int npair = hd >> 1, groups = kAttnThreads / npair >= 4 ? 4 : (kAttnThreads / npair > 0 ? kAttnThreads / npair : 1);
-  if (tid < groups * npair) {
-    const int g = tid / npair, dp = tid - g * npair;
-    float ax = 0.f, ay = 0.f;
-    for (int j = g; j < nk; j += groups) {
-      const float2 f = up2<BF16>(*reinterpret_cast<const uint32_t*>(vh + (long long)j * hd + 2 * dp));
+  // ---- weighted sum of the values
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int j0 = warp * kpw; j0 < nk; j0 += kstep) {
+    const int j = j0 + sub;
+    if (j < nk) {
+      const uint4 v = *reinterpret_cast<const uint4*>(vh + (long long)j * hd);
+      const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
       const float p = ps[j];
-      ax = fmaf(p, f.x, ax);
-      ay = fmaf(p, f.y, ay);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = up2<BF16>(ws[i]);
+        acc[2 * i] = fmaf(p, f.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(p, f.y, acc[2 * i + 1]);
+      }
     }
-    accs[g * hd + 2 * dp] = ax;
-    accs[g * hd + 2 * dp + 1] = ay;
+  }
+  // slot (warp, sub) holds a partial sum of all hd dimensions: [slot][hd]
+  {
+    float* a = accs + ((warp * kpw + sub) * hd + piece * 8);
+    *reinterpret_cast<float4*>(a) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(a + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
   __syncthreads();
   float* dst = part + (((long long)b * H + h) * gridDim.x + split) * (hd + 2);
+  const int nslot = (kAttnThreads / 32) * kpw;
   for (int d = tid; d < hd; d += kAttnThreads) {
     float o = accs[d];
-    for (int g = 1; g < groups; ++g) o += accs[g * hd + d];
+    for (int g = 1; g < nslot; ++g) o += accs[g * hd + d];
     dst[d] = o;
   }
   if (tid == 0) {
@@ -321,20 +340,21 @@ size_t blr_attention_decode_scratch_bytes(int64_t n_seq, int heads, int head_dim
 int blr_attention_decode(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, int64_t n_seq, int heads, int head_dim,
                          int slots, int n_keys, float scale, int dtype, void* out, int64_t ldo, void* scratch, size_t scratch_bytes,
                          void* stream) {
-  BLR_REQUIRE(n_seq >= 0 && heads > 0 && head_dim >= 8 && head_dim % 8 == 0 && head_dim <= 256 && slots > 0 && n_keys > 0 && n_keys <= slots,
-              BLR_ERR_ARG, "attention_decode: head_dim must be a multiple of 8 up to 256 and 1 <= n_keys <= slots");
+  BLR_REQUIRE(n_seq >= 0 && heads > 0 && head_dim >= 8 && head_dim <= 256 && (head_dim & (head_dim - 1)) == 0 && slots > 0 && n_keys > 0 &&
+                  n_keys <= slots,
+              BLR_ERR_ARG, "attention_decode: head_dim must be a power of two from 8 to 256 and 1 <= n_keys <= slots");
   BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
-  BLR_REQUIRE(ldq % 2 == 0 && ldo % 2 == 0, BLR_ERR_ARG, "attention_decode: row strides must be even");
+  BLR_REQUIRE(ldq % 8 == 0 && ldo % 2 == 0, BLR_ERR_ARG, "attention_decode: ldq must be a multiple of 8, ldo even");
   if (n_seq == 0) return BLR_OK;
   BLR_REQUIRE(q && k_cache && v_cache && out && scratch, BLR_ERR_ARG, "null pointer");
   BLR_REQUIRE(scratch_bytes >= blr_attention_decode_scratch_bytes(n_seq, heads, head_dim, n_keys), BLR_ERR_WORKSPACE,
               "attention_decode: scratch of %zu bytes is too small", scratch_bytes);
   BLR_REQUIRE(((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0 &&
-                  ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 3) == 0, BLR_ERR_ARG,
-              "attention_decode needs 16-byte aligned caches and 4-byte aligned q and out");
+                  (reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0, BLR_ERR_ARG,
+              "attention_decode needs 16-byte aligned caches and q, 4-byte aligned out");
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int ns = attn_splits(n_seq, heads, n_keys), ks = (n_keys + ns - 1) / ns;
-  const size_t smem = (size_t)(head_dim + ks + 16 + 4 * head_dim) * sizeof(float);
+  const size_t smem = (size_t)(((ks + 3) & ~3) + 16 + kAttnThreads * 8) * sizeof(float);
   BLR_REQUIRE(smem <= 200 * 1024, BLR_ERR_UNSUPPORTED, "attention_decode: %d keys per CTA need %zu bytes of shared memory", ks, smem);
   const uint16_t* qp = static_cast<const uint16_t*>(q);
   const uint16_t* kp = static_cast<const uint16_t*>(k_cache);

@@ -156,6 +156,7 @@ class LlamaLayer(nn.Module):
         super().__init__()
         s, mk = shape, lambda i, o, r: make_linear(method, i, o, shape.b, r, False, device, dtype, generator)
         self.heads, self.hd = s.heads, s.d // s.heads
+        self.fused_attention_max_batch = 16   # measured crossover against torch's scaled_dot_product_attention (2048 keys)
         self.q_proj, self.k_proj, self.v_proj, self.o_proj = (mk(s.d, s.d, s.rank_attn) for _ in range(4))
         self.gate_proj, self.up_proj = mk(s.d, s.ffn, s.rank_mlp), mk(s.d, s.ffn, s.rank_mlp)
         self.down_proj = mk(s.ffn, s.d, s.rank_mlp)
@@ -173,7 +174,10 @@ class LlamaLayer(nn.Module):
         h = self.input_layernorm(x)
         q, k, v = (t.view(B, d) for t in structured_multi([self.q_proj, self.k_proj, self.v_proj], h))
         ops.rope_append(q, k, v, cos_table, sin_table, pos, kc, vc, 1)
-        a = ops.attention_decode(q, kc, vc)
+        if B <= self.fused_attention_max_batch:
+            a = ops.attention_decode(q, kc, vc)
+        else:  # large batches stream gigabytes of cache per layer: torch's flash-decoding kernel is the faster one there
+            a = F.scaled_dot_product_attention(q.view(B, self.heads, 1, self.hd), kc, vc).view(B, d)
         (x,) = structured_multi([self.o_proj], a.view(B, 1, d), residual=x)
         h = self.post_attention_layernorm(x)
         g, u = structured_multi([self.gate_proj, self.up_proj], h)
@@ -233,8 +237,8 @@ class LlamaDecoder(nn.Module):
         B = ids.shape[0]   # a smaller batch than the cache was built for uses the first B sequences' slots
         # one new token per sequence on the GPU with 16-bit activations takes the fused decode path
         hd = self.shape.d // self.shape.heads
-        fused = (not causal and ids.shape[1] == 1 and x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and hd % 8 == 0
-                 and self.fused_decode)
+        fused = (not causal and ids.shape[1] == 1 and x.is_cuda and x.dtype in (torch.float16, torch.bfloat16)
+                 and hd in (8, 16, 32, 64, 128, 256) and self.fused_decode)
         tables = (self.cos, self.sin) if fused else None
         cos, sin = (None, None) if fused else (self.cos.index_select(0, pos), self.sin.index_select(0, pos))
         for i, layer in enumerate(self.layers):
