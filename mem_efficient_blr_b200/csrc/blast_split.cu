@@ -102,6 +102,7 @@ __host__ __device__ static inline BackLayout back_layout(const SplitParams& p) {
   return L;
 }
 
+size_t split_fx_row_bytes(int K, int wbits) { return fx_pitch(K, wbits); }
 size_t split_front_smem(const SplitParams& p) { return front_layout(p).total; }
 size_t split_back_smem(const SplitParams& p) { return back_layout(p).total; }
 
@@ -506,6 +507,55 @@ __device__ __forceinline__ uint32_t fastdiv(uint32_t t, uint32_t d, uint32_t mag
 #define BLR_CK(slot) do { } while (0)
 #endif
 
+// Fixed-point conversion of x once per call (more than 8 tokens, where every front CTA converting all of x itself
+// costs more than this extra launch): CTA c takes rows 16 c .. 16 c + 15 of the b * N (in-block, token) rows, a warp a
+// row, with the front kernel's own staging code, and writes the converted row and its scale to scratch in the layout
+// the front kernel keeps in shared memory.
+template <bool BF16, int WB, bool ACT>
+__global__ void __launch_bounds__(kSplitFrontThreads) blr_blast_fx_kernel(const __grid_constant__ SplitParams p) {
+  extern __shared__ __align__(16) uint8_t fx_smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N, P = p.P, pieces = P >> 3, nrows = p.b * N;
+  const uint32_t pitch = fx_pitch(P, WB);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int r = blockIdx.x * kW + warp;
+  if (r >= nrows) return;
+  const int j = (int)fastdiv((uint32_t)r, (uint32_t)N, p.magic_N), n = r - j * N;
+  const long long off = (long long)n * p.ldx + (long long)j * P;
+  const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x) + off;
+  const uint32_t row_addr = smem_u32(fx_smem) + (uint32_t)warp * pitch;
+#pragma unroll 1
+  for (int pc = lane; pc < pieces; pc += 32) cp_async16(row_addr + (uint32_t)pc * 16u, x + pc * 8);
+  cp_async_wait_all();
+  __syncwarp();
+  if constexpr (ACT) {
+    const uint16_t* xm = reinterpret_cast<const uint16_t*>(p.x_mul) + off;
+#pragma unroll 1
+    for (int pc = lane; pc < pieces; pc += 32) {
+      const uint32_t a = row_addr + (uint32_t)pc * 16u;
+      uint4 v;
+      lds128(a, v.x, v.y, v.z, v.w);
+      silu_mul8<BF16>(v, ld_global_cg_v4(xm + pc * 8));
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+    __syncwarp();
+  }
+  float inv;
+  const float sc = fx_scale(fx_row_absmax<BF16>(row_addr, 0, 32, pieces, lane), inv);
+  fx_row_convert<BF16, WB>(row_addr, 0, 32, pieces, inv, lane);
+  __syncwarp();
+  // the converted row (its padding included: whatever it holds meets weights that TMA filled with zeros) and its scale
+  uint8_t* dst = reinterpret_cast<uint8_t*>(p.xq) + (size_t)r * pitch;
+#pragma unroll 1
+  for (uint32_t o = (uint32_t)lane * 16u; o < pitch; o += 512u) {
+    uint4 v;
+    lds128(row_addr + o, v.x, v.y, v.z, v.w);
+    *reinterpret_cast<uint4*>(dst + o) = v;
+  }
+  if (lane == 0) p.xq_scale[r] = sc;
+}
+
 template <bool BF16, int NT, bool GS, int WB, bool ACT, bool MG>
 __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(const __grid_constant__ SplitParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -588,7 +638,15 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
     const uint16_t* xm = reinterpret_cast<const uint16_t*>(p.x_mul);
     constexpr bool act = ACT;
     const int nrows = nb * N;
-    if constexpr (FX) {
+    if (FX && p.xq != nullptr) {
+      // the rows were converted once for the whole grid by blr_blast_fx_kernel: same layout as here, one linear copy
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.xq);
+      const int total = nrows * (int)(xpitch >> 4);
+#pragma unroll 1
+      for (int i = tid; i < total; i += kSplitFrontThreads) cp_async16(smem_base + L.xs + (uint32_t)i * 16u, src + (size_t)i * 16);
+#pragma unroll 1
+      for (int i = tid; i < nrows; i += kSplitFrontThreads) sx[i] = __ldcg(p.xq_scale + i);
+    } else if constexpr (FX) {
       // raw rows into the fixed-point rows (asynchronously, all of the warp's rows in flight), then in place: the
       // input transform where asked for, the row maximum, the conversion.  The warp's rows come in runs of rr:
       // rows rb .. rb + rr - 1 with rb = rr (warp + 16 it); short rows (one piece per lane) go four at a time.
@@ -1169,13 +1227,14 @@ static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
   const size_t fs = split_front_smem(p), bs = split_back_smem(p);
   BLR_REQUIRE((int)fs <= di.max_smem_optin && (int)bs <= di.max_smem_optin, BLR_ERR_UNSUPPORTED,
               "needs %zu / %zu bytes of shared memory, device offers %d", fs, bs, di.max_smem_optin);
-  auto front = p.act == kSplitActSiluMul ? blr_blast_front_kernel<BF16, NT, GS, WB, true, MG> : blr_blast_front_kernel<BF16, NT, GS, WB, false, MG>;
+  const bool front_act = p.act == kSplitActSiluMul && p.xq == nullptr;
+  auto front = front_act ? blr_blast_front_kernel<BF16, NT, GS, WB, true, MG> : blr_blast_front_kernel<BF16, NT, GS, WB, false, MG>;
   auto back = blr_blast_back_kernel<BF16, NT, GS, WB, MG>;
   {
     int dev = 0;
     BLR_CUDA_OK(cudaGetDevice(&dev));
     static bool configured[2][64] = {};  // per template instance and front variant
-    bool& done = configured[p.act == kSplitActSiluMul][dev & 63];
+    bool& done = configured[front_act][dev & 63];
     if (!done) {
       BLR_CUDA_OK(cudaFuncSetAttribute(front, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
       BLR_CUDA_OK(cudaFuncSetAttribute(back, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem_optin));
@@ -1205,6 +1264,18 @@ static int launch_split_impl(const SplitParams& p, cudaStream_t stream) {
 #ifdef BLR_TIMELINE
   if (getenv("BLR_NO_PDL")) cfg.numAttrs = 0;  // profiling builds only: launches fully serialised
 #endif
+  if constexpr (WB != 16 && !MG) {
+    if (p.xq != nullptr) {
+      // x once for everybody (the input transform happens there, the front kernel then sees plain rows)
+      auto fx = p.act == kSplitActSiluMul ? blr_blast_fx_kernel<BF16, WB, true> : blr_blast_fx_kernel<BF16, WB, false>;
+      const size_t xs = (size_t)kW * fx_pitch(p.P, WB);
+      if (xs > 48 * 1024) BLR_CUDA_OK(cudaFuncSetAttribute(fx, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xs));
+      cfg.gridDim = dim3((unsigned)((p.b * p.N + kW - 1) / kW));
+      cfg.blockDim = dim3(kSplitFrontThreads);
+      cfg.dynamicSmemBytes = xs;
+      BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)fx, args));
+    }
+  }
   cfg.gridDim = dim3(p.R / kSplitRanks, p.nprob);
   cfg.blockDim = dim3(kSplitFrontThreads);
   cfg.dynamicSmemBytes = fs;

@@ -54,6 +54,8 @@ struct alignas(64) SplitParams {
   const void* x;
   const void* x_mul;       // second input of the input transform (same shape and row stride as x), or nullptr
   unsigned* status;        // set to 1 when a wait ran out
+  void* xq;                // scratch for x converted to fixed point once per call (more than 8 tokens, quantised
+  float* xq_scale;         // factors): b * N rows of the front kernel's row pitch, and their scales; nullptr otherwise
   long long ldx, s_i, s_j, s_r;
   int nprob, act;
   int N, b, bo, P, Q, R;
@@ -68,6 +70,8 @@ struct alignas(64) SplitParams {
 #endif
 };
 
+// Bytes of one fixed-point activation row over K contraction indices (the front kernel's row pitch).
+size_t split_fx_row_bytes(int K, int wbits);
 size_t split_front_smem(const SplitParams& p);
 size_t split_back_smem(const SplitParams& p);
 // Enqueues both kernels.  is_bf16 selects the 16-bit type.

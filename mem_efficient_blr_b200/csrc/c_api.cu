@@ -171,7 +171,7 @@ struct SplitLayer {
 static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int64_t N, int dtype, int nprob,
                              const SplitLayer* layers, int u_layout, int v_layout, int wb, int group, int64_t s_i, int64_t s_j,
                              int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* zbase, unsigned* status,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, void* xscratch = nullptr, size_t xscratch_bytes = 0) {
   // Measured against the cluster kernel on the Llama-7B shapes, the two-launch path wins at every token count it
   // takes (1..16) with 16-bit, int8 and packed int4 factors.
   if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > kStreamMaxTokens) return 1;
@@ -202,6 +202,15 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   auto magic = [](int d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d); };
   p.magic_N = magic((int)N); p.magic_rows = magic(p.gpc * 8);
   if ((long long)b * N >= 65536 || (long long)p.gpc * 16 * N >= 65536) return 1;
+  // more than 8 tokens with quantised factors: x is converted to fixed point once, by a launch of its own
+  if (wb != 16 && N > 8 && xscratch != nullptr) {
+    const size_t pitch = split_fx_row_bytes(P, wb);
+    const size_t rows_bytes = align256((size_t)b * N * pitch);
+    if (rows_bytes + (size_t)b * N * 4 <= xscratch_bytes) {
+      p.xq = xscratch;
+      p.xq_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(xscratch) + rows_bytes);
+    }
+  }
   p.nstages = 2;
   const int fs = (int)split_front_smem(p);
   if (fs > di.max_smem_optin) return 1;
@@ -246,7 +255,8 @@ static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const v
   if (u_bits != v_bits) return 1;
   const SplitLayer l = {U, u_scale, V, v_scale, S, nullptr, nullptr, out, ldo, 0};
   return split_blast_multi(x, ldx, nullptr, kSplitActNone, N, dtype, 1, &l, u_layout, v_layout, u_bits, group, s_i, s_j, s_r, b, bo,
-                           P, Q, R, act8, w.region_b, w.counters + 255, stream);
+                           P, Q, R, act8, w.region_b, w.counters + 255, stream, w.region_a,
+                           (size_t)(static_cast<uint8_t*>(w.region_b) - static_cast<uint8_t*>(w.region_a)));
 }
 
 // Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
@@ -615,10 +625,11 @@ int blr_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int6
   if (rc) return rc;
   rc = split_blast_multi(x, ldx, x_mul, act == BLR_ACT_SILU_MUL ? kSplitActSiluMul : kSplitActNone, N, dtype, n_problems, layers,
                          BLR_W_KMAJOR, BLR_W_KMAJOR, bits, group, s_i, s_j, s_r, b, b, P, Q, R, 0, w.region_b, w.counters + 255,
-                         static_cast<cudaStream_t>(stream));
+                         static_cast<cudaStream_t>(stream), w.region_a,
+                         (size_t)(static_cast<uint8_t*>(w.region_b) - static_cast<uint8_t*>(w.region_a)));
   BLR_REQUIRE(rc != 1, BLR_ERR_UNSUPPORTED,
-              "the fused call serves up to 8 tokens with 16-bit factors and 4 with quantised ones, contraction-contiguous "
-              "factors and shapes the two-launch path takes: run the layers one by one instead");
+              "the fused call serves 1..16 tokens, contraction-contiguous factors and shapes the two-launch path takes: run "
+              "the layers one by one instead");
   return rc;
 }
 
