@@ -202,8 +202,9 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   auto magic = [](int d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d); };
   p.magic_N = magic((int)N); p.magic_rows = magic(p.gpc * 8);
   if ((long long)b * N >= 65536 || (long long)p.gpc * 16 * N >= 65536) return 1;
-  // more than 4 tokens with quantised factors: x is converted to fixed point once, by a launch of its own
-  if (wb != 16 && N > 4 && xscratch != nullptr) {
+  // quantised factors, more than 4 tokens or an input transform: x is transformed and converted to fixed point once,
+  // by a launch of its own, instead of by every front CTA
+  if (wb != 16 && (N > 4 || act != kSplitActNone) && xscratch != nullptr) {
     const size_t pitch = split_fx_row_bytes(P, wb);
     const size_t rows_bytes = align256((size_t)b * N * pitch);
     if (rows_bytes + (size_t)b * N * 4 <= xscratch_bytes) {
