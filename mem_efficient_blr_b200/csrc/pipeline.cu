@@ -130,16 +130,19 @@ static int run_couple_generic(const void* y, const void* S, int64_t s_i, int64_t
 // than the coupling itself: a block takes 64 consecutive ranks, stages S[i][j][64 ranks] for all pairs of blocks in
 // shared memory once, and walks its share of the tokens; a thread owns 8 ranks of one token, holds the b vectors
 // y_j in registers and produces the b_out vectors z_i.  y, z: [block][token][R], S with unit rank stride.
+// With few tokens the out-blocks are shared out over grid.y as well (i_per per block), so that the grid still fills
+// the GPU: every such block re-reads the y vectors (from L2) but stages and applies only its own rows of S.
 template <typename T, int B>
 __global__ void __launch_bounds__(256) blast_couple_tile_kernel(const T* __restrict__ y, const T* __restrict__ S, long long s_i,
                                                                 long long s_j, T* __restrict__ z, int b_out, long long N, int R,
-                                                                int round_z, int tok_groups) {
+                                                                int round_z, int tok_groups, int i_per) {
   extern __shared__ __align__(16) unsigned char couple_smem[];
-  T* sS = reinterpret_cast<T*>(couple_smem);  // [b_out][B][64]
+  T* sS = reinterpret_cast<T*>(couple_smem);  // [i_per][B][64]
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int rt = blockIdx.x / tok_groups, tg = blockIdx.x - rt * tok_groups, r0 = rt * 64;
-  for (int e = threadIdx.x; e < b_out * B * 8; e += 256) {
-    const int ij = e >> 3, v = e & 7, i = ij / B, j = ij - i * B;
+  const int i_lo = blockIdx.y * i_per, i_n = min(i_per, b_out - i_lo);
+  for (int e = threadIdx.x; e < i_n * B * 8; e += 256) {
+    const int ij = e >> 3, v = e & 7, il = ij / B, j = ij - il * B, i = i_lo + il;
     uint4 w = make_uint4(0, 0, 0, 0);
     if (r0 + v * 8 < R) w = __ldg(reinterpret_cast<const uint4*>(S + i * s_i + j * s_j + r0 + v * 8));
     reinterpret_cast<uint4*>(sS)[e] = w;
@@ -158,11 +161,12 @@ __global__ void __launch_bounds__(256) blast_couple_tile_kernel(const T* __restr
 #pragma unroll
       for (int k = 0; k < 8; ++k) yv[j][k] = (float)h[k];
     }
-    for (int i = 0; i < b_out; ++i) {
+    for (int il = 0; il < i_n; ++il) {
+      const int i = i_lo + il;
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < B; ++j) {
-        const uint4 w = reinterpret_cast<const uint4*>(sS)[(i * B + j) * 8 + v];
+        const uint4 w = reinterpret_cast<const uint4*>(sS)[(il * B + j) * 8 + v];
         const T* h = reinterpret_cast<const T*>(&w);
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = fmaf((float)h[k], yv[j][k], acc[k]);
@@ -182,9 +186,15 @@ static int run_couple_tile(const void* y, const void* S, int64_t s_i, int64_t s_
   int tok_groups = (int)((N + 31) / 32);
   const int want = (2 * 148 + r_tiles - 1) / r_tiles;  // about two blocks per SM
   if (tok_groups > want) tok_groups = want;
-  const size_t smem = (size_t)b_out * b * 64 * sizeof(T);
+  // too few blocks for the GPU: share the out-blocks out as well (at least two per block)
+  int i_groups = want / tok_groups;
+  if (i_groups > b_out / 2) i_groups = b_out / 2;
+  if (i_groups < 1) i_groups = 1;
+  int i_per = (b_out + i_groups - 1) / i_groups;
+  i_groups = (b_out + i_per - 1) / i_per;
+  const size_t smem = (size_t)i_per * b * 64 * sizeof(T);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(r_tiles * tok_groups));
+  cfg.gridDim = dim3((unsigned)(r_tiles * tok_groups), (unsigned)i_groups);
   cfg.blockDim = dim3(256);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -197,7 +207,7 @@ static int run_couple_tile(const void* y, const void* S, int64_t s_i, int64_t s_
   const T* Sp = static_cast<const T*>(S);
   T* zp = static_cast<T*>(z);
   long long si = s_i, sj = s_j, n = N;
-  void* args[] = {&yp, &Sp, &si, &sj, &zp, &b_out, &n, &R, &round_z, &tok_groups};
+  void* args[] = {&yp, &Sp, &si, &sj, &zp, &b_out, &n, &R, &round_z, &tok_groups, &i_per};
   const void* kern = nullptr;
   switch (b) {
     case 2: kern = (const void*)blast_couple_tile_kernel<T, 2>; break;
