@@ -171,7 +171,8 @@ struct SplitLayer {
 static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int64_t N, int dtype, int nprob,
                              const SplitLayer* layers, int u_layout, int v_layout, int wb, int group, int64_t s_i, int64_t s_j,
                              int64_t s_r, int b, int bo, int P, int Q, int R, int act8, void* zbase, unsigned* status,
-                             cudaStream_t stream, void* xscratch = nullptr, size_t xscratch_bytes = 0) {
+                             cudaStream_t stream, void* xscratch = nullptr, size_t xscratch_bytes = 0,
+                             bool may_decline = false) {
   // Measured against the cluster kernel on the Llama-7B shapes, the two-launch path wins at every token count it
   // takes (1..16) with 16-bit, int8 and packed int4 factors.
   if (g_decode_path.load(std::memory_order_relaxed) != 0 || N > kStreamMaxTokens) return 1;
@@ -215,6 +216,14 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   p.nstages = 2;
   const int fs = (int)split_front_smem(p);
   if (fs > di.max_smem_optin) return 1;
+  // A front grid that needs two waves (ranks beyond 8 x SMs x the CTAs that fit an SM: rank 1488 with many tokens or
+  // long input blocks) loses to the cluster kernel from 4 tokens on (measured: int8 down projection, 4 tokens, 20.5 vs
+  // 15.8 us; fp16 gate projection, 16 tokens, 27.6 vs 24.8); callers that have that alternative take it.
+  if (may_decline && N >= 4) {
+    int per_sm = (227 * 1024) / fs;
+    if (per_sm < 1) per_sm = 1;
+    if ((long long)(R / kSplitRanks) * nprob > (long long)di.sm_count * per_sm) return 1;
+  }
   // ring of the back kernel: the CTA's whole share if it fits beside a front CTA of the next call on the same SM
   // (228 KB per SM, 1 KB of it reserved per CTA), else what fits, but never fewer than 4 stages
   const int nseg = (p.nch1 + kSplitStageChunks - 1) / kSplitStageChunks, total = p.gpc * nseg;
@@ -257,7 +266,8 @@ static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const v
   const SplitLayer l = {U, u_scale, V, v_scale, S, nullptr, nullptr, out, ldo, 0};
   return split_blast_multi(x, ldx, nullptr, kSplitActNone, N, dtype, 1, &l, u_layout, v_layout, u_bits, group, s_i, s_j, s_r, b, bo,
                            P, Q, R, act8, w.region_b, w.counters + 255, stream, w.region_a,
-                           (size_t)(static_cast<uint8_t*>(w.region_b) - static_cast<uint8_t*>(w.region_a)));
+                           (size_t)(static_cast<uint8_t*>(w.region_b) - static_cast<uint8_t*>(w.region_a)),
+                           /*may_decline=*/g_decode_path.load(std::memory_order_relaxed) == 0);
 }
 
 // Cluster kernel (blast_cluster.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
