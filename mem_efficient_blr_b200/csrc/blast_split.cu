@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   constexpr int wbits = WB, abox = 16 / WB;
   constexpr bool FX = WB != 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int N = p.N, nb = p.b, bo = p.bo, nch = p.nch0, R = p.R;
+  const int N = p.N, nb = p.b, bo = p.z_shared ? 1 : p.bo, nch = p.nch0, R = p.R;  // (one z for every out-block: see z_shared)
   const int nbx = nch * abox;
   const int r0 = blockIdx.x * kSplitRanks;
   const SplitProblem& q = p.pr[blockIdx.y];
@@ -1006,7 +1006,7 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
 #endif
   // ---- z of this out-block
   {
-    const uint16_t* z = reinterpret_cast<const uint16_t*>(q.z) + (long long)blk * N * R;
+    const uint16_t* z = reinterpret_cast<const uint16_t*>(q.z) + (p.z_shared ? 0ll : (long long)blk * N * R);
     if constexpr (FX) {
       // Every token row is shared out over wpr = 16 / N warps (at least one): each thread takes its 16-byte pieces,
       // the warps' maxima meet in shared memory, then every thread converts its own pieces.

@@ -61,6 +61,7 @@ struct alignas(64) SplitParams {
   int N, b, bo, P, Q, R;
   int wbits, group;
   int round_y, round_z;
+  int z_shared;            // no coupling factors (S == nullptr, low rank as BLAST): z is the same for every out-block, kept once
   int nch0, nch1;          // 128-byte chunks per row of V / of U
   int cpb, gpc;            // back kernel: CTAs per out-block, 16-row groups per CTA
   int nstages;             // back kernel: ring stages

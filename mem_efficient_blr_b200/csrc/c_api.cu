@@ -164,6 +164,7 @@ struct SplitLayer {
   const void *U, *u_scale, *V, *v_scale, *S, *bias, *residual;
   void* out;
   int64_t ldo, ldr;
+  int64_t v_row = 0, v_blk = 0;  // V as column blocks of a wider matrix: elements between rows / blocks (0: packed)
 };
 
 // Two-launch path (blast_split.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
@@ -191,6 +192,7 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   p.ldx = ldx; p.s_i = s_i; p.s_j = s_j; p.s_r = s_r;
   p.N = (int)N; p.b = b; p.bo = bo; p.P = P; p.Q = Q; p.R = R;
   p.wbits = wb; p.group = group; p.round_y = act8; p.round_z = act8;
+  p.z_shared = (nprob == 1 && layers[0].S == nullptr) ? 1 : 0;
   p.nch0 = (int)((kbV + 127) / 128);
   p.nch1 = (int)((kbU + 127) / 128);
   // back kernel: every CTA a run of 16-row groups of one out-block, about one CTA per SM over all layers of the call
@@ -244,7 +246,8 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
     q.out = l.out; q.ldo = l.ldo; q.bias = l.bias; q.residual = l.residual; q.ldr = l.ldr;
     {
       const uint64_t dims[3] = {wb == 16 ? (uint64_t)P : (uint64_t)kbV, (uint64_t)R, (uint64_t)b};
-      const uint64_t str[2] = {(uint64_t)kbV, (uint64_t)R * kbV};
+      const uint64_t esz = wb == 16 ? 2 : 1;  // (strided views only come with 16-bit factors)
+      const uint64_t str[2] = {l.v_row ? (uint64_t)l.v_row * esz : (uint64_t)kbV, l.v_blk ? (uint64_t)l.v_blk * esz : (uint64_t)R * kbV};
       const uint32_t box[3] = {inner_box, (uint32_t)kSplitRanks, (uint32_t)b};
       if ((rc = encode_tmap_3d(&q.tmV, dt, l.V, dims, str, box, Swz::B128))) return rc;
     }
@@ -847,6 +850,16 @@ int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
       if (I % (bb * 8) != 0 || O % (bb * 8) != 0) continue;
       const int Pb = I / bb, Qb = O / bb;
       const bool vk = v_layout == BLR_W_KMAJOR, uk = u_layout == BLR_W_KMAJOR;
+      if (vk && uk && (int64_t)Pb * 2 % 16 == 0) {
+        // the two-launch path: z is the same for every out-block and is kept once (the workspace holds N x R values)
+        SplitLayer l = {U, nullptr, V, nullptr, nullptr, nullptr, nullptr, out, ldo, 0};
+        l.v_row = I;
+        l.v_blk = Pb;
+        rc = split_blast_multi(x, ldx, nullptr, kSplitActNone, N, dtype, 1, &l, BLR_W_KMAJOR, BLR_W_KMAJOR, 16, 0, 0, 0, 0, bb, bb,
+                               Pb, Qb, R, 0, w.region_b, w.counters + 255, static_cast<cudaStream_t>(stream), nullptr, 0,
+                               /*may_decline=*/true);
+        if (rc <= 0) return rc;
+      }
       rc = cluster_blast(x, ldx, N, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, nullptr, 0, 0, 0, bb, bb, Pb,
                          Qb, R, 0, out, ldo, w, static_cast<cudaStream_t>(stream), vk ? I : 0, vk ? Pb : 0, uk ? 0 : O,
                          uk ? 0 : Qb);
