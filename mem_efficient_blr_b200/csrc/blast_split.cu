@@ -849,9 +849,23 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
       __syncthreads();
     }
   }
+  // ---- Monarch: no coupling; row m of in-block k goes to position k * per + jj of z_l, with (l, jj) = (m / per, m % per)
+  // for grouped rows or (m % b, m / b) for the reference's torch layout (the permutation between the two factors)
+  if (p.monarch) {
+    const int per = p.mon_per;
+#pragma unroll 1
+    for (int e = tid; e < nb * N * 8; e += kSplitFrontThreads) {
+      const int gg = e & 7, t = e >> 3, k = (int)fastdiv((uint32_t)t, (uint32_t)N, p.magic_N), n = t - k * N;
+      const int m = r0 + gg;
+      const int l = p.mon_torch ? m % nb : m / per, jj = p.mon_torch ? m / nb : m - l * per;
+      float a = ybuf[t * 8 + gg];
+      if (p.round_z) a = round_clamp_i8(a);
+      store16<BF16>(q.z, ((long long)l * N + n) * R + (long long)k * per + jj, a);
+    }
+  }
   // ---- z[i][n][r] = sum_j S[i][j][r] y[j][n][r].  Few points (fewer than threads): a thread per point with four
   // partial sums (terms j = q mod 4), added in a fixed order.
-  if (bo * N * 8 <= kSplitFrontThreads / 2) {
+  else if (bo * N * 8 <= kSplitFrontThreads / 2) {
     const uint32_t pitch = (uint32_t)nb * 16u + 16u;
 #pragma unroll 1
     for (int e = tid; e < bo * N * 8; e += kSplitFrontThreads) {
@@ -1195,6 +1209,12 @@ __global__ void __launch_bounds__(kSplitBackThreads, 2) blr_blast_back_kernel(co
       if constexpr (FX) {
         s0 *= sz[n];
         s1 *= sz[n];
+      }
+      if (p.out_interleaved) {  // Monarch's interleaved features: row s of block l is feature s * b + l
+        const long long o0 = (long long)n * q.ldo + (long long)qq * p.bo + blk;
+        store16<BF16>(q.out, o0, s0);
+        if (qq + 1 < Q) store16<BF16>(q.out, o0 + p.bo, s1);
+        continue;
       }
       const long long col = (long long)blk * Q + qq, o = (long long)n * q.ldo + col;
       const bool two = qq + 1 < Q;

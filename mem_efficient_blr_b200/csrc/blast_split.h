@@ -61,6 +61,8 @@ struct alignas(64) SplitParams {
   int N, b, bo, P, Q, R;
   int wbits, group;
   int round_y, round_z;
+  int monarch, mon_per, mon_torch;  // Monarch: no coupling, z_l[k * per + jj] = y_k[m]; rows m in the torch order (jj * b + l) or grouped (l * per + jj)
+  int out_interleaved;     // output feature of row s of out-block l: s * b + l instead of l * Q + s
   int z_shared;            // no coupling factors (S == nullptr, low rank as BLAST): z is the same for every out-block, kept once
   int nch0, nch1;          // 128-byte chunks per row of V / of U
   int cpb, gpc;            // back kernel: CTAs per out-block, 16-row groups per CTA

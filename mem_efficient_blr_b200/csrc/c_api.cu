@@ -165,6 +165,7 @@ struct SplitLayer {
   void* out;
   int64_t ldo, ldr;
   int64_t v_row = 0, v_blk = 0;  // V as column blocks of a wider matrix: elements between rows / blocks (0: packed)
+  int monarch = 0, mon_torch = 0, out_interleaved = 0;  // Monarch on the same kernels: permuted hand-over instead of coupling
 };
 
 // Two-launch path (blast_split.cu): returns 0 when launched, 1 when the call does not fit it, < 0 on error.
@@ -192,7 +193,8 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   p.ldx = ldx; p.s_i = s_i; p.s_j = s_j; p.s_r = s_r;
   p.N = (int)N; p.b = b; p.bo = bo; p.P = P; p.Q = Q; p.R = R;
   p.wbits = wb; p.group = group; p.round_y = act8; p.round_z = act8;
-  p.z_shared = (nprob == 1 && layers[0].S == nullptr) ? 1 : 0;
+  p.monarch = layers[0].monarch; p.mon_torch = layers[0].mon_torch; p.mon_per = R / b; p.out_interleaved = layers[0].out_interleaved;
+  p.z_shared = (nprob == 1 && layers[0].S == nullptr && !p.monarch) ? 1 : 0;
   p.nch0 = (int)((kbV + 127) / 128);
   p.nch1 = (int)((kbU + 127) / 128);
   // back kernel: every CTA a run of 16-row groups of one out-block, about one CTA per SM over all layers of the call
@@ -811,6 +813,17 @@ int blr_monarch(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const v
   const long long zplane = (long long)N * rank;
   const int grouped = w1_cols == BLR_MONARCH_COLS_GROUPED;
   if (N <= kStreamMaxTokens) {
+    if (w1_layout == BLR_W_KMAJOR && w2_layout == BLR_W_KMAJOR) {
+      // the two-launch path of BLAST: the first factor's blocks as V, the second's as U, the permutation in the hand-over
+      SplitLayer l = {w2, nullptr, w1, nullptr, nullptr, nullptr, nullptr, out, ldo, 0};
+      l.monarch = 1;
+      l.mon_torch = grouped ? 0 : 1;
+      l.out_interleaved = out_order == BLR_OUT_INTERLEAVED ? 1 : 0;
+      rc = split_blast_multi(x, ldx, nullptr, kSplitActNone, N, dtype, 1, &l, BLR_W_KMAJOR, BLR_W_KMAJOR, 16, 0, 0, 0, 0, b, b, P, Qs,
+                             rank, 0, w.region_b, w.counters + 255, static_cast<cudaStream_t>(stream), nullptr, 0,
+                             /*may_decline=*/true);
+      if (rc <= 0) return rc;
+    }
     rc = cluster_monarch(x, ldx, N, dtype, w1, w1_layout, grouped, w2, w2_layout, b, P, rank, Qs, out_order == BLR_OUT_INTERLEAVED,
                          out, ldo, w, static_cast<cudaStream_t>(stream));
     if (rc <= 0) return rc;  // 1: not applicable -> grid-wide streaming kernel
