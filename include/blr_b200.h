@@ -18,8 +18,8 @@
  *     layouts of the reference's Triton entry points).
  *   - n_tokens = 0 is valid for the 16-bit and quantised entry points: they return 0 without touching a pointer.
  *   - Return value: 0 on success, a negative BLR_ERR_* code otherwise; blr_last_error() has the text.
- *     Token counts up to 16 run one weight-streaming kernel (BLAST and low-rank, and Monarch on up to 8 tokens:
- *     a kernel of thread-block clusters, one cluster per slice of the rank index); larger counts run the
+ *     Token counts up to 16 run weight-streaming kernels (contraction-contiguous factors: a pair of dependent
+ *     launches; other layouts: a kernel of thread-block clusters or a grid-wide one); larger counts run the
  *     tensor-core pipeline.
  */
 #ifndef BLR_B200_H_
@@ -66,9 +66,10 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int blr_version(void);
 
-/* Test aid: which kernel serves 1..16 tokens.  0: automatic (BLAST with contraction-contiguous factors: the two-launch
- * path; other BLAST layouts, low-rank, Monarch on up to 8 tokens: the cluster kernel; the rest: the grid-wide streaming
- * kernel).  1: the grid-wide streaming kernel for everything.  2: automatic without the two-launch path.
+/* Test aid: which kernel serves 1..16 tokens.  0: automatic (BLAST, low-rank and Monarch with contraction-contiguous
+ * factors: the two-launch path; other layouts, and Monarch on up to 8 tokens: the cluster kernel; the rest: the
+ * grid-wide streaming kernel).  1: the grid-wide streaming kernel for everything.  2: automatic without the
+ * two-launch path.
  * Process-wide (an atomic). No reference counterpart. */
 int blr_debug_decode_path(int which);
 

@@ -121,7 +121,7 @@ def blast_multi_torch_layout(x, layers, x_mul=None, biases=None, residuals=None)
     """Several BLAST layers on one input, torch layouts: layers = [(U (b,Q,R), Vt (b,R,P), S (b,b,R)), ...] with equal
     shapes.  Optional: x_mul - the input becomes silu(x) * x_mul (a down projection fed with the gate and up results);
     biases[i] (O,) and residuals[i] (..., O) are added to layer i's result.  Returns the list of outputs.
-    At decode sizes (up to 8 tokens) everything is one pair of launches (blr_blast_multi: no counterpart in the
+    At decode sizes (up to 16 tokens) everything is one pair of launches (blr_blast_multi: no counterpart in the
     reference, which calls one operator per layer and separate torch kernels for the rest, models/wrappers.py:171-177);
     otherwise the layers run one by one with the same arithmetic."""
     U0, Vt0, S0 = layers[0]
