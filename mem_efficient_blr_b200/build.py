@@ -80,7 +80,9 @@ def build_torch_ext(force: bool = False, verbose: bool = False) -> str:
     libblr_b200.so; the result is copied next to it.  Needs libblr_b200.so built first."""
     if not force and not ext_needs_build():
         return EXT
+    import ctypes
     from torch.utils import cpp_extension as ce
+    ctypes.CDLL(LIB, mode=ctypes.RTLD_GLOBAL)  # the extension is loaded right after it is built and links against this library
     bdir = os.path.join(HERE, "build", "torch_ext")
     os.makedirs(bdir, exist_ok=True)
     ce.load(name="_blr_torch", sources=[os.path.join(CSRC, "torch_ext.cpp")], extra_cflags=["-O2", "-std=c++17"],
