@@ -45,14 +45,14 @@ L2_BYTES = 126 * 2 ** 20
 PASSES_PER_STEP = 25
 # Which kernels serve a point of the headline workload (the library's dispatch for this layer): up to 4 tokens the
 # two-launch path (two kernels per call), above it the cluster kernel (one).
-GROUPS = {"two_launch": ("blr_blast_front_kernel+blr_blast_back_kernel (+blr_blast_fx_kernel above 4 tokens)", 2),
+GROUPS = {"two_launch": ("blr_blast_front_kernel+blr_blast_back_kernel (+blr_blast_fx_kernel above 2 tokens)", 2),
           "cluster": ("blr_blast_cluster_kernel", 1)}
 
 
 def launches_of(bits: int, n: int) -> int:
-    """Kernel launches of one call of a point: front + back, and above 4 tokens the conversion of x ahead of them
+    """Kernel launches of one call of a point: front + back, and above 2 tokens the conversion of x ahead of them
     (blr_blast_fx_kernel)."""
-    return 3 if n > 4 else 2
+    return 3 if n > 2 else 2
 
 
 def group_of(bits: int, n: int) -> str:

@@ -73,7 +73,7 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
 
 def blast_wq_multi(x, layers, bits: int, group: int = 0, x_mul=None, biases=None, residuals=None):
     """blast_wq for several layers on one input: layers = [(Uq, u_scale, Vq, v_scale, S), ...] with equal shapes; the
-    options of blast_kernels.blast_multi_torch_layout.  One pair of launches up to 16 tokens (preceded above 4 tokens, or
+    options of blast_kernels.blast_multi_torch_layout.  One pair of launches up to 16 tokens (preceded above 2 tokens, or
     with x_mul, by one launch that converts x to fixed point once), else layer by layer."""
     assert bits in (8, 4)
     per = 1 if bits == 8 else 2

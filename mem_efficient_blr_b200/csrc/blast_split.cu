@@ -507,7 +507,7 @@ __device__ __forceinline__ uint32_t fastdiv(uint32_t t, uint32_t d, uint32_t mag
 #define BLR_CK(slot) do { } while (0)
 #endif
 
-// Fixed-point conversion of x once per call (more than 4 tokens, or an input transform: where every front CTA converting all of x itself
+// Fixed-point conversion of x once per call (more than 2 tokens, or an input transform: where every front CTA converting all of x itself
 // costs more than this extra launch): CTA c takes rows 16 c .. 16 c + 15 of the b * N (in-block, token) rows, a warp a
 // row, with the front kernel's own staging code, and writes the converted row and its scale to scratch in the layout
 // the front kernel keeps in shared memory.

@@ -54,7 +54,7 @@ struct alignas(64) SplitParams {
   const void* x;
   const void* x_mul;       // second input of the input transform (same shape and row stride as x), or nullptr
   unsigned* status;        // set to 1 when a wait ran out
-  void* xq;                // scratch for x converted to fixed point once per call (more than 4 tokens, quantised
+  void* xq;                // scratch for x converted to fixed point once per call (more than 2 tokens, quantised
   float* xq_scale;         // factors): b * N rows of the front kernel's row pitch, and their scales; nullptr otherwise
   long long ldx, s_i, s_j, s_r;
   int nprob, act;

@@ -159,6 +159,11 @@ static constexpr int kSubsliceMinTokens = 4;
 // 0: automatic, 1: grid-wide streaming kernel only, 2: no two-launch path (cluster kernel where it applies)
 static std::atomic<int> g_decode_path{0};
 
+// Set around the kernels of a host-buffer call: such calls are bound by the rate at which the host can enqueue work (two
+// copies, event operations and the launches per call), not by the GPU, so the extra launch that converts x once per call
+// costs them more than the conversion it saves.
+static thread_local bool t_host_call = false;
+
 // One layer of a two-launch call (all layers of a call share x, the shapes and the strides of S).
 struct SplitLayer {
   const void *U, *u_scale, *V, *v_scale, *S, *bias, *residual;
@@ -207,9 +212,9 @@ static int split_blast_multi(const void* x, int64_t ldx, const void* x_mul, int 
   auto magic = [](int d) { return d <= 1 ? 0u : (unsigned)((0x100000000ull + (unsigned)d - 1) / (unsigned)d); };
   p.magic_N = magic((int)N); p.magic_rows = magic(p.gpc * 8);
   if ((long long)b * N >= 65536 || (long long)p.gpc * 16 * N >= 65536) return 1;
-  // quantised factors, more than 4 tokens or an input transform: x is transformed and converted to fixed point once,
+  // quantised factors, more than 2 tokens or an input transform: x is transformed and converted to fixed point once,
   // by a launch of its own, instead of by every front CTA
-  if (wb != 16 && (N > 4 || act != kSplitActNone) && xscratch != nullptr) {
+  if (wb != 16 && (N > 2 || act != kSplitActNone) && xscratch != nullptr) {
     const size_t pitch = split_fx_row_bytes(P, wb);
     const size_t rows_bytes = align256((size_t)b * N * pitch);
     if (rows_bytes + (size_t)b * N * 4 <= xscratch_bytes) {
@@ -270,7 +275,7 @@ static int split_blast(const void* x, int64_t ldx, int64_t N, int dtype, const v
   if (u_bits != v_bits) return 1;
   const SplitLayer l = {U, u_scale, V, v_scale, S, nullptr, nullptr, out, ldo, 0};
   return split_blast_multi(x, ldx, nullptr, kSplitActNone, N, dtype, 1, &l, u_layout, v_layout, u_bits, group, s_i, s_j, s_r, b, bo,
-                           P, Q, R, act8, w.region_b, w.counters + 255, stream, w.region_a,
+                           P, Q, R, act8, w.region_b, w.counters + 255, stream, t_host_call ? nullptr : w.region_a,
                            (size_t)(static_cast<uint8_t*>(w.region_b) - static_cast<uint8_t*>(w.region_a)),
                            /*may_decline=*/g_decode_path.load(std::memory_order_relaxed) == 0);
 }
@@ -787,8 +792,10 @@ int blr_blast_wq_host(const void* x_host, int64_t ldx, int64_t n_tokens, int dty
   HostCall hc;
   int rc = stage_in(x_host, ldx, n_tokens, (int64_t)b * P, (int64_t)b * Q, staging, staging_bytes, st, &hc);
   if (rc) return rc;
+  t_host_call = true;
   rc = blr_blast_wq(hc.x_dev, (int64_t)b * P, n_tokens, dtype, Uq, u_scale, Vq, v_scale, S, s_i, s_j, s_r, bits, group, b, P, Q, R,
                     hc.out_dev, (int64_t)b * Q, ws, ws_bytes, stream);
+  t_host_call = false;
   if (rc) return rc;
   return stage_out(out_host, ldo, n_tokens, (int64_t)b * Q, st, &hc);
 }
