@@ -80,7 +80,7 @@ __host__ __device__ static inline FrontLayout front_layout(const SplitParams& p)
   L.vs = o; o += (uint32_t)p.b * 8 * 4;                   // per-channel scales of the slice's rows
   L.ypart = o; o += sl > 1 ? (uint32_t)p.b * sl * 8 * np * 4 : 0u;  // [in-block][sharing warp][8 ranks][np tokens] fp32
   L.ybuf = o; o += (uint32_t)p.b * p.N * 8 * 4;           // [in-block][token][8 ranks] fp32
-  L.bar = o; o += 16;
+  L.bar = o; o += 32;                                     // barrier of the weights, abort flag, barrier of the bulk copy of x
   L.total = o + 1024;  // room to align the base to 1 KiB
   return L;
 }
@@ -581,9 +581,11 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   long long tck = 0;
 #endif
 
+  const uint32_t xbar = bar + 16;
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar, 1);
+    mbar_init(xbar, 1);
     mbar_init_fence();
   }
   BLR_TL(0);
@@ -633,6 +635,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   tck = clock64();
 #endif
   // ---- x, all of it, one (in-block, token) row per warp and turn
+  bool x_bulk = false;
   {
     const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
     const uint16_t* xm = reinterpret_cast<const uint16_t*>(p.x_mul);
@@ -641,9 +644,19 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
     if (FX && p.xq != nullptr) {
       // the rows were converted once for the whole grid by blr_blast_fx_kernel: same layout as here, one linear copy
       const uint8_t* src = reinterpret_cast<const uint8_t*>(p.xq);
-      const int total = nrows * (int)(xpitch >> 4);
+      const uint32_t bytes = (uint32_t)nrows * xpitch;
+      x_bulk = bytes < (1u << 20);  // (an mbarrier counts at most 2^20 - 1 bytes per phase)
+      if (x_bulk) {
+        if (tid == 0) {  // a few bulk copies by one thread instead of thousands of 16-byte ones by all
+          mbar_arrive_expect_tx(xbar, bytes);
 #pragma unroll 1
-      for (int i = tid; i < total; i += kSplitFrontThreads) cp_async16(smem_base + L.xs + (uint32_t)i * 16u, src + (size_t)i * 16);
+          for (uint32_t o = 0; o < bytes; o += 32768u) bulk_load(smem_base + L.xs + o, src + o, min(32768u, bytes - o), xbar);
+        }
+      } else {
+        const int total = nrows * (int)(xpitch >> 4);
+#pragma unroll 1
+        for (int i = tid; i < total; i += kSplitFrontThreads) cp_async16(smem_base + L.xs + (uint32_t)i * 16u, src + (size_t)i * 16);
+      }
 #pragma unroll 1
       for (int i = tid; i < nrows; i += kSplitFrontThreads) sx[i] = __ldcg(p.xq_scale + i);
     } else if constexpr (FX) {
@@ -751,6 +764,7 @@ __global__ void __launch_bounds__(kSplitFrontThreads, 2) blr_blast_front_kernel(
   cp_async_wait_all();
   BLR_CK(7);
   bool ok = mbar_wait(bar, 0, abort_flag);
+  if (x_bulk) ok = mbar_wait(xbar, 0, abort_flag) && ok;
   if (__syncthreads_or(ok ? 0 : 1)) {
     if (tid == 0) atomicExch(p.status, 1u);
     return;
