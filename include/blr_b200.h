@@ -120,6 +120,21 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                    int b, int b_out, int P, int Q, int R, int flags,
                    void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream);
 
+/* Above 256 tokens the coupling runs on the tensor cores as a product with expanded coupling factors E (a function of
+ * S alone, blr_blast_coupling_bytes bytes; 0 for shapes whose coupling takes another route), which blr_blast rebuilds
+ * in its workspace at every call.  A caller whose S does not change between calls builds E once
+ * (blr_blast_expand_coupling; E 256-byte aligned) and passes it to blr_blast_rows_prepared, which is blr_blast_rows
+ * otherwise (E = NULL: exactly blr_blast_rows; E is ignored at token counts that do not use it).  No reference
+ * counterpart (the reference's kernels read S directly, blast_kernels.py:1990-2050). */
+size_t blr_blast_coupling_bytes(int b, int b_out, int R);
+int blr_blast_expand_coupling(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int R, int dtype,
+                              void* E, size_t E_bytes, void* stream);
+int blr_blast_rows_prepared(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
+                            const void* U, int u_layout, const void* V, int v_layout,
+                            const void* S, int64_t s_i, int64_t s_j, int64_t s_r,
+                            int b, int b_out, int P, int Q, int R, int flags,
+                            void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream, const void* E);
+
 /* Several BLAST layers that share their input and shapes in one pair of launches, with the element-wise work around
  * them folded in (no counterpart in the reference, whose modules call one operator per layer and add the bias and
  * the activation with separate torch kernels, models/wrappers.py:171-177):

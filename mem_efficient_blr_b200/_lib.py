@@ -46,6 +46,10 @@ SIGNATURES = {
                          _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
     "blr_blast_rows": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
                               _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp]),
+    "blr_blast_coupling_bytes": (_sz, [_int, _int, _int]),
+    "blr_blast_expand_coupling": (_int, [_vp, _i64, _i64, _i64, _int, _int, _int, _int, _vp, _sz, _vp]),
+    "blr_blast_rows_prepared": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,
+                                       _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp, _vp]),
     "blr_blast_multi": (_int, [_vp, _i64, _vp, _int, _i64, _int, _int, C.POINTER(BlastProblem), _i64, _i64, _i64,
                                _int, _int, _int, _int, _int, _int, _vp, _sz, _vp]),
     "blr_blast_static": (_int, [_vp, _i64, _i64, _int, _vp, _int, _vp, _int, _vp, _i64, _i64, _i64,

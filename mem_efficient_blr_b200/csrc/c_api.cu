@@ -432,7 +432,7 @@ static int cluster_monarch(const void* x, int64_t ldx, int64_t N, int dtype, con
 static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
-                      int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream) {
+                      int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream, const void* e_ready = nullptr) {
   int rc = check_common(x, ldx, N, dtype, out, ldo);
   if (rc) return rc < 0 ? rc : BLR_OK;
   BLR_REQUIRE(U && V && S, BLR_ERR_ARG, "factor pointers must not be null");
@@ -470,7 +470,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
   BLR_REQUIRE(u_bits == 16 && v_bits == 16, BLR_ERR_UNSUPPORTED,
               "quantised factors are implemented for up to %d tokens per call", kStreamMaxTokens);
   return pipeline_blast(x, ldx, N, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b, bo, P, Q, R, act8, out, ldo,
-                        w.region_a, w.region_b, w.region_c, stream);
+                        w.region_a, w.region_b, w.region_c, stream, e_ready);
 }
 
 // ---------------------------------------------------------------------------------- fixed scratch for blr_blast_static
@@ -573,6 +573,27 @@ int blr_blast_rows(const void* x, int64_t ldx, int64_t n_tokens, int dtype, cons
                    int flags, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream) {
   return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b_out,
                     P, Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+size_t blr_blast_coupling_bytes(int b, int b_out, int R) { return b >= 1 && b_out >= 1 && R > 0 ? pipeline_coupling_bytes(b, b_out, R) : 0; }
+
+int blr_blast_expand_coupling(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int R, int dtype, void* E,
+                              size_t E_bytes, void* stream) {
+  BLR_REQUIRE(S && E, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  BLR_REQUIRE(b >= 2 && b_out >= 1 && b_out <= b && R > 0, BLR_ERR_SHAPE, "bad dimensions");
+  const size_t need = pipeline_coupling_bytes(b, b_out, R);
+  BLR_REQUIRE(need > 0, BLR_ERR_UNSUPPORTED, "the coupling of b = %d, R = %d does not use expanded factors", b, R);
+  BLR_REQUIRE(E_bytes >= need && (reinterpret_cast<uintptr_t>(E) & 255) == 0, BLR_ERR_WORKSPACE,
+              "expanded coupling factors need %zu bytes, 256-byte aligned", need);
+  return pipeline_expand_coupling(S, s_i, s_j, s_r, b, b_out, R, dtype, E, static_cast<cudaStream_t>(stream));
+}
+
+int blr_blast_rows_prepared(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,
+                            int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q,
+                            int R, int flags, void* out, int64_t ldo, void* ws, size_t ws_bytes, void* stream, const void* E) {
+  return blast_impl(x, ldx, n_tokens, dtype, U, u_layout, 16, nullptr, V, v_layout, 16, nullptr, 0, S, s_i, s_j, s_r, b, b_out,
+                    P, Q, R, flags, out, ldo, ws, ws_bytes, static_cast<cudaStream_t>(stream), E);
 }
 
 int blr_blast_static(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const void* U, int u_layout, const void* V,

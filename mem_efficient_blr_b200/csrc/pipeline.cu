@@ -250,7 +250,7 @@ static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void
 // ------------------------------------------------------------------------------------------ operators
 int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, const void* V,
                    int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
-                   int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream) {
+                   int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream, const void* e_ready) {
   const long long plane = (long long)N * R;
   const bool bf = dtype == BLR_DTYPE_BF16;
   int rc;
@@ -272,9 +272,13 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
     const int gs = R % 16 == 0 ? 16 : 8, w = gs * b;
     rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, gs, (long long)R * b, w, 1, gs, act_int8}, stream);
     if (rc) return rc;
-    rc = bf ? run_expand<__nv_bfloat16>(S, s_i, s_j, s_r, e16, b, b_out, R, gs, stream)
-            : run_expand<__half>(S, s_i, s_j, s_r, e16, b, b_out, R, gs, stream);
-    if (rc) return rc;
+    if (e_ready != nullptr) {
+      e16 = const_cast<void*>(e_ready);  // expanded once by the caller (pipeline_expand_coupling), valid while S is unchanged
+    } else {
+      rc = bf ? run_expand<__nv_bfloat16>(S, s_i, s_j, s_r, e16, b, b_out, R, gs, stream)
+              : run_expand<__half>(S, s_i, s_j, s_r, e16, b, b_out, R, gs, stream);
+      if (rc) return rc;
+    }
     // z[i][n][GS*g + r'] = sum_k E[g][(i, r')][k] y'[n][g][k]
     rc = run_gemm(dtype, e16, BLR_W_KMAJOR, R / gs, gs * b_out, w, y16, N, (int64_t)R * b, w, OutSpec{z16, gs, R, plane, 1, gs, act_int8}, stream);
     if (rc) return rc;
@@ -288,6 +292,19 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
   }
   // out[n][i*Q + q] = sum_r U[i][q][r] z[i][n][r]
   return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
+}
+
+size_t pipeline_coupling_bytes(int b, int b_out, int R) {
+  if (b > 16 || R % 8 != 0) return 0;  // (the coupling of such shapes does not run as a GEMM over expanded factors)
+  const int gs = R % 16 == 0 ? 16 : 8;
+  return (size_t)R * gs * b_out * b * 2;
+}
+
+int pipeline_expand_coupling(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int R, int dtype, void* E,
+                             cudaStream_t stream) {
+  const int gs = R % 16 == 0 ? 16 : 8;
+  return dtype == BLR_DTYPE_BF16 ? run_expand<__nv_bfloat16>(S, s_i, s_j, s_r, E, b, b_out, R, gs, stream)
+                                 : run_expand<__half>(S, s_i, s_j, s_r, E, b, b_out, R, gs, stream);
 }
 
 // Transposes small matrices: in[a][c] (A x C, contiguous) -> out[c * out_c + a], kRowsPerCta matrices per CTA.

@@ -102,7 +102,7 @@ struct Call {
 // ----------------------------------------------------------------------------------------------- operators
 at::Tensor blast(const at::Tensor& x_in, const at::Tensor& U, const at::Tensor& V, const at::Tensor& S, int64_t u_layout,
                  int64_t v_layout, int64_t s_i, int64_t s_j, int64_t s_r, int64_t b, int64_t P, int64_t Q, int64_t R, int64_t flags,
-                 int64_t b_out) {
+                 int64_t b_out, const c10::optional<at::Tensor>& E) {
   need_factors(x_in, {&U, &V, &S});
   const int64_t bo = b_out < 0 ? b : b_out;
   if (x_in.size(0) == 0) return at::empty({0, bo * Q}, x_in.options());
@@ -113,9 +113,16 @@ at::Tensor blast(const at::Tensor& x_in, const at::Tensor& U, const at::Tensor& 
   const int64_t n = x.size(0);
   at::Tensor out = at::empty({n, bo * Q}, x.options());
   Scratch& w = c.ws(n, b, R);
-  check_rc(blr_blast_rows(x.data_ptr(), x.stride(0), n, dtype_code(x), U.data_ptr(), (int)u_layout, V.data_ptr(), (int)v_layout,
-                          S.data_ptr(), s_i, s_j, s_r, (int)b, (int)bo, (int)P, (int)Q, (int)R, (int)flags, out.data_ptr(),
-                          out.stride(0), w.ptr, w.bytes, c.st));
+  const void* e_ready = nullptr;  // expanded coupling factors built once by the caller (prefill sizes)
+  if (E.has_value() && E->defined()) {
+    TORCH_CHECK(E->is_cuda() && E->device() == x.device() && E->is_contiguous() &&
+                    (size_t)E->nbytes() >= blr_blast_coupling_bytes((int)b, (int)bo, (int)R),
+                "E must hold blr_blast_coupling_bytes bytes on x's device");
+    e_ready = E->data_ptr();
+  }
+  check_rc(blr_blast_rows_prepared(x.data_ptr(), x.stride(0), n, dtype_code(x), U.data_ptr(), (int)u_layout, V.data_ptr(),
+                                   (int)v_layout, S.data_ptr(), s_i, s_j, s_r, (int)b, (int)bo, (int)P, (int)Q, (int)R, (int)flags,
+                                   out.data_ptr(), out.stride(0), w.ptr, w.bytes, c.st, e_ready));
   return out;
 }
 
@@ -239,7 +246,7 @@ int64_t workspace_status(int64_t device, int64_t stream) {
 
 // ----------------------------------------------------------------------------------------------- shapes only
 at::Tensor blast_meta(const at::Tensor& x, const at::Tensor&, const at::Tensor&, const at::Tensor&, int64_t, int64_t, int64_t, int64_t,
-                      int64_t, int64_t b, int64_t, int64_t Q, int64_t, int64_t, int64_t b_out) {
+                      int64_t, int64_t b, int64_t, int64_t Q, int64_t, int64_t, int64_t b_out, const c10::optional<at::Tensor>&) {
   return at::empty_symint({x.sym_size(0), c10::SymInt((b_out < 0 ? b : b_out) * Q)}, x.options());
 }
 at::Tensor blast_wq_meta(const at::Tensor& x, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
@@ -261,7 +268,7 @@ at::Tensor dense_meta(const at::Tensor& x, const at::Tensor&, int64_t, int64_t, 
 
 TORCH_LIBRARY(blr_b200_ext, m) {
   m.def("blast(Tensor x, Tensor U, Tensor V, Tensor S, int u_layout, int v_layout, int s_i, int s_j, int s_r, int b, int P, int Q, "
-        "int R, int flags, int b_out=-1) -> Tensor");
+        "int R, int flags, int b_out=-1, Tensor? E=None) -> Tensor");
   m.def("blast_wq(Tensor x, Tensor Uq, Tensor u_scale, Tensor Vq, Tensor v_scale, Tensor S, int s_i, int s_j, int s_r, int bits, "
         "int group, int b, int P, int Q, int R) -> Tensor");
   m.def("monarch(Tensor x, Tensor w1, Tensor w2, int w1_layout, int w1_cols, int w2_layout, int b, int P, int rank, int Qs, "

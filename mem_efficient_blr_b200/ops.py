@@ -10,6 +10,8 @@ Launches go to the current stream, outputs come from torch's allocator, and noth
 """
 from __future__ import annotations
 
+import collections
+import weakref
 from typing import Tuple
 
 import torch
@@ -71,7 +73,7 @@ def _ws(x: torch.Tensor, n: int, groups: int, width: int):
 
 
 # ----------------------------------------------------------------------------- BLAST
-def _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
+def _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1, E=None):
     _need_cuda(x, U, V, S)
     if x.shape[0] == 0:  # an empty batch (e.g. a rank without tokens) is valid and needs no launch
         return x.new_empty((0, (b if b_out < 0 else b_out) * Q))
@@ -81,9 +83,10 @@ def _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags
     n = x.shape[0]
     out = torch.empty((n, bo * Q), dtype=x.dtype, device=x.device)
     ws, st = _ws(x, n, b, R)
-    L.check(L.load().blr_blast_rows(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), U.data_ptr(), u_layout,
-                                    V.data_ptr(), v_layout, S.data_ptr(), s_i, s_j, s_r, b, bo, P, Q, R, flags,
-                                    out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), st))
+    L.check(L.load().blr_blast_rows_prepared(x.data_ptr(), x.stride(0), n, L.dtype_code(x.dtype), U.data_ptr(), u_layout,
+                                             V.data_ptr(), v_layout, S.data_ptr(), s_i, s_j, s_r, b, bo, P, Q, R, flags,
+                                             out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), st,
+                                             None if E is None else E.data_ptr()))
     return out
 
 
@@ -94,13 +97,64 @@ def blast_op(x: torch.Tensor, U: torch.Tensor, V: torch.Tensor, S: torch.Tensor,
     return _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
 
 
+# Above this many tokens the library couples on the tensor cores with expanded coupling factors E, a function of S
+# alone that blr_blast rebuilds at every call (about 8 us at the headline shape).  The cache below keeps E per S.
+_COUPLING_MIN_TOKENS = 256
+coupling_cache_bytes = 4 << 30  # upper bound on the cached factors per process (least recently used go first); 0: off
+_coupling: "collections.OrderedDict" = collections.OrderedDict()
+_coupling_held = 0
+
+
+def clear_coupling_cache() -> None:
+    """Drops every cached set of expanded coupling factors.  The cache notices in-place changes of S that torch
+    counts (optimizer steps, copy_, load_state_dict); call this after writing through S.data or from outside torch."""
+    global _coupling_held
+    _coupling.clear()
+    _coupling_held = 0
+
+
+def _coupling_factors(x, S, s_i, s_j, s_r, b, bo, R):
+    """Expanded coupling factors of S for the current stream, built on first use; None where they do not apply
+    (few tokens, a shape that couples another way, tracing, stream capture: a captured graph must rebuild them at
+    every replay because S may change between replays)."""
+    global _coupling_held
+    if not (S.is_cuda and S.is_contiguous() and S.dtype == x.dtype) or torch.cuda.is_current_stream_capturing():
+        return None
+    root = S if S._base is None else S._base  # views made per call (a shard of S) share their base's version counter
+    st = L.stream_ptr(S.device)
+    key = (S.data_ptr(), s_i, s_j, s_r, b, bo, R, S.dtype, S.device.index, st)
+    hit = _coupling.get(key)
+    if hit is not None and hit[0]() is root and hit[1] == S._version:
+        _coupling.move_to_end(key)
+        return hit[2]
+    lib = L.load()
+    nbytes = lib.blr_blast_coupling_bytes(b, bo, R)
+    if nbytes == 0 or nbytes > coupling_cache_bytes:
+        return None
+    if hit is not None:
+        _coupling_held -= hit[2].numel()
+        del _coupling[key]
+    while _coupling and _coupling_held + nbytes > coupling_cache_bytes:
+        _coupling_held -= _coupling.popitem(last=False)[1][2].numel()
+    E = torch.empty(nbytes, dtype=torch.uint8, device=S.device)
+    L.check(lib.blr_blast_expand_coupling(S.data_ptr(), s_i, s_j, s_r, b, bo, R, L.dtype_code(S.dtype), E.data_ptr(), nbytes, st))
+    _coupling[key] = (weakref.ref(root), S._version, E)
+    _coupling_held += nbytes
+    return E
+
+
 def blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):
+    if not _eager():
+        e = L.ext()
+        op = blast_op if e is None else e.blast
+        return op(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
+    E = None
+    if x.shape[0] > _COUPLING_MIN_TOKENS and coupling_cache_bytes > 0 and b <= 16:
+        E = _coupling_factors(x, S, s_i, s_j, s_r, b, b if b_out < 0 else b_out, R)
     e = L.ext()
     if e is not None:
-        return e.blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
-    if _eager():
-        return _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
-    return blast_op(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out)
+        return e.blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out, E)
+    return _blast_impl(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out, E)
 
 
 @blast_op.register_fake

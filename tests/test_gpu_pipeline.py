@@ -170,3 +170,86 @@ def test_weight_quantised_blast_above_16_tokens(K, bits, group):
     got = bq.blast_wq(x.to(DEV), Uq.to(DEV), us.to(DEV), Vq.to(DEV), vs.to(DEV), S.to(DEV), bits, group)
     assert got.shape == ref.shape
     assert _err(got, ref) < TOL
+
+
+# ------------------------------------------------------------------------- expanded coupling factors kept per S
+def test_coupling_factors_cached_per_S_and_rebuilt_after_a_change(K):
+    """Above 256 tokens the expanded coupling factors are built once per S (ops._coupling_factors): the cached call is
+    bit-identical to the uncached one, and an in-place change of S (a version bump) rebuilds them."""
+    from mem_efficient_blr_b200 import ops
+    N, I, O, b, R = 300, 512, 768, 4, 128
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=5)
+    xd, Ud, Vtd, Sd = _cuda(x, U, Vt, S)
+    ops.clear_coupling_cache()
+    keep = ops.coupling_cache_bytes
+    try:
+        ops.coupling_cache_bytes = 0
+        plain = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+        assert len(ops._coupling) == 0
+        ops.coupling_cache_bytes = keep
+        first = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+        assert len(ops._coupling) == 1
+        held = next(iter(ops._coupling.values()))[2]
+        second = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+        assert len(ops._coupling) == 1 and next(iter(ops._coupling.values()))[2] is held
+        torch.cuda.synchronize()
+        assert torch.equal(plain, first) and torch.equal(plain, second)
+        assert _err(first, orc.blast(x, U, Vt, S)[0]) < TOL
+        # a shard of S made per call is a fresh view object of one base: still one entry per pointer
+        half = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd[:])
+        assert torch.equal(half, plain) and len(ops._coupling) == 1
+        Sd.mul_(-0.5)
+        changed = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+        assert _err(changed, orc.blast(x, U, Vt, S * -0.5)[0]) < TOL
+        assert len(ops._coupling) == 1
+        # few tokens never touch the cache
+        ops.clear_coupling_cache()
+        K.bk.blast_torch_layout(xd.reshape(-1, I)[:200], Ud, Vtd, Sd)
+        assert len(ops._coupling) == 0
+    finally:
+        ops.coupling_cache_bytes = keep
+        ops.clear_coupling_cache()
+
+
+def test_coupling_factors_stay_out_of_captured_graphs(K):
+    """A captured graph expands S at every replay (S may change between replays), so capture neither reads nor fills
+    the cache."""
+    from mem_efficient_blr_b200 import ops
+    N, I, O, b, R = 320, 512, 768, 4, 128
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.bfloat16, seed=6)
+    xd, Ud, Vtd, Sd = _cuda(x, U, Vt, S)
+    ops.clear_coupling_cache()
+    K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)  # scratch buffers at their final size, and one cache entry
+    torch.cuda.synchronize()
+    entries = len(ops._coupling)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+        torch.cuda.synchronize()
+        ops.clear_coupling_cache()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            out = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
+    assert len(ops._coupling) == 0 and entries == 1
+    Sd.mul_(2.0)
+    g.replay()
+    assert _err(out, orc.blast(x, U, Vt, S * 2.0)[0]) < TOL
+    ops.clear_coupling_cache()
+
+
+def test_coupling_entry_points_check_their_arguments(K):
+    from mem_efficient_blr_b200 import _lib as L
+    lib = L.load()
+    assert lib.blr_blast_coupling_bytes(16, 16, 1024) == 1024 * 16 * 16 * 16 * 2
+    assert lib.blr_blast_coupling_bytes(16, 4, 1032) == 1032 * 8 * 4 * 16 * 2   # R % 16 != 0: groups of 8 ranks
+    assert lib.blr_blast_coupling_bytes(32, 32, 1024) == 0 and lib.blr_blast_coupling_bytes(4, 4, 100) == 0
+    S = torch.randn(4, 4, 128, device=DEV, dtype=torch.float16)
+    need = lib.blr_blast_coupling_bytes(4, 4, 128)
+    E = torch.empty(need, dtype=torch.uint8, device=DEV)
+    st = L.stream_ptr(S.device)
+    args = (S.data_ptr(), 4 * 128, 128, 1, 4, 4)
+    assert lib.blr_blast_expand_coupling(*args, 128, 0, E.data_ptr(), need - 1, st) == -4  # BLR_ERR_WORKSPACE
+    assert lib.blr_blast_expand_coupling(*args, 100, 0, E.data_ptr(), need, st) == -6  # BLR_ERR_UNSUPPORTED
+    assert lib.blr_blast_expand_coupling(None, *args[1:], 128, 0, E.data_ptr(), need, st) == -1  # BLR_ERR_ARG
+    assert lib.blr_blast_expand_coupling(*args, 128, 0, E.data_ptr(), need, st) == 0
+    torch.cuda.synchronize()
