@@ -479,8 +479,9 @@ def run_ours(args):
     if args.ncu_case:
         # small case for a profiler capture: a few eager calls of one point over distinct replicas
         bits, n = (int(t) for t in args.ncu_case.split(":"))
+        xn = xs[n] if n in xs else torch.randn(n, I_F, device=dev, dtype=torch.float16)
         for q in reps[bits][:6]:
-            bq.blast_wq(xs[n], q[0], q[1], q[2], q[3], Sd, bits)
+            bq.blast_wq(xn, q[0], q[1], q[2], q[3], Sd, bits)
         torch.cuda.synchronize()
         _lib.workspace_status(dev)
         print(json.dumps({"ncu_case": args.ncu_case, "calls": 6}))

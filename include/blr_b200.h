@@ -194,7 +194,10 @@ int blr_blast_static_status(void* stream);
  * index in the low nibble; weight = q * scale.  `group` = 0: one scale per output channel, u_scale fp16 (b,Q),
  * v_scale fp16 (b,R).  `group` = 128: one scale per 128 consecutive contraction indices, u_scale fp16
  * (b,Q,R/128), v_scale fp16 (b,R,P/128); P and R must then be multiples of 128.  Other widths are rejected
- * with BLR_ERR_UNSUPPORTED.  Up to 16 tokens per call (BLR_ERR_UNSUPPORTED above: dequantise with
+ * with BLR_ERR_UNSUPPORTED.  Any token count; the quantised arrays are the only copy of the factors in device
+ * memory: up to 16 tokens the stored bytes are the MMA operands, above that the tensor-core GEMMs stage the stored
+ * bytes and widen them (q * scale rounded once to the 16-bit dtype) in shared memory ahead of the MMA.  Above 16
+ * tokens a row of P or R weights must be a multiple of 16 bytes (BLR_ERR_UNSUPPORTED otherwise: widen with
  * blr_dequantize_sym and call blr_blast, as the Python layer does). */
 int blr_blast_wq(const void* x, int64_t ldx, int64_t n_tokens, int dtype,
                  const void* Uq, const void* u_scale, const void* Vq, const void* v_scale,

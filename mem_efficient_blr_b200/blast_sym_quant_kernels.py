@@ -35,6 +35,11 @@ def get_triton_blast_bmm_usxv_int8_fp16_config():
     return None
 
 
+# Headline layer, int8, cold L2, us per call (in-GEMM widening | widening pass + 16-bit pipeline): 64 tokens 29.7 | 39.9,
+# 256: 44.0 | 49.2, 384: 49.1 | 50.2, 512: 59.8 | 56.4, 2048: 147 | 118.
+WQ_IN_GEMM_MAX_TOKENS = 384
+
+
 def quantize_blast_factors(U: torch.Tensor, Vt: torch.Tensor, bits: int, group: int = 0):
     """torch-layout factors U (b,Q,R), Vt (b,R,P) -> (Uq, u_scale, Vq, v_scale).
     One fp16 scale per output channel (group = 0: u_scale (b,Q), v_scale (b,R)) or per `group` contraction
@@ -48,8 +53,13 @@ def quantize_blast_factors(U: torch.Tensor, Vt: torch.Tensor, bits: int, group: 
 def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     """Weight-quantised BLAST. Uq (b,Q,R) int8 or (b,Q,R/2) uint8; Vq (b,R,P) int8 or (b,R,P/2) uint8;
     scales fp16 (b,Q) / (b,R), or (b,Q,R/group) / (b,R,P/group) with per-group scales;
-    S (b_out, b_in, R) in x's dtype.  Any token count: up to 16 tokens the factors stay quantised all the way to
-    the MMA, above that they are widened to x's dtype for the call."""
+    S (b_out, b_in, R) in x's dtype.  Any token count.  Up to 16 tokens the stored bytes are the MMA operands; up to
+    WQ_IN_GEMM_MAX_TOKENS the tensor-core GEMMs stage the stored bytes and widen them in shared memory (the quantised
+    arrays are then the only copy of the layer in device memory); above that every weight tile would be widened once
+    per 128 tokens, and one widening pass to x's dtype in front of the 16-bit pipeline is cheaper (both routes give
+    bit-identical results: the widened weight is q * scale rounded once either way).  Rows of P or R weights that
+    are not a multiple of 16 bytes (int4 with P = 48) cannot be staged by the copy engine and take the widening
+    pass from 17 tokens on."""
     assert bits in (8, 4)
     per = 1 if bits == 8 else 2
     b, q, r, p = u_scale.size(0), u_scale.size(1), v_scale.size(1), Vq.size(-1) * per
@@ -60,9 +70,8 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     else:
         assert tuple(u_scale.shape) == (b, q, r // group) and tuple(v_scale.shape) == (b, r, p // group)
     x2 = ops._flat2d(x)
-    if x2.shape[0] > 16:
-        # more than 16 tokens run on the tensor-core pipeline, which takes 16-bit factors: widen them for this call
-        # (about 10 us at the headline shape against 120 us of GEMMs; nothing is cached, the layer keeps its footprint)
+    n = x2.shape[0]
+    if n > WQ_IN_GEMM_MAX_TOKENS or (n > 16 and ((p * bits // 8) % 16 != 0 or (r * bits // 8) % 16 != 0)):
         U = ops.dequantize_sym(Uq, u_scale, bits, group, x.dtype)
         Vt = ops.dequantize_sym(Vq, v_scale, bits, group, x.dtype)
         out = ops.blast(x2, U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, L.FLAG_NONE)

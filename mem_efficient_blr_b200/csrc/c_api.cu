@@ -467,10 +467,10 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
     finish_params(p, N);
     return launch_stream(p, dtype == BLR_DTYPE_BF16, stream);
   }
-  BLR_REQUIRE(u_bits == 16 && v_bits == 16, BLR_ERR_UNSUPPORTED,
-              "quantised factors are implemented for up to %d tokens per call", kStreamMaxTokens);
+  // quantised factors stay quantised in global memory: the GEMMs widen the tiles they stage
+  const BlastQuant quant = {u_bits, v_bits, group, u_scale, v_scale};
   return pipeline_blast(x, ldx, N, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b, bo, P, Q, R, act8, out, ldo,
-                        w.region_a, w.region_b, w.region_c, stream, e_ready);
+                        w.region_a, w.region_b, w.region_c, stream, e_ready, u_bits != 16 || v_bits != 16 ? &quant : nullptr);
 }
 
 // ---------------------------------------------------------------------------------- fixed scratch for blr_blast_static

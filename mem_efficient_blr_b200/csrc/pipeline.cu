@@ -24,9 +24,17 @@ struct OutSpec {
   int round_out;
 };
 
+// Quantised weights of one GEMM: bits 8 | 4 (16: none), fp16 scales per weight row (group = 0) or per `group`
+// contraction indices.
+struct QuantSpec {
+  int bits = 16;
+  const void* scale = nullptr;
+  int group = 0;
+};
+
 // One grouped GEMM: W (G blocks of M rows over K), A[g][n][k] with element strides (1, ld_n, ld_g).
 static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, const void* A, int64_t N, int64_t ld_n,
-                    int64_t ld_g, const OutSpec& o, cudaStream_t stream) {
+                    int64_t ld_g, const OutSpec& o, cudaStream_t stream, const QuantSpec& q = QuantSpec()) {
   GemmParams p = {};
   p.G = G; p.M = M; p.K = K; p.N = (int)N;
   p.kmajor = layout == BLR_W_KMAJOR;
@@ -35,9 +43,25 @@ static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, c
   p.per = o.per; p.os_g = o.os_g; p.os_n = o.os_n; p.os_hi = o.os_hi; p.os_lo = o.os_lo; p.out = o.out;
   p.status = nullptr;
   BLR_REQUIRE(N < (1ll << 31), BLR_ERR_SHAPE, "too many tokens");
+  const bool quant = q.bits == 8 || q.bits == 4;
+  if (quant) {
+    p.w_bits = q.bits;
+    p.w_scale = q.scale;
+    p.scales_per_row = q.group == 0 ? 1 : K / q.group;
+  }
   umma_gemm_tiling(p);
   int rc;
-  if (p.kmajor) {
+  if (quant) {
+    // the stored bytes travel as they are: rows of K * bits / 8 bytes
+    const uint64_t row = (uint64_t)K * q.bits / 8;
+    BLR_REQUIRE(p.kmajor && row % 16 == 0, BLR_ERR_UNSUPPORTED,
+                "quantised factors above 16 tokens: contraction-contiguous rows of a multiple of 16 bytes (K = %d, %d bits)", K, q.bits);
+    BLR_REQUIRE(q.group == 0 || q.group == 128, BLR_ERR_UNSUPPORTED, "scale groups of 128 contraction indices");
+    const uint64_t dims[3] = {row, (uint64_t)M, (uint64_t)G};
+    const uint64_t str[2] = {row, (uint64_t)M * row};
+    const uint32_t box[3] = {(uint32_t)(8 * q.bits), (uint32_t)umma_w_tile_rows(p), 1};
+    rc = encode_tmap_3d(&p.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, W, dims, str, box, Swz::None);
+  } else if (p.kmajor) {
     BLR_REQUIRE(K % 8 == 0, BLR_ERR_SHAPE, "contraction length %d must be a multiple of 8", K);
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)G};
     const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * K * 2};
@@ -250,7 +274,13 @@ static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void
 // ------------------------------------------------------------------------------------------ operators
 int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, const void* V,
                    int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
-                   int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream, const void* e_ready) {
+                   int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream, const void* e_ready,
+                   const BlastQuant* quant) {
+  QuantSpec qu, qv;  // quantised U / V: widened tile by tile inside the GEMMs that read them
+  if (quant != nullptr) {
+    qu.bits = quant->u_bits, qu.scale = quant->u_scale, qu.group = quant->group;
+    qv.bits = quant->v_bits, qv.scale = quant->v_scale, qv.group = quant->group;
+  }
   const long long plane = (long long)N * R;
   const bool bf = dtype == BLR_DTYPE_BF16;
   int rc;
@@ -258,19 +288,19 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
   // memory) than as a GEMM over expanded factors (two kernels, 16x the products).
   const bool s_vec = s_r == 1 && (s_i & 7) == 0 && (s_j & 7) == 0 && (reinterpret_cast<uintptr_t>(S) & 15) == 0;
   if (N <= kCoupleTileMaxTokens && R % 8 == 0 && s_vec && b <= 16) {
-    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream);
+    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream, qv);
     if (rc) return rc;
     rc = bf ? run_couple_tile<__nv_bfloat16>(y16, S, s_i, s_j, z16, b, b_out, N, R, act_int8, stream)
             : run_couple_tile<__half>(y16, S, s_i, s_j, z16, b, b_out, N, R, act_int8, stream);
     if (rc < 0) return rc;
-    if (rc == 0) return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
+    if (rc == 0) return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream, qu);
     // rc == 1: no instantiation for this block count; y16 is overwritten below in the layout that path wants
   }
   if (b <= 16 && R % 8 == 0) {
     // y'[n][r/GS][j][r%GS] = sum_p V[j][r][p] x[n][j*P + p]: the (j, r%GS) index is contiguous, ready to be the
     // K dimension of the coupling GEMM
     const int gs = R % 16 == 0 ? 16 : 8, w = gs * b;
-    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, gs, (long long)R * b, w, 1, gs, act_int8}, stream);
+    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, gs, (long long)R * b, w, 1, gs, act_int8}, stream, qv);
     if (rc) return rc;
     if (e_ready != nullptr) {
       e16 = const_cast<void*>(e_ready);  // expanded once by the caller (pipeline_expand_coupling), valid while S is unchanged
@@ -284,14 +314,14 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
     if (rc) return rc;
   } else {
     // y[j][n][r] = sum_p V[j][r][p] x[n][j*P + p]
-    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream);
+    rc = run_gemm(dtype, V, v_layout, b, R, P, x, N, ldx, P, OutSpec{y16, plane, R, 0, 1, R, act_int8}, stream, qv);
     if (rc) return rc;
     rc = bf ? run_couple_generic<__nv_bfloat16>(y16, S, s_i, s_j, s_r, z16, b, b_out, N, R, act_int8, stream)
             : run_couple_generic<__half>(y16, S, s_i, s_j, s_r, z16, b, b_out, N, R, act_int8, stream);
     if (rc) return rc;
   }
   // out[n][i*Q + q] = sum_r U[i][q][r] z[i][n][r]
-  return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream);
+  return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0}, stream, qu);
 }
 
 size_t pipeline_coupling_bytes(int b, int b_out, int R) {

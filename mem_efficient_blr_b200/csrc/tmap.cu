@@ -82,7 +82,8 @@ int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, c
   cuuint32_t es[3] = {1, 1, 1};
   CUtensorMapSwizzle s = swz == Swz::B128 ? CU_TENSOR_MAP_SWIZZLE_128B
                          : swz == Swz::B64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                                           : CU_TENSOR_MAP_SWIZZLE_32B;
+                         : swz == Swz::B32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                           : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUresult r = fn(map, dt, 3, const_cast<void*>(base), gdims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, s,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   BLR_REQUIRE(r == CUDA_SUCCESS, BLR_ERR_CUDA,

@@ -30,7 +30,7 @@ void set_last_error(const char* fmt, ...);
     }                                         \
   } while (0)
 
-enum class Swz { B32, B64, B128 };
+enum class Swz { B32, B64, B128, None };
 
 // Encodes a rank-3 tiled tensor map.  dims are in elements (innermost first); strides[0..1] are the
 // byte strides of dims 1 and 2 (multiples of 16); box is in elements.  Out-of-range elements read 0.

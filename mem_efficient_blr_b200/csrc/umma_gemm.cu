@@ -6,6 +6,10 @@
 //   warps 2-9 epilogue: tcgen05.ld the accumulator (one MMA row per thread, two warps per 32 rows taking
 //             alternate 64-column chunks, loads of the next chunk in flight), convert, store
 // Which operand the tokens are is a template parameter (see umma_gemm.h).
+// Quantised weights (WQ = 8 | 4) add
+//   warps 10-17 converter: the producer stages the stored bytes of the weight tile next to the operand tiles; these
+//             warps widen them (q * scale, rounded once to the 16-bit dtype) into the swizzled weight tile of the
+//             stage and release it to the MMA issuer, so the quantised factors are the only copy in global memory
 // All waits are bounded; a time-out sets *status and the kernel drains and frees its TMEM.
 #include <stdlib.h>
 
@@ -20,6 +24,54 @@ static constexpr int kBM = 128;  // rows of the MMA (TMEM lanes)
 static constexpr int kBK = 64;
 static constexpr int kRowTileBytes = kBM * kBK * 2;
 static constexpr int kMaxStages = 8;
+static constexpr int kConvWarps = 8;  // converter warps of the quantised-weight variants
+
+// Bytes k0 and k0 + 1 of `w` hold u = q + OFF: returns (q * s) for both as two values of the 16-bit dtype, the
+// product rounded once (q and the fp16 scale are exact in either arithmetic: the result equals rn(float(q) * float(s))).
+template <bool BF16, int OFF, int K0>
+__device__ __forceinline__ uint32_t widen2(uint32_t w, float sf, __half2 sh) {
+  if constexpr (BF16) {
+    // 0x4B0000uu = 2^23 + u as a float
+    const float a = __uint_as_float(prmt(w, 0x4B000000u, 0x7650u | K0)) - (8388608.f + OFF);
+    const float b = __uint_as_float(prmt(w, 0x4B000000u, 0x7650u | (K0 + 1))) - (8388608.f + OFF);
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a * sf, b * sf);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    // 0x64uu = 1024 + u as a half
+    const uint32_t m = prmt(w, 0x64646464u, K0 == 0 ? 0x4140u : 0x4342u);
+    const __half2 off = __floats2half2_rn(1024.f + OFF, 1024.f + OFF);
+    const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&m), off), sh);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+// 16 consecutive quantised weights at `raw` (shared memory) -> 32 bytes of the 16-bit dtype in o[0..7]
+template <bool BF16, int WQ>
+__device__ __forceinline__ void widen16(uint32_t raw, __half scale, uint32_t (&o)[8]) {
+  uint32_t bw[4];
+  constexpr int OFF = WQ == 8 ? 128 : 8;
+  if constexpr (WQ == 8) {
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(bw[0]), "=r"(bw[1]), "=r"(bw[2]), "=r"(bw[3]) : "r"(raw));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) bw[i] ^= 0x80808080u;
+  } else {
+    uint32_t w[2];
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(raw));
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t lo = (w[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi = ((w[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+      bw[2 * i] = prmt(lo, hi, 0x5140u);      // weights 0..3 of the word: (low, high) nibbles of bytes 0, 1
+      bw[2 * i + 1] = prmt(lo, hi, 0x7362u);  // weights 4..7
+    }
+  }
+  const float sf = __half2float(scale);
+  const __half2 sh = __half2half2(scale);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = widen2<BF16, OFF, 0>(bw[i], sf, sh);
+    o[2 * i + 1] = widen2<BF16, OFF, 2>(bw[i], sf, sh);
+  }
+}
 
 template <bool BF16>
 __device__ __forceinline__ void gemm_store(void* base, long long off, float v) {
@@ -124,20 +176,26 @@ __device__ __forceinline__ void epilogue_rows(const EpiRow& e, uint32_t taddr, i
 // TR = tokens are the MMA rows (weights its columns); !TR = weights are the rows ("swap-AB").
 // MODE = store width of the TR epilogue (see epilogue_store32), RND = round the outputs to int8 steps; both are
 // chosen by the host from the parameters, so that the epilogue holds exactly one variant.
-template <bool BF16, bool TR, int MODE, bool RND>
-__global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __grid_constant__ GemmParams p) {
+// WQ = 0: 16-bit weights; 8 | 4: quantised weights widened by converter warps (K-major only).
+template <bool BF16, bool TR, int MODE, bool RND, int WQ>
+__global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
+    blr_umma_gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t col_tile_bytes = (uint32_t)p.bn * kBK * 2;
-  const uint32_t stage_bytes = kRowTileBytes + col_tile_bytes;
+  const uint32_t tiles_bytes = kRowTileBytes + col_tile_bytes;  // the two operand tiles of a stage
+  // quantised weights: the stored bytes of the weight tile follow them (8 * WQ bytes per row)
+  const uint32_t raw_bytes = WQ ? (uint32_t)(TR ? p.bn : kBM) * (8u * WQ) : 0u;
+  const uint32_t stage_bytes = tiles_bytes + raw_bytes;
   const uint32_t NST = p.nstages;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NST * stage_bytes);
-  // full[8], empty[8], tmem_full[2], tmem_empty[2]
+  // full[8], empty[8], tmem_full[2], tmem_empty[2], (slot, abort flag), raw_full[8]
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
   const uint32_t tfull0 = smem_u32(bars + 2 * kMaxStages), tempty0 = smem_u32(bars + 2 * kMaxStages + 2);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t rfull0 = smem_u32(bars + 2 * kMaxStages + 5);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // m_tiles: tiles along the weight rows; n_tiles: tiles along the tokens
@@ -154,8 +212,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (uint32_t s = 0; s < NST; ++s) {
-      mbar_init(full0 + 8 * s, 1);
+      mbar_init(full0 + 8 * s, WQ ? 1 + kConvWarps : 1);  // the producer's arrival (+ one per converter warp)
       mbar_init(empty0 + 8 * s, 1);
+      if constexpr (WQ != 0) mbar_init(rfull0 + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull0 + 8 * b, 1);
@@ -185,10 +244,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!first && !mbar_wait(empty0 + 8 * s, parity ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t dst = smem_base + s * stage_bytes, bar = full0 + 8 * s;
-          mbar_arrive_expect_tx(bar, stage_bytes);
-          if (p.kmajor) {
+          if constexpr (WQ != 0) {
+            // stored bytes to the converter warps; only the token tile completes `bar` by bytes
+            mbar_arrive_expect_tx(rfull0 + 8 * s, raw_bytes);
+            tma_load_3d(dst + tiles_bytes, &p.tmW, kb * (8 * WQ), mt * w_rows, g, rfull0 + 8 * s);
+            mbar_arrive_expect_tx(bar, TR ? (uint32_t)kRowTileBytes : col_tile_bytes);
+          } else if (p.kmajor) {
+            mbar_arrive_expect_tx(bar, stage_bytes);
             tma_load_3d(dst + w_off, &p.tmW, kb * kBK, mt * w_rows, g, bar);
           } else {
+            mbar_arrive_expect_tx(bar, stage_bytes);
             // output index contiguous: 64-wide column blocks of 64 k-rows, 8 KB each
             for (int blk = 0; blk < w_rows / 64; ++blk)
               tma_load_3d(dst + w_off + blk * 8192, &p.tmW, mt * w_rows + blk * 64, kb * kBK, g, bar);
@@ -228,6 +293,51 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
           if (++s == NST) { s = 0; parity ^= 1u; }
         }
         if (ok) umma_commit(tfull0 + 8 * buf);  // accumulator complete
+      }
+    }
+  } else if (WQ != 0 && warp >= kGemmThreads / 32) {
+    // ------------------------------------------------ converter: thread = (row of a band of rows, 16 weights of the
+    // 64-wide k block); a warp reads 8 rows of stored bytes contiguously and writes their 16-byte pieces to the
+    // places the 128-byte swizzle gives them (piece c of row r at c ^ (r & 7)): no bank conflicts either way
+    if constexpr (WQ != 0) {
+      const int ct = (int)threadIdx.x - kGemmThreads, j = ct & 3, r_in = ct >> 2;
+      const __half* sc = static_cast<const __half*>(p.w_scale);
+      constexpr int kBand = 8 * kConvWarps, kMaxBands = 256 / kBand;  // rows per pass of all converter threads
+      const int bands = w_rows / kBand;
+      const bool grouped = p.scales_per_row > 1;
+      __half scale[kMaxBands];
+      uint32_t s = 0, parity = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int gm = tile / n_tiles, mt = gm % m_tiles, g = gm / m_tiles;
+        const int row0 = mt * w_rows;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (kb == 0 || (grouped && (kb & 1) == 0)) {
+#pragma unroll
+            for (int i = 0; i < kMaxBands; ++i) {
+              const int m = row0 + r_in + kBand * i;
+              scale[i] = i < bands && m < p.M ? sc[((long long)g * p.M + m) * p.scales_per_row + (grouped ? kb >> 1 : 0)]
+                                              : __float2half(0.f);
+            }
+          }
+          if (!mbar_wait(rfull0 + 8 * s, parity, abort_flag)) { ok = false; break; }
+          const uint32_t st = smem_base + s * stage_bytes, raw = st + tiles_bytes, dstW = st + w_off;
+#pragma unroll
+          for (int i = 0; i < kMaxBands; ++i) {
+            if (i < bands) {
+              const int row = r_in + kBand * i;
+              uint32_t o[8];
+              widen16<BF16, WQ>(raw + row * (8 * WQ) + j * (2 * WQ), scale[i], o);
+              const uint32_t d = dstW + row * 128, x = (uint32_t)(row & 7);
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(d + (((2 * j) ^ x) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(d + (((2 * j + 1) ^ x) << 4)), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+            }
+          }
+          fence_proxy_async_smem();  // the MMA reads the tile through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full0 + 8 * s);
+          if (++s == NST) { s = 0; parity ^= 1u; }
+        }
       }
     }
   } else {
@@ -294,6 +404,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) blr_umma_gemm_kernel(const __
   }
 }
 
+static bool gemm_quantised(const GemmParams& p) { return p.w_bits == 8 || p.w_bits == 4; }
+static int gemm_stage_bytes(const GemmParams& p) {
+  const int w_rows = p.tokens_as_rows ? p.bn : kBM;
+  return kRowTileBytes + p.bn * kBK * 2 + (gemm_quantised(p) ? w_rows * 8 * p.w_bits : 0);
+}
+
 void umma_gemm_tiling(GemmParams& p) {
   if (p.N > 64) {
     // tokens as MMA rows; weight rows as columns, 256 at a time when the block is tall enough
@@ -312,21 +428,21 @@ void umma_gemm_tiling(GemmParams& p) {
     p.tokens_as_rows = 0;
     p.bn = (p.N + 15) / 16 * 16;
   }
-  const int stage = kRowTileBytes + p.bn * kBK * 2;
+  const int stage = gemm_stage_bytes(p);
   int nst = (232448 - 1024 - 512) / stage;
   p.nstages = nst > kMaxStages ? kMaxStages : nst;
 }
 
-template <bool BF16, bool TR, int MODE, bool RND>
+template <bool BF16, bool TR, int MODE, bool RND, int WQ = 0>
 static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
-    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR, MODE, RND>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR, MODE, RND, WQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     configured[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kGemmThreads);
+  cfg.blockDim = dim3(kGemmThreads + (WQ ? 32 * kConvWarps : 0));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute at[1];
@@ -335,12 +451,23 @@ static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, i
   cfg.attrs = at;
   cfg.numAttrs = 1;
   void* args[] = {const_cast<GemmParams*>(&p)};
-  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR, MODE, RND>, args));
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR, MODE, RND, WQ>, args));
   return BLR_OK;
+}
+
+// Quantised weights: no rounding variant (the rounded intermediates exist for 16-bit factors only).
+template <bool BF16, int WQ>
+static int launch_quantised(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
+  if (!p.tokens_as_rows) return launch_variant<BF16, false, 0, false, WQ>(p, grid, smem, dev, max_smem, stream);
+  if (mode == 2) return launch_variant<BF16, true, 2, false, WQ>(p, grid, smem, dev, max_smem, stream);
+  if (mode == 1) return launch_variant<BF16, true, 1, false, WQ>(p, grid, smem, dev, max_smem, stream);
+  return launch_variant<BF16, true, 0, false, WQ>(p, grid, smem, dev, max_smem, stream);
 }
 
 template <bool BF16>
 static int launch_dtype(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
+  if (p.w_bits == 8) return launch_quantised<BF16, 8>(p, mode, grid, smem, dev, max_smem, stream);
+  if (p.w_bits == 4) return launch_quantised<BF16, 4>(p, mode, grid, smem, dev, max_smem, stream);
   if (!p.tokens_as_rows) {
     return p.round_out ? launch_variant<BF16, false, 0, true>(p, grid, smem, dev, max_smem, stream)
                        : launch_variant<BF16, false, 0, false>(p, grid, smem, dev, max_smem, stream);
@@ -360,7 +487,14 @@ int launch_umma_gemm(const GemmParams& p_in, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc != BLR_OK) return rc;
-  const size_t smem = (size_t)p.nstages * (kRowTileBytes + p.bn * kBK * 2) + 512 + 1024;
+  const size_t smem = (size_t)p.nstages * gemm_stage_bytes(p) + 512 + 1024;
+  if (gemm_quantised(p)) {
+    BLR_REQUIRE(p.kmajor && !p.round_out && p.w_scale != nullptr && p.scales_per_row >= 1, BLR_ERR_ARG,
+                "quantised weights are contraction-contiguous, scaled and not combined with rounded outputs");
+    BLR_REQUIRE((p.tokens_as_rows ? p.bn : kBM) % (8 * kConvWarps) == 0, BLR_ERR_ARG, "bad tile configuration for quantised weights");
+    BLR_REQUIRE(p.scales_per_row == 1 || p.scales_per_row * 128 == p.K, BLR_ERR_SHAPE,
+                "scales per weight row: one, or one per 128 contraction indices");
+  }
   BLR_REQUIRE((int)smem <= di.max_smem_optin, BLR_ERR_UNSUPPORTED, "needs %zu bytes of shared memory, device offers %d",
               smem, di.max_smem_optin);
   BLR_REQUIRE(p.bn % 16 == 0 && p.bn >= 16 && p.bn <= 256 && p.nstages >= 2, BLR_ERR_ARG, "bad tile configuration");

@@ -14,6 +14,7 @@ namespace blr {
 
 struct alignas(64) GemmParams {
   CUtensorMap tmW;  // K-major: dims (K, M, G) box (64, row-tile, 1); M-major: dims (M, K, G) box (64, 64, 1)
+                    // quantised weights (w_bits 8 | 4, K-major): bytes, dims (K*w_bits/8, M, G) box (8*w_bits, row-tile, 1), no swizzle
   CUtensorMap tmA;  // dims (K, N, G) box (64, token-tile, 1)
   int G, M, K, N;
   int kmajor;          // weight layout
@@ -26,6 +27,12 @@ struct alignas(64) GemmParams {
   long long os_g, os_n, os_hi, os_lo;
   void* out;
   unsigned* status;  // optional: set to 1 when a device-side wait gave up
+  // Quantised weights: int8 or packed int4 (two per byte along k, even index in the low nibble, two's complement) with
+  // fp16 scales [g][m][scales_per_row] (1: per weight row; K / 128: per 128 contraction indices).  Converter warps
+  // widen every staged tile to the 16-bit dtype (q * scale, rounded once) in shared memory ahead of the MMA.
+  int w_bits;  // 0 / 16: 16-bit weights
+  int scales_per_row;
+  const void* w_scale;
 };
 
 int launch_umma_gemm(const GemmParams& p, cudaStream_t stream);

@@ -91,14 +91,59 @@ def test_blast_act_int8_prefill(K):
     assert _err(K.bq.triton_blast_bmm_int8_fp16(x.to(DEV), Ub, Vb, Sb), ref) < 3e-2
 
 
-def test_quantised_entry_point_rejects_more_than_16_tokens(K):
-    """The C entry point keeps quantised factors all the way to the MMA and takes up to 16 tokens; the Python
-    operator widens the factors above that (test_weight_quantised_blast_above_16_tokens)."""
+WQ_SHAPES = [
+    # N, I, O, b, R
+    (17, 512, 768, 4, 128),        # weights as the MMA rows (up to 64 tokens)
+    (64, 4096, 11008, 16, 1024),
+    (65, 4096, 11008, 16, 1024),   # tokens as the MMA rows
+    (300, 768, 1152, 3, 384),      # three blocks, the coupling over expanded factors
+    (200, 512, 288, 4, 128),       # Q = 72: a ragged weight tile
+    (1024, 4096, 4096, 16, 1024),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits,group", [(8, 0), (4, 0), (8, 128), (4, 128)])
+@pytest.mark.parametrize("shape", WQ_SHAPES)
+def test_quantised_factors_widened_inside_the_gemms(K, shape, bits, group, dtype):
+    """Above 16 tokens the C entry point stages the stored bytes and widens them in shared memory.  The widened tile
+    equals what blr_dequantize_sym writes (q * scale rounded once), so the result is bit-identical to the 16-bit
+    pipeline on the widened factors, which needs a second copy of the layer in device memory."""
     from mem_efficient_blr_b200 import ops
-    x, U, Vt, S = orc.make_blast_inputs(32, 512, 768, 4, 128, torch.float16, seed=2)
-    Uq, us, Vq, vs = K.bq.quantize_blast_factors(U.to(DEV), Vt.to(DEV), 8)
-    with pytest.raises(RuntimeError, match="quantised factors"):
-        ops.blast_wq(x.to(DEV)[0], Uq, us, Vq, vs, S.to(DEV), 4 * 128, 128, 1, 8, 0, 4, 128, 192, 128)
+    N, I, O, b, R = shape
+    P, Q = I // b, O // b
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, dtype, seed=N + bits + group)
+    Uq, us = orc.quantize_sym(U, bits, group)
+    Vq, vs = orc.quantize_sym(Vt, bits, group)
+    xd, Uqd, usd, Vqd, vsd, Sd = _cuda(x.reshape(-1, I), Uq, us, Vq, vs, S)
+    got = ops.blast_wq(xd, Uqd, usd, Vqd, vsd, Sd, b * R, R, 1, bits, group, b, P, Q, R)
+    Uw = ops.dequantize_sym(Uqd, usd, bits, group, dtype)
+    Vw = ops.dequantize_sym(Vqd, vsd, bits, group, dtype)
+    keep = ops.coupling_cache_bytes
+    ops.coupling_cache_bytes = 0
+    try:
+        want = ops.blast(xd, Uw, Vw, Sd, 0, 0, b * R, R, 1, b, P, Q, R, 0)
+    finally:
+        ops.coupling_cache_bytes = keep
+    torch.cuda.synchronize()
+    assert got.shape == want.shape and torch.equal(got, want)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, bits, group)
+    assert _err(got, ref.reshape(-1, O)) < TOL
+
+
+def test_quantised_rows_the_copy_engine_cannot_stage(K):
+    """int4 rows of P = 48 weights are 24 bytes: the C entry point refuses them above 16 tokens, the Python operator
+    widens such a layer for the call."""
+    from mem_efficient_blr_b200 import ops
+    N, I, O, b, R = 40, 768, 768, 16, 64
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=2)
+    Uq, us = orc.quantize_sym(U, 4, 0)
+    Vq, vs = orc.quantize_sym(Vt, 4, 0)
+    xd, Uqd, usd, Vqd, vsd, Sd = _cuda(x, Uq, us, Vq, vs, S)
+    with pytest.raises(RuntimeError, match="multiple of 16 bytes"):
+        ops.blast_wq(xd.reshape(-1, I), Uqd, usd, Vqd, vsd, Sd, b * R, R, 1, 4, 0, b, I // b, O // b, R)
+    ref, _, _ = orc.blast_wq(x, Uq, us, Vq, vs, S, 4, 0)
+    assert _err(K.bq.blast_wq(xd, Uqd, usd, Vqd, vsd, Sd, 4, 0), ref) < TOL
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -153,9 +198,9 @@ def test_linearity_at_full_size(K):
 
 @pytest.mark.parametrize("bits,group", [(8, 0), (4, 0), (8, 128), (4, 128)])
 def test_weight_quantised_blast_above_16_tokens(K, bits, group):
-    """Quantised layers on prefill sizes: factors widened to 16 bits for the call, then the tensor-core pipeline.
-    The widening rounds q * scale to the 16-bit type, which the oracle (fp32 dequantisation) does not; the bound
-    is the same 1e-2."""
+    """Quantised layers on prefill sizes through the reference-facing operator.  The widening (here in shared
+    memory, inside the GEMMs) rounds q * scale to the 16-bit type, which the oracle (fp32 dequantisation) does not;
+    the bound is the same 1e-2."""
     N, I, O, b, R = 197, 4096, 11008, 16, 1024
     x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, torch.float16, seed=bits + group)
     Uq, us = orc.quantize_sym(U, bits, group)
