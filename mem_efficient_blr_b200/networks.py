@@ -13,8 +13,10 @@ step has fixed shapes and can be captured in a CUDA graph (`GraphedCall`).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass, field
+from typing import Optional
 
 import torch
 import torch.nn as nn
@@ -25,6 +27,22 @@ from . import blast_sym_quant_kernels as bq
 
 
 # ------------------------------------------------------------------------------------------------ structured linears
+_EMPTY_INIT = False
+
+
+@contextlib.contextmanager
+def empty_init():
+    """Inside this context the networks and layers of this module are built with uninitialised weights (no random
+    numbers, and quantised layers without their 16-bit factors ever existing): the skeleton for
+    packed.load_packed_into."""
+    global _EMPTY_INIT
+    keep, _EMPTY_INIT = _EMPTY_INIT, True
+    try:
+        yield
+    finally:
+        _EMPTY_INIT = keep
+
+
 class BlastTorchLinear(nn.Module):
     """BLAST linear on the torch layouts U (b,Q,R), Vt (b,R,P), S (b,b,R) (torch_funcs/blast_funcs.py:3-47), with a
     variance-preserving random init: x ~ N(0,1) gives out ~ N(0,1) (Vt ~ N(0,1/P), S ~ U(0.5,1.5), U ~ N(0,1/(R b E[S^2])))."""
@@ -36,6 +54,11 @@ class BlastTorchLinear(nn.Module):
         P, Q = in_features // b, out_features // b
         g = generator
         gd = g.device if g is not None else "cpu"   # a CUDA generator fills the factors on the device (large models)
+        if _EMPTY_INIT:
+            for name, shp in (("U", (b, Q, rank)), ("Vt", (b, rank, P)), ("S", (b, b, rank))):
+                setattr(self, name, nn.Parameter(torch.empty(shp, device=device, dtype=dtype), requires_grad=False))
+            self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype), requires_grad=False) if bias else None
+            return
         rn = lambda *s: torch.randn(*s, generator=g, device=gd)
         self.U = nn.Parameter((rn(b, Q, rank) / math.sqrt(rank * b * 13.0 / 12.0)).to(device=device, dtype=dtype), requires_grad=False)
         self.Vt = nn.Parameter((rn(b, rank, P) / math.sqrt(P)).to(device=device, dtype=dtype), requires_grad=False)
@@ -58,14 +81,31 @@ class BlastTorchLinear(nn.Module):
 class BlastQuantLinear(nn.Module):
     """The same layer with int8 / packed-int4 factors and fp16 scales (the format of blr_blast_wq)."""
 
-    def __init__(self, src: BlastTorchLinear, bits: int, group: int = 0):
+    def __init__(self, src: Optional[BlastTorchLinear], bits: int, group: int = 0):
         super().__init__()
-        self.in_features, self.out_features, self.b, self.rank = src.in_features, src.out_features, src.b, src.rank
         self.bits, self.group = bits, group
+        if src is None:
+            return   # BlastQuantLinear.empty fills the rest
+        self.in_features, self.out_features, self.b, self.rank = src.in_features, src.out_features, src.b, src.rank
         Uq, us, Vq, vs = bq.quantize_blast_factors(src.U.data, src.Vt.data, bits, group)
         for name, t in (("Uq", Uq), ("u_scale", us), ("Vq", Vq), ("v_scale", vs), ("S", src.S.data)):
             self.register_buffer(name, t)
         self.bias = src.bias
+
+    @classmethod
+    def empty(cls, in_features, out_features, b, rank, bits, group=0, bias=False, device="cuda", dtype=torch.float16):
+        """The layer with uninitialised buffers of the right shapes (to be filled from a packed-weight file)."""
+        m = cls(None, bits, group)
+        m.in_features, m.out_features, m.b, m.rank = in_features, out_features, b, rank
+        P, Q, per = in_features // b, out_features // b, (1 if bits == 8 else 2)
+        e = lambda shp, dt: torch.empty(shp, device=device, dtype=dt)
+        m.register_buffer("Uq", e((b, Q, rank // per), torch.int8 if bits == 8 else torch.uint8))
+        m.register_buffer("u_scale", e((b, Q) if group == 0 else (b, Q, rank // group), torch.float16))
+        m.register_buffer("Vq", e((b, rank, P // per), torch.int8 if bits == 8 else torch.uint8))
+        m.register_buffer("v_scale", e((b, rank) if group == 0 else (b, rank, P // group), torch.float16))
+        m.register_buffer("S", e((b, b, rank), dtype))
+        m.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype), requires_grad=False) if bias else None
+        return m
 
     def U_device_ok(self) -> bool:
         return self.Uq.is_cuda
@@ -82,11 +122,15 @@ def make_linear(method: str, in_features: int, out_features: int, b: int, rank: 
     if method == "dense":
         lin = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=dtype)
         gd = generator.device if generator is not None else "cpu"
+        if _EMPTY_INIT:
+            return lin.requires_grad_(False)
         with torch.no_grad():
             lin.weight.copy_((torch.randn(out_features, in_features, generator=generator, device=gd) / math.sqrt(in_features)).to(dtype))
             if bias:
                 lin.bias.zero_()
         return lin.requires_grad_(False)
+    if _EMPTY_INIT and method in ("blast_int8", "blast_int4"):
+        return BlastQuantLinear.empty(in_features, out_features, b, rank, 8 if method == "blast_int8" else 4, 0, bias, device, dtype)
     base = BlastTorchLinear(in_features, out_features, b, rank, bias, device, dtype, generator)
     if method == "blast":
         return base
@@ -216,7 +260,8 @@ class LlamaDecoder(nn.Module):
         self.fused_decode = True   # False: the decode step runs the same torch modules as the prefill
         self.embed_tokens = nn.Embedding(shape.vocab, shape.d, device=device, dtype=dtype)
         with torch.no_grad():
-            self.embed_tokens.weight.copy_(torch.randn(shape.vocab, shape.d, generator=g, device=g.device).to(dtype))
+            if not _EMPTY_INIT:
+                self.embed_tokens.weight.copy_(torch.randn(shape.vocab, shape.d, generator=g, device=g.device).to(dtype))
         self.embed_tokens.requires_grad_(False)
         self.layers = nn.ModuleList(LlamaLayer(shape, method, device, dtype, g) for _ in range(shape.layers))
         self.norm = RMSNorm(shape.d, shape.eps, device, dtype)

@@ -75,3 +75,42 @@ def test_vit_shaped_encoder_matches_oracle_backed_twin():
     want = cpu(img.half().float())
     assert got.shape == (2, 17, 256)
     assert orc.rel_fro(got.float().cpu(), want) < TOL
+
+
+# ------------------------------------------------------------------------------------------------ packed-weight files
+@pytest.mark.parametrize("bits", [8, 4])
+def test_packed_weight_file_rebuilds_the_quantised_decoder(tmp_path, bits):
+    """16-bit decoder -> packer (device quantiser) -> file -> skeleton built without random numbers or 16-bit factors
+    -> the same logits, bit for bit, as the decoder quantised in memory; the file holds the quantised layers only."""
+    import os
+    from mem_efficient_blr_b200 import networks as nw, packed
+    shape = nw.LlamaShape(layers=2, d=256, heads=4, ffn=512, vocab=1000, b=4, rank_attn=64, rank_mlp=128)
+    method = f"blast_int{bits}"
+    src = nw.LlamaDecoder(shape, "blast", batch=2, cache_len=32, seed=11)
+    want_model = nw.LlamaDecoder(shape, method, batch=2, cache_len=32, seed=11)
+    tensors, layers = packed.pack_module(src, bits)
+    assert len(layers) == 2 * 7 and all(v["kind"] == "blast_wq" and v["bits"] == bits for v in layers.values())
+    assert not any(k.endswith((".U", ".Vt")) for k in tensors)
+    path = os.path.join(tmp_path, "decoder.blrpack")
+    size = packed.save_packed(path, tensors, layers, {"shape": vars(shape), "method": method})
+    dense16 = sum(p.numel() * p.element_size() for p in src.parameters())
+    assert size < dense16                      # the quantised factors are smaller than the 16-bit ones
+    del src, tensors
+    with nw.empty_init():
+        got_model = nw.LlamaDecoder(shape, method, batch=2, cache_len=32, seed=0)
+    meta = packed.load_packed_into(got_model, path)
+    assert meta["method"] == method and meta["shape"]["rank_mlp"] == 128
+    ids = torch.randint(0, shape.vocab, (2, 20), device="cuda")
+    want, got = want_model.prefill(ids), got_model.prefill(ids)
+    nxt = torch.randint(0, shape.vocab, (2, 1), device="cuda")
+    pos = torch.tensor([20], device="cuda")
+    want2, got2 = want_model.decode_step(nxt, pos), got_model.decode_step(nxt, pos)
+    torch.cuda.synchronize()
+    assert torch.equal(want, got) and torch.equal(want2, got2)
+    # and back to the torch layout: the widened factors are what blr_dequantize_sym gives
+    from mem_efficient_blr_b200 import ops
+    loaded, layers2, _ = packed.load_packed(path, "cuda")
+    state = packed.unpack_to_torch_layout(dict(loaded), layers2)
+    p0 = "layers.0.q_proj" if "layers.0.q_proj" in layers2 else sorted(layers2)[0]
+    U = ops.dequantize_sym(loaded[p0 + ".Uq"], loaded[p0 + ".u_scale"], bits, 0, torch.float16)
+    assert torch.equal(state[p0 + ".U"], U) and p0 + ".Uq" not in state
