@@ -388,10 +388,11 @@ def layer_sweep(dev, quick):
             mk_one = lambda: (h(B_BLK, o_f // B_BLK, r, fan=r), h(B_BLK, r, i_f // B_BLK, fan=i_f // B_BLK),
                               torch.rand(B_BLK, B_BLK, r, device=dev, dtype=torch.float16) + 0.5)
             call = lambda f: bk.blast_torch_layout(xn, *f)
-        elif kind == "monarch":
+        elif kind in ("monarch", "monarch_ideal"):
+            # monarch_ideal: the output stays in the block-major order of the reference's right_ideal variant
             wbytes, flops = 2 * r * (i_f + o_f), 2 * n * r * (i_f + o_f)
             mk_one = lambda: (h(4, r, i_f // 4, fan=i_f // 4), h(4, o_f // 4, r, fan=r))
-            call = lambda f: mk.monarch_torch_layout(xn, *f)
+            call = lambda f: mk.monarch_torch_layout(xn, *f, ideal=(kind == "monarch_ideal"))
         elif kind == "low_rank":
             wbytes, flops = 2 * r * (i_f + o_f), 2 * n * r * (i_f + o_f)
             mk_one = lambda: (h(r, i_f, fan=i_f), h(o_f, r, fan=r))
@@ -412,10 +413,24 @@ def layer_sweep(dev, quick):
     for lname, i_f, o_f, ranks in (("qkvo_4096x4096", 4096, 4096, {"blast": 1024, "monarch": 1024, "low_rank": 1024}),
                                    ("gate_4096x11008", 4096, 11008, {"blast": 1488, "monarch": 1536, "low_rank": 1024}),
                                    ("down_11008x4096", 11008, 4096, {"blast": 1488, "monarch": 1536, "low_rank": 1024})):
-        for kind in ("blast", "monarch", "low_rank", "dense"):
+        kinds = ("blast", "monarch", "low_rank", "dense") + (("monarch_ideal",) if lname.startswith("gate") else ())
+        for kind in kinds:
             for n in tokens:
-                res[f"{lname}/{kind}/n{n}"] = point(kind, i_f, o_f, ranks.get(kind, 0), n)
+                res[f"{lname}/{kind}/n{n}"] = point(kind, i_f, o_f, ranks.get(kind.split("_ideal")[0], 0), n)
                 torch.cuda.empty_cache()
+    # SwiGLU MLP on Monarch linears (4 blocks, rank 1536): gate / up in the ideal order feeding down directly (the
+    # reference's configs/networks/llama7b.yaml:164,180) against every layer interleaving its output
+    from mem_efficient_blr_b200 import networks as nw
+    nrep = int(2 * L2_BYTES // (3 * 2 * 1536 * (4096 + 11008))) + 1
+    for chain in ("ideal", "interleaved"):
+        mods = [nw.MonarchSwiGLU(4096, 11008, 4, 1536, chain, device=dev, generator=torch.Generator(device=dev).manual_seed(i))
+                for i in range(nrep)]
+        for n in tokens:
+            xn = torch.randn(n, 4096, device=dev, dtype=torch.float16)
+            us = gt.us_per_call([(lambda m=m: m(xn)) for m in mods], reps=5)
+            res[f"monarch_swiglu_mlp/{chain}/n{n}"] = {"us_per_mlp": round(us, 2)}
+        del mods
+        torch.cuda.empty_cache()
     return res
 
 

@@ -71,14 +71,45 @@ def triton_monarch_right_left_fp32(x, w1_bfly, w2_bfly):
     return out, None, out1, None
 
 
-def monarch_torch_layout(x, w1_t, w2_t):
+def monarch_torch_layout(x, w1_t, w2_t, ideal: bool = False):
     """Same operator on the reference's torch layouts (torch_funcs/monarch_funcs.py:4-45):
-    w1_t (b, rank, P), w2_t (b, Q, rank); returns out2 only."""
+    w1_t (b, rank, P), w2_t (b, Q, rank); returns out2 only.  ideal = True leaves the output in the block-major order
+    of the reference's right_ideal variant (feature l*S + s, monarch_kernels.py:1004) for a consumer that takes it
+    that way (ideal_order_index, fold_ideal_order_into_dense)."""
     b, rank, p = w1_t.shape
     l, s, r = w2_t.shape
     assert b == l and r == rank and b * p == x.shape[-1] and rank % b == 0
-    out = ops.monarch(ops._flat2d(x), w1_t, w2_t, L.KMAJOR, L.COLS_TORCH, L.KMAJOR, b, p, rank, s, L.OUT_INTERLEAVED)
+    out = ops.monarch(ops._flat2d(x), w1_t, w2_t, L.KMAJOR, L.COLS_TORCH, L.KMAJOR, b, p, rank, s,
+                      L.OUT_BLOCKED if ideal else L.OUT_INTERLEAVED)
     return ops._like_input(out, x)
+
+
+# ------------------------------------------------------------------- chaining on the un-interleaved (right_ideal) order
+# The reference's Llama configuration runs gate_proj and up_proj with the right_ideal variant, which skips the final
+# interleave and "assumes the next layer absorbs the permutation" (configs/networks/llama7b.yaml:164,180,
+# monarch_kernels.py:961-1005).  What absorbing means for the layer that follows:
+#   * an element-wise step (silu(gate) * up) is order-blind: both operands arrive in the same order;
+#   * a dense layer absorbs it exactly by a permutation of its input columns (fold_ideal_order_into_dense);
+#   * a Monarch layer with the same block count takes block l of the ideal order (the S outputs of second-stage block
+#     l) as its input block l.  That is a different linear map from the same factors on the interleaved order, and no
+#     re-packing of block-diagonal factors can turn one into the other (an input block of the interleaved order mixes
+#     all l): a chained Monarch MLP is a model of its own, trained in that order, as in the reference's configuration.
+def ideal_order_index(features: int, b: int, device=None):
+    """idx with y_ideal[..., idx] == y_interleaved: position of interleaved feature s*b + l in the ideal order, l*S + s."""
+    import torch
+    assert features % b == 0
+    S = features // b
+    f = torch.arange(features, device=device)
+    return (f % b) * S + f // b
+
+
+def fold_ideal_order_into_dense(weight, b: int):
+    """weight (O, I) of a dense layer fed with an interleaved Monarch output -> the weight that gives the same result
+    on the ideal-order output: W'[:, l*S + s] = W[:, s*b + l]."""
+    idx = ideal_order_index(weight.shape[-1], b, weight.device)
+    out = weight.new_empty(weight.shape)
+    out[..., idx] = weight
+    return out
 
 
 def get_triton_monarch_right_fp16_config():

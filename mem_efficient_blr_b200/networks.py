@@ -155,6 +155,32 @@ def structured_multi(mods, x, x_mul=None, residual=None):
     return [m(xe) if residual is None else residual + m(xe) for m in mods]
 
 
+class MonarchSwiGLU(nn.Module):
+    """SwiGLU MLP on Monarch linears, torch layouts (w1_t (b, rank, P), w2_t (b, Qs, rank)): down(silu(gate(x)) * up(x)).
+    chain = "ideal": gate and up leave their outputs in the block-major order of the reference's right_ideal variant
+    (no interleave; contiguous stores) and down takes block l of that order as its input block l - the chaining of
+    configs/networks/llama7b.yaml:164,180; "interleaved": every layer emits the interleaved order (the reference's
+    `right`).  The two are different networks on the same factors (monarch_kernels.ideal_order_index)."""
+
+    def __init__(self, d, ffn, b, rank, chain="ideal", device="cuda", dtype=torch.float16, generator=None):
+        super().__init__()
+        assert chain in ("ideal", "interleaved") and d % b == 0 and ffn % b == 0 and rank % b == 0
+        self.d, self.ffn, self.b, self.rank, self.chain = d, ffn, b, rank, chain
+        gd = generator.device if generator is not None else "cpu"
+        rn = lambda *s: torch.randn(*s, generator=generator, device=gd)
+        mk_ = lambda t: nn.Parameter(t.to(device=device, dtype=dtype), requires_grad=False)
+        for name, (i_f, o_f) in (("gate", (d, ffn)), ("up", (d, ffn)), ("down", (ffn, d))):
+            setattr(self, name + "_w1", mk_(rn(b, rank, i_f // b) / math.sqrt(i_f // b)))
+            setattr(self, name + "_w2", mk_(rn(b, o_f // b, rank) / math.sqrt(rank)))
+
+    def forward(self, x):
+        from . import monarch_kernels as mk
+        ideal = self.chain == "ideal"
+        g = mk.monarch_torch_layout(x, self.gate_w1, self.gate_w2, ideal)
+        u = mk.monarch_torch_layout(x, self.up_w1, self.up_w2, ideal)
+        return mk.monarch_torch_layout(F.silu(g) * u, self.down_w1, self.down_w2)
+
+
 # ------------------------------------------------------------------------------------------------ Llama-shaped decoder
 @dataclass
 class LlamaShape:

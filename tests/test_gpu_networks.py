@@ -114,3 +114,35 @@ def test_packed_weight_file_rebuilds_the_quantised_decoder(tmp_path, bits):
     p0 = "layers.0.q_proj" if "layers.0.q_proj" in layers2 else sorted(layers2)[0]
     U = ops.dequantize_sym(loaded[p0 + ".Uq"], loaded[p0 + ".u_scale"], bits, 0, torch.float16)
     assert torch.equal(state[p0 + ".U"], U) and p0 + ".Uq" not in state
+
+
+# ------------------------------------------------------------------------------------------------ right_ideal chaining
+@pytest.mark.parametrize("n", [1, 16, 200])
+@pytest.mark.parametrize("chain", ["ideal", "interleaved"])
+def test_monarch_swiglu_chained_on_the_ideal_order(chain, n):
+    """gate / up in the reference's right_ideal order feeding down directly, against the oracle composition; and the
+    dense layer with folded input columns that consumes the same activations."""
+    from mem_efficient_blr_b200 import networks as nw, monarch_kernels as mk
+    d, ffn, b, rank = 512, 1024, 4, 128
+    g = torch.Generator().manual_seed(5)
+    m = nw.MonarchSwiGLU(d, ffn, b, rank, chain, generator=g)
+    x = torch.randn(n, d, generator=g).half()
+    cpu = lambda t: t.detach().float().cpu()
+    gate = orc.monarch(x, cpu(m.gate_w1), cpu(m.gate_w2))[0]
+    up = orc.monarch(x, cpu(m.up_w1), cpu(m.up_w2))[0]
+    if chain == "ideal":
+        gate, up = orc.monarch_ideal_order(gate, b), orc.monarch_ideal_order(up, b)
+    act = (torch.nn.functional.silu(gate.half().float()) * up.half().float()).half()
+    ref = orc.monarch(act, cpu(m.down_w1), cpu(m.down_w2))[0]
+    got = m(x.cuda())
+    torch.cuda.synchronize()
+    assert orc.rel_fro(got.float().cpu(), ref) < 1e-2
+    if chain == "ideal":
+        # a dense consumer absorbs the order by a column permutation
+        W = (torch.randn(d, ffn, generator=g) / ffn ** 0.5).half()
+        y_ideal = mk.monarch_torch_layout(x.cuda(), m.gate_w1, m.gate_w2, ideal=True)
+        y_int = mk.monarch_torch_layout(x.cuda(), m.gate_w1, m.gate_w2)
+        a = torch.nn.functional.linear(y_ideal, mk.fold_ideal_order_into_dense(W.cuda(), b))
+        bb = torch.nn.functional.linear(y_int, W.cuda())
+        torch.cuda.synchronize()
+        assert orc.rel_fro(a.float().cpu(), bb.float().cpu()) < 2e-3

@@ -44,3 +44,18 @@ def test_vit_shapes_and_rank_rule():
     m = nw.ViTEncoder(small, "dense", device="cpu", dtype=torch.float32)
     out = m(torch.randn(2, 3, 32, 32))
     assert out.shape == (2, 5, 64) and len(m.structured_linears()) == 3
+
+
+def test_ideal_order_index_and_dense_folding_on_cpu():
+    """The block-major (right_ideal) order against the oracle's re-ordering, and a dense layer that absorbs it."""
+    from mem_efficient_blr_b200 import monarch_kernels as mk
+    from oracle import blr_oracle as orc
+    b, S, O = 4, 6, 5
+    g = torch.Generator().manual_seed(0)
+    y_int = torch.randn(3, S * b, generator=g)
+    y_ideal = orc.monarch_ideal_order(y_int, b)
+    idx = mk.ideal_order_index(S * b, b)
+    assert torch.equal(y_ideal[..., idx], y_int)
+    W = torch.randn(O, S * b, generator=g)
+    Wf = mk.fold_ideal_order_into_dense(W, b)
+    assert torch.allclose(y_ideal @ Wf.T, y_int @ W.T, atol=1e-6)
