@@ -12,7 +12,8 @@ of every launch, divided by device time), summed over ranks.
 Beside the headline the same JSON line carries, in top-level keys: the per-point times with the dense fp16
 cuBLAS bar (`sweep`), the layer sweep over all Llama-7B projections and operator families (`layer_sweep`), a
 Llama-7B-shaped decoder with BLAST linears - prefill at 2048 tokens and decode at batch 1/4/16/64 against a
-2048-token cache, 16-bit and int8 factors - and a ViT-B/16-shaped encoder (`llama7b_blast`, `vit_b16_blast`),
+2048-token cache, 16-bit and int8 factors - a ViT-B/16-shaped encoder and a DiT-XL/2-shaped denoiser (`llama7b_blast`,
+`vit_b16_blast`, `dit_xl2_blast`),
 and, on more than one GPU, BLAST sharded by output block with an all-gather (`row_block_sharding`).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
@@ -324,6 +325,27 @@ def vit_leg(dev, rank, world, dist, quick):
     return out
 
 
+def dit_leg(dev, rank, world, dist, quick):
+    """DiT-XL/2-shaped denoiser (256 tokens per 32 x 32 x 4 latent), attn.qkv / mlp.fc1 / adaLN linear as BLAST b = 9 with
+    the ranks of the reference's configs/networks/dit_xl.yaml; denoising steps (forward passes) per second at several
+    batch sizes, independent batches per rank."""
+    from mem_efficient_blr_b200 import networks as nw
+    shape = nw.DiTShape()
+    model = nw.DiTDenoiser(shape, "blast", device=dev, dtype=torch.float16, seed=rank, init_on_device=True)
+    out = {"shape": {"layers": shape.layers, "d": shape.d, "heads": shape.heads, "mlp": shape.mlp, "tokens": 256,
+                     "blast_b": shape.b, "ranks": shape.ranks}, "dtype": "f16", "parallelism": f"dp{world} (latent batches per rank)"}
+    for B in ((1, 16) if quick else (1, 8, 64)):
+        lat = torch.randn(B, shape.channels, shape.latent, shape.latent, device=dev, dtype=torch.float16)
+        t = torch.randint(0, 1000, (B,), device=dev)
+        y = torch.randint(0, shape.classes, (B,), device=dev)
+        ms = time_ms(lambda: model(lat, t, y), 5, warm=2)
+        (ms,) = max_over_ranks(dist, dev, [ms])
+        out[f"batch{B}"] = {"ms": ms, "latents_per_s": world * B / (ms * 1e-3), "tokens_per_s": world * B * 256 / (ms * 1e-3)}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def sharding_leg(dev, rank, world, dist):
     """BLAST sharded by output block over the ranks (gate_proj shape with the 50 %-parameter rank): every rank holds
     b / world blocks of U and S and all of V, computes its columns, and one NCCL all_gather along the feature axis
@@ -615,10 +637,11 @@ def run_ours(args):
     torch.cuda.empty_cache()
 
     # ---- network level and sharding (all ranks take part; rank 0 reports)
-    llama = vit = shard = None
+    llama = vit = dit = shard = None
     if not args.no_context:
         llama = llama_leg(dev, rank, world, dist, args.quick)
         vit = vit_leg(dev, rank, world, dist, args.quick)
+        dit = dit_leg(dev, rank, world, dist, args.quick)
         if world > 1 and B_BLK % world == 0:
             shard = sharding_leg(dev, rank, world, dist)
 
@@ -659,6 +682,7 @@ def run_ours(args):
             "sweep": sweep,
             "llama7b_blast": llama,
             "vit_b16_blast": vit,
+            "dit_xl2_blast": dit,
             "row_block_sharding": shard,
             "layer_sweep": lsweep,
         }

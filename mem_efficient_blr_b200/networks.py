@@ -1,4 +1,5 @@
-"""Network-level glue around the structured linears: a Llama-7B-shaped decoder and a ViT-B/16-shaped encoder.
+"""Network-level glue around the structured linears: a Llama-7B-shaped decoder, a ViT-B/16-shaped encoder and a
+DiT-XL/2-shaped denoiser.
 
 The reference times whole HuggingFace models whose nn.Linear layers were swapped for its structured modules
 (models/llama7b.py:24-92, models/vit_b_patch16_224.py:69-131, utils.py:46-116).  No checkpoint or tokenizer can be
@@ -393,6 +394,105 @@ class ViTEncoder(nn.Module):
         for layer in self.layers:
             x = layer(x)
         return self.ln(x)
+
+
+# ------------------------------------------------------------------------------------------------ DiT-shaped denoiser
+@dataclass
+class DiTShape:
+    """DiT-XL/2 on 32 x 32 x 4 latents (256 x 256 images): 28 blocks, d = 1152, 16 heads, MLP 4608, patch 2 -> 256
+    tokens, 1000 classes, adaLN-Zero conditioning on timestep + class.  Structured linears and their BLAST settings as
+    in the reference's configs/networks/dit_xl.yaml: attn.qkv (rank 384), mlp.fc1 (256), adaLN_modulation.1 (256),
+    all with b = 9; attn.proj and mlp.fc2 stay dense."""
+    layers: int = 28
+    d: int = 1152
+    heads: int = 16
+    mlp: int = 4608
+    latent: int = 32
+    patch: int = 2
+    channels: int = 4
+    classes: int = 1000
+    b: int = 9
+    freq: int = 256
+    eps: float = 1e-6
+    ranks: dict = field(default_factory=lambda: {"qkv": 384, "fc1": 256, "adaln": 256})
+
+
+def _modulate(x, shift, scale):
+    return x * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+
+
+class DiTBlock(nn.Module):
+    """x <- x + gate_a * attn(mod(norm(x))), x <- x + gate_m * mlp(mod(norm(x))); the six modulation vectors come
+    from one linear on silu(c), c (B, d) the conditioning of the image (one token per image: a decode-size call)."""
+
+    def __init__(self, shape: DiTShape, method: str, device, dtype, generator):
+        super().__init__()
+        s = shape
+        mk = lambda i, o, r: make_linear(method, i, o, s.b, r, True, device, dtype, generator)
+        dense = lambda i, o: make_linear("dense", i, o, 0, 0, True, device, dtype, generator)
+        self.heads = s.heads
+        self.qkv = mk(s.d, 3 * s.d, s.ranks["qkv"])
+        self.proj = dense(s.d, s.d)
+        self.fc1 = mk(s.d, s.mlp, s.ranks["fc1"])
+        self.fc2 = dense(s.mlp, s.d)
+        self.adaln = mk(s.d, 6 * s.d, s.ranks["adaln"])
+        self.norm1 = nn.LayerNorm(s.d, eps=s.eps, elementwise_affine=False, device=device, dtype=dtype)
+        self.norm2 = nn.LayerNorm(s.d, eps=s.eps, elementwise_affine=False, device=device, dtype=dtype)
+
+    def structured(self):
+        return [self.qkv, self.fc1, self.adaln]
+
+    def forward(self, x, c):
+        B, T, d = x.shape
+        sa, ca, ga, sm, cm, gm = self.adaln(F.silu(c)).chunk(6, dim=1)
+        q, k, v = self.qkv(_modulate(self.norm1(x), sa, ca)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v)
+        x = x + ga.unsqueeze(1) * self.proj(a.transpose(1, 2).reshape(B, T, d))
+        return x + gm.unsqueeze(1) * self.fc2(F.gelu(self.fc1(_modulate(self.norm2(x), sm, cm)), approximate="tanh"))
+
+
+class DiTDenoiser(nn.Module):
+    """Latents (B, C, H, W), timesteps (B,), class labels (B,) -> (B, 2C, H, W) (noise and variance channels).  Patch
+    embedding, positional embedding, timestep MLP on sinusoidal features, class embedding, the blocks, and an
+    adaLN-modulated linear back to patches.  Random weights of the shape (no checkpoint can be fetched here)."""
+
+    def __init__(self, shape: DiTShape, method: str, device="cuda", dtype=torch.float16, seed=0, init_on_device: bool = False):
+        super().__init__()
+        g = torch.Generator(device=device if init_on_device else "cpu").manual_seed(seed)
+        s = shape
+        self.shape, self.method = shape, method
+        self.x_embed = nn.Conv2d(s.channels, s.d, s.patch, s.patch, device=device, dtype=dtype).requires_grad_(False)
+        ntok = (s.latent // s.patch) ** 2
+        self.posemb = nn.Parameter((torch.randn(1, ntok, s.d, generator=g, device=g.device) * 0.02).to(device=device, dtype=dtype), requires_grad=False)
+        dense = lambda i, o: make_linear("dense", i, o, 0, 0, True, device, dtype, g)
+        self.t_fc1, self.t_fc2 = dense(s.freq, s.d), dense(s.d, s.d)
+        self.y_embed = nn.Embedding(s.classes + 1, s.d, device=device, dtype=dtype).requires_grad_(False)
+        self.blocks = nn.ModuleList(DiTBlock(s, method, device, dtype, g) for _ in range(s.layers))
+        self.final_norm = nn.LayerNorm(s.d, eps=s.eps, elementwise_affine=False, device=device, dtype=dtype)
+        self.final_adaln = dense(s.d, 2 * s.d)
+        self.final = dense(s.d, s.patch * s.patch * 2 * s.channels)
+        half = s.freq // 2
+        self.register_buffer("freqs", torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / half).to(device), persistent=False)
+
+    def structured_linears(self):
+        return [m for blk in self.blocks for m in blk.structured()]
+
+    @torch.no_grad()
+    def forward(self, latents: torch.Tensor, t: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        s = self.shape
+        B = latents.shape[0]
+        x = self.x_embed(latents).flatten(2).transpose(1, 2) + self.posemb
+        ang = t.float()[:, None] * self.freqs[None]
+        temb = torch.cat((ang.cos(), ang.sin()), dim=-1).to(x.dtype)
+        c = self.t_fc2(F.silu(self.t_fc1(temb))) + self.y_embed(y)
+        for blk in self.blocks:
+            x = blk(x, c)
+        shift, scale = self.final_adaln(F.silu(c)).chunk(2, dim=1)
+        x = self.final(_modulate(self.final_norm(x), shift, scale))
+        # patches back to the image grid: (B, h, w, p, p, C) -> (B, C, h p, w p)
+        h = s.latent // s.patch
+        x = x.view(B, h, h, s.patch, s.patch, 2 * s.channels).permute(0, 5, 1, 3, 2, 4)
+        return x.reshape(B, 2 * s.channels, h * s.patch, h * s.patch)
 
 
 # ------------------------------------------------------------------------------------------------ CUDA-graph replay

@@ -77,6 +77,29 @@ def test_vit_shaped_encoder_matches_oracle_backed_twin():
     assert orc.rel_fro(got.float().cpu(), want) < TOL
 
 
+def test_dit_shaped_denoiser_matches_oracle_backed_twin():
+    """DiT block structure (adaLN-Zero modulation from one conditioning token per image, attention, tanh-GELU MLP) with
+    the reference's swap list (qkv, fc1, adaLN linear; b = 9 blocks) against the twin on the oracle's BLAST."""
+    from mem_efficient_blr_b200 import networks as nw
+    shape = nw.DiTShape(layers=2, d=144, heads=4, mlp=288, latent=8, patch=2, channels=4, classes=10, b=9, freq=32,
+                        ranks={"qkv": 32, "fc1": 24, "adaln": 16})
+    g = torch.Generator().manual_seed(3)
+    lat = torch.randn(3, 4, 8, 8, generator=g)
+    t = torch.tensor([5.0, 400.0, 999.0])
+    y = torch.tensor([0, 7, 10])
+    gpu = nw.DiTDenoiser(shape, "blast", device=DEV, dtype=torch.float16, seed=4)
+    cpu = nw.DiTDenoiser(shape, "blast", device="cpu", dtype=torch.float32, seed=4)
+    cpu.load_state_dict({k: v.float().cpu() for k, v in gpu.state_dict().items()})
+    _round_params_like(cpu, torch.float16)
+    cpu.freqs.copy_(gpu.freqs.cpu())   # the fp32 frequency table is not a 16-bit weight: undo its rounding
+    _oracle_linears(nw, cpu, 16)
+    got = gpu(lat.to(DEV, torch.float16), t.to(DEV), y.to(DEV))
+    torch.cuda.synchronize()
+    want = cpu(lat.half().float(), t, y)
+    assert got.shape == (3, 8, 8, 8)
+    assert orc.rel_fro(got.float().cpu(), want) < TOL
+
+
 # ------------------------------------------------------------------------------------------------ packed-weight files
 @pytest.mark.parametrize("bits", [8, 4])
 def test_packed_weight_file_rebuilds_the_quantised_decoder(tmp_path, bits):
