@@ -78,7 +78,9 @@ int blr_debug_decode_path(int which);
 const char* blr_last_error(void);
 
 /* Bytes of scratch a call needs: `groups` blocks, `width` intermediate features per block, N tokens
- * (BLAST: b, R; Monarch: b, rank; low-rank: 1, R; dense: 0, 0).  No reference counterpart: the
+ * (BLAST: b, R; Monarch: b, rank; low-rank: 1, R; dense: 0, 0).  The size stops growing with N once the 16-bit
+ * intermediates of a call would outgrow the L2 cache (128 MB per intermediate): such a call runs as consecutive passes
+ * over equal parts of the tokens on the same scratch.  No reference counterpart: the
  * reference allocates its intermediates with torch.empty per call (blast_kernels.py:1967, 2703). */
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width);
 

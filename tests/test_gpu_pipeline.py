@@ -298,3 +298,44 @@ def test_coupling_entry_points_check_their_arguments(K):
     assert lib.blr_blast_expand_coupling(None, *args[1:], 128, 0, E.data_ptr(), need, st) == -1  # BLR_ERR_ARG
     assert lib.blr_blast_expand_coupling(*args, 128, 0, E.data_ptr(), need, st) == 0
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------- many tokens: passes over parts of the batch
+def test_token_counts_beyond_one_pass_run_as_passes_on_a_capped_workspace(K):
+    """When the 16-bit intermediates of a call would outgrow L2 the call runs as passes over equal parts of the tokens;
+    a token's result does not depend on which pass it is in, and the workspace stops growing."""
+    from mem_efficient_blr_b200 import _lib as L
+    lib = L.load()
+    assert lib.blr_workspace_bytes(9000, 16, 1024) == lib.blr_workspace_bytes(3072, 16, 1024) < lib.blr_workspace_bytes(4096, 16, 1024)
+    assert lib.blr_workspace_bytes(4096, 16, 1024) == lib.blr_workspace_bytes(8192, 16, 1024)
+    g = torch.Generator().manual_seed(12)
+    # BLAST, b = 16, R = 1024: 4096 tokens per pass at most -> 9000 tokens in three passes of 3072, 3072, 2856
+    N, b, P, Q, R = 9000, 16, 16, 16, 1024
+    x = torch.randn(N, b * P, generator=g).half()
+    U = (torch.randn(b, Q, R, generator=g) / R ** 0.5).half()
+    Vt = (torch.randn(b, R, P, generator=g) / P ** 0.5).half()
+    S = (torch.rand(b, b, R, generator=g) + 0.5).half()
+    xd, Ud, Vd, Sd = _cuda(x, U, Vt, S)
+    whole = K.bk.blast_torch_layout(xd, Ud, Vd, Sd)
+    parts = torch.cat([K.bk.blast_torch_layout(xd[i:i + 3000], Ud, Vd, Sd) for i in range(0, N, 3000)])
+    torch.cuda.synchronize()
+    assert torch.equal(whole, parts)
+    rows = torch.cat((torch.arange(0, 40), torch.arange(3050, 3100), torch.arange(N - 40, N)))
+    assert _err(whole[rows.to(DEV)], orc.blast(x[rows], U, Vt, S)[0]) < TOL
+    # the same with int8 factors widened inside the GEMMs (the C entry point; 300 tokens per slice keep the same kernels)
+    from mem_efficient_blr_b200 import ops
+    Uq, us, Vq, vs = K.bq.quantize_blast_factors(Ud, Vd, 8)
+    wq = ops.blast_wq(xd, Uq, us, Vq, vs, Sd, b * R, R, 1, 8, 0, b, P, Q, R)
+    wq_parts = torch.cat([ops.blast_wq(xd[i:i + 3000], Uq, us, Vq, vs, Sd, b * R, R, 1, 8, 0, b, P, Q, R) for i in range(0, N, 3000)])
+    torch.cuda.synchronize()
+    assert torch.equal(wq, wq_parts)
+    # Monarch, 4 blocks, rank 1024: 16384 tokens per pass at most
+    N2, I2, O2, b2, rank = 20000, 256, 256, 4, 1024
+    x2, w1, w2 = orc.make_monarch_inputs(N2, I2, O2, b2, rank, torch.float16, seed=3)
+    x2d, w1d, w2d = _cuda(x2.reshape(N2, I2), w1, w2)
+    whole2 = K.mk.monarch_torch_layout(x2d, w1d, w2d)
+    parts2 = torch.cat([K.mk.monarch_torch_layout(x2d[i:i + 5000], w1d, w2d) for i in range(0, N2, 5000)])
+    torch.cuda.synchronize()
+    assert torch.equal(whole2, parts2)
+    rows2 = torch.cat((torch.arange(0, 40), torch.arange(N2 - 40, N2)))
+    assert _err(whole2[rows2.to(DEV)], orc.monarch(x2.reshape(N2, I2)[rows2], w1, w2)[0]) < TOL
