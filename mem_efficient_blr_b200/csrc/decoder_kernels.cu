@@ -127,24 +127,24 @@ __global__ void __launch_bounds__(256) rope_append_kernel(uint16_t* __restrict__
 // ------------------------------------------------------------------------------------------------ attention of one token over the cache
 // CTA (split, head, sequence): keys [k0, k0 + ks) of the head's cache.  A key (and value) row of hd 16-bit values is
 // read by hd / 8 neighbouring lanes, 16 bytes each, so a warp's load covers whole rows back to back; a lane keeps its
-// 8 values of q in registers.  Phase A: dot products (reduced over a row's lanes by shuffles), block maximum, exp and
-// sum.  Phase B: every lane accumulates its 8 output dimensions over the keys of its row slot; the slots' sums meet
-// in shared memory.  Partial result (unnormalised output, maximum, sum) per split; the combine kernel merges the
+// 8 values of q in registers.  One pass with a running maximum per row slot (a warp's position in its load): the dot
+// product is reduced over the row's lanes by shuffles, the slot's sum and its 8 output dimensions per lane are rescaled
+// when the maximum moves; the slots' (maximum, sum, output) meet in shared memory at the end.  Partial result (unnormalised output, maximum, sum) per split; the combine kernel merges the
 // splits of a head.  hd / 8 must divide 32 (hd = 8, 16, 32, 64, 128 or 256).
 static constexpr int kAttnThreads = 256;
 
 template <bool BF16>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(const uint16_t* __restrict__ q, long long ldq,
+__global__ void __launch_bounds__(kAttnThreads, 3) attn_decode_partial_kernel(const uint16_t* __restrict__ q, long long ldq,
                                                                          const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                                                                          int H, int hd, int slots, int n_keys, int ks, float scale,
                                                                          float* __restrict__ part) {
-  extern __shared__ float sm[];  // p[ks] | red[16] | acc[256][8]
-  float* ps = sm;
-  float* red = ps + ((ks + 3) & ~3);  // (keeps the float4 stores into acc[] 16-byte aligned)
-  float* accs = red + 16;
+  extern __shared__ float sm[];  // per slot (warp, key of the warp's load): maximum, sum | acc[slot][hd]
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int lpk = hd >> 3, kpw = 32 / lpk, sub = lane / lpk, piece = lane - sub * lpk;
+  const int nslot = (kAttnThreads / 32) * kpw;
+  float* ml = sm;               // [nslot][2]
+  float* accs = sm + 2 * nslot;  // [nslot][hd]
   const int k0 = split * ks, nk = min(ks, n_keys - k0), kstep = (kAttnThreads / 32) * kpw;
   const uint16_t* kh = kc + (((long long)b * H + h) * slots + k0) * hd + piece * 8;
   const uint16_t* vh = vc + (((long long)b * H + h) * slots + k0) * hd + piece * 8;
@@ -160,78 +160,74 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(const
       qf[2 * i + 1] = f.y * scale;
     }
   }
-  // ---- scores
-  float m = -3.0e38f;
-#pragma unroll 4
-  for (int j0 = warp * kpw; j0 < nk; j0 += kstep) {  // warp-uniform bounds
-    const int j = j0 + sub;
-    float s = 0.f;
-    if (j < nk) {
-      const uint4 v = *reinterpret_cast<const uint4*>(kh + (long long)j * hd);
-      const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = up2<BF16>(ws[i]);
-        s = fmaf(f.x, qf[2 * i], fmaf(f.y, qf[2 * i + 1], s));
-      }
-    }
-    for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (j < nk) {
-      if (piece == 0) ps[j] = s;
-      m = fmaxf(m, s);
-    }
-  }
-  m = warp_maxf(m);
-  if (lane == 0) red[warp] = m;
-  __syncthreads();
-  m = red[0];
-#pragma unroll
-  for (int i = 1; i < kAttnThreads / 32; ++i) m = fmaxf(m, red[i]);
-  float l = 0.f;
-  for (int j = tid; j < nk; j += kAttnThreads) {
-    const float p = __expf(ps[j] - m);
-    ps[j] = p;
-    l += p;
-  }
-  l = warp_sum(l);
-  if (lane == 0) red[8 + warp] = l;
-  __syncthreads();
-  // ---- weighted sum of the values
+  // ---- one pass over the keys with a running maximum: the key and the value row of a step are loaded together, so
+  // both streams are in flight all the time and nothing waits at a barrier between them
+  float m = -3.0e38f, l = 0.f;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-  for (int j0 = warp * kpw; j0 < nk; j0 += kstep) {
-    const int j = j0 + sub;
-    if (j < nk) {
-      const uint4 v = *reinterpret_cast<const uint4*>(vh + (long long)j * hd);
-      const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
-      const float p = ps[j];
+  constexpr int kAhead = 4;  // steps whose key and value rows are requested before the first is used
+#pragma unroll 1
+  for (int j0 = warp * kpw; j0 < nk; j0 += kAhead * kstep) {  // warp-uniform bounds
+    uint4 kv[kAhead], vv[kAhead];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = up2<BF16>(ws[i]);
-        acc[2 * i] = fmaf(p, f.x, acc[2 * i]);
-        acc[2 * i + 1] = fmaf(p, f.y, acc[2 * i + 1]);
+    for (int u = 0; u < kAhead; ++u) {
+      const int j = j0 + u * kstep + sub;
+      kv[u] = vv[u] = make_uint4(0, 0, 0, 0);
+      if (j < nk) {
+        kv[u] = *reinterpret_cast<const uint4*>(kh + (long long)j * hd);
+        vv[u] = *reinterpret_cast<const uint4*>(vh + (long long)j * hd);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int j = j0 + u * kstep + sub;
+      float s = 0.f;
+      {
+        const uint32_t ws[4] = {kv[u].x, kv[u].y, kv[u].z, kv[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = up2<BF16>(ws[i]);
+          s = fmaf(f.x, qf[2 * i], fmaf(f.y, qf[2 * i + 1], s));
+        }
+      }
+      for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (j < nk) {
+        const float mn = fmaxf(m, s), corr = __expf(m - mn), p = __expf(s - mn);
+        m = mn;
+        l = fmaf(l, corr, p);
+        const uint32_t ws[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = up2<BF16>(ws[i]);
+          acc[2 * i] = fmaf(acc[2 * i], corr, p * f.x);
+          acc[2 * i + 1] = fmaf(acc[2 * i + 1], corr, p * f.y);
+        }
       }
     }
   }
-  // slot (warp, sub) holds a partial sum of all hd dimensions: [slot][hd]
+  // slot (warp, sub): maximum, sum and the partial output over all hd dimensions
   {
-    float* a = accs + ((warp * kpw + sub) * hd + piece * 8);
+    const int slot = warp * kpw + sub;
+    if (piece == 0) {
+      ml[2 * slot] = m;
+      ml[2 * slot + 1] = l;
+    }
+    float* a = accs + (slot * hd + piece * 8);
     *reinterpret_cast<float4*>(a) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     *reinterpret_cast<float4*>(a + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
   __syncthreads();
+  float M = -3.0e38f;
+  for (int g = 0; g < nslot; ++g) M = fmaxf(M, ml[2 * g]);
   float* dst = part + (((long long)b * H + h) * gridDim.x + split) * (hd + 2);
-  const int nslot = (kAttnThreads / 32) * kpw;
   for (int d = tid; d < hd; d += kAttnThreads) {
-    float o = accs[d];
-    for (int g = 1; g < nslot; ++g) o += accs[g * hd + d];
+    float o = 0.f;
+    for (int g = 0; g < nslot; ++g) o = fmaf(accs[g * hd + d], __expf(ml[2 * g] - M), o);  // (empty slots: 0 * exp(0))
     dst[d] = o;
   }
   if (tid == 0) {
     float lt = 0.f;
-#pragma unroll
-    for (int i = 0; i < kAttnThreads / 32; ++i) lt += red[8 + i];
-    dst[hd] = m;
+    for (int g = 0; g < nslot; ++g) lt = fmaf(ml[2 * g + 1], __expf(ml[2 * g] - M), lt);
+    dst[hd] = M;
     dst[hd + 1] = lt;
   }
 }
@@ -275,11 +271,21 @@ static int launch_pdl(K kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s
   return BLR_OK;
 }
 
+// Splits of a head's keys.  Three CTAs share an SM, so the grid runs in waves of 3 x 148 CTAs and a wave that is
+// nearly empty costs as much as a full one (16 sequences x 32 heads in one split each are 1.15 waves: 3.8 TB/s).
+// Among 1..16 splits of at least 128 keys, take the one with the smallest waves x (keys per CTA + a CTA's fixed cost,
+// about the time of 96 keys).
 static int attn_splits(int64_t B, int H, int n_keys) {
-  int ns = (int)((2 * 148 + B * H - 1) / (B * H));
-  if (ns > 8) ns = 8;
-  while (ns > 1 && (n_keys + ns - 1) / ns < 64) --ns;
-  return ns < 1 ? 1 : ns;
+  const int64_t wave = 3 * 148;
+  int best = 1;
+  int64_t best_cost = -1;
+  for (int ns = 1; ns <= 16; ++ns) {
+    const int keys = (n_keys + ns - 1) / ns;
+    if (ns > 1 && keys < 128) break;
+    const int64_t waves = (B * H * ns + wave - 1) / wave, cost = waves * (keys + 96);
+    if (best_cost < 0 || cost < best_cost) best = ns, best_cost = cost;
+  }
+  return best;
 }
 
 }  // namespace blr
@@ -354,8 +360,8 @@ int blr_attention_decode(const void* q, int64_t ldq, const void* k_cache, const 
               "attention_decode needs 16-byte aligned caches and q, 4-byte aligned out");
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int ns = attn_splits(n_seq, heads, n_keys), ks = (n_keys + ns - 1) / ns;
-  const size_t smem = (size_t)(((ks + 3) & ~3) + 16 + kAttnThreads * 8) * sizeof(float);
-  BLR_REQUIRE(smem <= 200 * 1024, BLR_ERR_UNSUPPORTED, "attention_decode: %d keys per CTA need %zu bytes of shared memory", ks, smem);
+  const int nslot = (kAttnThreads / 32) * (32 / (head_dim >> 3));
+  const size_t smem = (size_t)nslot * (head_dim + 2) * sizeof(float);  // 8 KB + 2 floats per slot for every head size
   const uint16_t* qp = static_cast<const uint16_t*>(q);
   const uint16_t* kp = static_cast<const uint16_t*>(k_cache);
   const uint16_t* vp = static_cast<const uint16_t*>(v_cache);

@@ -227,7 +227,11 @@ class LlamaLayer(nn.Module):
         super().__init__()
         s, mk = shape, lambda i, o, r: make_linear(method, i, o, shape.b, r, False, device, dtype, generator)
         self.heads, self.hd = s.heads, s.d // s.heads
-        self.fused_attention_max_batch = 16   # measured crossover against torch's scaled_dot_product_attention (2048 keys)
+        # Batches up to this size use the package's attention kernel (ops.attention_decode), larger ones torch's
+        # scaled_dot_product_attention.  Measured through the whole decode step at 2048 keys (ms, torch | package):
+        # batch 1 3.08 | 3.23, 4: 3.94 | 4.28, 16: 7.34 | 8.56, 64: 15.5 | 18.0 - torch's flash-decoding kernel streams the
+        # cache at 6.3 - 7.3 TB/s, the package's at 4.4 - 5.7: the library kernel serves every batch size.
+        self.fused_attention_max_batch = 0
         self.q_proj, self.k_proj, self.v_proj, self.o_proj = (mk(s.d, s.d, s.rank_attn) for _ in range(4))
         self.gate_proj, self.up_proj = mk(s.d, s.ffn, s.rank_mlp), mk(s.d, s.ffn, s.rank_mlp)
         self.down_proj = mk(s.ffn, s.d, s.rank_mlp)
@@ -247,7 +251,7 @@ class LlamaLayer(nn.Module):
         ops.rope_append(q, k, v, cos_table, sin_table, pos, kc, vc, 1)
         if B <= self.fused_attention_max_batch:
             a = ops.attention_decode(q, kc, vc)
-        else:  # large batches stream gigabytes of cache per layer: torch's flash-decoding kernel is the faster one there
+        else:
             a = F.scaled_dot_product_attention(q.view(B, self.heads, 1, self.hd), kc, vc).view(B, d)
         (x,) = structured_multi([self.o_proj], a.view(B, 1, d), residual=x)
         h = self.post_attention_layernorm(x)

@@ -55,6 +55,12 @@ def test_llama_shaped_decoder_matches_oracle_backed_twin(method, bits):
     again = step(ids[:, T - 1:].to(DEV), torch.tensor([T - 1], device=DEV))
     torch.cuda.synchronize()
     assert orc.rel_fro(again.float().cpu(), got_d.float().cpu()) < 1e-3
+    # the same step with the package's own attention kernel instead of torch's
+    for layer in gpu.layers:
+        layer.fused_attention_max_batch = B
+    own = gpu.decode_step(ids[:, T - 1:].to(DEV), torch.tensor([T - 1], device=DEV))
+    torch.cuda.synchronize()
+    assert orc.rel_fro(own.float().cpu(), want_d) < TOL
 
 
 def test_vit_shaped_encoder_matches_oracle_backed_twin():
