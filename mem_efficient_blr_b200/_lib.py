@@ -109,6 +109,16 @@ _ext = None
 _ext_tried = False
 
 
+def _ext_registered() -> bool:
+    """True when a copy of the extension is already loaded: its operators resolve.  Loading a second copy would
+    register the operator namespace twice, which torch answers by aborting the process."""
+    try:
+        torch.ops.blr_b200_ext.blast
+        return True
+    except (AttributeError, RuntimeError):
+        return False
+
+
 def ext():
     """torch.ops.blr_b200_ext once _blr_torch.so is loaded, None where it has not been built (the operators then go
     through ctypes: same kernels, more host time per call).  Setting BLR_B200_NO_TORCH_EXT=1 keeps it unloaded."""
@@ -119,7 +129,8 @@ def ext():
         if not _ext_tried:
             if os.path.exists(EXT_PATH) and LIB_PATH.endswith("libblr_b200.so") and not os.environ.get("BLR_B200_NO_TORCH_EXT"):
                 load()
-                torch.ops.load_library(EXT_PATH)
+                if not _ext_registered():  # (a process that has just built the extension has it loaded from the build folder)
+                    torch.ops.load_library(EXT_PATH)
                 _ext = torch.ops.blr_b200_ext
             _ext_tried = True
     return _ext

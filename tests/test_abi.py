@@ -118,3 +118,18 @@ def test_torch_extension_loads_and_declares_the_operators():
     assert e.blast(x, u, v, s_, _lib.KMAJOR, _lib.KMAJOR, 128, 32, 1, 4, 16, 12, 32, 0).shape == (5, 48)
     with pytest.raises(RuntimeError, match="no CPU implementation"):
         e.dense(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(8, 8, dtype=torch.float16), _lib.KMAJOR, 8, 8)
+
+
+def test_extension_built_and_used_in_one_process():
+    """A process that builds the extension has it loaded from the build folder already; taking it into use afterwards
+    must not load the in-tree copy on top (torch aborts the process on a second registration of the namespace)."""
+    import subprocess
+    import sys
+    code = ("from mem_efficient_blr_b200 import build as b, _lib\n"
+            "b.build()\n"
+            "b.build_torch_ext(force=True)\n"
+            "e = _lib.ext()\n"
+            "assert e is not None and hasattr(e, 'blast_wq')\n"
+            "print('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
