@@ -138,9 +138,18 @@ def _coupling_factors(x, S, s_i, s_j, s_r, b, bo, R):
         _coupling_held -= _coupling.popitem(last=False)[1][2].numel()
     E = torch.empty(nbytes, dtype=torch.uint8, device=S.device)
     L.check(lib.blr_blast_expand_coupling(S.data_ptr(), s_i, s_j, s_r, b, bo, R, L.dtype_code(S.dtype), E.data_ptr(), nbytes, st))
-    _coupling[key] = (weakref.ref(root), S._version, E)
+    _coupling[key] = (weakref.ref(root, lambda _r, key=key: _drop_coupling(key)), S._version, E)
     _coupling_held += nbytes
     return E
+
+
+def _drop_coupling(key) -> None:
+    """The tensor an entry was built from is gone: its factors go with it."""
+    global _coupling_held
+    hit = _coupling.get(key)
+    if hit is not None and hit[0]() is None:
+        _coupling_held -= hit[2].numel()
+        del _coupling[key]
 
 
 def blast(x, U, V, S, u_layout, v_layout, s_i, s_j, s_r, b, P, Q, R, flags, b_out=-1):

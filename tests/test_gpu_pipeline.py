@@ -247,6 +247,12 @@ def test_coupling_factors_cached_per_S_and_rebuilt_after_a_change(K):
         changed = K.bk.blast_torch_layout(xd, Ud, Vtd, Sd)
         assert _err(changed, orc.blast(x, U, Vt, S * -0.5)[0]) < TOL
         assert len(ops._coupling) == 1
+        # the factors of a tensor that is gone are dropped with it
+        S2 = Sd.clone()
+        K.bk.blast_torch_layout(xd, Ud, Vtd, S2)
+        assert len(ops._coupling) == 2
+        del S2
+        assert len(ops._coupling) == 1 and ops._coupling_held == next(iter(ops._coupling.values()))[2].numel()
         # few tokens never touch the cache
         ops.clear_coupling_cache()
         K.bk.blast_torch_layout(xd.reshape(-1, I)[:200], Ud, Vtd, Sd)
