@@ -206,9 +206,38 @@ __global__ void __launch_bounds__(256) blast_couple_tile_kernel(const T* __restr
 template <typename T>
 static int run_couple_tile(const void* y, const void* S, int64_t s_i, int64_t s_j, void* z, int b, int b_out, int64_t N, int R,
                            int round_z, cudaStream_t stream) {
+  const void* kern = nullptr;
+  switch (b) {
+    case 2: kern = (const void*)blast_couple_tile_kernel<T, 2>; break;
+    case 3: kern = (const void*)blast_couple_tile_kernel<T, 3>; break;
+    case 4: kern = (const void*)blast_couple_tile_kernel<T, 4>; break;
+    case 6: kern = (const void*)blast_couple_tile_kernel<T, 6>; break;
+    case 8: kern = (const void*)blast_couple_tile_kernel<T, 8>; break;
+    case 9: kern = (const void*)blast_couple_tile_kernel<T, 9>; break;
+    case 12: kern = (const void*)blast_couple_tile_kernel<T, 12>; break;
+    case 16: kern = (const void*)blast_couple_tile_kernel<T, 16>; break;
+    default: return 1;  // no instantiation for this block count
+  }
+  // One wave: as many blocks as are resident at once.  (With 16 blocks a thread holds 128 values of y in registers and
+  // one block fits an SM; twice as many blocks as fit ran as two waves, 12.5 instead of about 8 us at 128 tokens.)
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != BLR_OK) return rc;
+  static int resident[64][17] = {};  // blocks per SM of this instance, per device (0: not asked yet)
+  int dev = 0;
+  BLR_CUDA_OK(cudaGetDevice(&dev));
+  int& per_sm = resident[dev & 63][b];
+  if (per_sm == 0) {
+    int n = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, (size_t)2 * b * 64 * sizeof(T)) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = 1;
+    }
+    per_sm = n > 2 ? 2 : n;
+  }
   const int r_tiles = (R + 63) / 64;
   int tok_groups = (int)((N + 31) / 32);
-  const int want = (2 * 148 + r_tiles - 1) / r_tiles;  // about two blocks per SM
+  const int want = (per_sm * di.sm_count) / r_tiles > 0 ? (per_sm * di.sm_count) / r_tiles : 1;
   if (tok_groups > want) tok_groups = want;
   // too few blocks for the GPU: share the out-blocks out as well (at least two per block)
   int i_groups = want / tok_groups;
@@ -232,18 +261,6 @@ static int run_couple_tile(const void* y, const void* S, int64_t s_i, int64_t s_
   T* zp = static_cast<T*>(z);
   long long si = s_i, sj = s_j, n = N;
   void* args[] = {&yp, &Sp, &si, &sj, &zp, &b_out, &n, &R, &round_z, &tok_groups, &i_per};
-  const void* kern = nullptr;
-  switch (b) {
-    case 2: kern = (const void*)blast_couple_tile_kernel<T, 2>; break;
-    case 3: kern = (const void*)blast_couple_tile_kernel<T, 3>; break;
-    case 4: kern = (const void*)blast_couple_tile_kernel<T, 4>; break;
-    case 6: kern = (const void*)blast_couple_tile_kernel<T, 6>; break;
-    case 8: kern = (const void*)blast_couple_tile_kernel<T, 8>; break;
-    case 9: kern = (const void*)blast_couple_tile_kernel<T, 9>; break;
-    case 12: kern = (const void*)blast_couple_tile_kernel<T, 12>; break;
-    case 16: kern = (const void*)blast_couple_tile_kernel<T, 16>; break;
-    default: return 1;  // no instantiation for this block count
-  }
   if (smem > 48 * 1024) BLR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, kern, args));
   return BLR_OK;
