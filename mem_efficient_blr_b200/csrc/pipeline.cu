@@ -407,8 +407,82 @@ __global__ void __launch_bounds__(256) transpose_rows_kernel(const uint16_t* __r
   }
 }
 
+// The same re-ordering when one side of the matrices is small (D = 2, 4, 8 or 16: Monarch's block count): an 8 x D
+// piece is transposed in registers, 16-byte loads and stores on both sides, no shared memory and no division per element.
+//   GATHER:  in[d][c] (D rows of C)  -> out[c * D + d]        a thread takes 8 consecutive c of all D rows and writes
+//            8 * D consecutive outputs (the interleaved output features of a token)
+//   !GATHER: in[a][d] (A rows of D)  -> out[d * out_c + a]    a thread takes 8 consecutive a (8 * D contiguous inputs)
+//            and writes 8 of them to each of the D destinations (the middle permutation on the torch layout)
+// Matrix (g, r) at in + g * in_g + r * A * C, written at out + g * out_g + r * out_r; `items` threads per matrix.
+template <int D, bool GATHER>
+__global__ void __launch_bounds__(256) reorder_small_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int L,
+                                                            long long rows, long long in_g, long long out_g, long long out_r,
+                                                            long long out_c, int items, long long total) {
+  const long long id = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (id >= total) return;
+  const long long m = id / items;  // matrix (g, r)
+  const int it = (int)(id - m * items);
+  const long long g = m / rows, r = m - g * rows;
+  const uint16_t* src = in + g * in_g + r * (long long)L * D;
+  uint16_t* dst = out + g * out_g + r * out_r;
+  alignas(16) uint16_t v[D][8];  // GATHER: [d][c];  !GATHER: the 8 * D inputs in order, i.e. [a][d] flattened
+  alignas(16) uint16_t w[D][8];
+  if constexpr (GATHER) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) *reinterpret_cast<uint4*>(v[d]) = *reinterpret_cast<const uint4*>(src + (long long)d * L + it * 8);
+    uint16_t* wf = &w[0][0];  // outputs (c, d) in order
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+      for (int d = 0; d < D; ++d) wf[c * D + d] = v[d][c];
+#pragma unroll
+    for (int k = 0; k < D; ++k) *reinterpret_cast<uint4*>(dst + ((long long)it * 8) * D + k * 8) = *reinterpret_cast<const uint4*>(w[k]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < D; ++k) *reinterpret_cast<uint4*>(v[k]) = *reinterpret_cast<const uint4*>(src + ((long long)it * 8) * D + k * 8);
+    const uint16_t* vf = &v[0][0];  // inputs (a, d) in order
+#pragma unroll
+    for (int d = 0; d < D; ++d)
+#pragma unroll
+      for (int a = 0; a < 8; ++a) w[d][a] = vf[a * D + d];
+#pragma unroll
+    for (int d = 0; d < D; ++d) *reinterpret_cast<uint4*>(dst + d * out_c + it * 8) = *reinterpret_cast<const uint4*>(w[d]);
+  }
+}
+
+template <int D>
+static int reorder_small(bool gather, const uint16_t* in, uint16_t* out, int L, long long groups, long long rows, long long in_g,
+                         long long out_g, long long out_r, long long out_c, cudaStream_t stream) {
+  const int items = L / 8;
+  const long long total = groups * rows * items;
+  BLR_REQUIRE((total + 255) / 256 < (1ll << 31), BLR_ERR_SHAPE, "too many rows to re-order");
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (gather) reorder_small_kernel<D, true><<<blocks, 256, 0, stream>>>(in, out, L, rows, in_g, out_g, out_r, out_c, items, total);
+  else reorder_small_kernel<D, false><<<blocks, 256, 0, stream>>>(in, out, L, rows, in_g, out_g, out_r, out_c, items, total);
+  BLR_CUDA_OK(cudaGetLastError());
+  return BLR_OK;
+}
+
 static int transpose_rows(const void* in, void* out, int A, int C, long long groups, long long rows, long long in_g,
                           long long out_g, long long out_r, long long out_c, cudaStream_t stream) {
+  {
+    // one small side: the register version (everything it touches in 16-byte pieces must be aligned)
+    const bool al = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 && in_g % 8 == 0 && out_g % 8 == 0 &&
+                    out_r % 8 == 0;
+    const bool gather = al && (A == 2 || A == 4 || A == 8 || A == 16) && C % 8 == 0 && out_c == A;
+    const bool scatter = al && !gather && (C == 2 || C == 4 || C == 8 || C == 16) && A % 8 == 0 && out_c % 8 == 0;
+    if (gather || scatter) {
+      const uint16_t* ip = static_cast<const uint16_t*>(in);
+      uint16_t* op = static_cast<uint16_t*>(out);
+      const int D = gather ? A : C, L = gather ? C : A;
+      switch (D) {
+        case 2: return reorder_small<2>(gather, ip, op, L, groups, rows, in_g, out_g, out_r, out_c, stream);
+        case 4: return reorder_small<4>(gather, ip, op, L, groups, rows, in_g, out_g, out_r, out_c, stream);
+        case 8: return reorder_small<8>(gather, ip, op, L, groups, rows, in_g, out_g, out_r, out_c, stream);
+        default: return reorder_small<16>(gather, ip, op, L, groups, rows, in_g, out_g, out_r, out_c, stream);
+      }
+    }
+  }
   const size_t smem = (size_t)kRowsPerCta * A * (C + 2) * 2;
   BLR_REQUIRE((A * C) % 8 == 0, BLR_ERR_SHAPE, "re-ordering needs matrices of a multiple of 8 elements, got %d x %d", A, C);
   const long long chunks = (rows + kRowsPerCta - 1) / kRowsPerCta;
