@@ -47,6 +47,18 @@ static int64_t ws_tokens(int64_t N, int64_t groups, int64_t width) {
   return N <= kStreamMaxTokens ? N : pass_size(N, groups, width);
 }
 
+// Third region of a workspace, above 16 tokens: BLAST's expanded coupling factors ((width / 16) matrices of
+// (16 groups)^2 16-bit values); with one group (low rank) the partial results of a first stage whose contraction is cut
+// into up to 16 slices, which happens up to 1024 tokens.
+static size_t region_c_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
+  if (n_tokens <= kStreamMaxTokens) return 0;
+  const size_t c = (size_t)groups * groups * ((size_t)width + 16) * 32;
+  if (groups != 1) return c;
+  const int64_t t = ws_tokens(n_tokens, groups, width);
+  const size_t parts = (size_t)16 * (size_t)(t < 1024 ? t : 1024) * (size_t)width * 2;
+  return parts > c ? parts : c;
+}
+
 static int carve(void* ws, size_t ws_bytes, int64_t N, int64_t groups, int64_t width, Workspace* w) {
   const size_t need = blr_workspace_bytes(N, groups, width);
   N = ws_tokens(N, groups, width);
@@ -552,9 +564,7 @@ const char* blr_last_error(void) { return blr::last_error(); }
 size_t blr_workspace_bytes(int64_t n_tokens, int64_t groups, int64_t width) {
   if (n_tokens < 0 || groups < 0 || width < 0) return 0;
   const size_t e = (size_t)groups * (size_t)ws_tokens(n_tokens, groups, width) * (size_t)width;
-  // above 16 tokens BLAST also keeps its expanded coupling factors: (width / 16) matrices of (16 groups)^2 16-bit values
-  const size_t c = n_tokens > 16 ? (size_t)groups * groups * ((size_t)width + 16) * 32 : 0;
-  return kCtrlBytes + kClusterOut32Bytes + align256(e * 4) + align256(e * 2) + align256(c);
+  return kCtrlBytes + kClusterOut32Bytes + align256(e * 4) + align256(e * 2) + align256(region_c_bytes(n_tokens, groups, width));
 }
 
 void* blr_scratch_alloc(size_t bytes) {
@@ -958,7 +968,8 @@ int blr_low_rank(const void* x, int64_t ldx, int64_t n_tokens, int dtype, const 
   for (int64_t n0 = 0; n0 < N; n0 += per_pass) {
     const int64_t n = N - n0 < per_pass ? N - n0 : per_pass;
     rc = pipeline_low_rank(static_cast<const uint8_t*>(x) + n0 * ldx * 2, ldx, n, dtype, V, v_layout, U, u_layout, I, R, O,
-                           static_cast<uint8_t*>(out) + n0 * ldo * 2, ldo, w.region_b, static_cast<cudaStream_t>(stream));
+                           static_cast<uint8_t*>(out) + n0 * ldo * 2, ldo, w.region_b, w.region_c, region_c_bytes(N, 1, R),
+                           static_cast<cudaStream_t>(stream));
     if (rc) return rc;
   }
   return BLR_OK;

@@ -34,7 +34,10 @@ struct QuantSpec {
 
 // One grouped GEMM: W (G blocks of M rows over K), A[g][n][k] with element strides (1, ld_n, ld_g).
 static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, const void* A, int64_t N, int64_t ld_n,
-                    int64_t ld_g, const OutSpec& o, cudaStream_t stream, const QuantSpec& q = QuantSpec()) {
+                    int64_t ld_g, const OutSpec& o, cudaStream_t stream, const QuantSpec& q = QuantSpec(), int64_t w_row = 0,
+                    int64_t w_grp = 0) {
+  // w_row / w_grp (elements, 16-bit K-major weights only; 0 = packed): the distance between consecutive rows of a
+  // block and between blocks when the blocks are column slices of a wider matrix
   GemmParams p = {};
   p.G = G; p.M = M; p.K = K; p.N = (int)N;
   p.kmajor = layout == BLR_W_KMAJOR;
@@ -64,7 +67,7 @@ static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, c
   } else if (p.kmajor) {
     BLR_REQUIRE(K % 8 == 0, BLR_ERR_SHAPE, "contraction length %d must be a multiple of 8", K);
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)G};
-    const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * K * 2};
+    const uint64_t str[2] = {(uint64_t)(w_row ? w_row : K) * 2, (uint64_t)(w_grp ? w_grp : (int64_t)M * K) * 2};
     const uint32_t box[3] = {64, (uint32_t)umma_w_tile_rows(p), 1};
     rc = encode_tmap_3d(&p.tmW, dt16(dtype), W, dims, str, box, Swz::B128);
   } else {
@@ -541,10 +544,58 @@ int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const voi
   return run_gemm(dtype, w2, w2_layout, b, Qs, rank, z16, N, rank, plane, OutSpec{out, 1, ldo, 0, b, Qs, 0}, stream);
 }
 
+// z[e] = sum over the planes of parts[plane][e] (fp32 sums of 16-bit values), 8 elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) sum_planes_kernel(const T* __restrict__ parts, int nparts, long long plane, T* __restrict__ z) {
+  const long long e = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (e >= plane) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int g = 0; g < nparts; ++g) {
+    const uint4 v = *reinterpret_cast<const uint4*>(parts + (long long)g * plane + e);
+    const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] += (float)h[k];
+  }
+  alignas(16) T o[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = T(acc[k]);
+  *reinterpret_cast<uint4*>(z + e) = *reinterpret_cast<const uint4*>(o);
+}
+
+// parts: room for the first stage's partial results (parts_bytes; may be null).  With few tokens the first GEMM has
+// few tiles (R / 128 or so) over a long contraction, i.e. a handful of CTAs that each stream megabytes: the
+// contraction is then cut into up to 16 slices that run as the groups of one grouped GEMM (the slices of V are column
+// ranges of its rows, or packed row ranges when the output index is contiguous) and a small kernel adds the slices.
 int pipeline_low_rank(const void* x, int64_t ldx, int64_t N, int dtype, const void* V, int v_layout, const void* U,
-                      int u_layout, int I, int R, int O, void* out, int64_t ldo, void* z16, cudaStream_t stream) {
-  int rc = run_gemm(dtype, V, v_layout, 1, R, I, x, N, ldx, 0, OutSpec{z16, 0, R, 0, 1, R, 0}, stream);
-  if (rc) return rc;
+                      int u_layout, int I, int R, int O, void* out, int64_t ldo, void* z16, void* parts, size_t parts_bytes,
+                      cudaStream_t stream) {
+  int rc;
+  int split = 1;
+  const long long tiles = (long long)((R + 127) / 128) * ((N + 127) / 128);
+  if (parts != nullptr && tiles < 74 && ((long long)N * R) % 8 == 0) {
+    for (int sp = 16; sp >= 2; sp >>= 1) {
+      if (I % (sp * 8) != 0 || I / sp < 256 || tiles * sp > 2 * 148 || (size_t)sp * N * R * 2 > parts_bytes) continue;
+      split = sp;
+      break;
+    }
+  }
+  if (split > 1) {
+    const int Ks = I / split;
+    const bool vk = v_layout == BLR_W_KMAJOR;
+    rc = run_gemm(dtype, V, v_layout, split, R, Ks, x, N, ldx, Ks, OutSpec{parts, (long long)N * R, R, 0, 1, R, 0}, stream, QuantSpec(),
+                  vk ? I : 0, vk ? Ks : 0);
+    if (rc) return rc;
+    const long long plane = (long long)N * R;
+    const unsigned blocks = (unsigned)((plane / 8 + 255) / 256);
+    if (dtype == BLR_DTYPE_BF16)
+      sum_planes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(parts), split, plane, static_cast<__nv_bfloat16*>(z16));
+    else
+      sum_planes_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(parts), split, plane, static_cast<__half*>(z16));
+    BLR_CUDA_OK(cudaGetLastError());
+  } else {
+    rc = run_gemm(dtype, V, v_layout, 1, R, I, x, N, ldx, 0, OutSpec{z16, 0, R, 0, 1, R, 0}, stream);
+    if (rc) return rc;
+  }
   return run_gemm(dtype, U, u_layout, 1, O, R, z16, N, R, 0, OutSpec{out, 0, ldo, 0, 1, O, 0}, stream);
 }
 

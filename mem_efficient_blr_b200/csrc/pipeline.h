@@ -25,7 +25,8 @@ int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const voi
                      const void* w2, int w2_layout, int b, int P, int rank, int Qs, int interleaved, void* out,
                      int64_t ldo, void* z16, void* scratch, cudaStream_t stream);
 int pipeline_low_rank(const void* x, int64_t ldx, int64_t N, int dtype, const void* V, int v_layout, const void* U,
-                      int u_layout, int I, int R, int O, void* out, int64_t ldo, void* z16, cudaStream_t stream);
+                      int u_layout, int I, int R, int O, void* out, int64_t ldo, void* z16, void* parts, size_t parts_bytes,
+                      cudaStream_t stream);
 int pipeline_dense(const void* x, int64_t ldx, int64_t N, int dtype, const void* W, int w_layout, int I, int O,
                    void* out, int64_t ldo, cudaStream_t stream);
 
