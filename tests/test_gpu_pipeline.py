@@ -162,7 +162,8 @@ def test_monarch_prefill_all_variants(K, shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(17, 256, 384, 64), (128, 4096, 11008, 1024), (2048, 11008, 4096, 1024)])
+@pytest.mark.parametrize("shape", [(17, 256, 384, 64), (128, 4096, 11008, 1024), (2048, 11008, 4096, 1024),
+                                   (300, 2000, 1000, 200)])  # (the last: two contraction slices of 1000, not whole 64-wide blocks)
 def test_low_rank_prefill(K, shape, dtype):
     N, I, O, R = shape
     x, Vt, Ut = orc.make_low_rank_inputs(N, I, O, R, dtype, seed=N % 83)
