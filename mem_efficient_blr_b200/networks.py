@@ -422,7 +422,8 @@ class DiTShape:
 
 
 def _modulate(x, shift, scale):
-    return x * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+    """x * (1 + scale) + shift with shift, scale (B, d) broadcast over the tokens: one small add and one fused multiply-add."""
+    return torch.addcmul(shift.unsqueeze(1), x, (scale + 1).unsqueeze(1))
 
 
 class DiTBlock(nn.Module):
@@ -451,8 +452,8 @@ class DiTBlock(nn.Module):
         sa, ca, ga, sm, cm, gm = self.adaln(F.silu(c)).chunk(6, dim=1)
         q, k, v = self.qkv(_modulate(self.norm1(x), sa, ca)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
         a = F.scaled_dot_product_attention(q, k, v)
-        x = x + ga.unsqueeze(1) * self.proj(a.transpose(1, 2).reshape(B, T, d))
-        return x + gm.unsqueeze(1) * self.fc2(F.gelu(self.fc1(_modulate(self.norm2(x), sm, cm)), approximate="tanh"))
+        x = torch.addcmul(x, ga.unsqueeze(1), self.proj(a.transpose(1, 2).reshape(B, T, d)))
+        return torch.addcmul(x, gm.unsqueeze(1), self.fc2(F.gelu(self.fc1(_modulate(self.norm2(x), sm, cm)), approximate="tanh")))
 
 
 class DiTDenoiser(nn.Module):
