@@ -146,8 +146,10 @@ int blr_blast_rows_prepared(const void* x, int64_t ldx, int64_t n_tokens, int dt
  *     takes the gate and up results directly.
  * Factors are contraction-contiguous: U (b,Q,R), V (b,R,P) in the 16-bit dtype (bits = 16: scales ignored) or quantised
  * as for blr_blast_wq (bits = 8 | 4).  S element (i, j, r) of every layer at i*s_i + j*s_j + r*s_r.
- * Scratch: blr_workspace_bytes(n_tokens, n_problems * b, R).  Serves the token counts of the two-launch decode path
- * (1..16 tokens, K-major factors); BLR_ERR_UNSUPPORTED otherwise - run the layers one by one. */
+ * Scratch: the larger of blr_workspace_bytes(n_tokens, n_problems * b, R) and blr_workspace_bytes(n_tokens, b, R).
+ * 1..16 tokens: the two-launch decode path (BLR_ERR_UNSUPPORTED for shapes it does not take - run the layers one by
+ * one).  More tokens: the layers run one after the other through the tensor-core pipeline and the last GEMM's
+ * epilogue adds bias and residual; BLR_ACT_SILU_MUL is not available there (BLR_ERR_UNSUPPORTED). */
 #define BLR_ACT_NONE 0
 #define BLR_ACT_SILU_MUL 1
 typedef struct blr_blast_problem {

@@ -123,7 +123,7 @@ def blast_multi_torch_layout(x, layers, x_mul=None, biases=None, residuals=None)
     biases[i] (O,) and residuals[i] (..., O) are added to layer i's result.  Returns the list of outputs.
     At decode sizes (up to 16 tokens) everything is one pair of launches (blr_blast_multi: no counterpart in the
     reference, which calls one operator per layer and separate torch kernels for the rest, models/wrappers.py:171-177);
-    otherwise the layers run one by one with the same arithmetic."""
+    above that the layers run one by one, biases and residuals added by the last GEMM's epilogue."""
     U0, Vt0, S0 = layers[0]
     b, r, p = Vt0.shape
     q = U0.shape[1]
@@ -136,6 +136,9 @@ def blast_multi_torch_layout(x, layers, x_mul=None, biases=None, residuals=None)
     outs = ops.blast_multi(x2, layers, 16, 0, b, p, q, r, xm2, biases, res2) if 1 <= len(layers) <= 3 else None
     if outs is None:
         xe = x2 if xm2 is None else torch.nn.functional.silu(x2) * xm2
+        if xm2 is not None and 1 <= len(layers) <= 3:   # the input transform done here, the rest may still fuse
+            outs = ops.blast_multi(xe, layers, 16, 0, b, p, q, r, None, biases, res2)
+    if outs is None:
         outs = []
         for i, (U, Vt, S) in enumerate(layers):
             o = ops.blast(xe, U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, L.FLAG_NONE)

@@ -94,6 +94,9 @@ def blast_wq_multi(x, layers, bits: int, group: int = 0, x_mul=None, biases=None
     outs = ops.blast_multi(x2, layers, bits, group, b, p, q, r, xm2, biases, res2) if 1 <= len(layers) <= 3 else None
     if outs is None:
         xe = x2 if xm2 is None else torch.nn.functional.silu(x2) * xm2
+        if xm2 is not None and 1 <= len(layers) <= 3:   # the input transform done here, the rest may still fuse
+            outs = ops.blast_multi(xe, layers, bits, group, b, p, q, r, None, biases, res2)
+    if outs is None:
         outs = []
         for i, (Uq, us, Vq, vs, S) in enumerate(layers):
             o = ops._flat2d(blast_wq(xe, Uq, us, Vq, vs, S, bits, group))

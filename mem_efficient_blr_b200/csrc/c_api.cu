@@ -466,7 +466,9 @@ static int cluster_monarch(const void* x, int64_t ldx, int64_t N, int dtype, con
 static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, int u_bits,
                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
-                      int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream, const void* e_ready = nullptr) {
+                      int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream, const void* e_ready = nullptr,
+                      const void* bias = nullptr, const void* residual = nullptr, int64_t ldr = 0) {
+  // (bias / residual: added by the last GEMM above 16 tokens; callers with fewer tokens use the two-launch path's own)
   int rc = check_common(x, ldx, N, dtype, out, ldo);
   if (rc) return rc < 0 ? rc : BLR_OK;
   BLR_REQUIRE(U && V && S, BLR_ERR_ARG, "factor pointers must not be null");
@@ -508,7 +510,8 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
     const int64_t n = N - n0 < per_pass ? N - n0 : per_pass;
     rc = pipeline_blast(static_cast<const uint8_t*>(x) + n0 * ldx * 2, ldx, n, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b,
                         bo, P, Q, R, act8, static_cast<uint8_t*>(out) + n0 * ldo * 2, ldo, w.region_a, w.region_b, w.region_c, stream,
-                        e_ready, u_bits != 16 || v_bits != 16 ? &quant : nullptr);
+                        e_ready, u_bits != 16 || v_bits != 16 ? &quant : nullptr, bias,
+                        residual ? static_cast<const uint8_t*>(residual) + n0 * ldr * 2 : nullptr, ldr);
     if (rc) return rc;
   }
   return BLR_OK;
@@ -700,6 +703,18 @@ int blr_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int6
     BLR_REQUIRE(bits == 16 || (q.u_scale && q.v_scale), BLR_ERR_ARG, "layer %d: quantised factors need scales", i);
     BLR_REQUIRE(q.residual == nullptr || q.ldr >= (int64_t)b * Q, BLR_ERR_SHAPE, "layer %d: residual rows shorter than the output", i);
     layers[i] = {q.U, bits == 16 ? nullptr : q.u_scale, q.V, bits == 16 ? nullptr : q.v_scale, q.S, q.bias, q.residual, q.out, q.ldo, q.ldr};
+  }
+  if (N > kStreamMaxTokens) {
+    // prefill sizes: layer by layer through the tensor-core pipeline, bias and residual added by the last GEMM's epilogue
+    BLR_REQUIRE(act == BLR_ACT_NONE, BLR_ERR_UNSUPPORTED, "the silu-mul input transform is fused for 1..%d tokens only", kStreamMaxTokens);
+    for (int i = 0; i < n_problems; ++i) {
+      const blr_blast_problem& q = problems[i];
+      const int rc1 = blast_impl(x, ldx, N, dtype, q.U, BLR_W_KMAJOR, bits, bits == 16 ? nullptr : q.u_scale, q.V, BLR_W_KMAJOR, bits,
+                                 bits == 16 ? nullptr : q.v_scale, group, q.S, s_i, s_j, s_r, b, b, P, Q, R, BLR_FLAG_NONE, q.out, q.ldo,
+                                 ws, ws_bytes, static_cast<cudaStream_t>(stream), nullptr, q.bias, q.residual, q.ldr);
+      if (rc1) return rc1;
+    }
+    return BLR_OK;
   }
   Workspace w;
   int rc = carve(ws, ws_bytes, N, (int64_t)n_problems * b, R, &w);

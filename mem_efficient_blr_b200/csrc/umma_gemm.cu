@@ -94,8 +94,22 @@ __device__ __forceinline__ float gemm_round(float v) {
   else return v;
 }
 
+template <bool BF16>
+__device__ __forceinline__ float2 gemm_unpack(uint32_t w) {
+  if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool BF16>
+__device__ __forceinline__ float gemm_load(const uint16_t* p) {
+  if constexpr (BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+  else return __half2float(*reinterpret_cast<const __half*>(p));
+}
+
 // Epilogue of one tile when tokens are the MMA rows: this thread's token, its columns = consecutive weight rows.
 struct EpiRow {
+  const uint16_t* bias;  // at the group's first feature, or null
+  const uint16_t* res;   // the token's residual row at the group's first feature, or null
+  int extra_vec;
   void* out;
   long long nbase, os_hi, os_lo;  // element offset of the token; strides of (m / per) and (m % per)
   int per, M, m0, cend;           // first weight row of the tile, columns of the tile that exist
@@ -113,6 +127,32 @@ __device__ __forceinline__ void epilogue_store32(const EpiRow& e, int c0, uint32
     if (c >= e.cend) break;
     uint32_t(&r)[16] = rr[u];
     tmem_regs_ready(r);
+    if (e.bias != nullptr || e.res != nullptr) {
+      // bias and residual of features m0 + c .. + 15 (16-byte pieces where the host found them aligned)
+      const int m = e.m0 + c;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const uint16_t* src = part == 0 ? e.bias : e.res;
+        if (src == nullptr || (part == 1 && !e.n_ok)) continue;
+        if (e.extra_vec && m + 16 <= e.M) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + m + 8 * h);
+            const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = gemm_unpack<BF16>(ws[k]);
+              r[8 * h + 2 * k] = __float_as_uint(__uint_as_float(r[8 * h + 2 * k]) + f.x);
+              r[8 * h + 2 * k + 1] = __float_as_uint(__uint_as_float(r[8 * h + 2 * k + 1]) + f.y);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (m + j < e.M) r[j] = __float_as_uint(__uint_as_float(r[j]) + gemm_load<BF16>(src + m + j));
+        }
+      }
+    }
     if constexpr (MODE > 0) {
       uint32_t w[8];
 #pragma unroll
@@ -359,6 +399,9 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
         e.out = p.out;
         const int n = nt * kBM + q * 32 + lane;
         e.n_ok = n < p.N;
+        e.extra_vec = p.extra_vec;
+        e.bias = p.bias ? static_cast<const uint16_t*>(p.bias) + (long long)g * p.M : nullptr;
+        e.res = p.residual && e.n_ok ? static_cast<const uint16_t*>(p.residual) + (long long)n * p.ldr + (long long)g * p.M : nullptr;
         e.nbase = gbase + (long long)n * p.os_n;
         e.os_hi = p.os_hi, e.os_lo = p.os_lo, e.per = p.per, e.M = p.M, e.m0 = mt * p.bn;
         e.cend = min(p.bn, p.M - e.m0);
@@ -369,6 +412,8 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
         const bool m_ok = m < p.M;
         const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
         const int n0 = nt * p.bn;
+        const float bias_m = p.bias && m_ok ? gemm_load<BF16>(static_cast<const uint16_t*>(p.bias) + (long long)g * p.M + m) : 0.f;
+        const uint16_t* res_m = p.residual && m_ok ? static_cast<const uint16_t*>(p.residual) + (long long)g * p.M + m : nullptr;
         for (int c = 16 * half; c < p.bn; c += 32) {
           if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
           uint32_t r[16];
@@ -380,7 +425,8 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
             for (int j = 0; j < 16; ++j) {
               const int n = n0 + c + j;
               if (n < p.N) {
-                const float v = __uint_as_float(r[j]);
+                float v = __uint_as_float(r[j]) + bias_m;
+                if (res_m != nullptr) v += gemm_load<BF16>(res_m + (long long)n * p.ldr);
                 gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round<RND>(v));
               }
             }

@@ -27,6 +27,12 @@ struct alignas(64) GemmParams {
   long long os_g, os_n, os_hi, os_lo;
   void* out;
   unsigned* status;  // optional: set to 1 when a device-side wait gave up
+  // Optional additions in the epilogue, for outputs laid out [n][g * M + m] (per >= M, os_lo = 1): bias[g * M + m] and
+  // residual[n * ldr + g * M + m], both of the 16-bit dtype.  extra_vec: both may be read in 16-byte pieces.
+  const void* bias;
+  const void* residual;
+  long long ldr;
+  int extra_vec;
   // Quantised weights: int8 or packed int4 (two per byte along k, even index in the low nibble, two's complement) with
   // fp16 scales [g][m][scales_per_row] (1: per weight row; K / 128: per 128 contraction indices).  Converter warps
   // widen every staged tile to the 16-bit dtype (q * scale, rounded once) in shared memory ahead of the MMA.

@@ -67,10 +67,9 @@ class BlastTorchLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype), requires_grad=False) if bias else None
 
     def forward(self, x):
-        out = bk.blast_torch_layout(x, self.U, self.Vt, self.S)
-        if self.bias is not None:
-            out += self.bias
-        return out
+        if self.bias is not None:   # (added by the kernels' epilogue where the fused call applies)
+            return bk.blast_multi_torch_layout(x, [(self.U, self.Vt, self.S)], biases=[self.bias])[0]
+        return bk.blast_torch_layout(x, self.U, self.Vt, self.S)
 
     def U_device_ok(self) -> bool:
         return self.U.is_cuda
@@ -112,10 +111,10 @@ class BlastQuantLinear(nn.Module):
         return self.Uq.is_cuda
 
     def forward(self, x):
-        out = bq.blast_wq(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits, self.group)
         if self.bias is not None:
-            out += self.bias
-        return out
+            return bq.blast_wq_multi(x, [(self.Uq, self.u_scale, self.Vq, self.v_scale, self.S)], self.bits, self.group,
+                                     biases=[self.bias])[0]
+        return bq.blast_wq(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits, self.group)
 
 
 def make_linear(method: str, in_features: int, out_features: int, b: int, rank: int, bias: bool, device, dtype, generator):

@@ -62,12 +62,16 @@ def _eager() -> bool:
 _ws_bytes_cache: dict = {}
 
 
-def _ws(x: torch.Tensor, n: int, groups: int, width: int):
+def _ws(x: torch.Tensor, n: int, groups: int, width: int, also=None):
+    """The stream's workspace, at least blr_workspace_bytes(n, groups, width) bytes (and that of `also` = (groups, width))."""
     st = L.stream_ptr(x.device)
-    key = (n, groups, width)
+    key = (n, groups, width, also)
     nbytes = _ws_bytes_cache.get(key)
     if nbytes is None:
-        nbytes = _ws_bytes_cache[key] = L.load().blr_workspace_bytes(n, groups, width)
+        nbytes = L.load().blr_workspace_bytes(n, groups, width)
+        if also is not None:
+            nbytes = max(nbytes, L.load().blr_workspace_bytes(n, also[0], also[1]))
+        _ws_bytes_cache[key] = nbytes
     ws = L.workspace(x.device, st, nbytes)
     return ws, st
 
@@ -426,8 +430,16 @@ def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int
     layer's result ((b*Q,) / (N, b*Q)).  Returns the list of outputs, or None when the fused call does not apply
     (token count or shape outside the two-launch decode path): the caller then runs the layers one by one."""
     n = x.shape[0]
-    if n == 0 or n > (8 if bits == 16 else 4) or torch.compiler.is_compiling():
+    # decode sizes: the fused pair of launches where it is the faster route; prefill sizes: one call per layer list, worth
+    # it when there is a bias or a residual for the last GEMM's epilogue to add (otherwise the plain operators do the same)
+    has_res = any(t is not None for t in (residuals or []))
+    # (up to 64 tokens the weights are the MMA rows and a thread would fetch its residuals one 2-byte load per token:
+    # measured 23.4 us fused against 21.1 us with torch's add at 64 tokens - those calls stay unfused)
+    prefill = n > 16 and x_mul is None and (any(t is not None for t in (biases or [])) or has_res) and not (has_res and n <= 64)
+    if n == 0 or torch.compiler.is_compiling() or (n > (8 if bits == 16 else 4) and not prefill):
         return None
+    if prefill and bits != 16 and ((P * bits // 8) % 16 != 0 or (R * bits // 8) % 16 != 0 or n > 384):
+        return None   # (quantised rows the copy engine cannot stage, or token counts where a widening pass is faster)
     x = _rows(x)
     if x_mul is not None:
         x_mul = _rows(x_mul)
@@ -460,6 +472,8 @@ def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int
         outs.append(out)
         keep.append((bias, res))
     ws, st = _ws(x, n, k * b, R)
+    if prefill:
+        ws, st = _ws(x, n, k * b, R, also=(b, R))
     rc = L.load().blr_blast_multi(x.data_ptr(), x.stride(0), 0 if x_mul is None else x_mul.data_ptr(),
                                   L.ACT_NONE if x_mul is None else L.ACT_SILU_MUL, n, L.dtype_code(x.dtype), k, arr,
                                   b * R, R, 1, bits, group, b, P, Q, R, ws.data_ptr(), ws.numel(), st)

@@ -346,3 +346,57 @@ def test_token_counts_beyond_one_pass_run_as_passes_on_a_capped_workspace(K):
     assert torch.equal(whole2, parts2)
     rows2 = torch.cat((torch.arange(0, 40), torch.arange(N2 - 40, N2)))
     assert _err(whole2[rows2.to(DEV)], orc.monarch(x2.reshape(N2, I2)[rows2], w1, w2)[0]) < TOL
+
+
+# ------------------------------------------------------------------------- bias and residual in the last GEMM's epilogue
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [16, 8])
+@pytest.mark.parametrize("shape", [(17, 512, 768, 4, 128), (64, 4096, 4096, 16, 1024), (65, 768, 2304, 16, 256),
+                                   (300, 512, 288, 4, 128), (2048, 4096, 4096, 16, 1024)])
+def test_bias_and_residual_added_by_the_pipeline(K, shape, bits, dtype):
+    """Above 16 tokens the fused call runs the layers through the pipeline and the last GEMM adds bias and residual
+    (both orientations of the tile, ragged output blocks, 16-bit and quantised factors); against the oracle plus the
+    additions in fp32."""
+    from mem_efficient_blr_b200 import ops
+    N, I, O, b, R = shape
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, dtype, seed=N + bits)
+    g = torch.Generator().manual_seed(N)
+    bias = torch.randn(O, generator=g).to(dtype)
+    res = torch.randn(N, O, generator=g).to(dtype)
+    x2 = x.reshape(N, I)
+    if bits == 16:
+        ref = orc.blast(x, U, Vt, S)[0].reshape(N, O)
+        layers = [tuple(_cuda(U, Vt, S))]
+    else:
+        Uq, us = orc.quantize_sym(U, bits)
+        Vq, vs = orc.quantize_sym(Vt, bits)
+        ref = orc.blast_wq(x, Uq, us, Vq, vs, S, bits)[0].reshape(N, O)
+        layers = [tuple(_cuda(Uq, us, Vq, vs, S))]
+    xd, bd, rd = _cuda(x2, bias, res)
+    P, Q = I // b, O // b
+    outs = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, [bd], [rd])
+    if bits != 16 and N > 384:
+        assert outs is None   # (the widening route serves those; nothing fused)
+        return
+    only_bias = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, [bd], None)[0]
+    assert _err(only_bias, ref + bias.float()) < TOL
+    if N <= 64:
+        assert outs is None   # (residuals are not fused while the weights are the MMA rows: torch's add is faster there)
+        # the C entry point itself serves them all the same
+        import mem_efficient_blr_b200.blast_kernels as bk
+        keep = ops.blast_multi
+        try:
+            ops.blast_multi = lambda *a, **k: None
+            unfused = bk.blast_multi_torch_layout(xd, layers, None, [bd], [rd])[0] if bits == 16 else \
+                K.bq.blast_wq_multi(xd, layers, bits, 0, None, [bd], [rd])[0]
+        finally:
+            ops.blast_multi = keep
+        assert _err(unfused, ref + bias.float() + res.float()) < TOL
+        return
+    assert outs is not None and len(outs) == 1
+    assert _err(outs[0], ref + bias.float() + res.float()) < TOL
+    # a residual view with a longer row stride and an odd start (no 16-byte pieces)
+    wide = torch.zeros(N, O + 9, dtype=dtype, device=DEV)
+    wide[:, 1:O + 1] = rd
+    got = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, None, [wide[:, 1:O + 1]])[0]
+    assert _err(got, ref + res.float()) < TOL
