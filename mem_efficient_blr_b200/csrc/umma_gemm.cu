@@ -118,7 +118,7 @@ struct EpiRow {
 
 // MODE 2: 32-byte stores (16 consecutive outputs contiguous and aligned, no ragged tile edge), 1: 16-byte stores,
 // 0: element stores.  The mode is a template parameter so that a chunk executes only its own variant.
-template <bool BF16, bool RND, int MODE>
+template <bool BF16, bool RND, int MODE, bool EX>
 __device__ __forceinline__ void epilogue_store32(const EpiRow& e, int c0, uint32_t (&rr)[2][16]) {
   int hi = (e.m0 + c0) / e.per, lo = (e.m0 + c0) - hi * e.per;  // (m / per, m % per), kept incrementally
 #pragma unroll
@@ -127,7 +127,7 @@ __device__ __forceinline__ void epilogue_store32(const EpiRow& e, int c0, uint32
     if (c >= e.cend) break;
     uint32_t(&r)[16] = rr[u];
     tmem_regs_ready(r);
-    if (e.bias != nullptr || e.res != nullptr) {
+    if constexpr (EX) {
       // bias and residual of features m0 + c .. + 15 (16-byte pieces where the host found them aligned)
       const int m = e.m0 + c;
 #pragma unroll
@@ -195,7 +195,7 @@ __device__ __forceinline__ void epilogue_load32(uint32_t taddr, uint32_t (&rr)[2
 // Columns c_first, c_first + 64, ... of the tile, 32 per round; the loads of the next round are in flight while
 // this one is converted and stored.  (A round always loads 32 columns: the allocation has room behind the last
 // tile column.)
-template <bool BF16, bool RND, int MODE>
+template <bool BF16, bool RND, int MODE, bool EX>
 __device__ __forceinline__ void epilogue_rows(const EpiRow& e, uint32_t taddr, int c_first) {
   uint32_t ra[2][16], rb[2][16];
   int c0 = c_first;
@@ -203,12 +203,12 @@ __device__ __forceinline__ void epilogue_rows(const EpiRow& e, uint32_t taddr, i
   while (c0 < e.cend) {
     tmem_ld_wait();
     if (c0 + 64 < e.cend) epilogue_load32(taddr + c0 + 64, rb);
-    epilogue_store32<BF16, RND, MODE>(e, c0, ra);
+    epilogue_store32<BF16, RND, MODE, EX>(e, c0, ra);
     c0 += 64;
     if (c0 >= e.cend) break;
     tmem_ld_wait();
     if (c0 + 64 < e.cend) epilogue_load32(taddr + c0 + 64, ra);
-    epilogue_store32<BF16, RND, MODE>(e, c0, rb);
+    epilogue_store32<BF16, RND, MODE, EX>(e, c0, rb);
     c0 += 64;
   }
 }
@@ -217,7 +217,8 @@ __device__ __forceinline__ void epilogue_rows(const EpiRow& e, uint32_t taddr, i
 // MODE = store width of the TR epilogue (see epilogue_store32), RND = round the outputs to int8 steps; both are
 // chosen by the host from the parameters, so that the epilogue holds exactly one variant.
 // WQ = 0: 16-bit weights; 8 | 4: quantised weights widened by converter warps (K-major only).
-template <bool BF16, bool TR, int MODE, bool RND, int WQ>
+// EX: the epilogue adds a bias and / or a residual (an instance of its own: the additions cost registers).
+template <bool BF16, bool TR, int MODE, bool RND, int WQ, bool EX>
 __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
     blr_umma_gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -405,15 +406,19 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
         e.nbase = gbase + (long long)n * p.os_n;
         e.os_hi = p.os_hi, e.os_lo = p.os_lo, e.per = p.per, e.M = p.M, e.m0 = mt * p.bn;
         e.cend = min(p.bn, p.M - e.m0);
-        epilogue_rows<BF16, RND, MODE>(e, taddr, 32 * half);
+        epilogue_rows<BF16, RND, MODE, EX>(e, taddr, 32 * half);
       } else {
         // thread = weight row, columns = tokens
         const int m = mt * kBM + q * 32 + lane;
         const bool m_ok = m < p.M;
         const long long base = m_ok ? gbase + (long long)(m / p.per) * p.os_hi + (long long)(m % p.per) * p.os_lo : 0;
         const int n0 = nt * p.bn;
-        const float bias_m = p.bias && m_ok ? gemm_load<BF16>(static_cast<const uint16_t*>(p.bias) + (long long)g * p.M + m) : 0.f;
-        const uint16_t* res_m = p.residual && m_ok ? static_cast<const uint16_t*>(p.residual) + (long long)g * p.M + m : nullptr;
+        float bias_m = 0.f;
+        const uint16_t* res_m = nullptr;
+        if constexpr (EX) {
+          if (p.bias && m_ok) bias_m = gemm_load<BF16>(static_cast<const uint16_t*>(p.bias) + (long long)g * p.M + m);
+          if (p.residual && m_ok) res_m = static_cast<const uint16_t*>(p.residual) + (long long)g * p.M + m;
+        }
         for (int c = 16 * half; c < p.bn; c += 32) {
           if (n0 + c >= p.N) break;  // whole chunk past the last token (warp-uniform)
           uint32_t r[16];
@@ -425,8 +430,11 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
             for (int j = 0; j < 16; ++j) {
               const int n = n0 + c + j;
               if (n < p.N) {
-                float v = __uint_as_float(r[j]) + bias_m;
-                if (res_m != nullptr) v += gemm_load<BF16>(res_m + (long long)n * p.ldr);
+                float v = __uint_as_float(r[j]);
+                if constexpr (EX) {
+                  v += bias_m;
+                  if (res_m != nullptr) v += gemm_load<BF16>(res_m + (long long)n * p.ldr);
+                }
                 gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round<RND>(v));
               }
             }
@@ -479,11 +487,11 @@ void umma_gemm_tiling(GemmParams& p) {
   p.nstages = nst > kMaxStages ? kMaxStages : nst;
 }
 
-template <bool BF16, bool TR, int MODE, bool RND, int WQ = 0>
+template <bool BF16, bool TR, int MODE, bool RND, int WQ = 0, bool EX = false>
 static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
   static bool configured[64] = {};
   if (!configured[dev & 63]) {
-    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR, MODE, RND, WQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    BLR_CUDA_OK(cudaFuncSetAttribute(blr_umma_gemm_kernel<BF16, TR, MODE, RND, WQ, EX>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     configured[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -497,23 +505,33 @@ static int launch_variant(const GemmParams& p, int grid, size_t smem, int dev, i
   cfg.attrs = at;
   cfg.numAttrs = 1;
   void* args[] = {const_cast<GemmParams*>(&p)};
-  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR, MODE, RND, WQ>, args));
+  BLR_CUDA_OK(cudaLaunchKernelExC(&cfg, (const void*)blr_umma_gemm_kernel<BF16, TR, MODE, RND, WQ, EX>, args));
   return BLR_OK;
 }
 
-// Quantised weights: no rounding variant (the rounded intermediates exist for 16-bit factors only).
+// No rounding variant with quantised weights or with additions in the epilogue (the rounded intermediates exist for
+// 16-bit factors only, and they are never a layer's final result).
+template <bool BF16, int WQ, bool EX>
+static int launch_plain(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
+  if (!p.tokens_as_rows) return launch_variant<BF16, false, 0, false, WQ, EX>(p, grid, smem, dev, max_smem, stream);
+  if (mode == 2) return launch_variant<BF16, true, 2, false, WQ, EX>(p, grid, smem, dev, max_smem, stream);
+  if (mode == 1) return launch_variant<BF16, true, 1, false, WQ, EX>(p, grid, smem, dev, max_smem, stream);
+  return launch_variant<BF16, true, 0, false, WQ, EX>(p, grid, smem, dev, max_smem, stream);
+}
 template <bool BF16, int WQ>
 static int launch_quantised(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
-  if (!p.tokens_as_rows) return launch_variant<BF16, false, 0, false, WQ>(p, grid, smem, dev, max_smem, stream);
-  if (mode == 2) return launch_variant<BF16, true, 2, false, WQ>(p, grid, smem, dev, max_smem, stream);
-  if (mode == 1) return launch_variant<BF16, true, 1, false, WQ>(p, grid, smem, dev, max_smem, stream);
-  return launch_variant<BF16, true, 0, false, WQ>(p, grid, smem, dev, max_smem, stream);
+  return (p.bias || p.residual) ? launch_plain<BF16, WQ, true>(p, mode, grid, smem, dev, max_smem, stream)
+                                : launch_plain<BF16, WQ, false>(p, mode, grid, smem, dev, max_smem, stream);
 }
 
 template <bool BF16>
 static int launch_dtype(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
   if (p.w_bits == 8) return launch_quantised<BF16, 8>(p, mode, grid, smem, dev, max_smem, stream);
   if (p.w_bits == 4) return launch_quantised<BF16, 4>(p, mode, grid, smem, dev, max_smem, stream);
+  if (p.bias || p.residual) {
+    BLR_REQUIRE(!p.round_out, BLR_ERR_ARG, "bias and residual are not combined with rounded outputs");
+    return launch_plain<BF16, 0, true>(p, mode, grid, smem, dev, max_smem, stream);
+  }
   if (!p.tokens_as_rows) {
     return p.round_out ? launch_variant<BF16, false, 0, true>(p, grid, smem, dev, max_smem, stream)
                        : launch_variant<BF16, false, 0, false>(p, grid, smem, dev, max_smem, stream);

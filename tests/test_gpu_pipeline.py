@@ -380,8 +380,8 @@ def test_bias_and_residual_added_by_the_pipeline(K, shape, bits, dtype):
         return
     only_bias = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, [bd], None)[0]
     assert _err(only_bias, ref + bias.float()) < TOL
-    if N <= 64:
-        assert outs is None   # (residuals are not fused while the weights are the MMA rows: torch's add is faster there)
+    if N <= 64 or N > 512:
+        assert outs is None   # (residuals are fused only where that is faster than torch's add: 65..512 tokens)
         # the C entry point itself serves them all the same
         import mem_efficient_blr_b200.blast_kernels as bk
         keep = ops.blast_multi
