@@ -17,6 +17,24 @@ static CUtensorMapDataType dt16(int dtype) {
 
 static constexpr int kCoupleTileMaxTokens = 256;  // above: coupling as a grouped GEMM over expanded factors
 
+// Launch with programmatic stream serialisation: the kernel may start while its predecessor drains; it calls
+// griddepcontrol.launch_dependents at its start and griddepcontrol.wait before it touches what the predecessor wrote.
+template <typename K, typename... A>
+static int launch_pdl(K kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  BLR_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, args...));
+  return BLR_OK;
+}
+
 struct OutSpec {
   void* out;
   long long os_g, os_n, os_hi, os_lo;
@@ -428,6 +446,8 @@ template <int D, bool GATHER>
 __global__ void __launch_bounds__(256) reorder_small_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int L,
                                                             long long rows, long long in_g, long long out_g, long long out_r,
                                                             long long out_c, int items, long long total) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // (every thread: the grid completes after its predecessor)
   const long long id = (long long)blockIdx.x * 256 + threadIdx.x;
   if (id >= total) return;
   const long long m = id / items;  // matrix (g, r)
@@ -467,10 +487,8 @@ static int reorder_small(bool gather, const uint16_t* in, uint16_t* out, int L, 
   const long long total = groups * rows * items;
   BLR_REQUIRE((total + 255) / 256 < (1ll << 31), BLR_ERR_SHAPE, "too many rows to re-order");
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (gather) reorder_small_kernel<D, true><<<blocks, 256, 0, stream>>>(in, out, L, rows, in_g, out_g, out_r, out_c, items, total);
-  else reorder_small_kernel<D, false><<<blocks, 256, 0, stream>>>(in, out, L, rows, in_g, out_g, out_r, out_c, items, total);
-  BLR_CUDA_OK(cudaGetLastError());
-  return BLR_OK;
+  if (gather) return launch_pdl(reorder_small_kernel<D, true>, dim3(blocks), dim3(256), 0, stream, in, out, L, rows, in_g, out_g, out_r, out_c, items, total);
+  return launch_pdl(reorder_small_kernel<D, false>, dim3(blocks), dim3(256), 0, stream, in, out, L, rows, in_g, out_g, out_r, out_c, items, total);
 }
 
 static int transpose_rows(const void* in, void* out, int A, int C, long long groups, long long rows, long long in_g,
@@ -554,6 +572,8 @@ int pipeline_monarch(const void* x, int64_t ldx, int64_t N, int dtype, const voi
 // z[e] = sum over the planes of parts[plane][e] (fp32 sums of 16-bit values), 8 elements per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) sum_planes_kernel(const T* __restrict__ parts, int nparts, long long plane, T* __restrict__ z) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long e = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
   if (e >= plane) return;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -595,10 +615,12 @@ int pipeline_low_rank(const void* x, int64_t ldx, int64_t N, int dtype, const vo
     const long long plane = (long long)N * R;
     const unsigned blocks = (unsigned)((plane / 8 + 255) / 256);
     if (dtype == BLR_DTYPE_BF16)
-      sum_planes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(parts), split, plane, static_cast<__nv_bfloat16*>(z16));
+      rc = launch_pdl(sum_planes_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(parts), split, plane,
+                      static_cast<__nv_bfloat16*>(z16));
     else
-      sum_planes_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(parts), split, plane, static_cast<__half*>(z16));
-    BLR_CUDA_OK(cudaGetLastError());
+      rc = launch_pdl(sum_planes_kernel<__half>, dim3(blocks), dim3(256), 0, stream, static_cast<const __half*>(parts), split, plane,
+                      static_cast<__half*>(z16));
+    if (rc) return rc;
   } else {
     rc = run_gemm(dtype, V, v_layout, 1, R, I, x, N, ldx, 0, OutSpec{z16, 0, R, 0, 1, R, 0}, stream);
     if (rc) return rc;
