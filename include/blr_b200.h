@@ -310,6 +310,12 @@ int blr_load_store_probe(const void* a, size_t a_bytes, const void* b, size_t b_
  * of 8; pointers 16-byte aligned).  Models LlamaRMSNorm. */
 int blr_rmsnorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, float eps, int dtype,
                 void* out, int64_t ldo, void* stream);
+/* LayerNorm over the last dimension with optional weight and bias (NULL: none): out = (x - mean) * rsqrt(var + eps) * w + b,
+ * fp32 arithmetic on 16-bit rows, one rounding; d a multiple of 8 and at most 2048 (BLR_ERR_UNSUPPORTED above).  What the
+ * encoder and denoiser modules around the linears run between them (HuggingFace ViT's nn.LayerNorm in
+ * models/vit_b_patch16_224.py, DiT/models.py:107-109); no counterpart among the reference's operator files. */
+int blr_layernorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, const void* bias, float eps,
+                  int dtype, void* out, int64_t ldo, void* stream);
 
 /* Rotary embedding and append to a static KV cache.  q, k, v: n_seq * n_tok rows (sequence-major) of heads * head_dim
  * values, row strides ldq / ldk / ldv.  Token t takes cache slot pos[t] (device int64) and the rotation angle of that

@@ -83,6 +83,83 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
   }
 }
 
+// ------------------------------------------------------------------------------------------------ LayerNorm
+// out[r][:] = (x[r][:] - mean) * rsqrt(var + eps) * w[:] + b[:]  (w, b optional).  A warp per row, the row in registers
+// (up to 8 pieces of 8 values per lane: d <= 2048, d % 8 == 0), mean and variance in two passes over the registers.
+template <bool BF16>
+__global__ void __launch_bounds__(256) layernorm_kernel(const uint16_t* __restrict__ x, long long ldx, const uint16_t* __restrict__ w,
+                                                        const uint16_t* __restrict__ b, float eps, int d, long long rows,
+                                                        uint16_t* __restrict__ out, long long ldo) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31, pieces = d >> 3;
+  const uint16_t* xr = x + r * ldx;
+  float v[8][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int p = lane + 32 * i;
+    if (p < pieces) {
+      const uint4 t = *reinterpret_cast<const uint4*>(xr + p * 8);
+      const uint32_t ws[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = up2<BF16>(ws[k]);
+        v[i][2 * k] = f.x;
+        v[i][2 * k + 1] = f.y;
+        sum += f.x + f.y;
+      }
+    }
+  }
+  const float mean = warp_sum(sum) / (float)d;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (lane + 32 * i < pieces) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float c = v[i][k] - mean;
+        sq = fmaf(c, c, sq);
+      }
+    }
+  const float inv = rsqrtf(warp_sum(sq) / (float)d + eps);
+  uint16_t* orow = out + r * ldo;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int p = lane + 32 * i;
+    if (p < pieces) {
+      float g[8], h[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = 1.f, h[k] = 0.f;
+      if (w != nullptr) {
+        const uint4 t = *reinterpret_cast<const uint4*>(w + p * 8);
+        const uint32_t ws[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = up2<BF16>(ws[k]);
+          g[2 * k] = f.x, g[2 * k + 1] = f.y;
+        }
+      }
+      if (b != nullptr) {
+        const uint4 t = *reinterpret_cast<const uint4*>(b + p * 8);
+        const uint32_t ws[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = up2<BF16>(ws[k]);
+          h[2 * k] = f.x, h[2 * k + 1] = f.y;
+        }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = down2<BF16>(fmaf((v[i][2 * k] - mean) * inv, g[2 * k], h[2 * k]), fmaf((v[i][2 * k + 1] - mean) * inv, g[2 * k + 1], h[2 * k + 1]));
+      *reinterpret_cast<uint4*>(orow + p * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ rotary embedding + cache append
 // Row r = (sequence b, token t) of q, k, v (rows of H * hd values, row strides ldq / ldk / ldv).  Pairs (i, i + hd/2) of
 // every head of q and k are rotated by the angle of cache slot pos[t] (cos, sin tables (slots, hd/2), fp32); q is
@@ -310,6 +387,28 @@ int blr_rmsnorm(const void* x, int64_t ldx, int64_t rows, int d, const void* wei
   const long long lx = ldx, lo = ldo;
   if (dtype == BLR_DTYPE_BF16) return launch_pdl(rmsnorm_kernel<true>, dim3((unsigned)rows), dim3(256), 0, st, xp, lx, wp, eps, d, op, lo);
   return launch_pdl(rmsnorm_kernel<false>, dim3((unsigned)rows), dim3(256), 0, st, xp, lx, wp, eps, d, op, lo);
+}
+
+int blr_layernorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, const void* bias, float eps, int dtype, void* out,
+                  int64_t ldo, void* stream) {
+  BLR_REQUIRE(rows >= 0 && d > 0 && d % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0, BLR_ERR_ARG,
+              "layernorm needs d, ldx and ldo to be multiples of 8 (d = %d)", d);
+  BLR_REQUIRE(d <= 2048, BLR_ERR_UNSUPPORTED, "layernorm keeps a row in a warp's registers: d <= 2048, got %d", d);
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  if (rows == 0) return BLR_OK;
+  BLR_REQUIRE(x && out, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight) |
+                reinterpret_cast<uintptr_t>(bias)) & 15) == 0, BLR_ERR_ARG, "layernorm needs 16-byte aligned pointers");
+  BLR_REQUIRE((rows + 7) / 8 < (1ll << 31), BLR_ERR_SHAPE, "too many rows");
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const uint16_t* wp = static_cast<const uint16_t*>(weight);
+  const uint16_t* bp = static_cast<const uint16_t*>(bias);
+  uint16_t* op = static_cast<uint16_t*>(out);
+  const long long lx = ldx, lo = ldo, nr = rows;
+  const dim3 grid((unsigned)((rows + 7) / 8));
+  if (dtype == BLR_DTYPE_BF16) return launch_pdl(layernorm_kernel<true>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo);
+  return launch_pdl(layernorm_kernel<false>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo);
 }
 
 int blr_rope_append(void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const float* cos_table,

@@ -499,6 +499,21 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out if x.dim() == 2 else out.reshape(*x.shape[:-1], d)
 
 
+def layernorm(x: torch.Tensor, weight, bias, eps: float) -> torch.Tensor:
+    """x (..., d) 16-bit CUDA tensor -> LayerNorm over d with optional weight / bias (None: none), fp32 arithmetic, one
+    rounding; d a multiple of 8, at most 2048."""
+    _need_cuda(x)
+    d = x.shape[-1]
+    x2 = x if x.dim() == 2 else x.reshape(-1, d)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+    L.check(L.load().blr_layernorm(x2.data_ptr(), x2.stride(0), x2.shape[0], d, None if weight is None else weight.data_ptr(),
+                                   None if bias is None else bias.data_ptr(), float(eps), L.dtype_code(x.dtype), out.data_ptr(),
+                                   out.stride(0), L.stream_ptr(x.device)))
+    return out if x.dim() == 2 else out.reshape(x.shape)
+
+
 def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,
                 pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_tok: int) -> torch.Tensor:
     """q, k, v (n_seq * n_tok, heads * head_dim) rows (sequence-major); caches (n_seq, heads, slots, head_dim); cos / sin

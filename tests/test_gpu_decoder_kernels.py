@@ -115,3 +115,30 @@ def test_fused_decode_step_equals_the_module_by_module_step():
         m.prefill(ids[:, :T - 1])
         outs.append(m.decode_step(ids[:, T - 1:], torch.tensor([T - 1], device=DEV)).float().cpu())
     assert _rel(outs[0], outs[1]) < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("affine", [True, False])
+@pytest.mark.parametrize("rows,d", [(1, 768), (13, 1152), (197, 768), (1000, 2048), (9, 8)])
+def test_layernorm(ops, rows, d, affine, dtype):
+    """A warp per row, the row in registers: against F.layer_norm in fp32 on the same 16-bit inputs (rows with an
+    offset mean, so that a one-pass variance would lose digits), with and without weight / bias, strided rows."""
+    g = torch.Generator().manual_seed(rows + d)
+    x = (torch.randn(rows, d, generator=g) * 2 + 5).to(dtype)
+    w = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype) if affine else None
+    b = (0.1 * torch.randn(d, generator=g)).to(dtype) if affine else None
+    ref = F.layer_norm(x.float(), (d,), None if w is None else w.float(), None if b is None else b.float(), 1e-6)
+    got = ops.layernorm(x.to(DEV), None if w is None else w.to(DEV), None if b is None else b.to(DEV), 1e-6)
+    assert got.dtype == dtype and got.shape == x.shape and _rel(got.float().cpu(), ref) < _tol(dtype)
+    wide = torch.zeros(rows, 2, d, dtype=dtype)
+    wide[:, 0] = x
+    got2 = ops.layernorm(wide.to(DEV)[:, 0], None if w is None else w.to(DEV), None if b is None else b.to(DEV), 1e-6)
+    assert _rel(got2.float().cpu(), ref) < _tol(dtype)
+    got3 = ops.layernorm(x.to(DEV).view(1, rows, d), None if w is None else w.to(DEV), None if b is None else b.to(DEV), 1e-6)
+    assert got3.shape == (1, rows, d) and _rel(got3.float().cpu().view(rows, d), ref) < _tol(dtype)
+
+
+def test_layernorm_refuses_rows_a_warp_cannot_hold(ops):
+    x = torch.randn(4, 4096, device=DEV, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="d <= 2048"):
+        ops.layernorm(x, None, None, 1e-6)
