@@ -315,7 +315,16 @@ int blr_rmsnorm(const void* x, int64_t ldx, int64_t rows, int d, const void* wei
  * encoder and denoiser modules around the linears run between them (HuggingFace ViT's nn.LayerNorm in
  * models/vit_b_patch16_224.py, DiT/models.py:107-109); no counterpart among the reference's operator files. */
 int blr_layernorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, const void* bias, float eps,
-                  int dtype, void* out, int64_t ldo, void* stream);
+                  int dtype, void* out, int64_t ldo, int64_t rows_per_group, int64_t ldw, int64_t ldb, int weight_plus_one,
+                  void* stream);
+/* rows_per_group > 0: weight and bias are matrices with one row (ldw / ldb apart) per group of rows_per_group
+ * consecutive rows of x, and weight_plus_one uses 1 + weight: the adaLN modulation norm(x) * (1 + scale) + shift of a
+ * DiT block (DiT/models.py:19-20, 120-121) in the norm's own pass.  rows_per_group = 0: one weight / bias for all rows.
+ *
+ * out = x + gate * y with gate one row per group of rows_per_group rows (the gated residual of the same block,
+ * DiT/models.py:120-121): 16-byte accesses.  No counterpart among the reference's operator files. */
+int blr_gated_add(const void* x, int64_t ldx, const void* y, int64_t ldy, const void* gate, int64_t ldg, int64_t rows,
+                  int64_t rows_per_group, int d, int dtype, void* out, int64_t ldo, void* stream);
 
 /* Rotary embedding and append to a static KV cache.  q, k, v: n_seq * n_tok rows (sequence-major) of heads * head_dim
  * values, row strides ldq / ldk / ldv.  Token t takes cache slot pos[t] (device int64) and the rotation angle of that

@@ -75,7 +75,8 @@ SIGNATURES = {
     "blr_blast_wq_host": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                                  _int, _int, _int, _int, _int, _int, _vp, _i64, _vp, _sz, _vp, _sz, _vp]),
     "blr_rmsnorm": (_int, [_vp, _i64, _i64, _int, _vp, C.c_float, _int, _vp, _i64, _vp]),
-    "blr_layernorm": (_int, [_vp, _i64, _i64, _int, _vp, _vp, C.c_float, _int, _vp, _i64, _vp]),
+    "blr_layernorm": (_int, [_vp, _i64, _i64, _int, _vp, _vp, C.c_float, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "blr_gated_add": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _int, _int, _vp, _i64, _vp]),
     "blr_rope_append": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _int, _vp, _vp, _vp]),
     "blr_attention_decode_scratch_bytes": (_sz, [_i64, _int, _int, _int]),
     "blr_attention_decode": (_int, [_vp, _i64, _vp, _vp, _i64, _int, _int, _int, _int, C.c_float, _int, _vp, _i64, _vp, _sz, _vp]),

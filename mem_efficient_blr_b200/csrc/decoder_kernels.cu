@@ -84,16 +84,24 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
 }
 
 // ------------------------------------------------------------------------------------------------ LayerNorm
-// out[r][:] = (x[r][:] - mean) * rsqrt(var + eps) * w[:] + b[:]  (w, b optional).  A warp per row, the row in registers
+// out[r][:] = (x[r][:] - mean) * rsqrt(var + eps) * w[:] + b[:]  (w, b optional; per group of rows_per_group rows when
+// that is set, and 1 + w in place of w with w_plus_one: adaLN modulation).  A warp per row, the row in registers
 // (up to 8 pieces of 8 values per lane: d <= 2048, d % 8 == 0), mean and variance in two passes over the registers.
 template <bool BF16>
 __global__ void __launch_bounds__(256) layernorm_kernel(const uint16_t* __restrict__ x, long long ldx, const uint16_t* __restrict__ w,
                                                         const uint16_t* __restrict__ b, float eps, int d, long long rows,
-                                                        uint16_t* __restrict__ out, long long ldo) {
+                                                        uint16_t* __restrict__ out, long long ldo, long long rows_per_group,
+                                                        long long ldw, long long ldb, int w_plus_one) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= rows) return;
+  if (rows_per_group > 0) {  // weight and bias per group of consecutive rows (a modulation per image)
+    const long long grp = r / rows_per_group;
+    if (w != nullptr) w += grp * ldw;
+    if (b != nullptr) b += grp * ldb;
+  }
+  const float w_add = w_plus_one ? 1.f : 0.f;
   const int lane = threadIdx.x & 31, pieces = d >> 3;
   const uint16_t* xr = x + r * ldx;
   float v[8][8];
@@ -139,7 +147,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const uint16_t* __restri
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float2 f = up2<BF16>(ws[k]);
-          g[2 * k] = f.x, g[2 * k + 1] = f.y;
+          g[2 * k] = f.x + w_add, g[2 * k + 1] = f.y + w_add;
         }
       }
       if (b != nullptr) {
@@ -158,6 +166,33 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const uint16_t* __restri
       *reinterpret_cast<uint4*>(orow + p * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
+}
+
+// ------------------------------------------------------------------------------------------------ gated residual
+// out[r][:] = x[r][:] + gate[r / rows_per_group][:] * y[r][:]: 16-byte accesses, one thread per 8 values.
+template <bool BF16>
+__global__ void __launch_bounds__(256) gated_add_kernel(const uint16_t* __restrict__ x, long long ldx, const uint16_t* __restrict__ y,
+                                                        long long ldy, const uint16_t* __restrict__ gate, long long ldg,
+                                                        long long rows_per_group, int d, long long total, uint16_t* __restrict__ out,
+                                                        long long ldo) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const long long id = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (id >= total) return;
+  const int pieces = d >> 3;
+  const long long r = id / pieces;
+  const int p = (int)(id - r * pieces);
+  const uint4 a = *reinterpret_cast<const uint4*>(x + r * ldx + p * 8);
+  const uint4 c = *reinterpret_cast<const uint4*>(y + r * ldy + p * 8);
+  const uint4 g = *reinterpret_cast<const uint4*>(gate + (r / rows_per_group) * ldg + p * 8);
+  const uint32_t as[4] = {a.x, a.y, a.z, a.w}, cs[4] = {c.x, c.y, c.z, c.w}, gs[4] = {g.x, g.y, g.z, g.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 fa = up2<BF16>(as[k]), fc = up2<BF16>(cs[k]), fg = up2<BF16>(gs[k]);
+    o[k] = down2<BF16>(fmaf(fg.x, fc.x, fa.x), fmaf(fg.y, fc.y, fa.y));
+  }
+  *reinterpret_cast<uint4*>(out + r * ldo + p * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // ------------------------------------------------------------------------------------------------ rotary embedding + cache append
@@ -389,8 +424,32 @@ int blr_rmsnorm(const void* x, int64_t ldx, int64_t rows, int d, const void* wei
   return launch_pdl(rmsnorm_kernel<false>, dim3((unsigned)rows), dim3(256), 0, st, xp, lx, wp, eps, d, op, lo);
 }
 
+int blr_gated_add(const void* x, int64_t ldx, const void* y, int64_t ldy, const void* gate, int64_t ldg, int64_t rows,
+                  int64_t rows_per_group, int d, int dtype, void* out, int64_t ldo, void* stream) {
+  BLR_REQUIRE(rows >= 0 && rows_per_group > 0 && d > 0 && d % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && ldg % 8 == 0 && ldo % 8 == 0,
+              BLR_ERR_ARG, "gated_add needs d and the row strides to be multiples of 8 (d = %d)", d);
+  BLR_REQUIRE(dtype == BLR_DTYPE_F16 || dtype == BLR_DTYPE_BF16, BLR_ERR_ARG, "unknown dtype %d", dtype);
+  if (rows == 0) return BLR_OK;
+  BLR_REQUIRE(x && y && gate && out, BLR_ERR_ARG, "null pointer");
+  BLR_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gate) |
+                reinterpret_cast<uintptr_t>(out)) & 15) == 0, BLR_ERR_ARG, "gated_add needs 16-byte aligned pointers");
+  const long long total = rows * (d >> 3);
+  BLR_REQUIRE((total + 255) / 256 < (1ll << 31), BLR_ERR_SHAPE, "too many rows");
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const uint16_t* yp = static_cast<const uint16_t*>(y);
+  const uint16_t* gp = static_cast<const uint16_t*>(gate);
+  uint16_t* op = static_cast<uint16_t*>(out);
+  const long long lx = ldx, ly = ldy, lg = ldg, lo = ldo, rpg = rows_per_group;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == BLR_DTYPE_BF16) return launch_pdl(gated_add_kernel<true>, grid, dim3(256), 0, st, xp, lx, yp, ly, gp, lg, rpg, d, total, op, lo);
+  return launch_pdl(gated_add_kernel<false>, grid, dim3(256), 0, st, xp, lx, yp, ly, gp, lg, rpg, d, total, op, lo);
+}
+
 int blr_layernorm(const void* x, int64_t ldx, int64_t rows, int d, const void* weight, const void* bias, float eps, int dtype, void* out,
-                  int64_t ldo, void* stream) {
+                  int64_t ldo, int64_t rows_per_group, int64_t ldw, int64_t ldb, int weight_plus_one, void* stream) {
+  BLR_REQUIRE(rows_per_group >= 0 && (rows_per_group == 0 || (ldw % 8 == 0 && ldb % 8 == 0)), BLR_ERR_ARG,
+              "layernorm: per-group weights need row strides that are multiples of 8");
   BLR_REQUIRE(rows >= 0 && d > 0 && d % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0, BLR_ERR_ARG,
               "layernorm needs d, ldx and ldo to be multiples of 8 (d = %d)", d);
   BLR_REQUIRE(d <= 2048, BLR_ERR_UNSUPPORTED, "layernorm keeps a row in a warp's registers: d <= 2048, got %d", d);
@@ -405,10 +464,11 @@ int blr_layernorm(const void* x, int64_t ldx, int64_t rows, int d, const void* w
   const uint16_t* wp = static_cast<const uint16_t*>(weight);
   const uint16_t* bp = static_cast<const uint16_t*>(bias);
   uint16_t* op = static_cast<uint16_t*>(out);
-  const long long lx = ldx, lo = ldo, nr = rows;
+  const long long lx = ldx, lo = ldo, nr = rows, rpg = rows_per_group, lw = ldw, lb = ldb;
   const dim3 grid((unsigned)((rows + 7) / 8));
-  if (dtype == BLR_DTYPE_BF16) return launch_pdl(layernorm_kernel<true>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo);
-  return launch_pdl(layernorm_kernel<false>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo);
+  if (dtype == BLR_DTYPE_BF16)
+    return launch_pdl(layernorm_kernel<true>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo, rpg, lw, lb, weight_plus_one);
+  return launch_pdl(layernorm_kernel<false>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo, rpg, lw, lb, weight_plus_one);
 }
 
 int blr_rope_append(void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const float* cos_table,

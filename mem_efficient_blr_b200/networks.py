@@ -478,10 +478,20 @@ class DiTBlock(nn.Module):
     def forward(self, x, c):
         B, T, d = x.shape
         sa, ca, ga, sm, cm, gm = self.adaln(F.silu(c)).chunk(6, dim=1)
-        q, k, v = self.qkv(_modulate(self.norm1(x), sa, ca)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
+        # 16-bit tensors on the GPU: norm + modulation in one kernel and the gated residuals in another (torch's broadcast
+        # element-wise kernels ran at 1 TB/s: a quarter of the denoiser's time at batch 64)
+        fast = x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and d % 8 == 0 and d <= 2048 and not torch.compiler.is_compiling()
+        if fast:
+            from . import ops
+            mod = lambda norm, t, shift, scale: ops.layernorm_modulate(t, shift, scale, norm.eps)
+            gated = ops.gated_add
+        else:
+            mod = lambda norm, t, shift, scale: _modulate(norm(t), shift, scale)
+            gated = lambda t, gate, y: torch.addcmul(t, gate.unsqueeze(1), y)
+        q, k, v = self.qkv(mod(self.norm1, x, sa, ca)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
         a = F.scaled_dot_product_attention(q, k, v)
-        x = torch.addcmul(x, ga.unsqueeze(1), self.proj(a.transpose(1, 2).reshape(B, T, d)))
-        return torch.addcmul(x, gm.unsqueeze(1), self.fc2(F.gelu(self.fc1(_modulate(self.norm2(x), sm, cm)), approximate="tanh")))
+        x = gated(x, ga, self.proj(a.transpose(1, 2).reshape(B, T, d)))
+        return gated(x, gm, self.fc2(F.gelu(self.fc1(mod(self.norm2, x, sm, cm)), approximate="tanh")))
 
 
 class DiTDenoiser(nn.Module):
@@ -514,7 +524,12 @@ class DiTDenoiser(nn.Module):
     def forward(self, latents: torch.Tensor, t: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         s = self.shape
         B = latents.shape[0]
-        x = self.x_embed(latents).flatten(2).transpose(1, 2) + self.posemb
+        # patch embedding as a GEMM over unfolded patches, which also leaves x token-major and contiguous (the transposed
+        # view of a convolution's output made every element-wise kernel after it a strided one and every norm a copy)
+        C, p = s.channels, s.patch
+        hh = s.latent // p
+        x = latents.view(B, C, hh, p, hh, p).permute(0, 2, 4, 1, 3, 5).reshape(B, hh * hh, C * p * p)
+        x = F.linear(x, self.x_embed.weight.view(self.x_embed.weight.shape[0], -1), self.x_embed.bias) + self.posemb
         ang = t.float()[:, None] * self.freqs[None]
         temb = torch.cat((ang.cos(), ang.sin()), dim=-1).to(x.dtype)
         c = self.t_fc2(F.silu(self.t_fc1(temb))) + self.y_embed(y)

@@ -499,19 +499,52 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out if x.dim() == 2 else out.reshape(*x.shape[:-1], d)
 
 
+def _rows16(t: torch.Tensor, d: int) -> torch.Tensor:
+    """(..., d) -> (rows, d) with unit inner stride, a row stride that is a multiple of 8 and a 16-byte aligned base."""
+    t2 = t if t.dim() == 2 else t.reshape(-1, d)
+    if t2.stride(1) != 1 or t2.stride(0) % 8 != 0 or t2.data_ptr() % 16 != 0:
+        t2 = t2.contiguous()
+    return t2
+
+
 def layernorm(x: torch.Tensor, weight, bias, eps: float) -> torch.Tensor:
     """x (..., d) 16-bit CUDA tensor -> LayerNorm over d with optional weight / bias (None: none), fp32 arithmetic, one
     rounding; d a multiple of 8, at most 2048."""
     _need_cuda(x)
     d = x.shape[-1]
-    x2 = x if x.dim() == 2 else x.reshape(-1, d)
-    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
-        x2 = x2.contiguous()
+    x2 = _rows16(x, d)
     out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
     L.check(L.load().blr_layernorm(x2.data_ptr(), x2.stride(0), x2.shape[0], d, None if weight is None else weight.data_ptr(),
                                    None if bias is None else bias.data_ptr(), float(eps), L.dtype_code(x.dtype), out.data_ptr(),
-                                   out.stride(0), L.stream_ptr(x.device)))
+                                   out.stride(0), 0, 0, 0, 0, L.stream_ptr(x.device)))
     return out if x.dim() == 2 else out.reshape(x.shape)
+
+
+def layernorm_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float) -> torch.Tensor:
+    """norm(x) * (1 + scale) + shift in the norm's own pass: x (B, T, d), shift and scale (B, d) (rows of a wider matrix
+    are fine), no affine parameters (the adaLN modulation of a DiT block, DiT/models.py:19-20)."""
+    _need_cuda(x, )
+    B, T, d = x.shape
+    x2 = _rows16(x, d)
+    sh, sc = _rows16(shift, d), _rows16(scale, d)
+    assert tuple(sh.shape) == (B, d) and tuple(sc.shape) == (B, d) and sh.dtype == x.dtype and sc.dtype == x.dtype
+    out = torch.empty((B * T, d), dtype=x.dtype, device=x.device)
+    L.check(L.load().blr_layernorm(x2.data_ptr(), x2.stride(0), B * T, d, sc.data_ptr(), sh.data_ptr(), float(eps),
+                                   L.dtype_code(x.dtype), out.data_ptr(), out.stride(0), T, sc.stride(0), sh.stride(0), 1,
+                                   L.stream_ptr(x.device)))
+    return out.view(B, T, d)
+
+
+def gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x + gate[:, None, :] * y: x, y (B, T, d), gate (B, d) (the gated residual of a DiT block)."""
+    _need_cuda(x, )
+    B, T, d = x.shape
+    x2, y2, g2 = _rows16(x, d), _rows16(y, d), _rows16(gate, d)
+    assert y.shape == x.shape and tuple(g2.shape) == (B, d) and y.dtype == x.dtype and g2.dtype == x.dtype
+    out = torch.empty((B * T, d), dtype=x.dtype, device=x.device)
+    L.check(L.load().blr_gated_add(x2.data_ptr(), x2.stride(0), y2.data_ptr(), y2.stride(0), g2.data_ptr(), g2.stride(0), B * T, T, d,
+                                   L.dtype_code(x.dtype), out.data_ptr(), out.stride(0), L.stream_ptr(x.device)))
+    return out.view(B, T, d)
 
 
 def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,

@@ -142,3 +142,23 @@ def test_layernorm_refuses_rows_a_warp_cannot_hold(ops):
     x = torch.randn(4, 4096, device=DEV, dtype=torch.float16)
     with pytest.raises(RuntimeError, match="d <= 2048"):
         ops.layernorm(x, None, None, 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,T,d", [(1, 256, 1152), (3, 16, 144), (5, 7, 2048)])
+def test_layernorm_modulate_and_gated_add(ops, B, T, d, dtype):
+    """norm(x) * (1 + scale) + shift with one (shift, scale) row per image taken as column slices of a wider matrix, and
+    x + gate * y, against fp32 PyTorch on the same 16-bit inputs."""
+    g = torch.Generator().manual_seed(B * T + d)
+    x = (torch.randn(B, T, d, generator=g) + 2).to(dtype)
+    y = torch.randn(B, T, d, generator=g).to(dtype)
+    mod = torch.randn(B, 3 * d, generator=g).to(dtype)       # shift | scale | gate as an adaLN linear emits them
+    xd, yd, md = x.to(DEV), y.to(DEV), mod.to(DEV)
+    shift, scale, gate = md.chunk(3, dim=1)
+    sf, cf, gf = (t.float() for t in mod.chunk(3, dim=1))
+    ref = F.layer_norm(x.float(), (d,), None, None, 1e-6) * (1 + cf.unsqueeze(1)) + sf.unsqueeze(1)
+    got = ops.layernorm_modulate(xd, shift, scale, 1e-6)
+    assert got.shape == x.shape and got.dtype == dtype and _rel(got.float().cpu(), ref) < _tol(dtype)
+    ref2 = x.float() + gf.unsqueeze(1) * y.float()
+    got2 = ops.gated_add(xd, gate, yd)
+    assert got2.shape == x.shape and _rel(got2.float().cpu(), ref2) < _tol(dtype)
