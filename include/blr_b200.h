@@ -152,6 +152,10 @@ int blr_blast_rows_prepared(const void* x, int64_t ldx, int64_t n_tokens, int dt
  * epilogue adds bias and residual; BLR_ACT_SILU_MUL is not available there (BLR_ERR_UNSUPPORTED). */
 #define BLR_ACT_NONE 0
 #define BLR_ACT_SILU_MUL 1
+/* Output activations of the fused call above 16 tokens, OR-ed into `act`: applied to result + bias, ahead of the residual
+ * (the GELU between the two linears of an encoder / denoiser MLP: models/vit_b_patch16_224.py, DiT/models.py:111-112). */
+#define BLR_ACT_OUT_GELU 0x10
+#define BLR_ACT_OUT_GELU_TANH 0x20
 typedef struct blr_blast_problem {
   const void* U;
   const void* V;

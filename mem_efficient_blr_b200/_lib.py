@@ -30,6 +30,7 @@ class BlastProblem(C.Structure):
 
 
 ACT_NONE, ACT_SILU_MUL = 0, 1
+ACT_OUT = {None: 0, "gelu": 0x10, "gelu_tanh": 0x20}   # output activations of the fused call above 16 tokens
 
 # name -> (restype, argtypes); must list every symbol include/blr_b200.h declares
 SIGNATURES = {

@@ -117,13 +117,14 @@ def blast_torch_layout(x, U, Vt, S, flags=L.FLAG_NONE):
     return ops._like_input(out, x)
 
 
-def blast_multi_torch_layout(x, layers, x_mul=None, biases=None, residuals=None):
+def blast_multi_torch_layout(x, layers, x_mul=None, biases=None, residuals=None, out_act=None):
     """Several BLAST layers on one input, torch layouts: layers = [(U (b,Q,R), Vt (b,R,P), S (b,b,R)), ...] with equal
     shapes.  Optional: x_mul - the input becomes silu(x) * x_mul (a down projection fed with the gate and up results);
     biases[i] (O,) and residuals[i] (..., O) are added to layer i's result.  Returns the list of outputs.
     At decode sizes (up to 16 tokens) everything is one pair of launches (blr_blast_multi: no counterpart in the
     reference, which calls one operator per layer and separate torch kernels for the rest, models/wrappers.py:171-177);
-    above that the layers run one by one, biases and residuals added by the last GEMM's epilogue."""
+    above that the layers run one by one, biases and residuals added by the last GEMM's epilogue.
+    out_act ("gelu" | "gelu_tanh"): applied to result + bias ahead of the residual (in that epilogue above 16 tokens)."""
     U0, Vt0, S0 = layers[0]
     b, r, p = Vt0.shape
     q = U0.shape[1]
@@ -133,17 +134,19 @@ def blast_multi_torch_layout(x, layers, x_mul=None, biases=None, residuals=None)
     x2 = ops._flat2d(x)
     xm2 = None if x_mul is None else ops._flat2d(x_mul)
     res2 = None if residuals is None else [None if t is None else ops._flat2d(t) for t in residuals]
-    outs = ops.blast_multi(x2, layers, 16, 0, b, p, q, r, xm2, biases, res2) if 1 <= len(layers) <= 3 else None
+    outs = ops.blast_multi(x2, layers, 16, 0, b, p, q, r, xm2, biases, res2, out_act) if 1 <= len(layers) <= 3 else None
     if outs is None:
         xe = x2 if xm2 is None else torch.nn.functional.silu(x2) * xm2
         if xm2 is not None and 1 <= len(layers) <= 3:   # the input transform done here, the rest may still fuse
-            outs = ops.blast_multi(xe, layers, 16, 0, b, p, q, r, None, biases, res2)
+            outs = ops.blast_multi(xe, layers, 16, 0, b, p, q, r, None, biases, res2, out_act)
     if outs is None:
         outs = []
         for i, (U, Vt, S) in enumerate(layers):
             o = ops.blast(xe, U, Vt, S, L.KMAJOR, L.KMAJOR, b * r, r, 1, b, p, q, r, L.FLAG_NONE)
             if biases is not None and biases[i] is not None:
                 o += biases[i]
+            if out_act is not None:
+                o = torch.nn.functional.gelu(o, approximate="tanh" if out_act == "gelu_tanh" else "none")
             if res2 is not None and res2[i] is not None:
                 o += res2[i]
             outs.append(o)

@@ -80,7 +80,7 @@ def blast_wq(x, Uq, u_scale, Vq, v_scale, S, bits: int, group: int = 0):
     return ops._like_input(out, x)
 
 
-def blast_wq_multi(x, layers, bits: int, group: int = 0, x_mul=None, biases=None, residuals=None):
+def blast_wq_multi(x, layers, bits: int, group: int = 0, x_mul=None, biases=None, residuals=None, out_act=None):
     """blast_wq for several layers on one input: layers = [(Uq, u_scale, Vq, v_scale, S), ...] with equal shapes; the
     options of blast_kernels.blast_multi_torch_layout.  One pair of launches up to 16 tokens (preceded above 2 tokens, or
     with x_mul, by one launch that converts x to fixed point once), else layer by layer."""
@@ -91,17 +91,19 @@ def blast_wq_multi(x, layers, bits: int, group: int = 0, x_mul=None, biases=None
     x2 = ops._flat2d(x)
     xm2 = None if x_mul is None else ops._flat2d(x_mul)
     res2 = None if residuals is None else [None if t is None else ops._flat2d(t) for t in residuals]
-    outs = ops.blast_multi(x2, layers, bits, group, b, p, q, r, xm2, biases, res2) if 1 <= len(layers) <= 3 else None
+    outs = ops.blast_multi(x2, layers, bits, group, b, p, q, r, xm2, biases, res2, out_act) if 1 <= len(layers) <= 3 else None
     if outs is None:
         xe = x2 if xm2 is None else torch.nn.functional.silu(x2) * xm2
         if xm2 is not None and 1 <= len(layers) <= 3:   # the input transform done here, the rest may still fuse
-            outs = ops.blast_multi(xe, layers, bits, group, b, p, q, r, None, biases, res2)
+            outs = ops.blast_multi(xe, layers, bits, group, b, p, q, r, None, biases, res2, out_act)
     if outs is None:
         outs = []
         for i, (Uq, us, Vq, vs, S) in enumerate(layers):
             o = ops._flat2d(blast_wq(xe, Uq, us, Vq, vs, S, bits, group))
             if biases is not None and biases[i] is not None:
                 o += biases[i]
+            if out_act is not None:
+                o = torch.nn.functional.gelu(o, approximate="tanh" if out_act == "gelu_tanh" else "none")
             if res2 is not None and res2[i] is not None:
                 o += res2[i]
             outs.append(o)

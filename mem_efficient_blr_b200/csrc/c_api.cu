@@ -467,7 +467,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
                       const void* u_scale, const void* V, int v_layout, int v_bits, const void* v_scale, int group, const void* S,
                       int64_t s_i, int64_t s_j, int64_t s_r, int b, int bo, int P, int Q, int R, int flags, void* out,
                       int64_t ldo, void* ws, size_t ws_bytes, cudaStream_t stream, const void* e_ready = nullptr,
-                      const void* bias = nullptr, const void* residual = nullptr, int64_t ldr = 0) {
+                      const void* bias = nullptr, const void* residual = nullptr, int64_t ldr = 0, int out_act = 0) {
   // (bias / residual: added by the last GEMM above 16 tokens; callers with fewer tokens use the two-launch path's own)
   int rc = check_common(x, ldx, N, dtype, out, ldo);
   if (rc) return rc < 0 ? rc : BLR_OK;
@@ -511,7 +511,7 @@ static int blast_impl(const void* x, int64_t ldx, int64_t N, int dtype, const vo
     rc = pipeline_blast(static_cast<const uint8_t*>(x) + n0 * ldx * 2, ldx, n, dtype, U, u_layout, V, v_layout, S, s_i, s_j, s_r, b,
                         bo, P, Q, R, act8, static_cast<uint8_t*>(out) + n0 * ldo * 2, ldo, w.region_a, w.region_b, w.region_c, stream,
                         e_ready, u_bits != 16 || v_bits != 16 ? &quant : nullptr, bias,
-                        residual ? static_cast<const uint8_t*>(residual) + n0 * ldr * 2 : nullptr, ldr);
+                        residual ? static_cast<const uint8_t*>(residual) + n0 * ldr * 2 : nullptr, ldr, out_act);
     if (rc) return rc;
   }
   return BLR_OK;
@@ -693,7 +693,12 @@ int blr_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int6
   BLR_REQUIRE(n_problems >= 1 && n_problems <= kSplitMaxProblems, BLR_ERR_UNSUPPORTED, "1..%d layers per call, got %d",
               kSplitMaxProblems, n_problems);
   BLR_REQUIRE(bits == 16 || bits == 8 || bits == 4, BLR_ERR_ARG, "bits must be 16, 8 or 4, got %d", bits);
+  const int out_act = act >> 4;  // BLR_ACT_OUT_*: applied to result + bias, ahead of the residual
+  act &= 15;
   BLR_REQUIRE(act == BLR_ACT_NONE || act == BLR_ACT_SILU_MUL, BLR_ERR_ARG, "unknown input transform %d", act);
+  BLR_REQUIRE(out_act >= 0 && out_act <= 2, BLR_ERR_ARG, "unknown output activation %d", out_act);
+  BLR_REQUIRE(out_act == 0 || n_tokens > kStreamMaxTokens, BLR_ERR_UNSUPPORTED, "output activations are fused above %d tokens only",
+              kStreamMaxTokens);
   BLR_REQUIRE(act == BLR_ACT_NONE || x_mul != nullptr, BLR_ERR_ARG, "the silu-mul transform needs x_mul");
   BLR_REQUIRE(b >= 2 && P > 0 && Q > 0 && R > 0 && ldx >= (int64_t)b * P, BLR_ERR_SHAPE, "bad dimensions");
   SplitLayer layers[kSplitMaxProblems];
@@ -711,7 +716,7 @@ int blr_blast_multi(const void* x, int64_t ldx, const void* x_mul, int act, int6
       const blr_blast_problem& q = problems[i];
       const int rc1 = blast_impl(x, ldx, N, dtype, q.U, BLR_W_KMAJOR, bits, bits == 16 ? nullptr : q.u_scale, q.V, BLR_W_KMAJOR, bits,
                                  bits == 16 ? nullptr : q.v_scale, group, q.S, s_i, s_j, s_r, b, b, P, Q, R, BLR_FLAG_NONE, q.out, q.ldo,
-                                 ws, ws_bytes, static_cast<cudaStream_t>(stream), nullptr, q.bias, q.residual, q.ldr);
+                                 ws, ws_bytes, static_cast<cudaStream_t>(stream), nullptr, q.bias, q.residual, q.ldr, out_act);
       if (rc1) return rc1;
     }
     return BLR_OK;

@@ -44,6 +44,7 @@ struct OutSpec {
   const void* bias = nullptr;
   const void* residual = nullptr;
   long long ldr = 0;
+  int act = 0;  // after the bias, before the residual: 1 GELU, 2 GELU (tanh)
 };
 
 // Quantised weights of one GEMM: bits 8 | 4 (16: none), fp16 scales per weight row (group = 0) or per `group`
@@ -66,7 +67,7 @@ static int run_gemm(int dtype, const void* W, int layout, int G, int M, int K, c
   p.is_bf16 = dtype == BLR_DTYPE_BF16;
   p.round_out = o.round_out;
   p.per = o.per; p.os_g = o.os_g; p.os_n = o.os_n; p.os_hi = o.os_hi; p.os_lo = o.os_lo; p.out = o.out;
-  p.bias = o.bias; p.residual = o.residual; p.ldr = o.ldr;
+  p.bias = o.bias; p.residual = o.residual; p.ldr = o.ldr; p.act_out = o.act;
   p.extra_vec = M % 8 == 0 && (reinterpret_cast<uintptr_t>(o.bias) & 15) == 0 && (reinterpret_cast<uintptr_t>(o.residual) & 15) == 0 &&
                 o.ldr % 8 == 0;
   p.status = nullptr;
@@ -320,7 +321,7 @@ static int run_expand(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, void
 int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void* U, int u_layout, const void* V,
                    int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
                    int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream, const void* e_ready,
-                   const BlastQuant* quant, const void* bias, const void* residual, int64_t ldr) {
+                   const BlastQuant* quant, const void* bias, const void* residual, int64_t ldr, int out_act) {
   QuantSpec qu, qv;  // quantised U / V: widened tile by tile inside the GEMMs that read them
   if (quant != nullptr) {
     qu.bits = quant->u_bits, qu.scale = quant->u_scale, qu.group = quant->group;
@@ -338,7 +339,7 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
     rc = bf ? run_couple_tile<__nv_bfloat16>(y16, S, s_i, s_j, z16, b, b_out, N, R, act_int8, stream)
             : run_couple_tile<__half>(y16, S, s_i, s_j, z16, b, b_out, N, R, act_int8, stream);
     if (rc < 0) return rc;
-    if (rc == 0) return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0, bias, residual, ldr}, stream, qu);
+    if (rc == 0) return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0, bias, residual, ldr, out_act}, stream, qu);
     // rc == 1: no instantiation for this block count; y16 is overwritten below in the layout that path wants
   }
   if (b <= 16 && R % 8 == 0) {
@@ -366,7 +367,7 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
     if (rc) return rc;
   }
   // out[n][i*Q + q] = sum_r U[i][q][r] z[i][n][r]
-  return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0, bias, residual, ldr}, stream, qu);
+  return run_gemm(dtype, U, u_layout, b_out, Q, R, z16, N, R, plane, OutSpec{out, Q, ldo, 0, 1, Q, 0, bias, residual, ldr, out_act}, stream, qu);
 }
 
 size_t pipeline_coupling_bytes(int b, int b_out, int R) {

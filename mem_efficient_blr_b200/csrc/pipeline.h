@@ -17,7 +17,7 @@ int pipeline_blast(const void* x, int64_t ldx, int64_t N, int dtype, const void*
                    int v_layout, const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int P, int Q, int R,
                    int act_int8, void* out, int64_t ldo, void* y16, void* z16, void* e16, cudaStream_t stream,
                    const void* e_ready = nullptr, const BlastQuant* quant = nullptr, const void* bias = nullptr,
-                   const void* residual = nullptr, int64_t ldr = 0);
+                   const void* residual = nullptr, int64_t ldr = 0, int out_act = 0);
 // Expanded coupling factors of the prefill pipeline: size (0: shapes whose coupling does not use them) and construction.
 size_t pipeline_coupling_bytes(int b, int b_out, int R);
 int pipeline_expand_coupling(const void* S, int64_t s_i, int64_t s_j, int64_t s_r, int b, int b_out, int R, int dtype, void* E,

@@ -105,8 +105,19 @@ __device__ __forceinline__ float gemm_load(const uint16_t* p) {
   else return __half2float(*reinterpret_cast<const __half*>(p));
 }
 
+__device__ __forceinline__ float gemm_act(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (act == 2) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * v, v * v, v)));
+    return 0.5f * v * (1.f + t);
+  }
+  return v;
+}
+
 // Epilogue of one tile when tokens are the MMA rows: this thread's token, its columns = consecutive weight rows.
 struct EpiRow {
+  int act;
   const uint16_t* bias;  // at the group's first feature, or null
   const uint16_t* res;   // the token's residual row at the group's first feature, or null
   int extra_vec;
@@ -133,6 +144,10 @@ __device__ __forceinline__ void epilogue_store32(const EpiRow& e, int c0, uint32
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         const uint16_t* src = part == 0 ? e.bias : e.res;
+        if (part == 1 && e.act != 0) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(gemm_act(__uint_as_float(r[j]), e.act));
+        }
         if (src == nullptr || (part == 1 && !e.n_ok)) continue;
         if (e.extra_vec && m + 16 <= e.M) {
 #pragma unroll
@@ -401,6 +416,7 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
         const int n = nt * kBM + q * 32 + lane;
         e.n_ok = n < p.N;
         e.extra_vec = p.extra_vec;
+        e.act = p.act_out;
         e.bias = p.bias ? static_cast<const uint16_t*>(p.bias) + (long long)g * p.M : nullptr;
         e.res = p.residual && e.n_ok ? static_cast<const uint16_t*>(p.residual) + (long long)n * p.ldr + (long long)g * p.M : nullptr;
         e.nbase = gbase + (long long)n * p.os_n;
@@ -432,7 +448,7 @@ __global__ void __launch_bounds__(kGemmThreads + (WQ ? 32 * kConvWarps : 0), 1)
               if (n < p.N) {
                 float v = __uint_as_float(r[j]);
                 if constexpr (EX) {
-                  v += bias_m;
+                  v = gemm_act(v + bias_m, p.act_out);
                   if (res_m != nullptr) v += gemm_load<BF16>(res_m + (long long)n * p.ldr);
                 }
                 gemm_store<BF16>(p.out, base + (long long)n * p.os_n, gemm_round<RND>(v));
@@ -520,7 +536,7 @@ static int launch_plain(const GemmParams& p, int mode, int grid, size_t smem, in
 }
 template <bool BF16, int WQ>
 static int launch_quantised(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
-  return (p.bias || p.residual) ? launch_plain<BF16, WQ, true>(p, mode, grid, smem, dev, max_smem, stream)
+  return (p.bias || p.residual || p.act_out) ? launch_plain<BF16, WQ, true>(p, mode, grid, smem, dev, max_smem, stream)
                                 : launch_plain<BF16, WQ, false>(p, mode, grid, smem, dev, max_smem, stream);
 }
 
@@ -528,7 +544,7 @@ template <bool BF16>
 static int launch_dtype(const GemmParams& p, int mode, int grid, size_t smem, int dev, int max_smem, cudaStream_t stream) {
   if (p.w_bits == 8) return launch_quantised<BF16, 8>(p, mode, grid, smem, dev, max_smem, stream);
   if (p.w_bits == 4) return launch_quantised<BF16, 4>(p, mode, grid, smem, dev, max_smem, stream);
-  if (p.bias || p.residual) {
+  if (p.bias || p.residual || p.act_out) {
     BLR_REQUIRE(!p.round_out, BLR_ERR_ARG, "bias and residual are not combined with rounded outputs");
     return launch_plain<BF16, 0, true>(p, mode, grid, smem, dev, max_smem, stream);
   }

@@ -33,6 +33,7 @@ struct alignas(64) GemmParams {
   const void* residual;
   long long ldr;
   int extra_vec;
+  int act_out;  // applied after the bias, before the residual: 0 none, 1 GELU (erf), 2 GELU (tanh approximation)
   // Quantised weights: int8 or packed int4 (two per byte along k, even index in the low nibble, two's complement) with
   // fp16 scales [g][m][scales_per_row] (1: per weight row; K / 128: per 128 contraction indices).  Converter warps
   // widen every staged tile to the 16-bit dtype (q * scale, rounded once) in shared memory ahead of the MMA.

@@ -66,9 +66,11 @@ class BlastTorchLinear(nn.Module):
         self.S = nn.Parameter((torch.rand(b, b, rank, generator=g, device=gd) + 0.5).to(device=device, dtype=dtype), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype), requires_grad=False) if bias else None
 
-    def forward(self, x):
-        if self.bias is not None:   # (added by the kernels' epilogue where the fused call applies)
-            return bk.blast_multi_torch_layout(x, [(self.U, self.Vt, self.S)], biases=[self.bias])[0]
+    def forward(self, x, out_act=None):
+        """out_act ("gelu" | "gelu_tanh"): the activation that follows the layer, applied in the kernels' epilogue where
+        the fused call applies."""
+        if self.bias is not None or out_act is not None:   # (bias and activation in the kernels' epilogue where the fused call applies)
+            return bk.blast_multi_torch_layout(x, [(self.U, self.Vt, self.S)], biases=[self.bias], out_act=out_act)[0]
         return bk.blast_torch_layout(x, self.U, self.Vt, self.S)
 
     def U_device_ok(self) -> bool:
@@ -110,10 +112,10 @@ class BlastQuantLinear(nn.Module):
     def U_device_ok(self) -> bool:
         return self.Uq.is_cuda
 
-    def forward(self, x):
-        if self.bias is not None:
+    def forward(self, x, out_act=None):
+        if self.bias is not None or out_act is not None:
             return bq.blast_wq_multi(x, [(self.Uq, self.u_scale, self.Vq, self.v_scale, self.S)], self.bits, self.group,
-                                     biases=[self.bias])[0]
+                                     biases=[self.bias], out_act=out_act)[0]
         return bq.blast_wq(x, self.Uq, self.u_scale, self.Vq, self.v_scale, self.S, self.bits, self.group)
 
 
@@ -137,6 +139,14 @@ def make_linear(method: str, in_features: int, out_features: int, b: int, rank: 
     if method in ("blast_int8", "blast_int4"):
         return base.quantized(8 if method == "blast_int8" else 4)
     raise ValueError(f"unknown method {method!r}")
+
+
+def linear_act(m, x, act: str):
+    """act(m(x)) for act = "gelu" | "gelu_tanh": inside the layer's kernels where it is a BLAST layer of this module (and its
+    forward has not been replaced), else torch's activation on the layer's result."""
+    if isinstance(m, (BlastTorchLinear, BlastQuantLinear)) and "forward" not in vars(m) and m.U_device_ok():
+        return m(x, out_act=act)
+    return F.gelu(m(x), approximate="tanh" if act == "gelu_tanh" else "none")
 
 
 def structured_multi(mods, x, x_mul=None, residual=None):
@@ -394,7 +404,7 @@ class ViTLayer(nn.Module):
         q, k, v = self.qkv(self.ln1(x)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
         a = F.scaled_dot_product_attention(q, k, v)
         x = x + self.attn_out(a.transpose(1, 2).reshape(B, T, d))
-        return x + self.output(F.gelu(self.intermediate(self.ln2(x))))
+        return x + self.output(linear_act(self.intermediate, self.ln2(x), "gelu"))
 
 
 class ViTEncoder(nn.Module):
@@ -491,7 +501,7 @@ class DiTBlock(nn.Module):
         q, k, v = self.qkv(mod(self.norm1, x, sa, ca)).view(B, T, 3, self.heads, d // self.heads).permute(2, 0, 3, 1, 4)
         a = F.scaled_dot_product_attention(q, k, v)
         x = gated(x, ga, self.proj(a.transpose(1, 2).reshape(B, T, d)))
-        return gated(x, gm, self.fc2(F.gelu(self.fc1(mod(self.norm2, x, sm, cm)), approximate="tanh")))
+        return gated(x, gm, self.fc2(linear_act(self.fc1, mod(self.norm2, x, sm, cm), "gelu_tanh")))
 
 
 class DiTDenoiser(nn.Module):

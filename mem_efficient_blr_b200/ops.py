@@ -423,12 +423,14 @@ def load_store_probe(operands, n: int, out_features: int, dtype: torch.dtype, ti
 
 
 # ----------------------------------------------------------------------------- several layers in one pair of launches
-def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int, x_mul=None, biases=None, residuals=None):
+def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int, x_mul=None, biases=None, residuals=None,
+                out_act=None):
     """Up to three BLAST layers that share x (N, b*P) and their shapes, through blr_blast_multi.
     layers: tuples (U, Vt, S) of 16-bit factors (bits = 16) or (Uq, u_scale, Vq, v_scale, S) (bits = 8 | 4), torch
     layouts.  x_mul: the input becomes silu(x) * x_mul.  biases / residuals: per layer, None or a tensor added to the
     layer's result ((b*Q,) / (N, b*Q)).  Returns the list of outputs, or None when the fused call does not apply
-    (token count or shape outside the two-launch decode path): the caller then runs the layers one by one."""
+    (token count or shape outside the two-launch decode path): the caller then runs the layers one by one.
+    out_act ("gelu" | "gelu_tanh"): applied to result + bias ahead of the residual; fused above 16 tokens only."""
     n = x.shape[0]
     # decode sizes: the fused pair of launches where it is the faster route; prefill sizes: one call per layer list, worth
     # it when there is a bias or a residual for the last GEMM's epilogue to add (otherwise the plain operators do the same)
@@ -436,7 +438,9 @@ def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int
     # (up to 64 tokens the weights are the MMA rows and a thread would fetch its residuals one 2-byte load per token:
     # measured 23.4 us fused against 21.1 us with torch's add at 64 tokens; at 2048 tokens fused and unfused are within
     # 3 % of each other either way - residuals are fused from 65 to 512 tokens, where it gains 1 - 2 us per call)
-    prefill = (n > 16 and x_mul is None and (any(t is not None for t in (biases or [])) or has_res)
+    if out_act is not None and n <= 16:
+        return None
+    prefill = (n > 16 and x_mul is None and (any(t is not None for t in (biases or [])) or has_res or out_act is not None)
                and not (has_res and (n <= 64 or n > 512)))
     if n == 0 or torch.compiler.is_compiling() or (n > (8 if bits == 16 else 4) and not prefill):
         return None
@@ -477,7 +481,7 @@ def blast_multi(x, layers, bits: int, group: int, b: int, P: int, Q: int, R: int
     if prefill:
         ws, st = _ws(x, n, k * b, R, also=(b, R))
     rc = L.load().blr_blast_multi(x.data_ptr(), x.stride(0), 0 if x_mul is None else x_mul.data_ptr(),
-                                  L.ACT_NONE if x_mul is None else L.ACT_SILU_MUL, n, L.dtype_code(x.dtype), k, arr,
+                                  (L.ACT_NONE if x_mul is None else L.ACT_SILU_MUL) | L.ACT_OUT[out_act], n, L.dtype_code(x.dtype), k, arr,
                                   b * R, R, 1, bits, group, b, P, Q, R, ws.data_ptr(), ws.numel(), st)
     if rc == -6:   # BLR_ERR_UNSUPPORTED: shape outside the fused path
         return None

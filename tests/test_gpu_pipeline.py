@@ -400,3 +400,41 @@ def test_bias_and_residual_added_by_the_pipeline(K, shape, bits, dtype):
     wide[:, 1:O + 1] = rd
     got = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, None, [wide[:, 1:O + 1]])[0]
     assert _err(got, ref + res.float()) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("act", ["gelu", "gelu_tanh"])
+@pytest.mark.parametrize("shape,bits", [((40, 512, 768, 4, 128), 16), ((197, 768, 3072, 16, 288), 16), ((300, 1152, 4608, 9, 256), 16),
+                                        ((130, 512, 768, 4, 128), 8)])
+def test_output_activation_in_the_epilogue(K, shape, bits, act, dtype):
+    """gelu(result + bias) (+ residual) by the last GEMM's epilogue above 16 tokens, against the oracle and torch's GELU in
+    fp32; up to 16 tokens the wrappers apply torch's activation."""
+    from mem_efficient_blr_b200 import ops
+    N, I, O, b, R = shape
+    x, U, Vt, S = orc.make_blast_inputs(N, I, O, b, R, dtype, seed=N)
+    g = torch.Generator().manual_seed(N + 1)
+    bias = torch.randn(O, generator=g).to(dtype)
+    res = torch.randn(N, O, generator=g).to(dtype)
+    if bits == 16:
+        lin = orc.blast(x, U, Vt, S)[0].reshape(N, O)
+        layers = [tuple(_cuda(U, Vt, S))]
+    else:
+        Uq, us = orc.quantize_sym(U, bits)
+        Vq, vs = orc.quantize_sym(Vt, bits)
+        lin = orc.blast_wq(x, Uq, us, Vq, vs, S, bits)[0].reshape(N, O)
+        layers = [tuple(_cuda(Uq, us, Vq, vs, S))]
+    gelu = lambda t: torch.nn.functional.gelu(t, approximate="tanh" if act == "gelu_tanh" else "none")
+    xd, bd, rd = _cuda(x.reshape(N, I), bias, res)
+    P, Q = I // b, O // b
+    got = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, [bd], None, act)
+    assert got is not None and _err(got[0], gelu(lin + bias.float())) < TOL
+    if 64 < N <= 512:
+        got = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, [bd], [rd], act)
+        assert got is not None and _err(got[0], gelu(lin + bias.float()) + res.float()) < TOL
+    no_bias = ops.blast_multi(xd, layers, bits, 0, b, P, Q, R, None, None, None, act)
+    assert no_bias is not None and _err(no_bias[0], gelu(lin)) < TOL
+    # the reference-facing wrapper, also at a decode size (torch's activation there)
+    wrap = (lambda t: K.bk.blast_multi_torch_layout(t, layers, biases=[bd], out_act=act)[0]) if bits == 16 else \
+        (lambda t: K.bq.blast_wq_multi(t, layers, bits, 0, biases=[bd], out_act=act)[0])
+    assert _err(wrap(xd), gelu(lin + bias.float())) < TOL
+    assert _err(wrap(xd[:5]), gelu(lin[:5] + bias.float())) < TOL
