@@ -359,6 +359,43 @@ def dit_leg(dev, rank, world, dist, quick):
     return out
 
 
+def network_step_case(case, dev):
+    """Small case for a profiler launch list of one network step: 'step:llama:BATCH[:METHOD]' (four decoder layers, one
+    decode step against a full 2048-token cache), 'step:vit:BATCH' and 'step:dit:BATCH' (four layers, one forward).
+    Three warm-up steps, then one step between cudaProfilerStart / Stop (ncu --profile-from-start off)."""
+    from mem_efficient_blr_b200 import networks as nw, _lib
+    parts = case.split(":")
+    kind, B = parts[1], int(parts[2])
+    if kind == "llama":
+        shape = nw.LlamaShape(layers=4)
+        model = nw.LlamaDecoder(shape, parts[3] if len(parts) > 3 else "blast", batch=B, cache_len=2048, device=dev,
+                                dtype=torch.float16, seed=0, init_on_device=True)
+        ids, pos = torch.randint(0, shape.vocab, (B, 1), device=dev), torch.tensor([2047], device=dev)
+        step = lambda: model.decode_step(ids, pos)
+    elif kind == "vit":
+        shape = nw.ViTShape(layers=4)
+        model = nw.ViTEncoder(shape, "blast", device=dev, dtype=torch.float16, seed=0, init_on_device=True)
+        img = torch.randn(B, 3, shape.image, shape.image, device=dev, dtype=torch.float16)
+        step = lambda: model(img)
+    elif kind == "dit":
+        shape = nw.DiTShape(layers=4)
+        model = nw.DiTDenoiser(shape, "blast", device=dev, dtype=torch.float16, seed=0, init_on_device=True)
+        lat = torch.randn(B, shape.channels, shape.latent, shape.latent, device=dev, dtype=torch.float16)
+        t, y = torch.randint(0, 1000, (B,), device=dev), torch.randint(0, shape.classes, (B,), device=dev)
+        step = lambda: model(lat, t, y)
+    else:
+        raise SystemExit(f"unknown network case {case!r}")
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    _lib.workspace_status(dev)
+    print(json.dumps({"ncu_case": case, "steps": 1}))
+
+
 def sharding_leg(dev, rank, world, dist):
     """BLAST sharded by output block over the ranks (gate_proj shape with the 50 %-parameter rank): every rank holds
     b / world blocks of U and S and all of V, computes its columns, and one NCCL all_gather along the feature axis
@@ -487,6 +524,10 @@ def run_ours(args):
     import mem_efficient_blr_b200.blast_kernels as bk
     import mem_efficient_blr_b200.blast_sym_quant_kernels as bq
     from mem_efficient_blr_b200 import _lib
+
+    if args.ncu_case.startswith("step:"):
+        network_step_case(args.ncu_case, dev)
+        return
 
     # ---- synthetic factors with the headline configuration's distributions:
     # U, Vt ~ N(0, 1/sqrt(fan_in)), S ~ U(0.5, 1.5), x ~ N(0, 1), fp16, seeded per rank
@@ -713,7 +754,9 @@ def main():
     ap.add_argument("--no-context", action="store_true", help="headline only: skip the layer sweep, the networks and the sharding leg")
     ap.add_argument("--quick", action="store_true", help="smaller network legs (4 decoder layers, fewer batch sizes) and a two-point layer sweep")
     ap.add_argument("--ncu-case", default="", help="BITS:TOKENS, e.g. 8:16 - run six eager calls of one point and exit (for profiler captures); "
-                                                  "p16:TOKENS - three calls of the 16-bit layer on that many tokens")
+                                                  "p16:TOKENS - three calls of the 16-bit layer on that many tokens; "
+                                                  "step:llama:BATCH[:METHOD] | step:vit:BATCH | step:dit:BATCH - one step of a "
+                                                  "four-layer network between cudaProfilerStart / Stop")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

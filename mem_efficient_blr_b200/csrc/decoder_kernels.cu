@@ -87,11 +87,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
 // out[r][:] = (x[r][:] - mean) * rsqrt(var + eps) * w[:] + b[:]  (w, b optional; per group of rows_per_group rows when
 // that is set, and 1 + w in place of w with w_plus_one: adaLN modulation).  A warp per row, the row in registers
 // (up to 8 pieces of 8 values per lane: d <= 2048, d % 8 == 0), mean and variance in two passes over the registers.
-template <bool BF16>
-__global__ void __launch_bounds__(256) layernorm_kernel(const uint16_t* __restrict__ x, long long ldx, const uint16_t* __restrict__ w,
-                                                        const uint16_t* __restrict__ b, float eps, int d, long long rows,
-                                                        uint16_t* __restrict__ out, long long ldo, long long rows_per_group,
-                                                        long long ldw, long long ldb, int w_plus_one) {
+template <bool BF16, int NP, int MINB>
+__global__ void __launch_bounds__(256, MINB) layernorm_kernel(const uint16_t* __restrict__ x, long long ldx, const uint16_t* __restrict__ w,
+                                                              const uint16_t* __restrict__ b, float eps, int d, long long rows,
+                                                              uint16_t* __restrict__ out, long long ldo, long long rows_per_group,
+                                                              long long ldw, long long ldb, int w_plus_one) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -104,65 +104,60 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const uint16_t* __restri
   const float w_add = w_plus_one ? 1.f : 0.f;
   const int lane = threadIdx.x & 31, pieces = d >> 3;
   const uint16_t* xr = x + r * ldx;
-  float v[8][8];
+  // The row stays packed (NP 16-byte pieces per lane) so that enough warps fit an SM to keep the loads of several rows
+  // in flight while others reduce and store; the three passes widen it again.
+  uint4 t[NP];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int p = lane + 32 * i;
+    t[i] = p < pieces ? *reinterpret_cast<const uint4*>(xr + p * 8) : make_uint4(0, 0, 0, 0);
+  }
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int p = lane + 32 * i;
-    if (p < pieces) {
-      const uint4 t = *reinterpret_cast<const uint4*>(xr + p * 8);
-      const uint32_t ws[4] = {t.x, t.y, t.z, t.w};
+  for (int i = 0; i < NP; ++i) {
+    const uint32_t ws[4] = {t[i].x, t[i].y, t[i].z, t[i].w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = up2<BF16>(ws[k]);
-        v[i][2 * k] = f.x;
-        v[i][2 * k + 1] = f.y;
-        sum += f.x + f.y;
-      }
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = up2<BF16>(ws[k]);
+      sum += f.x + f.y;
     }
   }
   const float mean = warp_sum(sum) / (float)d;
   float sq = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < NP; ++i)
     if (lane + 32 * i < pieces) {
+      const uint32_t ws[4] = {t[i].x, t[i].y, t[i].z, t[i].w};
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float c = v[i][k] - mean;
-        sq = fmaf(c, c, sq);
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = up2<BF16>(ws[k]);
+        const float c0 = f.x - mean, c1 = f.y - mean;
+        sq = fmaf(c0, c0, sq);
+        sq = fmaf(c1, c1, sq);
       }
     }
   const float inv = rsqrtf(warp_sum(sq) / (float)d + eps);
   uint16_t* orow = out + r * ldo;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < NP; ++i) {
     const int p = lane + 32 * i;
     if (p < pieces) {
-      float g[8], h[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) g[k] = 1.f, h[k] = 0.f;
-      if (w != nullptr) {
-        const uint4 t = *reinterpret_cast<const uint4*>(w + p * 8);
-        const uint32_t ws[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 f = up2<BF16>(ws[k]);
-          g[2 * k] = f.x + w_add, g[2 * k + 1] = f.y + w_add;
-        }
-      }
-      if (b != nullptr) {
-        const uint4 t = *reinterpret_cast<const uint4*>(b + p * 8);
-        const uint32_t ws[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 f = up2<BF16>(ws[k]);
-          h[2 * k] = f.x, h[2 * k + 1] = f.y;
-        }
-      }
+      uint4 gw = make_uint4(0, 0, 0, 0), hb = make_uint4(0, 0, 0, 0);
+      if (w != nullptr) gw = *reinterpret_cast<const uint4*>(w + p * 8);
+      if (b != nullptr) hb = *reinterpret_cast<const uint4*>(b + p * 8);
+      const uint32_t ws[4] = {t[i].x, t[i].y, t[i].z, t[i].w}, gs[4] = {gw.x, gw.y, gw.z, gw.w}, hs[4] = {hb.x, hb.y, hb.z, hb.w};
       uint32_t o[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        o[k] = down2<BF16>(fmaf((v[i][2 * k] - mean) * inv, g[2 * k], h[2 * k]), fmaf((v[i][2 * k + 1] - mean) * inv, g[2 * k + 1], h[2 * k + 1]));
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = up2<BF16>(ws[k]);
+        float2 g = make_float2(1.f, 1.f), h = make_float2(0.f, 0.f);
+        if (w != nullptr) {
+          g = up2<BF16>(gs[k]);
+          g.x += w_add, g.y += w_add;
+        }
+        if (b != nullptr) h = up2<BF16>(hs[k]);
+        o[k] = down2<BF16>(fmaf((f.x - mean) * inv, g.x, h.x), fmaf((f.y - mean) * inv, g.y, h.y));
+      }
       *reinterpret_cast<uint4*>(orow + p * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
@@ -466,9 +461,12 @@ int blr_layernorm(const void* x, int64_t ldx, int64_t rows, int d, const void* w
   uint16_t* op = static_cast<uint16_t*>(out);
   const long long lx = ldx, lo = ldo, nr = rows, rpg = rows_per_group, lw = ldw, lb = ldb;
   const dim3 grid((unsigned)((rows + 7) / 8));
-  if (dtype == BLR_DTYPE_BF16)
-    return launch_pdl(layernorm_kernel<true>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo, rpg, lw, lb, weight_plus_one);
-  return launch_pdl(layernorm_kernel<false>, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo, rpg, lw, lb, weight_plus_one);
+  auto go = [&](auto kernel) { return launch_pdl(kernel, grid, dim3(256), 0, st, xp, lx, wp, bp, eps, d, nr, op, lo, rpg, lw, lb, weight_plus_one); };
+  const bool bf = dtype == BLR_DTYPE_BF16;
+  // pieces per lane by width: 3 (d <= 768), 5 (<= 1280), 8 (<= 2048), each with the occupancy its registers allow
+  if (d <= 768) return bf ? go(layernorm_kernel<true, 3, 5>) : go(layernorm_kernel<false, 3, 5>);
+  if (d <= 1280) return bf ? go(layernorm_kernel<true, 5, 4>) : go(layernorm_kernel<false, 5, 4>);
+  return bf ? go(layernorm_kernel<true, 8, 3>) : go(layernorm_kernel<false, 8, 3>);
 }
 
 int blr_rope_append(void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const float* cos_table,
